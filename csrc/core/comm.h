@@ -1,0 +1,172 @@
+// Communicator: everything the operator layer needs from "below" (HCCL's hcomm contract: identity, CCL buffer,
+// peer-addressable memory, keyed engine contexts, threads/streams, channels = flag slots, rank graph, and the
+// exchange-info side channel; reference call sites: src/ops/op_common/op_common.cc:951-970,1338,1616,1655).
+#pragma once
+#include <atomic>
+#include <condition_variable>
+#include <deque>
+#include <functional>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <thread>
+#include <unordered_map>
+#include <vector>
+#include "../common/env_config.h"
+#include "../topo/topo_info.h"
+#include "bootstrap.h"
+#include "dev_comm.h"
+#include "hccl/hccl_comm.h"
+
+namespace hccl {
+
+enum class BackendKind : uint8_t { SIM = 1, CUDA = 2 };
+
+// Keyed blobs per communicator (HcclEngineCtxCreate/Get/Copy/Destroy in HCCL): caches for topology results,
+// resource contexts and launch plans, on the host or in device memory.
+struct EngineCtxBlob {
+    std::vector<uint8_t> host;
+    void *dev = nullptr;
+    uint64_t devBytes = 0;
+};
+
+// Cross-rank parameter consistency record (reference: alg_param.h:695-706 OpExchangeInfo).
+struct OpExchangeInfo {
+    uint64_t cclBufferSize;
+    uint32_t root;
+    uint32_t opType;
+    uint32_t engine;
+    uint32_t reduceOp;
+    uint32_t dataType;
+    uint32_t pad;
+    uint64_t count;
+    uint32_t ctaLimit;
+    char group[128];
+    char algName[128];
+    char tag[128];
+};
+
+// Last-op registry entry and counters (DFX).
+struct OpRecord {
+    uint64_t seq;
+    HcclCMDType opType;
+    HcclDataType dtype;
+    HcclReduceOp reduceOp;
+    uint64_t count;
+    uint32_t root;
+    uint32_t engine;
+    char algName[64];
+    uint64_t beginNs, endNs;     // host timestamps around the enqueue
+};
+
+struct CommCounters {
+    std::atomic<uint64_t> ops{0}, bytes{0}, timeouts{0}, planCacheHits{0}, planCacheMisses{0}, fallbacks{0},
+        consistencyChecks{0}, chunkLoops{0}, kernelsLaunched{0};
+    std::mutex mu;
+    std::map<std::string, uint64_t> algoHistogram;
+};
+
+struct SymAllocBlock { uint64_t off, bytes; bool used; };
+
+class SimWorker;   // ordered async queue that plays the role of a stream for the host backend
+
+struct Comm {
+    uint32_t rank = 0, nranks = 1;
+    std::string name;                // group name
+    uint64_t commId = 0;
+    BackendKind backend = BackendKind::SIM;
+    int device = -1;
+    HcclCommConfig config{};
+    AlgEnvConfig env;                // snapshot with per-comm overrides applied
+    std::unique_ptr<Bootstrap> boot;
+    TopoInfo topo;
+    std::atomic<int> status{HCCL_COMM_STATUS_READY};
+
+    // symmetric heap
+    uint64_t heapBytes = 0;
+    std::vector<char *> heap;        // heap[r] mapped locally; heap[rank] is this rank's own
+    char *mcHeap = nullptr;          // NVLS multicast mapping or nullptr
+    DevComm devComm{};               // host copy
+    DevComm *devCommPtr = nullptr;   // device copy (CUDA) or == &devComm (sim)
+    DevStatus *hostStatus = nullptr; // pinned, device-mapped (CUDA) / plain (sim)
+    void *backendState = nullptr;    // CudaHeapState* / SimHeapState*
+    std::vector<SymAllocBlock> arena;
+    std::mutex arenaMu;
+
+    // host-engine notify bookkeeping and op parity (sim backend keeps them on the host side of the heap)
+    uint64_t opSeq = 0;
+    std::unique_ptr<SimWorker> worker;
+
+    // caches
+    std::mutex ctxMu;
+    std::unordered_map<std::string, EngineCtxBlob> engineCtx;
+    std::unordered_map<std::string, int> stickyFallback;      // algTag -> engine that finally worked
+    std::unordered_map<std::string, bool> consistencyDone;    // algTag -> checked
+
+    // DFX
+    CommCounters counters;
+    std::mutex opRingMu;
+    std::deque<OpRecord> opRing;     // last 64 ops
+    std::thread watchdog;
+    std::atomic<bool> watchdogStop{false};
+    std::atomic<int> remoteErrorRank{-1}, deadRank{-1};
+    std::vector<std::function<void(int)>> stateCallbacks;
+
+    // sub-communicators keep their parent's bootstrap alive
+    Comm *parent = nullptr;
+    bool destroyed = false;
+};
+
+// ---- lifecycle (comm.cc)
+HcclResult CommCreate(uint32_t nranks, const HcclRootInfo *info, uint32_t rank, const HcclCommConfig *cfg, Comm **out);
+HcclResult CommDestroy(Comm *c);
+Comm *CommFromHandle(HcclComm h);       // validates the handle (nullptr on garbage)
+HcclResult CommCheckReady(Comm *c);     // SUCCESS or HCCL_E_SUSPENDING; also folds in async device errors
+HcclResult CommSuspend(Comm *c);
+HcclResult CommResume(Comm *c);
+HcclResult CommPollAsyncError(Comm *c, HcclResult *asyncErr);
+
+// ---- engine-context store
+HcclResult EngineCtxCreate(Comm *c, const std::string &tag, bool onDevice, uint64_t bytes, void **ptr);
+HcclResult EngineCtxGet(Comm *c, const std::string &tag, bool onDevice, void **ptr, uint64_t *bytes);
+HcclResult EngineCtxCopy(Comm *c, const std::string &tag, const void *src, uint64_t bytes);  // host -> device blob
+HcclResult EngineCtxDestroy(Comm *c, const std::string &tag);
+
+// ---- symmetric arena
+HcclResult SymAlloc(Comm *c, uint64_t bytes, void **ptr);
+HcclResult SymFree(Comm *c, void *ptr);
+bool SymContains(Comm *c, const void *ptr, uint64_t bytes);
+uint64_t SymOffsetOf(Comm *c, const void *ptr);
+
+// ---- backend hooks (backend_sim.cc / backend_cuda.cc)
+HcclResult SimBackendInit(Comm *c);
+void SimBackendDestroy(Comm *c);
+HcclResult CudaBackendInit(Comm *c);
+void CudaBackendDestroy(Comm *c);
+HcclResult CudaBackendResetFlags(Comm *c);
+bool CudaDeviceAvailable(int *currentDevice);
+
+// ---- DFX
+void RecordOp(Comm *c, const OpRecord &r);
+void StartWatchdog(Comm *c);
+void StopWatchdog(Comm *c);
+
+// Sim stream: ordered async execution
+class SimWorker {
+public:
+    SimWorker();
+    ~SimWorker();
+    void Enqueue(std::function<HcclResult()> fn);
+    HcclResult Drain();                 // waits; returns the first error since the previous Drain
+private:
+    void Run();
+    std::thread th_;
+    std::mutex mu_;
+    std::condition_variable cv_, idleCv_;
+    std::deque<std::function<HcclResult()>> q_;
+    bool stop_ = false, busy_ = false;
+    HcclResult firstErr_ = HCCL_SUCCESS;
+};
+
+}  // namespace hccl

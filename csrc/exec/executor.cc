@@ -1,0 +1,495 @@
+#include "executor.h"
+#include <algorithm>
+#include <sstream>
+#include "../common/dtype.h"
+#include "../common/log.h"
+#include "../kernels/launch.h"
+#include "copy_engine.h"
+#include "host_engine.h"
+
+namespace hccl {
+
+uint64_t OpParam::DataBytes() const
+{
+    uint64_t es = DataTypeSize(dtype);
+    switch (opType) {
+        case HCCL_CMD_ALLTOALLV: case HCCL_CMD_ALLTOALLVC: case HCCL_CMD_ALLGATHER_V: case HCCL_CMD_REDUCE_SCATTER_V: {
+            uint64_t tot = 0;
+            for (uint64_t c : (sendCounts.empty() ? recvCounts : sendCounts)) tot += c;
+            return tot * es;
+        }
+        case HCCL_CMD_BATCH_SEND_RECV: {
+            uint64_t tot = 0;
+            for (auto &it : items) tot += it.count * DataTypeSize(it.dataType);
+            return tot;
+        }
+        default: return count * es;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ registry
+ExecutorRegistry &ExecutorRegistry::Instance()
+{
+    static ExecutorRegistry r;
+    return r;
+}
+void ExecutorRegistry::Register(const std::string &algName, HcclCMDType op, std::function<ExecutorBase *()> factory)
+{
+    map_[{(int)op, algName}] = std::move(factory);
+}
+std::unique_ptr<ExecutorBase> ExecutorRegistry::Create(HcclCMDType op, const std::string &algName) const
+{
+    auto it = map_.find({(int)op, algName});
+    if (it == map_.end()) return nullptr;
+    std::unique_ptr<ExecutorBase> e(it->second());
+    e->SetAlgName(algName);
+    return e;
+}
+std::vector<std::string> ExecutorRegistry::Names(HcclCMDType op) const
+{
+    std::vector<std::string> v;
+    for (auto &kv : map_) if (kv.first.first == (int)op) v.push_back(kv.first.second);
+    return v;
+}
+bool ExecutorRegistry::Has(HcclCMDType op, const std::string &algName) const { return map_.count({(int)op, algName}) != 0; }
+
+HcclResult ExecutorBase::CalcRes(Comm *c, const OpParam &p, AlgResourceRequest *req)
+{
+    req->scratchBytes = std::min<uint64_t>(c->devComm.cclBytes, p.DataBytes() * c->nranks + (64u << 10));
+    req->slaveStreams = 0;
+    req->notifyPerPeer = 4;
+    req->ctas = 0;
+    req->taskCount = 1;
+    return HCCL_SUCCESS;
+}
+
+// ------------------------------------------------------------------------------------------------ plan cache
+namespace {
+std::mutex g_pcMu;
+std::map<Comm *, std::unique_ptr<PlanCache>> g_planCaches;
+}
+PlanCache &PlanCache::Of(Comm *c)
+{
+    std::lock_guard<std::mutex> lk(g_pcMu);
+    auto &p = g_planCaches[c];
+    if (!p) p.reset(new PlanCache());
+    return *p;
+}
+void PlanCache::Drop(Comm *c)
+{
+    std::lock_guard<std::mutex> lk(g_pcMu);
+    g_planCaches.erase(c);
+}
+std::shared_ptr<const Plan> PlanCache::Find(const std::string &key)
+{
+    std::lock_guard<std::mutex> lk(mu_);
+    auto it = map_.find(key);
+    return it == map_.end() ? nullptr : it->second;
+}
+void PlanCache::Insert(const std::string &key, std::shared_ptr<const Plan> plan)
+{
+    std::lock_guard<std::mutex> lk(mu_);
+    if (map_.size() >= kCapacity) {
+        size_t evict = kCapacity / 5;
+        while (evict-- && !order_.empty()) { map_.erase(order_.front()); order_.pop_front(); }
+    }
+    if (map_.emplace(key, std::move(plan)).second) order_.push_back(key);
+}
+
+// ------------------------------------------------------------------------------------------------ chunking
+static uint64_t Clamp(uint64_t total, uint64_t lo, uint64_t chunk) { return total <= lo ? 0 : std::min(chunk, total - lo); }
+
+HcclResult BuildFlatChunks(const OpParam &p, uint32_t rank, uint32_t nranks, uint64_t cclBytes, const IrTemplate &tmpl,
+                           std::vector<TemplateCtx> *chunks)
+{
+    uint32_t es = DataTypeSize(p.dtype);
+    TemplateCtx base;
+    base.group.resize(nranks);
+    for (uint32_t r = 0; r < nranks; ++r) base.group[r] = r;
+    base.me = rank;
+    base.elemSize = es ? es : 1;
+    base.cclOff = 0;
+    base.cclBytes = cclBytes;
+    base.root = p.root;
+    base.inPlace = p.inputPtr == p.outputPtr;
+    uint64_t maxCount = tmpl.maxCountPerLoop ? tmpl.maxCountPerLoop(nranks, base.elemSize, cclBytes) : 0;
+
+    auto pushRange = [&](uint64_t total, const std::function<void(TemplateCtx &, uint64_t lo, uint64_t n)> &fill) {
+        if (total == 0 || maxCount == 0) { TemplateCtx c = base; fill(c, 0, total); chunks->push_back(std::move(c)); return; }
+        for (uint64_t lo = 0; lo < total; lo += maxCount) {
+            TemplateCtx c = base;
+            fill(c, lo, std::min(maxCount, total - lo));
+            chunks->push_back(std::move(c));
+        }
+    };
+
+    switch (p.opType) {
+        case HCCL_CMD_ALLREDUCE: case HCCL_CMD_REDUCE:
+            pushRange(p.count, [&](TemplateCtx &c, uint64_t lo, uint64_t n) {
+                c.count = n; c.in = {BufKind::INPUT, lo * es}; c.out = {BufKind::OUTPUT, lo * es};
+            });
+            break;
+        case HCCL_CMD_BROADCAST:
+            pushRange(p.count, [&](TemplateCtx &c, uint64_t lo, uint64_t n) {
+                c.count = n; c.in = {BufKind::OUTPUT, lo * es}; c.out = {BufKind::OUTPUT, lo * es}; c.inPlace = true;
+            });
+            break;
+        case HCCL_CMD_ALLGATHER:
+            pushRange(p.count, [&](TemplateCtx &c, uint64_t lo, uint64_t n) {
+                c.count = n; c.in = {BufKind::INPUT, lo * es}; c.out = {BufKind::OUTPUT, lo * es}; c.outStride = p.count * es;
+                c.inPlace = (const char *)p.inputPtr == (const char *)p.outputPtr + (uint64_t)rank * p.count * es;
+            });
+            break;
+        case HCCL_CMD_REDUCE_SCATTER: case HCCL_CMD_SCATTER:
+            pushRange(p.count, [&](TemplateCtx &c, uint64_t lo, uint64_t n) {
+                c.count = n; c.in = {BufKind::INPUT, lo * es}; c.out = {BufKind::OUTPUT, lo * es}; c.inStride = p.count * es; c.inPlace = false;
+            });
+            break;
+        case HCCL_CMD_ALLTOALL:
+            pushRange(p.count, [&](TemplateCtx &c, uint64_t lo, uint64_t n) {
+                c.count = n; c.in = {BufKind::INPUT, lo * es}; c.out = {BufKind::OUTPUT, lo * es};
+                c.inStride = p.count * es; c.outStride = p.count * es; c.inPlace = false;
+            });
+            break;
+        case HCCL_CMD_ALLGATHER_V: {
+            if (p.recvCounts.size() != nranks || p.recvDispls.size() != nranks) return HCCL_E_PARA;
+            uint64_t mx = *std::max_element(p.recvCounts.begin(), p.recvCounts.end());
+            pushRange(mx, [&](TemplateCtx &c, uint64_t lo, uint64_t n) {
+                c.count = n; c.in = {BufKind::INPUT, lo * es}; c.out = {BufKind::OUTPUT, 0};
+                c.recvBytes.resize(nranks); c.recvOff.resize(nranks);
+                for (uint32_t r = 0; r < nranks; ++r) { c.recvBytes[r] = Clamp(p.recvCounts[r], lo, n) * es; c.recvOff[r] = (p.recvDispls[r] + lo) * es; }
+                c.inPlace = false;
+            });
+            break;
+        }
+        case HCCL_CMD_REDUCE_SCATTER_V: {
+            if (p.sendCounts.size() != nranks || p.sendDispls.size() != nranks) return HCCL_E_PARA;
+            uint64_t mx = *std::max_element(p.sendCounts.begin(), p.sendCounts.end());
+            pushRange(mx, [&](TemplateCtx &c, uint64_t lo, uint64_t n) {
+                c.count = n; c.in = {BufKind::INPUT, 0}; c.out = {BufKind::OUTPUT, lo * es};
+                c.sendBytes.resize(nranks); c.sendOff.resize(nranks);
+                for (uint32_t r = 0; r < nranks; ++r) { c.sendBytes[r] = Clamp(p.sendCounts[r], lo, n) * es; c.sendOff[r] = (p.sendDispls[r] + lo) * es; }
+                c.inPlace = false;
+            });
+            break;
+        }
+        case HCCL_CMD_ALLTOALLV: case HCCL_CMD_ALLTOALLVC: {
+            if (p.sendCounts.size() != nranks || p.recvCounts.size() != nranks) return HCCL_E_PARA;
+            TemplateCtx c = base;
+            uint32_t esOut = DataTypeSize(p.outDtype);
+            c.in = {BufKind::INPUT, 0}; c.out = {BufKind::OUTPUT, 0}; c.inPlace = false;
+            c.sendBytes.resize(nranks); c.sendOff.resize(nranks); c.recvBytes.resize(nranks); c.recvOff.resize(nranks);
+            for (uint32_t r = 0; r < nranks; ++r) {
+                c.sendBytes[r] = p.sendCounts[r] * es; c.sendOff[r] = p.sendDispls[r] * es;
+                c.recvBytes[r] = p.recvCounts[r] * esOut; c.recvOff[r] = p.recvDispls[r] * esOut;
+            }
+            chunks->push_back(std::move(c));
+            break;
+        }
+        case HCCL_CMD_BARRIER: { TemplateCtx c = base; chunks->push_back(std::move(c)); break; }
+        default: return HCCL_E_NOT_SUPPORT;
+    }
+    return HCCL_SUCCESS;
+}
+
+static std::string PlanKey(const std::string &alg, const TemplateCtx &c, const OpParam &p)
+{
+    std::ostringstream os;
+    os << alg << '|' << c.count << '|' << (int)p.dtype << '|' << (int)p.reduceOp << '|' << c.root << '|' << c.inPlace << '|' << c.in.off << '|'
+       << c.out.off << '|' << c.inStride << '|' << c.outStride << '|' << c.N();
+    for (auto *v : {&c.sendBytes, &c.sendOff, &c.recvBytes, &c.recvOff}) { os << '|'; for (uint64_t x : *v) os << x << ','; }
+    return os.str();
+}
+
+// Runs one plan on the communicator's engine. Sim: queued on the worker. CUDA: issued on the stream.
+static HcclResult RunPlan(Comm *c, const OpParam &p, std::shared_ptr<const Plan> plan, bool usesCclHalf)
+{
+    ExecBuffers bufs;
+    bufs.in = (char *)p.inputPtr;
+    bufs.out = (char *)p.outputPtr;
+    bufs.cclHalf = usesCclHalf ? (uint32_t)(c->opSeq++ & 1) : 0;
+    c->counters.chunkLoops++;
+    if (c->backend == BackendKind::SIM) {
+        c->worker->Enqueue([c, plan, bufs] { return HostEngineRun(c, *plan, bufs); });
+        return HCCL_SUCCESS;
+    }
+    return CopyEngineRun(c, *plan, bufs, p.stream);
+}
+
+// ------------------------------------------------------------------------------------------------ IR sole executor
+class IrSoleExecutor : public ExecutorBase {
+public:
+    HcclResult Orchestrate(Comm *c, OpParam &p) override
+    {
+        RegisterBuiltinIrTemplates();
+        const IrTemplate *t = IrTemplateRegistry::Instance().Find(algName_);
+        if (!t) { HCCL_ERROR("no IR template named %s", algName_.c_str()); return HCCL_E_NOT_FOUND; }
+        std::vector<TemplateCtx> chunks;
+        CHK_RET(BuildFlatChunks(p, c->rank, c->nranks, c->devComm.cclBytes, *t, &chunks));
+        PlanCache &cache = PlanCache::Of(c);
+        for (const TemplateCtx &ctx : chunks) {
+            std::string key = PlanKey(algName_, ctx, p);
+            std::shared_ptr<const Plan> plan = cache.Find(key);
+            if (plan) c->counters.planCacheHits++;
+            else {
+                c->counters.planCacheMisses++;
+                auto fresh = std::make_shared<Plan>();
+                fresh->dtype = p.dtype;
+                fresh->op = p.reduceOp;
+                CHK_RET(t->gen(ctx, fresh.get()));
+                plan = fresh;
+                cache.Insert(key, plan);
+            }
+            CHK_RET(RunPlan(c, p, plan, true));
+        }
+        return HCCL_SUCCESS;
+    }
+    HcclResult CalcRes(Comm *c, const OpParam &p, AlgResourceRequest *req) override
+    {
+        RegisterBuiltinIrTemplates();
+        const IrTemplate *t = IrTemplateRegistry::Instance().Find(algName_);
+        if (!t) return HCCL_E_NOT_FOUND;
+        std::vector<TemplateCtx> chunks;
+        CHK_RET(BuildFlatChunks(p, c->rank, c->nranks, c->devComm.cclBytes, *t, &chunks));
+        req->taskCount = 0;
+        for (auto &ctx : chunks) { Plan pl; CHK_RET(t->gen(ctx, &pl)); req->taskCount += pl.TaskCount(); }
+        req->scratchBytes = c->devComm.cclBytes;
+        req->slaveStreams = 0;
+        req->notifyPerPeer = kNotifySlots;
+        return HCCL_SUCCESS;
+    }
+};
+
+// ------------------------------------------------------------------------------------------------ p2p plans
+HcclResult GenSendPlan(uint32_t, uint32_t dst, uint64_t bytes, uint64_t W, Plan *p, size_t queue, BufRef src)
+{
+    p->EnsureQueues(queue + 1);
+    auto &q = p->queues[queue];
+    uint64_t rounds = (bytes + W - 1) / W;
+    for (uint64_t k = 0; k < rounds; ++k) {
+        if (k >= 2) q.push_back(Task{TaskType::WAIT, dst, 9, {}, {}, 0});
+        uint64_t len = std::min(W, bytes - k * W);
+        BufRef s = src;
+        s.off += k * W;
+        q.push_back(Task{TaskType::LOCAL_COPY, 0, 0, BufRef{BufKind::MAILBOX, ((uint64_t)dst * 2 + (k & 1)) * W}, s, len});
+        q.push_back(Task{TaskType::POST, dst, 8, {}, {}, 0});
+    }
+    for (uint64_t k = 0; k < std::min<uint64_t>(rounds, 2); ++k) q.push_back(Task{TaskType::WAIT, dst, 9, {}, {}, 0});
+    return HCCL_SUCCESS;
+}
+
+HcclResult GenRecvPlan(uint32_t me, uint32_t src, uint64_t bytes, uint64_t W, Plan *p, size_t queue, BufRef dst)
+{
+    p->EnsureQueues(queue + 1);
+    auto &q = p->queues[queue];
+    uint64_t rounds = (bytes + W - 1) / W;
+    for (uint64_t k = 0; k < rounds; ++k) {
+        q.push_back(Task{TaskType::WAIT, src, 8, {}, {}, 0});
+        uint64_t len = std::min(W, bytes - k * W);
+        BufRef d = dst;
+        d.off += k * W;
+        q.push_back(Task{TaskType::READ, src, 0, d, BufRef{BufKind::MAILBOX, ((uint64_t)me * 2 + (k & 1)) * W}, len});
+        q.push_back(Task{TaskType::POST, src, 9, {}, {}, 0});
+    }
+    return HCCL_SUCCESS;
+}
+
+// Items are ordered the way HCCL orders them for deadlock freedom (sends by descending, receives by ascending
+// ring distance, ties by count then dtype; reference: ins_v2_batch_send_recv_executor.cc:106-206), self pairs
+// are matched and turned into local copies (:80-104), and every (peer, direction) pair gets its own queue so
+// unrelated pairs never wait for each other.
+HcclResult GenBatchSendRecvPlan(uint32_t me, uint32_t nranks, const std::vector<HcclSendRecvItem> &items, uint64_t W, Plan *p,
+                                std::vector<char *> *)
+{
+    std::vector<HcclSendRecvItem> sends, recvs, selfS, selfR;
+    for (auto &it : items) {
+        if (it.remoteRank >= nranks) return HCCL_E_PARA;
+        if (it.remoteRank == me) (it.sendRecvType == HCCL_SEND ? selfS : selfR).push_back(it);
+        else (it.sendRecvType == HCCL_SEND ? sends : recvs).push_back(it);
+    }
+    if (selfS.size() != selfR.size()) { HCCL_ERROR("BatchSendRecv: %zu self sends but %zu self receives", selfS.size(), selfR.size()); return HCCL_E_PARA; }
+    p->EnsureQueues(1);
+    for (size_t i = 0; i < selfS.size(); ++i) {
+        uint64_t sb = selfS[i].count * DataTypeSize(selfS[i].dataType), rb = selfR[i].count * DataTypeSize(selfR[i].dataType);
+        if (sb != rb) { HCCL_ERROR("BatchSendRecv: self pair %zu size mismatch (%llu vs %llu bytes)", i, (unsigned long long)sb, (unsigned long long)rb); return HCCL_E_PARA; }
+        if (sb) p->queues[0].push_back(Task{TaskType::LOCAL_COPY, 0, 0, BufRef{BufKind::ABS, (uint64_t)(uintptr_t)selfR[i].buf},
+                                            BufRef{BufKind::ABS, (uint64_t)(uintptr_t)selfS[i].buf}, sb});
+    }
+    auto keyOf = [&](uint32_t remote) { return remote <= me ? remote + nranks : remote; };
+    std::stable_sort(sends.begin(), sends.end(), [&](const HcclSendRecvItem &a, const HcclSendRecvItem &b) { return keyOf(a.remoteRank) > keyOf(b.remoteRank); });
+    std::stable_sort(recvs.begin(), recvs.end(), [&](const HcclSendRecvItem &a, const HcclSendRecvItem &b) { return keyOf(a.remoteRank) < keyOf(b.remoteRank); });
+    std::map<std::pair<uint32_t, int>, size_t> queueOf;
+    auto queueFor = [&](uint32_t peer, int dir) {
+        auto it = queueOf.find({peer, dir});
+        if (it != queueOf.end()) return it->second;
+        size_t q = queueOf.size() + 1;
+        queueOf[{peer, dir}] = q;
+        return q;
+    };
+    for (auto &it : sends) CHK_RET(GenSendPlan(me, it.remoteRank, it.count * DataTypeSize(it.dataType), W, p, queueFor(it.remoteRank, 0), BufRef{BufKind::ABS, (uint64_t)(uintptr_t)it.buf}));
+    for (auto &it : recvs) CHK_RET(GenRecvPlan(me, it.remoteRank, it.count * DataTypeSize(it.dataType), W, p, queueFor(it.remoteRank, 1), BufRef{BufKind::ABS, (uint64_t)(uintptr_t)it.buf}));
+    return HCCL_SUCCESS;
+}
+
+class IrP2pExecutor : public ExecutorBase {
+public:
+    HcclResult Orchestrate(Comm *c, OpParam &p) override
+    {
+        auto plan = std::make_shared<Plan>();
+        plan->dtype = p.dtype;
+        uint64_t W = c->devComm.mailboxBytes;
+        if (p.opType == HCCL_CMD_SEND) CHK_RET(GenSendPlan(c->rank, p.peer, p.DataBytes(), W, plan.get(), 0, BufRef{BufKind::INPUT, 0}));
+        else if (p.opType == HCCL_CMD_RECEIVE) CHK_RET(GenRecvPlan(c->rank, p.peer, p.DataBytes(), W, plan.get(), 0, BufRef{BufKind::OUTPUT, 0}));
+        else CHK_RET(GenBatchSendRecvPlan(c->rank, c->nranks, p.items, W, plan.get(), nullptr));
+        return RunPlan(c, p, plan, false);
+    }
+};
+
+// ------------------------------------------------------------------------------------------------ sequence executor
+namespace {
+struct LevelGroup { std::vector<uint32_t> ranks; uint32_t me; };
+
+const IrTemplate *Tmpl(const char *name)
+{
+    RegisterBuiltinIrTemplates();
+    return IrTemplateRegistry::Instance().Find(name);
+}
+uint64_t Al(uint64_t v) { return (v + 511) / 512 * 512; }
+}  // namespace
+
+HcclResult GenSequencePlan(const OpParam &p, const TopoInfo &topo, uint64_t cclBytes, Plan *plan)
+{
+    AlgHierarchyInfo h;
+    CHK_RET(TopoMatch(topo, TopoMatchKind::MULTI_LEVEL, &h));
+    if (h.levelRanks.size() < 2) return HCCL_E_NOT_SUPPORT;
+    uint32_t es = DataTypeSize(p.dtype);
+    const auto &g0 = h.levelRanks[0];
+    uint32_t n0 = (uint32_t)g0.size(), me0 = h.myIndex[0];
+    plan->dtype = p.dtype;
+    plan->op = p.reduceOp;
+    auto baseCtx = [&](uint32_t level) {
+        TemplateCtx c;
+        c.group = h.levelRanks[level];
+        c.me = h.myIndex[level];
+        c.elemSize = es;
+        return c;
+    };
+    if (p.opType == HCCL_CMD_ALLREDUCE) {
+        // level 0 reduce-scatter (uneven slices) -> all-reduce of my slice on every upper level -> level 0 all-gather
+        uint64_t per = (p.count + n0 - 1) / n0;
+        std::vector<uint64_t> len(n0), off(n0);
+        for (uint32_t j = 0; j < n0; ++j) { off[j] = std::min(p.count, per * j) * es; len[j] = Clamp(p.count, per * j, per) * es; }
+        uint64_t W0 = Al(per * es) * n0 + 4096;
+        uint64_t upperCount = len[me0] / es;
+        uint64_t W1 = 0;
+        for (size_t l = 1; l < h.levelRanks.size(); ++l) W1 = std::max<uint64_t>(W1, 4 * Al(per * es) + 65536);
+        uint64_t need = W0 + W1 * (h.levelRanks.size() - 1) + Al(per * es) + 4096;
+        if (need > cclBytes) { HCCL_ERROR("sequence all-reduce needs %llu bytes of scratch, have %llu (raise HCCL_BUFFSIZE)", (unsigned long long)need, (unsigned long long)cclBytes); return HCCL_E_MEMORY; }
+        TemplateCtx a = baseCtx(0);
+        a.in = {BufKind::INPUT, 0}; a.out = {BufKind::OUTPUT, off[me0]};
+        a.sendBytes = len; a.sendOff = off; a.cclOff = 0; a.cclBytes = W0;
+        CHK_RET(Tmpl("InsReduceScatterVMesh1D")->gen(a, plan));
+        uint64_t win = W0;
+        for (size_t l = 1; l < h.levelRanks.size(); ++l) {
+            TemplateCtx b = baseCtx((uint32_t)l);
+            b.count = upperCount; b.in = {BufKind::OUTPUT, off[me0]}; b.out = b.in; b.inPlace = true; b.cclOff = win; b.cclBytes = W1;
+            if (upperCount) CHK_RET(Tmpl("InsAllReduceNHR")->gen(b, plan));
+            win += W1;
+        }
+        TemplateCtx g = baseCtx(0);
+        g.in = {BufKind::OUTPUT, off[me0]}; g.out = {BufKind::OUTPUT, 0}; g.recvBytes = len; g.recvOff = off; g.cclOff = win; g.cclBytes = Al(per * es) + 4096;
+        CHK_RET(Tmpl("InsAllGatherVMesh1D")->gen(g, plan));
+        return HCCL_SUCCESS;
+    }
+    if (h.levelRanks.size() != 2) return HCCL_E_NOT_SUPPORT;
+    const auto &g1 = h.levelRanks[1];
+    uint32_t n1 = (uint32_t)g1.size();
+    uint64_t B = p.count * es, S = Al(B);
+    if (p.opType == HCCL_CMD_ALLGATHER) {
+        // level 1: gather my block across servers; level 0: one gather per server's block set
+        if (S * (1 + n1) + 8192 > cclBytes) return HCCL_E_MEMORY;
+        TemplateCtx a = baseCtx(1);
+        a.in = {BufKind::INPUT, 0}; a.out = {BufKind::OUTPUT, 0}; a.cclOff = 0; a.cclBytes = S + 4096;
+        a.recvBytes.assign(n1, B); a.recvOff.resize(n1);
+        for (uint32_t k = 0; k < n1; ++k) a.recvOff[k] = (uint64_t)g1[k] * B;
+        CHK_RET(Tmpl("InsAllGatherVMesh1D")->gen(a, plan));
+        for (uint32_t s = 0; s < n1; ++s) {
+            // the server that g1[s] belongs to: its level-0 group is {g1[s] - me0 + j}
+            uint32_t base = g1[s] - me0;
+            TemplateCtx b = baseCtx(0);
+            b.in = {BufKind::OUTPUT, (uint64_t)(base + me0) * B}; b.out = {BufKind::OUTPUT, 0};
+            b.cclOff = S + 4096 + (uint64_t)s * S; b.cclBytes = S;
+            b.recvBytes.assign(n0, B); b.recvOff.resize(n0);
+            for (uint32_t j = 0; j < n0; ++j) b.recvOff[j] = (uint64_t)(base + j) * B;
+            CHK_RET(Tmpl("InsAllGatherVMesh1D")->gen(b, plan));
+        }
+        return HCCL_SUCCESS;
+    }
+    if (p.opType == HCCL_CMD_REDUCE_SCATTER) {
+        // level 0: per server-block reduce-scatter into a work area; level 1: reduce-scatter of the n1 partials
+        uint64_t workOff = 0, win0 = Al(S * n1 + 4096), per0 = S * n0 + 4096, win1 = win0 + per0 * n1;
+        if (win1 + S * n1 + 4096 > cclBytes) return HCCL_E_MEMORY;
+        for (uint32_t s = 0; s < n1; ++s) {
+            uint32_t base = g1[s] - me0;
+            TemplateCtx a = baseCtx(0);
+            a.in = {BufKind::INPUT, 0}; a.out = {BufKind::CCL, workOff + (uint64_t)s * S};
+            a.sendBytes.assign(n0, B); a.sendOff.resize(n0);
+            for (uint32_t j = 0; j < n0; ++j) a.sendOff[j] = (uint64_t)(base + j) * B;
+            a.cclOff = win0 + per0 * s; a.cclBytes = per0;
+            CHK_RET(Tmpl("InsReduceScatterVMesh1D")->gen(a, plan));
+        }
+        TemplateCtx b = baseCtx(1);
+        b.count = p.count; b.in = {BufKind::CCL, workOff}; b.inStride = S; b.out = {BufKind::OUTPUT, 0}; b.cclOff = win1; b.cclBytes = S * n1 + 4096;
+        CHK_RET(Tmpl("InsReduceScatterMesh1D")->gen(b, plan));
+        return HCCL_SUCCESS;
+    }
+    return HCCL_E_NOT_SUPPORT;
+}
+
+class IrSequenceExecutor : public ExecutorBase {
+public:
+    HcclResult Orchestrate(Comm *c, OpParam &p) override
+    {
+        auto plan = std::make_shared<Plan>();
+        CHK_RET(GenSequencePlan(p, c->topo, c->devComm.cclBytes, plan.get()));
+        return RunPlan(c, p, plan, true);
+    }
+};
+
+// ------------------------------------------------------------------------------------------------ SM / NVLS executor
+class SmExecutor : public ExecutorBase {
+public:
+    HcclResult Orchestrate(Comm *c, OpParam &p) override
+    {
+        if (c->backend != BackendKind::CUDA) return HCCL_E_UNAVAIL;
+        return SmOrchestrate(c, p, algName_);
+    }
+    HcclResult CalcRes(Comm *c, const OpParam &p, AlgResourceRequest *req) override
+    {
+        ExecutorBase::CalcRes(c, p, req);
+        req->ctas = SmDefaultCtas(p.opType, algName_, p.DataBytes(), c->nranks);
+        return HCCL_SUCCESS;
+    }
+};
+
+void RegisterBuiltinExecutors()
+{
+    static std::once_flag once;
+    std::call_once(once, [] {
+        RegisterBuiltinIrTemplates();
+        auto &R = ExecutorRegistry::Instance();
+        for (int op = 1; op < (int)HCCL_CMD_MAX; ++op)
+            for (auto &nm : IrTemplateRegistry::Instance().Names((HcclCMDType)op))
+                R.Register(nm, (HcclCMDType)op, [] { return static_cast<ExecutorBase *>(new IrSoleExecutor()); });
+        R.Register("InsSend", HCCL_CMD_SEND, [] { return static_cast<ExecutorBase *>(new IrP2pExecutor()); });
+        R.Register("InsRecv", HCCL_CMD_RECEIVE, [] { return static_cast<ExecutorBase *>(new IrP2pExecutor()); });
+        R.Register("InsBatchSendRecv", HCCL_CMD_BATCH_SEND_RECV, [] { return static_cast<ExecutorBase *>(new IrP2pExecutor()); });
+        R.Register("InsAllReduceSequenceMesh1DNhr", HCCL_CMD_ALLREDUCE, [] { return static_cast<ExecutorBase *>(new IrSequenceExecutor()); });
+        R.Register("InsAllGatherSequenceNhrMesh1D", HCCL_CMD_ALLGATHER, [] { return static_cast<ExecutorBase *>(new IrSequenceExecutor()); });
+        R.Register("InsReduceScatterSequenceMesh1DNhr", HCCL_CMD_REDUCE_SCATTER, [] { return static_cast<ExecutorBase *>(new IrSequenceExecutor()); });
+        for (const SmAlgoDesc &d : SmAlgorithms())
+            R.Register(d.name, d.op, [] { return static_cast<ExecutorBase *>(new SmExecutor()); });
+    });
+}
+
+}  // namespace hccl

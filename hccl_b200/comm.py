@@ -1,0 +1,251 @@
+"""Python face of the C API: `Communicator` wraps an `HcclComm` handle and accepts torch tensors or numpy arrays.
+
+With CUDA tensors the ops are enqueued on `torch.cuda.current_stream()` (or the stream passed in); with host buffers the
+communicator runs on the simulation backend and `synchronize()` drains its worker queue.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Sequence
+
+from . import _lib
+from ._lib import HcclCommConfig, HcclRootInfo, HcclSendRecvItem, check, lib
+from .types import DataType, ReduceOp, from_numpy, from_torch
+
+
+def get_root_info() -> bytes:
+    info = HcclRootInfo()
+    check(lib().HcclGetRootInfo(ctypes.byref(info)), "HcclGetRootInfo")
+    return ctypes.string_at(ctypes.byref(info), _lib.HCCL_ROOT_INFO_BYTES)
+
+
+def _root_from_bytes(b: bytes) -> HcclRootInfo:
+    info = HcclRootInfo()
+    ctypes.memmove(ctypes.byref(info), b, _lib.HCCL_ROOT_INFO_BYTES)
+    return info
+
+
+def _describe(buf):
+    """-> (pointer, numel, DataType, is_cuda)"""
+    if buf is None:
+        return None, 0, DataType.INT8, False
+    if hasattr(buf, "data_ptr"):  # torch tensor
+        if not buf.is_contiguous():
+            raise ValueError("tensor must be contiguous")
+        return buf.data_ptr(), buf.numel(), from_torch(buf.dtype), buf.is_cuda
+    if hasattr(buf, "ctypes"):  # numpy
+        if not buf.flags["C_CONTIGUOUS"]:
+            raise ValueError("array must be C-contiguous")
+        return buf.ctypes.data, buf.size, from_numpy(buf.dtype), False
+    raise TypeError(f"unsupported buffer type {type(buf)}")
+
+
+def _u64_array(vals: Sequence[int]):
+    return (ctypes.c_uint64 * len(vals))(*[int(v) for v in vals])
+
+
+class Communicator:
+    def __init__(self, handle: int):
+        self._h = ctypes.c_void_p(handle)
+        r, n = ctypes.c_uint32(), ctypes.c_uint32()
+        check(lib().HcclGetRankId(self._h, ctypes.byref(r)), "HcclGetRankId")
+        check(lib().HcclGetRankSize(self._h, ctypes.byref(n)), "HcclGetRankSize")
+        self.rank, self.size = r.value, n.value
+
+    # ---- construction -------------------------------------------------------------------------------------
+    @classmethod
+    def from_root_info(cls, nranks: int, root_info: bytes, rank: int, *, buffer_mb: int = 0, backend: str = "auto",
+                       deterministic: Optional[int] = None, engine: int = 0, name: str = "",
+                       exec_timeout_s: int = 0) -> "Communicator":
+        cfg = HcclCommConfig()
+        lib().HcclCommConfigInit(ctypes.byref(cfg))
+        cfg.hcclBufferSize = buffer_mb
+        cfg.hcclBackend = {"auto": 0, "sim": 1, "cuda": 2}[backend]
+        if deterministic is not None:
+            cfg.hcclDeterministic = int(deterministic)
+        cfg.hcclOpExpansionMode = int(engine)
+        cfg.hcclExecTimeoutSec = exec_timeout_s
+        if name:
+            cfg.hcclCommName = name.encode()
+        info = _root_from_bytes(root_info)
+        h = ctypes.c_void_p()
+        check(lib().HcclCommInitRootInfoConfig(nranks, ctypes.byref(info), rank, ctypes.byref(cfg), ctypes.byref(h)),
+              "HcclCommInitRootInfoConfig")
+        return cls(h.value)
+
+    @classmethod
+    def from_cluster_info(cls, path: str, rank: int) -> "Communicator":
+        h = ctypes.c_void_p()
+        check(lib().HcclCommInitClusterInfo(path.encode(), rank, ctypes.byref(h)), "HcclCommInitClusterInfo")
+        return cls(h.value)
+
+    @classmethod
+    def from_torch_process_group(cls, group=None, **kw) -> "Communicator":
+        """Bootstraps over an existing torch.distributed group (any backend): rank 0's root info is broadcast as bytes."""
+        import torch.distributed as dist
+
+        rank, size = dist.get_rank(group), dist.get_world_size(group)
+        obj = [get_root_info() if rank == 0 else None]
+        dist.broadcast_object_list(obj, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+        return cls.from_root_info(size, obj[0], rank, **kw)
+
+    def create_sub_comm(self, ranks: Optional[Sequence[int]], sub_id: int) -> Optional["Communicator"]:
+        sub = ctypes.c_void_p()
+        parent = ctypes.c_void_p(self._h.value)
+        if ranks is None or self.rank not in ranks:
+            check(lib().HcclCreateSubCommConfig(ctypes.byref(parent), 0, None, sub_id, 0, None, ctypes.byref(sub)), "HcclCreateSubCommConfig")
+            return None
+        arr = (ctypes.c_uint32 * len(ranks))(*ranks)
+        check(lib().HcclCreateSubCommConfig(ctypes.byref(parent), len(ranks), arr, sub_id, list(ranks).index(self.rank), None,
+                                            ctypes.byref(sub)), "HcclCreateSubCommConfig")
+        return Communicator(sub.value)
+
+    def destroy(self) -> None:
+        if self._h is not None and self._h.value:
+            check(lib().HcclCommDestroy(self._h), "HcclCommDestroy")
+            self._h = None
+
+    # ---- helpers --------------------------------------------------------------------------------------------
+    @property
+    def handle(self) -> int:
+        return self._h.value
+
+    @property
+    def name(self) -> str:
+        buf = ctypes.create_string_buffer(128)
+        check(lib().HcclGetCommName(self._h, buf), "HcclGetCommName")
+        return buf.value.decode()
+
+    def _stream(self, is_cuda: bool, stream) -> ctypes.c_void_p:
+        if not is_cuda:
+            return ctypes.c_void_p(0)
+        if stream is None:
+            import torch
+
+            stream = torch.cuda.current_stream()
+        return ctypes.c_void_p(getattr(stream, "cuda_stream", stream))
+
+    def synchronize(self) -> None:
+        check(lib().HcclSimStreamSynchronize(self._h), "HcclSimStreamSynchronize")
+
+    def status(self) -> int:
+        s = ctypes.c_int()
+        check(lib().HcclCommGetStatus(self._h, ctypes.byref(s)), "HcclCommGetStatus")
+        return s.value
+
+    def async_error(self) -> int:
+        e = ctypes.c_int()
+        check(lib().HcclGetCommAsyncError(self._h, ctypes.byref(e)), "HcclGetCommAsyncError")
+        return e.value
+
+    def suspend(self) -> None:
+        check(lib().HcclCommSuspend(self._h), "HcclCommSuspend")
+
+    def resume(self) -> None:
+        check(lib().HcclCommResume(self._h), "HcclCommResume")
+
+    # ---- collectives ----------------------------------------------------------------------------------------
+    def all_reduce(self, send, recv=None, op: ReduceOp = ReduceOp.SUM, stream=None) -> None:
+        recv = send if recv is None else recv
+        sp, n, dt, cu = _describe(send)
+        rp, _, _, _ = _describe(recv)
+        check(lib().HcclAllReduce(sp, rp, n, dt, int(op), self._h, self._stream(cu, stream)), "HcclAllReduce")
+
+    def broadcast(self, buf, root: int, stream=None) -> None:
+        p, n, dt, cu = _describe(buf)
+        check(lib().HcclBroadcast(p, n, dt, root, self._h, self._stream(cu, stream)), "HcclBroadcast")
+
+    def reduce_scatter(self, send, recv, op: ReduceOp = ReduceOp.SUM, stream=None) -> None:
+        sp, _, dt, cu = _describe(send)
+        rp, n, _, _ = _describe(recv)
+        check(lib().HcclReduceScatter(sp, rp, n, dt, int(op), self._h, self._stream(cu, stream)), "HcclReduceScatter")
+
+    def reduce_scatter_v(self, send, send_counts, send_displs, recv, op: ReduceOp = ReduceOp.SUM, stream=None) -> None:
+        sp, _, dt, cu = _describe(send)
+        rp, n, _, cu2 = _describe(recv)
+        sc, sd = _u64_array(send_counts), _u64_array(send_displs)
+        check(lib().HcclReduceScatterV(sp, sc, sd, rp, int(send_counts[self.rank]), dt, int(op), self._h, self._stream(cu or cu2, stream)),
+              "HcclReduceScatterV")
+
+    def scatter(self, send, recv, root: int, stream=None) -> None:
+        sp, _, _, _ = _describe(send)
+        rp, n, dt, cu = _describe(recv)
+        check(lib().HcclScatter(sp, rp, n, dt, root, self._h, self._stream(cu, stream)), "HcclScatter")
+
+    def all_gather(self, send, recv, stream=None) -> None:
+        sp, n, dt, cu = _describe(send)
+        rp, _, _, _ = _describe(recv)
+        check(lib().HcclAllGather(sp, rp, n, dt, self._h, self._stream(cu, stream)), "HcclAllGather")
+
+    def all_gather_v(self, send, recv, recv_counts, recv_displs, stream=None) -> None:
+        sp, n, dt, cu = _describe(send)
+        rp, _, dt2, cu2 = _describe(recv)
+        rc, rd = _u64_array(recv_counts), _u64_array(recv_displs)
+        check(lib().HcclAllGatherV(sp, int(recv_counts[self.rank]), rp, rc, rd, dt2 if send is None else dt, self._h,
+                                   self._stream(cu or cu2, stream)), "HcclAllGatherV")
+
+    def reduce(self, send, recv, root: int, op: ReduceOp = ReduceOp.SUM, stream=None) -> None:
+        sp, n, dt, cu = _describe(send)
+        rp, _, _, _ = _describe(recv)
+        check(lib().HcclReduce(sp, rp, n, dt, int(op), root, self._h, self._stream(cu, stream)), "HcclReduce")
+
+    def all_to_all(self, send, recv, stream=None) -> None:
+        sp, n, dt, cu = _describe(send)
+        rp, m, dt2, _ = _describe(recv)
+        check(lib().HcclAlltoAll(sp, n // self.size, dt, rp, m // self.size, dt2, self._h, self._stream(cu, stream)), "HcclAlltoAll")
+
+    def all_to_all_v(self, send, send_counts, sdispls, recv, recv_counts, rdispls, stream=None) -> None:
+        sp, _, dt, cu = _describe(send)
+        rp, _, dt2, cu2 = _describe(recv)
+        if send is None:
+            dt = dt2
+        if recv is None:
+            dt2 = dt
+        check(lib().HcclAlltoAllV(sp, _u64_array(send_counts), _u64_array(sdispls), dt, rp, _u64_array(recv_counts), _u64_array(rdispls),
+                                  dt2, self._h, self._stream(cu or cu2, stream)), "HcclAlltoAllV")
+
+    def all_to_all_vc(self, send, count_matrix, recv, stream=None) -> None:
+        sp, _, dt, cu = _describe(send)
+        rp, _, dt2, cu2 = _describe(recv)
+        if send is None:
+            dt = dt2
+        if recv is None:
+            dt2 = dt
+        flat = [int(v) for row in count_matrix for v in row]
+        check(lib().HcclAlltoAllVC(sp, _u64_array(flat), dt, rp, dt2, self._h, self._stream(cu or cu2, stream)), "HcclAlltoAllVC")
+
+    def send(self, buf, dst: int, stream=None) -> None:
+        p, n, dt, cu = _describe(buf)
+        check(lib().HcclSend(p, n, dt, dst, self._h, self._stream(cu, stream)), "HcclSend")
+
+    def recv(self, buf, src: int, stream=None) -> None:
+        p, n, dt, cu = _describe(buf)
+        check(lib().HcclRecv(p, n, dt, src, self._h, self._stream(cu, stream)), "HcclRecv")
+
+    def batch_send_recv(self, items: Sequence[tuple], stream=None) -> None:
+        """items: ("send"|"recv", buffer, peer)"""
+        arr = (HcclSendRecvItem * len(items))()
+        any_cuda = False
+        for i, (kind, buf, peer) in enumerate(items):
+            p, n, dt, cu = _describe(buf)
+            any_cuda = any_cuda or cu
+            arr[i].sendRecvType = 0 if kind == "send" else 1
+            arr[i].buf = p
+            arr[i].count = n
+            arr[i].dataType = int(dt)
+            arr[i].remoteRank = peer
+        check(lib().HcclBatchSendRecv(arr, len(items), self._h, self._stream(any_cuda, stream)), "HcclBatchSendRecv")
+
+    def barrier(self, stream=None, cuda: Optional[bool] = None) -> None:
+        if cuda is None:
+            cuda = self.is_cuda
+        check(lib().HcclBarrier(self._h, self._stream(cuda, stream)), "HcclBarrier")
+
+    @property
+    def is_cuda(self) -> bool:
+        fn = getattr(lib(), "HcclCommIsCuda", None)
+        if fn is None:
+            return False
+        fn.argtypes = [ctypes.c_void_p]
+        fn.restype = ctypes.c_int
+        return bool(fn(self._h))

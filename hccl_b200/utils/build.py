@@ -1,0 +1,159 @@
+"""In-tree build of the native library and the torch extension.
+
+`build_native()` compiles every `.cc` / `.cu` under `csrc/` (except `csrc/torch/`) into
+`hccl_b200/lib/libhccl_b200.so` with `nvcc -gencode arch=compute_100a,code=sm_100a`; `build_torch_ext()` compiles the
+ProcessGroup binding against the installed torch headers into `hccl_b200/lib/hccl_b200_torch.so`. Both go through a
+generated ninja file so rebuilds are incremental and parallel. Nothing is JIT-cached outside the tree: the `.so`
+files sit next to the package and are what the Python side loads.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parents[2]
+CSRC = ROOT / "csrc"
+LIBDIR = ROOT / "hccl_b200" / "lib"
+BUILD = ROOT / "build"
+CUDA_HOME = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
+ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+
+
+def _cutlass_include() -> str | None:
+    """CuTe/CUTLASS headers vendored inside site-packages (used only for type/descriptor helpers)."""
+    import site
+
+    for sp in site.getsitepackages():
+        for rel in ("flashinfer/data/cutlass/include", "tilelang/3rdparty/cutlass/include"):
+            p = Path(sp) / rel
+            if (p / "cute").is_dir():
+                return str(p)
+    return None
+
+
+def _sources(exclude_dirs=("torch",)):
+    cc, cu = [], []
+    for p in sorted(CSRC.rglob("*")):
+        if any(part in exclude_dirs for part in p.relative_to(CSRC).parts[:-1]):
+            continue
+        if p.suffix == ".cc":
+            cc.append(p)
+        elif p.suffix == ".cu":
+            cu.append(p)
+    return cc, cu
+
+
+def _ninja(build_file: Path, jobs: int | None = None, verbose: bool = False) -> None:
+    cmd = [shutil.which("ninja") or "ninja", "-f", str(build_file)]
+    if jobs:
+        cmd += ["-j", str(jobs)]
+    if verbose:
+        cmd.append("-v")
+    res = subprocess.run(cmd, cwd=str(ROOT), stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if res.returncode != 0:
+        sys.stderr.write(res.stdout[-20000:])
+        raise RuntimeError("native build failed")
+    if verbose:
+        print(res.stdout)
+
+
+def build_native(verbose: bool = False, ptxas_info: bool = False) -> Path:
+    BUILD.mkdir(exist_ok=True)
+    LIBDIR.mkdir(parents=True, exist_ok=True)
+    cc, cu = _sources()
+    inc = [f"-I{ROOT / 'include'}", f"-I{CSRC}", f"-I{CUDA_HOME / 'include'}"]
+    cxxflags = ["-O2", "-g1", "-std=c++17", "-fPIC", "-Wall", "-Wno-unused-function", "-pthread"] + inc
+    nvflags = (["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC,-Wall,-Wno-unused-function",
+                "--threads", "2"] + ARCH_FLAGS + inc)
+    if ptxas_info:
+        nvflags += ["-Xptxas", "-v"]
+    out = LIBDIR / "libhccl_b200.so"
+    lines = [
+        "ninja_required_version = 1.3",
+        f"cxx = {shutil.which('g++') or 'g++'}",
+        f"nvcc = {CUDA_HOME / 'bin' / 'nvcc'}",
+        f"cxxflags = {' '.join(cxxflags)}",
+        f"nvflags = {' '.join(nvflags)}",
+        "rule cxx",
+        "  command = $cxx -MMD -MF $out.d $cxxflags -c $in -o $out",
+        "  depfile = $out.d",
+        "  deps = gcc",
+        "rule nvcc",
+        "  command = $nvcc -MD -MF $out.d $nvflags -c $in -o $out",
+        "  depfile = $out.d",
+        "  deps = gcc",
+        "rule link",
+        "  command = $nvcc -shared -o $out $in -cudart static -lpthread -ldl -lrt",
+    ]
+    objs = []
+    for src in cc + cu:
+        obj = BUILD / "obj" / (str(src.relative_to(CSRC)).replace("/", "_") + ".o")
+        objs.append(obj)
+        lines.append(f"build {obj}: {'cxx' if src.suffix == '.cc' else 'nvcc'} {src}")
+    lines.append(f"build {out}: link {' '.join(str(o) for o in objs)}")
+    lines.append(f"default {out}")
+    bf = BUILD / "native.ninja"
+    bf.write_text("\n".join(lines) + "\n")
+    _ninja(bf, verbose=verbose)
+    return out
+
+
+def build_torch_ext(verbose: bool = False) -> Path:
+    import torch
+    from torch.utils import cpp_extension as ce
+
+    BUILD.mkdir(exist_ok=True)
+    LIBDIR.mkdir(parents=True, exist_ok=True)
+    srcs = sorted((CSRC / "torch").glob("*.cc"))
+    if not srcs:
+        raise RuntimeError("no sources under csrc/torch")
+    inc = [f"-I{ROOT / 'include'}", f"-I{CSRC}", f"-I{CUDA_HOME / 'include'}"] + [f"-I{p}" for p in ce.include_paths()]
+    import sysconfig
+
+    inc.append(f"-I{sysconfig.get_paths()['include']}")
+    abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
+    cxxflags = ["-O2", "-std=c++17", "-fPIC", "-Wno-unused-function", "-pthread", f"-D_GLIBCXX_USE_CXX11_ABI={abi}",
+                "-DTORCH_EXTENSION_NAME=hccl_b200_torch", "-DTORCH_API_INCLUDE_EXTENSION_H", "-DUSE_C10D_NCCL=0"] + inc
+    torch_lib = Path(torch.__file__).parent / "lib"
+    out = LIBDIR / "hccl_b200_torch.so"
+    ldflags = [f"-L{torch_lib}", f"-Wl,-rpath,{torch_lib}", "-lc10", "-ltorch_cpu", "-ltorch", "-ltorch_python",
+               f"-L{LIBDIR}", "-Wl,-rpath,$$ORIGIN", "-lhccl_b200"]
+    if (torch_lib / "libc10_cuda.so").exists():
+        ldflags += ["-lc10_cuda", "-ltorch_cuda"]
+    lines = [
+        "ninja_required_version = 1.3",
+        f"cxx = {shutil.which('g++') or 'g++'}",
+        f"cxxflags = {' '.join(cxxflags)}",
+        f"ldflags = {' '.join(ldflags)}",
+        "rule cxx",
+        "  command = $cxx -MMD -MF $out.d $cxxflags -c $in -o $out",
+        "  depfile = $out.d",
+        "  deps = gcc",
+        "rule link",
+        "  command = $cxx -shared -o $out $in $ldflags",
+    ]
+    objs = []
+    for src in srcs:
+        obj = BUILD / "obj_torch" / (src.name + ".o")
+        objs.append(obj)
+        lines.append(f"build {obj}: cxx {src}")
+    lines.append(f"build {out}: link {' '.join(str(o) for o in objs)} | {LIBDIR / 'libhccl_b200.so'}")
+    lines.append(f"default {out}")
+    bf = BUILD / "torch_ext.ninja"
+    bf.write_text("\n".join(lines) + "\n")
+    _ninja(bf, verbose=verbose)
+    return out
+
+
+def build_all(verbose: bool = False) -> None:
+    build_native(verbose=verbose)
+    if (CSRC / "torch").is_dir() and any((CSRC / "torch").glob("*.cc")):
+        build_torch_ext(verbose=verbose)
+
+
+if __name__ == "__main__":
+    build_all(verbose="-v" in sys.argv)
+    print("built:", ", ".join(str(p) for p in sorted(LIBDIR.glob("*.so"))))

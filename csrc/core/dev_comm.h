@@ -18,6 +18,7 @@ namespace hccl {
 constexpr int kMaxRanks = 32;
 constexpr int kMaxChannels = 256;       // CTA channels with independent flag rows / epochs
 constexpr int kNotifySlots = 16;        // host-engine notify counters per peer
+constexpr int kP2pCtas = 8;             // CTAs per point-to-point transfer
 constexpr uint64_t kCtrlBytes = 64 << 10;
 constexpr uint64_t kFlagBytes = (1 << 20) - kCtrlBytes;
 constexpr uint64_t kHeapHeaderBytes = 1 << 20;
@@ -42,8 +43,8 @@ struct DevCtrl {
     uint32_t gridBar[2];              // software grid barrier (count, generation) for persistent kernels
     uint32_t pad0[3];
     uint32_t chanEpoch[kMaxChannels]; // per-channel barrier epoch
-    uint64_t p2pSendSeq[kMaxRanks];   // messages sent to peer r
-    uint64_t p2pRecvSeq[kMaxRanks];   // messages received from peer r
+    uint64_t p2pSendSeq[kMaxRanks][kP2pCtas];   // mailbox rounds sent to peer r by p2p CTA b
+    uint64_t p2pRecvSeq[kMaxRanks][kP2pCtas];   // mailbox rounds received from peer r by p2p CTA b
     uint64_t hostNotifySent[kMaxRanks][kNotifySlots];   // host-engine: posts issued towards peer r
     uint64_t hostNotifyWaited[kMaxRanks][kNotifySlots]; // host-engine: waits consumed from peer r
 };
@@ -53,8 +54,8 @@ static_assert(sizeof(DevCtrl) <= kCtrlBytes, "control block too large");
 struct DevFlags {
     uint32_t barrier[kMaxChannels][kMaxRanks];   // barrier[ch][src] = epoch reached by src on channel ch
     uint32_t chunk[kMaxChannels][kMaxRanks];     // chunk[ch][src] = chunks delivered by src on channel ch
-    uint64_t p2pData[kMaxRanks][2];              // [src][slot] = sequence number whose data is staged at src
-    uint64_t p2pAck[kMaxRanks][2];               // [dst][slot] = sequence number dst has consumed
+    uint64_t p2pData[kMaxRanks][kP2pCtas * 2];   // [src][cta*2+slot] = round number whose data is staged at src
+    uint64_t p2pAck[kMaxRanks][kP2pCtas * 2];    // [dst][cta*2+slot] = round number dst has consumed
     uint64_t hostNotify[kMaxRanks][kNotifySlots];// host-engine notify counters, [src][slot]
     uint32_t mc2Ready[kMaxRanks][64];            // fused-kernel tile/row-block ready counters, [src][block]
     uint32_t moeCount[kMaxRanks][320];           // MoE dispatch: per-source expert counts (+ epoch word)

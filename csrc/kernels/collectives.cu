@@ -1,0 +1,571 @@
+// Collective kernels of the SM and NVLS engines (sm_100a). Each operator chunk is ONE launch: data movement over
+// NVLink by plain peer loads/stores (or multimem.* through the NVSwitch multicast mapping), reduction in registers
+// in rank order, synchronisation by epoch flags in the symmetric heap with bounded waits.
+//
+// Shapes follow HCCL's vector-core kernel family (reference: src/ops/all_reduce/template/aiv/kernel/
+// aiv_all_reduce_mesh_1d_oneshot.h:17-120 and ..._twoshot.h:16-349, all_gather/.../aiv_all_gather_mesh_1d.h:17-237,
+// reduce_scatter/.../aiv_reduce_scatter_mesh_1d.h:16-93, all_to_all_v/.../aiv_all_to_all_v_mesh_1D.h:16-271,
+// broadcast/.../aiv_broadcast_mesh_1d.h, reduce/.../aiv_reduce_mesh_1d.h, scatter/.../aiv_scatter_mesh_1d.h,
+// send/recv .../aiv_send_mesh_1D.h:42-56) but are laid out for NVSwitch: every CTA ("channel") owns the same byte
+// range on every rank, so ranks synchronise per channel and never grid-wide, and no kernel ends with a barrier:
+// the two CCL halves alternate per operator (device-resident parity), and every operator contains at least one
+// all-peer synchronisation, so a rank entering operator k+2 knows every peer has left operator k.
+//
+// EMU = true: all ranks live on one GPU and blockIdx.y is the rank; launched cooperatively so that the CTAs that
+// wait for each other are co-resident. Used to test the protocols on a single device.
+#include <cooperative_groups.h>
+#include "coll_args.h"
+#include "primitives.cuh"
+
+namespace hccl {
+using namespace dev;
+
+namespace {
+
+constexpr int kThreads = 512;
+
+template <bool EMU> __device__ __forceinline__ const CollArgs &ArgsOf(const CollArgs &byValue, const CollArgs *emuArgs)
+{
+    return EMU ? emuArgs[blockIdx.y] : byValue;
+}
+
+__device__ __forceinline__ uint64_t Up128(uint64_t v) { return (v + 127) & ~127ull; }
+__device__ __forceinline__ uint64_t SliceLen(uint64_t total, uint64_t slice, int j)
+{
+    uint64_t off = slice * (uint64_t)j;
+    return off >= total ? 0 : (total - off < slice ? total - off : slice);
+}
+
+// ================================================================================================ AllReduce one-shot
+// Every rank pushes its part into slot[rank] of every rank's scratch; after the channel barrier each rank reduces the
+// n local slots in rank order.
+template <typename T, int OP, bool EMU> __device__ void AllReduceOneShotBody(KCtx &k, const CollArgs &A)
+{
+    const int n = k.nranks;
+    const uint64_t slot = Up128(A.bytes);
+    Part p = PartOf(A.bytes, gridDim.x, blockIdx.x);
+    const char *in = (const char *)A.in + p.off;
+    for (int d = 0; d < n; ++d) {
+        int r = (k.rank + d) % n;
+        BlockCopy(k.Ccl(r) + (uint64_t)k.rank * slot + p.off, in, p.len);
+    }
+    if (!ChannelBarrier(k, 1)) return;
+    const char *slots[kMaxRanks];
+    for (int r = 0; r < n; ++r) slots[r] = k.Ccl(k.rank) + (uint64_t)r * slot + p.off;
+    ReduceSlots<T, OP, kMaxRanks>((T *)((char *)A.out + p.off), (T *)nullptr, slots, n, p.len / sizeof(T));
+}
+
+// ================================================================================================ AllReduce two-shot
+// Reduce-scatter by push (slice j of every rank lands in rank j's slots), ordered reduce of the own slice, all-gather
+// by pull from the owners' result regions.
+template <typename T, int OP, bool EMU> __device__ void AllReduceTwoShotBody(KCtx &k, const CollArgs &A)
+{
+    const int n = k.nranks;
+    const uint64_t slice = Up128((A.bytes + n - 1) / n);
+    for (int d = 0; d < n; ++d) {
+        int r = (k.rank + d) % n;
+        Part p = PartOf(SliceLen(A.bytes, slice, r), gridDim.x, blockIdx.x);
+        BlockCopy(k.Ccl(r) + (uint64_t)k.rank * slice + p.off, (const char *)A.in + (uint64_t)r * slice + p.off, p.len);
+    }
+    if (!ChannelBarrier(k, 1)) return;
+    {
+        Part p = PartOf(SliceLen(A.bytes, slice, k.rank), gridDim.x, blockIdx.x);
+        const char *slots[kMaxRanks];
+        for (int r = 0; r < n; ++r) slots[r] = k.Ccl(k.rank) + (uint64_t)r * slice + p.off;
+        T *res = (T *)(k.Ccl(k.rank) + (uint64_t)n * slice + p.off);
+        ReduceSlots<T, OP, kMaxRanks>((T *)((char *)A.out + (uint64_t)k.rank * slice + p.off), res, slots, n, p.len / sizeof(T));
+    }
+    if (!ChannelBarrier(k, 2)) return;
+    for (int d = 1; d < n; ++d) {
+        int r = (k.rank + d) % n;
+        Part p = PartOf(SliceLen(A.bytes, slice, r), gridDim.x, blockIdx.x);
+        BlockCopy((char *)A.out + (uint64_t)r * slice + p.off, k.Ccl(r) + (uint64_t)n * slice + p.off, p.len);
+    }
+}
+
+// ================================================================================================ AllReduce NVLS
+// out[i] <- switch-reduced value; `out` may have any alignment (element-wise store then).
+template <typename T> __device__ __forceinline__ void StoreVec(T *out, uint64_t vecIdx, uint4 v, bool aligned)
+{
+    constexpr int VE = 16 / sizeof(T);
+    if (aligned) ((uint4 *)out)[vecIdx] = v;
+    else {
+        const T *e = (const T *)&v;
+#pragma unroll
+        for (int j = 0; j < VE; ++j) out[vecIdx * VE + j] = e[j];
+    }
+}
+
+template <typename T, int OP, bool EMU> __device__ void AllReduceNvlsOneShotBody(KCtx &k, const CollArgs &A)
+{
+    Part p = PartOf(A.bytes, gridDim.x, blockIdx.x);
+    BlockCopy(k.Ccl(k.rank) + p.off, (const char *)A.in + p.off, p.len);
+    if (!ChannelBarrier(k, 1)) return;
+    const char *mc = k.Mc() + p.off;
+    T *out = (T *)((char *)A.out + p.off);
+    bool aligned = ((uintptr_t)out & 15u) == 0;
+    uint64_t nvec = p.len >> 4;
+    for (uint64_t i = threadIdx.x; i < nvec; i += blockDim.x) StoreVec<T>(out, i, MultimemLdReduce<T, OP>::Ld(mc + (i << 4)), aligned);
+}
+
+template <typename T, int OP, bool EMU> __device__ void AllReduceNvlsTwoShotBody(KCtx &k, const CollArgs &A)
+{
+    const int n = k.nranks;
+    const uint64_t slice = Up128((A.bytes + n - 1) / n);
+    const uint64_t outRegion = (uint64_t)n * slice;
+    for (int j = 0; j < n; ++j) {
+        Part p = PartOf(SliceLen(A.bytes, slice, j), gridDim.x, blockIdx.x);
+        BlockCopy(k.Ccl(k.rank) + (uint64_t)j * slice + p.off, (const char *)A.in + (uint64_t)j * slice + p.off, p.len);
+    }
+    if (!ChannelBarrier(k, 1)) return;
+    {
+        Part p = PartOf(SliceLen(A.bytes, slice, k.rank), gridDim.x, blockIdx.x);
+        char *src = k.Mc() + (uint64_t)k.rank * slice + p.off;
+        char *dst = k.Mc() + outRegion + (uint64_t)k.rank * slice + p.off;
+        uint64_t nvec = p.len >> 4;
+        for (uint64_t i = threadIdx.x; i < nvec; i += blockDim.x) MultimemSt16(dst + (i << 4), MultimemLdReduce<T, OP>::Ld(src + (i << 4)));
+    }
+    if (!ChannelBarrier(k, 2)) return;
+    for (int j = 0; j < n; ++j) {
+        Part p = PartOf(SliceLen(A.bytes, slice, j), gridDim.x, blockIdx.x);
+        BlockCopy((char *)A.out + (uint64_t)j * slice + p.off, k.Ccl(k.rank) + outRegion + (uint64_t)j * slice + p.off, p.len);
+    }
+}
+
+// ================================================================================================ AllGather(V), pull
+template <bool EMU> __device__ void AllGatherVBody(KCtx &k, const CollArgs &A)
+{
+    const int n = k.nranks;
+    {
+        Part p = PartOf(A.recvBytes[k.rank], gridDim.x, blockIdx.x);
+        BlockCopy(k.Ccl(k.rank) + p.off, (const char *)A.in + p.off, p.len);
+    }
+    if (!ChannelBarrier(k, 1)) return;
+    for (int d = 1; d < n; ++d) {
+        int r = (k.rank + d) % n;
+        Part p = PartOf(A.recvBytes[r], gridDim.x, blockIdx.x);
+        BlockCopy((char *)A.out + A.recvOff[r] + p.off, k.Ccl(r) + p.off, p.len);
+    }
+    char *self = (char *)A.out + A.recvOff[k.rank];
+    if (self != (const char *)A.in) {
+        Part p = PartOf(A.recvBytes[k.rank], gridDim.x, blockIdx.x);
+        BlockCopy(self + p.off, (const char *)A.in + p.off, p.len);
+    }
+}
+
+// ================================================================================================ ReduceScatter(V), push
+template <typename T, int OP, bool EMU> __device__ void ReduceScatterVBody(KCtx &k, const CollArgs &A)
+{
+    const int n = k.nranks;
+    uint64_t slot = 0;
+    for (int r = 0; r < n; ++r) slot = A.sendBytes[r] > slot ? A.sendBytes[r] : slot;
+    slot = Up128(slot);
+    for (int d = 0; d < n; ++d) {
+        int r = (k.rank + d) % n;
+        Part p = PartOf(A.sendBytes[r], gridDim.x, blockIdx.x);
+        BlockCopy(k.Ccl(r) + (uint64_t)k.rank * slot + p.off, (const char *)A.in + A.sendOff[r] + p.off, p.len);
+    }
+    if (!ChannelBarrier(k, 1)) return;
+    Part p = PartOf(A.sendBytes[k.rank], gridDim.x, blockIdx.x);
+    const char *slots[kMaxRanks];
+    for (int r = 0; r < n; ++r) slots[r] = k.Ccl(k.rank) + (uint64_t)r * slot + p.off;
+    ReduceSlots<T, OP, kMaxRanks>((T *)((char *)A.out + p.off), (T *)nullptr, slots, n, p.len / sizeof(T));
+}
+
+template <typename T, int OP, bool EMU> __device__ void ReduceScatterNvlsBody(KCtx &k, const CollArgs &A)
+{
+    const int n = k.nranks;
+    const uint64_t slot = Up128(A.sendBytes[0]);
+    for (int j = 0; j < n; ++j) {
+        Part p = PartOf(A.sendBytes[j], gridDim.x, blockIdx.x);
+        BlockCopy(k.Ccl(k.rank) + (uint64_t)j * slot + p.off, (const char *)A.in + A.sendOff[j] + p.off, p.len);
+    }
+    if (!ChannelBarrier(k, 1)) return;
+    Part p = PartOf(A.sendBytes[k.rank], gridDim.x, blockIdx.x);
+    const char *mc = k.Mc() + (uint64_t)k.rank * slot + p.off;
+    T *out = (T *)((char *)A.out + p.off);
+    bool aligned = ((uintptr_t)out & 15u) == 0;
+    uint64_t nvec = p.len >> 4;
+    for (uint64_t i = threadIdx.x; i < nvec; i += blockDim.x) StoreVec<T>(out, i, MultimemLdReduce<T, OP>::Ld(mc + (i << 4)), aligned);
+}
+
+// ================================================================================================ Broadcast
+template <bool EMU> __device__ void BroadcastBody(KCtx &k, const CollArgs &A)
+{
+    Part p = PartOf(A.bytes, gridDim.x, blockIdx.x);
+    if (k.rank == (int)A.root) BlockCopy(k.Ccl(k.rank) + p.off, (const char *)A.in + p.off, p.len);
+    if (!ChannelBarrier(k, 1)) return;
+    if (k.rank != (int)A.root) BlockCopy((char *)A.out + p.off, k.Ccl((int)A.root) + p.off, p.len);
+}
+
+// Root multicasts once; the switch replicates to every rank's scratch, each rank copies out locally.
+template <bool EMU> __device__ void BroadcastNvlsBody(KCtx &k, const CollArgs &A)
+{
+    Part p = PartOf(A.bytes, gridDim.x, blockIdx.x);
+    if (k.rank == (int)A.root) {
+        const char *src = (const char *)A.in + p.off;
+        char *mc = k.Mc() + p.off;
+        uint64_t nvec = p.len >> 4;
+        if (((uintptr_t)src & 15u) == 0) {
+            for (uint64_t i = threadIdx.x; i < nvec; i += blockDim.x) MultimemSt16(mc + (i << 4), ((const uint4 *)src)[i]);
+        } else {
+            for (uint64_t i = threadIdx.x; i < nvec; i += blockDim.x) {
+                uint4 v;
+                char *b = (char *)&v;
+                for (int j = 0; j < 16; ++j) b[j] = src[(i << 4) + j];
+                MultimemSt16(mc + (i << 4), v);
+            }
+        }
+    }
+    if (!ChannelBarrier(k, 1)) return;
+    if (k.rank != (int)A.root) BlockCopy((char *)A.out + p.off, k.Ccl(k.rank) + p.off, p.len);
+}
+
+// ================================================================================================ Reduce (to root)
+template <typename T, int OP, bool EMU> __device__ void ReduceBody(KCtx &k, const CollArgs &A)
+{
+    const int n = k.nranks, root = (int)A.root;
+    const uint64_t slot = Up128(A.bytes);
+    Part p = PartOf(A.bytes, gridDim.x, blockIdx.x);
+    BlockCopy(k.Ccl(root) + (uint64_t)k.rank * slot + p.off, (const char *)A.in + p.off, p.len);
+    if (!ChannelBarrier(k, 1)) return;
+    if (k.rank != root) return;
+    const char *slots[kMaxRanks];
+    for (int r = 0; r < n; ++r) slots[r] = k.Ccl(root) + (uint64_t)r * slot + p.off;
+    ReduceSlots<T, OP, kMaxRanks>((T *)((char *)A.out + p.off), (T *)nullptr, slots, n, p.len / sizeof(T));
+}
+
+// ================================================================================================ Scatter (pull from root)
+template <bool EMU> __device__ void ScatterBody(KCtx &k, const CollArgs &A)
+{
+    const int n = k.nranks, root = (int)A.root;
+    const uint64_t blockBytes = A.bytes, slot = Up128(blockBytes);
+    Part p = PartOf(blockBytes, gridDim.x, blockIdx.x);
+    if (k.rank == root) {
+        for (int r = 0; r < n; ++r) {
+            if (r == root) continue;
+            BlockCopy(k.Ccl(root) + (uint64_t)r * slot + p.off, (const char *)A.in + A.sendOff[r] + p.off, p.len);
+        }
+    }
+    if (!ChannelBarrier(k, 1)) return;
+    if (k.rank == root) BlockCopy((char *)A.out + p.off, (const char *)A.in + A.sendOff[root] + p.off, p.len);
+    else BlockCopy((char *)A.out + p.off, k.Ccl(root) + (uint64_t)k.rank * slot + p.off, p.len);
+}
+
+// ================================================================================================ AlltoAll(V/VC), pull
+// Sender packs the segment for each peer into its own scratch and publishes the packed offsets (one copy per
+// channel, so a channel barrier orders it); receivers pull their segment.
+template <bool EMU> __device__ void AlltoAllVBody(KCtx &k, const CollArgs &A)
+{
+    const int n = k.nranks;
+    uint64_t *meta = (uint64_t *)(k.Ccl(k.rank) + k.c->cclBytes - kA2aMetaBytes) + (uint64_t)k.chan * kMaxRanks;
+    uint64_t po = 0;
+    for (int r = 0; r < n; ++r) {
+        if (r == k.rank) continue;
+        Part p = PartOf(A.sendBytes[r], gridDim.x, blockIdx.x);
+        BlockCopy(k.Ccl(k.rank) + po + p.off, (const char *)A.in + A.sendOff[r] + p.off, p.len);
+        if (threadIdx.x == 0) meta[r] = po;
+        po += Up128(A.sendBytes[r]);
+    }
+    if (!ChannelBarrier(k, 1)) return;
+    for (int d = 1; d < n; ++d) {
+        int r = (k.rank + d) % n;
+        const uint64_t *peerMeta = (const uint64_t *)(k.Ccl(r) + k.c->cclBytes - kA2aMetaBytes) + (uint64_t)k.chan * kMaxRanks;
+        uint64_t off = peerMeta[k.rank];
+        Part p = PartOf(A.recvBytes[r], gridDim.x, blockIdx.x);
+        BlockCopy((char *)A.out + A.recvOff[r] + p.off, k.Ccl(r) + off + p.off, p.len);
+    }
+    Part p = PartOf(A.sendBytes[k.rank], gridDim.x, blockIdx.x);
+    BlockCopy((char *)A.out + A.recvOff[k.rank] + p.off, (const char *)A.in + A.sendOff[k.rank] + p.off, p.len);
+}
+
+// ================================================================================================ kernels
+#define COLL_KERNEL_TYPED(NAME, BODY)                                                                                  \
+    template <typename T, bool EMU>                                                                                    \
+    __global__ void __launch_bounds__(kThreads) NAME(const DevComm *comms, const __grid_constant__ CollArgs a, const CollArgs *emuArgs) \
+    {                                                                                                                  \
+        KCtx k = EnterCollective<EMU>(comms);                                                                          \
+        const CollArgs &A = ArgsOf<EMU>(a, emuArgs);                                                                   \
+        switch (A.op) {                                                                                                \
+            case HCCL_REDUCE_SUM: BODY<T, HCCL_REDUCE_SUM, EMU>(k, A); break;                                          \
+            case HCCL_REDUCE_PROD: BODY<T, HCCL_REDUCE_PROD, EMU>(k, A); break;                                        \
+            case HCCL_REDUCE_MAX: BODY<T, HCCL_REDUCE_MAX, EMU>(k, A); break;                                          \
+            default: BODY<T, HCCL_REDUCE_MIN, EMU>(k, A); break;                                                       \
+        }                                                                                                              \
+        LeaveCollective(k);                                                                                            \
+    }
+COLL_KERNEL_TYPED(KAllReduceOneShot, AllReduceOneShotBody)
+COLL_KERNEL_TYPED(KAllReduceTwoShot, AllReduceTwoShotBody)
+COLL_KERNEL_TYPED(KReduceScatterV, ReduceScatterVBody)
+COLL_KERNEL_TYPED(KReduce, ReduceBody)
+
+#define COLL_KERNEL_NVLS(NAME, BODY)                                                                                   \
+    template <typename T, int OP, bool EMU>                                                                            \
+    __global__ void __launch_bounds__(kThreads) NAME(const DevComm *comms, const __grid_constant__ CollArgs a, const CollArgs *emuArgs) \
+    {                                                                                                                  \
+        KCtx k = EnterCollective<EMU>(comms);                                                                          \
+        BODY<T, OP, EMU>(k, ArgsOf<EMU>(a, emuArgs));                                                                  \
+        LeaveCollective(k);                                                                                            \
+    }
+COLL_KERNEL_NVLS(KAllReduceNvlsOneShot, AllReduceNvlsOneShotBody)
+COLL_KERNEL_NVLS(KAllReduceNvlsTwoShot, AllReduceNvlsTwoShotBody)
+COLL_KERNEL_NVLS(KReduceScatterNvls, ReduceScatterNvlsBody)
+
+#define COLL_KERNEL_BYTES(NAME, BODY)                                                                                  \
+    template <bool EMU>                                                                                                \
+    __global__ void __launch_bounds__(kThreads) NAME(const DevComm *comms, const __grid_constant__ CollArgs a, const CollArgs *emuArgs) \
+    {                                                                                                                  \
+        KCtx k = EnterCollective<EMU>(comms);                                                                          \
+        BODY<EMU>(k, ArgsOf<EMU>(a, emuArgs));                                                                         \
+        LeaveCollective(k);                                                                                            \
+    }
+COLL_KERNEL_BYTES(KAllGatherV, AllGatherVBody)
+COLL_KERNEL_BYTES(KBroadcast, BroadcastBody)
+COLL_KERNEL_BYTES(KBroadcastNvls, BroadcastNvlsBody)
+COLL_KERNEL_BYTES(KScatter, ScatterBody)
+COLL_KERNEL_BYTES(KAlltoAllV, AlltoAllVBody)
+
+template <bool EMU> __global__ void __launch_bounds__(kThreads) KBarrier(const DevComm *comms, const __grid_constant__ CollArgs a, const CollArgs *)
+{
+    KCtx k = EnterCollective<EMU>(comms);
+    ChannelBarrier(k, 1);
+    LeaveCollective(k);
+}
+
+// ================================================================================================ point to point
+// Mailbox protocol. The sender stages round m (1-based, cumulative per (peer, CTA)) in slot (m-1)&1 of its own
+// mailbox for that peer and raises data[src][cta][slot] = m at the receiver; the receiver pulls and raises
+// ack[dst][cta][slot] = m at the sender. A slot is refilled only after the round that used it two rounds earlier was
+// acknowledged, and a send returns only when all its rounds were acknowledged (rendezvous semantics, like
+// HCCL's send/recv kernels which stage into the CCL buffer and wait for the receiver's ack).
+struct P2pCtx {
+    const DevComm *c;
+    int rank;
+    char *heap;
+    DevCtrl *ctrl;
+    DevFlags *flags;
+    KCtx k;   // for the bounded waits / reporting
+};
+template <bool EMU> __device__ __forceinline__ P2pCtx EnterP2p(const DevComm *comms, uint32_t chan)
+{
+    P2pCtx x;
+    x.c = EMU ? &comms[blockIdx.y] : comms;
+    x.rank = x.c->rank;
+    x.heap = x.c->heap[x.rank];
+    x.ctrl = CtrlOf(x.heap);
+    x.flags = FlagsOf(x.heap);
+    x.k.c = x.c; x.k.rank = x.rank; x.k.nranks = x.c->nranks; x.k.heap = x.heap; x.k.ctrl = x.ctrl; x.k.flags = x.flags;
+    x.k.half = 0; x.k.chan = chan; x.k.epoch = 0; x.k.syncs = 0; x.k.ok = true;
+    return x;
+}
+
+// cta = index within the 8 CTAs of this transfer
+__device__ bool SendBody(P2pCtx &x, const char *src, uint64_t bytes, int dst, int cta)
+{
+    const uint64_t W = x.c->mailboxBytes, sub = W / kP2pBlocks;
+    uint64_t rounds = (bytes + W - 1) / W;
+    uint64_t base = x.ctrl->p2pSendSeq[dst][cta];
+    bool ok = true;
+    for (uint64_t r = 0; r < rounds && ok; ++r) {
+        uint64_t m = base + r + 1;
+        uint32_t slot = (uint32_t)((m - 1) & 1);
+        if (m > 2) {
+            if (threadIdx.x == 0) ok = WaitFlagGe64(x.k, &x.flags->p2pAck[dst][cta * 2 + slot], m - 2, (uint32_t)dst, 11);
+            ok = __syncthreads_and(ok ? 1 : 0) != 0;
+            if (!ok) break;
+        }
+        uint64_t chunk = bytes - r * W < W ? bytes - r * W : W;
+        Part p = PartOf(chunk, kP2pBlocks, cta);
+        (void)sub;
+        BlockCopy(x.heap + x.c->mailboxOff + ((uint64_t)dst * 2 + slot) * W + p.off, src + r * W + p.off, p.len);
+        __syncthreads();
+        if (threadIdx.x == 0) StReleaseSys64(&FlagsOf(x.c->heap[dst])->p2pData[x.rank][cta * 2 + slot], m);
+    }
+    // all rounds acknowledged before the send completes
+    if (ok && rounds > 0) {
+        uint64_t last = base + rounds;
+        if (threadIdx.x == 0) {
+            ok = WaitFlagGe64(x.k, &x.flags->p2pAck[dst][cta * 2 + (uint32_t)((last - 1) & 1)], last, (uint32_t)dst, 12);
+            if (ok && last >= 2) ok = WaitFlagGe64(x.k, &x.flags->p2pAck[dst][cta * 2 + (uint32_t)((last - 2) & 1)], last - 1, (uint32_t)dst, 13);
+        }
+        ok = __syncthreads_and(ok ? 1 : 0) != 0;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) x.ctrl->p2pSendSeq[dst][cta] = base + rounds;
+    return ok;
+}
+
+__device__ bool RecvBody(P2pCtx &x, char *dstBuf, uint64_t bytes, int src, int cta)
+{
+    const uint64_t W = x.c->mailboxBytes;
+    uint64_t rounds = (bytes + W - 1) / W;
+    uint64_t base = x.ctrl->p2pRecvSeq[src][cta];
+    bool ok = true;
+    for (uint64_t r = 0; r < rounds && ok; ++r) {
+        uint64_t m = base + r + 1;
+        uint32_t slot = (uint32_t)((m - 1) & 1);
+        if (threadIdx.x == 0) ok = WaitFlagGe64(x.k, &x.flags->p2pData[src][cta * 2 + slot], m, (uint32_t)src, 21);
+        ok = __syncthreads_and(ok ? 1 : 0) != 0;
+        if (!ok) break;
+        uint64_t chunk = bytes - r * W < W ? bytes - r * W : W;
+        Part p = PartOf(chunk, kP2pBlocks, cta);
+        BlockCopy(dstBuf + r * W + p.off, x.c->heap[src] + x.c->mailboxOff + ((uint64_t)x.rank * 2 + slot) * W + p.off, p.len);
+        __syncthreads();
+        if (threadIdx.x == 0) StReleaseSys64(&FlagsOf(x.c->heap[src])->p2pAck[x.rank][cta * 2 + slot], m);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) x.ctrl->p2pRecvSeq[src][cta] = base + rounds;
+    return ok;
+}
+
+template <bool EMU> __global__ void __launch_bounds__(kThreads) KSend(const DevComm *comms, const __grid_constant__ CollArgs a, const CollArgs *emuArgs)
+{
+    const CollArgs &A = ArgsOf<EMU>(a, emuArgs);
+    P2pCtx x = EnterP2p<EMU>(comms, blockIdx.x);
+    if (EMU && A.count == 0) return;   // emulation: ranks that do not take part
+    SendBody(x, (const char *)A.in, A.bytes, (int)A.peer, (int)blockIdx.x);
+}
+template <bool EMU> __global__ void __launch_bounds__(kThreads) KRecv(const DevComm *comms, const __grid_constant__ CollArgs a, const CollArgs *emuArgs)
+{
+    const CollArgs &A = ArgsOf<EMU>(a, emuArgs);
+    P2pCtx x = EnterP2p<EMU>(comms, blockIdx.x);
+    if (EMU && A.count == 0) return;
+    RecvBody(x, (char *)A.out, A.bytes, (int)A.peer, (int)blockIdx.x);
+}
+// Emulation only: rank A.root sends to rank A.peer inside one launch (flags 1 = sender, 2 = receiver in A.op).
+template <bool EMU> __global__ void __launch_bounds__(kThreads) KSendRecvPair(const DevComm *comms, const __grid_constant__ CollArgs a, const CollArgs *emuArgs)
+{
+    const CollArgs &A = ArgsOf<EMU>(a, emuArgs);
+    P2pCtx x = EnterP2p<EMU>(comms, blockIdx.x);
+    if (A.op == 1) SendBody(x, (const char *)A.in, A.bytes, (int)A.peer, (int)blockIdx.x);
+    else if (A.op == 2) RecvBody(x, (char *)A.out, A.bytes, (int)A.peer, (int)blockIdx.x);
+}
+
+// Queue q (one per (peer, direction), CTAs q*8..q*8+7) walks its items in order; queues run concurrently, so no
+// ordering of unrelated pairs can deadlock.
+template <bool EMU> __global__ void __launch_bounds__(kThreads) KBatchSendRecv(const DevComm *comms, const __grid_constant__ BatchArgs b, const BatchArgs *emuBatch)
+{
+    const BatchArgs &B = EMU ? emuBatch[blockIdx.y] : b;
+    uint32_t queue = blockIdx.x / kP2pBlocks, cta = blockIdx.x % kP2pBlocks;
+    if (queue >= B.nQueues) return;
+    P2pCtx x = EnterP2p<EMU>(comms, blockIdx.x);
+    uint32_t nInQueue = 0;
+    for (uint32_t i = 0; i < B.nItems; ++i) if (B.items[i].queue == queue) ++nInQueue;
+    for (uint32_t ord = 0; ord < nInQueue; ++ord) {
+        for (uint32_t i = 0; i < B.nItems; ++i) {
+            const BatchItem &it = B.items[i];
+            if (it.queue != queue || it.order != ord) continue;
+            bool ok = true;
+            if (it.isSend == 1) ok = SendBody(x, (const char *)it.buf, it.bytes, (int)it.peer, (int)cta);
+            else if (it.isSend == 0) ok = RecvBody(x, (char *)it.buf, it.bytes, (int)it.peer, (int)cta);
+            else { Part p = PartOf(it.bytes, kP2pBlocks, cta); BlockCopy((char *)it.buf2 + p.off, (const char *)it.buf + p.off, p.len); }
+            if (!ok) return;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------- launch tables
+using CollKernelFn = void (*)(const DevComm *, const CollArgs, const CollArgs *);
+
+template <bool EMU> CollKernelFn TypedKernel(SmKernelId id, HcclDataType dt)
+{
+#define PICK(KERN)                                                                 \
+    switch (dt) {                                                                  \
+        case HCCL_DATA_TYPE_INT8: return KERN<int8_t, EMU>;                        \
+        case HCCL_DATA_TYPE_INT16: return KERN<int16_t, EMU>;                      \
+        case HCCL_DATA_TYPE_INT32: return KERN<int32_t, EMU>;                      \
+        case HCCL_DATA_TYPE_INT64: return KERN<long long, EMU>;                    \
+        case HCCL_DATA_TYPE_UINT64: return KERN<unsigned long long, EMU>;          \
+        case HCCL_DATA_TYPE_FP16: return KERN<__half, EMU>;                        \
+        case HCCL_DATA_TYPE_FP32: return KERN<float, EMU>;                         \
+        case HCCL_DATA_TYPE_FP64: return KERN<double, EMU>;                        \
+        case HCCL_DATA_TYPE_BFP16: return KERN<__nv_bfloat16, EMU>;                \
+        default: return nullptr;                                                   \
+    }
+    switch (id) {
+        case K_ALLREDUCE_ONESHOT: PICK(KAllReduceOneShot)
+        case K_ALLREDUCE_TWOSHOT: PICK(KAllReduceTwoShot)
+        case K_REDUCESCATTER_V: PICK(KReduceScatterV)
+        case K_REDUCE: PICK(KReduce)
+        default: return nullptr;
+    }
+#undef PICK
+}
+
+template <bool EMU> CollKernelFn NvlsKernel(SmKernelId id, HcclDataType dt, HcclReduceOp op)
+{
+#define PICKN(KERN)                                                                                         \
+    if (dt == HCCL_DATA_TYPE_FP32 && op == HCCL_REDUCE_SUM) return KERN<float, HCCL_REDUCE_SUM, EMU>;       \
+    if (dt == HCCL_DATA_TYPE_BFP16 && op == HCCL_REDUCE_SUM) return KERN<__nv_bfloat16, HCCL_REDUCE_SUM, EMU>; \
+    if (dt == HCCL_DATA_TYPE_BFP16 && op == HCCL_REDUCE_MAX) return KERN<__nv_bfloat16, HCCL_REDUCE_MAX, EMU>; \
+    if (dt == HCCL_DATA_TYPE_BFP16 && op == HCCL_REDUCE_MIN) return KERN<__nv_bfloat16, HCCL_REDUCE_MIN, EMU>; \
+    if (dt == HCCL_DATA_TYPE_FP16 && op == HCCL_REDUCE_SUM) return KERN<__half, HCCL_REDUCE_SUM, EMU>;      \
+    if (dt == HCCL_DATA_TYPE_FP16 && op == HCCL_REDUCE_MAX) return KERN<__half, HCCL_REDUCE_MAX, EMU>;      \
+    if (dt == HCCL_DATA_TYPE_FP16 && op == HCCL_REDUCE_MIN) return KERN<__half, HCCL_REDUCE_MIN, EMU>;      \
+    return nullptr;
+    switch (id) {
+        case K_ALLREDUCE_NVLS_ONESHOT: PICKN(KAllReduceNvlsOneShot)
+        case K_ALLREDUCE_NVLS_TWOSHOT: PICKN(KAllReduceNvlsTwoShot)
+        case K_REDUCESCATTER_NVLS: PICKN(KReduceScatterNvls)
+        default: return nullptr;
+    }
+#undef PICKN
+}
+
+template <bool EMU> CollKernelFn KernelFor(const SmLaunch &l)
+{
+    switch (l.kernel) {
+        case K_ALLREDUCE_ONESHOT: case K_ALLREDUCE_TWOSHOT: case K_REDUCESCATTER_V: case K_REDUCE: return TypedKernel<EMU>(l.kernel, l.dtype);
+        case K_ALLREDUCE_NVLS_ONESHOT: case K_ALLREDUCE_NVLS_TWOSHOT: case K_REDUCESCATTER_NVLS:
+            return NvlsKernel<EMU>(l.kernel, l.dtype, (HcclReduceOp)l.args.op);
+        case K_ALLGATHER_V: return KAllGatherV<EMU>;
+        case K_BROADCAST: return KBroadcast<EMU>;
+        case K_BROADCAST_NVLS: return KBroadcastNvls<EMU>;
+        case K_SCATTER: return KScatter<EMU>;
+        case K_ALLTOALL_V: return KAlltoAllV<EMU>;
+        case K_BARRIER: return KBarrier<EMU>;
+        case K_SEND: return KSend<EMU>;
+        case K_RECV: return KRecv<EMU>;
+        default: return nullptr;
+    }
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------- host entry points
+HcclResult SmIssueLaunch(const DevComm *devComm, const SmLaunch &l, cudaStream_t stream)
+{
+    if (l.kernel == K_BATCH_SEND_RECV) {
+        KBatchSendRecv<false><<<l.ctas, kThreads, 0, stream>>>(devComm, l.batch, nullptr);
+    } else {
+        CollKernelFn fn = KernelFor<false>(l);
+        if (!fn) return HCCL_E_NOT_SUPPORT;
+        fn<<<l.ctas, kThreads, 0, stream>>>(devComm, l.args, nullptr);
+    }
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { return HCCL_E_RUNTIME; }
+    return HCCL_SUCCESS;
+}
+
+// Emulation: one cooperative launch covers all ranks (grid = ctas x nranks); argument blocks come from device memory.
+HcclResult SmIssueEmuLaunch(const DevComm *devComms, int nranks, const SmLaunch &l0, const CollArgs *devArgs, const BatchArgs *devBatch,
+                            cudaStream_t stream, bool pairKernel)
+{
+    dim3 grid(l0.ctas, nranks), block(kThreads);
+    cudaError_t e;
+    if (l0.kernel == K_BATCH_SEND_RECV) {
+        BatchArgs dummyB = l0.batch;
+        void *params[] = {(void *)&devComms, (void *)&dummyB, (void *)&devBatch};
+        e = cudaLaunchCooperativeKernel((void *)KBatchSendRecv<true>, grid, block, params, 0, stream);
+    } else {
+        CollKernelFn fn = pairKernel ? (CollKernelFn)KSendRecvPair<true> : KernelFor<true>(l0);
+        if (!fn) return HCCL_E_NOT_SUPPORT;
+        CollArgs dummy = l0.args;
+        void *params[] = {(void *)&devComms, (void *)&dummy, (void *)&devArgs};
+        e = cudaLaunchCooperativeKernel((void *)fn, grid, block, params, 0, stream);
+    }
+    if (e != cudaSuccess) return e == cudaErrorCooperativeLaunchTooLarge ? HCCL_E_PARA : HCCL_E_RUNTIME;
+    return HCCL_SUCCESS;
+}
+
+}  // namespace hccl

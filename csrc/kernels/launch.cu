@@ -1,0 +1,257 @@
+// Host side of the SM / NVLS engine: plan an operator into launches, issue them on the caller's stream, and the
+// single-GPU emulation harness used by the tests (all ranks on one device, one cooperative launch per chunk).
+#include "launch.h"
+#include <cuda_runtime.h>
+#include <cstring>
+#include "../common/dtype.h"
+#include "../common/log.h"
+#include "coll_args.h"
+#include "hccl/hccl_dfx.h"
+
+namespace hccl {
+
+HcclResult SmIssueLaunch(const DevComm *devComm, const SmLaunch &l, cudaStream_t stream);
+HcclResult SmIssueEmuLaunch(const DevComm *devComms, int nranks, const SmLaunch &l0, const CollArgs *devArgs, const BatchArgs *devBatch,
+                            cudaStream_t stream, bool pairKernel);
+
+const std::vector<SmAlgoDesc> &SmAlgorithms()
+{
+    static const std::vector<SmAlgoDesc> v = {
+        {"SmAllReduceMesh1DOneShot", HCCL_CMD_ALLREDUCE, false}, {"SmAllReduceMesh1DTwoShot", HCCL_CMD_ALLREDUCE, false},
+        {"NvlsAllReduceOneShot", HCCL_CMD_ALLREDUCE, true}, {"NvlsAllReduceTwoShot", HCCL_CMD_ALLREDUCE, true},
+        {"SmAllGatherMesh1D", HCCL_CMD_ALLGATHER, false}, {"SmAllGatherVMesh1D", HCCL_CMD_ALLGATHER_V, false},
+        {"SmReduceScatterMesh1D", HCCL_CMD_REDUCE_SCATTER, false}, {"SmReduceScatterVMesh1D", HCCL_CMD_REDUCE_SCATTER_V, false},
+        {"NvlsReduceScatter", HCCL_CMD_REDUCE_SCATTER, true},
+        {"SmBroadcastMesh1D", HCCL_CMD_BROADCAST, false}, {"NvlsBroadcast", HCCL_CMD_BROADCAST, true},
+        {"SmReduceMesh1D", HCCL_CMD_REDUCE, false}, {"SmScatterMesh1D", HCCL_CMD_SCATTER, false},
+        {"SmAlltoAllMesh1D", HCCL_CMD_ALLTOALL, false}, {"SmAlltoAllVMesh1D", HCCL_CMD_ALLTOALLV, false},
+        {"SmAlltoAllVCMesh1D", HCCL_CMD_ALLTOALLVC, false}, {"SmBarrierMesh1D", HCCL_CMD_BARRIER, false},
+        {"SmSend", HCCL_CMD_SEND, false}, {"SmRecv", HCCL_CMD_RECEIVE, false}, {"SmBatchSendRecv", HCCL_CMD_BATCH_SEND_RECV, false},
+    };
+    return v;
+}
+
+uint32_t SmDefaultCtas(HcclCMDType, const std::string &, uint64_t bytes, uint32_t) { return SmCtasFor(bytes, 0); }
+
+HcclResult SmOrchestrate(Comm *c, OpParam &p, const std::string &algName)
+{
+    SmPlanCtx ctx;
+    ctx.rank = c->rank;
+    ctx.nranks = c->nranks;
+    ctx.cclBytes = c->devComm.cclBytes;
+    ctx.mailboxBytes = c->devComm.mailboxBytes;
+    ctx.maxCtas = c->env.maxCtas;
+    ctx.nvls = c->mcHeap != nullptr;
+    std::vector<SmLaunch> launches;
+    HcclResult r = SmPlanOp(ctx, p, algName, &launches);
+    if (r != HCCL_SUCCESS) return r;
+    for (const SmLaunch &l : launches) {
+        HcclResult lr = SmIssueLaunch(c->devCommPtr, l, p.stream);
+        if (lr != HCCL_SUCCESS) {
+            HCCL_ERROR("launch of %s failed: %s", algName.c_str(), cudaGetErrorString(cudaGetLastError()));
+            return lr;
+        }
+        c->counters.kernelsLaunched++;
+        c->counters.chunkLoops++;
+    }
+    return HCCL_SUCCESS;
+}
+
+// ------------------------------------------------------------------------------------------------ emulation world
+struct EmuWorld {
+    int nranks = 0;
+    std::vector<char *> heaps;
+    DevComm *devComms = nullptr;
+    std::vector<DevComm> hostComms;
+    DevStatus *status = nullptr;       // pinned, one per rank
+    CollArgs *devArgs = nullptr;
+    BatchArgs *devBatch = nullptr;
+    uint64_t cclBytes = 0, mailboxBytes = 0;
+};
+
+}  // namespace hccl
+
+using namespace hccl;
+
+#define EMU_RT(call)                                                                              \
+    do {                                                                                          \
+        cudaError_t _e = (call);                                                                  \
+        if (_e != cudaSuccess) { HCCL_ERROR("%s: %s", #call, cudaGetErrorString(_e)); return HCCL_E_RUNTIME; } \
+    } while (0)
+
+extern "C" {
+
+HcclResult HcclEmuCreate(uint32_t nranks, uint64_t cclBytes, uint32_t waitTimeoutMs, void **emu)
+{
+    if (!emu || nranks == 0 || nranks > (uint32_t)kMaxRanks) return HCCL_E_PARA;
+    auto *w = new EmuWorld();
+    w->nranks = (int)nranks;
+    w->cclBytes = (cclBytes + 127) & ~127ull;
+    w->mailboxBytes = 256 << 10;
+    uint64_t mailboxTotal = w->mailboxBytes * 2 * nranks;
+    uint64_t heapBytes = kHeapHeaderBytes + 2 * w->cclBytes + mailboxTotal;
+    EMU_RT(cudaHostAlloc((void **)&w->status, sizeof(DevStatus) * nranks, cudaHostAllocMapped));
+    memset(w->status, 0, sizeof(DevStatus) * nranks);
+    DevStatus *devStatus = nullptr;
+    EMU_RT(cudaHostGetDevicePointer((void **)&devStatus, w->status, 0));
+    w->heaps.resize(nranks);
+    for (uint32_t r = 0; r < nranks; ++r) {
+        EMU_RT(cudaMalloc((void **)&w->heaps[r], heapBytes));
+        EMU_RT(cudaMemset(w->heaps[r], 0, kHeapHeaderBytes));
+    }
+    w->hostComms.resize(nranks);
+    for (uint32_t r = 0; r < nranks; ++r) {
+        DevComm &d = w->hostComms[r];
+        memset(&d, 0, sizeof(d));
+        d.rank = (int)r; d.nranks = (int)nranks; d.heapBytes = heapBytes;
+        for (uint32_t q = 0; q < nranks; ++q) d.heap[q] = w->heaps[q];
+        d.mcHeap = nullptr;
+        d.cclOff[0] = kHeapHeaderBytes; d.cclOff[1] = kHeapHeaderBytes + w->cclBytes; d.cclBytes = w->cclBytes;
+        d.mailboxOff = kHeapHeaderBytes + 2 * w->cclBytes; d.mailboxBytes = w->mailboxBytes;
+        d.timeoutNs = (uint64_t)waitTimeoutMs * 1000000ull;
+        d.status = devStatus + r;
+        d.emuRanks = (int)nranks;
+    }
+    EMU_RT(cudaMalloc((void **)&w->devComms, sizeof(DevComm) * nranks));
+    EMU_RT(cudaMemcpy(w->devComms, w->hostComms.data(), sizeof(DevComm) * nranks, cudaMemcpyHostToDevice));
+    EMU_RT(cudaMalloc((void **)&w->devArgs, sizeof(CollArgs) * nranks));
+    EMU_RT(cudaMalloc((void **)&w->devBatch, sizeof(BatchArgs) * nranks));
+    EMU_RT(cudaDeviceSynchronize());
+    *emu = w;
+    return HCCL_SUCCESS;
+}
+
+HcclResult HcclEmuDestroy(void *emu)
+{
+    auto *w = (EmuWorld *)emu;
+    if (!w) return HCCL_E_PTR;
+    cudaDeviceSynchronize();
+    for (char *h : w->heaps) cudaFree(h);
+    cudaFree(w->devComms);
+    cudaFree(w->devArgs);
+    cudaFree(w->devBatch);
+    cudaFreeHost(w->status);
+    delete w;
+    return HCCL_SUCCESS;
+}
+
+// Runs one operator on all emulated ranks. ins/outs: per-rank device pointers. countMatrix: n*n elements for the
+// AlltoAllV family (row i = what rank i sends), n elements for AllGatherV / ReduceScatterV, else unused.
+HcclResult HcclEmuRun(void *emu, HcclCMDType op, const char *algName, void **ins, void **outs, uint64_t count, HcclDataType dataType,
+                      HcclReduceOp reduceOp, uint32_t root, const uint64_t *countMatrix, uint32_t maxCtas)
+{
+    auto *w = (EmuWorld *)emu;
+    if (!w || !algName) return HCCL_E_PTR;
+    uint32_t n = (uint32_t)w->nranks;
+    std::vector<std::vector<SmLaunch>> per(n);
+    for (uint32_t r = 0; r < n; ++r) {
+        OpParam p;
+        p.opType = op; p.inputPtr = ins ? ins[r] : nullptr; p.outputPtr = outs ? outs[r] : nullptr; p.count = count;
+        p.dtype = p.outDtype = dataType; p.reduceOp = reduceOp; p.root = root;
+        if (op == HCCL_CMD_ALLTOALLV || op == HCCL_CMD_ALLTOALLVC) {
+            if (!countMatrix) return HCCL_E_PTR;
+            p.sendCounts.resize(n); p.sendDispls.resize(n); p.recvCounts.resize(n); p.recvDispls.resize(n);
+            uint64_t so = 0, ro = 0;
+            for (uint32_t j = 0; j < n; ++j) {
+                p.sendCounts[j] = countMatrix[r * n + j]; p.sendDispls[j] = so; so += p.sendCounts[j];
+                p.recvCounts[j] = countMatrix[j * n + r]; p.recvDispls[j] = ro; ro += p.recvCounts[j];
+            }
+        } else if (op == HCCL_CMD_ALLGATHER_V || op == HCCL_CMD_REDUCE_SCATTER_V) {
+            if (!countMatrix) return HCCL_E_PTR;
+            auto &cnt = op == HCCL_CMD_ALLGATHER_V ? p.recvCounts : p.sendCounts;
+            auto &dsp = op == HCCL_CMD_ALLGATHER_V ? p.recvDispls : p.sendDispls;
+            cnt.assign(countMatrix, countMatrix + n);
+            dsp.resize(n);
+            uint64_t o = 0;
+            for (uint32_t j = 0; j < n; ++j) { dsp[j] = o; o += cnt[j]; }
+            p.count = cnt[r];
+        }
+        SmPlanCtx ctx{r, n, w->cclBytes, w->mailboxBytes, maxCtas ? maxCtas : 4u, false};
+        HcclResult pr = SmPlanOp(ctx, p, algName, &per[r]);
+        if (pr != HCCL_SUCCESS) return pr;
+    }
+    for (uint32_t r = 1; r < n; ++r) {
+        if (per[r].size() != per[0].size()) { HCCL_ERROR("emu: ranks disagree on the number of launches"); return HCCL_E_INTERNAL; }
+    }
+    for (size_t i = 0; i < per[0].size(); ++i) {
+        std::vector<CollArgs> args(n);
+        for (uint32_t r = 0; r < n; ++r) {
+            if (per[r][i].kernel != per[0][i].kernel || per[r][i].ctas != per[0][i].ctas) { HCCL_ERROR("emu: ranks disagree on launch %zu", i); return HCCL_E_INTERNAL; }
+            args[r] = per[r][i].args;
+        }
+        EMU_RT(cudaMemcpyAsync(w->devArgs, args.data(), sizeof(CollArgs) * n, cudaMemcpyHostToDevice, 0));
+        HcclResult lr = SmIssueEmuLaunch(w->devComms, (int)n, per[0][i], w->devArgs, w->devBatch, 0, false);
+        if (lr != HCCL_SUCCESS) { HCCL_ERROR("emu launch failed: %s", cudaGetErrorString(cudaGetLastError())); return lr; }
+        EMU_RT(cudaStreamSynchronize(0));
+    }
+    for (uint32_t r = 0; r < n; ++r) if (w->status[r].code != 0) return HCCL_E_TIMEOUT;
+    return HCCL_SUCCESS;
+}
+
+// Point-to-point in emulation: items[i] = {src, dst, srcBuf, dstBuf, bytes}; all transfers run in ONE launch through
+// the batch kernel (each rank gets its own BatchArgs).
+HcclResult HcclEmuBatchSendRecv(void *emu, uint32_t nTransfers, const uint32_t *srcRanks, const uint32_t *dstRanks, void **srcBufs,
+                                void **dstBufs, const uint64_t *bytes)
+{
+    auto *w = (EmuWorld *)emu;
+    if (!w) return HCCL_E_PTR;
+    uint32_t n = (uint32_t)w->nranks;
+    std::vector<SmLaunch> per(n);
+    uint32_t maxCtas = 0;
+    for (uint32_t r = 0; r < n; ++r) {
+        OpParam p;
+        p.opType = HCCL_CMD_BATCH_SEND_RECV;
+        p.dtype = HCCL_DATA_TYPE_INT8;
+        for (uint32_t t = 0; t < nTransfers; ++t) {
+            if (srcRanks[t] == r) p.items.push_back(HcclSendRecvItem{HCCL_SEND, srcBufs[t], bytes[t], HCCL_DATA_TYPE_INT8, dstRanks[t]});
+            if (dstRanks[t] == r) p.items.push_back(HcclSendRecvItem{HCCL_RECV, dstBufs[t], bytes[t], HCCL_DATA_TYPE_INT8, srcRanks[t]});
+        }
+        std::vector<SmLaunch> ls;
+        SmPlanCtx ctx{r, n, w->cclBytes, w->mailboxBytes, 0, false};
+        if (p.items.empty()) { SmLaunch l{}; l.kernel = K_BATCH_SEND_RECV; l.batch.nItems = 0; l.batch.nQueues = 0; l.ctas = kP2pBlocks; ls.push_back(l); }
+        else { HcclResult pr = SmPlanOp(ctx, p, "SmBatchSendRecv", &ls); if (pr != HCCL_SUCCESS) return pr; }
+        per[r] = ls[0];
+        maxCtas = std::max(maxCtas, per[r].ctas);
+    }
+    std::vector<BatchArgs> b(n);
+    for (uint32_t r = 0; r < n; ++r) b[r] = per[r].batch;
+    EMU_RT(cudaMemcpyAsync(w->devBatch, b.data(), sizeof(BatchArgs) * n, cudaMemcpyHostToDevice, 0));
+    SmLaunch l0 = per[0];
+    l0.ctas = maxCtas;
+    HcclResult lr = SmIssueEmuLaunch(w->devComms, (int)n, l0, w->devArgs, w->devBatch, 0, false);
+    if (lr != HCCL_SUCCESS) { HCCL_ERROR("emu batch launch failed: %s", cudaGetErrorString(cudaGetLastError())); return lr; }
+    EMU_RT(cudaStreamSynchronize(0));
+    for (uint32_t r = 0; r < n; ++r) if (w->status[r].code != 0) return HCCL_E_TIMEOUT;
+    return HCCL_SUCCESS;
+}
+
+// Reads (and optionally clears) the status word of an emulated rank: out[0..7] = DevStatus fields.
+HcclResult HcclEmuStatus(void *emu, uint32_t rank, uint32_t *out, int clear)
+{
+    auto *w = (EmuWorld *)emu;
+    if (!w || !out || rank >= (uint32_t)w->nranks) return HCCL_E_PARA;
+    memcpy(out, &w->status[rank], sizeof(DevStatus));
+    if (clear) {
+        memset(&w->status[rank], 0, sizeof(DevStatus));
+        for (char *h : w->heaps) cudaMemset(h, 0, kHeapHeaderBytes);
+        cudaDeviceSynchronize();
+    }
+    return HCCL_SUCCESS;
+}
+
+// Test hook for the bounded wait: launches the barrier kernel for ONE emulated rank only, so its peers never
+// signal; the kernel must give up after the timeout, set the status word and return.
+HcclResult HcclEmuLonelyBarrier(void *emu, uint32_t rank)
+{
+    auto *w = (EmuWorld *)emu;
+    if (!w || rank >= (uint32_t)w->nranks) return HCCL_E_PARA;
+    SmLaunch l{};
+    l.kernel = K_BARRIER;
+    l.ctas = 1;
+    HcclResult lr = SmIssueLaunch(w->devComms + rank, l, 0);
+    if (lr != HCCL_SUCCESS) return lr;
+    EMU_RT(cudaStreamSynchronize(0));
+    return w->status[rank].code == 1 ? HCCL_E_TIMEOUT : HCCL_SUCCESS;
+}
+
+}  // extern "C"

@@ -1,0 +1,330 @@
+// Device-side building blocks of the SM / NVLS engine: system-scope flag accesses, bounded waits that report
+// instead of hanging, per-channel barriers with device-resident epochs, ping-pong selection of the CCL half,
+// vectorised block copies, typed reductions and multimem (NVLS) accessors.
+//
+// Replaces what HCCL's vector-core kernels get from AivCommBase (reference:
+// src/ops/op_common/template/aiv/aiv_communication_base_v2.h:439-446 Record, :495-505 WaitFlag -- an unbounded
+// poll there --, :550-571 BarrierAll, :650-713 CpGM2GM with reduce). Every wait here has a deadline taken from
+// DevComm::timeoutNs; on expiry the kernel writes a DevStatus record to pinned host memory, raises the abort flag
+// in its control block so sibling CTAs stop early, and returns normally: the context stays usable and the host
+// surfaces HCCL_E_TIMEOUT.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "../core/dev_comm.h"
+#include "hccl/hccl_types.h"
+
+namespace hccl {
+namespace dev {
+
+// ---------------------------------------------------------------------------------------------- flag accessors
+__device__ __forceinline__ uint32_t LdAcquireSys(const uint32_t *p)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint64_t LdAcquireSys64(const uint64_t *p)
+{
+    uint64_t v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void StReleaseSys(uint32_t *p, uint32_t v)
+{
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void StReleaseSys64(uint64_t *p, uint64_t v)
+{
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t LdVolatile(const uint32_t *p)
+{
+    uint32_t v;
+    asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint64_t GlobalTimerNs()
+{
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// ---------------------------------------------------------------------------------------------- kernel context
+struct KCtx {
+    const DevComm *c;
+    int rank, nranks;
+    char *heap;          // own heap
+    DevCtrl *ctrl;
+    DevFlags *flags;
+    uint32_t half;       // CCL half of this op
+    uint32_t chan;       // channel = blockIdx.x
+    uint32_t epoch;      // channel epoch at kernel entry; sync point i uses epoch + i
+    uint32_t syncs;      // sync points consumed so far
+    bool ok;             // false after a timeout
+    __device__ __forceinline__ char *PeerHeap(int r) const { return c->heap[r]; }
+    __device__ __forceinline__ char *Ccl(int r) const { return c->heap[r] + c->cclOff[half]; }
+    __device__ __forceinline__ char *Mc() const { return c->mcHeap + c->cclOff[half]; }
+};
+
+__device__ __forceinline__ void ReportTimeout(const KCtx &k, uint32_t peer, uint32_t phase, uint32_t observed, uint32_t expected)
+{
+    if (atomicCAS(&k.ctrl->abortFlag, 0u, 1u) == 0u) {
+        DevStatus *s = k.c->status;
+        s->rank = (uint32_t)k.rank;
+        s->peer = peer;
+        s->channel = k.chan;
+        s->phase = phase;
+        s->opSeq = k.ctrl->opCount;
+        s->observed = observed;
+        s->expected = expected;
+        __threadfence_system();
+        *((volatile uint32_t *)&s->code) = 1u;
+        __threadfence_system();
+    }
+}
+
+// Spins until *flag >= target (wrap-safe). Returns false on timeout or when a sibling CTA already aborted.
+__device__ __forceinline__ bool WaitFlagGe(const KCtx &k, const uint32_t *flag, uint32_t target, uint32_t peer, uint32_t phase)
+{
+    uint64_t start = 0;
+    uint32_t spins = 0;
+    while (true) {
+        uint32_t v = LdAcquireSys(flag);
+        if ((int32_t)(v - target) >= 0) return true;
+        if ((++spins & 0xffu) == 0) {
+            uint64_t now = GlobalTimerNs();
+            if (start == 0) start = now;
+            if (LdVolatile(&k.ctrl->abortFlag) != 0u) return false;
+            if (now - start > k.c->timeoutNs) { ReportTimeout(k, peer, phase, v, target); return false; }
+            __nanosleep(64);
+        }
+    }
+}
+__device__ __forceinline__ bool WaitFlagGe64(const KCtx &k, const uint64_t *flag, uint64_t target, uint32_t peer, uint32_t phase)
+{
+    uint64_t start = 0;
+    uint32_t spins = 0;
+    while (true) {
+        uint64_t v = LdAcquireSys64(flag);
+        if (v >= target) return true;
+        if ((++spins & 0xffu) == 0) {
+            uint64_t now = GlobalTimerNs();
+            if (start == 0) start = now;
+            if (LdVolatile(&k.ctrl->abortFlag) != 0u) return false;
+            if (now - start > k.c->timeoutNs) { ReportTimeout(k, peer, phase, (uint32_t)v, (uint32_t)target); return false; }
+            __nanosleep(64);
+        }
+    }
+}
+
+// Entry protocol of every collective kernel. EMU: several ranks share this GPU and blockIdx.y names the rank.
+// Reads the op counter (parity = CCL half) and the channel epoch, then takes a ticket; the last CTA to arrive
+// advances the op counter for the next launch.
+template <bool EMU> __device__ __forceinline__ KCtx EnterCollective(const DevComm *comms)
+{
+    __shared__ uint32_t sHalf, sEpoch;
+    KCtx k;
+    k.c = EMU ? &comms[blockIdx.y] : comms;
+    k.rank = k.c->rank;
+    k.nranks = k.c->nranks;
+    k.heap = k.c->heap[k.rank];
+    k.ctrl = CtrlOf(k.heap);
+    k.flags = FlagsOf(k.heap);
+    k.chan = blockIdx.x;
+    if (threadIdx.x == 0) {
+        uint32_t oc = LdVolatile(&k.ctrl->opCount);
+        sHalf = oc & 1u;
+        sEpoch = LdVolatile(&k.ctrl->chanEpoch[k.chan]);
+        __threadfence();
+        uint32_t t = atomicAdd(&k.ctrl->ticket, 1u);
+        if (t == gridDim.x - 1) {
+            k.ctrl->ticket = 0;
+            __threadfence();
+            *((volatile uint32_t *)&k.ctrl->opCount) = oc + 1u;
+        }
+    }
+    __syncthreads();
+    k.half = sHalf;
+    k.epoch = sEpoch;
+    k.syncs = 0;
+    k.ok = true;
+    return k;
+}
+
+__device__ __forceinline__ void LeaveCollective(KCtx &k)
+{
+    __syncthreads();
+    if (threadIdx.x == 0) *((volatile uint32_t *)&k.ctrl->chanEpoch[k.chan]) = k.epoch + k.syncs;
+}
+
+// Channel barrier across all ranks: every rank's CTA `chan` signals every peer and waits for every peer.
+// All stores issued by this CTA before the call are visible to a peer's CTA after its matching call returns.
+__device__ __forceinline__ bool ChannelBarrier(KCtx &k, uint32_t phase)
+{
+    k.syncs++;
+    uint32_t target = k.epoch + k.syncs;
+    __syncthreads();
+    bool mine = true;
+    int t = (int)threadIdx.x;
+    if (t < k.nranks && t != k.rank) {
+        StReleaseSys(&FlagsOf(k.PeerHeap(t))->barrier[k.chan][k.rank], target);
+        mine = WaitFlagGe(k, &k.flags->barrier[k.chan][t], target, (uint32_t)t, phase);
+    }
+    int all = __syncthreads_and(mine ? 1 : 0);
+    if (!all) k.ok = false;
+    return all != 0;
+}
+
+// One-directional variants for rooted operators.
+__device__ __forceinline__ void ChannelSignal(KCtx &k, int peer, uint32_t value)
+{
+    StReleaseSys(&FlagsOf(k.PeerHeap(peer))->barrier[k.chan][k.rank], value);
+}
+
+// ---------------------------------------------------------------------------------------------- partitioning
+// Part `b` of `total` bytes split over `parts` CTAs in 128-byte aligned pieces.
+struct Part { uint64_t off, len; };
+__device__ __forceinline__ Part PartOf(uint64_t total, uint32_t parts, uint32_t b)
+{
+    uint64_t per = ((total + parts - 1) / parts + 127) & ~127ull;
+    uint64_t off = per * b;
+    Part p;
+    p.off = off < total ? off : total;
+    p.len = off < total ? (total - off < per ? total - off : per) : 0;
+    return p;
+}
+
+// ---------------------------------------------------------------------------------------------- copies
+template <int UNROLL> __device__ __forceinline__ void CopyVec16(uint4 *__restrict__ d, const uint4 *__restrict__ s, uint64_t nvec)
+{
+    const uint64_t stride = (uint64_t)blockDim.x * UNROLL;
+    uint64_t i = threadIdx.x;
+    for (; i + (uint64_t)blockDim.x * (UNROLL - 1) < nvec; i += stride) {
+        uint4 v[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) v[u] = s[i + (uint64_t)u * blockDim.x];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) d[i + (uint64_t)u * blockDim.x] = v[u];
+    }
+    for (; i < nvec; i += blockDim.x) d[i] = s[i];
+}
+
+// Copies `n` bytes with all threads of the CTA. Any alignment; 16-byte vectors when both sides allow it.
+__device__ __forceinline__ void BlockCopy(void *dst, const void *src, uint64_t n)
+{
+    if (n == 0) return;
+    uintptr_t a = (uintptr_t)dst | (uintptr_t)src;
+    if ((a & 15u) == 0) {
+        uint64_t nvec = n >> 4;
+        CopyVec16<4>((uint4 *)dst, (const uint4 *)src, nvec);
+        uint64_t done = nvec << 4;
+        for (uint64_t i = done + threadIdx.x; i < n; i += blockDim.x) ((char *)dst)[i] = ((const char *)src)[i];
+    } else if ((a & 3u) == 0) {
+        uint64_t nw = n >> 2;
+        for (uint64_t i = threadIdx.x; i < nw; i += blockDim.x) ((uint32_t *)dst)[i] = ((const uint32_t *)src)[i];
+        for (uint64_t i = (nw << 2) + threadIdx.x; i < n; i += blockDim.x) ((char *)dst)[i] = ((const char *)src)[i];
+    } else {
+        for (uint64_t i = threadIdx.x; i < n; i += blockDim.x) ((char *)dst)[i] = ((const char *)src)[i];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------- typed reduction
+template <typename T> struct Acc { using type = T; };
+template <> struct Acc<__half> { using type = float; };
+template <> struct Acc<__nv_bfloat16> { using type = float; };
+
+template <typename T> __device__ __forceinline__ typename Acc<T>::type ToAcc(T v) { return v; }
+template <> __device__ __forceinline__ float ToAcc<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float ToAcc<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T FromAcc(typename Acc<T>::type v) { return v; }
+template <> __device__ __forceinline__ __half FromAcc<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 FromAcc<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+template <int OP, typename A> __device__ __forceinline__ A Combine(A a, A b)
+{
+    if (OP == HCCL_REDUCE_SUM) return a + b;
+    if (OP == HCCL_REDUCE_PROD) return a * b;
+    if (OP == HCCL_REDUCE_MAX) return a > b ? a : b;
+    return a < b ? a : b;
+}
+
+// out[i] = slot_0[i] (op) slot_1[i] ... (op) slot_{n-1}[i], slots in rank order (the same order on every rank, so
+// every rank that reduces the same data obtains identical bits). Half-precision types accumulate in fp32.
+// slot r lives at slotBase[r] (local or peer memory), all 16-byte aligned. `out2` optionally receives a second copy.
+template <typename T, int OP, int MAXR>
+__device__ __forceinline__ void ReduceSlots(T *out, T *out2, const char *const *slotBase, int nslots, uint64_t nElems)
+{
+    using A = typename Acc<T>::type;
+    constexpr int VE = 16 / sizeof(T);
+    bool vecOk = (((uintptr_t)out | (uintptr_t)out2) & 15u) == 0;
+    uint64_t nvec = vecOk ? nElems / VE : 0;
+    for (uint64_t i = threadIdx.x; i < nvec; i += blockDim.x) {
+        A acc[VE];
+        {
+            uint4 raw = ((const uint4 *)slotBase[0])[i];
+            const T *e = (const T *)&raw;
+#pragma unroll
+            for (int j = 0; j < VE; ++j) acc[j] = ToAcc<T>(e[j]);
+        }
+        for (int r = 1; r < nslots; ++r) {
+            uint4 raw = ((const uint4 *)slotBase[r])[i];
+            const T *e = (const T *)&raw;
+#pragma unroll
+            for (int j = 0; j < VE; ++j) acc[j] = Combine<OP, A>(acc[j], ToAcc<T>(e[j]));
+        }
+        uint4 res;
+        T *e = (T *)&res;
+#pragma unroll
+        for (int j = 0; j < VE; ++j) e[j] = FromAcc<T>(acc[j]);
+        ((uint4 *)out)[i] = res;
+        if (out2) ((uint4 *)out2)[i] = res;
+    }
+    for (uint64_t i = nvec * VE + threadIdx.x; i < nElems; i += blockDim.x) {
+        A acc = ToAcc<T>(((const T *)slotBase[0])[i]);
+        for (int r = 1; r < nslots; ++r) acc = Combine<OP, A>(acc, ToAcc<T>(((const T *)slotBase[r])[i]));
+        T v = FromAcc<T>(acc);
+        out[i] = v;
+        if (out2) out2[i] = v;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------- multimem (NVLS)
+// 16-byte reduce-load from the multicast address: the switch returns the element-wise reduction over all ranks.
+template <typename T, int OP> struct MultimemLdReduce;
+template <> struct MultimemLdReduce<float, HCCL_REDUCE_SUM> {
+    __device__ __forceinline__ static uint4 Ld(const void *mc)
+    {
+        uint4 v;
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+        return v;
+    }
+};
+#define HCCL_MM_HALF(T, PTXT, OPV, OPNAME, ACC)                                                                                    \
+    template <> struct MultimemLdReduce<T, OPV> {                                                                                  \
+        __device__ __forceinline__ static uint4 Ld(const void *mc)                                                                 \
+        {                                                                                                                          \
+            uint4 v;                                                                                                               \
+            asm volatile("multimem.ld_reduce.relaxed.sys.global." OPNAME ACC ".v4." PTXT " {%0,%1,%2,%3}, [%4];"                   \
+                         : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");                                       \
+            return v;                                                                                                              \
+        }                                                                                                                          \
+    };
+HCCL_MM_HALF(__nv_bfloat16, "bf16x2", HCCL_REDUCE_SUM, "add", ".acc::f32")
+HCCL_MM_HALF(__nv_bfloat16, "bf16x2", HCCL_REDUCE_MAX, "max", "")
+HCCL_MM_HALF(__nv_bfloat16, "bf16x2", HCCL_REDUCE_MIN, "min", "")
+HCCL_MM_HALF(__half, "f16x2", HCCL_REDUCE_SUM, "add", ".acc::f32")
+HCCL_MM_HALF(__half, "f16x2", HCCL_REDUCE_MAX, "max", "")
+HCCL_MM_HALF(__half, "f16x2", HCCL_REDUCE_MIN, "min", "")
+#undef HCCL_MM_HALF
+
+__device__ __forceinline__ void MultimemSt16(void *mc, uint4 v)
+{
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+}  // namespace dev
+}  // namespace hccl

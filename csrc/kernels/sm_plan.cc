@@ -1,0 +1,216 @@
+#include <algorithm>
+#include <functional>
+#include "../common/dtype.h"
+#include "../common/log.h"
+#include "coll_args.h"
+
+namespace hccl {
+
+namespace {
+uint64_t Down128(uint64_t v) { return v & ~127ull; }
+uint64_t Up128(uint64_t v) { return (v + 127) & ~127ull; }
+uint64_t Clamp(uint64_t total, uint64_t lo, uint64_t chunk) { return total <= lo ? 0 : std::min(chunk, total - lo); }
+}  // namespace
+
+// Enough CTAs to keep NVLink busy (about 1 MB in flight at 512 threads x 4 x 16 B per CTA), few for small payloads
+// where launch and flag latency dominate.
+uint32_t SmCtasFor(uint64_t bytes, uint32_t maxCtas)
+{
+    uint32_t c;
+    if (bytes <= (32u << 10)) c = 1;
+    else if (bytes <= (256u << 10)) c = 4;
+    else if (bytes <= (2u << 20)) c = 16;
+    else if (bytes <= (16u << 20)) c = 32;
+    else c = 64;
+    if (maxCtas) c = std::min(c, maxCtas);
+    return std::max(1u, std::min<uint32_t>(c, kMaxChannels));
+}
+
+HcclResult SmPlanOp(const SmPlanCtx &ctx, const OpParam &p, const std::string &alg, std::vector<SmLaunch> *out)
+{
+    const uint32_t n = ctx.nranks, me = ctx.rank;
+    const uint32_t es = DataTypeSize(p.dtype);
+    const uint64_t ccl = ctx.cclBytes;
+    SmLaunch base{};
+    base.dtype = p.dtype;
+    base.args.elemSize = es;
+    base.args.root = p.root;
+    base.args.op = (uint32_t)p.reduceOp;
+    base.args.peer = p.peer;
+
+    // chunk loop: calls emit(lo, n) for element ranges of at most maxCount
+    auto loop = [&](uint64_t total, uint64_t maxCount, const std::function<void(uint64_t, uint64_t)> &emit) -> HcclResult {
+        if (maxCount == 0) { HCCL_ERROR("%s: CCL buffer of %llu bytes is too small for %u ranks", alg.c_str(), (unsigned long long)ccl, n); return HCCL_E_MEMORY; }
+        for (uint64_t lo = 0; lo < total; lo += maxCount) emit(lo, std::min(maxCount, total - lo));
+        return HCCL_SUCCESS;
+    };
+    auto push = [&](SmKernelId k, uint64_t lo, uint64_t cnt, uint64_t ctaBytes, const std::function<void(SmLaunch &)> &fill) {
+        SmLaunch l = base;
+        l.kernel = k;
+        l.args.count = cnt;
+        l.args.bytes = cnt * es;
+        l.ctas = SmCtasFor(ctaBytes, ctx.maxCtas);
+        (void)lo;
+        fill(l);
+        out->push_back(l);
+    };
+    const char *in = (const char *)p.inputPtr;
+    char *outp = (char *)p.outputPtr;
+
+    if (alg == "SmAllReduceMesh1DOneShot" || alg == "NvlsAllReduceOneShot") {
+        bool nv = alg[0] == 'N';
+        if (nv && (!ctx.nvls || (p.count * es) % 16 != 0)) return HCCL_E_NOT_SUPPORT;
+        uint64_t maxCount = nv ? Down128(ccl) / es : Down128(ccl / n) / es;
+        return loop(p.count, maxCount, [&](uint64_t lo, uint64_t cnt) {
+            push(nv ? K_ALLREDUCE_NVLS_ONESHOT : K_ALLREDUCE_ONESHOT, lo, cnt, cnt * es, [&](SmLaunch &l) { l.args.in = in + lo * es; l.args.out = outp + lo * es; });
+        });
+    }
+    if (alg == "SmAllReduceMesh1DTwoShot" || alg == "NvlsAllReduceTwoShot") {
+        bool nv = alg[0] == 'N';
+        if (nv && (!ctx.nvls || (p.count * es) % 16 != 0)) return HCCL_E_NOT_SUPPORT;
+        uint64_t maxSlice = Down128(ccl / (nv ? 2 * n : n + 1));
+        uint64_t maxCount = maxSlice * n / es;
+        return loop(p.count, maxCount, [&](uint64_t lo, uint64_t cnt) {
+            push(nv ? K_ALLREDUCE_NVLS_TWOSHOT : K_ALLREDUCE_TWOSHOT, lo, cnt, cnt * es / n * 2, [&](SmLaunch &l) { l.args.in = in + lo * es; l.args.out = outp + lo * es; });
+        });
+    }
+    if (alg == "SmAllGatherMesh1D" || alg == "SmAllGatherVMesh1D") {
+        bool v = p.opType == HCCL_CMD_ALLGATHER_V;
+        uint64_t total = v ? *std::max_element(p.recvCounts.begin(), p.recvCounts.end()) : p.count;
+        return loop(total, Down128(ccl) / es, [&](uint64_t lo, uint64_t cnt) {
+            push(K_ALLGATHER_V, lo, cnt, cnt * es * (n - 1), [&](SmLaunch &l) {
+                l.args.in = in + lo * es;
+                l.args.out = outp;
+                for (uint32_t r = 0; r < n; ++r) {
+                    l.args.recvBytes[r] = (v ? Clamp(p.recvCounts[r], lo, cnt) : cnt) * es;
+                    l.args.recvOff[r] = ((v ? p.recvDispls[r] : (uint64_t)r * p.count) + lo) * es;
+                }
+            });
+        });
+    }
+    if (alg == "SmReduceScatterMesh1D" || alg == "SmReduceScatterVMesh1D" || alg == "NvlsReduceScatter") {
+        bool v = p.opType == HCCL_CMD_REDUCE_SCATTER_V;
+        bool nv = alg[0] == 'N';
+        if (nv && (!ctx.nvls || v || (p.count * es) % 16 != 0)) return HCCL_E_NOT_SUPPORT;
+        uint64_t total = v ? *std::max_element(p.sendCounts.begin(), p.sendCounts.end()) : p.count;
+        return loop(total, Down128(ccl / n) / es, [&](uint64_t lo, uint64_t cnt) {
+            push(nv ? K_REDUCESCATTER_NVLS : K_REDUCESCATTER_V, lo, cnt, cnt * es * (n - 1), [&](SmLaunch &l) {
+                l.args.in = in;
+                l.args.out = outp + lo * es;
+                for (uint32_t r = 0; r < n; ++r) {
+                    l.args.sendBytes[r] = (v ? Clamp(p.sendCounts[r], lo, cnt) : cnt) * es;
+                    l.args.sendOff[r] = ((v ? p.sendDispls[r] : (uint64_t)r * p.count) + lo) * es;
+                }
+            });
+        });
+    }
+    if (alg == "SmBroadcastMesh1D" || alg == "NvlsBroadcast") {
+        bool nv = alg[0] == 'N';
+        if (nv && (!ctx.nvls || (p.count * es) % 16 != 0)) return HCCL_E_NOT_SUPPORT;
+        return loop(p.count, Down128(ccl) / es, [&](uint64_t lo, uint64_t cnt) {
+            push(nv ? K_BROADCAST_NVLS : K_BROADCAST, lo, cnt, cnt * es, [&](SmLaunch &l) { l.args.in = outp + lo * es; l.args.out = outp + lo * es; });
+        });
+    }
+    if (alg == "SmReduceMesh1D") {
+        return loop(p.count, Down128(ccl / n) / es, [&](uint64_t lo, uint64_t cnt) {
+            push(K_REDUCE, lo, cnt, cnt * es, [&](SmLaunch &l) { l.args.in = in + lo * es; l.args.out = outp ? outp + lo * es : nullptr; });
+        });
+    }
+    if (alg == "SmScatterMesh1D") {
+        return loop(p.count, Down128(ccl / n) / es, [&](uint64_t lo, uint64_t cnt) {
+            push(K_SCATTER, lo, cnt, cnt * es, [&](SmLaunch &l) {
+                l.args.in = in;
+                l.args.out = outp + lo * es;
+                for (uint32_t r = 0; r < n; ++r) { l.args.sendBytes[r] = cnt * es; l.args.sendOff[r] = ((uint64_t)r * p.count + lo) * es; }
+            });
+        });
+    }
+    if (alg == "SmAlltoAllMesh1D") {
+        uint64_t usable = ccl > kA2aMetaBytes ? ccl - kA2aMetaBytes : 0;
+        return loop(p.count, Down128(usable / n) / es, [&](uint64_t lo, uint64_t cnt) {
+            push(K_ALLTOALL_V, lo, cnt, cnt * es * (n - 1), [&](SmLaunch &l) {
+                l.args.in = in;
+                l.args.out = outp;
+                for (uint32_t r = 0; r < n; ++r) {
+                    l.args.sendBytes[r] = l.args.recvBytes[r] = cnt * es;
+                    l.args.sendOff[r] = l.args.recvOff[r] = ((uint64_t)r * p.count + lo) * es;
+                }
+            });
+        });
+    }
+    if (alg == "SmAlltoAllVMesh1D" || alg == "SmAlltoAllVCMesh1D") {
+        uint32_t esOut = DataTypeSize(p.outDtype);
+        uint64_t packed = 0, moved = 0;
+        for (uint32_t r = 0; r < n; ++r) if (r != me) { packed += Up128(p.sendCounts[r] * es); moved += p.recvCounts[r] * esOut; }
+        if (packed + kA2aMetaBytes > ccl) {
+            HCCL_ERROR("AlltoAllV: this rank sends %llu bytes, more than the CCL buffer holds (%llu); raise HCCL_BUFFSIZE", (unsigned long long)packed,
+                       (unsigned long long)(ccl - kA2aMetaBytes));
+            return HCCL_E_MEMORY;
+        }
+        push(K_ALLTOALL_V, 0, 0, std::max(packed, moved), [&](SmLaunch &l) {
+            l.args.in = in;
+            l.args.out = outp;
+            for (uint32_t r = 0; r < n; ++r) {
+                l.args.sendBytes[r] = p.sendCounts[r] * es; l.args.sendOff[r] = p.sendDispls[r] * es;
+                l.args.recvBytes[r] = p.recvCounts[r] * esOut; l.args.recvOff[r] = p.recvDispls[r] * esOut;
+            }
+        });
+        return HCCL_SUCCESS;
+    }
+    if (alg == "SmBarrierMesh1D") {
+        push(K_BARRIER, 0, 0, 0, [&](SmLaunch &) {});
+        return HCCL_SUCCESS;
+    }
+    if (alg == "SmSend" || alg == "SmRecv") {
+        bool snd = alg == "SmSend";
+        push(snd ? K_SEND : K_RECV, 0, p.count, 0, [&](SmLaunch &l) { l.args.in = in; l.args.out = outp; l.ctas = kP2pBlocks; });
+        return HCCL_SUCCESS;
+    }
+    if (alg == "SmBatchSendRecv") {
+        // queue per (peer, direction); self pairs become local copies. Same ordering rules as the host engine.
+        std::vector<HcclSendRecvItem> sends, recvs, selfS, selfR;
+        for (auto &it : p.items) {
+            if (it.remoteRank == me) (it.sendRecvType == HCCL_SEND ? selfS : selfR).push_back(it);
+            else (it.sendRecvType == HCCL_SEND ? sends : recvs).push_back(it);
+        }
+        if (selfS.size() != selfR.size()) return HCCL_E_PARA;
+        if (p.items.size() > (size_t)kMaxBatchItems) return HCCL_E_NOT_SUPPORT;   // the host-issued engine takes large batches
+        SmLaunch l = base;
+        l.kernel = K_BATCH_SEND_RECV;
+        BatchArgs &b = l.batch;
+        b.nItems = 0;
+        std::vector<std::pair<uint32_t, uint32_t>> queues;   // (peer, dir)
+        auto queueOf = [&](uint32_t peer, uint32_t dir) {
+            for (size_t q = 0; q < queues.size(); ++q) if (queues[q] == std::make_pair(peer, dir)) return (uint32_t)q;
+            queues.push_back({peer, dir});
+            return (uint32_t)queues.size() - 1;
+        };
+        std::vector<uint32_t> orderInQueue;
+        auto add = [&](const HcclSendRecvItem &it, uint32_t isSend) {
+            BatchItem &bi = b.items[b.nItems++];
+            bi.buf = it.buf; bi.bytes = it.count * DataTypeSize(it.dataType); bi.peer = it.remoteRank; bi.isSend = isSend; bi.buf2 = nullptr;
+            bi.queue = queueOf(it.remoteRank, isSend);
+            if (orderInQueue.size() <= bi.queue) orderInQueue.resize(bi.queue + 1, 0);
+            bi.order = orderInQueue[bi.queue]++;
+        };
+        for (auto &it : sends) add(it, 1);
+        for (auto &it : recvs) add(it, 0);
+        for (size_t i = 0; i < selfS.size(); ++i) {
+            uint64_t sb = selfS[i].count * DataTypeSize(selfS[i].dataType), rb = selfR[i].count * DataTypeSize(selfR[i].dataType);
+            if (sb != rb) return HCCL_E_PARA;
+            BatchItem &bi = b.items[b.nItems++];
+            bi.buf = selfS[i].buf; bi.buf2 = selfR[i].buf; bi.bytes = sb; bi.peer = me; bi.isSend = 2;
+            bi.queue = queueOf(me, 2 + (uint32_t)i);
+            bi.order = 0;
+        }
+        b.nQueues = (uint32_t)queues.size();
+        l.ctas = b.nQueues * kP2pBlocks;
+        if (l.ctas > (uint32_t)kMaxChannels) return HCCL_E_NOT_SUPPORT;
+        out->push_back(l);
+        return HCCL_SUCCESS;
+    }
+    HCCL_ERROR("unknown SM algorithm %s", alg.c_str());
+    return HCCL_E_NOT_FOUND;
+}
+
+}  // namespace hccl

@@ -1,0 +1,125 @@
+// Plain bf16 GEMM entry (C = A * B^T, both K-major) on the tcgen05 kernel, and the helpers the fused ops share.
+#include <mutex>
+#include "../common/log.h"
+#include "gemm_host.h"
+#include "gemm_sm100.cuh"
+#include "hccl/hccl_mc2.h"
+
+namespace hccl {
+namespace mc2 {
+
+namespace {
+using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                              const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn GetEncode()
+{
+    static EncodeFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        cudaDriverEntryPointQueryResult q;
+        void *p = nullptr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess) fn = (EncodeFn)p;
+        else (void)cudaGetLastError();
+    });
+    return fn;
+}
+}  // namespace
+
+HcclResult EncodeTmap2D(CUtensorMap *out, const void *base, uint64_t rows, uint64_t cols, uint64_t pitchBytes, uint32_t boxRows, uint32_t boxCols,
+                        uint32_t elemBytes)
+{
+    EncodeFn enc = GetEncode();
+    if (!enc) { HCCL_ERROR("cuTensorMapEncodeTiled is unavailable"); return HCCL_E_UNAVAIL; }
+    if (((uintptr_t)base & 15u) || (pitchBytes & 15u) || boxCols * elemBytes != 128 || boxRows > 256) {
+        HCCL_ERROR("tensor map: base %p / pitch %llu must be 16-byte aligned, box %ux%u", base, (unsigned long long)pitchBytes, boxRows, boxCols);
+        return HCCL_E_PARA;
+    }
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {pitchBytes};
+    cuuint32_t box[2] = {boxCols, boxRows};
+    cuuint32_t estr[2] = {1, 1};
+    CUtensorMapDataType dt = elemBytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    CUresult r = enc(out, dt, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { HCCL_ERROR("cuTensorMapEncodeTiled failed: %d", (int)r); return HCCL_E_DRV; }
+    return HCCL_SUCCESS;
+}
+
+uint32_t *GemmErrorWord()
+{
+    static uint32_t *w[64] = {nullptr};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!w[dev]) {
+        cudaMalloc((void **)&w[dev], 4);
+        cudaMemset(w[dev], 0, 4);
+    }
+    return w[dev];
+}
+
+HcclResult GemmCheckError()
+{
+    uint32_t v = 0;
+    if (cudaMemcpy(&v, GemmErrorWord(), 4, cudaMemcpyDeviceToHost) != cudaSuccess) return HCCL_E_RUNTIME;
+    if (v) { cudaMemset(GemmErrorWord(), 0, 4); return HCCL_E_TIMEOUT; }
+    return HCCL_SUCCESS;
+}
+
+int SmCount()
+{
+    static int n[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!n[dev]) cudaDeviceGetAttribute(&n[dev], cudaDevAttrMultiProcessorCount, dev);
+    return n[dev];
+}
+
+template <int BN> static HcclResult LaunchPlain(const void *a, const void *b, void *c, uint32_t M, uint32_t N, uint32_t K, bool outFp32, cudaStream_t s)
+{
+    GemmParams p{};
+    CHK_RET(EncodeTmap2D(&p.tmapA, a, M, K, (uint64_t)K * 2, kBM, kBK, 2));
+    CHK_RET(EncodeTmap2D(&p.tmapB, b, N, K, (uint64_t)K * 2, BN, kBK, 2));
+    p.C = c; p.M = M; p.N = N; p.K = K; p.ldc = N; p.outFp32 = outFp32; p.groupM = 16; p.errorWord = GemmErrorWord();
+    using S = GemmSmem<BN>;
+    static bool attrSet = false;
+    auto kern = GemmKernel<BN, PlainPolicy>;
+    size_t smem = S::kTotal + 1024;
+    if (!attrSet) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return HCCL_E_RUNTIME;
+        attrSet = true;
+    }
+    uint32_t tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
+    uint32_t grid = std::min<uint32_t>(tiles, (uint32_t)SmCount());
+    kern<<<grid, kGemmThreads, smem, s>>>(p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { HCCL_ERROR("GEMM launch failed: %s", cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
+    return HCCL_SUCCESS;
+}
+
+}  // namespace mc2
+}  // namespace hccl
+
+using namespace hccl;
+using namespace hccl::mc2;
+
+extern "C" {
+
+// C[M,N] = A[M,K] * B[N,K]^T, bf16 operands (row-major, K contiguous), bf16 or fp32 output. K % 8 == 0, N % 8 == 0.
+HcclResult HcclGemmBf16(const void *a, const void *b, void *c, uint64_t m, uint64_t n, uint64_t k, int outFp32, cudaStream_t stream)
+{
+    if (!a || !b || !c) return HCCL_E_PTR;
+    if (m == 0 || n == 0 || k == 0 || (k % 8) || (n % 8) || m > 0x7fffffff || n > 0x7fffffff || k > 0x7fffffff) {
+        HCCL_ERROR("HcclGemmBf16: unsupported shape %llux%llux%llu (K and N must be multiples of 8)", (unsigned long long)m, (unsigned long long)n, (unsigned long long)k);
+        return HCCL_E_PARA;
+    }
+    // narrow tiles when the problem has too few 128x256 tiles to fill the GPU
+    uint64_t tiles256 = ((m + 127) / 128) * ((n + 255) / 256);
+    if (tiles256 >= (uint64_t)SmCount() || n % 256 == 0 && tiles256 * 2 > (uint64_t)SmCount()) return LaunchPlain<256>(a, b, c, m, n, k, outFp32 != 0, stream);
+    uint64_t tiles128 = ((m + 127) / 128) * ((n + 127) / 128);
+    if (tiles128 >= (uint64_t)SmCount() / 2) return LaunchPlain<128>(a, b, c, m, n, k, outFp32 != 0, stream);
+    return LaunchPlain<64>(a, b, c, m, n, k, outFp32 != 0, stream);
+}
+
+HcclResult HcclGemmCheckError(void) { return GemmCheckError(); }
+
+}  // extern "C"

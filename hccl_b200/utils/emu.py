@@ -1,0 +1,86 @@
+"""Single-GPU emulation of a multi-rank communicator for kernel tests.
+
+All ranks' heaps live on the current CUDA device and each operator chunk is ONE cooperative launch whose
+`blockIdx.y` is the rank, so CTAs that wait for each other are guaranteed to be co-resident. This exercises the
+flag protocols, index arithmetic and reductions of the SM-engine kernels without NVLink.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional, Sequence
+
+import torch
+
+from .._lib import check, lib
+from ..types import DataType, ReduceOp, from_torch
+
+
+def _decl():
+    l = lib()
+    vp, u32, u64, i32 = ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint64, ctypes.c_int
+    P = ctypes.POINTER
+    l.HcclEmuCreate.argtypes = [u32, u64, u32, P(vp)]
+    l.HcclEmuDestroy.argtypes = [vp]
+    l.HcclEmuRun.argtypes = [vp, i32, ctypes.c_char_p, P(vp), P(vp), u64, i32, i32, u32, P(u64), u32]
+    l.HcclEmuBatchSendRecv.argtypes = [vp, u32, P(u32), P(u32), P(vp), P(vp), P(u64)]
+    l.HcclEmuStatus.argtypes = [vp, u32, P(u32), i32]
+    l.HcclEmuLonelyBarrier.argtypes = [vp, u32]
+    for f in (l.HcclEmuCreate, l.HcclEmuDestroy, l.HcclEmuRun, l.HcclEmuBatchSendRecv, l.HcclEmuStatus, l.HcclEmuLonelyBarrier):
+        f.restype = ctypes.c_int
+    return l
+
+
+class EmuWorld:
+    def __init__(self, nranks: int, ccl_bytes: int = 8 << 20, wait_timeout_ms: int = 2000):
+        self._l = _decl()
+        self.n = nranks
+        h = ctypes.c_void_p()
+        check(self._l.HcclEmuCreate(nranks, ccl_bytes, wait_timeout_ms, ctypes.byref(h)), "HcclEmuCreate")
+        self._h = h
+
+    def close(self):
+        if self._h:
+            self._l.HcclEmuDestroy(self._h)
+            self._h = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+    def _ptrs(self, tensors: Optional[Sequence[Optional[torch.Tensor]]]):
+        if tensors is None:
+            return None
+        arr = (ctypes.c_void_p * self.n)()
+        for i, t in enumerate(tensors):
+            arr[i] = t.data_ptr() if t is not None else None
+        return arr
+
+    def run(self, op: int, alg: str, ins, outs, count: int, dtype: torch.dtype, reduce_op: ReduceOp = ReduceOp.SUM, root: int = 0,
+            counts: Optional[Sequence[int]] = None, max_ctas: int = 4) -> int:
+        cm = (ctypes.c_uint64 * len(counts))(*counts) if counts is not None else None
+        rc = self._l.HcclEmuRun(self._h, op, alg.encode(), self._ptrs(ins), self._ptrs(outs), count, int(from_torch(dtype)), int(reduce_op), root,
+                                cm, max_ctas)
+        torch.cuda.synchronize()
+        return rc
+
+    def batch_send_recv(self, transfers: List[tuple]) -> int:
+        """transfers: (src_rank, dst_rank, src_tensor, dst_tensor)"""
+        n = len(transfers)
+        s = (ctypes.c_uint32 * n)(*[t[0] for t in transfers])
+        d = (ctypes.c_uint32 * n)(*[t[1] for t in transfers])
+        sb = (ctypes.c_void_p * n)(*[t[2].data_ptr() for t in transfers])
+        db = (ctypes.c_void_p * n)(*[t[3].data_ptr() for t in transfers])
+        by = (ctypes.c_uint64 * n)(*[t[2].numel() * t[2].element_size() for t in transfers])
+        rc = self._l.HcclEmuBatchSendRecv(self._h, n, s, d, sb, db, by)
+        torch.cuda.synchronize()
+        return rc
+
+    def status(self, rank: int, clear: bool = False):
+        out = (ctypes.c_uint32 * 8)()
+        check(self._l.HcclEmuStatus(self._h, rank, out, int(clear)), "HcclEmuStatus")
+        return list(out)
+
+    def lonely_barrier(self, rank: int) -> int:
+        return self._l.HcclEmuLonelyBarrier(self._h, rank)

@@ -1,0 +1,68 @@
+/*
+ * hccl_mc2.h -- matmul + communication ("MC2") interface.
+ *
+ * Part 1 keeps HCCL's argument / resource-context API (reference: include/hccl_mc2.h:25-82, implementation
+ * src/common/hccl_mc2.cc:21-165): an opaque HcclOpArgs blob with setters, and HcclCreateOpResCtx which returns a
+ * device-resident context (peer heap table, flag arena, workspace window) that a caller's own fused kernel can use to
+ * talk to the other ranks.
+ * Part 2 is new: the fused operators themselves, each ONE sm_100a kernel that overlaps tcgen05 GEMM tiles with the
+ * peer-memory traffic of the collective (HCCL ships no such kernels; they live in external operator libraries there).
+ */
+#ifndef HCCL_B200_MC2_H_
+#define HCCL_B200_MC2_H_
+
+#include "hccl_comm.h"
+#include "hccl_types.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- Part 1: argument blob + resource context ------------------------------------------------------------------ */
+HcclResult HcclKfcAllocOpArgs(void **opArgs);
+HcclResult HcclKfcFreeOpArgs(void *opArgs);
+HcclResult HcclKfcOpArgsSetSrcDataType(void *opArgs, uint8_t srcDataType);
+HcclResult HcclKfcOpArgsSetDstDataType(void *opArgs, uint8_t dstDataType);
+HcclResult HcclKfcOpArgsSetReduceType(void *opArgs, uint32_t reduceType);
+HcclResult HcclKfcOpArgsSetCount(void *opArgs, uint64_t count);
+HcclResult HcclKfcOpArgsSetAlgConfig(void *opArgs, char *algConfig);   /* at most 128 characters */
+HcclResult HcclKfcOpArgsSetCommEngine(void *opArgs, uint8_t commEngine); /* HCCL_ENGINE_SM or HCCL_ENGINE_NVLS */
+HcclResult HcclCreateOpResCtx(HcclComm comm, uint8_t opType, void *opArgs, void **opResCtx);
+
+/* Layout of the device-resident context returned by HcclCreateOpResCtx (read it from device code). */
+typedef struct HcclOpResCtxDef {
+    uint32_t magic;             /* 'MC2C' */
+    uint32_t opType;
+    uint32_t rank, nranks;
+    uint32_t srcDataType, dstDataType, reduceType, commEngine;
+    uint64_t count;
+    uint64_t heapBytes;
+    void *heap[32];             /* heap[r]: rank r's symmetric heap as mapped on this device */
+    void *mcHeap;               /* multicast mapping, or NULL */
+    uint64_t workspaceOff;      /* window inside every heap reserved for this context */
+    uint64_t workspaceBytes;
+    uint64_t flagOff;           /* 64 KB of zero-initialised flag words inside the window */
+    uint64_t timeoutNs;         /* bound the library uses for its own waits */
+    char algConfig[128];
+} HcclOpResCtx;
+
+/* ---- Part 2: fused operators (bf16; weights are [N, K] row-major, i.e. K contiguous) ---------------------------- */
+/* C[M,N] = A[M,K] * B[N,K]^T on one GPU (the building block; also the N = 1 degenerate case of the fused ops). */
+HcclResult HcclGemmBf16(const void *a, const void *b, void *c, uint64_t m, uint64_t n, uint64_t k, int outFp32, cudaStream_t stream);
+HcclResult HcclGemmCheckError(void);
+
+/* out[nranks*mLocal, n] = AllGather_rows(aLocal[mLocal, k]) * b[n, k]^T. gathered (optional, [nranks*mLocal, k]) receives the
+ * gathered activations for reuse in the backward pass. */
+HcclResult HcclAllGatherMatmul(const void *aLocal, const void *b, void *out, void *gathered, uint64_t mLocal, uint64_t n, uint64_t k,
+                               HcclDataType dataType, HcclComm comm, cudaStream_t stream);
+/* out[m/nranks, n] = ReduceScatter_rows(a[m, kLocal] * b[n, kLocal]^T), sum in rank order. */
+HcclResult HcclMatmulReduceScatter(const void *a, const void *b, void *out, uint64_t m, uint64_t n, uint64_t kLocal, HcclDataType dataType,
+                                   HcclComm comm, cudaStream_t stream);
+/* out[m, n] = AllReduce(a[m, kLocal] * b[n, kLocal]^T), sum in rank order (decode-sized m). */
+HcclResult HcclMatmulAllReduce(const void *a, const void *b, void *out, uint64_t m, uint64_t n, uint64_t kLocal, HcclDataType dataType,
+                               HcclComm comm, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,215 @@
+"""SM-engine collective kernels on ONE GPU: all ranks emulated in a single cooperative launch (blockIdx.y = rank).
+Numerics are compared with a plain PyTorch fp32/fp64 reference of the same operator."""
+import pytest
+import torch
+
+from hccl_b200.types import ReduceOp
+
+pytestmark = pytest.mark.gpu
+
+CMD = dict(BROADCAST=1, ALLREDUCE=2, REDUCE=3, ALLGATHER=6, REDUCE_SCATTER=7, ALLTOALLV=8, ALLTOALLVC=9, ALLTOALL=10, SCATTER=12,
+           BARRIER=14, ALLGATHER_V=15, REDUCE_SCATTER_V=16)
+
+
+@pytest.fixture(scope="module")
+def emu_mod():
+    from hccl_b200.utils import emu
+    return emu
+
+
+def _rand(n, dtype, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    if dtype.is_floating_point:
+        return (torch.rand(n, generator=g, device="cuda", dtype=torch.float32) * 2 - 1).to(dtype)
+    return torch.randint(-50, 50, (n,), generator=g, device="cuda", dtype=torch.int64).to(dtype)
+
+
+def _ref_reduce(xs, op, dtype):
+    acc = torch.stack([x.to(torch.float64) if dtype.is_floating_point else x.to(torch.int64) for x in xs])
+    if op == ReduceOp.SUM:
+        r = acc.sum(0)
+    elif op == ReduceOp.PROD:
+        r = acc.prod(0)
+    elif op == ReduceOp.MAX:
+        r = acc.max(0).values
+    else:
+        r = acc.min(0).values
+    return r
+
+
+def _tol(dtype, n):
+    if dtype == torch.bfloat16:
+        return 2e-2 * n ** 0.5
+    if dtype == torch.float16:
+        return 3e-3 * n ** 0.5
+    if dtype == torch.float32:
+        return 1e-5 * n
+    return 0
+
+
+@pytest.mark.parametrize("nranks", [2, 3, 4, 8])
+@pytest.mark.parametrize("alg", ["SmAllReduceMesh1DOneShot", "SmAllReduceMesh1DTwoShot"])
+@pytest.mark.parametrize("count", [1, 7, 1024, 4099, 65536 + 3])
+def test_allreduce_fp32_sum(emu_mod, nranks, alg, count):
+    with emu_mod.EmuWorld(nranks, 1 << 20) as w:
+        xs = [_rand(count, torch.float32, 100 + r) for r in range(nranks)]
+        outs = [torch.empty_like(x) for x in xs]
+        assert w.run(CMD["ALLREDUCE"], alg, xs, outs, count, torch.float32) == 0
+        ref = _ref_reduce(xs, ReduceOp.SUM, torch.float32)
+        for o in outs:
+            assert torch.allclose(o.double(), ref, atol=_tol(torch.float32, nranks), rtol=1e-5)
+            assert torch.equal(o, outs[0])   # rank-order reduction: identical bits on every rank
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.int32, torch.int64, torch.int8, torch.float64, torch.int16])
+@pytest.mark.parametrize("op", [ReduceOp.SUM, ReduceOp.MAX, ReduceOp.MIN])
+def test_allreduce_dtypes_ops(emu_mod, dtype, op):
+    nranks, count = 4, 3001
+    with emu_mod.EmuWorld(nranks, 1 << 20) as w:
+        for alg in ("SmAllReduceMesh1DOneShot", "SmAllReduceMesh1DTwoShot"):
+            xs = [_rand(count, dtype, 7 + r) for r in range(nranks)]
+            outs = [torch.empty_like(x) for x in xs]
+            assert w.run(CMD["ALLREDUCE"], alg, xs, outs, count, dtype, op) == 0
+            ref = _ref_reduce(xs, op, dtype)
+            for o in outs:
+                if dtype.is_floating_point:
+                    assert torch.allclose(o.double(), ref, atol=_tol(dtype, nranks), rtol=1e-2 if dtype != torch.float64 else 1e-12)
+                else:
+                    assert torch.equal(o.to(torch.int64), ref.to(dtype).to(torch.int64))
+
+
+def test_allreduce_prod_and_inplace(emu_mod):
+    nranks, count = 3, 513
+    with emu_mod.EmuWorld(nranks, 1 << 20) as w:
+        xs = [(_rand(count, torch.float32, r) * 0.5 + 1.0) for r in range(nranks)]
+        ref = _ref_reduce(xs, ReduceOp.PROD, torch.float32)
+        bufs = [x.clone() for x in xs]
+        assert w.run(CMD["ALLREDUCE"], "SmAllReduceMesh1DTwoShot", bufs, bufs, count, torch.float32, ReduceOp.PROD) == 0
+        for b in bufs:
+            assert torch.allclose(b.double(), ref, rtol=1e-5)
+
+
+def test_allreduce_chunk_loop_and_back_to_back(emu_mod):
+    """Scratch smaller than the payload forces several launches; repeated calls exercise the ping-pong halves."""
+    nranks, count = 4, 300_000
+    with emu_mod.EmuWorld(nranks, 256 << 10) as w:
+        for it in range(3):
+            xs = [_rand(count, torch.float32, 50 * it + r) for r in range(nranks)]
+            outs = [torch.empty_like(x) for x in xs]
+            alg = "SmAllReduceMesh1DTwoShot" if it != 1 else "SmAllReduceMesh1DOneShot"
+            assert w.run(CMD["ALLREDUCE"], alg, xs, outs, count, torch.float32) == 0
+            ref = _ref_reduce(xs, ReduceOp.SUM, torch.float32)
+            for o in outs:
+                assert torch.allclose(o.double(), ref, atol=1e-4)
+
+
+@pytest.mark.parametrize("nranks", [2, 5, 8])
+def test_allgather_reducescatter(emu_mod, nranks):
+    count = 2049
+    with emu_mod.EmuWorld(nranks, 1 << 20) as w:
+        xs = [_rand(count, torch.bfloat16, r) for r in range(nranks)]
+        outs = [torch.empty(count * nranks, dtype=torch.bfloat16, device="cuda") for _ in range(nranks)]
+        assert w.run(CMD["ALLGATHER"], "SmAllGatherMesh1D", xs, outs, count, torch.bfloat16) == 0
+        want = torch.cat(xs)
+        for o in outs:
+            assert torch.equal(o, want)
+        full = [_rand(count * nranks, torch.float32, 10 + r) for r in range(nranks)]
+        rs = [torch.empty(count, dtype=torch.float32, device="cuda") for _ in range(nranks)]
+        assert w.run(CMD["REDUCE_SCATTER"], "SmReduceScatterMesh1D", full, rs, count, torch.float32) == 0
+        ref = _ref_reduce(full, ReduceOp.SUM, torch.float32)
+        for r in range(nranks):
+            assert torch.allclose(rs[r].double(), ref[r * count:(r + 1) * count], atol=1e-4)
+
+
+@pytest.mark.parametrize("root", [0, 2])
+def test_broadcast_reduce_scatter_rooted(emu_mod, root):
+    nranks, count = 4, 5000
+    with emu_mod.EmuWorld(nranks, 1 << 20) as w:
+        bufs = [_rand(count, torch.float32, r) for r in range(nranks)]
+        want = bufs[root].clone()
+        assert w.run(CMD["BROADCAST"], "SmBroadcastMesh1D", bufs, bufs, count, torch.float32, root=root) == 0
+        for b in bufs:
+            assert torch.equal(b, want)
+        xs = [_rand(count, torch.float32, 20 + r) for r in range(nranks)]
+        outs = [torch.zeros(count, dtype=torch.float32, device="cuda") for _ in range(nranks)]
+        assert w.run(CMD["REDUCE"], "SmReduceMesh1D", xs, outs, count, torch.float32, root=root) == 0
+        assert torch.allclose(outs[root].double(), _ref_reduce(xs, ReduceOp.SUM, torch.float32), atol=1e-4)
+        send = [_rand(count * nranks, torch.float32, 30 + r) for r in range(nranks)]
+        recv = [torch.zeros(count, dtype=torch.float32, device="cuda") for _ in range(nranks)]
+        assert w.run(CMD["SCATTER"], "SmScatterMesh1D", send, recv, count, torch.float32, root=root) == 0
+        for r in range(nranks):
+            assert torch.equal(recv[r], send[root][r * count:(r + 1) * count])
+
+
+def test_alltoall_and_v(emu_mod):
+    nranks, count = 4, 777
+    with emu_mod.EmuWorld(nranks, 1 << 20) as w:
+        send = [_rand(count * nranks, torch.float32, r) for r in range(nranks)]
+        recv = [torch.zeros(count * nranks, dtype=torch.float32, device="cuda") for _ in range(nranks)]
+        assert w.run(CMD["ALLTOALL"], "SmAlltoAllMesh1D", send, recv, count, torch.float32) == 0
+        for r in range(nranks):
+            for s in range(nranks):
+                assert torch.equal(recv[r][s * count:(s + 1) * count], send[s][r * count:(r + 1) * count])
+        # variable counts, including zeros
+        M = [[(3 * i + 5 * j) % 7 * 100 + (0 if (i + j) % 3 else 1) * 13 for j in range(nranks)] for i in range(nranks)]
+        M[1][2] = 0
+        sends = [_rand(max(1, sum(M[i])), torch.float32, 40 + i) for i in range(nranks)]
+        recvs = [torch.zeros(max(1, sum(M[j][i] for j in range(nranks))), dtype=torch.float32, device="cuda") for i in range(nranks)]
+        flat = [v for row in M for v in row]
+        assert w.run(CMD["ALLTOALLV"], "SmAlltoAllVMesh1D", sends, recvs, 0, torch.float32, counts=flat) == 0
+        for i in range(nranks):
+            ro = 0
+            for j in range(nranks):
+                so = sum(M[j][:i])
+                assert torch.equal(recvs[i][ro:ro + M[j][i]], sends[j][so:so + M[j][i]])
+                ro += M[j][i]
+
+
+def test_allgatherv_reducescatterv(emu_mod):
+    nranks = 4
+    counts = [100, 0, 1025, 33]
+    with emu_mod.EmuWorld(nranks, 1 << 20) as w:
+        xs = [_rand(max(1, counts[r]), torch.float32, r) for r in range(nranks)]
+        outs = [torch.zeros(sum(counts), dtype=torch.float32, device="cuda") for _ in range(nranks)]
+        assert w.run(CMD["ALLGATHER_V"], "SmAllGatherVMesh1D", xs, outs, 0, torch.float32, counts=counts) == 0
+        want = torch.cat([xs[r][:counts[r]] for r in range(nranks)])
+        for o in outs:
+            assert torch.equal(o, want)
+        full = [_rand(sum(counts), torch.float32, 60 + r) for r in range(nranks)]
+        rs = [torch.zeros(max(1, counts[r]), dtype=torch.float32, device="cuda") for r in range(nranks)]
+        assert w.run(CMD["REDUCE_SCATTER_V"], "SmReduceScatterVMesh1D", full, rs, 0, torch.float32, counts=counts) == 0
+        ref = _ref_reduce(full, ReduceOp.SUM, torch.float32)
+        off = 0
+        for r in range(nranks):
+            assert torch.allclose(rs[r][:counts[r]].double(), ref[off:off + counts[r]], atol=1e-4)
+            off += counts[r]
+
+
+def test_batch_send_recv_ring_and_barrier(emu_mod):
+    nranks = 4
+    with emu_mod.EmuWorld(nranks, 1 << 20) as w:
+        n = 200_000   # several mailbox rounds
+        src = [_rand(n, torch.float32, r) for r in range(nranks)]
+        dst = [torch.zeros(n, dtype=torch.float32, device="cuda") for _ in range(nranks)]
+        transfers = [(r, (r + 1) % nranks, src[r], dst[(r + 1) % nranks]) for r in range(nranks)]
+        assert w.batch_send_recv(transfers) == 0
+        for r in range(nranks):
+            assert torch.equal(dst[(r + 1) % nranks], src[r])
+        # a second round reuses the mailbox sequence numbers
+        dst2 = [torch.zeros(1000, dtype=torch.float32, device="cuda") for _ in range(nranks)]
+        assert w.batch_send_recv([(0, 3, src[0][:1000], dst2[3]), (3, 0, src[3][:1000], dst2[0])]) == 0
+        assert torch.equal(dst2[3], src[0][:1000]) and torch.equal(dst2[0], src[3][:1000])
+        assert w.run(CMD["BARRIER"], "SmBarrierMesh1D", None, None, 0, torch.int8) == 0
+
+
+def test_bounded_wait_reports_timeout(emu_mod):
+    """A rank whose peers never arrive gives up after the deadline, records who it waited for, and the context stays
+    usable (the next operator on a cleared world succeeds)."""
+    with emu_mod.EmuWorld(2, 1 << 20, wait_timeout_ms=200) as w:
+        assert w.lonely_barrier(0) == 9   # HCCL_E_TIMEOUT
+        st = w.status(0, clear=True)
+        assert st[0] == 1 and st[1] == 0 and st[2] == 1   # code, rank, peer
+        xs = [_rand(100, torch.float32, r) for r in range(2)]
+        outs = [torch.empty_like(x) for x in xs]
+        assert w.run(CMD["ALLREDUCE"], "SmAllReduceMesh1DOneShot", xs, outs, 100, torch.float32) == 0
+        assert torch.allclose(outs[0], xs[0] + xs[1])

@@ -1,0 +1,117 @@
+"""Collective primitive sweep: bus GB/s of this library against NCCL on the same GPUs.
+
+Launch:  python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+             benchmarks/coll_sweep.py [--ops allreduce,allgather,...] [--dtypes fp32,bf16] [--min 1024] [--max 1073741824]
+Per-rank message sizes are powers of two; inputs are uniform[-1,1] seeded with rank*1000 + size_index. Every number is
+device time (CUDA events on the launching stream, after warm-up), max over ranks. busBW = algBW * {allreduce 2(n-1)/n;
+allgather / reducescatter / alltoall (n-1)/n; broadcast 1}. Results go to stdout (table) and, with --json, to a file.
+"""
+import argparse
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), ".."))
+from hccl_b200.comm import init_from_env  # noqa: E402
+
+DT = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16}
+
+
+def time_fn(fn, iters, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(iters):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([s.elapsed_time(e) / iters], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.item() * 1e-3
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--ops", default="allreduce,allgather,reducescatter,broadcast,alltoall")
+    ap.add_argument("--dtypes", default="fp32,bf16")
+    ap.add_argument("--min", type=int, default=1024)
+    ap.add_argument("--max", type=int, default=1 << 30)
+    ap.add_argument("--json", default="")
+    ap.add_argument("--skip-nccl", action="store_true")
+    args = ap.parse_args()
+    dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0))))
+    comm = init_from_env()
+    rank, n = comm.rank, comm.size
+    rows = []
+    for op in args.ops.split(","):
+        for dname in args.dtypes.split(","):
+            dtype = DT[dname]
+            es = torch.empty((), dtype=dtype).element_size()
+            size, idx = args.min, 0
+            while size <= args.max:
+                cnt = size // es
+                g = torch.Generator(device="cuda").manual_seed(rank * 1000 + idx)
+                iters = 200 if size <= (1 << 20) else 30 if size <= (64 << 20) else 8
+                warm = 5 if size <= (64 << 20) else 3
+                if op == "allreduce":
+                    x = (torch.rand(cnt, generator=g, device="cuda") * 2 - 1).to(dtype)
+                    y = torch.empty_like(x)
+                    ours = lambda: comm.all_reduce(x, y)
+                    ref = lambda: dist.all_reduce(y)
+                    factor = 2 * (n - 1) / n
+                elif op == "allgather":
+                    x = (torch.rand(cnt, generator=g, device="cuda") * 2 - 1).to(dtype)
+                    y = torch.empty(cnt * n, dtype=dtype, device="cuda")
+                    ours = lambda: comm.all_gather(x, y)
+                    ref = lambda: dist.all_gather_into_tensor(y, x)
+                    factor = (n - 1) / n * n   # size counts the per-rank message; bytes received = size * (n-1)
+                elif op == "reducescatter":
+                    x = (torch.rand(cnt * n, generator=g, device="cuda") * 2 - 1).to(dtype)
+                    y = torch.empty(cnt, dtype=dtype, device="cuda")
+                    ours = lambda: comm.reduce_scatter(x, y)
+                    ref = lambda: dist.reduce_scatter_tensor(y, x)
+                    factor = (n - 1) / n * n
+                elif op == "broadcast":
+                    x = (torch.rand(cnt, generator=g, device="cuda") * 2 - 1).to(dtype)
+                    ours = lambda: comm.broadcast(x, 0)
+                    ref = lambda: dist.broadcast(x, 0)
+                    factor = 1.0
+                elif op == "alltoall":
+                    per = max(1, cnt // n)
+                    x = (torch.rand(per * n, generator=g, device="cuda") * 2 - 1).to(dtype)
+                    y = torch.empty_like(x)
+                    ours = lambda: comm.all_to_all(x, y)
+                    ref = lambda: dist.all_to_all_single(y, x)
+                    factor = (n - 1) / n
+                else:
+                    raise SystemExit(f"unknown op {op}")
+                t_ours = time_fn(ours, iters, warm)
+                t_ref = float("nan") if args.skip_nccl else time_fn(ref, iters, warm)
+                bus_ours = size * factor / t_ours / 1e9
+                bus_ref = size * factor / t_ref / 1e9
+                rows.append(dict(op=op, dtype=dname, bytes=size, ranks=n, ours_us=t_ours * 1e6, nccl_us=t_ref * 1e6, ours_busGBs=bus_ours,
+                                 nccl_busGBs=bus_ref, ratio=bus_ours / bus_ref if bus_ref == bus_ref else None))
+                if rank == 0:
+                    print(f"{op:13s} {dname:5s} {size:>11d} B  ours {t_ours*1e6:9.1f} us {bus_ours:8.1f} GB/s | nccl {t_ref*1e6:9.1f} us {bus_ref:8.1f} GB/s"
+                          f" | x{bus_ours / bus_ref if bus_ref == bus_ref else float('nan'):.2f}", flush=True)
+                del x
+                size *= 4 if size >= (1 << 22) and args.max > (1 << 28) else 2
+                idx += 1
+    if rank == 0 and args.json:
+        os.makedirs(os.path.dirname(os.path.abspath(args.json)), exist_ok=True)
+        with open(args.json, "w") as f:
+            json.dump(rows, f, indent=1)
+    torch.cuda.synchronize()
+    comm.destroy()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

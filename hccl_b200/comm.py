@@ -249,3 +249,42 @@ class Communicator:
         fn.argtypes = [ctypes.c_void_p]
         fn.restype = ctypes.c_int
         return bool(fn(self._h))
+
+
+def _store_exchange_root_info(rank: int, world: int) -> bytes:
+    """Shares rank 0's root info through a torch TCPStore on MASTER_ADDR:(MASTER_PORT + 17)."""
+    import os
+    from datetime import timedelta
+
+    from torch.distributed import TCPStore
+
+    host = os.environ.get("MASTER_ADDR", "127.0.0.1")
+    port = int(os.environ.get("MASTER_PORT", "29500")) + 17
+    store = TCPStore(host, port, world, is_master=(rank == 0), timeout=timedelta(seconds=120), wait_for_workers=False)
+    key = "hccl_b200_root_info_" + os.environ.get("HCCL_B200_COMM_EPOCH", "0")
+    if rank == 0:
+        store.set(key, get_root_info())
+    return store.get(key)
+
+
+def init_from_env(**kw) -> Communicator:
+    """One process per GPU, launched by torchrun (RANK / WORLD_SIZE / LOCAL_RANK / MASTER_ADDR / MASTER_PORT).
+
+    Selects cuda:LOCAL_RANK when CUDA is available, shares the root info through torch.distributed if it is already
+    initialised (any backend) or through a TCPStore otherwise, and returns the communicator."""
+    import os
+
+    import torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if torch.cuda.is_available() and kw.get("backend", "auto") != "sim":
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank % max(1, torch.cuda.device_count()))))
+        torch.cuda.init()
+        torch.zeros(1, device="cuda")   # create the context before the native library asks for the current device
+    import torch.distributed as dist
+
+    if dist.is_available() and dist.is_initialized():
+        return Communicator.from_torch_process_group(None, **kw)
+    root = _store_exchange_root_info(rank, world) if world > 1 else get_root_info()
+    return Communicator.from_root_info(world, root, rank, **kw)

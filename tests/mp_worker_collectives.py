@@ -1,0 +1,137 @@
+"""Worker of the multi-GPU collective tests (one process per GPU, started by torchrun). Every rank can regenerate every
+rank's input (seeded by rank), so expected results are computed locally in fp64/int64 without another library."""
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.join(os.path.dirname(__file__), ".."))
+import hccl_b200  # noqa: E402
+from hccl_b200.comm import init_from_env  # noqa: E402
+from hccl_b200.types import ReduceOp  # noqa: E402
+
+
+def gen(rank, n, dtype, salt=0):
+    g = torch.Generator(device="cuda").manual_seed(1000 * rank + salt)
+    if dtype.is_floating_point:
+        return (torch.rand(n, generator=g, device="cuda") * 2 - 1).to(dtype)
+    return torch.randint(-40, 40, (n,), generator=g, device="cuda", dtype=torch.int64).to(dtype)
+
+
+def ref_reduce(world, n, dtype, op, salt=0):
+    acc = torch.stack([gen(r, n, dtype, salt).to(torch.float64 if dtype.is_floating_point else torch.int64) for r in range(world)])
+    return {ReduceOp.SUM: lambda: acc.sum(0), ReduceOp.MAX: lambda: acc.max(0).values, ReduceOp.MIN: lambda: acc.min(0).values,
+            ReduceOp.PROD: lambda: acc.prod(0)}[op]()
+
+
+def close(out, ref, dtype, world):
+    if not dtype.is_floating_point:
+        return torch.equal(out.to(torch.int64), ref.to(dtype).to(torch.int64))
+    tol = {torch.bfloat16: 3e-2, torch.float16: 4e-3, torch.float32: 1e-5, torch.float64: 1e-12}[dtype] * world
+    return torch.allclose(out.double(), ref, atol=tol, rtol=tol)
+
+
+def main():
+    comm = init_from_env()
+    rank, world = comm.rank, comm.size
+    fails = []
+
+    def check(name, ok):
+        if not ok:
+            fails.append(name)
+            print(f"[rank {rank}] FAIL {name}", flush=True)
+
+    sizes = [1, 33, 1024, 65537, 1 << 20, (3 << 20) + 5]
+    for dtype in (torch.float32, torch.bfloat16, torch.float16, torch.int32, torch.int64):
+        for n in sizes if dtype in (torch.float32, torch.bfloat16) else sizes[:4]:
+            for op in (ReduceOp.SUM, ReduceOp.MAX):
+                x = gen(rank, n, dtype)
+                out = torch.empty_like(x)
+                comm.all_reduce(x, out, op)
+                torch.cuda.synchronize()
+                check(f"allreduce {dtype} n={n} {op.name}", close(out, ref_reduce(world, n, dtype, op), dtype, world))
+    # in place + repeated calls (ping-pong halves, plan reuse)
+    for it in range(4):
+        x = gen(rank, 50_000, torch.float32, salt=it)
+        comm.all_reduce(x)
+        torch.cuda.synchronize()
+        check(f"allreduce inplace it={it}", close(x, ref_reduce(world, 50_000, torch.float32, ReduceOp.SUM, salt=it), torch.float32, world))
+    for n in (5, 4096, 300_001):
+        x = gen(rank, n, torch.bfloat16)
+        out = torch.empty(n * world, dtype=torch.bfloat16, device="cuda")
+        comm.all_gather(x, out)
+        torch.cuda.synchronize()
+        check(f"allgather n={n}", torch.equal(out, torch.cat([gen(r, n, torch.bfloat16) for r in range(world)])))
+        full = gen(rank, n * world, torch.float32, salt=3)
+        rs = torch.empty(n, dtype=torch.float32, device="cuda")
+        comm.reduce_scatter(full, rs)
+        torch.cuda.synchronize()
+        check(f"reducescatter n={n}", close(rs, ref_reduce(world, n * world, torch.float32, ReduceOp.SUM, salt=3)[rank * n:(rank + 1) * n], torch.float32, world))
+        for root in (0, world - 1):
+            b = gen(rank, n, torch.float32, salt=5)
+            comm.broadcast(b, root)
+            torch.cuda.synchronize()
+            check(f"broadcast n={n} root={root}", torch.equal(b, gen(root, n, torch.float32, salt=5)))
+            x = gen(rank, n, torch.float32, salt=6)
+            out = torch.zeros(n, dtype=torch.float32, device="cuda")
+            comm.reduce(x, out, root)
+            torch.cuda.synchronize()
+            if rank == root:
+                check(f"reduce n={n} root={root}", close(out, ref_reduce(world, n, torch.float32, ReduceOp.SUM, salt=6), torch.float32, world))
+            send = gen(rank, n * world, torch.float32, salt=7)
+            recv = torch.zeros(n, dtype=torch.float32, device="cuda")
+            comm.scatter(send, recv, root)
+            torch.cuda.synchronize()
+            check(f"scatter n={n} root={root}", torch.equal(recv, gen(root, n * world, torch.float32, salt=7)[rank * n:(rank + 1) * n]))
+        send = gen(rank, n * world, torch.float32, salt=8)
+        recv = torch.zeros(n * world, dtype=torch.float32, device="cuda")
+        comm.all_to_all(send, recv)
+        torch.cuda.synchronize()
+        want = torch.cat([gen(s, n * world, torch.float32, salt=8)[rank * n:(rank + 1) * n] for s in range(world)])
+        check(f"alltoall n={n}", torch.equal(recv, want))
+    # AlltoAllV with a skewed matrix
+    M = [[((i * 7 + j * 13) % 5) * 1000 + (i + j) % 2 for j in range(world)] for i in range(world)]
+    send = gen(rank, max(1, sum(M[rank])), torch.float32, salt=9)
+    recv = torch.zeros(max(1, sum(M[j][rank] for j in range(world))), dtype=torch.float32, device="cuda")
+    sd = [sum(M[rank][:j]) for j in range(world)]
+    rc = [M[j][rank] for j in range(world)]
+    rd = [sum(rc[:j]) for j in range(world)]
+    comm.all_to_all_v(send, M[rank], sd, recv, rc, rd)
+    torch.cuda.synchronize()
+    want = torch.cat([gen(j, max(1, sum(M[j])), torch.float32, salt=9)[sum(M[j][:rank]):sum(M[j][:rank]) + M[j][rank]] for j in range(world)])
+    check("alltoallv", torch.equal(recv[:want.numel()], want))
+    recv.zero_()
+    comm.all_to_all_vc(send, M, recv)
+    torch.cuda.synchronize()
+    check("alltoallvc", torch.equal(recv[:want.numel()], want))
+    # send / recv ring, then batch
+    n = 700_000
+    x = gen(rank, n, torch.float32, salt=11)
+    y = torch.zeros(n, dtype=torch.float32, device="cuda")
+    nxt, prv = (rank + 1) % world, (rank - 1) % world
+    if rank % 2 == 0:
+        comm.send(x, nxt)
+        comm.recv(y, prv)
+    else:
+        comm.recv(y, prv)
+        comm.send(x, nxt)
+    torch.cuda.synchronize()
+    check("send/recv ring", torch.equal(y, gen(prv, n, torch.float32, salt=11)))
+    y.zero_()
+    comm.batch_send_recv([("send", x, nxt), ("recv", y, prv)])
+    torch.cuda.synchronize()
+    check("batch_send_recv ring", torch.equal(y, gen(prv, n, torch.float32, salt=11)))
+    comm.barrier()
+    torch.cuda.synchronize()
+    check("async error clean", comm.async_error() == 0)
+    comm.destroy()
+    if fails:
+        print(f"[rank {rank}] {len(fails)} failures: {fails[:8]}", flush=True)
+        sys.exit(1)
+    if rank == 0:
+        print(f"all multi-GPU collective checks passed on {world} ranks (nvls={os.environ.get('HCCL_NVLS_ENABLE', 'auto')}, "
+              f"engine={os.environ.get('HCCL_OP_EXPANSION_MODE', 'auto')}, buffsize={os.environ.get('HCCL_BUFFSIZE', 'default')})", flush=True)
+
+
+if __name__ == "__main__":
+    main()

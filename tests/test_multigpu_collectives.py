@@ -1,0 +1,33 @@
+"""Real multi-GPU runs of the C API (one process per GPU over NVLink): every operator, several dtypes, chunk loops forced by
+a small CCL buffer, with the NVLS engine on and off."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(nproc, extra_env, port):
+    env = dict(os.environ)
+    env.update(extra_env)
+    env.setdefault("HCCL_DEVICE_WAIT_TIMEOUT_MS", "10000")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(HERE, "mp_worker_collectives.py")]
+    res = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-6000:]
+    assert "all multi-GPU collective checks passed" in res.stdout, res.stdout[-3000:]
+
+
+@pytest.mark.parametrize("cfg", [
+    {"HCCL_NVLS_ENABLE": "0"},
+    {"HCCL_NVLS_ENABLE": "0", "HCCL_BUFFSIZE": "4"},
+    {"HCCL_NVLS_ENABLE": "1"},
+    {"HCCL_NVLS_ENABLE": "1", "HCCL_BUFFSIZE": "4"},
+])
+def test_collectives_two_or_more_gpus(cfg):
+    n = min(torch.cuda.device_count(), 8)
+    _run(n, cfg, 29610 + len(cfg) * 7 + int(cfg.get("HCCL_NVLS_ENABLE", "0")) * 3)

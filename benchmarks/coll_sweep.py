@@ -1,7 +1,7 @@
 """Collective primitive sweep: bus GB/s of this library against NCCL on the same GPUs.
 
 Launch:  python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
-             benchmarks/coll_sweep.py [--ops allreduce,allgather,...] [--dtypes fp32,bf16] [--min 1024] [--max 1073741824]
+             benchmarks/coll_sweep.py [--ops allreduce,allgather,...] [--dtypes fp32,bf16] [--min-bytes 1024] [--max-bytes 1073741824]
 Per-rank message sizes are powers of two; inputs are uniform[-1,1] seeded with rank*1000 + size_index. Every number is
 device time (CUDA events on the launching stream, after warm-up), max over ranks. busBW = algBW * {allreduce 2(n-1)/n;
 allgather / reducescatter / alltoall (n-1)/n; broadcast 1}. Results go to stdout (table) and, with --json, to a file.
@@ -41,8 +41,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ops", default="allreduce,allgather,reducescatter,broadcast,alltoall")
     ap.add_argument("--dtypes", default="fp32,bf16")
-    ap.add_argument("--min", type=int, default=1024)
-    ap.add_argument("--max", type=int, default=1 << 30)
+    ap.add_argument("--min-bytes", type=int, default=1024)
+    ap.add_argument("--max-bytes", type=int, default=1 << 30)
     ap.add_argument("--json", default="")
     ap.add_argument("--skip-nccl", action="store_true")
     args = ap.parse_args()
@@ -54,8 +54,8 @@ def main():
         for dname in args.dtypes.split(","):
             dtype = DT[dname]
             es = torch.empty((), dtype=dtype).element_size()
-            size, idx = args.min, 0
-            while size <= args.max:
+            size, idx = args.min_bytes, 0
+            while size <= args.max_bytes:
                 cnt = size // es
                 g = torch.Generator(device="cuda").manual_seed(rank * 1000 + idx)
                 iters = 200 if size <= (1 << 20) else 30 if size <= (64 << 20) else 8
@@ -102,7 +102,7 @@ def main():
                     print(f"{op:13s} {dname:5s} {size:>11d} B  ours {t_ours*1e6:9.1f} us {bus_ours:8.1f} GB/s | nccl {t_ref*1e6:9.1f} us {bus_ref:8.1f} GB/s"
                           f" | x{bus_ours / bus_ref if bus_ref == bus_ref else float('nan'):.2f}", flush=True)
                 del x
-                size *= 4 if size >= (1 << 22) and args.max > (1 << 28) else 2
+                size *= 4 if size >= (1 << 22) and args.max_bytes > (1 << 28) else 2
                 idx += 1
     if rank == 0 and args.json:
         os.makedirs(os.path.dirname(os.path.abspath(args.json)), exist_ok=True)

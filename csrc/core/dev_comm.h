@@ -57,7 +57,9 @@ struct DevFlags {
     uint64_t p2pData[kMaxRanks][kP2pCtas * 2];   // [src][cta*2+slot] = round number whose data is staged at src
     uint64_t p2pAck[kMaxRanks][kP2pCtas * 2];    // [dst][cta*2+slot] = round number dst has consumed
     uint64_t hostNotify[kMaxRanks][kNotifySlots];// host-engine notify counters, [src][slot]
-    uint32_t mc2Ready[kMaxRanks][64];            // fused-kernel tile/row-block ready counters, [src][block]
+    // fused-kernel counters, one set per op parity; the owner zeroes its set when the op ends
+    uint32_t mc2Ready[2][kMaxRanks][64];         // [half][src][block]: pieces of `block` delivered by src
+    uint32_t mc2Done[2][kMaxRanks][4];           // [half][src][k]: second-stage counters (results delivered by src)
     uint32_t moeCount[kMaxRanks][320];           // MoE dispatch: per-source expert counts (+ epoch word)
 };
 static_assert(sizeof(DevFlags) <= kFlagBytes, "flag arena too large");

@@ -173,6 +173,7 @@ HcclResult HcclExecOp(Comm *c, OpParam &p)
         }
     }
     HcclResult res = HCCL_E_INTERNAL;
+    bool resourceFallback = false;   // only a missing resource is remembered; a call-specific "not supported" is not
     for (int attempt = 0; attempt < 4; ++attempt) {
         CHK_RET(SelectAlgorithm(c, p, excluded));
         CHK_RET(CheckOpConsistency(c, p));
@@ -186,11 +187,13 @@ HcclResult HcclExecOp(Comm *c, OpParam &p)
         NvtxPop();
         if (res != HCCL_E_UNAVAIL && res != HCCL_E_NOT_SUPPORT) break;
         if (p.engine == HCCL_ENGINE_HOST || p.engine == HCCL_ENGINE_COPY_ENGINE) break;   // nothing below to fall back to
-        HCCL_WARNING("%s on engine %s is unavailable (%d); falling back", p.algName.c_str(), EngineName(p.engine), (int)res);
+        if (res == HCCL_E_NOT_SUPPORT) HCCL_INFO("%s on engine %s does not take this call; falling back", p.algName.c_str(), EngineName(p.engine));
+        else HCCL_WARNING("%s on engine %s is unavailable (%d); falling back", p.algName.c_str(), EngineName(p.engine), (int)res);
+        if (res == HCCL_E_UNAVAIL) resourceFallback = true;
         excluded.push_back(p.engine);
         c->counters.fallbacks++;
     }
-    if (res == HCCL_SUCCESS && !excluded.empty()) {
+    if (res == HCCL_SUCCESS && resourceFallback) {
         std::lock_guard<std::mutex> lk(c->ctxMu);
         c->stickyFallback[stickyKey] = (int)p.engine;
     }

@@ -96,6 +96,22 @@ template <typename T> __device__ __forceinline__ void StoreVec(T *out, uint64_t 
     }
 }
 
+// Switch-side reductions are long-latency loads: keep several 16-byte requests in flight per thread.
+template <typename T, int OP, typename Sink> __device__ __forceinline__ void MultimemReduceLoop(const char *mc, uint64_t nvec, Sink sink)
+{
+    constexpr int U = 4;
+    const uint64_t stride = (uint64_t)blockDim.x * U;
+    uint64_t i = threadIdx.x;
+    for (; i + (uint64_t)blockDim.x * (U - 1) < nvec; i += stride) {
+        uint4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) v[u] = MultimemLdReduce<T, OP>::Ld(mc + ((i + (uint64_t)u * blockDim.x) << 4));
+#pragma unroll
+        for (int u = 0; u < U; ++u) sink(i + (uint64_t)u * blockDim.x, v[u]);
+    }
+    for (; i < nvec; i += blockDim.x) sink(i, MultimemLdReduce<T, OP>::Ld(mc + (i << 4)));
+}
+
 template <typename T, int OP, bool EMU> __device__ void AllReduceNvlsOneShotBody(KCtx &k, const CollArgs &A)
 {
     Part p = PartOf(A.bytes, gridDim.x, blockIdx.x);
@@ -105,7 +121,7 @@ template <typename T, int OP, bool EMU> __device__ void AllReduceNvlsOneShotBody
     T *out = (T *)((char *)A.out + p.off);
     bool aligned = ((uintptr_t)out & 15u) == 0;
     uint64_t nvec = p.len >> 4;
-    for (uint64_t i = threadIdx.x; i < nvec; i += blockDim.x) StoreVec<T>(out, i, MultimemLdReduce<T, OP>::Ld(mc + (i << 4)), aligned);
+    MultimemReduceLoop<T, OP>(mc, nvec, [&](uint64_t i, uint4 v) { StoreVec<T>(out, i, v, aligned); });
 }
 
 template <typename T, int OP, bool EMU> __device__ void AllReduceNvlsTwoShotBody(KCtx &k, const CollArgs &A)
@@ -123,7 +139,7 @@ template <typename T, int OP, bool EMU> __device__ void AllReduceNvlsTwoShotBody
         char *src = k.Mc() + (uint64_t)k.rank * slice + p.off;
         char *dst = k.Mc() + outRegion + (uint64_t)k.rank * slice + p.off;
         uint64_t nvec = p.len >> 4;
-        for (uint64_t i = threadIdx.x; i < nvec; i += blockDim.x) MultimemSt16(dst + (i << 4), MultimemLdReduce<T, OP>::Ld(src + (i << 4)));
+        MultimemReduceLoop<T, OP>(src, nvec, [&](uint64_t i, uint4 v) { MultimemSt16(dst + (i << 4), v); });
     }
     if (!ChannelBarrier(k, 2)) return;
     for (int j = 0; j < n; ++j) {
@@ -186,7 +202,7 @@ template <typename T, int OP, bool EMU> __device__ void ReduceScatterNvlsBody(KC
     T *out = (T *)((char *)A.out + p.off);
     bool aligned = ((uintptr_t)out & 15u) == 0;
     uint64_t nvec = p.len >> 4;
-    for (uint64_t i = threadIdx.x; i < nvec; i += blockDim.x) StoreVec<T>(out, i, MultimemLdReduce<T, OP>::Ld(mc + (i << 4)), aligned);
+    MultimemReduceLoop<T, OP>(mc, nvec, [&](uint64_t i, uint4 v) { StoreVec<T>(out, i, v, aligned); });
 }
 
 // ================================================================================================ Broadcast

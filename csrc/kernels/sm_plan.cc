@@ -17,11 +17,13 @@ uint64_t Clamp(uint64_t total, uint64_t lo, uint64_t chunk) { return total <= lo
 uint32_t SmCtasFor(uint64_t bytes, uint32_t maxCtas)
 {
     uint32_t c;
-    if (bytes <= (32u << 10)) c = 1;
-    else if (bytes <= (256u << 10)) c = 4;
-    else if (bytes <= (2u << 20)) c = 16;
-    else if (bytes <= (16u << 20)) c = 32;
-    else c = 64;
+    if (bytes <= (16u << 10)) c = 1;
+    else if (bytes <= (64u << 10)) c = 4;
+    else if (bytes <= (256u << 10)) c = 8;
+    else if (bytes <= (1u << 20)) c = 16;
+    else if (bytes <= (4u << 20)) c = 32;
+    else if (bytes <= (32u << 20)) c = 64;
+    else c = 96;
     if (maxCtas) c = std::min(c, maxCtas);
     return std::max(1u, std::min<uint32_t>(c, kMaxChannels));
 }

@@ -82,7 +82,7 @@ template <int BN> static HcclResult LaunchPlain(const void *a, const void *b, vo
     p.C = c; p.M = M; p.N = N; p.K = K; p.ldc = N; p.outFp32 = outFp32; p.groupM = 16; p.errorWord = GemmErrorWord();
     using S = GemmSmem<BN>;
     static bool attrSet = false;
-    auto kern = GemmKernel<BN, PlainPolicy>;
+    auto kern = GemmKernel<BN, PlainPolicy, false>;
     size_t smem = S::kTotal + 1024;
     if (!attrSet) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return HCCL_E_RUNTIME;
@@ -90,7 +90,7 @@ template <int BN> static HcclResult LaunchPlain(const void *a, const void *b, vo
     }
     uint32_t tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
     uint32_t grid = std::min<uint32_t>(tiles, (uint32_t)SmCount());
-    kern<<<grid, kGemmThreads, smem, s>>>(p);
+    kern<<<grid, kGemmThreads, smem, s>>>(p, nullptr);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { HCCL_ERROR("GEMM launch failed: %s", cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
     return HCCL_SUCCESS;

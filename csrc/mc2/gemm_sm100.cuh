@@ -1,20 +1,28 @@
 // Persistent, warp-specialised tcgen05 GEMM for sm_100a:  C[M,N] = A[M,K] * B[N,K]^T  (both operands K-major, bf16 in,
-// fp32 accumulate in tensor memory, bf16 or fp32 out).
+// fp32 accumulate in tensor memory, bf16 or fp32 out), and the skeleton the fused matmul+collective kernels share.
 //
 //   warp 0   TMA producer: streams 128xBK A tiles and BNxBK B tiles into a STAGES-deep shared-memory ring
 //   warp 1   MMA issuer: one elected thread issues tcgen05.mma (M=128, N=BN, K=16) into one of two TMEM accumulators
 //   warp 2   owns the TMEM allocation
 //   warps 4-7 epilogue: tcgen05.ld the finished accumulator (each warp its own 32-lane quarter), convert, store
 // The two accumulators let the epilogue of tile i overlap the main loop of tile i+1. The kernel is persistent: one CTA
-// per SM walks tiles in an L2-friendly grouped order.
+// per SM walks tiles in an L2-friendly order.
 //
-// The collective fusions reuse this skeleton through a Policy type:
-//   Policy::TileCoord(p, linearTile, &mBlk, &nBlk)    tile order (e.g. local rows first for AllGather+matmul)
-//   Policy::WaitRowsReady(p, mBlk, abortWord)         producer-side gate before loading A rows (gathered rows landed?)
-//   Policy::Store(p, row, col0, v[32], lane info)     epilogue sink (local C, a peer's reduce-scatter slot, ...)
-//   Policy::TileDone(p, mBlk, nBlk)                   after a tile's stores (signal the consumer rank)
-// HCCL has no counterpart: its MC2 header only hands a communication context to external fused kernels (reference:
-// include/hccl_mc2.h:25-82, src/common/hccl_mc2.cc:141-165); the kernels themselves are new here.
+// A Policy type customises the skeleton (all hooks are static device functions):
+//   Init(p, ctx)                         per-CTA context (rank, op parity, ...)
+//   CommCtas(p)                          leading CTAs that run CommRole instead of GEMM tiles
+//   CommRole(p, ctx, smem)               e.g. push the local activation shard to every peer with bulk copies
+//   TileCoord(p, ctx, t, mBlocks, nBlocks, &mb, &nb)   tile order
+//   WaitRowsReady(p, ctx, mb, abort)     producer-side gate before loading A rows
+//   SelectA(p, ctx, mb, &tmap, &row)     which tensor map / row coordinate serves this row block
+//   Store(p, ctx, row, col0, v[32])      epilogue sink (local C, a peer's reduce-scatter slot, ...)
+//   TileDone(p, ctx, mb, nb, ew, lane)   after a tile's stores (signal the consumer rank)
+//   PostPhase(p, ctx, cta, ctas, abort)  work after the last tile (ordered reduction of the received partials)
+//   Exit(p, ctx)                         per-CTA exit protocol
+// EMU = true: several ranks share the GPU, blockIdx.y is the rank and parameters come from an array in device memory
+// (cooperative launch; used by the single-GPU tests).
+// HCCL has no counterpart of these kernels: its MC2 header only hands a communication context to external fused
+// kernels (reference: include/hccl_mc2.h:25-82, src/common/hccl_mc2.cc:141-165).
 #pragma once
 #include <cuda_bf16.h>
 #include "sm100_ptx.cuh"
@@ -30,6 +38,8 @@ constexpr int kGemmThreads = 256;
 
 struct GemmParams {
     CUtensorMap tmapA;           // [M, K] bf16, box 64 x 128, 128B swizzle
+    CUtensorMap tmapA1;          // policy-specific second A map (other parity half)
+    CUtensorMap tmapALocal;      // policy-specific third A map (the local shard)
     CUtensorMap tmapB;           // [N, K] bf16, box 64 x BN
     void *C;                     // output, row-major, leading dimension ldc (elements)
     uint32_t M, N, K;
@@ -37,8 +47,7 @@ struct GemmParams {
     uint32_t outFp32;            // 1 = fp32 output
     uint32_t groupM;             // M blocks per rasterisation group
     uint32_t *errorWord;         // device word set to 1 when a wait ran out
-    // fusion fields (meaning defined by the policy)
-    const void *comm;            // DevComm*
+    const void *comm;            // DevComm* of this rank (fused policies)
     uint64_t u64[8];
     uint32_t u32[8];
 };
@@ -52,8 +61,36 @@ template <int BN> struct GemmSmem {
     static constexpr int kTotal = kRing + 256;
 };
 
+__device__ __forceinline__ void StoreRow32(void *C, uint32_t ldc, uint32_t N, bool fp32, uint32_t row, uint32_t col0, const uint32_t (&v)[32])
+{
+    if (fp32) {
+        float *c = (float *)C + (size_t)row * ldc + col0;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+            if (col0 + j < N) *(uint4 *)(c + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    } else {
+        __nv_bfloat16 *c = (__nv_bfloat16 *)C + (size_t)row * ldc + col0;
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+            if (col0 + j < N) {
+                uint4 o;
+                __nv_bfloat162 t0 = __floats2bfloat162_rn(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+                __nv_bfloat162 t1 = __floats2bfloat162_rn(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
+                __nv_bfloat162 t3 = __floats2bfloat162_rn(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
+                o.x = *(uint32_t *)&t0; o.y = *(uint32_t *)&t1; o.z = *(uint32_t *)&t2; o.w = *(uint32_t *)&t3;
+                *(uint4 *)(c + j) = o;
+            }
+        }
+    }
+}
+
 struct PlainPolicy {
-    __device__ static void TileCoord(const GemmParams &p, uint32_t t, uint32_t mBlocks, uint32_t nBlocks, uint32_t *mb, uint32_t *nb)
+    struct Ctx {};
+    __device__ static void Init(const GemmParams &, Ctx &) {}
+    __device__ static uint32_t CommCtas(const GemmParams &) { return 0; }
+    __device__ static void CommRole(const GemmParams &, Ctx &, uint8_t *) {}
+    __device__ static void TileCoord(const GemmParams &p, const Ctx &, uint32_t t, uint32_t mBlocks, uint32_t nBlocks, uint32_t *mb, uint32_t *nb)
     {
         // grouped rasterisation: walk groupM row-blocks down, then move one column-block right
         uint32_t g = p.groupM ? p.groupM : 16;
@@ -65,45 +102,42 @@ struct PlainPolicy {
         *mb = first + in % size;
         *nb = in / size;
     }
-    __device__ static bool WaitRowsReady(const GemmParams &, uint32_t, volatile uint32_t *) { return true; }
-    __device__ static void Store(const GemmParams &p, uint32_t row, uint32_t col0, const uint32_t (&v)[32])
+    __device__ static bool WaitRowsReady(const GemmParams &, const Ctx &, uint32_t, volatile uint32_t *) { return true; }
+    __device__ static void SelectA(const GemmParams &p, const Ctx &, uint32_t mb, const CUtensorMap **tm, int32_t *row)
     {
-        if (row >= p.M) return;
-        if (p.outFp32) {
-            float *c = (float *)p.C + (size_t)row * p.ldc + col0;
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-                if (col0 + j < p.N) *(uint4 *)(c + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-            }
-        } else {
-            __nv_bfloat16 *c = (__nv_bfloat16 *)p.C + (size_t)row * p.ldc + col0;
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-                if (col0 + j < p.N) {
-                    uint4 o;
-                    __nv_bfloat162 t0 = __floats2bfloat162_rn(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
-                    __nv_bfloat162 t1 = __floats2bfloat162_rn(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-                    __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
-                    __nv_bfloat162 t3 = __floats2bfloat162_rn(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
-                    o.x = *(uint32_t *)&t0; o.y = *(uint32_t *)&t1; o.z = *(uint32_t *)&t2; o.w = *(uint32_t *)&t3;
-                    *(uint4 *)(c + j) = o;
-                }
-            }
-        }
+        *tm = &p.tmapA;
+        *row = (int32_t)(mb * kBM);
     }
-    __device__ static void TileDone(const GemmParams &, uint32_t, uint32_t, uint32_t) {}
+    __device__ static void Store(const GemmParams &p, const Ctx &, uint32_t row, uint32_t col0, const uint32_t (&v)[32])
+    {
+        if (row < p.M) StoreRow32(p.C, p.ldc, p.N, p.outFp32 != 0, row, col0, v);
+    }
+    __device__ static void TileDone(const GemmParams &, const Ctx &, uint32_t, uint32_t, uint32_t, uint32_t) {}
+    __device__ static void PostPhase(const GemmParams &, Ctx &, uint32_t, uint32_t, volatile uint32_t *) {}
+    __device__ static void Exit(const GemmParams &, Ctx &) {}
 };
 
-template <int BN, class Policy>
-__global__ void __launch_bounds__(kGemmThreads, 1) GemmKernel(const __grid_constant__ GemmParams p)
+template <int BN, class Policy, bool EMU>
+__global__ void __launch_bounds__(kGemmThreads, 1) GemmKernel(const __grid_constant__ GemmParams pv, const GemmParams *emuParams)
 {
+    const GemmParams &p = EMU ? emuParams[blockIdx.y] : pv;
     using S = GemmSmem<BN>;
     constexpr int STAGES = S::kStages;
     constexpr uint32_t kTmemCols = BN * 2 >= 32 ? BN * 2 : 32;       // two accumulators
     constexpr uint32_t kIdesc = MakeInstrDesc(FMT_BF16, FMT_BF16, kBM, BN);
     extern __shared__ uint8_t smemRaw[];
-    // 1024-byte alignment for the swizzle atoms
-    uint8_t *smem = (uint8_t *)(((uintptr_t)smemRaw + 1023) & ~(uintptr_t)1023);
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smemRaw + 1023) & ~(uintptr_t)1023);   // swizzle atoms want 1024-byte alignment
+
+    typename Policy::Ctx ctx;
+    Policy::Init(p, ctx);
+    const uint32_t commCtas = Policy::CommCtas(p);
+    if (blockIdx.x < commCtas) {
+        Policy::CommRole(p, ctx, smem);
+        Policy::Exit(p, ctx);
+        return;
+    }
+    const uint32_t cta = blockIdx.x - commCtas, ctas = gridDim.x - commCtas;
+
     uint8_t *sA = smem;
     uint8_t *sB = smem + STAGES * S::kABytes;
     uint64_t *full = (uint64_t *)(smem + S::kBarOff);
@@ -123,8 +157,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) GemmKernel(const __grid_const
         for (int s = 0; s < 2; ++s) { MbarInit(&tmemFull[s], 1); MbarInit(&tmemEmpty[s], 128); }
         *abortWord = 0;
         MbarInitFence();
-        PrefetchTmap(&p.tmapA);
-        PrefetchTmap(&p.tmapB);
     }
     if (warp == 2) { TmemAlloc(tmemPtr, kTmemCols); TmemRelinquish(); }
     TcFenceBefore();
@@ -136,15 +168,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1) GemmKernel(const __grid_const
         if (ElectOne()) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            for (uint32_t t = blockIdx.x; t < numTiles && ok; t += gridDim.x) {
+            for (uint32_t t = cta; t < numTiles && ok; t += ctas) {
                 uint32_t mb, nb;
-                Policy::TileCoord(p, t, mBlocks, nBlocks, &mb, &nb);
-                ok = Policy::WaitRowsReady(p, mb, abortWord);
+                Policy::TileCoord(p, ctx, t, mBlocks, nBlocks, &mb, &nb);
+                ok = Policy::WaitRowsReady(p, ctx, mb, abortWord);
+                const CUtensorMap *ta;
+                int32_t rowA;
+                Policy::SelectA(p, ctx, mb, &ta, &rowA);
                 for (uint32_t kb = 0; kb < kIters && ok; ++kb) {
                     ok = MbarWait(&empty[stage], phase ^ 1, abortWord);
                     if (!ok) break;
                     MbarExpectTx(&full[stage], S::kABytes + S::kBBytes);
-                    TmaLoad2D(sA + stage * S::kABytes, &p.tmapA, &full[stage], (int32_t)(kb * kBK), (int32_t)(mb * kBM));
+                    TmaLoad2D(sA + stage * S::kABytes, ta, &full[stage], (int32_t)(kb * kBK), rowA);
                     TmaLoad2D(sB + stage * S::kBBytes, &p.tmapB, &full[stage], (int32_t)(kb * kBK), (int32_t)(nb * BN));
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
@@ -154,7 +189,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) GemmKernel(const __grid_const
         if (ElectOne()) {
             uint32_t stage = 0, phase = 0, acc = 0, accPhase = 0;
             bool ok = true;
-            for (uint32_t t = blockIdx.x; t < numTiles && ok; t += gridDim.x) {
+            for (uint32_t t = cta; t < numTiles && ok; t += ctas) {
                 ok = MbarWait(&tmemEmpty[acc], accPhase ^ 1, abortWord);
                 if (!ok) break;
                 TcFenceAfter();
@@ -181,9 +216,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) GemmKernel(const __grid_const
         const uint32_t ew = warp - 4;
         uint32_t acc = 0, accPhase = 0;
         bool ok = true;
-        for (uint32_t t = blockIdx.x; t < numTiles && ok; t += gridDim.x) {
+        for (uint32_t t = cta; t < numTiles && ok; t += ctas) {
             uint32_t mb, nb;
-            Policy::TileCoord(p, t, mBlocks, nBlocks, &mb, &nb);
+            Policy::TileCoord(p, ctx, t, mBlocks, nBlocks, &mb, &nb);
             ok = MbarWait(&tmemFull[acc], accPhase, abortWord);
             if (!ok) break;
             TcFenceAfter();
@@ -193,18 +228,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1) GemmKernel(const __grid_const
                 uint32_t v[32];
                 TmemLd32x32(tmemBase + ((ew * 32) << 16) + acc * BN + c * 32, v);
                 TmemLdWait();
-                Policy::Store(p, row, nb * BN + c * 32, v);
+                Policy::Store(p, ctx, row, nb * BN + c * 32, v);
             }
             TcFenceBefore();
             MbarArrive(&tmemEmpty[acc]);
-            Policy::TileDone(p, mb, nb, ew);
+            Policy::TileDone(p, ctx, mb, nb, ew, lane);
             acc ^= 1;
             if (acc == 0) accPhase ^= 1;
         }
     }
     __syncthreads();
-    if (threadIdx.x == 0 && *abortWord != 0 && p.errorWord) *p.errorWord = 1;
     if (warp == 2) { TcFenceAfter(); TmemDealloc(tmemBase, kTmemCols); }
+    Policy::PostPhase(p, ctx, cta, ctas, abortWord);
+    if (threadIdx.x == 0 && *abortWord != 0 && p.errorWord) *p.errorWord = 1;
+    Policy::Exit(p, ctx);
 }
 
 }  // namespace mc2

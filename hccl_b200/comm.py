@@ -251,6 +251,9 @@ class Communicator:
         return bool(fn(self._h))
 
 
+_LIVE_STORES = []
+
+
 def _store_exchange_root_info(rank: int, world: int) -> bytes:
     """Shares rank 0's root info through a torch TCPStore on MASTER_ADDR:(MASTER_PORT + 17)."""
     import os
@@ -261,6 +264,7 @@ def _store_exchange_root_info(rank: int, world: int) -> bytes:
     host = os.environ.get("MASTER_ADDR", "127.0.0.1")
     port = int(os.environ.get("MASTER_PORT", "29500")) + 17
     store = TCPStore(host, port, world, is_master=(rank == 0), timeout=timedelta(seconds=120), wait_for_workers=False)
+    _LIVE_STORES.append(store)   # the server side lives in rank 0: keep it until the process exits
     key = "hccl_b200_root_info_" + os.environ.get("HCCL_B200_COMM_EPOCH", "0")
     if rank == 0:
         store.set(key, get_root_info())

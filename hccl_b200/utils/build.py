@@ -73,6 +73,7 @@ def build_native(verbose: bool = False, ptxas_info: bool = False) -> Path:
     out = LIBDIR / "libhccl_b200.so"
     lines = [
         "ninja_required_version = 1.3",
+        f"builddir = {BUILD}",
         f"cxx = {shutil.which('g++') or 'g++'}",
         f"nvcc = {CUDA_HOME / 'bin' / 'nvcc'}",
         f"cxxflags = {' '.join(cxxflags)}",
@@ -125,6 +126,7 @@ def build_torch_ext(verbose: bool = False) -> Path:
         ldflags += ["-lc10_cuda", "-ltorch_cuda"]
     lines = [
         "ninja_required_version = 1.3",
+        f"builddir = {BUILD}",
         f"cxx = {shutil.which('g++') or 'g++'}",
         f"cxxflags = {' '.join(cxxflags)}",
         f"ldflags = {' '.join(ldflags)}",

@@ -6,6 +6,7 @@
 #include "../common/dtype.h"
 #include "../common/log.h"
 #include "coll_args.h"
+#include "emu_world.h"
 #include "hccl/hccl_dfx.h"
 
 namespace hccl {
@@ -57,18 +58,6 @@ HcclResult SmOrchestrate(Comm *c, OpParam &p, const std::string &algName)
     return HCCL_SUCCESS;
 }
 
-// ------------------------------------------------------------------------------------------------ emulation world
-struct EmuWorld {
-    int nranks = 0;
-    std::vector<char *> heaps;
-    DevComm *devComms = nullptr;
-    std::vector<DevComm> hostComms;
-    DevStatus *status = nullptr;       // pinned, one per rank
-    CollArgs *devArgs = nullptr;
-    BatchArgs *devBatch = nullptr;
-    uint64_t cclBytes = 0, mailboxBytes = 0;
-};
-
 }  // namespace hccl
 
 using namespace hccl;
@@ -81,7 +70,7 @@ using namespace hccl;
 
 extern "C" {
 
-HcclResult HcclEmuCreate(uint32_t nranks, uint64_t cclBytes, uint32_t waitTimeoutMs, void **emu)
+HcclResult HcclEmuCreate(uint32_t nranks, uint64_t cclBytes, uint64_t arenaBytes, uint32_t waitTimeoutMs, void **emu)
 {
     if (!emu || nranks == 0 || nranks > (uint32_t)kMaxRanks) return HCCL_E_PARA;
     auto *w = new EmuWorld();
@@ -89,7 +78,9 @@ HcclResult HcclEmuCreate(uint32_t nranks, uint64_t cclBytes, uint32_t waitTimeou
     w->cclBytes = (cclBytes + 127) & ~127ull;
     w->mailboxBytes = 256 << 10;
     uint64_t mailboxTotal = w->mailboxBytes * 2 * nranks;
-    uint64_t heapBytes = kHeapHeaderBytes + 2 * w->cclBytes + mailboxTotal;
+    w->arenaOff = (kHeapHeaderBytes + 2 * w->cclBytes + mailboxTotal + 1023) & ~1023ull;
+    w->arenaBytes = arenaBytes;
+    uint64_t heapBytes = w->arenaOff + arenaBytes;
     EMU_RT(cudaHostAlloc((void **)&w->status, sizeof(DevStatus) * nranks, cudaHostAllocMapped));
     memset(w->status, 0, sizeof(DevStatus) * nranks);
     DevStatus *devStatus = nullptr;
@@ -108,6 +99,7 @@ HcclResult HcclEmuCreate(uint32_t nranks, uint64_t cclBytes, uint32_t waitTimeou
         d.mcHeap = nullptr;
         d.cclOff[0] = kHeapHeaderBytes; d.cclOff[1] = kHeapHeaderBytes + w->cclBytes; d.cclBytes = w->cclBytes;
         d.mailboxOff = kHeapHeaderBytes + 2 * w->cclBytes; d.mailboxBytes = w->mailboxBytes;
+        d.arenaOff = w->arenaOff; d.arenaBytes = w->arenaBytes;
         d.timeoutNs = (uint64_t)waitTimeoutMs * 1000000ull;
         d.status = devStatus + r;
         d.emuRanks = (int)nranks;
@@ -116,6 +108,7 @@ HcclResult HcclEmuCreate(uint32_t nranks, uint64_t cclBytes, uint32_t waitTimeou
     EMU_RT(cudaMemcpy(w->devComms, w->hostComms.data(), sizeof(DevComm) * nranks, cudaMemcpyHostToDevice));
     EMU_RT(cudaMalloc((void **)&w->devArgs, sizeof(CollArgs) * nranks));
     EMU_RT(cudaMalloc((void **)&w->devBatch, sizeof(BatchArgs) * nranks));
+    EMU_RT(cudaMalloc(&w->devFusedParams, 2048 * nranks));
     EMU_RT(cudaDeviceSynchronize());
     *emu = w;
     return HCCL_SUCCESS;
@@ -130,6 +123,7 @@ HcclResult HcclEmuDestroy(void *emu)
     cudaFree(w->devComms);
     cudaFree(w->devArgs);
     cudaFree(w->devBatch);
+    cudaFree(w->devFusedParams);
     cudaFreeHost(w->status);
     delete w;
     return HCCL_SUCCESS;

@@ -1,0 +1,307 @@
+// Policies that turn the tcgen05 GEMM skeleton into the three fused matmul + collective operators.
+//
+//   AgmmPolicy   AllGather + matmul: leading "comm" CTAs push the local activation shard to every peer's gather buffer
+//                with bulk copies through shared memory (one counter bump per 128-row block); GEMM CTAs start with the
+//                local rows and take the peers' row blocks in arrival order, gating only the TMA producer.
+//   MmrsPolicy   matmul + ReduceScatter: tiles destined to other ranks are computed first and their bf16 partials are
+//                stored straight into the owner's slot; after its last tile every CTA reduces a share of the rows this
+//                rank owns, in rank order with fp32 accumulation.
+//   MmarPolicy   matmul + AllReduce for decode-sized M: partial tiles go to the column owner, owners reduce and write the
+//                result into every rank's result window, each rank copies its window to the user buffer.
+#pragma once
+#include "fused_common.cuh"
+
+namespace hccl {
+namespace mc2 {
+
+// =============================================================================================== AllGather + matmul
+struct AgmmPolicy {
+    using Ctx = FusedCtx;
+    // u64: 0 gatherOff (half 0), 1 gatherBytes per half, 2 aLocal   u32: 0 mLocal, 1 commCtas, 2 blocksPerRank
+    __device__ static void Init(const GemmParams &p, Ctx &x) { FusedInit(p, x); }
+    __device__ static uint32_t CommCtas(const GemmParams &p) { return p.u32[1]; }
+
+    __device__ static void CommRole(const GemmParams &p, Ctx &x, uint8_t *smem)
+    {
+        constexpr uint32_t SLOTS = 8, PIECE = 16384;
+        uint64_t *full = (uint64_t *)(smem + SLOTS * PIECE);
+        uint64_t *empty = full + SLOTS;
+        volatile uint32_t *abortWord = (volatile uint32_t *)(empty + SLOTS);
+        if (threadIdx.x == 0) {
+            for (uint32_t s = 0; s < SLOTS; ++s) { MbarInit(&full[s], 1); MbarInit(&empty[s], 1); }
+            *abortWord = 0;
+            MbarInitFence();
+        }
+        __syncthreads();
+        const uint32_t bpr = p.u32[2], n = (uint32_t)x.n, C = p.u32[1];
+        const uint64_t blockBytes = (uint64_t)kBM * p.K * 2;
+        const uint32_t pieces = (uint32_t)((blockBytes + PIECE - 1) / PIECE);
+        const char *aLocal = (const char *)p.u64[2];
+        const uint64_t gatherBase = p.u64[0] + (uint64_t)x.half * p.u64[1];
+        const uint32_t items = (n - 1) * bpr;
+        const uint32_t warp = threadIdx.x >> 5;
+        if (warp == 0 && ElectOne()) {            // loader: local shard -> shared memory ring
+            uint32_t j = 0;
+            for (uint32_t it = blockIdx.x; it < items; it += C) {
+                uint32_t blk = it % bpr;
+                const char *src = aLocal + (uint64_t)blk * blockBytes;
+                for (uint32_t q = 0; q < pieces; ++q, ++j) {
+                    uint32_t s = j % SLOTS, ph = (j / SLOTS) & 1;
+                    if (!MbarWait(&empty[s], ph ^ 1, abortWord)) return;
+                    uint32_t bytes = (uint32_t)(blockBytes - (uint64_t)q * PIECE < PIECE ? blockBytes - (uint64_t)q * PIECE : PIECE);
+                    MbarExpectTx(&full[s], bytes);
+                    BulkLoad(smem + s * PIECE, src + (uint64_t)q * PIECE, bytes, &full[s]);
+                }
+            }
+        } else if (warp == 1 && ElectOne()) {     // storer: ring -> the peer's gather buffer, then bump its counter
+            uint32_t j = 0, rel = 0;              // pieces stored / ring slots handed back to the loader
+            for (uint32_t it = blockIdx.x; it < items; it += C) {
+                uint32_t d = it / bpr + 1, blk = it % bpr;
+                uint32_t peer = ((uint32_t)x.rank + d) % n;
+                char *dst = x.c->heap[peer] + gatherBase + ((uint64_t)x.rank * p.u32[0] + (uint64_t)blk * kBM) * p.K * 2;
+                for (uint32_t q = 0; q < pieces; ++q, ++j) {
+                    uint32_t s = j % SLOTS, ph = (j / SLOTS) & 1;
+                    if (!MbarWait(&full[s], ph, abortWord)) return;
+                    uint32_t bytes = (uint32_t)(blockBytes - (uint64_t)q * PIECE < PIECE ? blockBytes - (uint64_t)q * PIECE : PIECE);
+                    BulkStore(dst + (uint64_t)q * PIECE, smem + s * PIECE, bytes);
+                    TmaStoreCommit();
+                    BulkWaitRead<1>();             // every piece before this one has left shared memory
+                    for (; rel < j; ++rel) MbarArrive(&empty[rel % SLOTS]);
+                }
+                TmaStoreWaitAll();                 // every byte of this block is written at the peer
+                for (; rel < j; ++rel) MbarArrive(&empty[rel % SLOTS]);
+                FenceProxyAsyncGlobal();
+                __threadfence_system();
+                RemoteAddRelease(&FlagsOf(x.c->heap[peer])->mc2Ready[x.half][x.rank][blk], 1u);
+            }
+        }
+    }
+
+    __device__ static void TileCoord(const GemmParams &p, const Ctx &x, uint32_t t, uint32_t, uint32_t nBlocks, uint32_t *mb, uint32_t *nb)
+    {
+        const uint32_t bpr = p.u32[2], perSrc = bpr * nBlocks;
+        uint32_t d = t / perSrc, rem = t % perSrc;
+        uint32_t src = ((uint32_t)x.rank + (uint32_t)x.n - d % (uint32_t)x.n) % (uint32_t)x.n;
+        *mb = src * bpr + rem / nBlocks;
+        *nb = rem % nBlocks;
+    }
+    __device__ static bool WaitRowsReady(const GemmParams &p, const Ctx &x, uint32_t mb, volatile uint32_t *abortWord)
+    {
+        const uint32_t bpr = p.u32[2], src = mb / bpr, blk = mb % bpr;
+        if ((int)src == x.rank) return true;
+        Ctx &xm = const_cast<Ctx &>(x);
+        bool ok = WaitCounterGe(xm, &x.flags->mc2Ready[x.half][src][blk], 1u, src, 31, abortWord);
+        asm volatile("fence.proxy.async;" ::: "memory");   // peer's generic/async writes -> this CTA's TMA reads
+        return ok;
+    }
+    __device__ static void SelectA(const GemmParams &p, const Ctx &x, uint32_t mb, const CUtensorMap **tm, int32_t *row)
+    {
+        const uint32_t bpr = p.u32[2], src = mb / bpr, blk = mb % bpr;
+        if ((int)src == x.rank) { *tm = &p.tmapALocal; *row = (int32_t)(blk * kBM); }
+        else { *tm = x.half ? &p.tmapA1 : &p.tmapA; *row = (int32_t)(mb * kBM); }
+    }
+    __device__ static void Store(const GemmParams &p, const Ctx &, uint32_t row, uint32_t col0, const uint32_t (&v)[32])
+    {
+        if (row < p.M) StoreRow32(p.C, p.ldc, p.N, p.outFp32 != 0, row, col0, v);
+    }
+    __device__ static void TileDone(const GemmParams &, const Ctx &, uint32_t, uint32_t, uint32_t, uint32_t) {}
+    __device__ static void PostPhase(const GemmParams &, Ctx &, uint32_t, uint32_t, volatile uint32_t *) {}
+    __device__ static void Exit(const GemmParams &, Ctx &x) { FusedExit(x); }
+};
+
+// Stores 32 fp32 accumulators of one row as bf16 (64 bytes) at `dst` (16-byte aligned, local or peer memory).
+__device__ __forceinline__ void StoreBf16x32(__nv_bfloat16 *dst, const uint32_t (&v)[32], uint32_t validCols = 32)
+{
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+        if ((uint32_t)j >= validCols) break;
+        uint4 o;
+        __nv_bfloat162 t0 = __floats2bfloat162_rn(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+        __nv_bfloat162 t1 = __floats2bfloat162_rn(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+        __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
+        __nv_bfloat162 t3 = __floats2bfloat162_rn(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
+        o.x = *(uint32_t *)&t0; o.y = *(uint32_t *)&t1; o.z = *(uint32_t *)&t2; o.w = *(uint32_t *)&t3;
+        *(uint4 *)(dst + j) = o;
+    }
+}
+
+// acc[0..7] (+)= the 8 bf16 values of `raw`
+__device__ __forceinline__ void AccumBf16x8(float (&acc)[8], uint4 raw, bool first)
+{
+    const __nv_bfloat162 *h = (const __nv_bfloat162 *)&raw;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        float2 f = __bfloat1622float2(h[j]);
+        if (first) { acc[2 * j] = f.x; acc[2 * j + 1] = f.y; }
+        else { acc[2 * j] += f.x; acc[2 * j + 1] += f.y; }
+    }
+}
+__device__ __forceinline__ uint4 PackBf16x8(const float (&acc)[8])
+{
+    uint4 o;
+    __nv_bfloat162 t0 = __floats2bfloat162_rn(acc[0], acc[1]), t1 = __floats2bfloat162_rn(acc[2], acc[3]);
+    __nv_bfloat162 t2 = __floats2bfloat162_rn(acc[4], acc[5]), t3 = __floats2bfloat162_rn(acc[6], acc[7]);
+    o.x = *(uint32_t *)&t0; o.y = *(uint32_t *)&t1; o.z = *(uint32_t *)&t2; o.w = *(uint32_t *)&t3;
+    return o;
+}
+
+// 128 epilogue threads (warps 4..7) meet on named barrier 1
+__device__ __forceinline__ void EpilogueBarrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// =============================================================================================== matmul + ReduceScatter
+struct MmrsPolicy {
+    using Ctx = FusedCtx;
+    // u64: 0 wsOff (half 0), 1 wsBytes per half   u32: 0 mOwn (rows per rank), 1 blocksPerOwner, 2 nBlocks (N / BN)
+    __device__ static void Init(const GemmParams &p, Ctx &x) { FusedInit(p, x); }
+    __device__ static uint32_t CommCtas(const GemmParams &) { return 0; }
+    __device__ static void CommRole(const GemmParams &, Ctx &, uint8_t *) {}
+    // other owners first (rank+1, rank+2, ...), own rows last
+    __device__ static void TileCoord(const GemmParams &p, const Ctx &x, uint32_t t, uint32_t, uint32_t nBlocks, uint32_t *mb, uint32_t *nb)
+    {
+        const uint32_t bpo = p.u32[1], perOwner = bpo * nBlocks, n = (uint32_t)x.n;
+        uint32_t d = t / perOwner, rem = t % perOwner;
+        uint32_t owner = ((uint32_t)x.rank + 1 + d) % n;
+        *mb = owner * bpo + rem / nBlocks;
+        *nb = rem % nBlocks;
+    }
+    __device__ static bool WaitRowsReady(const GemmParams &, const Ctx &, uint32_t, volatile uint32_t *) { return true; }
+    __device__ static void SelectA(const GemmParams &p, const Ctx &, uint32_t mb, const CUtensorMap **tm, int32_t *row)
+    {
+        *tm = &p.tmapA;
+        *row = (int32_t)(mb * kBM);
+    }
+    __device__ static void Store(const GemmParams &p, const Ctx &x, uint32_t row, uint32_t col0, const uint32_t (&v)[32])
+    {
+        if (row >= p.M || col0 >= p.N) return;
+        const uint32_t mOwn = p.u32[0], owner = row / mOwn, r = row - owner * mOwn;
+        char *ws = x.c->heap[owner] + p.u64[0] + (uint64_t)x.half * p.u64[1];
+        __nv_bfloat16 *dst = (__nv_bfloat16 *)ws + ((uint64_t)x.rank * mOwn + r) * p.N + col0;
+        StoreBf16x32(dst, v, p.N - col0);
+    }
+    __device__ static void TileDone(const GemmParams &p, const Ctx &x, uint32_t mb, uint32_t, uint32_t ew, uint32_t lane)
+    {
+        EpilogueBarrier();
+        if (ew == 0 && lane == 0) {
+            const uint32_t bpo = p.u32[1], owner = mb / bpo, blk = mb % bpo;
+            __threadfence_system();
+            RemoteAddRelease(&FlagsOf(x.c->heap[owner])->mc2Ready[x.half][x.rank][blk], 1u);
+        }
+    }
+    // ordered reduction of the rows this rank owns: out[r, :] = sum over src (rank order) of slot[src][r, :]
+    __device__ static void PostPhase(const GemmParams &p, Ctx &x, uint32_t cta, uint32_t ctas, volatile uint32_t *abortWord)
+    {
+        const uint32_t mOwn = p.u32[0], bpo = p.u32[1], nBlocks = p.u32[2], n = (uint32_t)x.n;
+        const uint32_t colChunks = (p.N + 255) / 256;
+        const char *ws = x.heap + p.u64[0] + (uint64_t)x.half * p.u64[1];
+        for (uint32_t u = cta; u < bpo * colChunks; u += ctas) {
+            const uint32_t blk = u / colChunks, cc = u % colChunks;
+            bool mine = true;
+            if (threadIdx.x < n) mine = WaitCounterGe(x, &x.flags->mc2Ready[x.half][threadIdx.x][blk], nBlocks, threadIdx.x, 41, abortWord);
+            if (!__syncthreads_and(mine ? 1 : 0)) return;
+            const uint32_t colsHere = p.N - cc * 256 < 256 ? p.N - cc * 256 : 256, vecPerRow = colsHere / 8;
+            const uint32_t rows = mOwn - blk * kBM < (uint32_t)kBM ? mOwn - blk * kBM : (uint32_t)kBM;
+            for (uint32_t v = threadIdx.x; v < rows * vecPerRow; v += blockDim.x) {
+                const uint32_t r = blk * kBM + v / vecPerRow, c = cc * 256 + (v % vecPerRow) * 8;
+                float acc[8];
+                for (uint32_t s = 0; s < n; ++s) {
+                    uint4 raw = *(const uint4 *)((const __nv_bfloat16 *)ws + ((uint64_t)s * mOwn + r) * p.N + c);
+                    AccumBf16x8(acc, raw, s == 0);
+                }
+                *(uint4 *)((__nv_bfloat16 *)p.C + (uint64_t)r * p.ldc + c) = PackBf16x8(acc);
+            }
+        }
+    }
+    __device__ static void Exit(const GemmParams &, Ctx &x) { FusedExit(x); }
+};
+
+// =============================================================================================== matmul + AllReduce (decode)
+struct MmarPolicy {
+    using Ctx = FusedCtx;
+    // u64: 0 wsOff, 1 wsBytes per half ([src][M][colsOwn] bf16), 2 resOff, 3 resBytes per half ([M][N] bf16)
+    // u32: 0 colsOwn (N / ranks), 1 tilesPerOwnerRow (colsOwn / BN), 2 BN
+    __device__ static void Init(const GemmParams &p, Ctx &x) { FusedInit(p, x); }
+    __device__ static uint32_t CommCtas(const GemmParams &) { return 0; }
+    __device__ static void CommRole(const GemmParams &, Ctx &, uint8_t *) {}
+    __device__ static void TileCoord(const GemmParams &, const Ctx &x, uint32_t t, uint32_t mBlocks, uint32_t nBlocks, uint32_t *mb, uint32_t *nb)
+    {
+        // rotate the column blocks so that every rank starts with tiles owned by its right neighbour
+        uint32_t nbRaw = t / mBlocks;
+        uint32_t shift = ((uint32_t)x.rank + 1) * (nBlocks / (uint32_t)x.n);
+        *nb = (nbRaw + shift) % nBlocks;
+        *mb = t % mBlocks;
+    }
+    __device__ static bool WaitRowsReady(const GemmParams &, const Ctx &, uint32_t, volatile uint32_t *) { return true; }
+    __device__ static void SelectA(const GemmParams &p, const Ctx &, uint32_t mb, const CUtensorMap **tm, int32_t *row)
+    {
+        *tm = &p.tmapA;
+        *row = (int32_t)(mb * kBM);
+    }
+    __device__ static void Store(const GemmParams &p, const Ctx &x, uint32_t row, uint32_t col0, const uint32_t (&v)[32])
+    {
+        if (row >= p.M || col0 >= p.N) return;
+        const uint32_t colsOwn = p.u32[0], owner = col0 / colsOwn;
+        char *ws = x.c->heap[owner] + p.u64[0] + (uint64_t)x.half * p.u64[1];
+        __nv_bfloat16 *dst = (__nv_bfloat16 *)ws + ((uint64_t)x.rank * p.M + row) * colsOwn + (col0 - owner * colsOwn);
+        StoreBf16x32(dst, v);
+    }
+    __device__ static uint32_t CounterIndex(const GemmParams &p, uint32_t mb, uint32_t nb)
+    {
+        return (mb * p.u32[1] + nb % p.u32[1]) & 63u;
+    }
+    __device__ static void TileDone(const GemmParams &p, const Ctx &x, uint32_t mb, uint32_t nb, uint32_t ew, uint32_t lane)
+    {
+        EpilogueBarrier();
+        if (ew == 0 && lane == 0) {
+            const uint32_t owner = nb / p.u32[1];
+            __threadfence_system();
+            RemoteAddRelease(&FlagsOf(x.c->heap[owner])->mc2Ready[x.half][x.rank][CounterIndex(p, mb, nb)], 1u);
+        }
+    }
+    __device__ static void PostPhase(const GemmParams &p, Ctx &x, uint32_t cta, uint32_t ctas, volatile uint32_t *abortWord)
+    {
+        const uint32_t colsOwn = p.u32[0], tpr = p.u32[1], BN = p.u32[2], n = (uint32_t)x.n;
+        const uint32_t mBlocks = (p.M + kBM - 1) / kBM;
+        constexpr uint32_t ROWS = 16;                        // rows per reduce unit
+        const uint32_t rowChunks = kBM / ROWS;
+        const uint32_t units = mBlocks * tpr * rowChunks;    // reduce units this rank owns
+        const char *ws = x.heap + p.u64[0] + (uint64_t)x.half * p.u64[1];
+        const uint64_t resBase = p.u64[2] + (uint64_t)x.half * p.u64[3];
+        // stage A: reduce the tiles this rank owns and write the result into every rank's result window
+        for (uint32_t u = cta; u < units; u += ctas) {
+            const uint32_t tile = u / rowChunks, rc = u % rowChunks, mb = tile / tpr, tc = tile % tpr;
+            bool mine = true;
+            if (threadIdx.x < n) mine = WaitCounterGe(x, &x.flags->mc2Ready[x.half][threadIdx.x][(mb * tpr + tc) & 63u], 1u, threadIdx.x, 51, abortWord);
+            if (!__syncthreads_and(mine ? 1 : 0)) return;
+            const uint32_t vecPerRow = BN / 8;
+            for (uint32_t v = threadIdx.x; v < ROWS * vecPerRow; v += blockDim.x) {
+                const uint32_t r = mb * kBM + rc * ROWS + v / vecPerRow, c = tc * BN + (v % vecPerRow) * 8;
+                if (r >= p.M) continue;
+                float acc[8];
+                for (uint32_t s = 0; s < n; ++s) {
+                    uint4 raw = *(const uint4 *)((const __nv_bfloat16 *)ws + ((uint64_t)s * p.M + r) * colsOwn + c);
+                    AccumBf16x8(acc, raw, s == 0);
+                }
+                uint4 packed = PackBf16x8(acc);
+                for (uint32_t q = 0; q < n; ++q) {
+                    uint32_t dstRank = ((uint32_t)x.rank + q) % n;
+                    *(uint4 *)((__nv_bfloat16 *)(x.c->heap[dstRank] + resBase) + (uint64_t)r * p.N + (uint64_t)x.rank * colsOwn + c) = packed;
+                }
+            }
+            __syncthreads();
+            if (threadIdx.x < n) {
+                __threadfence_system();
+                RemoteAddRelease(&FlagsOf(x.c->heap[threadIdx.x])->mc2Done[x.half][x.rank][0], 1u);
+            }
+        }
+        // stage B: all owners have delivered -> copy the result window to the user buffer
+        bool mine = true;
+        if (threadIdx.x < n) mine = WaitCounterGe(x, &x.flags->mc2Done[x.half][threadIdx.x][0], units, threadIdx.x, 52, abortWord);
+        if (!__syncthreads_and(mine ? 1 : 0)) return;
+        dev::Part part = dev::PartOf((uint64_t)p.M * p.N * 2, ctas, cta);
+        dev::BlockCopy((char *)p.C + part.off, x.heap + resBase + part.off, part.len);
+    }
+    __device__ static void Exit(const GemmParams &, Ctx &x) { FusedExit(x); }
+};
+
+}  // namespace mc2
+}  // namespace hccl

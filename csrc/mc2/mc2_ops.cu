@@ -1,0 +1,267 @@
+// Host side of the fused matmul + collective operators: argument checks, symmetric workspace, tensor maps, launch.
+// Real communicators launch one kernel per rank (cooperatively, so every CTA of the op is resident); the emulation
+// entry launches one kernel for all ranks of a single-GPU world.
+#include <algorithm>
+#include <map>
+#include <mutex>
+#include "../common/dtype.h"
+#include "../common/log.h"
+#include "../core/comm.h"
+#include "../exec/op_common.h"
+#include "../kernels/emu_world.h"
+#include "fused_policies.cuh"
+#include "gemm_host.h"
+#include "hccl/hccl_mc2.h"
+
+namespace hccl {
+namespace mc2 {
+
+namespace {
+
+enum FusedKind { AGMM = 0, MMRS = 1, MMAR = 2 };
+
+struct FusedShape {
+    FusedKind kind;
+    uint32_t n, rank;
+    uint64_t m, N, K;          // AGMM: m = mLocal; MMRS/MMAR: m = full M, K = kLocal
+};
+
+// workspace bytes per parity half
+uint64_t WorkspaceHalfBytes(const FusedShape &s)
+{
+    switch (s.kind) {
+        case AGMM: return (uint64_t)s.n * s.m * s.K * 2;
+        case MMRS: return (uint64_t)s.m * s.N * 2;                       // n slots of (m/n) x N
+        default: return (uint64_t)s.n * s.m * (s.N / s.n) * 2 + (uint64_t)s.m * s.N * 2;   // partial slots + result window
+    }
+}
+
+uint32_t CommCtasDefault()
+{
+    if (const char *e = getenv("HCCL_MC2_COMM_CTAS")) { int v = atoi(e); if (v > 0 && v < 64) return (uint32_t)v; }
+    return 8;
+}
+
+template <int BN, class Policy, bool EMU> HcclResult SetSmemAttr()
+{
+    static bool done = false;
+    if (!done) {
+        auto kern = GemmKernel<BN, Policy, EMU>;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN>::kTotal + 1024) != cudaSuccess) return HCCL_E_RUNTIME;
+        done = true;
+    }
+    return HCCL_SUCCESS;
+}
+
+// Fills everything except the DevComm pointer. heapLocal = this rank's heap base as mapped here.
+HcclResult BuildParams(const FusedShape &s, char *heapLocal, uint64_t wsOff, const void *a, const void *b, void *out, uint32_t commCtas, GemmParams *p)
+{
+    memset(p, 0, sizeof(*p));
+    const uint64_t half = WorkspaceHalfBytes(s);
+    p->errorWord = GemmErrorWord();
+    p->groupM = 16;
+    p->outFp32 = 0;
+    if (s.kind == AGMM) {
+        p->M = (uint32_t)(s.n * s.m); p->N = (uint32_t)s.N; p->K = (uint32_t)s.K; p->ldc = (uint32_t)s.N; p->C = out;
+        CHK_RET(EncodeTmap2D(&p->tmapA, heapLocal + wsOff, p->M, s.K, s.K * 2, kBM, kBK, 2));
+        CHK_RET(EncodeTmap2D(&p->tmapA1, heapLocal + wsOff + half, p->M, s.K, s.K * 2, kBM, kBK, 2));
+        CHK_RET(EncodeTmap2D(&p->tmapALocal, a, s.m, s.K, s.K * 2, kBM, kBK, 2));
+        CHK_RET(EncodeTmap2D(&p->tmapB, b, s.N, s.K, s.K * 2, 256, kBK, 2));
+        p->u64[0] = wsOff; p->u64[1] = half; p->u64[2] = (uint64_t)(uintptr_t)a;
+        p->u32[0] = (uint32_t)s.m; p->u32[1] = commCtas; p->u32[2] = (uint32_t)(s.m / kBM);
+    } else if (s.kind == MMRS) {
+        p->M = (uint32_t)s.m; p->N = (uint32_t)s.N; p->K = (uint32_t)s.K; p->ldc = (uint32_t)s.N; p->C = out;
+        CHK_RET(EncodeTmap2D(&p->tmapA, a, s.m, s.K, s.K * 2, kBM, kBK, 2));
+        CHK_RET(EncodeTmap2D(&p->tmapB, b, s.N, s.K, s.K * 2, 256, kBK, 2));
+        p->u64[0] = wsOff; p->u64[1] = half;
+        p->u32[0] = (uint32_t)(s.m / s.n); p->u32[1] = (uint32_t)(s.m / s.n / kBM); p->u32[2] = (uint32_t)((s.N + 255) / 256);
+    } else {
+        const uint32_t colsOwn = (uint32_t)(s.N / s.n);
+        p->M = (uint32_t)s.m; p->N = (uint32_t)s.N; p->K = (uint32_t)s.K; p->ldc = (uint32_t)s.N; p->C = out;
+        CHK_RET(EncodeTmap2D(&p->tmapA, a, s.m, s.K, s.K * 2, kBM, kBK, 2));
+        CHK_RET(EncodeTmap2D(&p->tmapB, b, s.N, s.K, s.K * 2, 64, kBK, 2));
+        const uint64_t partials = (uint64_t)s.n * s.m * colsOwn * 2, result = (uint64_t)s.m * s.N * 2;
+        p->u64[0] = wsOff; p->u64[1] = partials; p->u64[2] = wsOff + 2 * partials; p->u64[3] = result;
+        p->u32[0] = colsOwn; p->u32[1] = colsOwn / 64; p->u32[2] = 64;
+    }
+    return HCCL_SUCCESS;
+}
+
+uint32_t GridFor(const FusedShape &s, uint32_t commCtas, uint32_t maxCtas)
+{
+    uint64_t tiles;
+    if (s.kind == AGMM) tiles = (s.n * s.m / kBM) * ((s.N + 255) / 256);
+    else if (s.kind == MMRS) tiles = ((s.m + kBM - 1) / kBM) * ((s.N + 255) / 256);
+    else tiles = ((s.m + kBM - 1) / kBM) * (s.N / 64);
+    uint32_t g = (uint32_t)std::min<uint64_t>(tiles + commCtas, maxCtas);
+    return std::max(g, commCtas + 1);
+}
+
+HcclResult CheckShape(const FusedShape &s)
+{
+    if (s.K % 8 || s.N % 8 || s.m == 0 || s.N == 0 || s.K == 0) { HCCL_ERROR("fused matmul: K and N must be non-zero multiples of 8"); return HCCL_E_PARA; }
+    if (s.kind == AGMM && s.m % kBM) { HCCL_ERROR("AllGatherMatmul: rows per rank (%llu) must be a multiple of 128", (unsigned long long)s.m); return HCCL_E_PARA; }
+    if (s.kind == AGMM && s.m / kBM > 64) { HCCL_ERROR("AllGatherMatmul: at most 8192 rows per rank"); return HCCL_E_PARA; }
+    if (s.kind == MMRS && (s.m % ((uint64_t)s.n * kBM) || s.m / s.n / kBM > 64)) { HCCL_ERROR("MatmulReduceScatter: M (%llu) must be a multiple of 128 x ranks, at most 8192 rows per rank", (unsigned long long)s.m); return HCCL_E_PARA; }
+    if (s.kind == MMAR && (s.N % ((uint64_t)s.n * 64) || ((s.m + kBM - 1) / kBM) * (s.N / s.n / 64) > 64)) {
+        HCCL_ERROR("MatmulAllReduce: N (%llu) must be a multiple of 64 x ranks and the tiles per owner at most 64", (unsigned long long)s.N);
+        return HCCL_E_PARA;
+    }
+    return HCCL_SUCCESS;
+}
+
+template <bool EMU> HcclResult LaunchFused(const FusedShape &s, const GemmParams &p, const GemmParams *devParams, uint32_t grid, uint32_t ranksY, cudaStream_t stream)
+{
+    const void *fn = nullptr;
+    size_t smem = 0;
+    if (s.kind == AGMM) { CHK_RET((SetSmemAttr<256, AgmmPolicy, EMU>())); fn = (const void *)GemmKernel<256, AgmmPolicy, EMU>; smem = GemmSmem<256>::kTotal + 1024; }
+    else if (s.kind == MMRS) { CHK_RET((SetSmemAttr<256, MmrsPolicy, EMU>())); fn = (const void *)GemmKernel<256, MmrsPolicy, EMU>; smem = GemmSmem<256>::kTotal + 1024; }
+    else { CHK_RET((SetSmemAttr<64, MmarPolicy, EMU>())); fn = (const void *)GemmKernel<64, MmarPolicy, EMU>; smem = GemmSmem<64>::kTotal + 1024; }
+    GemmParams pv = p;
+    void *args[] = {(void *)&pv, (void *)&devParams};
+    cudaError_t e = cudaLaunchCooperativeKernel(fn, dim3(grid, ranksY), dim3(kGemmThreads), args, smem, stream);
+    if (e != cudaSuccess) { HCCL_ERROR("fused kernel launch failed: %s (grid %u x %u)", cudaGetErrorString(e), grid, ranksY); return HCCL_E_RUNTIME; }
+    return HCCL_SUCCESS;
+}
+
+// ---- symmetric workspace per communicator (grown on demand; every rank makes the same calls, so offsets agree)
+struct Workspace { void *ptr = nullptr; uint64_t bytes = 0; };
+std::mutex g_wsMu;
+std::map<Comm *, Workspace> g_ws;
+
+HcclResult EnsureWorkspace(Comm *c, uint64_t bytes, uint64_t *off)
+{
+    std::lock_guard<std::mutex> lk(g_wsMu);
+    Workspace &w = g_ws[c];
+    if (w.bytes < bytes) {
+        if (w.ptr) {
+            // the old window may still be in use by kernels in flight on this or a peer rank
+            cudaDeviceSynchronize();
+            CHK_RET(c->boot->Barrier());
+            SymFree(c, w.ptr);
+            w.ptr = nullptr;
+            w.bytes = 0;
+        }
+        uint64_t want = (bytes + (1 << 20) - 1) & ~((1ull << 20) - 1);
+        CHK_RET(SymAlloc(c, want, &w.ptr));
+        w.bytes = want;
+    }
+    *off = SymOffsetOf(c, w.ptr);
+    return HCCL_SUCCESS;
+}
+
+// copies the gathered activations of the op that just ran (parity = opCount - 1) into a user buffer
+__global__ void CopyGatheredKernel(const DevComm *c, uint64_t gatherOff, uint64_t halfBytes, const char *aLocal, char *dst, uint64_t shardBytes)
+{
+    char *heap = c->heap[c->rank];
+    uint32_t half = (CtrlOf(heap)->opCount - 1u) & 1u;
+    const char *src = heap + gatherOff + (uint64_t)half * halfBytes;
+    for (int r = 0; r < c->nranks; ++r) {
+        dev::Part p = dev::PartOf(shardBytes, gridDim.x, blockIdx.x);
+        const char *from = r == c->rank ? aLocal : src + (uint64_t)r * shardBytes;
+        dev::BlockCopy(dst + (uint64_t)r * shardBytes + p.off, from + p.off, p.len);
+    }
+}
+
+}  // namespace
+
+void DropWorkspace(Comm *c)
+{
+    std::lock_guard<std::mutex> lk(g_wsMu);
+    g_ws.erase(c);
+}
+
+HcclResult RunFused(FusedKind kind, Comm *c, const void *a, const void *b, void *out, void *gathered, uint64_t m, uint64_t N, uint64_t K, cudaStream_t stream)
+{
+    CHK_RET(CommCheckReady(c));
+    if (c->backend != BackendKind::CUDA) { HCCL_ERROR("fused matmul operators need a CUDA communicator"); return HCCL_E_NOT_SUPPORT; }
+    FusedShape s{kind, c->nranks, c->rank, m, N, K};
+    CHK_RET(CheckShape(s));
+    uint64_t wsOff = 0;
+    CHK_RET(EnsureWorkspace(c, 2 * WorkspaceHalfBytes(s) + 4096, &wsOff));
+    uint32_t commCtas = kind == AGMM ? CommCtasDefault() : 0;
+    GemmParams p;
+    CHK_RET(BuildParams(s, c->heap[c->rank], wsOff, a, b, out, commCtas, &p));
+    p.comm = c->devCommPtr;
+    uint32_t grid = GridFor(s, commCtas, (uint32_t)SmCount());
+    CHK_RET(LaunchFused<false>(s, p, nullptr, grid, 1, stream));
+    c->counters.kernelsLaunched++;
+    c->counters.ops++;
+    if (kind == AGMM && gathered) {
+        CopyGatheredKernel<<<32, 512, 0, stream>>>(c->devCommPtr, wsOff, WorkspaceHalfBytes(s), (const char *)a, (char *)gathered, m * K * 2);
+        if (cudaGetLastError() != cudaSuccess) return HCCL_E_RUNTIME;
+    }
+    return HCCL_SUCCESS;
+}
+
+}  // namespace mc2
+}  // namespace hccl
+
+using namespace hccl;
+using namespace hccl::mc2;
+
+extern "C" {
+
+HcclResult HcclAllGatherMatmul(const void *aLocal, const void *b, void *out, void *gathered, uint64_t mLocal, uint64_t n, uint64_t k,
+                               HcclDataType dataType, HcclComm comm, cudaStream_t stream)
+{
+    Comm *c = CommFromHandle(comm);
+    if (!c) return HCCL_E_PTR;
+    if (!aLocal || !b || !out) { HCCL_ERROR("[EI0003] HcclAllGatherMatmul: null buffer"); return HCCL_E_PTR; }
+    if (dataType != HCCL_DATA_TYPE_BFP16) { HCCL_ERROR("HcclAllGatherMatmul supports bf16 (got %s)", DataTypeName(dataType)); return HCCL_E_NOT_SUPPORT; }
+    if (c->nranks == 1) {
+        if (gathered && gathered != aLocal) CHK_RET(LocalCopyAsync(c, gathered, aLocal, mLocal * k * 2, stream));
+        return HcclGemmBf16(aLocal, b, out, mLocal, n, k, 0, stream);
+    }
+    return RunFused(AGMM, c, aLocal, b, out, gathered, mLocal, n, k, stream);
+}
+
+HcclResult HcclMatmulReduceScatter(const void *a, const void *b, void *out, uint64_t m, uint64_t n, uint64_t kLocal, HcclDataType dataType,
+                                   HcclComm comm, cudaStream_t stream)
+{
+    Comm *c = CommFromHandle(comm);
+    if (!c) return HCCL_E_PTR;
+    if (!a || !b || !out) { HCCL_ERROR("[EI0003] HcclMatmulReduceScatter: null buffer"); return HCCL_E_PTR; }
+    if (dataType != HCCL_DATA_TYPE_BFP16) return HCCL_E_NOT_SUPPORT;
+    if (c->nranks == 1) return HcclGemmBf16(a, b, out, m, n, kLocal, 0, stream);
+    return RunFused(MMRS, c, a, b, out, nullptr, m, n, kLocal, stream);
+}
+
+HcclResult HcclMatmulAllReduce(const void *a, const void *b, void *out, uint64_t m, uint64_t n, uint64_t kLocal, HcclDataType dataType,
+                               HcclComm comm, cudaStream_t stream)
+{
+    Comm *c = CommFromHandle(comm);
+    if (!c) return HCCL_E_PTR;
+    if (!a || !b || !out) { HCCL_ERROR("[EI0003] HcclMatmulAllReduce: null buffer"); return HCCL_E_PTR; }
+    if (dataType != HCCL_DATA_TYPE_BFP16) return HCCL_E_NOT_SUPPORT;
+    if (c->nranks == 1) return HcclGemmBf16(a, b, out, m, n, kLocal, 0, stream);
+    return RunFused(MMAR, c, a, b, out, nullptr, m, n, kLocal, stream);
+}
+
+// Emulation: kind 0 AllGatherMatmul (m = rows per rank), 1 MatmulReduceScatter, 2 MatmulAllReduce. as/bs/outs: per-rank
+// device pointers. ctasPerRank * nranks must fit on the GPU (one CTA per SM).
+HcclResult HcclEmuFusedRun(void *emu, int kind, void **as, void **bs, void **outs, uint64_t m, uint64_t n, uint64_t k, uint32_t ctasPerRank, uint32_t commCtas)
+{
+    auto *w = (EmuWorld *)emu;
+    if (!w || !as || !bs || !outs) return HCCL_E_PTR;
+    uint32_t R = (uint32_t)w->nranks;
+    std::vector<GemmParams> ps(R);
+    FusedShape s0{(FusedKind)kind, R, 0, m, n, k};
+    CHK_RET(CheckShape(s0));
+    if (2 * WorkspaceHalfBytes(s0) + 4096 > w->arenaBytes) { HCCL_ERROR("emu arena too small: need %llu", (unsigned long long)(2 * WorkspaceHalfBytes(s0) + 4096)); return HCCL_E_MEMORY; }
+    if (kind != AGMM) commCtas = 0;
+    for (uint32_t r = 0; r < R; ++r) {
+        FusedShape s{(FusedKind)kind, R, r, m, n, k};
+        CHK_RET(BuildParams(s, w->heaps[r], w->arenaOff, as[r], bs[r], outs[r], commCtas, &ps[r]));
+        ps[r].comm = w->devComms + r;
+    }
+    if (sizeof(GemmParams) > 2048) return HCCL_E_INTERNAL;
+    if (cudaMemcpy(w->devFusedParams, ps.data(), sizeof(GemmParams) * R, cudaMemcpyHostToDevice) != cudaSuccess) return HCCL_E_RUNTIME;
+    uint32_t grid = std::max(ctasPerRank, commCtas + 1);
+    CHK_RET(LaunchFused<true>(s0, ps[0], (const GemmParams *)w->devFusedParams, grid, R, 0));
+    if (cudaStreamSynchronize(0) != cudaSuccess) { HCCL_ERROR("emu fused kernel failed: %s", cudaGetErrorString(cudaGetLastError())); return HCCL_E_RUNTIME; }
+    for (uint32_t r = 0; r < R; ++r) if (w->status[r].code != 0) return HCCL_E_TIMEOUT;
+    return GemmCheckError();
+}
+
+}  // extern "C"

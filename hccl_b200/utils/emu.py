@@ -19,23 +19,25 @@ def _decl():
     l = lib()
     vp, u32, u64, i32 = ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint64, ctypes.c_int
     P = ctypes.POINTER
-    l.HcclEmuCreate.argtypes = [u32, u64, u32, P(vp)]
+    l.HcclEmuCreate.argtypes = [u32, u64, u64, u32, P(vp)]
     l.HcclEmuDestroy.argtypes = [vp]
     l.HcclEmuRun.argtypes = [vp, i32, ctypes.c_char_p, P(vp), P(vp), u64, i32, i32, u32, P(u64), u32]
     l.HcclEmuBatchSendRecv.argtypes = [vp, u32, P(u32), P(u32), P(vp), P(vp), P(u64)]
     l.HcclEmuStatus.argtypes = [vp, u32, P(u32), i32]
     l.HcclEmuLonelyBarrier.argtypes = [vp, u32]
+    l.HcclEmuFusedRun.argtypes = [vp, i32, P(vp), P(vp), P(vp), u64, u64, u64, u32, u32]
+    l.HcclEmuFusedRun.restype = ctypes.c_int
     for f in (l.HcclEmuCreate, l.HcclEmuDestroy, l.HcclEmuRun, l.HcclEmuBatchSendRecv, l.HcclEmuStatus, l.HcclEmuLonelyBarrier):
         f.restype = ctypes.c_int
     return l
 
 
 class EmuWorld:
-    def __init__(self, nranks: int, ccl_bytes: int = 8 << 20, wait_timeout_ms: int = 2000):
+    def __init__(self, nranks: int, ccl_bytes: int = 8 << 20, wait_timeout_ms: int = 2000, arena_bytes: int = 0):
         self._l = _decl()
         self.n = nranks
         h = ctypes.c_void_p()
-        check(self._l.HcclEmuCreate(nranks, ccl_bytes, wait_timeout_ms, ctypes.byref(h)), "HcclEmuCreate")
+        check(self._l.HcclEmuCreate(nranks, ccl_bytes, arena_bytes, wait_timeout_ms, ctypes.byref(h)), "HcclEmuCreate")
         self._h = h
 
     def close(self):
@@ -74,6 +76,12 @@ class EmuWorld:
         db = (ctypes.c_void_p * n)(*[t[3].data_ptr() for t in transfers])
         by = (ctypes.c_uint64 * n)(*[t[2].numel() * t[2].element_size() for t in transfers])
         rc = self._l.HcclEmuBatchSendRecv(self._h, n, s, d, sb, db, by)
+        torch.cuda.synchronize()
+        return rc
+
+    def fused(self, kind: int, a_list, b_list, out_list, m: int, n: int, k: int, ctas_per_rank: int, comm_ctas: int = 2) -> int:
+        """kind 0 AllGatherMatmul (m = rows per rank), 1 MatmulReduceScatter, 2 MatmulAllReduce"""
+        rc = self._l.HcclEmuFusedRun(self._h, kind, self._ptrs(a_list), self._ptrs(b_list), self._ptrs(out_list), m, n, k, ctas_per_rank, comm_ctas)
         torch.cuda.synchronize()
         return rc
 

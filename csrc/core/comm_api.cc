@@ -13,6 +13,7 @@
 using namespace hccl;
 
 namespace hccl {
+namespace mc2 { void DropWorkspace(Comm *c); }
 extern HcclResult CudaSetDeviceChecked(int dev);
 HcclResult BootstrapFixedRootInfo(const std::string &ip, uint32_t port, uint64_t nonce, bool listen, HcclRootInfo *out);
 }
@@ -177,6 +178,7 @@ HcclResult HcclCommDestroy(HcclComm comm)
     Comm *c = CommFromHandle(comm);
     if (!c) return comm ? HCCL_E_PARA : HCCL_E_PTR;
     PlanCache::Drop(c);
+    mc2::DropWorkspace(c);
     return CommDestroy(c);
 }
 

@@ -74,6 +74,19 @@ __device__ __forceinline__ void FusedExit(FusedCtx &x)
     }
 }
 
+// Tile order inside one segment of `rows` row blocks x `nBlocks` column blocks: groups of up to 16 row blocks are walked
+// column by column, so a wave of CTAs touches few distinct A and B panels and both stay in L2.
+__device__ __forceinline__ void SegmentTile(uint32_t rem, uint32_t rows, uint32_t nBlocks, uint32_t *rowBlk, uint32_t *nb)
+{
+    const uint32_t g = rows < 16 ? rows : 16;
+    const uint32_t perGroup = g * nBlocks;
+    const uint32_t group = rem / perGroup, first = group * g;
+    const uint32_t size = rows - first < g ? rows - first : g;
+    const uint32_t in = rem % perGroup;
+    *rowBlk = first + in % size;
+    *nb = in / size;
+}
+
 // counter at a (possibly remote) rank += v, releasing this thread's (and, after a CTA barrier, this CTA's) prior writes
 __device__ __forceinline__ void RemoteAddRelease(uint32_t *addr, uint32_t v)
 {

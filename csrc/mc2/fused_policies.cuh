@@ -82,8 +82,9 @@ struct AgmmPolicy {
         const uint32_t bpr = p.u32[2], perSrc = bpr * nBlocks;
         uint32_t d = t / perSrc, rem = t % perSrc;
         uint32_t src = ((uint32_t)x.rank + (uint32_t)x.n - d % (uint32_t)x.n) % (uint32_t)x.n;
-        *mb = src * bpr + rem / nBlocks;
-        *nb = rem % nBlocks;
+        uint32_t blk;
+        SegmentTile(rem, bpr, nBlocks, &blk, nb);
+        *mb = src * bpr + blk;
     }
     __device__ static bool WaitRowsReady(const GemmParams &p, const Ctx &x, uint32_t mb, volatile uint32_t *abortWord)
     {
@@ -100,10 +101,14 @@ struct AgmmPolicy {
         if ((int)src == x.rank) { *tm = &p.tmapALocal; *row = (int32_t)(blk * kBM); }
         else { *tm = x.half ? &p.tmapA1 : &p.tmapA; *row = (int32_t)(mb * kBM); }
     }
-    __device__ static void Store(const GemmParams &p, const Ctx &, uint32_t row, uint32_t col0, const uint32_t (&v)[32])
+    __device__ static bool UseDirect(const GemmParams &) { return false; }
+    __device__ static void Store(const GemmParams &, const Ctx &, uint32_t, uint32_t, const uint32_t (&)[32]) {}
+    __device__ static __nv_bfloat16 *RowDst(const GemmParams &p, const Ctx &, uint32_t row, uint32_t col)
     {
-        if (row < p.M) StoreRow32(p.C, p.ldc, p.N, p.outFp32 != 0, row, col0, v);
+        return (row < p.M && col < p.N) ? (__nv_bfloat16 *)p.C + (size_t)row * p.ldc + col : nullptr;
     }
+    __device__ static bool EpilogueGate(const GemmParams &, Ctx &, uint32_t, volatile uint32_t *) { return true; }
+    __device__ static void Combine(const GemmParams &, const Ctx &, uint32_t, uint32_t, uint32_t, uint32_t (&)[32]) {}
     __device__ static void TileDone(const GemmParams &, const Ctx &, uint32_t, uint32_t, uint32_t, uint32_t) {}
     __device__ static void PostPhase(const GemmParams &, Ctx &, uint32_t, uint32_t, volatile uint32_t *) {}
     __device__ static void Exit(const GemmParams &, Ctx &x) { FusedExit(x); }
@@ -161,8 +166,9 @@ struct MmrsPolicy {
         const uint32_t bpo = p.u32[1], perOwner = bpo * nBlocks, n = (uint32_t)x.n;
         uint32_t d = t / perOwner, rem = t % perOwner;
         uint32_t owner = ((uint32_t)x.rank + 1 + d) % n;
-        *mb = owner * bpo + rem / nBlocks;
-        *nb = rem % nBlocks;
+        uint32_t blk;
+        SegmentTile(rem, bpo, nBlocks, &blk, nb);
+        *mb = owner * bpo + blk;
     }
     __device__ static bool WaitRowsReady(const GemmParams &, const Ctx &, uint32_t, volatile uint32_t *) { return true; }
     __device__ static void SelectA(const GemmParams &p, const Ctx &, uint32_t mb, const CUtensorMap **tm, int32_t *row)
@@ -170,47 +176,71 @@ struct MmrsPolicy {
         *tm = &p.tmapA;
         *row = (int32_t)(mb * kBM);
     }
-    __device__ static void Store(const GemmParams &p, const Ctx &x, uint32_t row, uint32_t col0, const uint32_t (&v)[32])
+    __device__ static bool UseDirect(const GemmParams &) { return false; }
+    __device__ static void Store(const GemmParams &, const Ctx &, uint32_t, uint32_t, const uint32_t (&)[32]) {}
+    // Tiles of rows owned by a peer: the bf16 partial goes into slot[rank] of the owner's workspace. Tiles of the own
+    // rows come last; by then the peers' partials have long arrived, so their epilogue adds them (rank order, fp32) to
+    // the accumulator and writes the final result: no separate reduction pass, no round trip of the own partial.
+    __device__ static __nv_bfloat16 *RowDst(const GemmParams &p, const Ctx &x, uint32_t row, uint32_t col)
     {
-        if (row >= p.M || col0 >= p.N) return;
+        if (row >= p.M || col >= p.N) return nullptr;
         const uint32_t mOwn = p.u32[0], owner = row / mOwn, r = row - owner * mOwn;
+        if ((int)owner == x.rank) return (__nv_bfloat16 *)p.C + (uint64_t)r * p.ldc + col;
         char *ws = x.c->heap[owner] + p.u64[0] + (uint64_t)x.half * p.u64[1];
-        __nv_bfloat16 *dst = (__nv_bfloat16 *)ws + ((uint64_t)x.rank * mOwn + r) * p.N + col0;
-        StoreBf16x32(dst, v, p.N - col0);
+        return (__nv_bfloat16 *)ws + ((uint64_t)x.rank * mOwn + r) * p.N + col;
+    }
+    __device__ static bool EpilogueGate(const GemmParams &p, Ctx &x, uint32_t mb, volatile uint32_t *abortWord)
+    {
+        const uint32_t bpo = p.u32[1], owner = mb / bpo, blk = mb % bpo, nBlocks = p.u32[2];
+        if ((int)owner != x.rank) return true;
+        const uint32_t et = threadIdx.x - 128;
+        if (et < (uint32_t)x.n && (int)et != x.rank) WaitCounterGe(x, &x.flags->mc2Ready[x.half][et][blk], nBlocks, et, 41, abortWord);
+        EpilogueBarrier();
+        return *abortWord == 0;
+    }
+    __device__ static void Combine(const GemmParams &p, const Ctx &x, uint32_t mb, uint32_t row, uint32_t col0, uint32_t (&v)[32])
+    {
+        const uint32_t mOwn = p.u32[0], bpo = p.u32[1];
+        if ((int)(mb / bpo) != x.rank || row >= p.M || col0 >= p.N) return;
+        const uint32_t r = row - (uint32_t)x.rank * mOwn, n = (uint32_t)x.n;
+        const __nv_bfloat16 *ws = (const __nv_bfloat16 *)(x.heap + p.u64[0] + (uint64_t)x.half * p.u64[1]);
+        const uint32_t valid = p.N - col0 < 32 ? p.N - col0 : 32;
+        float sum[32];
+        bool first = true;
+        for (uint32_t s = 0; s < n; ++s) {
+            if ((int)s == x.rank) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) sum[j] = first ? __uint_as_float(v[j]) : sum[j] + __uint_as_float(v[j]);
+            } else {
+                const uint4 *src = (const uint4 *)(ws + ((uint64_t)s * mOwn + r) * p.N + col0);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    if ((uint32_t)q * 8 >= valid) break;
+                    uint4 raw = src[q];
+                    const __nv_bfloat162 *h = (const __nv_bfloat162 *)&raw;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        float2 f = __bfloat1622float2(h[j]);
+                        sum[q * 8 + 2 * j] = first ? f.x : sum[q * 8 + 2 * j] + f.x;
+                        sum[q * 8 + 2 * j + 1] = first ? f.y : sum[q * 8 + 2 * j + 1] + f.y;
+                    }
+                }
+            }
+            first = false;
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(sum[j]);
     }
     __device__ static void TileDone(const GemmParams &p, const Ctx &x, uint32_t mb, uint32_t, uint32_t ew, uint32_t lane)
     {
-        EpilogueBarrier();
-        if (ew == 0 && lane == 0) {
-            const uint32_t bpo = p.u32[1], owner = mb / bpo, blk = mb % bpo;
+        const uint32_t bpo = p.u32[1], owner = mb / bpo, blk = mb % bpo;
+        if ((int)owner == x.rank) return;
+        if (ew == 0 && lane == 0) {     // the write-out ended with a barrier of the 128 epilogue threads
             __threadfence_system();
             RemoteAddRelease(&FlagsOf(x.c->heap[owner])->mc2Ready[x.half][x.rank][blk], 1u);
         }
     }
-    // ordered reduction of the rows this rank owns: out[r, :] = sum over src (rank order) of slot[src][r, :]
-    __device__ static void PostPhase(const GemmParams &p, Ctx &x, uint32_t cta, uint32_t ctas, volatile uint32_t *abortWord)
-    {
-        const uint32_t mOwn = p.u32[0], bpo = p.u32[1], nBlocks = p.u32[2], n = (uint32_t)x.n;
-        const uint32_t colChunks = (p.N + 255) / 256;
-        const char *ws = x.heap + p.u64[0] + (uint64_t)x.half * p.u64[1];
-        for (uint32_t u = cta; u < bpo * colChunks; u += ctas) {
-            const uint32_t blk = u / colChunks, cc = u % colChunks;
-            bool mine = true;
-            if (threadIdx.x < n) mine = WaitCounterGe(x, &x.flags->mc2Ready[x.half][threadIdx.x][blk], nBlocks, threadIdx.x, 41, abortWord);
-            if (!__syncthreads_and(mine ? 1 : 0)) return;
-            const uint32_t colsHere = p.N - cc * 256 < 256 ? p.N - cc * 256 : 256, vecPerRow = colsHere / 8;
-            const uint32_t rows = mOwn - blk * kBM < (uint32_t)kBM ? mOwn - blk * kBM : (uint32_t)kBM;
-            for (uint32_t v = threadIdx.x; v < rows * vecPerRow; v += blockDim.x) {
-                const uint32_t r = blk * kBM + v / vecPerRow, c = cc * 256 + (v % vecPerRow) * 8;
-                float acc[8];
-                for (uint32_t s = 0; s < n; ++s) {
-                    uint4 raw = *(const uint4 *)((const __nv_bfloat16 *)ws + ((uint64_t)s * mOwn + r) * p.N + c);
-                    AccumBf16x8(acc, raw, s == 0);
-                }
-                *(uint4 *)((__nv_bfloat16 *)p.C + (uint64_t)r * p.ldc + c) = PackBf16x8(acc);
-            }
-        }
-    }
+    __device__ static void PostPhase(const GemmParams &, Ctx &, uint32_t, uint32_t, volatile uint32_t *) {}
     __device__ static void Exit(const GemmParams &, Ctx &x) { FusedExit(x); }
 };
 
@@ -236,14 +266,17 @@ struct MmarPolicy {
         *tm = &p.tmapA;
         *row = (int32_t)(mb * kBM);
     }
-    __device__ static void Store(const GemmParams &p, const Ctx &x, uint32_t row, uint32_t col0, const uint32_t (&v)[32])
+    __device__ static bool UseDirect(const GemmParams &) { return false; }
+    __device__ static void Store(const GemmParams &, const Ctx &, uint32_t, uint32_t, const uint32_t (&)[32]) {}
+    __device__ static __nv_bfloat16 *RowDst(const GemmParams &p, const Ctx &x, uint32_t row, uint32_t col)
     {
-        if (row >= p.M || col0 >= p.N) return;
-        const uint32_t colsOwn = p.u32[0], owner = col0 / colsOwn;
+        if (row >= p.M || col >= p.N) return nullptr;
+        const uint32_t colsOwn = p.u32[0], owner = col / colsOwn;
         char *ws = x.c->heap[owner] + p.u64[0] + (uint64_t)x.half * p.u64[1];
-        __nv_bfloat16 *dst = (__nv_bfloat16 *)ws + ((uint64_t)x.rank * p.M + row) * colsOwn + (col0 - owner * colsOwn);
-        StoreBf16x32(dst, v);
+        return (__nv_bfloat16 *)ws + ((uint64_t)x.rank * p.M + row) * colsOwn + (col - owner * colsOwn);
     }
+    __device__ static bool EpilogueGate(const GemmParams &, Ctx &, uint32_t, volatile uint32_t *) { return true; }
+    __device__ static void Combine(const GemmParams &, const Ctx &, uint32_t, uint32_t, uint32_t, uint32_t (&)[32]) {}
     __device__ static uint32_t CounterIndex(const GemmParams &p, uint32_t mb, uint32_t nb)
     {
         return (mb * p.u32[1] + nb % p.u32[1]) & 63u;
@@ -261,8 +294,10 @@ struct MmarPolicy {
     {
         const uint32_t colsOwn = p.u32[0], tpr = p.u32[1], BN = p.u32[2], n = (uint32_t)x.n;
         const uint32_t mBlocks = (p.M + kBM - 1) / kBM;
-        constexpr uint32_t ROWS = 16;                        // rows per reduce unit
-        const uint32_t rowChunks = kBM / ROWS;
+        // reduce units: each owned tile is cut into row chunks so that there is about one unit per CTA
+        uint32_t rowChunks = ctas / (mBlocks * tpr);
+        rowChunks = rowChunks >= 8 ? 8 : rowChunks >= 4 ? 4 : rowChunks >= 2 ? 2 : 1;
+        const uint32_t ROWS = kBM / rowChunks;
         const uint32_t units = mBlocks * tpr * rowChunks;    // reduce units this rank owns
         const char *ws = x.heap + p.u64[0] + (uint64_t)x.half * p.u64[1];
         const uint64_t resBase = p.u64[2] + (uint64_t)x.half * p.u64[3];

@@ -16,6 +16,7 @@
 //   WaitRowsReady(p, ctx, mb, abort)     producer-side gate before loading A rows
 //   SelectA(p, ctx, mb, &tmap, &row)     which tensor map / row coordinate serves this row block
 //   Store(p, ctx, row, col0, v[32])      epilogue sink (local C, a peer's reduce-scatter slot, ...)
+//   EpilogueGate / Combine               per-tile gate and per-chunk transform of the accumulator (add received partials)
 //   TileDone(p, ctx, mb, nb, ew, lane)   after a tile's stores (signal the consumer rank)
 //   PostPhase(p, ctx, cta, ctas, abort)  work after the last tile (ordered reduction of the received partials)
 //   Exit(p, ctx)                         per-CTA exit protocol
@@ -57,8 +58,11 @@ template <int BN> struct GemmSmem {
     static constexpr int kABytes = kBM * kBK * 2;
     static constexpr int kBBytes = BN * kBK * 2;
     static constexpr int kRing = kStages * (kABytes + kBBytes);
-    static constexpr int kBarOff = kRing;
-    static constexpr int kTotal = kRing + 256;
+    static constexpr int kStageCols = BN < 128 ? BN : 128;                 // columns staged per epilogue pass
+    static constexpr int kStagingOff = kRing;
+    static constexpr int kStagingBytes = kBM * kStageCols * 2;             // bf16 tile slice, XOR-swizzled 16-byte chunks
+    static constexpr int kBarOff = kRing + kStagingBytes;
+    static constexpr int kTotal = kBarOff + 256;
 };
 
 __device__ __forceinline__ void StoreRow32(void *C, uint32_t ldc, uint32_t N, bool fp32, uint32_t row, uint32_t col0, const uint32_t (&v)[32])
@@ -108,10 +112,21 @@ struct PlainPolicy {
         *tm = &p.tmapA;
         *row = (int32_t)(mb * kBM);
     }
+    // fp32 output goes straight from registers; bf16 output is staged through shared memory and written as whole
+    // 16-byte chunks of contiguous row segments
+    __device__ static bool UseDirect(const GemmParams &p) { return p.outFp32 != 0; }
     __device__ static void Store(const GemmParams &p, const Ctx &, uint32_t row, uint32_t col0, const uint32_t (&v)[32])
     {
         if (row < p.M) StoreRow32(p.C, p.ldc, p.N, p.outFp32 != 0, row, col0, v);
     }
+    // destination of 8 consecutive bf16 results at (row, col), or nullptr when outside the output
+    __device__ static __nv_bfloat16 *RowDst(const GemmParams &p, const Ctx &, uint32_t row, uint32_t col)
+    {
+        return (row < p.M && col < p.N) ? (__nv_bfloat16 *)p.C + (size_t)row * p.ldc + col : nullptr;
+    }
+    // called by all 128 epilogue threads before a tile's accumulator is read / for every 32-column chunk read
+    __device__ static bool EpilogueGate(const GemmParams &, Ctx &, uint32_t, volatile uint32_t *) { return true; }
+    __device__ static void Combine(const GemmParams &, const Ctx &, uint32_t, uint32_t, uint32_t, uint32_t (&)[32]) {}
     __device__ static void TileDone(const GemmParams &, const Ctx &, uint32_t, uint32_t, uint32_t, uint32_t) {}
     __device__ static void PostPhase(const GemmParams &, Ctx &, uint32_t, uint32_t, volatile uint32_t *) {}
     __device__ static void Exit(const GemmParams &, Ctx &) {}
@@ -222,16 +237,56 @@ __global__ void __launch_bounds__(kGemmThreads, 1) GemmKernel(const __grid_const
             ok = MbarWait(&tmemFull[acc], accPhase, abortWord);
             if (!ok) break;
             TcFenceAfter();
-            const uint32_t row = mb * kBM + ew * 32 + lane;
+            const uint32_t rowInTile = ew * 32 + lane;
+            const uint32_t row = mb * kBM + rowInTile;
+            if (Policy::UseDirect(p)) {
 #pragma unroll 1
-            for (uint32_t c = 0; c < BN / 32; ++c) {
-                uint32_t v[32];
-                TmemLd32x32(tmemBase + ((ew * 32) << 16) + acc * BN + c * 32, v);
-                TmemLdWait();
-                Policy::Store(p, ctx, row, nb * BN + c * 32, v);
+                for (uint32_t c = 0; c < BN / 32; ++c) {
+                    uint32_t v[32];
+                    TmemLd32x32(tmemBase + ((ew * 32) << 16) + acc * BN + c * 32, v);
+                    TmemLdWait();
+                    Policy::Store(p, ctx, row, nb * BN + c * 32, v);
+                }
+                TcFenceBefore();
+                MbarArrive(&tmemEmpty[acc]);
+            } else {
+                constexpr uint32_t SC = S::kStageCols, CH = SC / 8;          // staged columns / 16-byte chunks per row
+                uint4 *stg = (uint4 *)(smem + S::kStagingOff);
+                const uint32_t et = threadIdx.x - 128;                       // 0..127 among the epilogue threads
+                if (!Policy::EpilogueGate(p, ctx, mb, abortWord)) { ok = false; break; }
+#pragma unroll 1
+                for (uint32_t pass = 0; pass < BN / SC; ++pass) {
+#pragma unroll 1
+                    for (uint32_t c = 0; c < SC / 32; ++c) {
+                        uint32_t v[32];
+                        TmemLd32x32(tmemBase + ((ew * 32) << 16) + acc * BN + pass * SC + c * 32, v);
+                        TmemLdWait();
+                        Policy::Combine(p, ctx, mb, row, nb * BN + pass * SC + c * 32, v);
+#pragma unroll
+                        for (uint32_t q = 0; q < 4; ++q) {
+                            uint4 o;
+                            __nv_bfloat162 t0 = __floats2bfloat162_rn(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]));
+                            __nv_bfloat162 t1 = __floats2bfloat162_rn(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]));
+                            __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]));
+                            __nv_bfloat162 t3 = __floats2bfloat162_rn(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]));
+                            o.x = *(uint32_t *)&t0; o.y = *(uint32_t *)&t1; o.z = *(uint32_t *)&t2; o.w = *(uint32_t *)&t3;
+                            stg[rowInTile * CH + ((c * 4 + q) ^ (rowInTile & 7))] = o;
+                        }
+                    }
+                    if (pass + 1 == BN / SC) {                               // accumulator fully read: hand it back early
+                        TcFenceBefore();
+                        MbarArrive(&tmemEmpty[acc]);
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll 4
+                    for (uint32_t i = et; i < (uint32_t)kBM * CH; i += 128) {
+                        const uint32_t r = i / CH, ch = i % CH;
+                        __nv_bfloat16 *dst = Policy::RowDst(p, ctx, mb * kBM + r, nb * BN + pass * SC + ch * 8);
+                        if (dst) *(uint4 *)dst = stg[r * CH + (ch ^ (r & 7))];
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                }
             }
-            TcFenceBefore();
-            MbarArrive(&tmemEmpty[acc]);
             Policy::TileDone(p, ctx, mb, nb, ew, lane);
             acc ^= 1;
             if (acc == 0) accPhase ^= 1;

@@ -4,6 +4,7 @@
 #include <algorithm>
 #include <map>
 #include <mutex>
+#include <tuple>
 #include "../common/dtype.h"
 #include "../common/log.h"
 #include "../core/comm.h"
@@ -125,7 +126,13 @@ template <bool EMU> HcclResult LaunchFused(const FusedShape &s, const GemmParams
 }
 
 // ---- symmetric workspace per communicator (grown on demand; every rank makes the same calls, so offsets agree)
-struct Workspace { void *ptr = nullptr; uint64_t bytes = 0; };
+struct ParamKey {
+    int kind; const void *a, *b, *out; uint64_t m, N, K, wsOff;
+    bool operator<(const ParamKey &o) const { return std::tie(kind, a, b, out, m, N, K, wsOff) < std::tie(o.kind, o.a, o.b, o.out, o.m, o.N, o.K, o.wsOff); }
+};
+// Encoded tensor maps are reused while the same buffers and shapes come back (decode loops, training steps): encoding four
+// maps costs more host time than a decode-sized fused kernel runs.
+struct Workspace { void *ptr = nullptr; uint64_t bytes = 0; std::map<ParamKey, GemmParams> params; };
 std::mutex g_wsMu;
 std::map<Comm *, Workspace> g_ws;
 
@@ -141,6 +148,7 @@ HcclResult EnsureWorkspace(Comm *c, uint64_t bytes, uint64_t *off)
             SymFree(c, w.ptr);
             w.ptr = nullptr;
             w.bytes = 0;
+            w.params.clear();
         }
         uint64_t want = (bytes + (1 << 20) - 1) & ~((1ull << 20) - 1);
         CHK_RET(SymAlloc(c, want, &w.ptr));
@@ -181,8 +189,19 @@ HcclResult RunFused(FusedKind kind, Comm *c, const void *a, const void *b, void 
     CHK_RET(EnsureWorkspace(c, 2 * WorkspaceHalfBytes(s) + 4096, &wsOff));
     uint32_t commCtas = kind == AGMM ? CommCtasDefault() : 0;
     GemmParams p;
-    CHK_RET(BuildParams(s, c->heap[c->rank], wsOff, a, b, out, commCtas, &p));
-    p.comm = c->devCommPtr;
+    {
+        std::lock_guard<std::mutex> lk(g_wsMu);
+        auto &cache = g_ws[c].params;
+        ParamKey key{(int)kind, a, b, out, m, N, K, wsOff};
+        auto it = cache.find(key);
+        if (it != cache.end()) p = it->second;
+        else {
+            CHK_RET(BuildParams(s, c->heap[c->rank], wsOff, a, b, out, commCtas, &p));
+            p.comm = c->devCommPtr;
+            if (cache.size() > 256) cache.clear();
+            cache[key] = p;
+        }
+    }
     uint32_t grid = GridFor(s, commCtas, (uint32_t)SmCount());
     CHK_RET(LaunchFused<false>(s, p, nullptr, grid, 1, stream));
     c->counters.kernelsLaunched++;

@@ -11,15 +11,15 @@ pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _run(nproc, extra_env, port):
+def _run(nproc, extra_env, port, worker="mp_worker_collectives.py", expect="all multi-GPU collective checks passed"):
     env = dict(os.environ)
     env.update(extra_env)
     env.setdefault("HCCL_DEVICE_WAIT_TIMEOUT_MS", "10000")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
-           "--master-port", str(port), os.path.join(HERE, "mp_worker_collectives.py")]
+           "--master-port", str(port), os.path.join(HERE, worker)]
     res = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
     assert res.returncode == 0, res.stdout[-6000:]
-    assert "all multi-GPU collective checks passed" in res.stdout, res.stdout[-3000:]
+    assert expect in res.stdout, res.stdout[-3000:]
 
 
 @pytest.mark.parametrize("cfg", [
@@ -31,3 +31,9 @@ def _run(nproc, extra_env, port):
 def test_collectives_two_or_more_gpus(cfg):
     n = min(torch.cuda.device_count(), 8)
     _run(n, cfg, 29610 + len(cfg) * 7 + int(cfg.get("HCCL_NVLS_ENABLE", "0")) * 3)
+
+
+def test_fused_matmul_collectives_two_or_more_gpus():
+    n = min(torch.cuda.device_count(), 8)
+    n = 8 if n >= 8 else 4 if n >= 4 else 2
+    _run(n, {}, 29655, worker="mp_worker_fused.py", expect="all fused multi-GPU checks passed")

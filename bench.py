@@ -101,11 +101,12 @@ def main() -> None:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return t.item()
 
-    for _ in range(max(args.warmup, 3)):
-        step()
     sampler = ClockSampler(local)
     if rank == 0:
-        sampler.start()
+        sampler.start()          # nvidia-smi needs a moment to come up; samples taken before the timed region are dropped
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sampler.mark()
     ms = timed(step, args.steps)
     clocks = sampler.stop() if rank == 0 else {}
     flops = 2 * 2.0 * M_TOTAL * HIDDEN * FFN

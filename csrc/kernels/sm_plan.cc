@@ -149,7 +149,11 @@ HcclResult SmPlanOp(const SmPlanCtx &ctx, const OpParam &p, const std::string &a
                        (unsigned long long)(ccl - kA2aMetaBytes));
             return HCCL_E_MEMORY;
         }
-        push(K_ALLTOALL_V, 0, 0, std::max(packed, moved), [&](SmLaunch &l) {
+        (void)moved;
+        push(K_ALLTOALL_V, 0, 0, 0, [&](SmLaunch &l) {
+            // the grid must be the same on every rank (channels synchronise pairwise across ranks), so it cannot depend
+            // on this rank's own counts
+            l.ctas = ctx.maxCtas ? std::min(16u, ctx.maxCtas) : 16u;
             l.args.in = in;
             l.args.out = outp;
             for (uint32_t r = 0; r < n; ++r) {

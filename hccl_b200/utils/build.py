@@ -87,7 +87,7 @@ def build_native(verbose: bool = False, ptxas_info: bool = False) -> Path:
         "  depfile = $out.d",
         "  deps = gcc",
         "rule link",
-        "  command = $nvcc -shared -o $out $in -cudart static -lpthread -ldl -lrt",
+        "  command = $nvcc -shared -o $out $in -cudart static -lpthread -ldl -lrt -Xlinker -soname=libhccl_b200.so",
     ]
     objs = []
     for src in cc + cu:
@@ -121,7 +121,7 @@ def build_torch_ext(verbose: bool = False) -> Path:
     torch_lib = Path(torch.__file__).parent / "lib"
     out = LIBDIR / "hccl_b200_torch.so"
     ldflags = [f"-L{torch_lib}", f"-Wl,-rpath,{torch_lib}", "-lc10", "-ltorch_cpu", "-ltorch", "-ltorch_python",
-               f"-L{LIBDIR}", "-Wl,-rpath,$$ORIGIN", "-lhccl_b200"]
+               f"-L{LIBDIR}", "-Wl,-rpath,'$$ORIGIN'", "-lhccl_b200"]
     if (torch_lib / "libc10_cuda.so").exists():
         ldflags += ["-lc10_cuda", "-ltorch_cuda"]
     lines = [

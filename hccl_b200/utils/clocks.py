@@ -17,6 +17,11 @@ class ClockSampler:
         self.rows: List[List[str]] = []
         self._proc = None
         self._thread = None
+        self._skip = 0
+
+    def mark(self) -> None:
+        """Samples taken so far belong to warm-up; only later ones are summarised."""
+        self._skip = len(self.rows)
 
     def start(self) -> None:
         try:
@@ -41,7 +46,8 @@ class ClockSampler:
             except Exception:
                 pass
         sm, mx, reasons = [], [], set()
-        for r in self.rows:
+        rows = self.rows[self._skip:] or self.rows[-3:]
+        for r in rows:
             if len(r) < 8:
                 continue
             try:

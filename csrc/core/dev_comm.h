@@ -60,7 +60,7 @@ struct DevFlags {
     // fused-kernel counters, one set per op parity; the owner zeroes its set when the op ends
     uint32_t mc2Ready[2][kMaxRanks][64];         // [half][src][block]: pieces of `block` delivered by src
     uint32_t mc2Done[2][kMaxRanks][4];           // [half][src][k]: second-stage counters (results delivered by src)
-    uint32_t moeCount[kMaxRanks][320];           // MoE dispatch: per-source expert counts (+ epoch word)
+    uint32_t moeCount[kMaxRanks][320];           // MoE dispatch: moeCount[src][e] = tokens rank src routes to expert e
 };
 static_assert(sizeof(DevFlags) <= kFlagBytes, "flag arena too large");
 

@@ -257,6 +257,13 @@ HcclResult CommDestroy(Comm *c)
     return HCCL_SUCCESS;
 }
 
+Comm *CommFindByName(const char *name)
+{
+    std::lock_guard<std::mutex> lk(g_commsMu);
+    for (Comm *c : g_comms) if (c->name == name) return c;
+    return nullptr;
+}
+
 Comm *CommFromHandle(HcclComm h)
 {
     std::lock_guard<std::mutex> lk(g_commsMu);

@@ -27,6 +27,13 @@ HcclResult CudaMemcpyAsyncD2D(void *dst, const void *src, uint64_t bytes, cudaSt
     return HCCL_SUCCESS;
 }
 
+HcclResult CudaMemsetDevice(void *dst, int v, uint64_t bytes)
+{
+    cudaError_t e = cudaMemset(dst, v, bytes);
+    if (e != cudaSuccess) { HCCL_ERROR("cudaMemset: %s", cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
+    return HCCL_SUCCESS;
+}
+
 void NvtxPush(const char *name) { nvtxRangePushA(name); }
 void NvtxPop() { nvtxRangePop(); }
 

@@ -17,7 +17,7 @@ namespace hccl {
 
 constexpr int kMaxRanks = 32;
 constexpr int kMaxChannels = 256;       // CTA channels with independent flag rows / epochs
-constexpr int kNotifySlots = 16;        // host-engine notify counters per peer
+constexpr int kNotifySlots = 24;        // host-engine notify counters per peer
 constexpr int kP2pCtas = 8;             // CTAs per point-to-point transfer
 constexpr uint64_t kCtrlBytes = 64 << 10;
 constexpr uint64_t kFlagBytes = (1 << 20) - kCtrlBytes;

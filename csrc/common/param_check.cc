@@ -29,18 +29,15 @@ bool IsReduceDataTypeSupported(HcclDataType t)
     switch (t) {
         case HCCL_DATA_TYPE_INT8: case HCCL_DATA_TYPE_INT16: case HCCL_DATA_TYPE_INT32: case HCCL_DATA_TYPE_INT64:
         case HCCL_DATA_TYPE_UINT64: case HCCL_DATA_TYPE_FP16: case HCCL_DATA_TYPE_FP32: case HCCL_DATA_TYPE_FP64:
-        case HCCL_DATA_TYPE_BFP16: return true;
+        case HCCL_DATA_TYPE_BFP16: case HCCL_DATA_TYPE_UINT8: case HCCL_DATA_TYPE_UINT16: case HCCL_DATA_TYPE_UINT32: return true;
         default: return false;
     }
 }
 
 bool IsProdDataTypeSupported(HcclDataType t)
 {
-    switch (t) {
-        case HCCL_DATA_TYPE_INT8: case HCCL_DATA_TYPE_INT32: case HCCL_DATA_TYPE_INT64: case HCCL_DATA_TYPE_UINT64:
-        case HCCL_DATA_TYPE_FP16: case HCCL_DATA_TYPE_FP32: case HCCL_DATA_TYPE_FP64: return true;
-        default: return false;
-    }
+    // every reducible type multiplies here (the reference excludes int16 and bf16: an engine limit this hardware lacks)
+    return IsReduceDataTypeSupported(t);
 }
 
 HcclResult HcomCheckReductionOp(HcclReduceOp op)

@@ -180,6 +180,7 @@ HcclResult CommCreate(uint32_t nranks, const HcclRootInfo *info, uint32_t rank, 
     c->commId = blob->nonce;
     if (cfg && cfg->hcclCommName[0]) c->name = cfg->hcclCommName;
     else { char nm[64]; snprintf(nm, sizeof(nm), "hccl_world_%08llx", (unsigned long long)(blob->nonce & 0xffffffffull)); c->name = nm; }
+    c->creatorThread = std::this_thread::get_id();
     int dev = -1;
     uint32_t want = cfg ? cfg->hcclBackend : 0;
     if (const char *e = getenv("HCCL_BACKEND")) { if (!strcasecmp(e, "sim") || !strcasecmp(e, "host")) want = 1; else if (!strcasecmp(e, "cuda")) want = 2; }
@@ -259,9 +260,19 @@ HcclResult CommDestroy(Comm *c)
 
 Comm *CommFindByName(const char *name)
 {
+    // One process may hold several ranks of the same group (HcclCommInitAll, or simulated ranks as threads): among
+    // same-named communicators prefer the one on the calling thread's current device, then the one this thread created.
+    int dev = -1;
+    bool haveDev = CudaDeviceAvailable(&dev);
     std::lock_guard<std::mutex> lk(g_commsMu);
-    for (Comm *c : g_comms) if (c->name == name) return c;
-    return nullptr;
+    Comm *first = nullptr, *byThread = nullptr;
+    for (Comm *c : g_comms) {
+        if (c->name != name) continue;
+        if (!first) first = c;
+        if (haveDev && c->backend == BackendKind::CUDA && c->device == dev) return c;
+        if (c->creatorThread == std::this_thread::get_id()) byThread = c;
+    }
+    return byThread ? byThread : first;
 }
 
 Comm *CommFromHandle(HcclComm h)

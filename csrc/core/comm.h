@@ -74,6 +74,7 @@ class SimWorker;   // ordered async queue that plays the role of a stream for th
 struct Comm {
     uint32_t rank = 0, nranks = 1;
     std::string name;                // group name
+    std::thread::id creatorThread;   // disambiguates same-named communicators of one process (ranks as threads)
     uint64_t commId = 0;
     BackendKind backend = BackendKind::SIM;
     int device = -1;

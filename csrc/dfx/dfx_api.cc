@@ -195,6 +195,29 @@ HcclResult HcclCheckAlgorithm(HcclCMDType op, const char *algName, uint32_t supe
 
 void HcclResetEnvConfigForTest(void) { ResetAlgEnvConfigInitState(); }
 
+HcclResult HcclDescribeEnvConfig(char *buf, uint32_t bufLen)
+{
+    ResetAlgEnvConfigInitState();
+    HcclResult r = InitEnvConfig();
+    if (r != HCCL_SUCCESS) { ResetAlgEnvConfigInitState(); return r; }
+    const AlgEnvConfig &c = GetEnvConfig();
+    std::ostringstream o;
+    o << "expansion=" << EngineName(c.expansionMode);
+    for (auto &kv : c.expansionModePerOp) o << ";expansion." << CmdName(kv.first) << "=" << EngineName(kv.second);
+    o << ";algoSet=" << (c.algoSet ? 1 : 0) << ";algo=" << AlgoTypeName(c.algo.level[0]) << "," << AlgoTypeName(c.algo.level[1]) << "," << AlgoTypeName(c.algo.level[2]);
+    for (auto &kv : c.algoPerOp) o << ";algo." << CmdName(kv.first) << "=" << AlgoTypeName(kv.second.level[0]) << "," << AlgoTypeName(kv.second.level[1]) << "," << AlgoTypeName(kv.second.level[2]);
+    for (auto &kv : c.algoNamePerOp) o << ";algoName." << CmdName(kv.first) << "=" << kv.second;
+    o << ";deterministic=" << (int)c.deterministic << ";execTimeout=" << c.execTimeoutSec << ";deviceWaitMs=" << c.deviceWaitTimeoutMs
+      << ";connectTimeout=" << c.connectTimeoutSec << ";bufferBytes=" << c.bufferSizeBytes << ";entryLog=" << c.entryLogEnable
+      << ";retry=" << c.opRetryIntraServer << c.opRetryInterServer << c.opRetryInterSuperPod << ";retryMax=" << c.opRetryMaxCnt << ";retryHold=" << c.opRetryHoldTimeMs
+      << ";retryInterval=" << c.opRetryIntervalMs << ";heartbeat=" << c.clusterHeartbeat << ";stuck=" << c.stuckDetection << ";taskException=" << c.taskException
+      << ";faultDetect=" << c.connectionFaultDetectionSec << ";monitorMs=" << c.taskMonitorIntervalMs << ";inconsistent=" << (int)c.inconsistentCheck
+      << ";split=" << c.multiDimSplitRatio[0] << ":" << c.multiDimSplitRatio[1] << ";nvls=" << c.nvlsEnable << ";maxCtas=" << c.maxCtas << ";ifIp=" << c.ifIp
+      << ";basePort=" << c.ifBasePort << ";tuningFile=" << c.tuningFile;
+    CopyOut(o.str(), buf, bufLen);
+    return HCCL_SUCCESS;
+}
+
 HcclResult HcclInjectBootstrapDrop(HcclComm comm, int n)
 {
     Comm *c = CommFromHandle(comm);

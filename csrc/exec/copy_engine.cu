@@ -64,6 +64,9 @@ cudaError_t LaunchReduce(void *dst, const void *src, uint64_t bytes, HcclDataTyp
         case HCCL_DATA_TYPE_INT32: return LaunchReduceT<int32_t>(dst, src, n, op, s);
         case HCCL_DATA_TYPE_INT64: return LaunchReduceT<long long>(dst, src, n, op, s);
         case HCCL_DATA_TYPE_UINT64: return LaunchReduceT<unsigned long long>(dst, src, n, op, s);
+        case HCCL_DATA_TYPE_UINT8: return LaunchReduceT<uint8_t>(dst, src, n, op, s);
+        case HCCL_DATA_TYPE_UINT16: return LaunchReduceT<uint16_t>(dst, src, n, op, s);
+        case HCCL_DATA_TYPE_UINT32: return LaunchReduceT<uint32_t>(dst, src, n, op, s);
         case HCCL_DATA_TYPE_FP16: return LaunchReduceT<__half>(dst, src, n, op, s);
         case HCCL_DATA_TYPE_FP32: return LaunchReduceT<float>(dst, src, n, op, s);
         case HCCL_DATA_TYPE_FP64: return LaunchReduceT<double>(dst, src, n, op, s);

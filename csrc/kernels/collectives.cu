@@ -492,6 +492,9 @@ template <bool EMU> CollKernelFn TypedKernel(SmKernelId id, HcclDataType dt)
         case HCCL_DATA_TYPE_INT32: return KERN<int32_t, EMU>;                      \
         case HCCL_DATA_TYPE_INT64: return KERN<long long, EMU>;                    \
         case HCCL_DATA_TYPE_UINT64: return KERN<unsigned long long, EMU>;          \
+        case HCCL_DATA_TYPE_UINT8: return KERN<uint8_t, EMU>;                      \
+        case HCCL_DATA_TYPE_UINT16: return KERN<uint16_t, EMU>;                    \
+        case HCCL_DATA_TYPE_UINT32: return KERN<uint32_t, EMU>;                    \
         case HCCL_DATA_TYPE_FP16: return KERN<__half, EMU>;                        \
         case HCCL_DATA_TYPE_FP32: return KERN<float, EMU>;                         \
         case HCCL_DATA_TYPE_FP64: return KERN<double, EMU>;                        \

@@ -35,12 +35,20 @@ def run_ranks(n: int, fn: Callable, *, buffer_mb: int = 0, timeout_s: float = 12
     threads = [threading.Thread(target=body, args=(r,), daemon=True) for r in range(n)]
     for t in threads:
         t.start()
-    for t in threads:
-        t.join(timeout_s)
-    for t in threads:
-        if t.is_alive():
-            raise TimeoutError("a simulated rank did not finish")
+    import time
+
+    deadline = time.time() + timeout_s
+    while time.time() < deadline and any(t.is_alive() for t in threads):
+        # a rank that raised leaves its peers waiting inside a collective: report the error, not the wait
+        if any(e is not None for e in errors):
+            grace = time.time() + 2.0
+            while time.time() < grace and any(t.is_alive() for t in threads):
+                time.sleep(0.02)
+            break
+        time.sleep(0.02)
     for e in errors:
         if e is not None:
             raise e
+    if any(t.is_alive() for t in threads):
+        raise TimeoutError("a simulated rank did not finish")
     return results

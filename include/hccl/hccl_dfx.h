@@ -62,6 +62,8 @@ HcclResult HcclListAlgorithms(HcclCMDType op, char *buf, uint32_t bufLen);
 
 /* Test hooks. */
 void HcclResetEnvConfigForTest(void);
+/* Re-parses every HCCL_* environment variable and writes the result as "key=value;..."; the parse error otherwise. */
+HcclResult HcclDescribeEnvConfig(char *buf, uint32_t bufLen);
 HcclResult HcclInjectBootstrapDrop(HcclComm comm, int n);   /* next n bootstrap contributions of this rank vanish */
 
 #ifdef __cplusplus

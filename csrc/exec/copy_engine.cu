@@ -124,6 +124,10 @@ HcclResult CopyEngineRun(Comm *c, const Plan &plan, const ExecBuffers &bufs, cud
     };
     std::lock_guard<std::mutex> lk(g_mu);
     const size_t nq = plan.queues.size();
+    if (nq > 1) {
+        HCCL_ERROR("copy engine: schedules with %zu queues need launches that wait on one another on one GPU; use the SM engine", nq);
+        return HCCL_E_NOT_SUPPORT;
+    }
     HelperStreams &h = HelpersFor(c, nq > 1 ? nq - 1 : 0);
     const bool collective = nq <= 1;       // point-to-point plans (several queues, mailbox) involve only some ranks: no barrier
     if (collective) barrier(stream);

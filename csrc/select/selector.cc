@@ -217,7 +217,13 @@ SelectorStatus AutoSelectorBase::Select(const SelectorCtx &ctx, OpParam &param) 
             if (!ctx.nvls || ctx.env->deterministic != Deterministic::OFF) continue;   // switch reduction order is not ours to fix
             st = SelectNvls(ctx, param);
         } else if (e == HCCL_ENGINE_SM) st = SelectSm(ctx, param);
-        else st = SelectIr(ctx, param);
+        else {
+            // Point-to-point schedules use several queues whose waits resolve through the peer; as stream work on one GPU
+            // those would be separate launches that depend on one another, which nothing guarantees to co-run. The SM
+            // engine serves them in a single launch instead.
+            if (param.opType == HCCL_CMD_SEND || param.opType == HCCL_CMD_RECEIVE || param.opType == HCCL_CMD_BATCH_SEND_RECV) continue;
+            st = SelectIr(ctx, param);
+        }
         if (st == SelectorStatus::MATCH) return st;
     }
     return SelectorStatus::NOT_MATCH;

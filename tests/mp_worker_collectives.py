@@ -89,6 +89,49 @@ def main():
         torch.cuda.synchronize()
         want = torch.cat([gen(s, n * world, torch.float32, salt=8)[rank * n:(rank + 1) * n] for s in range(world)])
         check(f"alltoall n={n}", torch.equal(recv, want))
+    # variable-count gather / reduce-scatter (zero-length contributions included) and unsigned bytes
+    vcnt = [((7 * r) % 5) * 1031 for r in range(world)]
+    vdis = [sum(vcnt[:r]) for r in range(world)]
+    mine = gen(rank, max(1, vcnt[rank]), torch.float32, salt=21)[:vcnt[rank]]
+    agv = torch.zeros(max(1, sum(vcnt)), dtype=torch.float32, device="cuda")
+    comm.all_gather_v(mine if vcnt[rank] else None, agv, vcnt, vdis)
+    torch.cuda.synchronize()
+    want = torch.cat([gen(r, max(1, vcnt[r]), torch.float32, salt=21)[:vcnt[r]] for r in range(world)])
+    check("allgatherv", torch.equal(agv[:want.numel()], want))
+    full = gen(rank, max(1, sum(vcnt)), torch.float32, salt=22)
+    rsv = torch.zeros(max(1, vcnt[rank]), dtype=torch.float32, device="cuda")
+    comm.reduce_scatter_v(full, vcnt, vdis, rsv if vcnt[rank] else None)
+    torch.cuda.synchronize()
+    ref = ref_reduce(world, max(1, sum(vcnt)), torch.float32, ReduceOp.SUM, salt=22)
+    check("reducescatterv", close(rsv[:vcnt[rank]], ref[vdis[rank]:vdis[rank] + vcnt[rank]], torch.float32, world))
+    u8 = (torch.arange(5000, device="cuda") % 7 + rank).to(torch.uint8)
+    u8o = torch.empty_like(u8)
+    comm.all_reduce(u8, u8o, ReduceOp.MAX)
+    torch.cuda.synchronize()
+    check("allreduce uint8 max", torch.equal(u8o, (torch.arange(5000, device="cuda") % 7 + world - 1).to(torch.uint8)))
+    # CUDA graph capture: all synchronisation state is on the device, so a captured operator replays with new data
+    n = 200_000
+    gx = gen(rank, n, torch.float32, salt=30)
+    gout = torch.empty_like(gx)
+    ggat = torch.empty(n * world, dtype=torch.float32, device="cuda")
+    comm.all_reduce(gx, gout)
+    comm.all_gather(gx, ggat)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        comm.all_reduce(gx, gout)
+        comm.all_gather(gout, ggat)
+    for it in range(3):
+        gx.copy_(gen(rank, n, torch.float32, salt=31 + it))
+        graph.replay()
+        torch.cuda.synchronize()
+        ref = ref_reduce(world, n, torch.float32, ReduceOp.SUM, salt=31 + it)
+        check(f"graph replay {it} allreduce", close(gout, ref, torch.float32, world))
+        check(f"graph replay {it} allgather", torch.equal(ggat, gout.repeat(world)))
+    # eager calls after replays: the device-side sequence numbers moved on during the replays
+    comm.all_reduce(gx, gout)
+    torch.cuda.synchronize()
+    check("eager after graph", close(gout, ref_reduce(world, n, torch.float32, ReduceOp.SUM, salt=33), torch.float32, world))
     # AlltoAllV with a skewed matrix
     M = [[((i * 7 + j * 13) % 5) * 1000 + (i + j) % 2 for j in range(world)] for i in range(world)]
     send = gen(rank, max(1, sum(M[rank])), torch.float32, salt=9)

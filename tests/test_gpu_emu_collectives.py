@@ -78,6 +78,19 @@ def test_allreduce_dtypes_ops(emu_mod, dtype, op):
                     assert torch.equal(o.to(torch.int64), ref.to(dtype).to(torch.int64))
 
 
+@pytest.mark.parametrize("dtype", [torch.uint8, torch.uint16, torch.uint32])
+def test_allreduce_unsigned(emu_mod, dtype):
+    nranks, count = 4, 2051
+    with emu_mod.EmuWorld(nranks, 1 << 20) as w:
+        xs64 = [torch.randint(0, 60, (count,), device="cuda", dtype=torch.int64) for _ in range(nranks)]
+        xs = [x.to(dtype) for x in xs64]
+        for op, ref in ((ReduceOp.SUM, torch.stack(xs64).sum(0)), (ReduceOp.MAX, torch.stack(xs64).max(0).values)):
+            outs = [torch.empty_like(x) for x in xs]
+            assert w.run(CMD["ALLREDUCE"], "SmAllReduceMesh1DTwoShot", xs, outs, count, dtype, op) == 0
+            for o in outs:
+                assert torch.equal(o.to(torch.int64), ref)
+
+
 def test_allreduce_prod_and_inplace(emu_mod):
     nranks, count = 3, 513
     with emu_mod.EmuWorld(nranks, 1 << 20) as w:

@@ -27,9 +27,18 @@ def _fused_ok(*ts) -> bool:
     return all(t.is_cuda and t.dtype == torch.bfloat16 for t in ts)
 
 
+_NATIVE_GEMM = True
+
+
+def use_native_gemm(flag: bool) -> None:
+    """False routes the non-fused matmuls (weight gradients) to torch.matmul; used by the NCCL + cuBLAS baseline arm."""
+    global _NATIVE_GEMM
+    _NATIVE_GEMM = flag
+
+
 def _mm_nt(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """a[M, K] @ w[N, K].T on the tcgen05 GEMM where its shape rules allow, torch.matmul otherwise."""
-    if _fused_ok(a, w) and a.shape[1] % 8 == 0 and w.shape[0] % 8 == 0:
+    if _NATIVE_GEMM and _fused_ok(a, w) and a.shape[1] % 8 == 0 and w.shape[0] % 8 == 0:
         return _gemm.gemm_bf16(a.contiguous(), w.contiguous())
     return a @ w.t()
 
@@ -37,7 +46,7 @@ def _mm_nt(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 def all_gather_matmul(comm, x_local: torch.Tensor, w: torch.Tensor, want_gathered: bool = False):
     """-> (all_gather_rows(x_local) @ w.T, gathered rows or None)"""
     m, k = x_local.shape
-    if _fused_ok(x_local, w) and m % 128 == 0 and m <= 8192 and k % 8 == 0 and w.shape[0] % 8 == 0:
+    if getattr(comm, "fused", True) and _fused_ok(x_local, w) and m % 128 == 0 and m <= 8192 and k % 8 == 0 and w.shape[0] % 8 == 0:
         gathered = torch.empty((m * comm.size, k), dtype=x_local.dtype, device=x_local.device) if want_gathered else None
         out = _mc2.all_gather_matmul(comm, x_local.contiguous(), w.contiguous(), gathered=gathered)
         return out, gathered
@@ -51,7 +60,7 @@ def matmul_reduce_scatter(comm, a: torch.Tensor, w: torch.Tensor) -> torch.Tenso
     """-> reduce_scatter_rows(a @ w.T)"""
     m, k = a.shape
     n = w.shape[0]
-    if _fused_ok(a, w) and m % (128 * comm.size) == 0 and m // comm.size <= 8192 and k % 8 == 0 and n % 8 == 0:
+    if getattr(comm, "fused", True) and _fused_ok(a, w) and m % (128 * comm.size) == 0 and m // comm.size <= 8192 and k % 8 == 0 and n % 8 == 0:
         return _mc2.matmul_reduce_scatter(comm, a.contiguous(), w.contiguous())
     partial = _mm_nt(a, w).contiguous()
     out = torch.empty((m // comm.size, n), dtype=a.dtype, device=a.device)
@@ -62,7 +71,7 @@ def matmul_reduce_scatter(comm, a: torch.Tensor, w: torch.Tensor) -> torch.Tenso
 
 def matmul_all_reduce(comm, a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """-> all_reduce(a @ w.T)"""
-    if _fused_ok(a, w) and a.shape[1] % 8 == 0 and w.shape[0] % 64 == 0:
+    if getattr(comm, "fused", True) and _fused_ok(a, w) and a.shape[1] % 8 == 0 and w.shape[0] % 64 == 0:
         return _mc2.matmul_all_reduce(comm, a.contiguous(), w.contiguous())
     out = _mm_nt(a, w).contiguous()
     comm.all_reduce(out)

@@ -20,7 +20,11 @@ from hccl_b200.comm import init_from_env  # noqa: E402
 DT = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16}
 
 
-def time_fn(fn, iters, warmup):
+HOST_US = {}
+
+
+def time_fn(fn, iters, warmup, tag=None):
+    import time
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
@@ -28,10 +32,14 @@ def time_fn(fn, iters, warmup):
     torch.cuda.synchronize()
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     s.record()
+    h0 = time.perf_counter()
     for _ in range(iters):
         fn()
+    h1 = time.perf_counter()            # host time to ISSUE the calls (no synchronisation inside)
     e.record()
     torch.cuda.synchronize()
+    if tag is not None:
+        HOST_US[tag] = (h1 - h0) / iters * 1e6
     t = torch.tensor([s.elapsed_time(e) / iters], device="cuda")
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return t.item() * 1e-3
@@ -92,15 +100,15 @@ def main():
                     factor = (n - 1) / n
                 else:
                     raise SystemExit(f"unknown op {op}")
-                t_ours = time_fn(ours, iters, warm)
+                t_ours = time_fn(ours, iters, warm, tag="ours")
                 t_ref = float("nan") if args.skip_nccl else time_fn(ref, iters, warm)
                 bus_ours = size * factor / t_ours / 1e9
                 bus_ref = size * factor / t_ref / 1e9
                 rows.append(dict(op=op, dtype=dname, bytes=size, ranks=n, ours_us=t_ours * 1e6, nccl_us=t_ref * 1e6, ours_busGBs=bus_ours,
-                                 nccl_busGBs=bus_ref, ratio=bus_ours / bus_ref if bus_ref == bus_ref else None))
+                                 nccl_busGBs=bus_ref, ratio=bus_ours / bus_ref if bus_ref == bus_ref else None, ours_host_issue_us=HOST_US.get("ours")))
                 if rank == 0:
                     print(f"{op:13s} {dname:5s} {size:>11d} B  ours {t_ours*1e6:9.1f} us {bus_ours:8.1f} GB/s | nccl {t_ref*1e6:9.1f} us {bus_ref:8.1f} GB/s"
-                          f" | x{bus_ours / bus_ref if bus_ref == bus_ref else float('nan'):.2f}", flush=True)
+                          f" | x{bus_ours / bus_ref if bus_ref == bus_ref else float('nan'):.2f} | host {HOST_US.get('ours', 0):.1f} us", flush=True)
                 del x
                 size *= 4 if size >= (1 << 22) and args.max_bytes > (1 << 28) else 2
                 idx += 1

@@ -17,6 +17,7 @@ namespace hccl {
 
 constexpr int kMaxRanks = 32;
 constexpr int kMaxChannels = 256;       // CTA channels with independent flag rows / epochs
+constexpr int kPipeChannels = 128;      // channels of the pipelined (warp-specialised) collectives
 constexpr int kNotifySlots = 24;        // host-engine notify counters per peer
 constexpr int kP2pCtas = 8;             // CTAs per point-to-point transfer
 constexpr uint64_t kCtrlBytes = 64 << 10;
@@ -47,6 +48,7 @@ struct DevCtrl {
     uint64_t p2pRecvSeq[kMaxRanks][kP2pCtas];   // mailbox rounds received from peer r by p2p CTA b
     uint64_t hostNotifySent[kMaxRanks][kNotifySlots];   // host-engine: posts issued towards peer r
     uint64_t hostNotifyWaited[kMaxRanks][kNotifySlots]; // host-engine: waits consumed from peer r
+    uint32_t pipeEpoch[kPipeChannels];                  // pipelined collectives: flag value reached by the previous operator
 };
 static_assert(sizeof(DevCtrl) <= kCtrlBytes, "control block too large");
 
@@ -61,6 +63,7 @@ struct DevFlags {
     uint32_t mc2Ready[2][kMaxRanks][64];         // [half][src][block]: pieces of `block` delivered by src
     uint32_t mc2Done[2][kMaxRanks][4];           // [half][src][k]: second-stage counters (results delivered by src)
     uint32_t moeCount[kMaxRanks][320];           // MoE dispatch: moeCount[src][e] = tokens rank src routes to expert e
+    uint32_t pipe[3][kPipeChannels][kMaxRanks];  // pipelined collectives: [staged|moved|drained][ch][src] = sub-chunks done by src
 };
 static_assert(sizeof(DevFlags) <= kFlagBytes, "flag arena too large");
 

@@ -27,6 +27,12 @@ enum SmKernelId : uint32_t {
     K_SEND,
     K_RECV,
     K_BATCH_SEND_RECV,
+    K_ALLREDUCE_PIPE,         // warp-specialised pipelines (pipelined.cuh): any payload in one launch
+    K_ALLREDUCE_PIPE_NVLS,
+    K_REDUCESCATTER_PIPE,     // also ReduceScatterV
+    K_REDUCESCATTER_PIPE_NVLS,
+    K_ALLGATHER_PIPE,         // also AllGatherV
+    K_ALLGATHER_PIPE_NVLS,
     K_COUNT
 };
 
@@ -43,6 +49,7 @@ struct CollArgs {
     uint32_t root;
     uint32_t op;              // HcclReduceOp
     uint32_t peer;            // Send / Recv
+    uint64_t pipeSub;         // pipelined kernels: bytes of one sub-chunk per (slice, channel), a multiple of 128
     // per-rank byte counts / offsets (V-form kernels; the plain forms fill them uniformly)
     uint64_t sendBytes[kMaxRanks];
     uint64_t sendOff[kMaxRanks];

@@ -295,6 +295,8 @@ template <bool EMU> __device__ void AlltoAllVBody(KCtx &k, const CollArgs &A)
     BlockCopy((char *)A.out + A.recvOff[k.rank] + p.off, (const char *)A.in + A.sendOff[k.rank] + p.off, p.len);
 }
 
+#include "pipelined.cuh"
+
 // ================================================================================================ kernels
 #define COLL_KERNEL_TYPED(NAME, BODY)                                                                                  \
     template <typename T, bool EMU>                                                                                    \
@@ -314,6 +316,14 @@ COLL_KERNEL_TYPED(KAllReduceOneShot, AllReduceOneShotBody)
 COLL_KERNEL_TYPED(KAllReduceTwoShot, AllReduceTwoShotBody)
 COLL_KERNEL_TYPED(KReduceScatterV, ReduceScatterVBody)
 COLL_KERNEL_TYPED(KReduce, ReduceBody)
+template <typename T, int OP, bool EMU> __device__ void AllReducePipePlainBody(KCtx &k, const CollArgs &A) { pipe::AllReduceBody<T, OP, EMU, false>(k, A); }
+template <typename T, int OP, bool EMU> __device__ void AllReducePipeNvlsBody(KCtx &k, const CollArgs &A) { pipe::AllReduceBody<T, OP, EMU, true>(k, A); }
+template <typename T, int OP, bool EMU> __device__ void ReduceScatterPipePlainBody(KCtx &k, const CollArgs &A) { pipe::ReduceScatterBody<T, OP, EMU, false>(k, A); }
+template <typename T, int OP, bool EMU> __device__ void ReduceScatterPipeNvlsBody(KCtx &k, const CollArgs &A) { pipe::ReduceScatterBody<T, OP, EMU, true>(k, A); }
+template <bool EMU> __device__ void AllGatherPipePlainBody(KCtx &k, const CollArgs &A) { pipe::AllGatherBody<EMU, false>(k, A); }
+template <bool EMU> __device__ void AllGatherPipeNvlsBody(KCtx &k, const CollArgs &A) { pipe::AllGatherBody<EMU, true>(k, A); }
+COLL_KERNEL_TYPED(KAllReducePipe, AllReducePipePlainBody)
+COLL_KERNEL_TYPED(KReduceScatterPipe, ReduceScatterPipePlainBody)
 
 #define COLL_KERNEL_NVLS(NAME, BODY)                                                                                   \
     template <typename T, int OP, bool EMU>                                                                            \
@@ -326,6 +336,8 @@ COLL_KERNEL_TYPED(KReduce, ReduceBody)
 COLL_KERNEL_NVLS(KAllReduceNvlsOneShot, AllReduceNvlsOneShotBody)
 COLL_KERNEL_NVLS(KAllReduceNvlsTwoShot, AllReduceNvlsTwoShotBody)
 COLL_KERNEL_NVLS(KReduceScatterNvls, ReduceScatterNvlsBody)
+COLL_KERNEL_NVLS(KAllReducePipeNvls, AllReducePipeNvlsBody)
+COLL_KERNEL_NVLS(KReduceScatterPipeNvls, ReduceScatterPipeNvlsBody)
 
 #define COLL_KERNEL_BYTES(NAME, BODY)                                                                                  \
     template <bool EMU>                                                                                                \
@@ -340,6 +352,8 @@ COLL_KERNEL_BYTES(KBroadcast, BroadcastBody)
 COLL_KERNEL_BYTES(KBroadcastNvls, BroadcastNvlsBody)
 COLL_KERNEL_BYTES(KScatter, ScatterBody)
 COLL_KERNEL_BYTES(KAlltoAllV, AlltoAllVBody)
+COLL_KERNEL_BYTES(KAllGatherPipe, AllGatherPipePlainBody)
+COLL_KERNEL_BYTES(KAllGatherPipeNvls, AllGatherPipeNvlsBody)
 
 template <bool EMU> __global__ void __launch_bounds__(kThreads) KBarrier(const DevComm *comms, const __grid_constant__ CollArgs a, const CollArgs *)
 {
@@ -506,6 +520,8 @@ template <bool EMU> CollKernelFn TypedKernel(SmKernelId id, HcclDataType dt)
         case K_ALLREDUCE_TWOSHOT: PICK(KAllReduceTwoShot)
         case K_REDUCESCATTER_V: PICK(KReduceScatterV)
         case K_REDUCE: PICK(KReduce)
+        case K_ALLREDUCE_PIPE: PICK(KAllReducePipe)
+        case K_REDUCESCATTER_PIPE: PICK(KReduceScatterPipe)
         default: return nullptr;
     }
 #undef PICK
@@ -526,6 +542,8 @@ template <bool EMU> CollKernelFn NvlsKernel(SmKernelId id, HcclDataType dt, Hccl
         case K_ALLREDUCE_NVLS_ONESHOT: PICKN(KAllReduceNvlsOneShot)
         case K_ALLREDUCE_NVLS_TWOSHOT: PICKN(KAllReduceNvlsTwoShot)
         case K_REDUCESCATTER_NVLS: PICKN(KReduceScatterNvls)
+        case K_ALLREDUCE_PIPE_NVLS: PICKN(KAllReducePipeNvls)
+        case K_REDUCESCATTER_PIPE_NVLS: PICKN(KReduceScatterPipeNvls)
         default: return nullptr;
     }
 #undef PICKN
@@ -534,9 +552,12 @@ template <bool EMU> CollKernelFn NvlsKernel(SmKernelId id, HcclDataType dt, Hccl
 template <bool EMU> CollKernelFn KernelFor(const SmLaunch &l)
 {
     switch (l.kernel) {
-        case K_ALLREDUCE_ONESHOT: case K_ALLREDUCE_TWOSHOT: case K_REDUCESCATTER_V: case K_REDUCE: return TypedKernel<EMU>(l.kernel, l.dtype);
-        case K_ALLREDUCE_NVLS_ONESHOT: case K_ALLREDUCE_NVLS_TWOSHOT: case K_REDUCESCATTER_NVLS:
+        case K_ALLREDUCE_ONESHOT: case K_ALLREDUCE_TWOSHOT: case K_REDUCESCATTER_V: case K_REDUCE: case K_ALLREDUCE_PIPE: case K_REDUCESCATTER_PIPE:
+            return TypedKernel<EMU>(l.kernel, l.dtype);
+        case K_ALLREDUCE_NVLS_ONESHOT: case K_ALLREDUCE_NVLS_TWOSHOT: case K_REDUCESCATTER_NVLS: case K_ALLREDUCE_PIPE_NVLS: case K_REDUCESCATTER_PIPE_NVLS:
             return NvlsKernel<EMU>(l.kernel, l.dtype, (HcclReduceOp)l.args.op);
+        case K_ALLGATHER_PIPE: return KAllGatherPipe<EMU>;
+        case K_ALLGATHER_PIPE_NVLS: return KAllGatherPipeNvls<EMU>;
         case K_ALLGATHER_V: return KAllGatherV<EMU>;
         case K_BROADCAST: return KBroadcast<EMU>;
         case K_BROADCAST_NVLS: return KBroadcastNvls<EMU>;

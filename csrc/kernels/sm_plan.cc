@@ -76,6 +76,60 @@ HcclResult SmPlanOp(const SmPlanCtx &ctx, const OpParam &p, const std::string &a
             push(nv ? K_ALLREDUCE_NVLS_TWOSHOT : K_ALLREDUCE_TWOSHOT, lo, cnt, cnt * es / n * 2, [&](SmLaunch &l) { l.args.in = in + lo * es; l.args.out = outp + lo * es; });
         });
     }
+    // ---- warp-specialised pipelines: one launch for any payload; the scratch half holds rings of sub-chunks
+    auto pipeSub = [&](uint32_t rings, uint32_t ctas) -> uint64_t {
+        uint64_t s = Down128(ccl / ((uint64_t)rings * 2 /* depth */ * n * ctas));
+        return std::min<uint64_t>(s, 256u << 10);
+    };
+    auto pipeCtas = [&](uint64_t movedBytes) { return std::min<uint32_t>(SmCtasFor(movedBytes, ctx.maxCtas), kPipeChannels); };
+    if (alg == "SmAllReducePipelined" || alg == "NvlsAllReducePipelined") {
+        bool nv = alg[0] == 'N';
+        if (nv && (!ctx.nvls || (p.count * es) % 16 != 0)) return HCCL_E_NOT_SUPPORT;
+        SmLaunch l = base;
+        l.kernel = nv ? K_ALLREDUCE_PIPE_NVLS : K_ALLREDUCE_PIPE;
+        l.args.count = p.count; l.args.bytes = p.count * es; l.args.in = in; l.args.out = outp;
+        l.ctas = pipeCtas(p.count * es / n * 2);
+        l.args.pipeSub = pipeSub(2, l.ctas);
+        if (l.args.pipeSub < 128) return HCCL_E_NOT_SUPPORT;
+        out->push_back(l);
+        return HCCL_SUCCESS;
+    }
+    if (alg == "SmReduceScatterPipelined" || alg == "SmReduceScatterVPipelined" || alg == "NvlsReduceScatterPipelined") {
+        bool v = p.opType == HCCL_CMD_REDUCE_SCATTER_V;
+        bool nv = alg[0] == 'N';
+        if (nv && (!ctx.nvls || v || (p.count * es) % 16 != 0)) return HCCL_E_NOT_SUPPORT;
+        uint64_t longest = v ? *std::max_element(p.sendCounts.begin(), p.sendCounts.end()) : p.count;
+        SmLaunch l = base;
+        l.kernel = nv ? K_REDUCESCATTER_PIPE_NVLS : K_REDUCESCATTER_PIPE;
+        l.args.in = in; l.args.out = outp;
+        for (uint32_t r = 0; r < n; ++r) {
+            l.args.sendBytes[r] = (v ? p.sendCounts[r] : p.count) * es;
+            l.args.sendOff[r] = (v ? p.sendDispls[r] : (uint64_t)r * p.count) * es;
+        }
+        l.ctas = pipeCtas(longest * es * (n - 1));
+        l.args.pipeSub = pipeSub(1, l.ctas);
+        if (l.args.pipeSub < 128) return HCCL_E_NOT_SUPPORT;
+        out->push_back(l);
+        return HCCL_SUCCESS;
+    }
+    if (alg == "SmAllGatherPush" || alg == "SmAllGatherVPush" || alg == "NvlsAllGatherPush" || alg == "NvlsAllGatherVPush") {
+        bool v = p.opType == HCCL_CMD_ALLGATHER_V;
+        bool nv = alg[0] == 'N';
+        if (nv && !ctx.nvls) return HCCL_E_NOT_SUPPORT;
+        uint64_t longest = v ? *std::max_element(p.recvCounts.begin(), p.recvCounts.end()) : p.count;
+        SmLaunch l = base;
+        l.kernel = nv ? K_ALLGATHER_PIPE_NVLS : K_ALLGATHER_PIPE;
+        l.args.in = in; l.args.out = outp;
+        for (uint32_t r = 0; r < n; ++r) {
+            l.args.recvBytes[r] = (v ? p.recvCounts[r] : p.count) * es;
+            l.args.recvOff[r] = (v ? p.recvDispls[r] : (uint64_t)r * p.count) * es;
+        }
+        l.ctas = pipeCtas(longest * es * (n - 1));
+        l.args.pipeSub = pipeSub(1, l.ctas);
+        if (l.args.pipeSub < 128) return HCCL_E_NOT_SUPPORT;
+        out->push_back(l);
+        return HCCL_SUCCESS;
+    }
     if (alg == "SmAllGatherMesh1D" || alg == "SmAllGatherVMesh1D") {
         bool v = p.opType == HCCL_CMD_ALLGATHER_V;
         uint64_t total = v ? *std::max_element(p.recvCounts.begin(), p.recvCounts.end()) : p.count;

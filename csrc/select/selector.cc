@@ -44,7 +44,7 @@ bool SmReduceSupports(HcclDataType t, HcclReduceOp op)
     switch (t) {
         case HCCL_DATA_TYPE_INT8: case HCCL_DATA_TYPE_INT16: case HCCL_DATA_TYPE_INT32: case HCCL_DATA_TYPE_INT64:
         case HCCL_DATA_TYPE_UINT64: case HCCL_DATA_TYPE_FP16: case HCCL_DATA_TYPE_FP32: case HCCL_DATA_TYPE_FP64:
-        case HCCL_DATA_TYPE_BFP16: return op <= HCCL_REDUCE_MIN;
+        case HCCL_DATA_TYPE_BFP16: case HCCL_DATA_TYPE_UINT8: case HCCL_DATA_TYPE_UINT16: case HCCL_DATA_TYPE_UINT32: return op <= HCCL_REDUCE_MIN;
         default: return false;
     }
 }
@@ -301,6 +301,7 @@ class CopyFamilySelector : public AutoSelectorBase {     // everything that only
 protected:
     SelectorStatus SelectNvls(const SelectorCtx &ctx, OpParam &p) const override
     {
+        if (p.opType == HCCL_CMD_ALLGATHER || p.opType == HCCL_CMD_ALLGATHER_V) return FromTable(ctx, p, HCCL_ENGINE_NVLS);
         if (p.opType != HCCL_CMD_BROADCAST) return SelectorStatus::NOT_MATCH;
         if (IsSmallData(p.DataBytes())) return SelectorStatus::NOT_MATCH;   // pull from root wins on latency
         return FromTable(ctx, p, HCCL_ENGINE_NVLS);

@@ -226,3 +226,67 @@ def test_bounded_wait_reports_timeout(emu_mod):
         outs = [torch.empty_like(x) for x in xs]
         assert w.run(CMD["ALLREDUCE"], "SmAllReduceMesh1DOneShot", xs, outs, 100, torch.float32) == 0
         assert torch.allclose(outs[0], xs[0] + xs[1])
+
+
+# ---- warp-specialised pipelined kernels (plain peer-memory variants; the NVLS variants need a real multicast mapping) ----
+@pytest.mark.parametrize("nranks,ccl_kb,ctas", [(2, 1024, 4), (4, 256, 4), (8, 256, 2), (3, 64, 3)])
+@pytest.mark.parametrize("count", [1, 37, 4099, 300_001])
+def test_pipelined_allreduce(emu_mod, nranks, ccl_kb, ctas, count):
+    """Small scratch + large count walks the ring many times (sub-chunks of a few KB), which exercises slot reuse."""
+    with emu_mod.EmuWorld(nranks, ccl_kb << 10) as w:
+        for it, (dtype, op) in enumerate(((torch.float32, ReduceOp.SUM), (torch.bfloat16, ReduceOp.MAX), (torch.int32, ReduceOp.SUM))):
+            xs = [_rand(count, dtype, 300 + 10 * it + r) for r in range(nranks)]
+            outs = [torch.empty_like(x) for x in xs]
+            assert w.run(CMD["ALLREDUCE"], "SmAllReducePipelined", xs, outs, count, dtype, op, max_ctas=ctas) == 0
+            ref = _ref_reduce(xs, op, dtype)
+            for o in outs:
+                if dtype.is_floating_point:
+                    assert torch.allclose(o.double(), ref, atol=_tol(dtype, nranks), rtol=1e-2)
+                else:
+                    assert torch.equal(o.to(torch.int64), ref)
+                assert torch.equal(o, outs[0])
+
+
+@pytest.mark.parametrize("nranks", [2, 5, 8])
+@pytest.mark.parametrize("count", [3, 2049, 150_001])
+def test_pipelined_allgather_reducescatter(emu_mod, nranks, count):
+    with emu_mod.EmuWorld(nranks, 256 << 10) as w:
+        for it in range(2):                                   # back-to-back operators: flag bases carry over
+            xs = [_rand(count, torch.bfloat16, 7 * it + r) for r in range(nranks)]
+            outs = [torch.empty(count * nranks, dtype=torch.bfloat16, device="cuda") for _ in range(nranks)]
+            assert w.run(CMD["ALLGATHER"], "SmAllGatherPush", xs, outs, count, torch.bfloat16, max_ctas=3) == 0
+            want = torch.cat(xs)
+            for o in outs:
+                assert torch.equal(o, want)
+            full = [_rand(count * nranks, torch.float32, 10 + r + it) for r in range(nranks)]
+            rs = [torch.empty(count, dtype=torch.float32, device="cuda") for _ in range(nranks)]
+            assert w.run(CMD["REDUCE_SCATTER"], "SmReduceScatterPipelined", full, rs, count, torch.float32, max_ctas=3) == 0
+            ref = _ref_reduce(full, ReduceOp.SUM, torch.float32)
+            for r in range(nranks):
+                assert torch.allclose(rs[r].double(), ref[r * count:(r + 1) * count], atol=1e-4)
+
+
+def test_pipelined_v_forms_and_unaligned_input(emu_mod):
+    nranks = 4
+    counts = [100, 0, 70_001, 33]
+    with emu_mod.EmuWorld(nranks, 128 << 10) as w:
+        xs = [_rand(max(1, counts[r]) + 1, torch.float32, r)[1:] for r in range(nranks)]       # 4-byte aligned only
+        outs = [torch.zeros(sum(counts), dtype=torch.float32, device="cuda") for _ in range(nranks)]
+        assert w.run(CMD["ALLGATHER_V"], "SmAllGatherVPush", xs, outs, 0, torch.float32, counts=counts, max_ctas=2) == 0
+        want = torch.cat([xs[r][:counts[r]] for r in range(nranks)])
+        for o in outs:
+            assert torch.equal(o, want)
+        full = [_rand(sum(counts), torch.float32, 60 + r) for r in range(nranks)]
+        rs = [torch.zeros(max(1, counts[r]), dtype=torch.float32, device="cuda") for r in range(nranks)]
+        assert w.run(CMD["REDUCE_SCATTER_V"], "SmReduceScatterVPipelined", full, rs, 0, torch.float32, counts=counts, max_ctas=2) == 0
+        ref = _ref_reduce(full, ReduceOp.SUM, torch.float32)
+        off = 0
+        for r in range(nranks):
+            assert torch.allclose(rs[r][:counts[r]].double(), ref[off:off + counts[r]], atol=1e-4)
+            off += counts[r]
+        # one-byte elements at an odd address
+        b = [torch.randint(0, 255, (10_001,), device="cuda", dtype=torch.uint8)[1:] for _ in range(nranks)]
+        bo = [torch.zeros(10_000 * nranks, dtype=torch.uint8, device="cuda") for _ in range(nranks)]
+        assert w.run(CMD["ALLGATHER"], "SmAllGatherPush", b, bo, 10_000, torch.uint8, max_ctas=2) == 0
+        for o in bo:
+            assert torch.equal(o, torch.cat(b))

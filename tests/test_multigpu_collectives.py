@@ -28,10 +28,14 @@ def _run(nproc, extra_env, port, worker="mp_worker_collectives.py", expect="all 
     {"HCCL_NVLS_ENABLE": "1"},
     {"HCCL_NVLS_ENABLE": "1", "HCCL_BUFFSIZE": "4"},
     {"HCCL_NVLS_ENABLE": "0", "HCCL_OP_EXPANSION_MODE": "COPY_ENGINE", "HCCL_BUFFSIZE": "16"},
+    {"HCCL_NVLS_ENABLE": "1", "HCCL_BUFFSIZE": "8", "HCCL_ALGO_NAME": "allreduce=NvlsAllReducePipelined;allgather=NvlsAllGatherPush;"
+     "reducescatter=NvlsReduceScatterPipelined;allgatherv=NvlsAllGatherVPush;reducescatterv=SmReduceScatterVPipelined"},
+    {"HCCL_NVLS_ENABLE": "0", "HCCL_BUFFSIZE": "8", "HCCL_ALGO_NAME": "allreduce=SmAllReducePipelined;allgather=SmAllGatherPush;"
+     "reducescatter=SmReduceScatterPipelined;allgatherv=SmAllGatherVPush;reducescatterv=SmReduceScatterVPipelined"},
 ])
 def test_collectives_two_or_more_gpus(cfg):
     n = min(torch.cuda.device_count(), 8)
-    _run(n, cfg, 29610 + len(cfg) * 7 + int(cfg.get("HCCL_NVLS_ENABLE", "0")) * 3 + len(cfg.get("HCCL_OP_EXPANSION_MODE", "")))
+    _run(n, cfg, 29610 + len(cfg) * 7 + int(cfg.get("HCCL_NVLS_ENABLE", "0")) * 3 + len(cfg.get("HCCL_OP_EXPANSION_MODE", "")) + len(cfg.get("HCCL_ALGO_NAME", "")) % 97)
 
 
 def test_fused_matmul_collectives_two_or_more_gpus():

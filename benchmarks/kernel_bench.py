@@ -46,9 +46,9 @@ def bench_gemm(a):
     w = (torch.randn(a.n, a.k, device="cuda") * 0.02).to(torch.bfloat16)
     out = torch.empty(a.m, a.n, device="cuda", dtype=torch.bfloat16)
     flush = torch.empty(160 << 20, dtype=torch.uint8, device="cuda") if a.flush else None
-    ours = _time(lambda: gemm.gemm_bf16(x, w, out=out), a.iters, flush=flush)
+    ours = _time(lambda: gemm.gemm_bf16(x, w, out=out, variant=a.variant), a.iters, flush=flush)
     gemm.check_error()
-    res = {"case": "gemm", "m": a.m, "n": a.n, "k": a.k, "ours_ms": round(ours, 4), "ours_tflops": round(2 * a.m * a.n * a.k / ours / 1e9, 1)}
+    res = {"case": "gemm", "variant": a.variant, "m": a.m, "n": a.n, "k": a.k, "ours_ms": round(ours, 4), "ours_tflops": round(2 * a.m * a.n * a.k / ours / 1e9, 1)}
     if not a.no_cublas:
         ref = torch.empty_like(out)
         cub = _time(lambda: torch.matmul(x, w.t(), out=ref), a.iters, flush=flush)
@@ -134,6 +134,7 @@ def main():
     g = sub.add_parser("gemm")
     g.add_argument("--m", type=int, default=8192); g.add_argument("--n", type=int, default=8192); g.add_argument("--k", type=int, default=4096)
     g.add_argument("--iters", type=int, default=10); g.add_argument("--flush", action="store_true"); g.add_argument("--no-cublas", action="store_true")
+    g.add_argument("--variant", type=int, default=0, help="0 auto, 1 one-CTA tiles, 2 CTA-pair 256x256 tiles")
     r = sub.add_parser("emu-allreduce")
     r.add_argument("--ranks", type=int, default=4); r.add_argument("--mb", type=int, default=64); r.add_argument("--dtype", default="fp32")
     r.add_argument("--alg", default="SmAllReduceMesh1DTwoShot"); r.add_argument("--ctas", type=int, default=32); r.add_argument("--iters", type=int, default=5)

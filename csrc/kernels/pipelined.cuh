@@ -51,6 +51,7 @@ __device__ __forceinline__ void Signal(KCtx &k, const Role &r, int kind, uint32_
 __device__ __forceinline__ void Copy(void *dst, const void *src, uint64_t n, const Role &r)
 {
     if (n == 0) return;
+    HCCL_CHECK_RANGE(dst, src, n);
     uintptr_t a = (uintptr_t)dst | (uintptr_t)src;
     if ((a & 15u) == 0) {
         constexpr int U = 8;

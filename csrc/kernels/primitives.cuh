@@ -19,6 +19,10 @@
 namespace hccl {
 namespace dev {
 
+#ifdef HCCL_DEBUG_BOUNDS
+static __device__ const DevComm *g_boundsComm = nullptr;   // debug flavor: communicator of the running kernel (see HeapRangeOk)
+#endif
+
 // ---------------------------------------------------------------------------------------------- flag accessors
 __device__ __forceinline__ uint32_t LdAcquireSys(const uint32_t *p)
 {
@@ -129,6 +133,9 @@ template <bool EMU> __device__ __forceinline__ KCtx EnterCollective(const DevCom
     __shared__ uint32_t sHalf, sEpoch;
     KCtx k;
     k.c = EMU ? &comms[blockIdx.y] : comms;
+#ifdef HCCL_DEBUG_BOUNDS
+    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) g_boundsComm = k.c;
+#endif
     k.rank = k.c->rank;
     k.nranks = k.c->nranks;
     k.heap = k.c->heap[k.rank];
@@ -213,10 +220,38 @@ template <int UNROLL> __device__ __forceinline__ void CopyVec16(uint4 *__restric
     for (; i < nvec; i += blockDim.x) d[i] = s[i];
 }
 
+#ifdef HCCL_DEBUG_BOUNDS
+// Debug flavor (-DHCCL_DEBUG_BOUNDS): every kernel registers its communicator at entry; a copy whose source or
+// destination starts inside some rank's heap must also end inside it. A violation records status code 2 with the
+// offending offset and the copy is skipped -- nothing out of range is ever touched.
+__device__ __forceinline__ bool HeapRangeOk(const void *p, uint64_t n)
+{
+    const DevComm *c = g_boundsComm;
+    if (!c) return true;
+    const char *b = (const char *)p;
+    for (int r = 0; r < c->nranks; ++r) {
+        const char *h = c->heap[r];
+        if (b >= h && b < h + c->heapBytes) {
+            if (b + n <= h + c->heapBytes) return true;
+            DevStatus *s = c->status;
+            s->rank = (uint32_t)c->rank; s->peer = (uint32_t)r; s->phase = 900; s->observed = (uint32_t)((b - h) >> 10); s->expected = (uint32_t)(c->heapBytes >> 10);
+            __threadfence_system();
+            *((volatile uint32_t *)&s->code) = 2u;
+            return false;
+        }
+    }
+    return true;    // user memory: extent unknown to the library
+}
+#define HCCL_CHECK_RANGE(dst, src, n) if (!HeapRangeOk(dst, n) || !HeapRangeOk(src, n)) return
+#else
+#define HCCL_CHECK_RANGE(dst, src, n)
+#endif
+
 // Copies `n` bytes with all threads of the CTA. Any alignment; 16-byte vectors when both sides allow it.
 __device__ __forceinline__ void BlockCopy(void *dst, const void *src, uint64_t n)
 {
     if (n == 0) return;
+    HCCL_CHECK_RANGE(dst, src, n);
     uintptr_t a = (uintptr_t)dst | (uintptr_t)src;
     if ((a & 15u) == 0) {
         uint64_t nvec = n >> 4;

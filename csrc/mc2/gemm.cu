@@ -3,6 +3,8 @@
 #include "../common/log.h"
 #include "gemm_host.h"
 #include "gemm_sm100.cuh"
+#include "gemm_sm100_2cta.cuh"
+#include <cstdlib>
 #include "hccl/hccl_mc2.h"
 
 namespace hccl {
@@ -96,6 +98,45 @@ template <int BN> static HcclResult LaunchPlain(const void *a, const void *b, vo
     return HCCL_SUCCESS;
 }
 
+// 256 x 256 tiles on CTA pairs (cta_group::2). Needs an even grid; one cluster of two CTAs per tile.
+static HcclResult LaunchPlain2Cta(const void *a, const void *b, void *c, uint32_t M, uint32_t N, uint32_t K, bool outFp32, cudaStream_t s)
+{
+    GemmParams p{};
+    using S = Gemm2CtaSmem;
+    CHK_RET(EncodeTmap2D(&p.tmapA, a, M, K, (uint64_t)K * 2, kBM, kBK, 2));
+    CHK_RET(EncodeTmap2D(&p.tmapB, b, N, K, (uint64_t)K * 2, S::BN / 2, kBK, 2));
+    p.C = c; p.M = M; p.N = N; p.K = K; p.ldc = N; p.outFp32 = outFp32; p.groupM = 8; p.errorWord = GemmErrorWord();
+    static bool attrSet = false;
+    auto kern = GemmKernel2Cta<PlainPolicy>;
+    size_t smem = S::kTotal + 1024;
+    if (!attrSet) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return HCCL_E_RUNTIME;
+        attrSet = true;
+    }
+    uint32_t tiles = ((M + 2 * kBM - 1) / (2 * kBM)) * ((N + S::BN - 1) / S::BN);
+    uint32_t pairs = std::min<uint32_t>(tiles, (uint32_t)SmCount() / 2);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(pairs * 2);
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
+    if (e != cudaSuccess) { HCCL_ERROR("2-CTA GEMM launch failed: %s", cudaGetErrorString(e)); (void)cudaGetLastError(); return HCCL_E_RUNTIME; }
+    return HCCL_SUCCESS;
+}
+
+bool Gemm2CtaEnabled()
+{
+    static int v = -1;
+    if (v < 0) { const char *e = getenv("HCCL_GEMM_2CTA"); v = e ? atoi(e) : 0; }
+    return v != 0;
+}
+
 }  // namespace mc2
 }  // namespace hccl
 
@@ -114,10 +155,22 @@ HcclResult HcclGemmBf16(const void *a, const void *b, void *c, uint64_t m, uint6
     }
     // narrow tiles when the problem has too few 128x256 tiles to fill the GPU
     uint64_t tiles256 = ((m + 127) / 128) * ((n + 255) / 256);
+    if (Gemm2CtaEnabled() && tiles256 >= (uint64_t)SmCount()) return LaunchPlain2Cta(a, b, c, (uint32_t)m, (uint32_t)n, (uint32_t)k, outFp32 != 0, stream);
     if (tiles256 >= (uint64_t)SmCount() || n % 256 == 0 && tiles256 * 2 > (uint64_t)SmCount()) return LaunchPlain<256>(a, b, c, m, n, k, outFp32 != 0, stream);
     uint64_t tiles128 = ((m + 127) / 128) * ((n + 127) / 128);
     if (tiles128 >= (uint64_t)SmCount() / 2) return LaunchPlain<128>(a, b, c, m, n, k, outFp32 != 0, stream);
     return LaunchPlain<64>(a, b, c, m, n, k, outFp32 != 0, stream);
+}
+
+// variant 0 = automatic choice, 1 = one-CTA tiles, 2 = 256 x 256 tiles on CTA pairs (cta_group::2)
+HcclResult HcclGemmBf16Variant(const void *a, const void *b, void *c, uint64_t m, uint64_t n, uint64_t k, int outFp32, int variant, cudaStream_t stream)
+{
+    if (variant == 2) {
+        if (!a || !b || !c) return HCCL_E_PTR;
+        if (m == 0 || n == 0 || k == 0 || (k % 8) || (n % 8) || m > 0x7fffffff || n > 0x7fffffff || k > 0x7fffffff) return HCCL_E_PARA;
+        return LaunchPlain2Cta(a, b, c, (uint32_t)m, (uint32_t)n, (uint32_t)k, outFp32 != 0, stream);
+    }
+    return HcclGemmBf16(a, b, c, m, n, k, outFp32, stream);
 }
 
 HcclResult HcclGemmCheckError(void) { return GemmCheckError(); }

@@ -10,7 +10,8 @@ import os
 from pathlib import Path
 
 _LIB = None
-LIB_PATH = Path(__file__).resolve().parent / "lib" / "libhccl_b200.so"
+# HCCL_B200_LIB selects another build flavor of the same library (e.g. lib/libhccl_b200_debug.so with bounds checks)
+LIB_PATH = Path(os.environ.get("HCCL_B200_LIB") or Path(__file__).resolve().parent / "lib" / "libhccl_b200.so")
 
 HCCL_ROOT_INFO_BYTES = 4108
 

@@ -60,7 +60,21 @@ def _ninja(build_file: Path, jobs: int | None = None, verbose: bool = False) -> 
         print(res.stdout)
 
 
-def build_native(verbose: bool = False, ptxas_info: bool = False) -> Path:
+def build_native(verbose: bool = False, ptxas_info: bool = False, flavor: str = "") -> Path:
+    """flavor "" = release; "debug" = device-side bounds checks on every heap access (-DHCCL_DEBUG_BOUNDS) and host asserts;
+    "asan" = host code under AddressSanitizer. Flavors build into their own directory and library
+    (libhccl_b200_<flavor>.so); load one by pointing HCCL_B200_LIB at it."""
+    global BUILD
+    release_build = BUILD
+    if flavor:
+        BUILD = ROOT / f"build_{flavor}"
+    try:
+        return _build_native(verbose, ptxas_info, flavor)
+    finally:
+        BUILD = release_build
+
+
+def _build_native(verbose: bool, ptxas_info: bool, flavor: str) -> Path:
     BUILD.mkdir(exist_ok=True)
     LIBDIR.mkdir(parents=True, exist_ok=True)
     cc, cu = _sources()
@@ -68,9 +82,14 @@ def build_native(verbose: bool = False, ptxas_info: bool = False) -> Path:
     cxxflags = ["-O2", "-g1", "-std=c++17", "-fPIC", "-Wall", "-Wno-unused-function", "-pthread"] + inc
     nvflags = (["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC,-Wall,-Wno-unused-function",
                 "--threads", "2"] + ARCH_FLAGS + inc)
+    if flavor == "debug":
+        cxxflags = [f for f in cxxflags if f != "-O2"] + ["-O1", "-g", "-DHCCL_DEBUG_BOUNDS", "-D_GLIBCXX_ASSERTIONS"]
+        nvflags += ["-DHCCL_DEBUG_BOUNDS"]
+    elif flavor == "asan":
+        cxxflags += ["-fsanitize=address", "-fno-omit-frame-pointer"]
     if ptxas_info:
         nvflags += ["-Xptxas", "-v"]
-    out = LIBDIR / "libhccl_b200.so"
+    out = LIBDIR / (f"libhccl_b200_{flavor}.so" if flavor else "libhccl_b200.so")
     lines = [
         "ninja_required_version = 1.3",
         f"builddir = {BUILD}",
@@ -87,7 +106,7 @@ def build_native(verbose: bool = False, ptxas_info: bool = False) -> Path:
         "  depfile = $out.d",
         "  deps = gcc",
         "rule link",
-        "  command = $nvcc -shared -o $out $in -cudart static -lpthread -ldl -lrt -Xlinker -soname=libhccl_b200.so",
+        "  command = $nvcc -shared -o $out $in -cudart static -lpthread -ldl -lrt -Xlinker -soname=" + out.name + (" -Xcompiler -fsanitize=address" if flavor == "asan" else ""),
     ]
     objs = []
     for src in cc + cu:
@@ -156,6 +175,32 @@ def build_all(verbose: bool = False) -> None:
         build_torch_ext(verbose=verbose)
 
 
+def package(dest: Path | None = None) -> Path:
+    """dist/hccl_b200-<version>-sm100a.tar.gz: public headers, the built libraries, the Python package and the samples."""
+    import tarfile
+
+    sys.path.insert(0, str(ROOT))
+    from hccl_b200 import __version__
+
+    dest = dest or ROOT / "dist"
+    dest.mkdir(exist_ok=True)
+    name = f"hccl_b200-{__version__}-sm100a"
+    out = dest / f"{name}.tar.gz"
+    with tarfile.open(out, "w:gz") as tf:
+        for rel in ("include", "hccl_b200", "examples", "README.md"):
+            p = ROOT / rel
+            if p.exists():
+                tf.add(p, arcname=f"{name}/{rel}", filter=lambda ti: None if ("__pycache__" in ti.name or ti.name.endswith("/bin")) else ti)
+    return out
+
+
 if __name__ == "__main__":
-    build_all(verbose="-v" in sys.argv)
-    print("built:", ", ".join(str(p) for p in sorted(LIBDIR.glob("*.so"))))
+    args = sys.argv[1:]
+    flavor = next((a.split("=", 1)[1] for a in args if a.startswith("--flavor=")), "")
+    if flavor:
+        print("built:", build_native(verbose="-v" in args, flavor=flavor))
+    else:
+        build_all(verbose="-v" in args)
+        print("built:", ", ".join(str(p) for p in sorted(LIBDIR.glob("*.so"))))
+    if "--pkg" in args:
+        print("package:", package())

@@ -49,6 +49,8 @@ typedef struct HcclOpResCtxDef {
 /* ---- Part 2: fused operators (bf16; weights are [N, K] row-major, i.e. K contiguous) ---------------------------- */
 /* C[M,N] = A[M,K] * B[N,K]^T on one GPU (the building block; also the N = 1 degenerate case of the fused ops). */
 HcclResult HcclGemmBf16(const void *a, const void *b, void *c, uint64_t m, uint64_t n, uint64_t k, int outFp32, cudaStream_t stream);
+/* variant 0 = automatic, 1 = one-CTA 128 x BN tiles, 2 = 256 x 256 tiles on CTA pairs (tcgen05 cta_group::2) */
+HcclResult HcclGemmBf16Variant(const void *a, const void *b, void *c, uint64_t m, uint64_t n, uint64_t k, int outFp32, int variant, cudaStream_t stream);
 HcclResult HcclGemmCheckError(void);
 
 /* out[nranks*mLocal, n] = AllGather_rows(aLocal[mLocal, k]) * b[n, k]^T. gathered (optional, [nranks*mLocal, k]) receives the

@@ -76,11 +76,11 @@ __device__ __forceinline__ void FusedExit(FusedCtx &x)
 
 // Tile order inside one segment of `rows` row blocks x `nBlocks` column blocks: groups of up to 16 row blocks are walked
 // column by column, so a wave of CTAs touches few distinct A and B panels and both stay in L2.
-__device__ __forceinline__ void SegmentTile(uint32_t rem, uint32_t rows, uint32_t nBlocks, uint32_t *rowBlk, uint32_t *nb)
+__device__ __forceinline__ void SegmentTile(uint32_t rem, uint32_t rows, uint32_t nBlocks, uint32_t *rowBlk, uint32_t *nb, uint32_t group = 16)
 {
-    const uint32_t g = rows < 16 ? rows : 16;
+    const uint32_t g = rows < group ? rows : group;
     const uint32_t perGroup = g * nBlocks;
-    const uint32_t group = rem / perGroup, first = group * g;
+    const uint32_t grp = rem / perGroup, first = grp * g;
     const uint32_t size = rows - first < g ? rows - first : g;
     const uint32_t in = rem % perGroup;
     *rowBlk = first + in % size;

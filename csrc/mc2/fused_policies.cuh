@@ -86,6 +86,16 @@ struct AgmmPolicy {
         SegmentTile(rem, bpr, nBlocks, &blk, nb);
         *mb = src * bpr + blk;
     }
+    // CTA-pair kernel (blocks per rank even): the same source order over pairs of row blocks
+    __device__ static void TileCoordPairs(const GemmParams &p, const Ctx &x, uint32_t t, uint32_t, uint32_t nBlocks, uint32_t *mb2, uint32_t *nb)
+    {
+        const uint32_t ppr = p.u32[2] / 2, perSrc = ppr * nBlocks;
+        uint32_t d = t / perSrc, rem = t % perSrc;
+        uint32_t src = ((uint32_t)x.rank + (uint32_t)x.n - d % (uint32_t)x.n) % (uint32_t)x.n;
+        uint32_t blk2;
+        SegmentTile(rem, ppr, nBlocks, &blk2, nb, 8);
+        *mb2 = src * ppr + blk2;
+    }
     __device__ static bool WaitRowsReady(const GemmParams &p, const Ctx &x, uint32_t mb, volatile uint32_t *abortWord)
     {
         const uint32_t bpr = p.u32[2], src = mb / bpr, blk = mb % bpr;
@@ -169,6 +179,15 @@ struct MmrsPolicy {
         uint32_t blk;
         SegmentTile(rem, bpo, nBlocks, &blk, nb);
         *mb = owner * bpo + blk;
+    }
+    __device__ static void TileCoordPairs(const GemmParams &p, const Ctx &x, uint32_t t, uint32_t, uint32_t nBlocks, uint32_t *mb2, uint32_t *nb)
+    {
+        const uint32_t ppo = p.u32[1] / 2, perOwner = ppo * nBlocks, n = (uint32_t)x.n;
+        uint32_t d = t / perOwner, rem = t % perOwner;
+        uint32_t owner = ((uint32_t)x.rank + 1 + d) % n;
+        uint32_t blk2;
+        SegmentTile(rem, ppo, nBlocks, &blk2, nb, 8);
+        *mb2 = owner * ppo + blk2;
     }
     __device__ static bool WaitRowsReady(const GemmParams &, const Ctx &, uint32_t, volatile uint32_t *) { return true; }
     __device__ static void SelectA(const GemmParams &p, const Ctx &, uint32_t mb, const CUtensorMap **tm, int32_t *row)

@@ -67,6 +67,14 @@ HcclResult GemmCheckError()
     return HCCL_SUCCESS;
 }
 
+// HCCL_GEMM_GROUP_M overrides the rasterisation group (row blocks, or row-block pairs for the CTA-pair kernel) for tuning runs.
+static uint32_t GroupMOverride(uint32_t dflt)
+{
+    static int v = -1;
+    if (v < 0) { const char *e = getenv("HCCL_GEMM_GROUP_M"); v = e ? atoi(e) : 0; }
+    return v > 0 ? (uint32_t)v : dflt;
+}
+
 int SmCount()
 {
     static int n[64] = {0};
@@ -81,7 +89,7 @@ template <int BN> static HcclResult LaunchPlain(const void *a, const void *b, vo
     GemmParams p{};
     CHK_RET(EncodeTmap2D(&p.tmapA, a, M, K, (uint64_t)K * 2, kBM, kBK, 2));
     CHK_RET(EncodeTmap2D(&p.tmapB, b, N, K, (uint64_t)K * 2, BN, kBK, 2));
-    p.C = c; p.M = M; p.N = N; p.K = K; p.ldc = N; p.outFp32 = outFp32; p.groupM = 16; p.errorWord = GemmErrorWord();
+    p.C = c; p.M = M; p.N = N; p.K = K; p.ldc = N; p.outFp32 = outFp32; p.groupM = GroupMOverride(16); p.errorWord = GemmErrorWord();
     using S = GemmSmem<BN>;
     static bool attrSet = false;
     auto kern = GemmKernel<BN, PlainPolicy, false>;
@@ -105,7 +113,7 @@ static HcclResult LaunchPlain2Cta(const void *a, const void *b, void *c, uint32_
     using S = Gemm2CtaSmem;
     CHK_RET(EncodeTmap2D(&p.tmapA, a, M, K, (uint64_t)K * 2, kBM, kBK, 2));
     CHK_RET(EncodeTmap2D(&p.tmapB, b, N, K, (uint64_t)K * 2, S::BN / 2, kBK, 2));
-    p.C = c; p.M = M; p.N = N; p.K = K; p.ldc = N; p.outFp32 = outFp32; p.groupM = 8; p.errorWord = GemmErrorWord();
+    p.C = c; p.M = M; p.N = N; p.K = K; p.ldc = N; p.outFp32 = outFp32; p.groupM = GroupMOverride(8); p.errorWord = GemmErrorWord();
     static bool attrSet = false;
     auto kern = GemmKernel2Cta<PlainPolicy>;
     size_t smem = S::kTotal + 1024;
@@ -133,7 +141,7 @@ static HcclResult LaunchPlain2Cta(const void *a, const void *b, void *c, uint32_
 bool Gemm2CtaEnabled()
 {
     static int v = -1;
-    if (v < 0) { const char *e = getenv("HCCL_GEMM_2CTA"); v = e ? atoi(e) : 0; }
+    if (v < 0) { const char *e = getenv("HCCL_GEMM_2CTA"); v = e ? atoi(e) : 1; }
     return v != 0;
 }
 

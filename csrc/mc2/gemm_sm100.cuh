@@ -106,6 +106,11 @@ struct PlainPolicy {
         *mb = first + in % size;
         *nb = in / size;
     }
+    // CTA-pair kernel: the same order over 256-row block pairs
+    __device__ static void TileCoordPairs(const GemmParams &p, const Ctx &c, uint32_t t, uint32_t mPairs, uint32_t nBlocks, uint32_t *mb2, uint32_t *nb)
+    {
+        TileCoord(p, c, t, mPairs, nBlocks, mb2, nb);
+    }
     __device__ static bool WaitRowsReady(const GemmParams &, const Ctx &, uint32_t, volatile uint32_t *) { return true; }
     __device__ static void SelectA(const GemmParams &p, const Ctx &, uint32_t mb, const CUtensorMap **tm, int32_t *row)
     {

@@ -101,9 +101,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) GemmKernel2Cta(const __grid_c
 
     typename Policy::Ctx ctx;
     Policy::Init(p, ctx);
+    const uint32_t commCtas = Policy::CommCtas(p);          // an even number: whole pairs run the communication role
+    if (blockIdx.x < commCtas) {
+        Policy::CommRole(p, ctx, smem);
+        Policy::Exit(p, ctx);
+        return;
+    }
     const uint32_t rankInPair = cg2::CtaRankInCluster();
     const bool leader = rankInPair == 0;
-    const uint32_t pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    const uint32_t pair = (blockIdx.x - commCtas) >> 1, pairs = (gridDim.x - commCtas) >> 1;
 
     uint8_t *sA = smem;
     uint8_t *sB = smem + STAGES * S::kABytes;
@@ -138,7 +144,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) GemmKernel2Cta(const __grid_c
             bool ok = true;
             for (uint32_t t = pair; t < numTiles && ok; t += pairs) {
                 uint32_t mb2, nb;
-                Policy::TileCoord(p, ctx, t, mPairs, nBlocks, &mb2, &nb);
+                Policy::TileCoordPairs(p, ctx, t, mPairs, nBlocks, &mb2, &nb);
                 const uint32_t mb = mb2 * 2 + rankInPair;
                 const bool valid = mb < mBlocks;
                 const CUtensorMap *ta = &p.tmapA;
@@ -192,7 +198,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) GemmKernel2Cta(const __grid_c
         const uint32_t emptyLeader0 = cg2::MapToCta(SmemAddr(&tmemEmpty[0]), 0), emptyLeader1 = cg2::MapToCta(SmemAddr(&tmemEmpty[1]), 0);
         for (uint32_t t = pair; t < numTiles && ok; t += pairs) {
             uint32_t mb2, nb;
-            Policy::TileCoord(p, ctx, t, mPairs, nBlocks, &mb2, &nb);
+            Policy::TileCoordPairs(p, ctx, t, mPairs, nBlocks, &mb2, &nb);
             const uint32_t mb = mb2 * 2 + rankInPair;
             const bool valid = mb < mBlocks;
             ok = MbarWait(&tmemFull[acc], accPhase, abortWord);
@@ -254,7 +260,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) GemmKernel2Cta(const __grid_c
     TcFenceBefore();
     cg2::ClusterSync();
     if (warp == 2) { TcFenceAfter(); cg2::TmemDealloc2(tmemBase, kTmemCols); }
-    Policy::PostPhase(p, ctx, blockIdx.x, gridDim.x, abortWord);
+    Policy::PostPhase(p, ctx, blockIdx.x - commCtas, gridDim.x - commCtas, abortWord);
     if (threadIdx.x == 0 && *abortWord != 0 && p.errorWord) *p.errorWord = 1;
     Policy::Exit(p, ctx);
 }

@@ -11,6 +11,7 @@
 #include "../exec/op_common.h"
 #include "../kernels/emu_world.h"
 #include "fused_policies.cuh"
+#include "gemm_sm100_2cta.cuh"
 #include "gemm_host.h"
 #include "hccl/hccl_mc2.h"
 
@@ -55,7 +56,20 @@ template <int BN, class Policy, bool EMU> HcclResult SetSmemAttr()
 }
 
 // Fills everything except the DevComm pointer. heapLocal = this rank's heap base as mapped here.
-HcclResult BuildParams(const FusedShape &s, char *heapLocal, uint64_t wsOff, const void *a, const void *b, void *out, uint32_t commCtas, GemmParams *p)
+// The CTA-pair (cta_group::2) kernel serves AllGatherMatmul and MatmulReduceScatter when every rank's rows split into
+// whole 256-row pairs. HCCL_MC2_CTA_PAIR=0 keeps the one-CTA kernels.
+bool PairModeFor(const FusedShape &s)
+{
+    static int enabled = -1;
+    if (enabled < 0) { const char *e = getenv("HCCL_MC2_CTA_PAIR"); enabled = e ? atoi(e) : 1; }
+    if (!enabled || s.N < 256) return false;
+    if (s.kind == AGMM) return (s.m / kBM) % 2 == 0;
+    if (s.kind == MMRS) return (s.m / s.n / kBM) % 2 == 0;
+    return false;
+}
+
+HcclResult BuildParams(const FusedShape &s, char *heapLocal, uint64_t wsOff, const void *a, const void *b, void *out, uint32_t commCtas, GemmParams *p,
+                       bool pairMode = false)
 {
     memset(p, 0, sizeof(*p));
     const uint64_t half = WorkspaceHalfBytes(s);
@@ -67,13 +81,13 @@ HcclResult BuildParams(const FusedShape &s, char *heapLocal, uint64_t wsOff, con
         CHK_RET(EncodeTmap2D(&p->tmapA, heapLocal + wsOff, p->M, s.K, s.K * 2, kBM, kBK, 2));
         CHK_RET(EncodeTmap2D(&p->tmapA1, heapLocal + wsOff + half, p->M, s.K, s.K * 2, kBM, kBK, 2));
         CHK_RET(EncodeTmap2D(&p->tmapALocal, a, s.m, s.K, s.K * 2, kBM, kBK, 2));
-        CHK_RET(EncodeTmap2D(&p->tmapB, b, s.N, s.K, s.K * 2, 256, kBK, 2));
+        CHK_RET(EncodeTmap2D(&p->tmapB, b, s.N, s.K, s.K * 2, pairMode ? 128 : 256, kBK, 2));
         p->u64[0] = wsOff; p->u64[1] = half; p->u64[2] = (uint64_t)(uintptr_t)a;
         p->u32[0] = (uint32_t)s.m; p->u32[1] = commCtas; p->u32[2] = (uint32_t)(s.m / kBM);
     } else if (s.kind == MMRS) {
         p->M = (uint32_t)s.m; p->N = (uint32_t)s.N; p->K = (uint32_t)s.K; p->ldc = (uint32_t)s.N; p->C = out;
         CHK_RET(EncodeTmap2D(&p->tmapA, a, s.m, s.K, s.K * 2, kBM, kBK, 2));
-        CHK_RET(EncodeTmap2D(&p->tmapB, b, s.N, s.K, s.K * 2, 256, kBK, 2));
+        CHK_RET(EncodeTmap2D(&p->tmapB, b, s.N, s.K, s.K * 2, pairMode ? 128 : 256, kBK, 2));
         p->u64[0] = wsOff; p->u64[1] = half;
         p->u32[0] = (uint32_t)(s.m / s.n); p->u32[1] = (uint32_t)(s.m / s.n / kBM); p->u32[2] = (uint32_t)((s.N + 255) / 256);
     } else {
@@ -125,9 +139,36 @@ template <bool EMU> HcclResult LaunchFused(const FusedShape &s, const GemmParams
     return HCCL_SUCCESS;
 }
 
+// CTA-pair kernels: clusters of two CTAs, launched cooperatively (every CTA of the op resident) on an even grid.
+template <class Policy> HcclResult LaunchFusedPair(const GemmParams &p, uint32_t grid, cudaStream_t stream)
+{
+    static bool attrSet = false;
+    auto kern = GemmKernel2Cta<Policy>;
+    const size_t smem = Gemm2CtaSmem::kTotal + 1024;
+    if (!attrSet) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return HCCL_E_RUNTIME;
+        attrSet = true;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid & ~1u);
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeCooperative;
+    attr[1].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
+    if (e != cudaSuccess) { HCCL_ERROR("fused CTA-pair kernel launch failed: %s (grid %u)", cudaGetErrorString(e), grid); (void)cudaGetLastError(); return HCCL_E_RUNTIME; }
+    return HCCL_SUCCESS;
+}
+
 // ---- symmetric workspace per communicator (grown on demand; every rank makes the same calls, so offsets agree)
 struct ParamKey {
-    int kind; const void *a, *b, *out; uint64_t m, N, K, wsOff;
+    int kind; const void *a, *b, *out; uint64_t m, N, K, wsOff;     // kind + 16 = parameters of the CTA-pair kernel
     bool operator<(const ParamKey &o) const { return std::tie(kind, a, b, out, m, N, K, wsOff) < std::tie(o.kind, o.a, o.b, o.out, o.m, o.N, o.K, o.wsOff); }
 };
 // Encoded tensor maps are reused while the same buffers and shapes come back (decode loops, training steps): encoding four
@@ -188,22 +229,31 @@ HcclResult RunFused(FusedKind kind, Comm *c, const void *a, const void *b, void 
     uint64_t wsOff = 0;
     CHK_RET(EnsureWorkspace(c, 2 * WorkspaceHalfBytes(s) + 4096, &wsOff));
     uint32_t commCtas = kind == AGMM ? CommCtasDefault() : 0;
+    const bool pairMode = PairModeFor(s) && commCtas % 2 == 0;
     GemmParams p;
     {
         std::lock_guard<std::mutex> lk(g_wsMu);
         auto &cache = g_ws[c].params;
-        ParamKey key{(int)kind, a, b, out, m, N, K, wsOff};
+        ParamKey key{(int)kind + (pairMode ? 16 : 0), a, b, out, m, N, K, wsOff};
         auto it = cache.find(key);
         if (it != cache.end()) p = it->second;
         else {
-            CHK_RET(BuildParams(s, c->heap[c->rank], wsOff, a, b, out, commCtas, &p));
+            CHK_RET(BuildParams(s, c->heap[c->rank], wsOff, a, b, out, commCtas, &p, pairMode));
             p.comm = c->devCommPtr;
             if (cache.size() > 256) cache.clear();
             cache[key] = p;
         }
     }
-    uint32_t grid = GridFor(s, commCtas, (uint32_t)SmCount());
-    CHK_RET(LaunchFused<false>(s, p, nullptr, grid, 1, stream));
+    if (pairMode) {
+        uint64_t pairTiles = (kind == AGMM ? s.n * s.m / kBM / 2 : s.m / kBM / 2) * ((s.N + 255) / 256);
+        uint32_t grid = (uint32_t)std::min<uint64_t>(pairTiles * 2 + commCtas, (uint64_t)SmCount() & ~1ull);
+        grid = std::max(grid, commCtas + 2);
+        if (kind == AGMM) CHK_RET(LaunchFusedPair<AgmmPolicy>(p, grid, stream));
+        else CHK_RET(LaunchFusedPair<MmrsPolicy>(p, grid, stream));
+    } else {
+        uint32_t grid = GridFor(s, commCtas, (uint32_t)SmCount());
+        CHK_RET(LaunchFused<false>(s, p, nullptr, grid, 1, stream));
+    }
     c->counters.kernelsLaunched++;
     c->counters.ops++;
     if (kind == AGMM && gathered) {

@@ -17,7 +17,8 @@ namespace mc2 {
 // =============================================================================================== AllGather + matmul
 struct AgmmPolicy {
     using Ctx = FusedCtx;
-    // u64: 0 gatherOff (half 0), 1 gatherBytes per half, 2 aLocal   u32: 0 mLocal, 1 commCtas, 2 blocksPerRank
+    // u64: 0 gatherOff (half 0), 1 gatherBytes per half, 2 aLocal
+    // u32: 0 mLocal, 1 commCtas, 2 blocksPerRank, 3 pieces per 128-row block pushed by spare warps (0 = comm CTAs push whole blocks)
     __device__ static void Init(const GemmParams &p, Ctx &x) { FusedInit(p, x); }
     __device__ static uint32_t CommCtas(const GemmParams &p) { return p.u32[1]; }
 
@@ -86,6 +87,41 @@ struct AgmmPolicy {
         SegmentTile(rem, bpr, nBlocks, &blk, nb);
         *mb = src * bpr + blk;
     }
+    // CTA-pair kernel without communication CTAs: warps 2 and 3 of every GEMM CTA push pieces of the local shard to the
+    // peers with plain 16-byte loads / peer stores, nearest consumer first, one counter bump per piece.
+    __device__ static void SpareWarps(const GemmParams &p, Ctx &x, uint32_t which, uint32_t cta, uint32_t ctas, uint32_t lane, volatile uint32_t *)
+    {
+        const uint32_t P = p.u32[3];
+        if (P == 0) return;
+        const uint32_t bpr = p.u32[2], n = (uint32_t)x.n;
+        const uint32_t items = (n - 1) * bpr * P, worker = cta * 2 + which, workers = ctas * 2;
+        const uint64_t rowBytes = (uint64_t)p.K * 2, pieceRows = kBM / P, pieceBytes = pieceRows * rowBytes;
+        const char *aLocal = (const char *)p.u64[2];
+        const uint64_t gatherBase = p.u64[0] + (uint64_t)x.half * p.u64[1];
+        for (uint32_t it = worker; it < items; it += workers) {
+            const uint32_t d = it / (bpr * P) + 1, rem = it % (bpr * P), blk = rem / P, piece = rem % P;
+            const uint32_t peer = ((uint32_t)x.rank + d) % n;
+            const uint64_t rowOff = ((uint64_t)blk * kBM + (uint64_t)piece * pieceRows) * rowBytes;
+            const uint4 *src = (const uint4 *)(aLocal + rowOff);
+            uint4 *dst = (uint4 *)(x.c->heap[peer] + gatherBase + (uint64_t)x.rank * p.u32[0] * rowBytes + rowOff);
+            const uint64_t nvec = pieceBytes >> 4;
+            constexpr int U = 8;
+            uint64_t i = lane;
+            for (; i + 32ull * (U - 1) < nvec; i += 32ull * U) {
+                uint4 v[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u) v[u] = src[i + 32ull * u];
+#pragma unroll
+                for (int u = 0; u < U; ++u) dst[i + 32ull * u] = v[u];
+            }
+            for (; i < nvec; i += 32) dst[i] = src[i];
+            __syncwarp();
+            if (lane == 0) {
+                __threadfence_system();
+                RemoteAddRelease(&FlagsOf(x.c->heap[peer])->mc2Ready[x.half][x.rank][blk], 1u);
+            }
+        }
+    }
     // CTA-pair kernel (blocks per rank even): the same source order over pairs of row blocks
     __device__ static void TileCoordPairs(const GemmParams &p, const Ctx &x, uint32_t t, uint32_t, uint32_t nBlocks, uint32_t *mb2, uint32_t *nb)
     {
@@ -101,7 +137,7 @@ struct AgmmPolicy {
         const uint32_t bpr = p.u32[2], src = mb / bpr, blk = mb % bpr;
         if ((int)src == x.rank) return true;
         Ctx &xm = const_cast<Ctx &>(x);
-        bool ok = WaitCounterGe(xm, &x.flags->mc2Ready[x.half][src][blk], 1u, src, 31, abortWord);
+        bool ok = WaitCounterGe(xm, &x.flags->mc2Ready[x.half][src][blk], p.u32[3] ? p.u32[3] : 1u, src, 31, abortWord);
         asm volatile("fence.proxy.async;" ::: "memory");   // peer's generic/async writes -> this CTA's TMA reads
         return ok;
     }
@@ -180,6 +216,7 @@ struct MmrsPolicy {
         SegmentTile(rem, bpo, nBlocks, &blk, nb);
         *mb = owner * bpo + blk;
     }
+    __device__ static void SpareWarps(const GemmParams &, Ctx &, uint32_t, uint32_t, uint32_t, uint32_t, volatile uint32_t *) {}
     __device__ static void TileCoordPairs(const GemmParams &p, const Ctx &x, uint32_t t, uint32_t, uint32_t nBlocks, uint32_t *mb2, uint32_t *nb)
     {
         const uint32_t ppo = p.u32[1] / 2, perOwner = ppo * nBlocks, n = (uint32_t)x.n;

@@ -107,15 +107,15 @@ template <int BN> static HcclResult LaunchPlain(const void *a, const void *b, vo
 }
 
 // 256 x 256 tiles on CTA pairs (cta_group::2). Needs an even grid; one cluster of two CTAs per tile.
-static HcclResult LaunchPlain2Cta(const void *a, const void *b, void *c, uint32_t M, uint32_t N, uint32_t K, bool outFp32, cudaStream_t s)
+template <int BN> static HcclResult LaunchPlain2CtaT(const void *a, const void *b, void *c, uint32_t M, uint32_t N, uint32_t K, bool outFp32, cudaStream_t s)
 {
     GemmParams p{};
-    using S = Gemm2CtaSmem;
+    using S = Gemm2CtaSmemT<BN>;
     CHK_RET(EncodeTmap2D(&p.tmapA, a, M, K, (uint64_t)K * 2, kBM, kBK, 2));
     CHK_RET(EncodeTmap2D(&p.tmapB, b, N, K, (uint64_t)K * 2, S::BN / 2, kBK, 2));
     p.C = c; p.M = M; p.N = N; p.K = K; p.ldc = N; p.outFp32 = outFp32; p.groupM = GroupMOverride(8); p.errorWord = GemmErrorWord();
     static bool attrSet = false;
-    auto kern = GemmKernel2Cta<PlainPolicy>;
+    auto kern = GemmKernel2Cta<PlainPolicy, BN>;
     size_t smem = S::kTotal + 1024;
     if (!attrSet) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return HCCL_E_RUNTIME;
@@ -136,6 +136,15 @@ static HcclResult LaunchPlain2Cta(const void *a, const void *b, void *c, uint32_
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
     if (e != cudaSuccess) { HCCL_ERROR("2-CTA GEMM launch failed: %s", cudaGetErrorString(e)); (void)cudaGetLastError(); return HCCL_E_RUNTIME; }
     return HCCL_SUCCESS;
+}
+
+static HcclResult LaunchPlain2Cta(const void *a, const void *b, void *c, uint32_t M, uint32_t N, uint32_t K, bool outFp32, cudaStream_t s)
+{
+    // 224-wide tiles when they waste fewer waves (e.g. N = 3584 = 16 x 224 on 74 CTA pairs)
+    const uint64_t rowPairs = (M + 2 * kBM - 1) / (2 * kBM), pairs = (uint64_t)SmCount() / 2;
+    auto cost = [&](uint32_t bn) { uint64_t tiles = rowPairs * ((N + bn - 1) / bn); return ((tiles + pairs - 1) / pairs) * bn; };
+    if (cost(224) < cost(256)) return LaunchPlain2CtaT<224>(a, b, c, M, N, K, outFp32, s);
+    return LaunchPlain2CtaT<256>(a, b, c, M, N, K, outFp32, s);
 }
 
 bool Gemm2CtaEnabled()

@@ -111,6 +111,7 @@ struct PlainPolicy {
     {
         TileCoord(p, c, t, mPairs, nBlocks, mb2, nb);
     }
+    __device__ static void SpareWarps(const GemmParams &, Ctx &, uint32_t, uint32_t, uint32_t, uint32_t, volatile uint32_t *) {}
     __device__ static bool WaitRowsReady(const GemmParams &, const Ctx &, uint32_t, volatile uint32_t *) { return true; }
     __device__ static void SelectA(const GemmParams &p, const Ctx &, uint32_t mb, const CUtensorMap **tm, int32_t *row)
     {

@@ -76,23 +76,24 @@ __device__ __forceinline__ void UmmaCommitPair(uint64_t *bar)
 }
 }  // namespace cg2
 
-struct Gemm2CtaSmem {
-    static constexpr int BN = 256;
+template <int BN_> struct Gemm2CtaSmemT {
+    static constexpr int BN = BN_;                           // 256, or 224 when that wastes fewer tile waves
     static constexpr int kStages = 6;
     static constexpr int kABytes = kBM * kBK * 2;            // 128 rows of A
-    static constexpr int kBBytes = (BN / 2) * kBK * 2;       // this CTA's half of the B tile
+    static constexpr int kBBytes = (BN / 2) * kBK * 2;       // this CTA's half of the B tile (a multiple of the 1 KB swizzle atom)
     static constexpr int kRing = kStages * (kABytes + kBBytes);
-    static constexpr int kStageCols = 64;
+    static constexpr int kStageCols = BN % 64 == 0 ? 64 : 32;
     static constexpr int kStagingOff = kRing;
     static constexpr int kStagingBytes = kBM * kStageCols * 2;
     static constexpr int kBarOff = kRing + kStagingBytes;
     static constexpr int kTotal = kBarOff + 256;
 };
+using Gemm2CtaSmem = Gemm2CtaSmemT<256>;
 
-template <class Policy>
+template <class Policy, int BN_ = 256>
 __global__ void __launch_bounds__(kGemmThreads, 1) GemmKernel2Cta(const __grid_constant__ GemmParams p)
 {
-    using S = Gemm2CtaSmem;
+    using S = Gemm2CtaSmemT<BN_>;
     constexpr int BN = S::BN, STAGES = S::kStages;
     constexpr uint32_t kTmemCols = 512;                                        // two 256-column accumulators
     constexpr uint32_t kIdesc = MakeInstrDesc(FMT_BF16, FMT_BF16, 2 * kBM, BN);
@@ -191,6 +192,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) GemmKernel2Cta(const __grid_c
                 if (acc == 0) accPhase ^= 1;
             }
         }
+    } else if (warp == 2 || warp == 3) {
+        // spare warps: a fused policy may move data with them (AllGatherMatmul pushes the local shard to the peers)
+        Policy::SpareWarps(p, ctx, warp - 2, blockIdx.x - commCtas, gridDim.x - commCtas, lane, abortWord);
     } else if (warp >= 4) {
         const uint32_t ew = warp - 4;
         uint32_t acc = 0, accPhase = 0;
@@ -206,7 +210,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) GemmKernel2Cta(const __grid_c
             TcFenceAfter();
             const uint32_t rowInTile = ew * 32 + lane;
             const uint32_t row = mb * kBM + rowInTile;
-            constexpr uint32_t SC = S::kStageCols, CH = SC / 8;
+            constexpr uint32_t SC = S::kStageCols, CH = SC / 8, kSwz = (CH - 1) & 7;   // bank-conflict swizzle within a staged row
             uint4 *stg = (uint4 *)(smem + S::kStagingOff);
             const uint32_t et = threadIdx.x - 128;
             if (valid && !Policy::EpilogueGate(p, ctx, mb, abortWord)) { ok = false; break; }
@@ -232,7 +236,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) GemmKernel2Cta(const __grid_c
                         __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]));
                         __nv_bfloat162 t3 = __floats2bfloat162_rn(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]));
                         o.x = *(uint32_t *)&t0; o.y = *(uint32_t *)&t1; o.z = *(uint32_t *)&t2; o.w = *(uint32_t *)&t3;
-                        stg[rowInTile * CH + ((c * 4 + q) ^ (rowInTile & 7))] = o;
+                        stg[rowInTile * CH + ((c * 4 + q) ^ (rowInTile & kSwz))] = o;
                     }
                 }
                 if (pass + 1 == BN / SC) {                               // accumulator fully read: hand it back to the leader's MMA thread
@@ -246,7 +250,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) GemmKernel2Cta(const __grid_c
                     for (uint32_t i = et; i < (uint32_t)kBM * CH; i += 128) {
                         const uint32_t r = i / CH, ch = i % CH;
                         __nv_bfloat16 *dst = Policy::RowDst(p, ctx, mb * kBM + r, nb * BN + pass * SC + ch * 8);
-                        if (dst) *(uint4 *)dst = stg[r * CH + (ch ^ (r & 7))];
+                        if (dst) *(uint4 *)dst = stg[r * CH + (ch ^ (r & kSwz))];
                     }
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");

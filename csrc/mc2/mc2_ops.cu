@@ -68,9 +68,17 @@ bool PairModeFor(const FusedShape &s)
     return false;
 }
 
-HcclResult BuildParams(const FusedShape &s, char *heapLocal, uint64_t wsOff, const void *a, const void *b, void *out, uint32_t commCtas, GemmParams *p,
-                       bool pairMode = false)
+// Tile width of the CTA-pair kernels: 256, or 224 when that needs less work-in-waves on `pairs` CTA pairs.
+uint32_t PairTileN(uint64_t rowPairs, uint64_t N, uint32_t pairs)
 {
+    auto cost = [&](uint32_t bn) { uint64_t tiles = rowPairs * ((N + bn - 1) / bn); return ((tiles + pairs - 1) / pairs) * bn; };
+    return cost(224) < cost(256) ? 224u : 256u;
+}
+
+HcclResult BuildParams(const FusedShape &s, char *heapLocal, uint64_t wsOff, const void *a, const void *b, void *out, uint32_t commCtas, GemmParams *p,
+                       uint32_t pairBN = 0)
+{
+    const bool pairMode = pairBN != 0;
     memset(p, 0, sizeof(*p));
     const uint64_t half = WorkspaceHalfBytes(s);
     p->errorWord = GemmErrorWord();
@@ -81,15 +89,17 @@ HcclResult BuildParams(const FusedShape &s, char *heapLocal, uint64_t wsOff, con
         CHK_RET(EncodeTmap2D(&p->tmapA, heapLocal + wsOff, p->M, s.K, s.K * 2, kBM, kBK, 2));
         CHK_RET(EncodeTmap2D(&p->tmapA1, heapLocal + wsOff + half, p->M, s.K, s.K * 2, kBM, kBK, 2));
         CHK_RET(EncodeTmap2D(&p->tmapALocal, a, s.m, s.K, s.K * 2, kBM, kBK, 2));
-        CHK_RET(EncodeTmap2D(&p->tmapB, b, s.N, s.K, s.K * 2, pairMode ? 128 : 256, kBK, 2));
+        CHK_RET(EncodeTmap2D(&p->tmapB, b, s.N, s.K, s.K * 2, pairMode ? pairBN / 2 : 256, kBK, 2));
         p->u64[0] = wsOff; p->u64[1] = half; p->u64[2] = (uint64_t)(uintptr_t)a;
         p->u32[0] = (uint32_t)s.m; p->u32[1] = commCtas; p->u32[2] = (uint32_t)(s.m / kBM);
+        p->u32[3] = pairMode ? 8u : 0u;      // pair kernel: spare warps push the shard in 16-row pieces, no communication CTAs
     } else if (s.kind == MMRS) {
         p->M = (uint32_t)s.m; p->N = (uint32_t)s.N; p->K = (uint32_t)s.K; p->ldc = (uint32_t)s.N; p->C = out;
         CHK_RET(EncodeTmap2D(&p->tmapA, a, s.m, s.K, s.K * 2, kBM, kBK, 2));
-        CHK_RET(EncodeTmap2D(&p->tmapB, b, s.N, s.K, s.K * 2, pairMode ? 128 : 256, kBK, 2));
+        CHK_RET(EncodeTmap2D(&p->tmapB, b, s.N, s.K, s.K * 2, pairMode ? pairBN / 2 : 256, kBK, 2));
         p->u64[0] = wsOff; p->u64[1] = half;
-        p->u32[0] = (uint32_t)(s.m / s.n); p->u32[1] = (uint32_t)(s.m / s.n / kBM); p->u32[2] = (uint32_t)((s.N + 255) / 256);
+        const uint32_t bn = pairMode ? pairBN : 256;
+        p->u32[0] = (uint32_t)(s.m / s.n); p->u32[1] = (uint32_t)(s.m / s.n / kBM); p->u32[2] = (uint32_t)((s.N + bn - 1) / bn);
     } else {
         const uint32_t colsOwn = (uint32_t)(s.N / s.n);
         p->M = (uint32_t)s.m; p->N = (uint32_t)s.N; p->K = (uint32_t)s.K; p->ldc = (uint32_t)s.N; p->C = out;
@@ -140,11 +150,11 @@ template <bool EMU> HcclResult LaunchFused(const FusedShape &s, const GemmParams
 }
 
 // CTA-pair kernels: clusters of two CTAs, launched cooperatively (every CTA of the op resident) on an even grid.
-template <class Policy> HcclResult LaunchFusedPair(const GemmParams &p, uint32_t grid, cudaStream_t stream)
+template <class Policy, int BN> HcclResult LaunchFusedPair(const GemmParams &p, uint32_t grid, cudaStream_t stream)
 {
     static bool attrSet = false;
-    auto kern = GemmKernel2Cta<Policy>;
-    const size_t smem = Gemm2CtaSmem::kTotal + 1024;
+    auto kern = GemmKernel2Cta<Policy, BN>;
+    const size_t smem = Gemm2CtaSmemT<BN>::kTotal + 1024;
     if (!attrSet) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return HCCL_E_RUNTIME;
         attrSet = true;
@@ -228,28 +238,33 @@ HcclResult RunFused(FusedKind kind, Comm *c, const void *a, const void *b, void 
     CHK_RET(CheckShape(s));
     uint64_t wsOff = 0;
     CHK_RET(EnsureWorkspace(c, 2 * WorkspaceHalfBytes(s) + 4096, &wsOff));
-    uint32_t commCtas = kind == AGMM ? CommCtasDefault() : 0;
-    const bool pairMode = PairModeFor(s) && commCtas % 2 == 0;
+    const bool pairMode = PairModeFor(s);
+    uint32_t commCtas = kind == AGMM && !pairMode ? CommCtasDefault() : 0;
+    const uint32_t pairs = (uint32_t)SmCount() / 2;
+    const uint64_t rowPairs = kind == AGMM ? s.n * s.m / kBM / 2 : s.m / kBM / 2;
+    const uint32_t pairBN = pairMode ? PairTileN(rowPairs, s.N, pairs) : 0;
     GemmParams p;
     {
         std::lock_guard<std::mutex> lk(g_wsMu);
         auto &cache = g_ws[c].params;
-        ParamKey key{(int)kind + (pairMode ? 16 : 0), a, b, out, m, N, K, wsOff};
+        ParamKey key{(int)kind + (int)pairBN, a, b, out, m, N, K, wsOff};
         auto it = cache.find(key);
         if (it != cache.end()) p = it->second;
         else {
-            CHK_RET(BuildParams(s, c->heap[c->rank], wsOff, a, b, out, commCtas, &p, pairMode));
+            CHK_RET(BuildParams(s, c->heap[c->rank], wsOff, a, b, out, commCtas, &p, pairBN));
             p.comm = c->devCommPtr;
             if (cache.size() > 256) cache.clear();
             cache[key] = p;
         }
     }
     if (pairMode) {
-        uint64_t pairTiles = (kind == AGMM ? s.n * s.m / kBM / 2 : s.m / kBM / 2) * ((s.N + 255) / 256);
-        uint32_t grid = (uint32_t)std::min<uint64_t>(pairTiles * 2 + commCtas, (uint64_t)SmCount() & ~1ull);
-        grid = std::max(grid, commCtas + 2);
-        if (kind == AGMM) CHK_RET(LaunchFusedPair<AgmmPolicy>(p, grid, stream));
-        else CHK_RET(LaunchFusedPair<MmrsPolicy>(p, grid, stream));
+        uint64_t pairTiles = rowPairs * ((s.N + pairBN - 1) / pairBN);
+        uint32_t grid = (uint32_t)std::min<uint64_t>(pairTiles * 2, (uint64_t)pairs * 2);
+        grid = std::max(grid, 2u);
+        if (kind == AGMM && pairBN == 224) CHK_RET((LaunchFusedPair<AgmmPolicy, 224>(p, grid, stream)));
+        else if (kind == AGMM) CHK_RET((LaunchFusedPair<AgmmPolicy, 256>(p, grid, stream)));
+        else if (pairBN == 224) CHK_RET((LaunchFusedPair<MmrsPolicy, 224>(p, grid, stream)));
+        else CHK_RET((LaunchFusedPair<MmrsPolicy, 256>(p, grid, stream)));
     } else {
         uint32_t grid = GridFor(s, commCtas, (uint32_t)SmCount());
         CHK_RET(LaunchFused<false>(s, p, nullptr, grid, 1, stream));

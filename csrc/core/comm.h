@@ -104,6 +104,7 @@ struct Comm {
     std::unordered_map<std::string, EngineCtxBlob> engineCtx;
     std::unordered_map<std::string, int> stickyFallback;      // algTag -> engine that finally worked
     std::unordered_map<std::string, bool> consistencyDone;    // algTag -> checked
+    std::shared_ptr<void> fastOps;                            // dispatch core: launch lists of repeated calls (op_common.cc)
 
     // DFX
     CommCounters counters;

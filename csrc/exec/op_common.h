@@ -15,6 +15,8 @@ HcclResult CheckOpConsistency(Comm *c, const OpParam &p);
 HcclResult CompareOpExchangeInfos(const std::vector<OpExchangeInfo> &all, uint32_t myRank, std::string *why);
 void FillOpExchangeInfo(Comm *c, const OpParam &p, OpExchangeInfo *info);
 bool StreamIsCapturing(cudaStream_t s);
+// Invalidates every cached launch list (tuning table or algorithm configuration changed).
+void BumpSelectionGeneration();
 HcclResult LocalCopyAsync(Comm *c, void *dst, const void *src, uint64_t bytes, cudaStream_t s);
 
 }  // namespace hccl

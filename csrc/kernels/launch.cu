@@ -11,7 +11,7 @@
 
 namespace hccl {
 
-HcclResult SmIssueLaunch(const DevComm *devComm, const SmLaunch &l, cudaStream_t stream);
+thread_local std::vector<SmLaunch> *g_captureLaunches = nullptr;
 HcclResult SmIssueEmuLaunch(const DevComm *devComms, int nranks, const SmLaunch &l0, const CollArgs *devArgs, const BatchArgs *devBatch,
                             cudaStream_t stream, bool pairKernel);
 
@@ -60,6 +60,7 @@ HcclResult SmOrchestrate(Comm *c, OpParam &p, const std::string &algName)
         c->counters.kernelsLaunched++;
         c->counters.chunkLoops++;
     }
+    if (g_captureLaunches) *g_captureLaunches = std::move(launches);
     return HCCL_SUCCESS;
 }
 

@@ -19,6 +19,12 @@ const std::vector<SmAlgoDesc> &SmAlgorithms();
 
 // Runs the whole operator (chunk loop inside) with the named SM / NVLS algorithm.
 HcclResult SmOrchestrate(Comm *c, OpParam &p, const std::string &algName);
+// Issues one planned launch on `stream` (used by the dispatch core to replay a cached launch list).
+struct SmLaunch;
+struct DevComm;
+HcclResult SmIssueLaunch(const DevComm *devComm, const SmLaunch &l, cudaStream_t stream);
+// While non-null on the calling thread, SmOrchestrate copies the launch list it issued here.
+extern thread_local std::vector<SmLaunch> *g_captureLaunches;
 // Grid size the engine would use (selector hint / graph-mode resource query).
 uint32_t SmDefaultCtas(HcclCMDType op, const std::string &algName, uint64_t bytes, uint32_t nranks);
 

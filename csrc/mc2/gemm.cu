@@ -143,7 +143,9 @@ static HcclResult LaunchPlain2Cta(const void *a, const void *b, void *c, uint32_
     // 224-wide tiles when they waste fewer waves (e.g. N = 3584 = 16 x 224 on 74 CTA pairs)
     const uint64_t rowPairs = (M + 2 * kBM - 1) / (2 * kBM), pairs = (uint64_t)SmCount() / 2;
     auto cost = [&](uint32_t bn) { uint64_t tiles = rowPairs * ((N + bn - 1) / bn); return ((tiles + pairs - 1) / pairs) * bn; };
-    if (cost(224) < cost(256)) return LaunchPlain2CtaT<224>(a, b, c, M, N, K, outFp32, s);
+    static int level = -1;
+    if (level < 0) { const char *e = getenv("HCCL_MC2_CTA_PAIR"); level = e ? atoi(e) : 1; }
+    if (level >= 2 && cost(224) < cost(256)) return LaunchPlain2CtaT<224>(a, b, c, M, N, K, outFp32, s);
     return LaunchPlain2CtaT<256>(a, b, c, M, N, K, outFp32, s);
 }
 

@@ -58,12 +58,19 @@ template <int BN, class Policy, bool EMU> HcclResult SetSmemAttr()
 // Fills everything except the DevComm pointer. heapLocal = this rank's heap base as mapped here.
 // The CTA-pair (cta_group::2) kernel serves AllGatherMatmul and MatmulReduceScatter when every rank's rows split into
 // whole 256-row pairs. HCCL_MC2_CTA_PAIR=0 keeps the one-CTA kernels.
+// HCCL_MC2_CTA_PAIR: 0 = one-CTA kernels only; 1 = MatmulReduceScatter on CTA pairs with 256-wide tiles;
+// 2 = also AllGatherMatmul on CTA pairs (spare warps push the shard) and 224-wide tiles where they waste fewer waves.
+int PairLevel()
+{
+    static int level = -1;
+    if (level < 0) { const char *e = getenv("HCCL_MC2_CTA_PAIR"); level = e ? atoi(e) : 1; }
+    return level;
+}
+
 bool PairModeFor(const FusedShape &s)
 {
-    static int enabled = -1;
-    if (enabled < 0) { const char *e = getenv("HCCL_MC2_CTA_PAIR"); enabled = e ? atoi(e) : 1; }
-    if (!enabled || s.N < 256) return false;
-    if (s.kind == AGMM) return (s.m / kBM) % 2 == 0;
+    if (PairLevel() <= 0 || s.N < 256) return false;
+    if (s.kind == AGMM) return PairLevel() >= 2 && (s.m / kBM) % 2 == 0;
     if (s.kind == MMRS) return (s.m / s.n / kBM) % 2 == 0;
     return false;
 }
@@ -72,7 +79,7 @@ bool PairModeFor(const FusedShape &s)
 uint32_t PairTileN(uint64_t rowPairs, uint64_t N, uint32_t pairs)
 {
     auto cost = [&](uint32_t bn) { uint64_t tiles = rowPairs * ((N + bn - 1) / bn); return ((tiles + pairs - 1) / pairs) * bn; };
-    return cost(224) < cost(256) ? 224u : 256u;
+    return PairLevel() >= 2 && cost(224) < cost(256) ? 224u : 256u;
 }
 
 HcclResult BuildParams(const FusedShape &s, char *heapLocal, uint64_t wsOff, const void *a, const void *b, void *out, uint32_t commCtas, GemmParams *p,

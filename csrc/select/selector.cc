@@ -1,4 +1,5 @@
 #include "selector.h"
+#include "../exec/op_common.h"
 #include <algorithm>
 #include <fstream>
 #include <sstream>
@@ -61,6 +62,7 @@ void TuningTable::Set(HcclCMDType op, uint32_t nranks, HcclCommEngine engine, st
 {
     std::sort(rows.begin(), rows.end(), [](const TuningRow &a, const TuningRow &b) { return a.maxBytes < b.maxBytes; });
     rows_[Key{op, nranks, engine}] = std::move(rows);
+    BumpSelectionGeneration();
 }
 
 const TuningRow *TuningTable::Lookup(HcclCMDType op, uint32_t nranks, HcclCommEngine engine, uint64_t bytes) const

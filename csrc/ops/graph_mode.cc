@@ -71,8 +71,9 @@ HcclResult CalcRes(Comm *c, uint32_t nranks, uint64_t cclBytes, bool nvls, const
     if (c) {
         CHK_RET(SelectAlgorithm(c, p, {}));
     } else {
-        // offline: the CUDA cascade without a communicator (NVLS assumed absent)
-        static AlgEnvConfig env;
+        // offline: the CUDA cascade without a communicator, under the current environment; an NVSwitch multicast mapping
+        // is assumed to exist unless HCCL_NVLS_ENABLE=0 (the target is an 8 x B200 NVSwitch box)
+        const AlgEnvConfig &env = GetEnvConfig();
         TopoInfo topo;
         CHK_RET(BuildSimTopoInfo(1, 1, nranks, 0, &topo));
         SelectorCtx ctx{nullptr, &topo, &env, true, nvls, cclBytes, {}};
@@ -269,7 +270,7 @@ HcclResult HcclCalcOpResOfflineGraphMode(HcclOpParamGraphMode param, uint32_t ra
     if (!g || !res) return HCCL_E_PTR;
     if (rankSize < 2 || rankSize > (uint32_t)kMaxRanks) return HCCL_E_PARA;
     InitEnvConfig();
-    return Guard("HcclCalcOpResOfflineGraphMode", [&] { return CalcRes(nullptr, rankSize, GetEnvConfig().bufferSizeBytes, false, *g, res); });
+    return Guard("HcclCalcOpResOfflineGraphMode", [&] { return CalcRes(nullptr, rankSize, GetEnvConfig().bufferSizeBytes, GetEnvConfig().nvlsEnable, *g, res); });
 }
 HcclResult HcclCalcOpResOnlineGraphMode(HcclComm comm, HcclOpParamGraphMode param, HcclOpResGraphMode *res)
 {

@@ -51,7 +51,8 @@ typedef struct HcclOpResGraphModeDef {
     uint32_t engine;
 } HcclOpResGraphMode;
 
-/* Without a communicator: estimate for `rankSize` ranks with the default buffer size and the CUDA engine cascade. */
+/* Without a communicator: estimate for `rankSize` ranks on an NVSwitch box under the current environment (buffer size, engine
+ * and algorithm overrides; NVLS assumed unless HCCL_NVLS_ENABLE=0). */
 HcclResult HcclCalcOpResOfflineGraphMode(HcclOpParamGraphMode param, uint32_t rankSize, HcclOpResGraphMode *res);
 /* With the communicator named by the param's group (or `comm` if non-NULL): what would actually run. */
 HcclResult HcclCalcOpResOnlineGraphMode(HcclComm comm, HcclOpParamGraphMode param, HcclOpResGraphMode *res);

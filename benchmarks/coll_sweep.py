@@ -23,6 +23,23 @@ DT = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16}
 HOST_US = {}
 
 
+def native_host_us(comm):
+    """Mean time the last 16 calls spent inside the native library (entry to return), from the communicator's op ring."""
+    import ctypes
+
+    from hccl_b200._lib import lib
+
+    class Rec(ctypes.Structure):
+        _fields_ = [("seq", ctypes.c_uint64), ("opType", ctypes.c_uint32), ("dataType", ctypes.c_uint32), ("reduceOp", ctypes.c_uint32),
+                    ("root", ctypes.c_uint32), ("engine", ctypes.c_uint32), ("pad", ctypes.c_uint32), ("count", ctypes.c_uint64),
+                    ("algName", ctypes.c_char * 64), ("beginNs", ctypes.c_uint64), ("endNs", ctypes.c_uint64)]
+    recs = (Rec * 16)()
+    n = ctypes.c_uint32()
+    if lib().HcclGetLastOps(ctypes.c_void_p(comm.handle), recs, 16, ctypes.byref(n)) != 0 or n.value == 0:
+        return float("nan"), ""
+    return sum(recs[i].endNs - recs[i].beginNs for i in range(n.value)) / n.value / 1e3, recs[n.value - 1].algName.decode()
+
+
 def time_fn(fn, iters, warmup, tag=None):
     import time
     for _ in range(warmup):
@@ -101,14 +118,15 @@ def main():
                 else:
                     raise SystemExit(f"unknown op {op}")
                 t_ours = time_fn(ours, iters, warm, tag="ours")
+                nat_us, alg_used = native_host_us(comm)
                 t_ref = float("nan") if args.skip_nccl else time_fn(ref, iters, warm)
                 bus_ours = size * factor / t_ours / 1e9
                 bus_ref = size * factor / t_ref / 1e9
                 rows.append(dict(op=op, dtype=dname, bytes=size, ranks=n, ours_us=t_ours * 1e6, nccl_us=t_ref * 1e6, ours_busGBs=bus_ours,
-                                 nccl_busGBs=bus_ref, ratio=bus_ours / bus_ref if bus_ref == bus_ref else None, ours_host_issue_us=HOST_US.get("ours")))
+                                 nccl_busGBs=bus_ref, ratio=bus_ours / bus_ref if bus_ref == bus_ref else None, ours_host_issue_us=HOST_US.get("ours"), ours_native_us=nat_us, alg=alg_used))
                 if rank == 0:
                     print(f"{op:13s} {dname:5s} {size:>11d} B  ours {t_ours*1e6:9.1f} us {bus_ours:8.1f} GB/s | nccl {t_ref*1e6:9.1f} us {bus_ref:8.1f} GB/s"
-                          f" | x{bus_ours / bus_ref if bus_ref == bus_ref else float('nan'):.2f} | host {HOST_US.get('ours', 0):.1f} us", flush=True)
+                          f" | x{bus_ours / bus_ref if bus_ref == bus_ref else float('nan'):.2f} | host {HOST_US.get('ours', 0):.1f} us (native {nat_us:.1f}) {alg_used}", flush=True)
                 del x
                 size *= 4 if size >= (1 << 22) and args.max_bytes > (1 << 28) else 2
                 idx += 1

@@ -25,11 +25,19 @@ def _root_from_bytes(b: bytes) -> HcclRootInfo:
     return info
 
 
+_TORCH_TENSOR = None
+
+
 def _describe(buf):
     """-> (pointer, numel, DataType, is_cuda)"""
+    global _TORCH_TENSOR
     if buf is None:
         return None, 0, DataType.INT8, False
-    if hasattr(buf, "data_ptr"):  # torch tensor
+    if _TORCH_TENSOR is None:
+        import torch
+
+        _TORCH_TENSOR = torch.Tensor
+    if isinstance(buf, _TORCH_TENSOR):
         if not buf.is_contiguous():
             raise ValueError("tensor must be contiguous")
         return buf.data_ptr(), buf.numel(), from_torch(buf.dtype), buf.is_cuda
@@ -38,6 +46,33 @@ def _describe(buf):
             raise ValueError("array must be C-contiguous")
         return buf.ctypes.data, buf.size, from_numpy(buf.dtype), False
     raise TypeError(f"unsupported buffer type {type(buf)}")
+
+
+_FN = {}
+
+
+def _LIBFN(name):
+    fn = _FN.get(name)
+    if fn is None:
+        fn = _FN[name] = getattr(lib(), name)
+    return fn
+
+
+_CUR_STREAM = None
+
+
+def _current_stream_ptr() -> int:
+    """Raw handle of torch's current CUDA stream without constructing a Stream object."""
+    global _CUR_STREAM
+    if _CUR_STREAM is None:
+        import torch
+
+        raw = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+        if raw is not None:
+            _CUR_STREAM = lambda: raw(torch.cuda.current_device())
+        else:
+            _CUR_STREAM = lambda: torch.cuda.current_stream().cuda_stream
+    return _CUR_STREAM()
 
 
 def _u64_array(vals: Sequence[int]):
@@ -116,14 +151,12 @@ class Communicator:
         check(lib().HcclGetCommName(self._h, buf), "HcclGetCommName")
         return buf.value.decode()
 
-    def _stream(self, is_cuda: bool, stream) -> ctypes.c_void_p:
+    def _stream(self, is_cuda: bool, stream):
         if not is_cuda:
-            return ctypes.c_void_p(0)
+            return None
         if stream is None:
-            import torch
-
-            stream = torch.cuda.current_stream()
-        return ctypes.c_void_p(getattr(stream, "cuda_stream", stream))
+            return _current_stream_ptr()
+        return getattr(stream, "cuda_stream", stream)
 
     def synchronize(self) -> None:
         check(lib().HcclSimStreamSynchronize(self._h), "HcclSimStreamSynchronize")
@@ -146,10 +179,11 @@ class Communicator:
 
     # ---- collectives ----------------------------------------------------------------------------------------
     def all_reduce(self, send, recv=None, op: ReduceOp = ReduceOp.SUM, stream=None) -> None:
-        recv = send if recv is None else recv
         sp, n, dt, cu = _describe(send)
-        rp, _, _, _ = _describe(recv)
-        check(lib().HcclAllReduce(sp, rp, n, dt, int(op), self._h, self._stream(cu, stream)), "HcclAllReduce")
+        rp = sp if recv is None or recv is send else _describe(recv)[0]
+        rc = _LIBFN("HcclAllReduce")(sp, rp, n, dt, int(op), self._h, self._stream(cu, stream))
+        if rc:
+            check(rc, "HcclAllReduce")
 
     def broadcast(self, buf, root: int, stream=None) -> None:
         p, n, dt, cu = _describe(buf)

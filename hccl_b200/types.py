@@ -63,7 +63,17 @@ def from_numpy(dt) -> DataType:
     return _NP[str(dt)]
 
 
+_TORCH = None
+
+
 def from_torch(dt) -> DataType:
+    global _TORCH
+    if _TORCH is None:
+        _TORCH = _torch_table()
+    return _TORCH[dt]
+
+
+def _torch_table():
     import torch
 
     table = {torch.int8: DataType.INT8, torch.int16: DataType.INT16, torch.int32: DataType.INT32,
@@ -75,7 +85,7 @@ def from_torch(dt) -> DataType:
                     ("float8_e8m0fnu", DataType.FP8E8M0)):
         if hasattr(torch, name):
             table[getattr(torch, name)] = v
-    return table[dt]
+    return {k: int(v) for k, v in table.items()}
 
 
 def reduce_op_from_torch(op) -> ReduceOp:

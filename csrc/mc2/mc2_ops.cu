@@ -58,8 +58,10 @@ template <int BN, class Policy, bool EMU> HcclResult SetSmemAttr()
 // Fills everything except the DevComm pointer. heapLocal = this rank's heap base as mapped here.
 // The CTA-pair (cta_group::2) kernel serves AllGatherMatmul and MatmulReduceScatter when every rank's rows split into
 // whole 256-row pairs. HCCL_MC2_CTA_PAIR=0 keeps the one-CTA kernels.
-// HCCL_MC2_CTA_PAIR: 0 = one-CTA kernels only; 1 = MatmulReduceScatter on CTA pairs with 256-wide tiles;
-// 2 = also AllGatherMatmul on CTA pairs (spare warps push the shard) and 224-wide tiles where they waste fewer waves.
+// HCCL_MC2_CTA_PAIR: 0 = one-CTA kernels only; 1 (default) = AllGatherMatmul and MatmulReduceScatter on CTA pairs with
+// 256-wide tiles (AllGatherMatmul keeps its communication CTAs); 2 = also 224-wide tiles where they waste fewer waves;
+// 3 = AllGatherMatmul without communication CTAs, warps 2 and 3 of every GEMM CTA push the shard (measured slower at 2 GPUs:
+// the pushes of all CTAs contend with the operand loads during the first hundred microseconds).
 int PairLevel()
 {
     static int level = -1;
@@ -70,7 +72,7 @@ int PairLevel()
 bool PairModeFor(const FusedShape &s)
 {
     if (PairLevel() <= 0 || s.N < 256) return false;
-    if (s.kind == AGMM) return PairLevel() >= 2 && (s.m / kBM) % 2 == 0;
+    if (s.kind == AGMM) return (s.m / kBM) % 2 == 0;
     if (s.kind == MMRS) return (s.m / s.n / kBM) % 2 == 0;
     return false;
 }
@@ -99,7 +101,7 @@ HcclResult BuildParams(const FusedShape &s, char *heapLocal, uint64_t wsOff, con
         CHK_RET(EncodeTmap2D(&p->tmapB, b, s.N, s.K, s.K * 2, pairMode ? pairBN / 2 : 256, kBK, 2));
         p->u64[0] = wsOff; p->u64[1] = half; p->u64[2] = (uint64_t)(uintptr_t)a;
         p->u32[0] = (uint32_t)s.m; p->u32[1] = commCtas; p->u32[2] = (uint32_t)(s.m / kBM);
-        p->u32[3] = pairMode ? 8u : 0u;      // pair kernel: spare warps push the shard in 16-row pieces, no communication CTAs
+        p->u32[3] = pairMode && commCtas == 0 ? 8u : 0u;   // no communication CTAs: spare warps push the shard in 16-row pieces
     } else if (s.kind == MMRS) {
         p->M = (uint32_t)s.m; p->N = (uint32_t)s.N; p->K = (uint32_t)s.K; p->ldc = (uint32_t)s.N; p->C = out;
         CHK_RET(EncodeTmap2D(&p->tmapA, a, s.m, s.K, s.K * 2, kBM, kBK, 2));
@@ -246,8 +248,9 @@ HcclResult RunFused(FusedKind kind, Comm *c, const void *a, const void *b, void 
     uint64_t wsOff = 0;
     CHK_RET(EnsureWorkspace(c, 2 * WorkspaceHalfBytes(s) + 4096, &wsOff));
     const bool pairMode = PairModeFor(s);
-    uint32_t commCtas = kind == AGMM && !pairMode ? CommCtasDefault() : 0;
-    const uint32_t pairs = (uint32_t)SmCount() / 2;
+    uint32_t commCtas = kind == AGMM && !(pairMode && PairLevel() >= 3) ? CommCtasDefault() : 0;
+    if (pairMode) commCtas &= ~1u;                       // whole CTA pairs take the communication role
+    const uint32_t pairs = ((uint32_t)SmCount() - commCtas) / 2;
     const uint64_t rowPairs = kind == AGMM ? s.n * s.m / kBM / 2 : s.m / kBM / 2;
     const uint32_t pairBN = pairMode ? PairTileN(rowPairs, s.N, pairs) : 0;
     GemmParams p;
@@ -266,8 +269,8 @@ HcclResult RunFused(FusedKind kind, Comm *c, const void *a, const void *b, void 
     }
     if (pairMode) {
         uint64_t pairTiles = rowPairs * ((s.N + pairBN - 1) / pairBN);
-        uint32_t grid = (uint32_t)std::min<uint64_t>(pairTiles * 2, (uint64_t)pairs * 2);
-        grid = std::max(grid, 2u);
+        uint32_t grid = (uint32_t)std::min<uint64_t>(pairTiles * 2, (uint64_t)pairs * 2) + commCtas;
+        grid = std::max(grid, commCtas + 2u);
         if (kind == AGMM && pairBN == 224) CHK_RET((LaunchFusedPair<AgmmPolicy, 224>(p, grid, stream)));
         else if (kind == AGMM) CHK_RET((LaunchFusedPair<AgmmPolicy, 256>(p, grid, stream)));
         else if (pairBN == 224) CHK_RET((LaunchFusedPair<MmrsPolicy, 224>(p, grid, stream)));

@@ -1,3 +1,4 @@
+#include <cstdlib>
 #include "param_check.h"
 #include <cstring>
 #include "dtype.h"
@@ -24,8 +25,19 @@ HcclResult HcomCheckDataType(HcclDataType t)
     return HCCL_SUCCESS;
 }
 
+// HCCL_STRICT_DTYPE_RULES=1 reproduces the reference's operand rules exactly (no unsigned 8/16/32-bit reductions, PROD
+// only for int8/int32/int64/uint64/fp16/fp32/fp64; reference: src/ops/op_common/op_common.cc:2038-2050,2091-2107). By
+// default this library accepts the superset its kernels implement.
+static bool StrictRules()
+{
+    static int v = -1;
+    if (v < 0) { const char *e = getenv("HCCL_STRICT_DTYPE_RULES"); v = (e && *e && *e != '0') ? 1 : 0; }
+    return v == 1;
+}
+
 bool IsReduceDataTypeSupported(HcclDataType t)
 {
+    if (StrictRules() && (t == HCCL_DATA_TYPE_UINT8 || t == HCCL_DATA_TYPE_UINT16 || t == HCCL_DATA_TYPE_UINT32)) return false;
     switch (t) {
         case HCCL_DATA_TYPE_INT8: case HCCL_DATA_TYPE_INT16: case HCCL_DATA_TYPE_INT32: case HCCL_DATA_TYPE_INT64:
         case HCCL_DATA_TYPE_UINT64: case HCCL_DATA_TYPE_FP16: case HCCL_DATA_TYPE_FP32: case HCCL_DATA_TYPE_FP64:
@@ -37,6 +49,7 @@ bool IsReduceDataTypeSupported(HcclDataType t)
 bool IsProdDataTypeSupported(HcclDataType t)
 {
     // every reducible type multiplies here (the reference excludes int16 and bf16: an engine limit this hardware lacks)
+    if (StrictRules() && (t == HCCL_DATA_TYPE_INT16 || t == HCCL_DATA_TYPE_BFP16)) return false;
     return IsReduceDataTypeSupported(t);
 }
 

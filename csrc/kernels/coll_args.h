@@ -33,6 +33,7 @@ enum SmKernelId : uint32_t {
     K_REDUCESCATTER_PIPE_NVLS,
     K_ALLGATHER_PIPE,         // also AllGatherV
     K_ALLGATHER_PIPE_NVLS,
+    K_ALLTOALL_PIPE,          // AlltoAll with uniform counts
     K_COUNT
 };
 

@@ -322,6 +322,7 @@ template <typename T, int OP, bool EMU> __device__ void ReduceScatterPipePlainBo
 template <typename T, int OP, bool EMU> __device__ void ReduceScatterPipeNvlsBody(KCtx &k, const CollArgs &A) { pipe::ReduceScatterBody<T, OP, EMU, true>(k, A); }
 template <bool EMU> __device__ void AllGatherPipePlainBody(KCtx &k, const CollArgs &A) { pipe::AllGatherBody<EMU, false>(k, A); }
 template <bool EMU> __device__ void AllGatherPipeNvlsBody(KCtx &k, const CollArgs &A) { pipe::AllGatherBody<EMU, true>(k, A); }
+template <bool EMU> __device__ void AlltoAllPipeBody(KCtx &k, const CollArgs &A) { pipe::AllGatherBody<EMU, false, true>(k, A); }
 COLL_KERNEL_TYPED(KAllReducePipe, AllReducePipePlainBody)
 COLL_KERNEL_TYPED(KReduceScatterPipe, ReduceScatterPipePlainBody)
 
@@ -354,6 +355,7 @@ COLL_KERNEL_BYTES(KScatter, ScatterBody)
 COLL_KERNEL_BYTES(KAlltoAllV, AlltoAllVBody)
 COLL_KERNEL_BYTES(KAllGatherPipe, AllGatherPipePlainBody)
 COLL_KERNEL_BYTES(KAllGatherPipeNvls, AllGatherPipeNvlsBody)
+COLL_KERNEL_BYTES(KAlltoAllPipe, AlltoAllPipeBody)
 
 template <bool EMU> __global__ void __launch_bounds__(kThreads) KBarrier(const DevComm *comms, const __grid_constant__ CollArgs a, const CollArgs *)
 {
@@ -558,6 +560,7 @@ template <bool EMU> CollKernelFn KernelFor(const SmLaunch &l)
             return NvlsKernel<EMU>(l.kernel, l.dtype, (HcclReduceOp)l.args.op);
         case K_ALLGATHER_PIPE: return KAllGatherPipe<EMU>;
         case K_ALLGATHER_PIPE_NVLS: return KAllGatherPipeNvls<EMU>;
+        case K_ALLTOALL_PIPE: return KAlltoAllPipe<EMU>;
         case K_ALLGATHER_V: return KAllGatherV<EMU>;
         case K_BROADCAST: return KBroadcast<EMU>;
         case K_BROADCAST_NVLS: return KBroadcastNvls<EMU>;

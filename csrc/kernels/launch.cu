@@ -32,6 +32,8 @@ const std::vector<SmAlgoDesc> &SmAlgorithms()
         {"NvlsReduceScatterPipelined", HCCL_CMD_REDUCE_SCATTER, true},
         {"SmAllGatherPush", HCCL_CMD_ALLGATHER, false}, {"SmAllGatherVPush", HCCL_CMD_ALLGATHER_V, false},
         {"NvlsAllGatherPush", HCCL_CMD_ALLGATHER, true}, {"NvlsAllGatherVPush", HCCL_CMD_ALLGATHER_V, true},
+        {"SmBroadcastPush", HCCL_CMD_BROADCAST, false}, {"NvlsBroadcastPush", HCCL_CMD_BROADCAST, true},
+        {"SmAlltoAllPush", HCCL_CMD_ALLTOALL, false},
         {"SmSend", HCCL_CMD_SEND, false}, {"SmRecv", HCCL_CMD_RECEIVE, false}, {"SmBatchSendRecv", HCCL_CMD_BATCH_SEND_RECV, false},
     };
     return v;

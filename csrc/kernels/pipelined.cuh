@@ -322,7 +322,10 @@ template <typename T, int OP, bool EMU, bool NVLS> __device__ void ReduceScatter
 // ---------------------------------------------------------------------------------------------- AllGather(V)
 // No input staging: the movers read the user buffer and push sub-chunk c into slot (d, rank) of every rank's ring
 // (one multimem.st through the switch, or one plain store per peer); the drainers copy all n slots out.
-template <bool EMU, bool NVLS> __device__ void AllGatherBody(KCtx &k, const CollArgs &A)
+//
+// A2A = true turns the same pipeline into AlltoAll: the piece pushed to rank q is block q of the send buffer
+// (sendOff[q], sendBytes[q]) instead of one piece for everybody, always with plain peer stores.
+template <bool EMU, bool NVLS, bool A2A = false> __device__ void AllGatherBody(KCtx &k, const CollArgs &A)
 {
     __shared__ int sFail;
     const int n = k.nranks;
@@ -338,6 +341,15 @@ template <bool EMU, bool NVLS> __device__ void AllGatherBody(KCtx &k, const Coll
         for (uint32_t c = 0; c < g.chunks; ++c) {
             const int d = c % kDepth;
             if (c >= (uint32_t)kDepth && !Wait(k, r, DRAINED, g.base + c - kDepth + 1, &sFail)) break;
+            if constexpr (A2A) {
+                for (int q = 0; q < n; ++q) {
+                    const int dstRank = (k.rank + q) % n;
+                    Part ps = PartOf(A.sendBytes[dstRank], gridDim.x, blockIdx.x);
+                    Copy(k.Ccl(dstRank) + g.Slot(d, k.rank), (const char *)A.in + A.sendOff[dstRank] + ps.off + (uint64_t)c * g.sub, SubLen(ps.len, g.sub, c), r);
+                }
+                Signal(k, r, MOVED, g.base + c + 1);
+                continue;
+            }
             const uint64_t len = SubLen(p.len, g.sub, c);
             const char *src = (const char *)A.in + p.off + (uint64_t)c * g.sub;
             const uint64_t slot = g.Slot(d, k.rank);
@@ -396,7 +408,7 @@ template <bool EMU, bool NVLS> __device__ void AllGatherBody(KCtx &k, const Coll
         }
     } else {                                                    // ---- drainers
         Role r{(int)threadIdx.x - 192, 320, 2};
-        const bool inPlace = (const char *)A.in == (const char *)A.out + A.recvOff[k.rank];
+        const bool inPlace = !A2A && (const char *)A.in == (const char *)A.out + A.recvOff[k.rank];
         for (uint32_t c = 0; c < g.chunks; ++c) {
             const int d = c % kDepth;
             if (!Wait(k, r, MOVED, g.base + c + 1, &sFail)) break;

@@ -130,6 +130,35 @@ HcclResult SmPlanOp(const SmPlanCtx &ctx, const OpParam &p, const std::string &a
         out->push_back(l);
         return HCCL_SUCCESS;
     }
+    // Broadcast as a one-contributor push: only the root owns a (non-empty) piece, everybody drains slot `root`.
+    if (alg == "SmBroadcastPush" || alg == "NvlsBroadcastPush") {
+        bool nv = alg[0] == 'N';
+        if (nv && !ctx.nvls) return HCCL_E_NOT_SUPPORT;
+        SmLaunch l = base;
+        l.kernel = nv ? K_ALLGATHER_PIPE_NVLS : K_ALLGATHER_PIPE;
+        l.args.in = outp; l.args.out = outp;
+        for (uint32_t r = 0; r < n; ++r) { l.args.recvBytes[r] = r == p.root ? p.count * es : 0; l.args.recvOff[r] = 0; }
+        if (me != p.root) l.args.in = nullptr;
+        l.ctas = pipeCtas(p.count * es);
+        l.args.pipeSub = pipeSub(1, l.ctas);
+        if (l.args.pipeSub < 128) return HCCL_E_NOT_SUPPORT;
+        out->push_back(l);
+        return HCCL_SUCCESS;
+    }
+    if (alg == "SmAlltoAllPush") {
+        SmLaunch l = base;
+        l.kernel = K_ALLTOALL_PIPE;
+        l.args.in = in; l.args.out = outp;
+        for (uint32_t r = 0; r < n; ++r) {
+            l.args.sendBytes[r] = l.args.recvBytes[r] = p.count * es;
+            l.args.sendOff[r] = l.args.recvOff[r] = (uint64_t)r * p.count * es;
+        }
+        l.ctas = pipeCtas(p.count * es * (n - 1));
+        l.args.pipeSub = pipeSub(1, l.ctas);
+        if (l.args.pipeSub < 128) return HCCL_E_NOT_SUPPORT;
+        out->push_back(l);
+        return HCCL_SUCCESS;
+    }
     if (alg == "SmAllGatherMesh1D" || alg == "SmAllGatherVMesh1D") {
         bool v = p.opType == HCCL_CMD_ALLGATHER_V;
         uint64_t total = v ? *std::max_element(p.recvCounts.begin(), p.recvCounts.end()) : p.count;

@@ -290,3 +290,21 @@ def test_pipelined_v_forms_and_unaligned_input(emu_mod):
         assert w.run(CMD["ALLGATHER"], "SmAllGatherPush", b, bo, 10_000, torch.uint8, max_ctas=2) == 0
         for o in bo:
             assert torch.equal(o, torch.cat(b))
+
+
+@pytest.mark.parametrize("nranks", [2, 4, 7])
+@pytest.mark.parametrize("count", [5, 4099, 120_001])
+def test_pipelined_broadcast_and_alltoall(emu_mod, nranks, count):
+    with emu_mod.EmuWorld(nranks, 128 << 10) as w:
+        for root in (0, nranks - 1):
+            bufs = [_rand(count, torch.float32, 900 + r) for r in range(nranks)]
+            want = bufs[root].clone()
+            assert w.run(CMD["BROADCAST"], "SmBroadcastPush", bufs, bufs, count, torch.float32, root=root, max_ctas=3) == 0
+            for b in bufs:
+                assert torch.equal(b, want)
+        send = [_rand(count * nranks, torch.float32, 950 + r) for r in range(nranks)]
+        recv = [torch.zeros(count * nranks, dtype=torch.float32, device="cuda") for _ in range(nranks)]
+        assert w.run(CMD["ALLTOALL"], "SmAlltoAllPush", send, recv, count, torch.float32, max_ctas=3) == 0
+        for r in range(nranks):
+            for s in range(nranks):
+                assert torch.equal(recv[r][s * count:(s + 1) * count], send[s][r * count:(r + 1) * count])

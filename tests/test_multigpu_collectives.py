@@ -29,9 +29,11 @@ def _run(nproc, extra_env, port, worker="mp_worker_collectives.py", expect="all 
     {"HCCL_NVLS_ENABLE": "1", "HCCL_BUFFSIZE": "4"},
     {"HCCL_NVLS_ENABLE": "0", "HCCL_OP_EXPANSION_MODE": "COPY_ENGINE", "HCCL_BUFFSIZE": "16"},
     {"HCCL_NVLS_ENABLE": "1", "HCCL_BUFFSIZE": "8", "HCCL_ALGO_NAME": "allreduce=NvlsAllReducePipelined;allgather=NvlsAllGatherPush;"
-     "reducescatter=NvlsReduceScatterPipelined;allgatherv=NvlsAllGatherVPush;reducescatterv=SmReduceScatterVPipelined"},
+     "reducescatter=NvlsReduceScatterPipelined;allgatherv=NvlsAllGatherVPush;reducescatterv=SmReduceScatterVPipelined;"
+     "broadcast=NvlsBroadcastPush;alltoall=SmAlltoAllPush"},
     {"HCCL_NVLS_ENABLE": "0", "HCCL_BUFFSIZE": "8", "HCCL_ALGO_NAME": "allreduce=SmAllReducePipelined;allgather=SmAllGatherPush;"
-     "reducescatter=SmReduceScatterPipelined;allgatherv=SmAllGatherVPush;reducescatterv=SmReduceScatterVPipelined"},
+     "reducescatter=SmReduceScatterPipelined;allgatherv=SmAllGatherVPush;reducescatterv=SmReduceScatterVPipelined;"
+     "broadcast=SmBroadcastPush;alltoall=SmAlltoAllPush"},
 ])
 def test_collectives_two_or_more_gpus(cfg):
     n = min(torch.cuda.device_count(), 8)

@@ -1,4 +1,5 @@
 #include "comm.h"
+#include "../select/selector.h"
 #include <chrono>
 #include <cstring>
 #include <set>
@@ -152,6 +153,7 @@ void SimBackendDestroy(Comm *c)
 static void ApplyConfig(Comm *c, const HcclCommConfig *cfg)
 {
     c->env = GetEnvConfig();
+    if (TuningTable::Instance().LoadConfigured(c->env.tuningFile) != HCCL_SUCCESS) HCCL_WARNING("HCCL_TUNING_FILE=%s could not be loaded; built-in table in use", c->env.tuningFile.c_str());
     HcclCommConfigInit(&c->config);
     if (cfg == nullptr) return;
     c->config = *cfg;

@@ -1,6 +1,8 @@
 #include "selector.h"
 #include "../exec/op_common.h"
+#include <dlfcn.h>
 #include <algorithm>
+#include <mutex>
 #include <fstream>
 #include <sstream>
 #include <tuple>
@@ -135,6 +137,29 @@ HcclResult TuningTable::LoadFile(const std::string &path)
     return LoadText(ss.str());
 }
 
+HcclResult TuningTable::LoadConfigured(const std::string &envFile)
+{
+    static std::once_flag once;
+    static HcclResult result = HCCL_SUCCESS;
+    std::call_once(once, [&] {
+        Dl_info info;
+        if (dladdr((const void *)&TuningTable::Instance, &info) && info.dli_fname) {
+            std::string lib = info.dli_fname;
+            size_t slash = lib.rfind('/');
+            std::string packaged = (slash == std::string::npos ? std::string(".") : lib.substr(0, slash)) + "/../tuning/b200.txt";
+            std::ifstream f(packaged);
+            if (f) {
+                std::stringstream ss;
+                ss << f.rdbuf();
+                if (LoadText(ss.str()) == HCCL_SUCCESS) HCCL_RUN_INFO("tuning table: loaded %s", packaged.c_str());
+                else HCCL_WARNING("tuning table: %s is malformed and was ignored", packaged.c_str());
+            }
+        }
+        if (!envFile.empty()) result = LoadFile(envFile);
+    });
+    return result;
+}
+
 std::string TuningTable::Dump() const
 {
     std::ostringstream os;
@@ -261,7 +286,7 @@ AlgoType ForcedAlgo(const SelectorCtx &ctx, HcclCMDType op)
 SelectorStatus FromTable(const SelectorCtx &ctx, OpParam &p, HcclCommEngine eng)
 {
     const TuningRow *row = TuningTable::Instance().Lookup(p.opType, ctx.topo->nranks, eng, p.DataBytes());
-    if (!row) return SelectorStatus::NOT_MATCH;
+    if (!row || row->algName == "none") return SelectorStatus::NOT_MATCH;   // "none": this engine passes on the size range
     p.algName = row->algName;
     return SelectorStatus::MATCH;
 }

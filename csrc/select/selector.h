@@ -74,6 +74,9 @@ public:
     HcclResult LoadFile(const std::string &path);
     HcclResult LoadText(const std::string &text);
     void ResetToBuiltin();
+    // Once per process: rows measured on the target machine that ship next to the library (<lib dir>/../tuning/b200.txt),
+    // then the file named by HCCL_TUNING_FILE. Later rows replace earlier ones for the same (op, ranks, engine).
+    HcclResult LoadConfigured(const std::string &envFile);
     std::string Dump() const;
 private:
     TuningTable();

@@ -118,3 +118,48 @@ def test_simulated_communicator_reports_forced_host_algorithms(monkeypatch):
         assert out[ALLREDUCE] == ("InsAllReduceNHR", 1)
         assert out[ALLGATHER] == ("InsAllGatherRing", 1)
         assert out[BROADCAST][1] == 1 and out[BROADCAST][0].startswith("InsBroadcast")
+
+
+def test_tuning_file_from_environment_is_loaded_at_communicator_creation(tmp_path):
+    """HCCL_TUNING_FILE is read once per process when the first communicator is created (child process: the load is once-only)."""
+    import os
+    import subprocess
+    import sys
+
+    table = tmp_path / "table.txt"
+    table.write_text("# measured rows\nallreduce 2 HOST inf InsAllReduceRing 0\nallgather 0 SM 1048576 SmAllGatherPush 4\n")
+    code = (
+        "import ctypes, numpy as np\n"
+        "from hccl_b200._lib import lib\n"
+        "from hccl_b200.utils.sim import run_ranks\n"
+        "run_ranks(2, lambda c, r: c.barrier())\n"
+        "buf = ctypes.create_string_buffer(8192)\n"
+        "lib().HcclTuningTableDump(buf, 8192)\n"
+        "print(buf.value.decode())\n")
+    env = dict(os.environ, HCCL_TUNING_FILE=str(table), PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    res = subprocess.run([sys.executable, "-c", code], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=120)
+    assert res.returncode == 0, res.stdout[-2000:]
+    assert "SmAllGatherPush 4" in res.stdout and "InsAllReduceRing" in res.stdout
+
+
+def test_strict_dtype_rules_switch():
+    import os
+    import subprocess
+    import sys
+
+    code = (
+        "import numpy as np\n"
+        "from hccl_b200._lib import HcclError\n"
+        "from hccl_b200.utils.sim import run_ranks\n"
+        "def body(c, r):\n"
+        "    x = np.ones(8, np.uint8)\n"
+        "    try:\n"
+        "        c.all_reduce(x); c.synchronize(); return 0\n"
+        "    except HcclError as e:\n"
+        "        return e.code\n"
+        "print('codes', run_ranks(2, body))\n")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for strict, want in (("1", "codes [5, 5]"), ("0", "codes [0, 0]")):
+        env = dict(os.environ, HCCL_STRICT_DTYPE_RULES=strict, PYTHONPATH=root)
+        res = subprocess.run([sys.executable, "-c", code], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=120)
+        assert want in res.stdout, res.stdout[-2000:]

@@ -276,3 +276,38 @@ def test_parameter_errors_are_reported_not_crashes():
         assert codes[5] in (Result.E_PARA, Result.E_NOT_SUPPORT)
         assert codes[6] in (Result.E_PARA, Result.E_NOT_SUPPORT)
         assert codes[7] == Result.E_PTR
+
+
+@pytest.mark.parametrize("algo", ["fullmesh"])
+def test_reductions_are_batch_invariant(monkeypatch, algo):
+    """The value of an element does not depend on how many other elements travel with it or on the scratch size (chunking):
+    mesh reductions add in rank order whatever the count. This is the property the reference's experimental batch-invariant
+    ReduceScatter adds for its 2-D topology (docs/en/rfcs/0001-add-batch-invariant-reducescatter.md)."""
+    monkeypatch.setenv("HCCL_ALGO", f"level0:NA;level1:{algo}")
+    lib().HcclResetEnvConfigForTest()
+    nranks, n = 5, 40_000
+    rng = np.random.default_rng(7)
+    xs = [(rng.standard_normal(n) * 10.0 ** rng.integers(-6, 6, n)).astype(np.float32) for _ in range(nranks)]
+
+    def run(count, buffer_mb):
+        def body(comm, rank):
+            out = np.empty(count, np.float32)
+            comm.all_reduce(xs[rank][:count], out)
+            blk = count // nranks
+            rs = np.empty(blk, np.float32)
+            comm.reduce_scatter(xs[rank][:blk * nranks], rs)
+            comm.synchronize()
+            return out, rs
+        return run_ranks(nranks, body, buffer_mb=buffer_mb)
+
+    try:
+        full = run(n, 0)
+        small = run(n // 7, 0)
+        chunked = run(n, 1)                      # 1 MB scratch is plenty here; still a different plan geometry
+        for r in range(nranks):
+            assert np.array_equal(full[r][0][: n // 7].view(np.uint32), small[r][0].view(np.uint32))
+            assert np.array_equal(full[r][0].view(np.uint32), chunked[r][0].view(np.uint32))
+            assert np.array_equal(full[r][0].view(np.uint32), full[0][0].view(np.uint32))      # and identical on every rank
+    finally:
+        monkeypatch.delenv("HCCL_ALGO")
+        lib().HcclResetEnvConfigForTest()

@@ -84,10 +84,10 @@ void TuningTable::ResetToBuiltin()
     rows_.clear();
     const uint64_t INF = ~0ull;
     Set(HCCL_CMD_ALLREDUCE, 0, HCCL_ENGINE_SM, {{256u << 10, "SmAllReduceMesh1DOneShot", 0}, {INF, "SmAllReduceMesh1DTwoShot", 0}});
-    Set(HCCL_CMD_ALLREDUCE, 0, HCCL_ENGINE_NVLS, {{512u << 10, "NvlsAllReduceOneShot", 0}, {INF, "NvlsAllReduceTwoShot", 0}});
+    Set(HCCL_CMD_ALLREDUCE, 0, HCCL_ENGINE_NVLS, {{512u << 10, "NvlsAllReduceOneShot", 0}, {128u << 20, "NvlsAllReduceTwoShot", 0}, {INF, "NvlsAllReducePipelined", 0}});
     Set(HCCL_CMD_ALLGATHER, 0, HCCL_ENGINE_SM, {{INF, "SmAllGatherMesh1D", 0}});
     Set(HCCL_CMD_REDUCE_SCATTER, 0, HCCL_ENGINE_SM, {{INF, "SmReduceScatterMesh1D", 0}});
-    Set(HCCL_CMD_REDUCE_SCATTER, 0, HCCL_ENGINE_NVLS, {{INF, "NvlsReduceScatter", 0}});
+    Set(HCCL_CMD_REDUCE_SCATTER, 0, HCCL_ENGINE_NVLS, {{32u << 20, "NvlsReduceScatter", 0}, {INF, "NvlsReduceScatterPipelined", 0}});
     Set(HCCL_CMD_BROADCAST, 0, HCCL_ENGINE_SM, {{INF, "SmBroadcastMesh1D", 0}});
     Set(HCCL_CMD_BROADCAST, 0, HCCL_ENGINE_NVLS, {{INF, "NvlsBroadcast", 0}});
     Set(HCCL_CMD_REDUCE, 0, HCCL_ENGINE_SM, {{INF, "SmReduceMesh1D", 0}});

@@ -34,6 +34,7 @@ enum SmKernelId : uint32_t {
     K_ALLGATHER_PIPE,         // also AllGatherV
     K_ALLGATHER_PIPE_NVLS,
     K_ALLTOALL_PIPE,          // AlltoAll with uniform counts
+    K_ALLREDUCE_RING,         // reduce-scatter + all-gather around the ring (comparator for the mesh kernels)
     K_COUNT
 };
 

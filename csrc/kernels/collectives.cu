@@ -83,6 +83,90 @@ template <typename T, int OP, bool EMU> __device__ void AllReduceTwoShotBody(KCt
     }
 }
 
+// ================================================================================================ AllReduce ring
+// Reduce-scatter then all-gather around the ring rank -> rank + 1, one slice per step, every step into its own scratch
+// slot at the receiver (2(n-1) slots, so no slot is reused inside an operator and no acknowledgements are needed). The
+// comparator for the mesh kernels: same bytes per link as two-shot but 2(n-1) dependent steps instead of 2 (reference:
+// docs/zh/user_guide/coll_algo_intro/Ring.md:25-31 for the cost model; HCCL's ring runs as host-issued tasks).
+template <typename T, int OP> __device__ __forceinline__ void ReduceTwoTo(char *dst, char *dst2, const char *a, const char *b, uint64_t bytes)
+{
+    using Ac = typename Acc<T>::type;
+    constexpr int VE = 16 / sizeof(T);
+    const bool vecOk = ((((uintptr_t)dst | (uintptr_t)dst2 | (uintptr_t)a | (uintptr_t)b) & 15u) == 0);
+    const uint64_t nvec = vecOk ? bytes >> 4 : 0;
+    for (uint64_t i = threadIdx.x; i < nvec; i += blockDim.x) {
+        uint4 ra = ((const uint4 *)a)[i], rb = ((const uint4 *)b)[i], out;
+        const T *ea = (const T *)&ra, *eb = (const T *)&rb;
+        T *eo = (T *)&out;
+#pragma unroll
+        for (int j = 0; j < VE; ++j) eo[j] = FromAcc<T>(Combine<OP, Ac>(ToAcc<T>(ea[j]), ToAcc<T>(eb[j])));
+        ((uint4 *)dst)[i] = out;
+        if (dst2) ((uint4 *)dst2)[i] = out;
+    }
+    const uint64_t nElems = bytes / sizeof(T);
+    for (uint64_t i = nvec * VE + threadIdx.x; i < nElems; i += blockDim.x) {
+        T v = FromAcc<T>(Combine<OP, Ac>(ToAcc<T>(((const T *)a)[i]), ToAcc<T>(((const T *)b)[i])));
+        ((T *)dst)[i] = v;
+        if (dst2) ((T *)dst2)[i] = v;
+    }
+}
+
+template <typename T, int OP, bool EMU> __device__ void AllReduceRingBody(KCtx &k, const CollArgs &A)
+{
+    const int n = k.nranks, next = (k.rank + 1) % n, prev = (k.rank + n - 1) % n;
+    const uint64_t slice = Up128((A.bytes + n - 1) / n);
+    auto part = [&](int j) { return PartOf(SliceLen(A.bytes, slice, j), gridDim.x, blockIdx.x); };
+    auto slot = [&](int rk, int step) { return k.Ccl(rk) + (uint64_t)step * slice; };
+    const char *in = (const char *)A.in;
+    char *out = (char *)A.out;
+    // after all stores of the CTA: tell `next` that step `done` (1-based) has arrived in its scratch
+    auto signal = [&](uint32_t done) {
+        __syncthreads();
+        if (threadIdx.x == 0) StReleaseSys(&FlagsOf(k.PeerHeap(next))->barrier[k.chan][k.rank], k.epoch + done);
+    };
+    auto waitFor = [&](uint32_t done) -> bool {
+        bool mine = true;
+        if (threadIdx.x == 0) mine = WaitFlagGe(k, &k.flags->barrier[k.chan][prev], k.epoch + done, (uint32_t)prev, 300u + done);
+        int all = __syncthreads_and(mine ? 1 : 0);
+        if (!all) k.ok = false;
+        return all != 0;
+    };
+    // ---- reduce-scatter: at step s this rank sends (its partial of) slice (rank - s) and receives slice (rank - 1 - s)
+    for (int s = 0; s < n - 1; ++s) {
+        const int j = (k.rank - s + n) % n;
+        Part p = part(j);
+        if (s == 0) BlockCopy(slot(next, 0) + p.off, in + (uint64_t)j * slice + p.off, p.len);
+        else {
+            if (!waitFor((uint32_t)s)) return;
+            ReduceTwoTo<T, OP>(slot(next, s) + p.off, nullptr, slot(k.rank, s - 1) + p.off, in + (uint64_t)j * slice + p.off, p.len);
+        }
+        signal((uint32_t)s + 1);
+    }
+    // ---- the last partial received is slice (rank + 1): finish it, keep it, and start the all-gather with it
+    {
+        if (!waitFor((uint32_t)n - 1)) return;
+        const int j = (k.rank + 1) % n;
+        Part p = part(j);
+        ReduceTwoTo<T, OP>(out + (uint64_t)j * slice + p.off, n > 2 ? slot(next, n - 1) + p.off : nullptr, slot(k.rank, n - 2) + p.off,
+                           in + (uint64_t)j * slice + p.off, p.len);
+        if (n == 2) BlockCopy(slot(next, n - 1) + p.off, out + (uint64_t)j * slice + p.off, p.len);
+        signal((uint32_t)n);
+    }
+    // ---- all-gather: step a delivers slice (rank + 1 - a); forward it unless it is the last hop
+    for (int a = 1; a < n; ++a) {
+        if (!waitFor((uint32_t)(n - 1 + a))) return;
+        const int j = (k.rank + 1 - a + n) % n;
+        Part p = part(j);
+        const char *got = slot(k.rank, n - 2 + a) + p.off;
+        BlockCopy(out + (uint64_t)j * slice + p.off, got, p.len);
+        if (a < n - 1) {
+            BlockCopy(slot(next, n - 1 + a) + p.off, got, p.len);
+            signal((uint32_t)(n + a));
+        }
+    }
+    k.syncs += (uint32_t)(2 * n - 2);
+}
+
 // ================================================================================================ AllReduce NVLS
 // out[i] <- switch-reduced value; `out` may have any alignment (element-wise store then).
 template <typename T> __device__ __forceinline__ void StoreVec(T *out, uint64_t vecIdx, uint4 v, bool aligned)
@@ -323,6 +407,7 @@ template <typename T, int OP, bool EMU> __device__ void ReduceScatterPipeNvlsBod
 template <bool EMU> __device__ void AllGatherPipePlainBody(KCtx &k, const CollArgs &A) { pipe::AllGatherBody<EMU, false>(k, A); }
 template <bool EMU> __device__ void AllGatherPipeNvlsBody(KCtx &k, const CollArgs &A) { pipe::AllGatherBody<EMU, true>(k, A); }
 template <bool EMU> __device__ void AlltoAllPipeBody(KCtx &k, const CollArgs &A) { pipe::AllGatherBody<EMU, false, true>(k, A); }
+COLL_KERNEL_TYPED(KAllReduceRing, AllReduceRingBody)
 COLL_KERNEL_TYPED(KAllReducePipe, AllReducePipePlainBody)
 COLL_KERNEL_TYPED(KReduceScatterPipe, ReduceScatterPipePlainBody)
 
@@ -522,6 +607,7 @@ template <bool EMU> CollKernelFn TypedKernel(SmKernelId id, HcclDataType dt)
         case K_ALLREDUCE_TWOSHOT: PICK(KAllReduceTwoShot)
         case K_REDUCESCATTER_V: PICK(KReduceScatterV)
         case K_REDUCE: PICK(KReduce)
+        case K_ALLREDUCE_RING: PICK(KAllReduceRing)
         case K_ALLREDUCE_PIPE: PICK(KAllReducePipe)
         case K_REDUCESCATTER_PIPE: PICK(KReduceScatterPipe)
         default: return nullptr;
@@ -554,7 +640,7 @@ template <bool EMU> CollKernelFn NvlsKernel(SmKernelId id, HcclDataType dt, Hccl
 template <bool EMU> CollKernelFn KernelFor(const SmLaunch &l)
 {
     switch (l.kernel) {
-        case K_ALLREDUCE_ONESHOT: case K_ALLREDUCE_TWOSHOT: case K_REDUCESCATTER_V: case K_REDUCE: case K_ALLREDUCE_PIPE: case K_REDUCESCATTER_PIPE:
+        case K_ALLREDUCE_ONESHOT: case K_ALLREDUCE_TWOSHOT: case K_REDUCESCATTER_V: case K_REDUCE: case K_ALLREDUCE_PIPE: case K_REDUCESCATTER_PIPE: case K_ALLREDUCE_RING:
             return TypedKernel<EMU>(l.kernel, l.dtype);
         case K_ALLREDUCE_NVLS_ONESHOT: case K_ALLREDUCE_NVLS_TWOSHOT: case K_REDUCESCATTER_NVLS: case K_ALLREDUCE_PIPE_NVLS: case K_REDUCESCATTER_PIPE_NVLS:
             return NvlsKernel<EMU>(l.kernel, l.dtype, (HcclReduceOp)l.args.op);

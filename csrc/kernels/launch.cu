@@ -27,7 +27,7 @@ const std::vector<SmAlgoDesc> &SmAlgorithms()
         {"SmReduceMesh1D", HCCL_CMD_REDUCE, false}, {"SmScatterMesh1D", HCCL_CMD_SCATTER, false},
         {"SmAlltoAllMesh1D", HCCL_CMD_ALLTOALL, false}, {"SmAlltoAllVMesh1D", HCCL_CMD_ALLTOALLV, false},
         {"SmAlltoAllVCMesh1D", HCCL_CMD_ALLTOALLVC, false}, {"SmBarrierMesh1D", HCCL_CMD_BARRIER, false},
-        {"SmAllReducePipelined", HCCL_CMD_ALLREDUCE, false}, {"NvlsAllReducePipelined", HCCL_CMD_ALLREDUCE, true},
+        {"SmAllReduceRing", HCCL_CMD_ALLREDUCE, false}, {"SmAllReducePipelined", HCCL_CMD_ALLREDUCE, false}, {"NvlsAllReducePipelined", HCCL_CMD_ALLREDUCE, true},
         {"SmReduceScatterPipelined", HCCL_CMD_REDUCE_SCATTER, false}, {"SmReduceScatterVPipelined", HCCL_CMD_REDUCE_SCATTER_V, false},
         {"NvlsReduceScatterPipelined", HCCL_CMD_REDUCE_SCATTER, true},
         {"SmAllGatherPush", HCCL_CMD_ALLGATHER, false}, {"SmAllGatherVPush", HCCL_CMD_ALLGATHER_V, false},

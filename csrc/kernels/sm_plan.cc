@@ -76,6 +76,14 @@ HcclResult SmPlanOp(const SmPlanCtx &ctx, const OpParam &p, const std::string &a
             push(nv ? K_ALLREDUCE_NVLS_TWOSHOT : K_ALLREDUCE_TWOSHOT, lo, cnt, cnt * es / n * 2, [&](SmLaunch &l) { l.args.in = in + lo * es; l.args.out = outp + lo * es; });
         });
     }
+    if (alg == "SmAllReduceRing") {
+        if (n < 2) return HCCL_E_NOT_SUPPORT;
+        uint64_t maxSlice = Down128(ccl / (2 * (n - 1)));
+        uint64_t maxCount = maxSlice * n / es;
+        return loop(p.count, maxCount, [&](uint64_t lo, uint64_t cnt) {
+            push(K_ALLREDUCE_RING, lo, cnt, cnt * es / n * 2, [&](SmLaunch &l) { l.args.in = in + lo * es; l.args.out = outp + lo * es; });
+        });
+    }
     // ---- warp-specialised pipelines: one launch for any payload; the scratch half holds rings of sub-chunks
     auto pipeSub = [&](uint32_t rings, uint32_t ctas) -> uint64_t {
         uint64_t s = Down128(ccl / ((uint64_t)rings * 2 /* depth */ * n * ctas));

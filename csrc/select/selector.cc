@@ -318,6 +318,7 @@ protected:
     {
         if (!SmReduceSupports(p.dtype, p.reduceOp)) return SelectorStatus::NOT_MATCH;
         AlgoType f = ForcedAlgo(ctx, p.opType);
+        if (f == AlgoType::RING && p.opType == HCCL_CMD_ALLREDUCE) { p.algName = "SmAllReduceRing"; return SelectorStatus::MATCH; }
         if (f == AlgoType::RING || f == AlgoType::NHR) return SelectorStatus::NOT_MATCH;   // those live in the IR engines
         return FromTable(ctx, p, HCCL_ENGINE_SM);
     }

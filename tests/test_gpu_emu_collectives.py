@@ -308,3 +308,21 @@ def test_pipelined_broadcast_and_alltoall(emu_mod, nranks, count):
         for r in range(nranks):
             for s in range(nranks):
                 assert torch.equal(recv[r][s * count:(s + 1) * count], send[s][r * count:(r + 1) * count])
+
+
+@pytest.mark.parametrize("nranks", [2, 3, 4, 8])
+@pytest.mark.parametrize("count", [1, 37, 4099, 200_003])
+def test_ring_allreduce(emu_mod, nranks, count):
+    """Ring reduce-scatter + all-gather on the SM engine (the comparator for the mesh kernels); small scratch forces the chunk loop."""
+    with emu_mod.EmuWorld(nranks, 256 << 10) as w:
+        for dtype, op in ((torch.float32, ReduceOp.SUM), (torch.bfloat16, ReduceOp.MAX), (torch.int32, ReduceOp.SUM)):
+            xs = [_rand(count, dtype, 500 + r) for r in range(nranks)]
+            bufs = [x.clone() for x in xs]
+            assert w.run(CMD["ALLREDUCE"], "SmAllReduceRing", bufs, bufs, count, dtype, op, max_ctas=3) == 0      # in place
+            ref = _ref_reduce(xs, op, dtype)
+            for b in bufs:
+                if dtype.is_floating_point:
+                    assert torch.allclose(b.double(), ref, atol=_tol(dtype, nranks), rtol=1e-2)
+                else:
+                    assert torch.equal(b.to(torch.int64), ref)
+                assert torch.equal(b, bufs[0])

@@ -58,20 +58,23 @@ template <int BN, class Policy, bool EMU> HcclResult SetSmemAttr()
 // Fills everything except the DevComm pointer. heapLocal = this rank's heap base as mapped here.
 // The CTA-pair (cta_group::2) kernel serves AllGatherMatmul and MatmulReduceScatter when every rank's rows split into
 // whole 256-row pairs. HCCL_MC2_CTA_PAIR=0 keeps the one-CTA kernels.
-// HCCL_MC2_CTA_PAIR: 0 = one-CTA kernels only; 1 (default) = AllGatherMatmul and MatmulReduceScatter on CTA pairs with
-// 256-wide tiles (AllGatherMatmul keeps its communication CTAs); 2 = also 224-wide tiles where they waste fewer waves;
+// HCCL_MC2_CTA_PAIR: 0 = one-CTA kernels only; 1 = AllGatherMatmul and MatmulReduceScatter on CTA pairs with 256-wide
+// tiles (AllGatherMatmul keeps its communication CTAs); 2 = also 224-wide tiles where they waste fewer waves;
 // 3 = AllGatherMatmul without communication CTAs, warps 2 and 3 of every GEMM CTA push the shard (measured slower at 2 GPUs:
 // the pushes of all CTAs contend with the operand loads during the first hundred microseconds).
-int PairLevel()
+// Unset: pairs on 2 ranks (measured +1..3 % on the 2-GPU step), one-CTA kernels on more ranks (at 8 GPUs the per-rank
+// GEMMs are short and the pair kernels measured 0..3 % slower: 1.019-1.029 ms against 0.997-1.016 ms per step).
+int PairLevel(uint32_t nranks = 2)
 {
-    static int level = -1;
-    if (level < 0) { const char *e = getenv("HCCL_MC2_CTA_PAIR"); level = e ? atoi(e) : 1; }
-    return level;
+    static int level = -2;
+    if (level == -2) { const char *e = getenv("HCCL_MC2_CTA_PAIR"); level = e ? atoi(e) : -1; }
+    if (level >= 0) return level;
+    return nranks <= 2 ? 1 : 0;
 }
 
 bool PairModeFor(const FusedShape &s)
 {
-    if (PairLevel() <= 0 || s.N < 256) return false;
+    if (PairLevel(s.n) <= 0 || s.N < 256) return false;
     if (s.kind == AGMM) return (s.m / kBM) % 2 == 0;
     if (s.kind == MMRS) return (s.m / s.n / kBM) % 2 == 0;
     return false;

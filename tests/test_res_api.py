@@ -1,0 +1,121 @@
+"""Communicator resource API (hccl_res.h) on the simulation backend: state callbacks, configuration read-back, keyed
+blobs, memory registration, rank graph queries on flat and multi-server topologies, exchanged blobs."""
+import ctypes
+
+from hccl_b200._lib import HcclCommConfig, lib
+from hccl_b200.types import Result
+from hccl_b200.utils.sim import run_ranks
+
+vp, u32, u64 = ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint64
+
+
+class LinkInfo(ctypes.Structure):
+    _fields_ = [("type", ctypes.c_int), ("layer", u32), ("bandwidthGBs", ctypes.c_double), ("peerAccess", u32)]
+
+
+CB = ctypes.CFUNCTYPE(None, vp, ctypes.c_int)
+
+
+def _decl():
+    l = lib()
+    l.HcclCommRegCommStateCallback.argtypes = [vp, CB, vp]
+    l.HcclConfigGetInfo.argtypes = [vp, ctypes.POINTER(HcclCommConfig)]
+    l.HcclGroupStatusGet.argtypes = [ctypes.c_char_p, ctypes.POINTER(ctypes.c_int)]
+    l.HcclEngineCtxCreate.argtypes = [vp, ctypes.c_char_p, ctypes.c_int, u64, ctypes.POINTER(vp)]
+    l.HcclEngineCtxGet.argtypes = [vp, ctypes.c_char_p, ctypes.c_int, ctypes.POINTER(vp), ctypes.POINTER(u64)]
+    l.HcclEngineCtxCopy.argtypes = [vp, ctypes.c_char_p, vp, u64]
+    l.HcclEngineCtxDestroy.argtypes = [vp, ctypes.c_char_p]
+    l.HcclCommMemReg.argtypes = [vp, vp, u64, ctypes.POINTER(u64)]
+    l.HcclCommMemDereg.argtypes = [vp, vp]
+    l.HcclRankGraphGetLayers.argtypes = [vp, ctypes.POINTER(u32)]
+    l.HcclRankGraphGetRanksByLayer.argtypes = [vp, u32, ctypes.POINTER(u32), ctypes.POINTER(u32)]
+    l.HcclRankGraphGetInstSizeListByLayer.argtypes = [vp, u32, ctypes.POINTER(u32), ctypes.POINTER(u32)]
+    l.HcclRankGraphGetTopoTypeByLayer.argtypes = [vp, u32, ctypes.POINTER(ctypes.c_int)]
+    l.HcclRankGraphGetLinks.argtypes = [vp, u32, u32, ctypes.POINTER(LinkInfo)]
+    l.HcclCommAddExchangeInfo.argtypes = [vp, ctypes.c_char_p, vp, u32]
+    l.HcclCommGetExchangeInfo.argtypes = [vp, u32, ctypes.c_char_p, vp, ctypes.POINTER(u32)]
+    return l
+
+
+def test_state_callback_config_and_group_status():
+    l = _decl()
+
+    def body(comm, rank):
+        seen = []
+        cb = CB(lambda user, st: seen.append(st))
+        h = vp(comm.handle)
+        assert l.HcclCommRegCommStateCallback(h, cb, None) == 0
+        cfg = HcclCommConfig()
+        assert l.HcclConfigGetInfo(h, ctypes.byref(cfg)) == 0
+        st = ctypes.c_int(-1)
+        assert l.HcclGroupStatusGet(comm.name.encode(), ctypes.byref(st)) == 0 and st.value == 0
+        assert l.HcclGroupStatusGet(b"no_such_group", ctypes.byref(st)) == Result.E_NOT_FOUND
+        comm.barrier()
+        comm.synchronize()
+        comm.suspend()
+        assert l.HcclGroupStatusGet(comm.name.encode(), ctypes.byref(st)) == 0 and st.value == 1
+        comm.resume()
+        return seen, cfg.hcclBufferSize, cfg.hcclBackend, cfg.hcclCommName.decode(), comm.name, cb
+
+    for seen, buf_mb, backend, cfg_name, name, _cb in run_ranks(2, body, buffer_mb=3):
+        assert seen == [1, 0]                     # SUSPENDING, then READY again
+        assert buf_mb == 3 and backend == 1 and cfg_name == name
+
+
+def test_engine_ctx_blobs_and_memory_registration():
+    l = _decl()
+
+    def body(comm, rank):
+        h = vp(comm.handle)
+        p, q, n = vp(), vp(), u64()
+        assert l.HcclEngineCtxGet(h, b"plan", 0, ctypes.byref(p), ctypes.byref(n)) == Result.E_NOT_FOUND
+        assert l.HcclEngineCtxCreate(h, b"plan", 0, 64, ctypes.byref(p)) == 0
+        assert l.HcclEngineCtxCreate(h, b"plan", 0, 64, ctypes.byref(q)) == Result.E_PARA            # exists already
+        src = (ctypes.c_uint8 * 64)(*range(64))
+        assert l.HcclEngineCtxCopy(h, b"plan", src, 64) == 0
+        assert l.HcclEngineCtxGet(h, b"plan", 0, ctypes.byref(q), ctypes.byref(n)) == 0 and n.value == 64
+        got = bytes((ctypes.c_uint8 * 64).from_address(q.value))
+        assert l.HcclEngineCtxDestroy(h, b"plan") == 0
+        assert l.HcclEngineCtxGet(h, b"plan", 0, ctypes.byref(q), ctypes.byref(n)) == Result.E_NOT_FOUND
+        sym, off, off2 = vp(), u64(), u64()
+        assert l.HcclCommSymAlloc(h, 8192, ctypes.byref(sym)) == 0
+        assert l.HcclCommMemReg(h, sym, 8192, ctypes.byref(off)) == 0
+        assert l.HcclCommMemReg(h, vp(sym.value + 4096), 4096, ctypes.byref(off2)) == 0 and off2.value == off.value + 4096
+        stack = (ctypes.c_uint8 * 16)()
+        assert l.HcclCommMemReg(h, stack, 16, ctypes.byref(off2)) == Result.E_NOT_SUPPORT
+        assert l.HcclCommMemDereg(h, sym) == 0 and l.HcclCommMemDereg(h, stack) == Result.E_NOT_FOUND
+        return got, off.value
+
+    res = run_ranks(2, body)
+    assert res[0][0] == bytes(range(64))
+    assert res[0][1] == res[1][1]                 # the window offset is the same on every rank
+
+
+def test_rank_graph_flat_and_exchange_info():
+    l = _decl()
+
+    def body(comm, rank):
+        h = vp(comm.handle)
+        layers = u32()
+        assert l.HcclRankGraphGetLayers(h, ctypes.byref(layers)) == 0
+        ranks, n = (u32 * 8)(), u32(8)
+        assert l.HcclRankGraphGetRanksByLayer(h, 0, ranks, ctypes.byref(n)) == 0
+        small = u32(1)
+        assert l.HcclRankGraphGetRanksByLayer(h, 0, ranks, ctypes.byref(small)) == Result.E_MEMORY and small.value == 3
+        sizes, ns = (u32 * 4)(), u32(4)
+        assert l.HcclRankGraphGetInstSizeListByLayer(h, 0, sizes, ctypes.byref(ns)) == 0
+        t = ctypes.c_int(-1)
+        assert l.HcclRankGraphGetTopoTypeByLayer(h, 0, ctypes.byref(t)) == 0
+        assert l.HcclRankGraphGetTopoTypeByLayer(h, 5, ctypes.byref(t)) == Result.E_PARA
+        link = LinkInfo()
+        assert l.HcclRankGraphGetLinks(h, rank, (rank + 1) % 3, ctypes.byref(link)) == 0
+        mine = f"hello from {rank}".encode()
+        assert l.HcclCommAddExchangeInfo(h, b"greeting", mine, len(mine)) == 0
+        buf, blen = ctypes.create_string_buffer(64), u32(64)
+        assert l.HcclCommGetExchangeInfo(h, (rank + 1) % 3, b"greeting", buf, ctypes.byref(blen)) == 0
+        return layers.value, list(ranks[: n.value]), list(sizes[: ns.value]), (link.type, link.layer, link.peerAccess), buf.raw[: blen.value].decode()
+
+    for r, (layers, ranks, sizes, link, msg) in enumerate(run_ranks(3, body)):
+        assert layers == 1 and ranks == [0, 1, 2] and sizes == [3]
+        assert link == (3, 0, 1)                  # shared memory between simulated ranks, layer 0, directly addressable
+        assert msg == f"hello from {(r + 1) % 3}"

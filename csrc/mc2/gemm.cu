@@ -149,11 +149,16 @@ static HcclResult LaunchPlain2Cta(const void *a, const void *b, void *c, uint32_
     return LaunchPlain2CtaT<256>(a, b, c, M, N, K, outFp32, s);
 }
 
-bool Gemm2CtaEnabled()
+// HCCL_GEMM_2CTA: 0 never, 1 always, unset = by size. The CTA-pair kernel keeps the tensor pipe busier (99.5 % against
+// 88 % of the active cycles) and wins on kernels that finish before the 1 kW power cap bites (1635 against 1480 TFLOP/s on
+// 8192 x 8192 x 4096); on multi-millisecond GEMMs run back to back its extra DRAM traffic costs clock under the cap and the
+// one-CTA kernel measured faster (1313 against 1250 TFLOP/s on the 8192 x 28672 x 8192 pair of the single-GPU step).
+bool Gemm2CtaEnabled(uint64_t m, uint64_t n, uint64_t k)
 {
-    static int v = -1;
-    if (v < 0) { const char *e = getenv("HCCL_GEMM_2CTA"); v = e ? atoi(e) : 1; }
-    return v != 0;
+    static int v = -2;
+    if (v == -2) { const char *e = getenv("HCCL_GEMM_2CTA"); v = e ? atoi(e) : -1; }
+    if (v >= 0) return v != 0;
+    return 2.0 * (double)m * (double)n * (double)k < 2.5e12;
 }
 
 }  // namespace mc2
@@ -174,7 +179,7 @@ HcclResult HcclGemmBf16(const void *a, const void *b, void *c, uint64_t m, uint6
     }
     // narrow tiles when the problem has too few 128x256 tiles to fill the GPU
     uint64_t tiles256 = ((m + 127) / 128) * ((n + 255) / 256);
-    if (Gemm2CtaEnabled() && tiles256 >= (uint64_t)SmCount()) return LaunchPlain2Cta(a, b, c, (uint32_t)m, (uint32_t)n, (uint32_t)k, outFp32 != 0, stream);
+    if (Gemm2CtaEnabled(m, n, k) && tiles256 >= (uint64_t)SmCount()) return LaunchPlain2Cta(a, b, c, (uint32_t)m, (uint32_t)n, (uint32_t)k, outFp32 != 0, stream);
     if (tiles256 >= (uint64_t)SmCount() || n % 256 == 0 && tiles256 * 2 > (uint64_t)SmCount()) return LaunchPlain<256>(a, b, c, m, n, k, outFp32 != 0, stream);
     uint64_t tiles128 = ((m + 127) / 128) * ((n + 127) / 128);
     if (tiles128 >= (uint64_t)SmCount() / 2) return LaunchPlain<128>(a, b, c, m, n, k, outFp32 != 0, stream);

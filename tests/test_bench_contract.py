@@ -1,0 +1,23 @@
+"""The parts of the benchmark contract that can be checked without a GPU."""
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def test_reference_arm_reports_unavailable_and_exits_zero():
+    res = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--gpus", "1", "--steps", "2", "--warmup", "1"],
+                         stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=120)
+    assert res.returncode == 0, res.stderr[-2000:]
+    line = [l for l in res.stdout.splitlines() if l.startswith("{")][-1]
+    d = json.loads(line)
+    assert d["impl"] == "reference" and isinstance(d["unavailable"], str) and "\n" not in d["unavailable"]
+
+
+def test_graft_entry_exposes_build_and_smoke():
+    sys.path.insert(0, str(ROOT))
+    import __graft_entry__ as g
+
+    assert callable(g.build) and callable(g.smoke)

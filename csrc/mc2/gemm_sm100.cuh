@@ -47,6 +47,7 @@ struct GemmParams {
     uint32_t ldc;
     uint32_t outFp32;            // 1 = fp32 output
     uint32_t groupM;             // M blocks per rasterisation group
+    uint32_t waitSleepNs;        // back-off of the off-critical-path barrier waits (0 = spin)
     uint32_t *errorWord;         // device word set to 1 when a wait ran out
     const void *comm;            // DevComm* of this rank (fused policies)
     uint64_t u64[8];
@@ -197,7 +198,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) GemmKernel(const __grid_const
                 int32_t rowA;
                 Policy::SelectA(p, ctx, mb, &ta, &rowA);
                 for (uint32_t kb = 0; kb < kIters && ok; ++kb) {
-                    ok = MbarWait(&empty[stage], phase ^ 1, abortWord);
+                    ok = MbarWaitRelaxed(&empty[stage], phase ^ 1, abortWord, p.waitSleepNs);
                     if (!ok) break;
                     MbarExpectTx(&full[stage], S::kABytes + S::kBBytes);
                     TmaLoad2D(sA + stage * S::kABytes, ta, &full[stage], (int32_t)(kb * kBK), rowA);
@@ -240,7 +241,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) GemmKernel(const __grid_const
         for (uint32_t t = cta; t < numTiles && ok; t += ctas) {
             uint32_t mb, nb;
             Policy::TileCoord(p, ctx, t, mBlocks, nBlocks, &mb, &nb);
-            ok = MbarWait(&tmemFull[acc], accPhase, abortWord);
+            ok = MbarWaitRelaxed(&tmemFull[acc], accPhase, abortWord, p.waitSleepNs);
             if (!ok) break;
             TcFenceAfter();
             const uint32_t rowInTile = ew * 32 + lane;

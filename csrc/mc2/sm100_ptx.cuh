@@ -73,6 +73,25 @@ __device__ __forceinline__ bool MbarWait(uint64_t *bar, uint32_t parity, volatil
     return true;
 }
 
+// Same wait for threads that are off the critical path (epilogue warps waiting for a whole tile, the producer waiting for a
+// free stage): between polls the thread sleeps `sleepNs`, so a 128-thread group does not burn issue slots (and power
+// under the board's cap) for the tens of microseconds a main loop takes.
+__device__ __forceinline__ bool MbarWaitRelaxed(uint64_t *bar, uint32_t parity, volatile uint32_t *abortWord, uint32_t sleepNs)
+{
+    uint64_t start = 0;
+    uint32_t spins = 0;
+    while (!MbarTryWait(bar, parity)) {
+        if (sleepNs) __nanosleep(sleepNs);
+        if ((++spins & 0xffu) == 0) {
+            uint64_t now;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+            if (start == 0) start = now;
+            if (*abortWord != 0 || now - start > 2000000000ull) { *abortWord = 1; return false; }
+        }
+    }
+    return true;
+}
+
 // ---------------------------------------------------------------------------------------------- TMA
 __device__ __forceinline__ void PrefetchTmap(const CUtensorMap *m)
 {

@@ -77,6 +77,20 @@ def test_multi_level_sequence_executors(topo):
             assert "Sequence" in msg
 
 
+@pytest.mark.parametrize("nranks", [24, 32])
+def test_flat_algorithms_at_the_rank_limit(nranks):
+    for op, algs in ALGOS.items():
+        for alg in algs:
+            rc, msg = check(CMD[op], alg, (1, 1, nranks), 1000, root=nranks - 1)
+            assert rc == 0, msg
+
+
+@pytest.mark.parametrize("topo", [(2, 2, 4), (1, 4, 8), (2, 4, 4)])
+def test_large_multi_level_allreduce(topo):
+    rc, msg = check(CMD["ALLREDUCE"], None, topo, 999)
+    assert rc == 0, msg
+
+
 def test_checker_catches_a_broken_schedule():
     # a scratch window too small for the one-shot slots must be reported as an overrun, not silently accepted
     rc, msg = check(CMD["ALLREDUCE"], "InsAllReduceMesh1DOneShot", (1, 1, 4), 128, ccl=700)

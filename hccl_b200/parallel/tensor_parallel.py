@@ -43,6 +43,23 @@ def _mm_nt(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return a @ w.t()
 
 
+_NATIVE_WGRAD = False
+
+
+def use_native_wgrad(flag: bool) -> None:
+    """True computes weight gradients on the tcgen05 GEMM (needs explicit transposes of both operands, because that kernel
+    takes K-major operands only); the default leaves this plain, collective-free GEMM with transposed operands to cuBLAS."""
+    global _NATIVE_WGRAD
+    _NATIVE_WGRAD = flag
+
+
+def _wgrad(dy: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    """dW[N, K] = dy[M, N]^T @ x[M, K]"""
+    if _NATIVE_WGRAD:
+        return _mm_nt(dy.t().contiguous(), x.t().contiguous())
+    return dy.t() @ x
+
+
 def all_gather_matmul(comm, x_local: torch.Tensor, w: torch.Tensor, want_gathered: bool = False):
     """-> (all_gather_rows(x_local) @ w.T, gathered rows or None)"""
     m, k = x_local.shape
@@ -100,7 +117,7 @@ class _ColumnSeqParallel(torch.autograd.Function):
         gathered, w = ctx.saved_tensors
         dy = dy.contiguous()
         dx = matmul_reduce_scatter(ctx.comm, dy, w.t().contiguous())          # RS(dy @ W): the mirror of the forward
-        dw = _mm_nt(dy.t().contiguous(), gathered.t().contiguous())             # dy^T @ AG(x)
+        dw = _wgrad(dy, gathered)                                               # dy^T @ AG(x)
         return dx, dw, None
 
 
@@ -117,7 +134,7 @@ class _RowSeqParallel(torch.autograd.Function):
     def backward(ctx, dy_local):
         x, w = ctx.saved_tensors
         dx, dyg = all_gather_matmul(ctx.comm, dy_local.contiguous(), w.t().contiguous(), want_gathered=True)   # AG(dy) @ W
-        dw = _mm_nt(dyg.t().contiguous(), x.t().contiguous())                                                  # AG(dy)^T @ x
+        dw = _wgrad(dyg, x)                                                                                    # AG(dy)^T @ x
         return dx, dw, None
 
 
@@ -133,7 +150,7 @@ class _RowAllReduce(torch.autograd.Function):
     def backward(ctx, dy):
         x, w = ctx.saved_tensors
         dy = dy.contiguous()
-        return _mm_nt(dy, w.t().contiguous()), _mm_nt(dy.t().contiguous(), x.t().contiguous()), None
+        return _mm_nt(dy, w.t().contiguous()), _wgrad(dy, x), None
 
 
 class _ColumnReplicatedInput(torch.autograd.Function):
@@ -150,7 +167,7 @@ class _ColumnReplicatedInput(torch.autograd.Function):
         x, w = ctx.saved_tensors
         dy = dy.contiguous()
         dx = matmul_all_reduce(ctx.comm, dy, w.t().contiguous())
-        return dx, _mm_nt(dy.t().contiguous(), x.t().contiguous()), None
+        return dx, _wgrad(dy, x), None
 
 
 # ---- modules -------------------------------------------------------------------------------------------------------

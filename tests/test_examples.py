@@ -8,7 +8,7 @@ import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 EX = os.path.join(ROOT, "examples")
-SAMPLES = ["send_recv", "batch_send_recv_ring", "allreduce", "broadcast", "allgather", "reduce_scatter", "reduce", "alltoall", "alltoallv",
+SAMPLES = ["comm_init_all", "send_recv", "batch_send_recv_ring", "allreduce", "broadcast", "allgather", "reduce_scatter", "reduce", "alltoall", "alltoallv",
            "alltoallvc", "scatter", "custom_allgather"]
 
 

@@ -294,6 +294,14 @@ SelectorStatus FromTable(const SelectorCtx &ctx, OpParam &p, HcclCommEngine eng)
 SelectorStatus IrDefault(const SelectorCtx &ctx, OpParam &p)
 {
     AlgoType forced = ForcedAlgo(ctx, p.opType);
+    // HCCL_DETERMINISTIC=strict (the reference's order-preserved executors, reference:
+    // src/ops/all_reduce/selector/all_reduce_auto_selector.cc:360-371): reductions use the flat mesh templates, whose
+    // fixed rank order makes an element's bits independent of count, chunking, topology level split and of which of the
+    // one-shot / two-shot forms the size selects. Ring / NHR / sequence requests are overridden for reductions.
+    const bool reduces = p.opType == HCCL_CMD_ALLREDUCE || p.opType == HCCL_CMD_REDUCE_SCATTER || p.opType == HCCL_CMD_REDUCE_SCATTER_V ||
+                         p.opType == HCCL_CMD_REDUCE;
+    const bool strict = ctx.env->deterministic == Deterministic::STRICT && reduces;
+    if (strict) forced = AlgoType::FULLMESH;
     // multi-level topologies use the sequence executors for the ops that have one
     if (ctx.topo->numLevels > 1 && forced == AlgoType::DEFAULT) {
         if (p.opType == HCCL_CMD_ALLREDUCE) { p.algName = "InsAllReduceSequenceMesh1DNhr"; return SelectorStatus::MATCH; }

@@ -163,3 +163,36 @@ def test_strict_dtype_rules_switch():
         env = dict(os.environ, HCCL_STRICT_DTYPE_RULES=strict, PYTHONPATH=root)
         res = subprocess.run([sys.executable, "-c", code], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=120)
         assert want in res.stdout, res.stdout[-2000:]
+
+
+def test_strict_determinism_overrides_ring_and_gives_identical_bits(monkeypatch):
+    """HCCL_DETERMINISTIC=strict: reductions run the rank-ordered mesh templates even when ring is requested, and the bits
+    are the same as without any algorithm request."""
+    import numpy as np
+
+    rng = np.random.default_rng(3)
+    xs = [(rng.standard_normal(30_000) * 10.0 ** rng.integers(-5, 5, 30_000)).astype(np.float32) for _ in range(4)]
+
+    def body(comm, rank):
+        alg = ctypes.create_string_buffer(128)
+        eng = ctypes.c_uint32()
+        assert lib().HcclQuerySelection(ctypes.c_void_p(comm.handle), ALLREDUCE, 30_000, FP32, 0, alg, 128, ctypes.byref(eng)) == 0
+        out = np.empty_like(xs[rank])
+        comm.all_reduce(xs[rank], out)
+        comm.synchronize()
+        return alg.value.decode(), out
+
+    monkeypatch.setenv("HCCL_ALGO", "level0:NA;level1:ring")
+    lib().HcclResetEnvConfigForTest()
+    ring = run_ranks(4, body)
+    monkeypatch.setenv("HCCL_DETERMINISTIC", "strict")
+    lib().HcclResetEnvConfigForTest()
+    strict = run_ranks(4, body)
+    monkeypatch.delenv("HCCL_ALGO")
+    lib().HcclResetEnvConfigForTest()
+    plain = run_ranks(4, body)
+    assert ring[0][0] == "InsAllReduceRing"
+    assert strict[0][0].startswith("InsAllReduceMesh1D") and plain[0][0].startswith("InsAllReduceMesh1D")
+    for r in range(4):
+        assert np.array_equal(strict[r][1].view(np.uint32), plain[r][1].view(np.uint32))
+        assert np.array_equal(strict[r][1].view(np.uint32), strict[0][1].view(np.uint32))

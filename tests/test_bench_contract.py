@@ -21,3 +21,12 @@ def test_graft_entry_exposes_build_and_smoke():
     import __graft_entry__ as g
 
     assert callable(g.build) and callable(g.smoke)
+
+
+def test_public_headers_compile_as_c99(tmp_path):
+    src = tmp_path / "hdr.c"
+    src.write_text("".join(f'#include "hccl/{h}"\n' for h in ("hccl.h", "hccl_comm.h", "hccl_types.h", "hccl_mc2.h", "hccl_moe.h", "hccl_dfx.h",
+                                                              "hccl_res.h", "hccl_graph_mode.h", "hccl_noalloc.h")) + "int main(void) { return 0; }\n")
+    res = subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", f"-I{ROOT / 'include'}", "-c", str(src), "-o", str(tmp_path / "hdr.o")],
+                         stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    assert res.returncode == 0, res.stdout

@@ -30,9 +30,8 @@ HcclResult HcomCheckDataType(HcclDataType t)
 // default this library accepts the superset its kernels implement.
 static bool StrictRules()
 {
-    static int v = -1;
-    if (v < 0) { const char *e = getenv("HCCL_STRICT_DTYPE_RULES"); v = (e && *e && *e != '0') ? 1 : 0; }
-    return v == 1;
+    static const bool v = [] { const char *e = getenv("HCCL_STRICT_DTYPE_RULES"); return e && *e && *e != '0'; }();
+    return v;
 }
 
 bool IsReduceDataTypeSupported(HcclDataType t)

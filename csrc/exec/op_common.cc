@@ -182,8 +182,7 @@ std::atomic<uint64_t> g_selectGeneration{1};
 
 bool FastEligible(const Comm *c, const OpParam &p)
 {
-    static int enabled = -1;
-    if (enabled < 0) { const char *e = getenv("HCCL_FAST_DISPATCH"); enabled = e ? atoi(e) : 1; }
+    static const bool enabled = [] { const char *e = getenv("HCCL_FAST_DISPATCH"); return e ? atoi(e) != 0 : true; }();
     if (!enabled) return false;
     if (c->backend != BackendKind::CUDA || p.mode != OpMode::OPBASE || c->env.entryLogEnable) return false;
     if (!p.sendCounts.empty() || !p.recvCounts.empty() || !p.items.empty()) return false;

@@ -1,4 +1,5 @@
 // Plain bf16 GEMM entry (C = A * B^T, both K-major) on the tcgen05 kernel, and the helpers the fused ops share.
+#include <atomic>
 #include <mutex>
 #include "../common/log.h"
 #include "gemm_host.h"
@@ -70,8 +71,7 @@ HcclResult GemmCheckError()
 // HCCL_GEMM_GROUP_M overrides the rasterisation group (row blocks, or row-block pairs for the CTA-pair kernel) for tuning runs.
 static uint32_t GroupMOverride(uint32_t dflt)
 {
-    static int v = -1;
-    if (v < 0) { const char *e = getenv("HCCL_GEMM_GROUP_M"); v = e ? atoi(e) : 0; }
+    static const int v = [] { const char *e = getenv("HCCL_GEMM_GROUP_M"); return e ? atoi(e) : 0; }();
     return v > 0 ? (uint32_t)v : dflt;
 }
 
@@ -80,9 +80,8 @@ static uint32_t GroupMOverride(uint32_t dflt)
 // critical path at every tile boundary), so sleeping saves no clock under the power cap.
 uint32_t GemmWaitSleepNs()
 {
-    static int v = -1;
-    if (v < 0) { const char *e = getenv("HCCL_GEMM_WAIT_SLEEP_NS"); v = e ? atoi(e) : 0; }
-    return (uint32_t)v;
+    static const int v = [] { const char *e = getenv("HCCL_GEMM_WAIT_SLEEP_NS"); return e ? atoi(e) : 0; }();
+    return (uint32_t)(v > 0 ? v : 0);
 }
 
 int SmCount()
@@ -101,7 +100,7 @@ template <int BN> static HcclResult LaunchPlain(const void *a, const void *b, vo
     CHK_RET(EncodeTmap2D(&p.tmapB, b, N, K, (uint64_t)K * 2, BN, kBK, 2));
     p.C = c; p.M = M; p.N = N; p.K = K; p.ldc = N; p.outFp32 = outFp32; p.groupM = GroupMOverride(16); p.errorWord = GemmErrorWord(); p.waitSleepNs = GemmWaitSleepNs();
     using S = GemmSmem<BN>;
-    static bool attrSet = false;
+    static std::atomic<bool> attrSet{false};
     auto kern = GemmKernel<BN, PlainPolicy, false>;
     size_t smem = S::kTotal + 1024;
     if (!attrSet) {
@@ -124,7 +123,7 @@ template <int BN> static HcclResult LaunchPlain2CtaT(const void *a, const void *
     CHK_RET(EncodeTmap2D(&p.tmapA, a, M, K, (uint64_t)K * 2, kBM, kBK, 2));
     CHK_RET(EncodeTmap2D(&p.tmapB, b, N, K, (uint64_t)K * 2, S::BN / 2, kBK, 2));
     p.C = c; p.M = M; p.N = N; p.K = K; p.ldc = N; p.outFp32 = outFp32; p.groupM = GroupMOverride(8); p.errorWord = GemmErrorWord();
-    static bool attrSet = false;
+    static std::atomic<bool> attrSet{false};
     auto kern = GemmKernel2Cta<PlainPolicy, BN>;
     size_t smem = S::kTotal + 1024;
     if (!attrSet) {
@@ -153,8 +152,7 @@ static HcclResult LaunchPlain2Cta(const void *a, const void *b, void *c, uint32_
     // 224-wide tiles when they waste fewer waves (e.g. N = 3584 = 16 x 224 on 74 CTA pairs)
     const uint64_t rowPairs = (M + 2 * kBM - 1) / (2 * kBM), pairs = (uint64_t)SmCount() / 2;
     auto cost = [&](uint32_t bn) { uint64_t tiles = rowPairs * ((N + bn - 1) / bn); return ((tiles + pairs - 1) / pairs) * bn; };
-    static int level = -1;
-    if (level < 0) { const char *e = getenv("HCCL_MC2_CTA_PAIR"); level = e ? atoi(e) : 1; }
+    static const int level = [] { const char *e = getenv("HCCL_MC2_CTA_PAIR"); return e ? atoi(e) : 1; }();
     if (level >= 2 && cost(224) < cost(256)) return LaunchPlain2CtaT<224>(a, b, c, M, N, K, outFp32, s);
     return LaunchPlain2CtaT<256>(a, b, c, M, N, K, outFp32, s);
 }
@@ -165,8 +163,7 @@ static HcclResult LaunchPlain2Cta(const void *a, const void *b, void *c, uint32_
 // one-CTA kernel measured faster (1313 against 1250 TFLOP/s on the 8192 x 28672 x 8192 pair of the single-GPU step).
 bool Gemm2CtaEnabled(uint64_t m, uint64_t n, uint64_t k)
 {
-    static int v = -2;
-    if (v == -2) { const char *e = getenv("HCCL_GEMM_2CTA"); v = e ? atoi(e) : -1; }
+    static const int v = [] { const char *e = getenv("HCCL_GEMM_2CTA"); return e ? atoi(e) : -1; }();
     if (v >= 0) return v != 0;
     return 2.0 * (double)m * (double)n * (double)k < 2.5e12;
 }

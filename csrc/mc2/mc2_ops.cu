@@ -2,6 +2,7 @@
 // Real communicators launch one kernel per rank (cooperatively, so every CTA of the op is resident); the emulation
 // entry launches one kernel for all ranks of a single-GPU world.
 #include <algorithm>
+#include <atomic>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -46,7 +47,7 @@ uint32_t CommCtasDefault()
 
 template <int BN, class Policy, bool EMU> HcclResult SetSmemAttr()
 {
-    static bool done = false;
+    static std::atomic<bool> done{false};
     if (!done) {
         auto kern = GemmKernel<BN, Policy, EMU>;
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN>::kTotal + 1024) != cudaSuccess) return HCCL_E_RUNTIME;
@@ -66,8 +67,7 @@ template <int BN, class Policy, bool EMU> HcclResult SetSmemAttr()
 // GEMMs are short and the pair kernels measured 0..3 % slower: 1.019-1.029 ms against 0.997-1.016 ms per step).
 int PairLevel(uint32_t nranks = 2)
 {
-    static int level = -2;
-    if (level == -2) { const char *e = getenv("HCCL_MC2_CTA_PAIR"); level = e ? atoi(e) : -1; }
+    static const int level = [] { const char *e = getenv("HCCL_MC2_CTA_PAIR"); return e ? atoi(e) : -1; }();
     if (level >= 0) return level;
     return nranks <= 2 ? 1 : 0;
 }
@@ -164,7 +164,7 @@ template <bool EMU> HcclResult LaunchFused(const FusedShape &s, const GemmParams
 // CTA-pair kernels: clusters of two CTAs, launched cooperatively (every CTA of the op resident) on an even grid.
 template <class Policy, int BN> HcclResult LaunchFusedPair(const GemmParams &p, uint32_t grid, cudaStream_t stream)
 {
-    static bool attrSet = false;
+    static std::atomic<bool> attrSet{false};
     auto kern = GemmKernel2Cta<Policy, BN>;
     const size_t smem = Gemm2CtaSmemT<BN>::kTotal + 1024;
     if (!attrSet) {

@@ -25,6 +25,8 @@ void SelectorRegistry::Register(HcclCMDType op, int priority, std::function<Auto
 }
 std::vector<AutoSelectorBase *> SelectorRegistry::Get(HcclCMDType op)
 {
+    static std::mutex mu;                    // selectors are instantiated on first use; ranks of one process race here
+    std::lock_guard<std::mutex> lk(mu);
     std::vector<AutoSelectorBase *> out;
     auto it = map_.find(op);
     if (it == map_.end()) return out;

@@ -62,7 +62,8 @@ def _ninja(build_file: Path, jobs: int | None = None, verbose: bool = False) -> 
 
 def build_native(verbose: bool = False, ptxas_info: bool = False, flavor: str = "") -> Path:
     """flavor "" = release; "debug" = device-side bounds checks on every heap access (-DHCCL_DEBUG_BOUNDS) and host asserts;
-    "asan" / "tsan" / "ubsan" = host code under Address-, Thread- or UndefinedBehaviorSanitizer. Flavors build into their own directory and library
+    "asan" / "tsan" / "ubsan" = host code under Address-, Thread- or UndefinedBehaviorSanitizer; "cov" = host code
+    instrumented for gcov (run tests with HCCL_B200_LIB pointing at it, then `gcov -o build_cov/obj <source>`). Flavors build into their own directory and library
     (libhccl_b200_<flavor>.so); load one by pointing HCCL_B200_LIB at it."""
     global BUILD
     release_build = BUILD
@@ -87,6 +88,8 @@ def _build_native(verbose: bool, ptxas_info: bool, flavor: str) -> Path:
         nvflags += ["-DHCCL_DEBUG_BOUNDS"]
     elif flavor == "asan":
         cxxflags += ["-fsanitize=address", "-fno-omit-frame-pointer"]
+    elif flavor == "cov":
+        cxxflags = [f for f in cxxflags if f != "-O2"] + ["-O0", "--coverage"]
     elif flavor == "tsan":
         cxxflags += ["-fsanitize=thread", "-fno-omit-frame-pointer"]
     elif flavor == "ubsan":
@@ -110,7 +113,7 @@ def _build_native(verbose: bool, ptxas_info: bool, flavor: str) -> Path:
         "  depfile = $out.d",
         "  deps = gcc",
         "rule link",
-        "  command = $nvcc -shared -o $out $in -cudart static -lpthread -ldl -lrt -Xlinker -soname=" + out.name + ({"asan": " -Xcompiler -fsanitize=address", "tsan": " -Xcompiler -fsanitize=thread", "ubsan": " -Xcompiler -fsanitize=undefined"}.get(flavor, "")),
+        "  command = $nvcc -shared -o $out $in -cudart static -lpthread -ldl -lrt -Xlinker -soname=" + out.name + ({"cov": " -Xcompiler --coverage", "asan": " -Xcompiler -fsanitize=address", "tsan": " -Xcompiler -fsanitize=thread", "ubsan": " -Xcompiler -fsanitize=undefined"}.get(flavor, "")),
     ]
     objs = []
     for src in cc + cu:

@@ -196,3 +196,34 @@ def test_strict_determinism_overrides_ring_and_gives_identical_bits(monkeypatch)
     for r in range(4):
         assert np.array_equal(strict[r][1].view(np.uint32), plain[r][1].view(np.uint32))
         assert np.array_equal(strict[r][1].view(np.uint32), strict[0][1].view(np.uint32))
+
+
+SM_ALGOS = {
+    ALLREDUCE: ["SmAllReduceMesh1DOneShot", "SmAllReduceMesh1DTwoShot", "NvlsAllReduceOneShot", "NvlsAllReduceTwoShot", "SmAllReducePipelined",
+                "NvlsAllReducePipelined", "SmAllReduceRing"],
+    ALLGATHER: ["SmAllGatherMesh1D", "SmAllGatherPush", "NvlsAllGatherPush"],
+    REDUCE_SCATTER: ["SmReduceScatterMesh1D", "NvlsReduceScatter", "SmReduceScatterPipelined", "NvlsReduceScatterPipelined"],
+    BROADCAST: ["SmBroadcastMesh1D", "NvlsBroadcast", "SmBroadcastPush", "NvlsBroadcastPush"],
+    ALLTOALL: ["SmAlltoAllMesh1D", "SmAlltoAllPush"],
+}
+OPNAME = {ALLREDUCE: "allreduce", ALLGATHER: "allgather", REDUCE_SCATTER: "reducescatter", BROADCAST: "broadcast", ALLTOALL: "alltoall"}
+
+
+@pytest.mark.parametrize("ranks", [2, 8])
+def test_launch_plans_of_every_device_algorithm(monkeypatch, ranks):
+    """The launch planner is pure host arithmetic: every SM / NVLS algorithm must produce a plan for small, mid and huge payloads
+    (one launch for the pipelined forms, a chunk loop for the scratch-bound ones) with a sane grid."""
+    for op, algs in SM_ALGOS.items():
+        for alg in algs:
+            monkeypatch.setenv("HCCL_ALGO_NAME", f"{OPNAME[op]}={alg}")
+            lib().HcclResetEnvConfigForTest()
+            for count in (8, 64 << 10, 16 << 20, 1 << 30):
+                name, eng, ctas, tasks, scratch = offline(op, count, BF16, ranks=ranks)
+                assert name == alg and eng in (3, 4), (alg, count, name)
+                assert 1 <= ctas <= 256 and tasks >= 1 and scratch > 0
+                if "Pipelined" in alg or "Push" in alg:
+                    assert tasks == 1 and ctas <= 128            # any payload in one launch
+                if count == 1 << 30 and alg in ("SmAllReduceMesh1DOneShot", "SmAllGatherMesh1D", "SmReduceScatterMesh1D"):
+                    assert tasks > 1                              # 2 GB does not fit the 200 MB scratch window
+    monkeypatch.delenv("HCCL_ALGO_NAME")
+    lib().HcclResetEnvConfigForTest()

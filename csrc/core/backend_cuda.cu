@@ -281,6 +281,15 @@ HcclResult CudaBackendInit(Comm *c)
     return c->boot->Barrier();
 }
 
+// Waits for every kernel and copy this rank has queued on its device. Called before the host barriers of destroy and
+// resume: once all ranks have passed such a barrier no kernel anywhere can still touch a peer's heap or flags.
+HcclResult CudaBackendQuiesce(Comm *c)
+{
+    RT_CHK(cudaSetDevice(c->device));
+    RT_CHK(cudaDeviceSynchronize());
+    return HCCL_SUCCESS;
+}
+
 HcclResult CudaBackendResetFlags(Comm *c)
 {
     RT_CHK(cudaSetDevice(c->device));
@@ -297,8 +306,8 @@ void CudaBackendDestroy(Comm *c)
     DriverApi &api = Drv();
     cudaSetDevice(c->device);
     cudaDeviceSynchronize();
-    // Multicast first: unmap the multicast VA, unbind this device's memory, drop the object. Peers do the same
-    // after the destroy barrier, so no rank leaves while its memory is still bound and in use by others.
+    // Multicast first: unmap the multicast VA, unbind this device's memory, drop the object. CommDestroy has drained
+    // every rank's device BEFORE its host barrier, so no peer kernel can still read or reduce through this binding.
     if (st->mcVa) { api.MemUnmap(st->mcVa, st->bytes); api.MemAddressFree(st->mcVa, st->bytes); }
     if (st->mcBound) api.MulticastUnbind(st->mc, st->cuDev, 0, st->bytes);
     if (st->mc) api.MemRelease(st->mc);

@@ -232,6 +232,24 @@ HcclResult CommCreate(uint32_t nranks, const HcclRootInfo *info, uint32_t rank, 
     return HCCL_SUCCESS;
 }
 
+// Ordered record of the teardown / resume steps of the communicators of this process ("rank:step,..."): lets a test
+// check that the device is drained before the host barrier and that mappings / flags change only after it.
+static std::mutex g_lifecycleMu;
+static std::string g_lifecycleLog;
+static void LifecycleNote(Comm *c, const char *step)
+{
+    std::lock_guard<std::mutex> lk(g_lifecycleMu);
+    if (g_lifecycleLog.size() > 16384) g_lifecycleLog.erase(0, 8192);
+    g_lifecycleLog += std::to_string(c->rank) + ":" + step + ",";
+}
+std::string LifecycleLogTake()
+{
+    std::lock_guard<std::mutex> lk(g_lifecycleMu);
+    std::string out;
+    out.swap(g_lifecycleLog);
+    return out;
+}
+
 HcclResult CommDestroy(Comm *c)
 {
     if (c == nullptr) return HCCL_E_PTR;
@@ -242,8 +260,12 @@ HcclResult CommDestroy(Comm *c)
     }
     StopWatchdog(c);
     if (c->worker) c->worker->Drain();
-    // Everyone reaches this point before any mapping goes away (a rank must not unmap memory a peer's kernel
-    // may still touch). A failed barrier (dead peer) is logged and teardown continues.
+    // Teardown order: (1) every rank drains its own device, (2) host barrier, (3) unmap / unbind. After (2) all ranks
+    // have finished (1), so no kernel anywhere can still load, store or multimem-reduce through a mapping that (3)
+    // removes. A failed barrier (dead peer) is logged and teardown continues.
+    LifecycleNote(c, "destroy:quiesce");
+    if (c->backend == BackendKind::CUDA) (void)CudaBackendQuiesce(c);
+    LifecycleNote(c, "destroy:barrier");
     if (c->boot && c->status.load() == HCCL_COMM_STATUS_READY) {
         LogPushErrorToWarn();
         (void)c->boot->Barrier();
@@ -254,6 +276,7 @@ HcclResult CommDestroy(Comm *c)
         if (kv.second.dev && c->backend == BackendKind::CUDA) CudaFreeDevice(kv.second.dev);
     }
     c->engineCtx.clear();
+    LifecycleNote(c, "destroy:unmap");
     if (c->backend == BackendKind::CUDA) CudaBackendDestroy(c); else SimBackendDestroy(c);
     if (c->boot) c->boot->Close();
     delete c;
@@ -326,12 +349,19 @@ HcclResult CommSuspend(Comm *c)
 // that no rank launches into half-cleared state.
 HcclResult CommResume(Comm *c)
 {
+    // Order: drain this rank's device, barrier, clear the own header, barrier. A peer that had passed the first barrier
+    // while still running a kernel could otherwise store a stale (large) flag into a header that was already zeroed.
     if (c->worker) c->worker->Drain();
+    LifecycleNote(c, "resume:quiesce");
+    if (c->backend == BackendKind::CUDA) CHK_RET(CudaBackendQuiesce(c));
+    LifecycleNote(c, "resume:barrier");
     CHK_RET(c->boot->Barrier());
+    LifecycleNote(c, "resume:clear");
     if (c->backend == BackendKind::CUDA) CHK_RET(CudaBackendResetFlags(c));
     else memset(c->heap[c->rank], 0, kHeapHeaderBytes);
     if (c->hostStatus) memset(c->hostStatus, 0, sizeof(DevStatus));
     c->remoteErrorRank = -1;
+    LifecycleNote(c, "resume:barrier");
     CHK_RET(c->boot->Barrier());
     c->status = HCCL_COMM_STATUS_READY;
     for (auto &cb : c->stateCallbacks) cb(HCCL_COMM_STATUS_READY);

@@ -147,9 +147,11 @@ void SimBackendDestroy(Comm *c);
 HcclResult CudaBackendInit(Comm *c);
 void CudaBackendDestroy(Comm *c);
 HcclResult CudaBackendResetFlags(Comm *c);
+HcclResult CudaBackendQuiesce(Comm *c);
 bool CudaDeviceAvailable(int *currentDevice);
 
 // ---- DFX
+std::string LifecycleLogTake();   // and clears it
 void RecordOp(Comm *c, const OpRecord &r);
 void StartWatchdog(Comm *c);
 void StopWatchdog(Comm *c);

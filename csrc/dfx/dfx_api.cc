@@ -218,6 +218,14 @@ HcclResult HcclDescribeEnvConfig(char *buf, uint32_t bufLen)
     return HCCL_SUCCESS;
 }
 
+HcclResult HcclTakeLifecycleLog(char *buf, uint32_t bufLen)
+{
+    if (!buf || bufLen == 0) return HCCL_E_PTR;
+    std::string s = LifecycleLogTake();
+    snprintf(buf, bufLen, "%s", s.c_str());
+    return HCCL_SUCCESS;
+}
+
 HcclResult HcclInjectBootstrapDrop(HcclComm comm, int n)
 {
     Comm *c = CommFromHandle(comm);

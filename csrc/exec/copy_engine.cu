@@ -5,6 +5,7 @@
 // Queue 0 runs on the caller's stream, further queues (BatchSendRecv) on helper streams forked / joined with events.
 // Every plan is bracketed by a notify barrier so that this engine can be mixed freely with the SM / NVLS kernels, whose
 // scratch-half parity lives on the device.
+#include "../common/launch_count.h"
 #include <cuda_runtime.h>
 #include <map>
 #include <mutex>
@@ -154,6 +155,7 @@ HcclResult CopyEngineRun(Comm *c, const Plan &plan, const ExecBuffers &bufs, cud
             }
             if (e != cudaSuccess) { HCCL_ERROR("copy engine: %s failed: %s", TaskTypeName(t.type), cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
             c->counters.kernelsLaunched++;
+            CountLaunch();
         }
     }
     for (size_t q = 1; q < nq; ++q) {

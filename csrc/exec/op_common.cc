@@ -1,3 +1,4 @@
+#include "../common/launch_count.h"
 #include "op_common.h"
 #include <atomic>
 #include <unordered_map>
@@ -212,6 +213,7 @@ HcclResult HcclExecOp(Comm *c, OpParam &p)
                 if (lr != HCCL_SUCCESS) return lr;
             }
             c->counters.kernelsLaunched += e.launches.size();
+            CountLaunch(e.launches.size());
             c->counters.chunkLoops += e.launches.size();
             c->counters.planCacheHits++;
             OpRecord rec{};

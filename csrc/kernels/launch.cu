@@ -1,5 +1,6 @@
 // Host side of the SM / NVLS engine: plan an operator into launches, issue them on the caller's stream, and the
 // single-GPU emulation harness used by the tests (all ranks on one device, one cooperative launch per chunk).
+#include "../common/launch_count.h"
 #include "launch.h"
 #include <cuda_runtime.h>
 #include <cstring>
@@ -60,6 +61,7 @@ HcclResult SmOrchestrate(Comm *c, OpParam &p, const std::string &algName)
             return lr;
         }
         c->counters.kernelsLaunched++;
+        CountLaunch();
         c->counters.chunkLoops++;
     }
     if (g_captureLaunches) *g_captureLaunches = std::move(launches);

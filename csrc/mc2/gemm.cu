@@ -1,4 +1,5 @@
 // Plain bf16 GEMM entry (C = A * B^T, both K-major) on the tcgen05 kernel, and the helpers the fused ops share.
+#include "../common/launch_count.h"
 #include <atomic>
 #include <mutex>
 #include "../common/log.h"
@@ -110,6 +111,7 @@ template <int BN> static HcclResult LaunchPlain(const void *a, const void *b, vo
     uint32_t tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
     uint32_t grid = std::min<uint32_t>(tiles, (uint32_t)SmCount());
     kern<<<grid, kGemmThreads, smem, s>>>(p, nullptr);
+    CountLaunch();
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { HCCL_ERROR("GEMM launch failed: %s", cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
     return HCCL_SUCCESS;
@@ -143,6 +145,7 @@ template <int BN> static HcclResult LaunchPlain2CtaT(const void *a, const void *
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
+    CountLaunch();
     if (e != cudaSuccess) { HCCL_ERROR("2-CTA GEMM launch failed: %s", cudaGetErrorString(e)); (void)cudaGetLastError(); return HCCL_E_RUNTIME; }
     return HCCL_SUCCESS;
 }
@@ -205,5 +208,7 @@ HcclResult HcclGemmBf16Variant(const void *a, const void *b, void *c, uint64_t m
 }
 
 HcclResult HcclGemmCheckError(void) { return GemmCheckError(); }
+
+uint64_t HcclGetKernelLaunchCount(void) { return KernelLaunchCounter().load(); }
 
 }  // extern "C"

@@ -1,6 +1,7 @@
 // Host side of the fused matmul + collective operators: argument checks, symmetric workspace, tensor maps, launch.
 // Real communicators launch one kernel per rank (cooperatively, so every CTA of the op is resident); the emulation
 // entry launches one kernel for all ranks of a single-GPU world.
+#include "../common/launch_count.h"
 #include <algorithm>
 #include <atomic>
 #include <map>
@@ -283,6 +284,7 @@ HcclResult RunFused(FusedKind kind, Comm *c, const void *a, const void *b, void 
         CHK_RET(LaunchFused<false>(s, p, nullptr, grid, 1, stream));
     }
     c->counters.kernelsLaunched++;
+    CountLaunch();
     c->counters.ops++;
     if (kind == AGMM && gathered) {
         CopyGatheredKernel<<<32, 512, 0, stream>>>(c->devCommPtr, wsOff, WorkspaceHalfBytes(s), (const char *)a, (char *)gathered, m * K * 2);

@@ -1,4 +1,5 @@
 // Host side of the MoE dispatch / combine operators: symmetric workspace layout, launches, emulation entry.
+#include "../common/launch_count.h"
 #include <cuda_fp8.h>
 #include <algorithm>
 #include "../common/log.h"
@@ -133,6 +134,7 @@ HcclResult HcclMoeDispatch(HcclMoeHandle handle, const void *x, const int32_t *t
     CHK_RET(LaunchMoe<false>(true, c->devCommPtr, a, nullptr, st->ctas, 1, stream));
     st->lastTokens = numTokens;
     c->counters.kernelsLaunched++;
+    CountLaunch();
     c->counters.ops++;
     char *ws = (char *)st->ws;
     if (recvX) *recvX = ws + st->L.recvX;
@@ -162,6 +164,7 @@ HcclResult HcclMoeCombine(HcclMoeHandle handle, const float *topkWeights, void *
     a.out = out;
     CHK_RET(LaunchMoe<false>(false, c->devCommPtr, a, nullptr, st->ctas, 1, stream));
     c->counters.kernelsLaunched++;
+    CountLaunch();
     c->counters.ops++;
     return HCCL_SUCCESS;
 }

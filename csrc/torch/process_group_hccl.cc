@@ -130,8 +130,15 @@ public:
     ~ProcessGroupHCCL() override
     {
         for (auto &kv : comms_) {
+            // work may still be queued on the private communication stream: let it finish before the communicator (and the
+            // peer mappings its kernels use) goes away
+            if (kv.second.cuda && kv.second.stream) {
+                cudaSetDevice(kv.second.device);
+                cudaStreamSynchronize(kv.second.stream);
+            }
             if (kv.second.comm) HcclCommDestroy(kv.second.comm);
             if (kv.second.inputReady) cudaEventDestroy(kv.second.inputReady);
+            if (kv.second.stream) cudaStreamDestroy(kv.second.stream);
         }
     }
     const std::string getBackendName() const override { return "hccl"; }

@@ -64,6 +64,8 @@ HcclResult HcclListAlgorithms(HcclCMDType op, char *buf, uint32_t bufLen);
 void HcclResetEnvConfigForTest(void);
 /* Re-parses every HCCL_* environment variable and writes the result as "key=value;..."; the parse error otherwise. */
 HcclResult HcclDescribeEnvConfig(char *buf, uint32_t bufLen);
+/* Ordered "rank:phase:step," record of communicator destroy / resume steps taken by this process since the last call. */
+HcclResult HcclTakeLifecycleLog(char *buf, uint32_t bufLen);
 HcclResult HcclInjectBootstrapDrop(HcclComm comm, int n);   /* next n bootstrap contributions of this rank vanish */
 
 #ifdef __cplusplus

@@ -52,6 +52,8 @@ HcclResult HcclGemmBf16(const void *a, const void *b, void *c, uint64_t m, uint6
 /* variant 0 = automatic, 1 = one-CTA 128 x BN tiles, 2 = 256 x 256 tiles on CTA pairs (tcgen05 cta_group::2) */
 HcclResult HcclGemmBf16Variant(const void *a, const void *b, void *c, uint64_t m, uint64_t n, uint64_t k, int outFp32, int variant, cudaStream_t stream);
 HcclResult HcclGemmCheckError(void);
+/* Kernels this library has launched in this process so far (all operators; benchmarks report the delta over a region). */
+uint64_t HcclGetKernelLaunchCount(void);
 
 /* out[nranks*mLocal, n] = AllGather_rows(aLocal[mLocal, k]) * b[n, k]^T. gathered (optional, [nranks*mLocal, k]) receives the
  * gathered activations for reuse in the backward pass. */

@@ -22,7 +22,13 @@
  *     calls issued on one stream are independent, but calls whose kernels could overlap on the GPU (different
  *     streams, different host threads) race on the scratch and must be serialised by the caller.
  *   - Asynchronous: returns after enqueueing on `stream`. Neither this function nor anything it calls allocates
- *     device or pinned host memory.
+ *     device or pinned host memory. The per-call tables travel to the device by value, as parameters of a small set-up
+ *     kernel, so no host memory of the caller has to outlive the call.
+ *   - The kernel's waits are bounded (2 s). A wait that runs out cannot be reported by the call that launched it, which
+ *     has long returned: it leaves a record in the scratch array. HcclLocalAllReduceNoAllocStatus copies those records
+ *     to host memory you supply (one 32-byte record per buffer pair, first word 0 = fine, 1 = a wait ran out); it does
+ *     not allocate either. Host threads may call both functions concurrently as far as the address look-up goes; the
+ *     rule about overlapping kernels above still applies.
  */
 #ifndef HCCL_B200_NOALLOC_H_
 #define HCCL_B200_NOALLOC_H_
@@ -40,6 +46,11 @@ extern "C" {
 /* recvBufs[i] = reduce over j of sendBufs[j], for every i < nBufs (sendBufs[i] == recvBufs[i] is allowed). */
 HcclResult HcclLocalAllReduceNoAlloc(const void *const *sendBufs, void *const *recvBufs, uint32_t nBufs, uint64_t count,
                                      HcclDataType dataType, HcclReduceOp op, cudaStream_t stream);
+
+
+/* Copies nRecords (1..HCCL_NOALLOC_MAX_BUFFERS) 32-byte status records {code, rank, peer, channel, phase, opSeq, observed,
+ * expected} of the most recent call into hostRecords, asynchronously on `stream` (synchronise it before reading). */
+HcclResult HcclLocalAllReduceNoAllocStatus(void *hostRecords, uint32_t nRecords, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

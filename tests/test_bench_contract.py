@@ -7,13 +7,17 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parents[1]
 
 
-def test_reference_arm_reports_unavailable_and_exits_zero():
+def test_reference_arm_without_a_gpu_reports_unavailable_and_exits_zero():
+    """On a GPU box the reference arm runs the unfused NCCL + cuBLAS baseline; without a device it must still exit 0 with
+    the one-line reason, and it must never import this package."""
     res = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--gpus", "1", "--steps", "2", "--warmup", "1"],
                          stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=120)
     assert res.returncode == 0, res.stderr[-2000:]
     line = [l for l in res.stdout.splitlines() if l.startswith("{")][-1]
     d = json.loads(line)
     assert d["impl"] == "reference" and isinstance(d["unavailable"], str) and "\n" not in d["unavailable"]
+    src = (ROOT / "bench.py").read_text()
+    assert "from hccl_b200" in src and src.index("if ours:\n        sys.path.insert") < src.index("from hccl_b200._lib")
 
 
 def test_graft_entry_exposes_build_and_smoke():

@@ -252,6 +252,37 @@ def test_suspend_resume_blocks_and_restores_operators():
     assert run_ranks(3, body) == [3.0, 3.0, 3.0]
 
 
+def _steps_of(log, rank, phase):
+    return [e.split(":")[2] for e in log.split(",") if e.startswith(f"{rank}:{phase}:")]
+
+
+def test_destroy_and_resume_drain_the_device_before_the_host_barrier():
+    """No rank may unmap memory (destroy) or clear its flags (resume) while a peer's kernel can still touch them: every rank
+    drains its own device first, THEN all meet at the host barrier, and only then mappings and flags change."""
+    buf = ctypes.create_string_buffer(1 << 16)
+    lib().HcclTakeLifecycleLog(buf, len(buf))              # drop what earlier tests left
+
+    def body(comm, rank):
+        x = np.ones(16, np.float32)
+        comm.all_reduce(x)
+        comm.synchronize()
+        comm.suspend()
+        comm.resume()
+
+    run_ranks(3, body)
+    assert lib().HcclTakeLifecycleLog(buf, len(buf)) == 0
+    log = buf.value.decode()
+    for r in range(3):
+        assert _steps_of(log, r, "resume") == ["quiesce", "barrier", "clear", "barrier"]
+        assert _steps_of(log, r, "destroy") == ["quiesce", "barrier", "unmap"]
+    # across ranks: every quiesce of a phase precedes every state change of that phase
+    events = [e for e in log.split(",") if e]
+    for phase, change in (("resume", "clear"), ("destroy", "unmap")):
+        last_quiesce = max(i for i, e in enumerate(events) if e.endswith(f"{phase}:quiesce"))
+        first_change = min(i for i, e in enumerate(events) if e.endswith(f"{phase}:{change}"))
+        assert last_quiesce < first_change
+
+
 def test_inconsistent_arguments_are_detected(monkeypatch):
     monkeypatch.setenv("HCCL_DFS_CONFIG", "inconsistent_check:every")
     lib().HcclResetEnvConfigForTest()

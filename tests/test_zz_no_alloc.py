@@ -33,7 +33,12 @@ def test_no_alloc_allreduce_matches_allocating_entry_twice():
         xs = [(torch.rand(count, generator=g, device="cuda") * 2 - 1).to(dtype) for _ in range(n)]
         outs = [torch.zeros_like(x) for x in xs]
         assert _call(l, xs, outs, dtype) == 0
+        # the status records of that call, copied into host memory this test owns: no wait ran out
+        records = (ctypes.c_uint32 * (8 * n))(*([7] * (8 * n)))
+        l.HcclLocalAllReduceNoAllocStatus.argtypes = [ctypes.c_void_p, ctypes.c_uint32, ctypes.c_void_p]
+        assert l.HcclLocalAllReduceNoAllocStatus(records, n, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)) == 0
         torch.cuda.synchronize()
+        assert all(records[8 * i] == 0 for i in range(n))
         with emu.EmuWorld(n, 512 << 10) as w:
             ref = [torch.zeros_like(x) for x in xs]
             assert w.run(2, "SmAllReduceMesh1DTwoShot", xs, ref, count, dtype, ReduceOp.SUM) == 0

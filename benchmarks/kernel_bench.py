@@ -57,6 +57,34 @@ def bench_gemm(a):
     print(json.dumps(res), flush=True)
 
 
+def bench_mxgemm(a):
+    """Block-scaled fp8 GEMM of this library against torch._scaled_mm (cuBLASLt fp8, one scale per tensor) and bf16 cuBLAS."""
+    from hccl_b200.ops import gemm, mxfp8 as mx
+
+    x = torch.randn(a.m, a.k, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(a.n, a.k, device="cuda") * 0.02).to(torch.bfloat16)
+    qa, qw = mx.quantize(x), mx.quantize(w)
+    out = torch.empty(a.m, a.n, device="cuda", dtype=torch.bfloat16)
+    flush = torch.empty(160 << 20, dtype=torch.uint8, device="cuda") if a.flush else None
+    ours = _time(lambda: mx.gemm(qa, qw, out=out, tile_n=a.variant), a.iters, flush=flush)
+    gemm.check_error()
+    quant = _time(lambda: mx.quantize(x, out=qa), a.iters, flush=flush)
+    flops = 2 * a.m * a.n * a.k
+    ref = mx.dequantize(qa) @ mx.dequantize(qw).t() if a.m * a.n <= (1 << 26) else None
+    res = {"case": "mxgemm", "tile_n": a.variant, "m": a.m, "n": a.n, "k": a.k, "ours_ms": round(ours, 4), "ours_tflops": round(flops / ours / 1e9, 1),
+           "quantize_ms": round(quant, 4)}
+    if ref is not None:
+        res["rel_err"] = float((out.float() - ref).abs().max() / ref.abs().max())
+    if not a.no_cublas:
+        one = torch.ones((), device="cuda")
+        x8, w8 = x.to(torch.float8_e4m3fn), w.to(torch.float8_e4m3fn)
+        o2 = torch.empty_like(out)
+        t8 = _time(lambda: torch._scaled_mm(x8, w8.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16, out=o2), a.iters, flush=flush)
+        t16 = _time(lambda: torch.matmul(x, w.t(), out=o2), a.iters, flush=flush)
+        res.update(scaled_mm_fp8_ms=round(t8, 4), scaled_mm_fp8_tflops=round(flops / t8 / 1e9, 1), cublas_bf16_ms=round(t16, 4))
+    print(json.dumps(res), flush=True)
+
+
 def bench_emu_allreduce(a):
     from hccl_b200.types import ReduceOp
     from hccl_b200.utils import emu
@@ -135,6 +163,10 @@ def main():
     g.add_argument("--m", type=int, default=8192); g.add_argument("--n", type=int, default=8192); g.add_argument("--k", type=int, default=4096)
     g.add_argument("--iters", type=int, default=10); g.add_argument("--flush", action="store_true"); g.add_argument("--no-cublas", action="store_true")
     g.add_argument("--variant", type=int, default=0, help="0 auto, 1 one-CTA tiles, 2 CTA-pair 256x256 tiles")
+    x = sub.add_parser("mxgemm")
+    x.add_argument("--m", type=int, default=8192); x.add_argument("--n", type=int, default=8192); x.add_argument("--k", type=int, default=4096)
+    x.add_argument("--iters", type=int, default=10); x.add_argument("--flush", action="store_true"); x.add_argument("--no-cublas", action="store_true")
+    x.add_argument("--variant", type=int, default=0, help="tile width: 0 auto, 128, 256")
     r = sub.add_parser("emu-allreduce")
     r.add_argument("--ranks", type=int, default=4); r.add_argument("--mb", type=int, default=64); r.add_argument("--dtype", default="fp32")
     r.add_argument("--alg", default="SmAllReduceMesh1DTwoShot"); r.add_argument("--ctas", type=int, default=32); r.add_argument("--iters", type=int, default=5)
@@ -145,7 +177,7 @@ def main():
     m.add_argument("--ranks", type=int, default=4); m.add_argument("--tokens", type=int, default=1024); m.add_argument("--experts", type=int, default=64)
     m.add_argument("--topk", type=int, default=8); m.add_argument("--hidden", type=int, default=4096); m.add_argument("--iters", type=int, default=5)
     a = ap.parse_args()
-    {"gemm": bench_gemm, "emu-allreduce": bench_emu_allreduce, "emu-fused": bench_emu_fused, "emu-moe": bench_emu_moe}[a.case](a)
+    {"gemm": bench_gemm, "mxgemm": bench_mxgemm, "emu-allreduce": bench_emu_allreduce, "emu-fused": bench_emu_fused, "emu-moe": bench_emu_moe}[a.case](a)
 
 
 if __name__ == "__main__":

@@ -17,7 +17,7 @@ namespace mc2 {
 // =============================================================================================== AllGather + matmul
 struct AgmmPolicy {
     using Ctx = FusedCtx;
-    // u64: 0 gatherOff (half 0), 1 gatherBytes per half, 2 aLocal
+    // u64: 0 gatherOff (half 0), 1 gatherBytes per half, 2 aLocal, 3 scale window (half 0) and 5 local scale atoms (block-scaled operands)
     // u32: 0 mLocal, 1 commCtas, 2 blocksPerRank, 3 pieces per 128-row block pushed by spare warps (0 = comm CTAs push whole blocks)
     __device__ static void Init(const GemmParams &p, Ctx &x) { FusedInit(p, x); }
     __device__ static uint32_t CommCtas(const GemmParams &p) { return p.u32[1]; }
@@ -35,23 +35,29 @@ struct AgmmPolicy {
         }
         __syncthreads();
         const uint32_t bpr = p.u32[2], n = (uint32_t)x.n, C = p.u32[1];
-        const uint64_t blockBytes = (uint64_t)kBM * p.K * 2;
-        const uint32_t pieces = (uint32_t)((blockBytes + PIECE - 1) / PIECE);
-        const char *aLocal = (const char *)p.u64[2];
-        const uint64_t gatherBase = p.u64[0] + (uint64_t)x.half * p.u64[1];
+        // Every (peer, 128-row block) item moves up to two segments: the rows themselves and, for block-scaled operands,
+        // the block's scale atoms (u64[3] = scale window of half 0 inside the heap, u64[5] = local scale array).
+        const uint32_t eb = p.elemBytes ? p.elemBytes : 2;
+        const uint64_t segBytes[2] = {(uint64_t)kBM * p.K * eb, p.u64[5] ? (uint64_t)(p.K / 128) * 512 : 0};
+        const char *segSrc[2] = {(const char *)p.u64[2], (const char *)p.u64[5]};
+        const uint64_t segDstBase[2] = {p.u64[0] + (uint64_t)x.half * p.u64[1], p.u64[3] + (uint64_t)x.half * p.u64[1]};
+        const uint32_t nseg = segBytes[1] ? 2 : 1;
         const uint32_t items = (n - 1) * bpr;
         const uint32_t warp = threadIdx.x >> 5;
         if (warp == 0 && ElectOne()) {            // loader: local shard -> shared memory ring
             uint32_t j = 0;
             for (uint32_t it = blockIdx.x; it < items; it += C) {
                 uint32_t blk = it % bpr;
-                const char *src = aLocal + (uint64_t)blk * blockBytes;
-                for (uint32_t q = 0; q < pieces; ++q, ++j) {
-                    uint32_t s = j % SLOTS, ph = (j / SLOTS) & 1;
-                    if (!MbarWait(&empty[s], ph ^ 1, abortWord)) return;
-                    uint32_t bytes = (uint32_t)(blockBytes - (uint64_t)q * PIECE < PIECE ? blockBytes - (uint64_t)q * PIECE : PIECE);
-                    MbarExpectTx(&full[s], bytes);
-                    BulkLoad(smem + s * PIECE, src + (uint64_t)q * PIECE, bytes, &full[s]);
+                for (uint32_t g = 0; g < nseg; ++g) {
+                    const char *src = segSrc[g] + (uint64_t)blk * segBytes[g];
+                    const uint32_t pieces = (uint32_t)((segBytes[g] + PIECE - 1) / PIECE);
+                    for (uint32_t q = 0; q < pieces; ++q, ++j) {
+                        uint32_t s = j % SLOTS, ph = (j / SLOTS) & 1;
+                        if (!MbarWait(&empty[s], ph ^ 1, abortWord)) return;
+                        uint32_t bytes = (uint32_t)(segBytes[g] - (uint64_t)q * PIECE < PIECE ? segBytes[g] - (uint64_t)q * PIECE : PIECE);
+                        MbarExpectTx(&full[s], bytes);
+                        BulkLoad(smem + s * PIECE, src + (uint64_t)q * PIECE, bytes, &full[s]);
+                    }
                 }
             }
         } else if (warp == 1 && ElectOne()) {     // storer: ring -> the peer's gather buffer, then bump its counter
@@ -59,15 +65,18 @@ struct AgmmPolicy {
             for (uint32_t it = blockIdx.x; it < items; it += C) {
                 uint32_t d = it / bpr + 1, blk = it % bpr;
                 uint32_t peer = ((uint32_t)x.rank + d) % n;
-                char *dst = x.c->heap[peer] + gatherBase + ((uint64_t)x.rank * p.u32[0] + (uint64_t)blk * kBM) * p.K * 2;
-                for (uint32_t q = 0; q < pieces; ++q, ++j) {
-                    uint32_t s = j % SLOTS, ph = (j / SLOTS) & 1;
-                    if (!MbarWait(&full[s], ph, abortWord)) return;
-                    uint32_t bytes = (uint32_t)(blockBytes - (uint64_t)q * PIECE < PIECE ? blockBytes - (uint64_t)q * PIECE : PIECE);
-                    BulkStore(dst + (uint64_t)q * PIECE, smem + s * PIECE, bytes);
-                    TmaStoreCommit();
-                    BulkWaitRead<1>();             // every piece before this one has left shared memory
-                    for (; rel < j; ++rel) MbarArrive(&empty[rel % SLOTS]);
+                for (uint32_t g = 0; g < nseg; ++g) {
+                    char *dst = x.c->heap[peer] + segDstBase[g] + ((uint64_t)x.rank * bpr + blk) * segBytes[g];
+                    const uint32_t pieces = (uint32_t)((segBytes[g] + PIECE - 1) / PIECE);
+                    for (uint32_t q = 0; q < pieces; ++q, ++j) {
+                        uint32_t s = j % SLOTS, ph = (j / SLOTS) & 1;
+                        if (!MbarWait(&full[s], ph, abortWord)) return;
+                        uint32_t bytes = (uint32_t)(segBytes[g] - (uint64_t)q * PIECE < PIECE ? segBytes[g] - (uint64_t)q * PIECE : PIECE);
+                        BulkStore(dst + (uint64_t)q * PIECE, smem + s * PIECE, bytes);
+                        TmaStoreCommit();
+                        BulkWaitRead<1>();             // every piece before this one has left shared memory
+                        for (; rel < j; ++rel) MbarArrive(&empty[rel % SLOTS]);
+                    }
                 }
                 TmaStoreWaitAll();                 // every byte of this block is written at the peer
                 for (; rel < j; ++rel) MbarArrive(&empty[rel % SLOTS]);
@@ -95,7 +104,7 @@ struct AgmmPolicy {
         if (P == 0) return;
         const uint32_t bpr = p.u32[2], n = (uint32_t)x.n;
         const uint32_t items = (n - 1) * bpr * P, worker = cta * 2 + which, workers = ctas * 2;
-        const uint64_t rowBytes = (uint64_t)p.K * 2, pieceRows = kBM / P, pieceBytes = pieceRows * rowBytes;
+        const uint64_t rowBytes = (uint64_t)p.K * (p.elemBytes ? p.elemBytes : 2), pieceRows = kBM / P, pieceBytes = pieceRows * rowBytes;
         const char *aLocal = (const char *)p.u64[2];
         const uint64_t gatherBase = p.u64[0] + (uint64_t)x.half * p.u64[1];
         for (uint32_t it = worker; it < items; it += workers) {
@@ -146,6 +155,14 @@ struct AgmmPolicy {
         const uint32_t bpr = p.u32[2], src = mb / bpr, blk = mb % bpr;
         if ((int)src == x.rank) { *tm = &p.tmapALocal; *row = (int32_t)(blk * kBM); }
         else { *tm = x.half ? &p.tmapA1 : &p.tmapA; *row = (int32_t)(mb * kBM); }
+    }
+    // block-scaled operands: scale atoms of row block mb -- the local array for the own rows, the gathered window otherwise
+    __device__ static const uint8_t *SelectSfA(const GemmParams &p, const Ctx &x, uint32_t mb)
+    {
+        const uint32_t bpr = p.u32[2], src = mb / bpr, blk = mb % bpr;
+        const uint64_t blockSf = (uint64_t)(p.K / 128) * 512;
+        if ((int)src == x.rank) return (const uint8_t *)p.u64[5] + (uint64_t)blk * blockSf;
+        return (const uint8_t *)x.heap + p.u64[3] + (uint64_t)x.half * p.u64[1] + (uint64_t)mb * blockSf;
     }
     __device__ static bool UseDirect(const GemmParams &) { return false; }
     __device__ static void Store(const GemmParams &, const Ctx &, uint32_t, uint32_t, const uint32_t (&)[32]) {}
@@ -232,6 +249,7 @@ struct MmrsPolicy {
         *tm = &p.tmapA;
         *row = (int32_t)(mb * kBM);
     }
+    __device__ static const uint8_t *SelectSfA(const GemmParams &p, const Ctx &, uint32_t mb) { return p.sfA + (uint64_t)mb * (p.K / 128) * 512; }
     __device__ static bool UseDirect(const GemmParams &) { return false; }
     __device__ static void Store(const GemmParams &, const Ctx &, uint32_t, uint32_t, const uint32_t (&)[32]) {}
     // Tiles of rows owned by a peer: the bf16 partial goes into slot[rank] of the owner's workspace. Tiles of the own
@@ -322,6 +340,7 @@ struct MmarPolicy {
         *tm = &p.tmapA;
         *row = (int32_t)(mb * kBM);
     }
+    __device__ static const uint8_t *SelectSfA(const GemmParams &p, const Ctx &, uint32_t mb) { return p.sfA + (uint64_t)mb * (p.K / 128) * 512; }
     __device__ static bool UseDirect(const GemmParams &) { return false; }
     __device__ static void Store(const GemmParams &, const Ctx &, uint32_t, uint32_t, const uint32_t (&)[32]) {}
     __device__ static __nv_bfloat16 *RowDst(const GemmParams &p, const Ctx &x, uint32_t row, uint32_t col)

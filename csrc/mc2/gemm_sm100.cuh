@@ -52,6 +52,11 @@ struct GemmParams {
     const void *comm;            // DevComm* of this rank (fused policies)
     uint64_t u64[8];
     uint32_t u32[8];
+    // block-scaled (MXFP8) kernels: e8m0 scale atoms of A and B, [rows / 128][K / 128][512 bytes]
+    const uint8_t *sfA;
+    const uint8_t *sfB;
+    uint32_t sfAtomsB;           // 128-row atoms B's scale array holds along N
+    uint32_t elemBytes;          // operand element size (0 or 2 = bf16, 1 = fp8)
 };
 
 template <int BN> struct GemmSmem {
@@ -119,6 +124,8 @@ struct PlainPolicy {
         *tm = &p.tmapA;
         *row = (int32_t)(mb * kBM);
     }
+    // block-scaled kernels: the scale atoms (512 bytes per 128 rows x 128 K) of row block mb, K block 0
+    __device__ static const uint8_t *SelectSfA(const GemmParams &p, const Ctx &, uint32_t mb) { return p.sfA + (uint64_t)mb * (p.K / 128) * 512; }
     // fp32 output goes straight from registers; bf16 output is staged through shared memory and written as whole
     // 16-byte chunks of contiguous row segments
     __device__ static bool UseDirect(const GemmParams &p) { return p.outFp32 != 0; }

@@ -14,6 +14,7 @@
 #include "../kernels/emu_world.h"
 #include "fused_policies.cuh"
 #include "gemm_sm100_2cta.cuh"
+#include "gemm_sm100_mx.cuh"
 #include "gemm_host.h"
 #include "hccl/hccl_mc2.h"
 
@@ -28,13 +29,17 @@ struct FusedShape {
     FusedKind kind;
     uint32_t n, rank;
     uint64_t m, N, K;          // AGMM: m = mLocal; MMRS/MMAR: m = full M, K = kLocal
+    bool mx = false;           // block-scaled fp8 operands (e4m3 + e8m0 scale atoms) instead of bf16
 };
+
+// bytes of the scale atoms that go with `rows` x K block-scaled elements (rows a multiple of 128)
+uint64_t SfBytes(uint64_t rows, uint64_t K) { return ((rows + 127) / 128) * (K / 128) * 512; }
 
 // workspace bytes per parity half
 uint64_t WorkspaceHalfBytes(const FusedShape &s)
 {
     switch (s.kind) {
-        case AGMM: return (uint64_t)s.n * s.m * s.K * 2;
+        case AGMM: return s.mx ? (uint64_t)s.n * s.m * s.K + SfBytes((uint64_t)s.n * s.m, s.K) : (uint64_t)s.n * s.m * s.K * 2;
         case MMRS: return (uint64_t)s.m * s.N * 2;                       // n slots of (m/n) x N
         default: return (uint64_t)s.n * s.m * (s.N / s.n) * 2 + (uint64_t)s.m * s.N * 2;   // partial slots + result window
     }
@@ -44,6 +49,17 @@ uint32_t CommCtasDefault()
 {
     if (const char *e = getenv("HCCL_MC2_COMM_CTAS")) { int v = atoi(e); if (v > 0 && v < 64) return (uint32_t)v; }
     return 8;
+}
+
+template <int BN, class Policy, bool EMU> HcclResult SetSmemAttrMx()
+{
+    static std::atomic<bool> done{false};
+    if (!done) {
+        auto kern = GemmKernelMx<BN, Policy, EMU>;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmMxSmem<BN>::kTotal + 1024) != cudaSuccess) return HCCL_E_RUNTIME;
+        done = true;
+    }
+    return HCCL_SUCCESS;
 }
 
 template <int BN, class Policy, bool EMU> HcclResult SetSmemAttr()
@@ -75,6 +91,7 @@ int PairLevel(uint32_t nranks = 2)
 
 bool PairModeFor(const FusedShape &s)
 {
+    if (s.mx) return false;                              // the block-scaled kernels are one-CTA
     if (PairLevel(s.n) <= 0 || s.N < 256) return false;
     if (s.kind == AGMM) return (s.m / kBM) % 2 == 0;
     if (s.kind == MMRS) return (s.m / s.n / kBM) % 2 == 0;
@@ -86,6 +103,46 @@ uint32_t PairTileN(uint64_t rowPairs, uint64_t N, uint32_t pairs)
 {
     auto cost = [&](uint32_t bn) { uint64_t tiles = rowPairs * ((N + bn - 1) / bn); return ((tiles + pairs - 1) / pairs) * bn; };
     return PairLevel() >= 2 && cost(224) < cost(256) ? 224u : 256u;
+}
+
+// Block-scaled form: a / b are e4m3 payloads, sfa / sfb their scale atoms; 256-wide tiles (128-wide for MatmulAllReduce).
+HcclResult BuildParamsMx(const FusedShape &s, char *heapLocal, uint64_t wsOff, const void *a, const void *sfa, const void *b, const void *sfb, void *out,
+                         uint32_t commCtas, GemmParams *p)
+{
+    memset(p, 0, sizeof(*p));
+    const uint64_t half = WorkspaceHalfBytes(s);
+    p->errorWord = GemmErrorWord();
+    p->groupM = 16;
+    p->elemBytes = 1;
+    p->sfA = (const uint8_t *)sfa;
+    p->sfB = (const uint8_t *)sfb;
+    p->sfAtomsB = (uint32_t)((s.N + 127) / 128);
+    p->N = (uint32_t)s.N; p->K = (uint32_t)s.K; p->ldc = (uint32_t)s.N; p->C = out;
+    if (s.kind == AGMM) {
+        p->M = (uint32_t)(s.n * s.m);
+        const uint64_t payload = (uint64_t)s.n * s.m * s.K;
+        CHK_RET(EncodeTmap2D(&p->tmapA, heapLocal + wsOff, p->M, s.K, s.K, kBM, kMxBK, 1));
+        CHK_RET(EncodeTmap2D(&p->tmapA1, heapLocal + wsOff + half, p->M, s.K, s.K, kBM, kMxBK, 1));
+        CHK_RET(EncodeTmap2D(&p->tmapALocal, a, s.m, s.K, s.K, kBM, kMxBK, 1));
+        CHK_RET(EncodeTmap2D(&p->tmapB, b, s.N, s.K, s.K, 256, kMxBK, 1));
+        p->u64[0] = wsOff; p->u64[1] = half; p->u64[2] = (uint64_t)(uintptr_t)a; p->u64[3] = wsOff + payload; p->u64[5] = (uint64_t)(uintptr_t)sfa;
+        p->u32[0] = (uint32_t)s.m; p->u32[1] = commCtas; p->u32[2] = (uint32_t)(s.m / kBM);
+    } else if (s.kind == MMRS) {
+        p->M = (uint32_t)s.m;
+        CHK_RET(EncodeTmap2D(&p->tmapA, a, s.m, s.K, s.K, kBM, kMxBK, 1));
+        CHK_RET(EncodeTmap2D(&p->tmapB, b, s.N, s.K, s.K, 256, kMxBK, 1));
+        p->u64[0] = wsOff; p->u64[1] = half;
+        p->u32[0] = (uint32_t)(s.m / s.n); p->u32[1] = (uint32_t)(s.m / s.n / kBM); p->u32[2] = (uint32_t)((s.N + 255) / 256);
+    } else {
+        const uint32_t colsOwn = (uint32_t)(s.N / s.n);
+        p->M = (uint32_t)s.m;
+        CHK_RET(EncodeTmap2D(&p->tmapA, a, s.m, s.K, s.K, kBM, kMxBK, 1));
+        CHK_RET(EncodeTmap2D(&p->tmapB, b, s.N, s.K, s.K, 128, kMxBK, 1));
+        const uint64_t partials = (uint64_t)s.n * s.m * colsOwn * 2, result = (uint64_t)s.m * s.N * 2;
+        p->u64[0] = wsOff; p->u64[1] = partials; p->u64[2] = wsOff + 2 * partials; p->u64[3] = result;
+        p->u32[0] = colsOwn; p->u32[1] = colsOwn / 128; p->u32[2] = 128;
+    }
+    return HCCL_SUCCESS;
 }
 
 HcclResult BuildParams(const FusedShape &s, char *heapLocal, uint64_t wsOff, const void *a, const void *b, void *out, uint32_t commCtas, GemmParams *p,
@@ -130,7 +187,7 @@ uint32_t GridFor(const FusedShape &s, uint32_t commCtas, uint32_t maxCtas)
     uint64_t tiles;
     if (s.kind == AGMM) tiles = (s.n * s.m / kBM) * ((s.N + 255) / 256);
     else if (s.kind == MMRS) tiles = ((s.m + kBM - 1) / kBM) * ((s.N + 255) / 256);
-    else tiles = ((s.m + kBM - 1) / kBM) * (s.N / 64);
+    else tiles = ((s.m + kBM - 1) / kBM) * (s.N / (s.mx ? 128 : 64));
     uint32_t g = (uint32_t)std::min<uint64_t>(tiles + commCtas, maxCtas);
     return std::max(g, commCtas + 1);
 }
@@ -141,7 +198,12 @@ HcclResult CheckShape(const FusedShape &s)
     if (s.kind == AGMM && s.m % kBM) { HCCL_ERROR("AllGatherMatmul: rows per rank (%llu) must be a multiple of 128", (unsigned long long)s.m); return HCCL_E_PARA; }
     if (s.kind == AGMM && s.m / kBM > 64) { HCCL_ERROR("AllGatherMatmul: at most 8192 rows per rank"); return HCCL_E_PARA; }
     if (s.kind == MMRS && (s.m % ((uint64_t)s.n * kBM) || s.m / s.n / kBM > 64)) { HCCL_ERROR("MatmulReduceScatter: M (%llu) must be a multiple of 128 x ranks, at most 8192 rows per rank", (unsigned long long)s.m); return HCCL_E_PARA; }
-    if (s.kind == MMAR && (s.N % ((uint64_t)s.n * 64) || ((s.m + kBM - 1) / kBM) * (s.N / s.n / 64) > 64)) {
+    if (s.mx && s.K % 128) { HCCL_ERROR("block-scaled fused matmul: K (%llu) must be a multiple of 128", (unsigned long long)s.K); return HCCL_E_PARA; }
+    if (s.mx && s.kind == MMAR && (s.N % ((uint64_t)s.n * 128) || ((s.m + kBM - 1) / kBM) * (s.N / s.n / 128) > 64)) {
+        HCCL_ERROR("block-scaled MatmulAllReduce: N (%llu) must be a multiple of 128 x ranks", (unsigned long long)s.N);
+        return HCCL_E_PARA;
+    }
+    if (!s.mx && s.kind == MMAR && (s.N % ((uint64_t)s.n * 64) || ((s.m + kBM - 1) / kBM) * (s.N / s.n / 64) > 64)) {
         HCCL_ERROR("MatmulAllReduce: N (%llu) must be a multiple of 64 x ranks and the tiles per owner at most 64", (unsigned long long)s.N);
         return HCCL_E_PARA;
     }
@@ -152,6 +214,11 @@ template <bool EMU> HcclResult LaunchFused(const FusedShape &s, const GemmParams
 {
     const void *fn = nullptr;
     size_t smem = 0;
+    if (s.mx) {
+        if (s.kind == AGMM) { CHK_RET((SetSmemAttrMx<256, AgmmPolicy, EMU>())); fn = (const void *)GemmKernelMx<256, AgmmPolicy, EMU>; smem = GemmMxSmem<256>::kTotal + 1024; }
+        else if (s.kind == MMRS) { CHK_RET((SetSmemAttrMx<256, MmrsPolicy, EMU>())); fn = (const void *)GemmKernelMx<256, MmrsPolicy, EMU>; smem = GemmMxSmem<256>::kTotal + 1024; }
+        else { CHK_RET((SetSmemAttrMx<128, MmarPolicy, EMU>())); fn = (const void *)GemmKernelMx<128, MmarPolicy, EMU>; smem = GemmMxSmem<128>::kTotal + 1024; }
+    } else
     if (s.kind == AGMM) { CHK_RET((SetSmemAttr<256, AgmmPolicy, EMU>())); fn = (const void *)GemmKernel<256, AgmmPolicy, EMU>; smem = GemmSmem<256>::kTotal + 1024; }
     else if (s.kind == MMRS) { CHK_RET((SetSmemAttr<256, MmrsPolicy, EMU>())); fn = (const void *)GemmKernel<256, MmrsPolicy, EMU>; smem = GemmSmem<256>::kTotal + 1024; }
     else { CHK_RET((SetSmemAttr<64, MmarPolicy, EMU>())); fn = (const void *)GemmKernel<64, MmarPolicy, EMU>; smem = GemmSmem<64>::kTotal + 1024; }
@@ -191,8 +258,12 @@ template <class Policy, int BN> HcclResult LaunchFusedPair(const GemmParams &p, 
 
 // ---- symmetric workspace per communicator (grown on demand; every rank makes the same calls, so offsets agree)
 struct ParamKey {
-    int kind; const void *a, *b, *out; uint64_t m, N, K, wsOff;     // kind + 16 = parameters of the CTA-pair kernel
-    bool operator<(const ParamKey &o) const { return std::tie(kind, a, b, out, m, N, K, wsOff) < std::tie(o.kind, o.a, o.b, o.out, o.m, o.N, o.K, o.wsOff); }
+    int kind; const void *a, *b, *out; uint64_t m, N, K, wsOff;     // kind + pair tile width = parameters of the CTA-pair kernel
+    const void *sfa = nullptr, *sfb = nullptr;                     // block-scaled operands (kind + 1000)
+    bool operator<(const ParamKey &o) const
+    {
+        return std::tie(kind, a, b, out, m, N, K, wsOff, sfa, sfb) < std::tie(o.kind, o.a, o.b, o.out, o.m, o.N, o.K, o.wsOff, o.sfa, o.sfb);
+    }
 };
 // Encoded tensor maps are reused while the same buffers and shapes come back (decode loops, training steps): encoding four
 // maps costs more host time than a decode-sized fused kernel runs.
@@ -243,11 +314,12 @@ void DropWorkspace(Comm *c)
     g_ws.erase(c);
 }
 
-HcclResult RunFused(FusedKind kind, Comm *c, const void *a, const void *b, void *out, void *gathered, uint64_t m, uint64_t N, uint64_t K, cudaStream_t stream)
+HcclResult RunFused(FusedKind kind, Comm *c, const void *a, const void *b, void *out, void *gathered, uint64_t m, uint64_t N, uint64_t K, cudaStream_t stream,
+                    const void *sfa = nullptr, const void *sfb = nullptr)
 {
     CHK_RET(CommCheckReady(c));
     if (c->backend != BackendKind::CUDA) { HCCL_ERROR("fused matmul operators need a CUDA communicator"); return HCCL_E_NOT_SUPPORT; }
-    FusedShape s{kind, c->nranks, c->rank, m, N, K};
+    FusedShape s{kind, c->nranks, c->rank, m, N, K, sfa != nullptr};
     CHK_RET(CheckShape(s));
     uint64_t wsOff = 0;
     CHK_RET(EnsureWorkspace(c, 2 * WorkspaceHalfBytes(s) + 4096, &wsOff));
@@ -261,11 +333,12 @@ HcclResult RunFused(FusedKind kind, Comm *c, const void *a, const void *b, void 
     {
         std::lock_guard<std::mutex> lk(g_wsMu);
         auto &cache = g_ws[c].params;
-        ParamKey key{(int)kind + (int)pairBN, a, b, out, m, N, K, wsOff};
+        ParamKey key{(int)kind + (int)pairBN + (s.mx ? 1000 : 0), a, b, out, m, N, K, wsOff, sfa, sfb};
         auto it = cache.find(key);
         if (it != cache.end()) p = it->second;
         else {
-            CHK_RET(BuildParams(s, c->heap[c->rank], wsOff, a, b, out, commCtas, &p, pairBN));
+            if (s.mx) CHK_RET(BuildParamsMx(s, c->heap[c->rank], wsOff, a, sfa, b, sfb, out, commCtas, &p));
+            else CHK_RET(BuildParams(s, c->heap[c->rank], wsOff, a, b, out, commCtas, &p, pairBN));
             p.comm = c->devCommPtr;
             if (cache.size() > 256) cache.clear();
             cache[key] = p;
@@ -286,7 +359,7 @@ HcclResult RunFused(FusedKind kind, Comm *c, const void *a, const void *b, void 
     c->counters.kernelsLaunched++;
     CountLaunch();
     c->counters.ops++;
-    if (kind == AGMM && gathered) {
+    if (kind == AGMM && gathered && !s.mx) {
         CopyGatheredKernel<<<32, 512, 0, stream>>>(c->devCommPtr, wsOff, WorkspaceHalfBytes(s), (const char *)a, (char *)gathered, m * K * 2);
         if (cudaGetLastError() != cudaSuccess) return HCCL_E_RUNTIME;
     }
@@ -335,6 +408,63 @@ HcclResult HcclMatmulAllReduce(const void *a, const void *b, void *out, uint64_t
     if (dataType != HCCL_DATA_TYPE_BFP16) return HCCL_E_NOT_SUPPORT;
     if (c->nranks == 1) return HcclGemmBf16(a, b, out, m, n, kLocal, 0, stream);
     return RunFused(MMAR, c, a, b, out, nullptr, m, n, kLocal, stream);
+}
+
+// ---- block-scaled (MXFP8) forms: e4m3 payloads with e8m0 scale atoms as written by HcclQuantizeMxfp8; bf16 results.
+HcclResult HcclAllGatherMatmulMxfp8(const void *aLocal, const void *sfaLocal, const void *b, const void *sfb, void *out, uint64_t mLocal, uint64_t n,
+                                    uint64_t k, HcclComm comm, cudaStream_t stream)
+{
+    Comm *c = CommFromHandle(comm);
+    if (!c) return HCCL_E_PTR;
+    if (!aLocal || !sfaLocal || !b || !sfb || !out) { HCCL_ERROR("[EI0003] HcclAllGatherMatmulMxfp8: null buffer"); return HCCL_E_PTR; }
+    if (c->nranks == 1) return HcclGemmMxfp8(aLocal, sfaLocal, b, sfb, out, mLocal, n, k, 0, stream);
+    return RunFused(AGMM, c, aLocal, b, out, nullptr, mLocal, n, k, stream, sfaLocal, sfb);
+}
+
+HcclResult HcclMatmulReduceScatterMxfp8(const void *a, const void *sfa, const void *b, const void *sfb, void *out, uint64_t m, uint64_t n, uint64_t kLocal,
+                                        HcclComm comm, cudaStream_t stream)
+{
+    Comm *c = CommFromHandle(comm);
+    if (!c) return HCCL_E_PTR;
+    if (!a || !sfa || !b || !sfb || !out) { HCCL_ERROR("[EI0003] HcclMatmulReduceScatterMxfp8: null buffer"); return HCCL_E_PTR; }
+    if (c->nranks == 1) return HcclGemmMxfp8(a, sfa, b, sfb, out, m, n, kLocal, 0, stream);
+    return RunFused(MMRS, c, a, b, out, nullptr, m, n, kLocal, stream, sfa, sfb);
+}
+
+HcclResult HcclMatmulAllReduceMxfp8(const void *a, const void *sfa, const void *b, const void *sfb, void *out, uint64_t m, uint64_t n, uint64_t kLocal,
+                                    HcclComm comm, cudaStream_t stream)
+{
+    Comm *c = CommFromHandle(comm);
+    if (!c) return HCCL_E_PTR;
+    if (!a || !sfa || !b || !sfb || !out) { HCCL_ERROR("[EI0003] HcclMatmulAllReduceMxfp8: null buffer"); return HCCL_E_PTR; }
+    if (c->nranks == 1) return HcclGemmMxfp8(a, sfa, b, sfb, out, m, n, kLocal, 0, stream);
+    return RunFused(MMAR, c, a, b, out, nullptr, m, n, kLocal, stream, sfa, sfb);
+}
+
+// Emulation of the block-scaled forms (same conventions as HcclEmuFusedRun; sfas / sfbs: per-rank scale atoms).
+HcclResult HcclEmuFusedRunMx(void *emu, int kind, void **as, void **sfas, void **bs, void **sfbs, void **outs, uint64_t m, uint64_t n, uint64_t k,
+                             uint32_t ctasPerRank, uint32_t commCtas)
+{
+    auto *w = (EmuWorld *)emu;
+    if (!w || !as || !sfas || !bs || !sfbs || !outs) return HCCL_E_PTR;
+    uint32_t R = (uint32_t)w->nranks;
+    std::vector<GemmParams> ps(R);
+    FusedShape s0{(FusedKind)kind, R, 0, m, n, k, true};
+    CHK_RET(CheckShape(s0));
+    if (2 * WorkspaceHalfBytes(s0) + 4096 > w->arenaBytes) { HCCL_ERROR("emu arena too small: need %llu", (unsigned long long)(2 * WorkspaceHalfBytes(s0) + 4096)); return HCCL_E_MEMORY; }
+    if (kind != AGMM) commCtas = 0;
+    for (uint32_t r = 0; r < R; ++r) {
+        FusedShape s{(FusedKind)kind, R, r, m, n, k, true};
+        CHK_RET(BuildParamsMx(s, w->heaps[r], w->arenaOff, as[r], sfas[r], bs[r], sfbs[r], outs[r], commCtas, &ps[r]));
+        ps[r].comm = w->devComms + r;
+    }
+    if (sizeof(GemmParams) > 2048) return HCCL_E_INTERNAL;
+    if (cudaMemcpy(w->devFusedParams, ps.data(), sizeof(GemmParams) * R, cudaMemcpyHostToDevice) != cudaSuccess) return HCCL_E_RUNTIME;
+    uint32_t grid = std::max(ctasPerRank, commCtas + 1);
+    CHK_RET(LaunchFused<true>(s0, ps[0], (const GemmParams *)w->devFusedParams, grid, R, 0));
+    if (cudaStreamSynchronize(0) != cudaSuccess) { HCCL_ERROR("emu fused kernel failed: %s", cudaGetErrorString(cudaGetLastError())); return HCCL_E_RUNTIME; }
+    for (uint32_t r = 0; r < R; ++r) if (w->status[r].code != 0) return HCCL_E_TIMEOUT;
+    return GemmCheckError();
 }
 
 // Emulation: kind 0 AllGatherMatmul (m = rows per rank), 1 MatmulReduceScatter, 2 MatmulAllReduce. as/bs/outs: per-rank

@@ -8,6 +8,7 @@
 //     offset >> 4 | [46,48) version = 1 | [49,52) base offset | [61,64) layout (2 = 128-byte swizzle)
 //   instruction descriptor (32 bit): [4,6) D format (1 = f32) | [7,10) A format | [10,13) B format (1 = bf16,
 //     0 = f16 / e4m3) | [15] A major | [16] B major (0 = K-major) | [17,23) N >> 3 | [24,29) M >> 4
+//   (the block-scaled form used by the MXFP8 kernels is described at MakeInstrDescMx)
 // Every wait is bounded: after the limit the caller gets `false`, raises the kernel's error word and unwinds
 // (the TMEM allocation is released before the CTA exits).
 #pragma once
@@ -138,15 +139,41 @@ __device__ __forceinline__ void UmmaF16(uint32_t dTmem, uint64_t aDesc, uint64_t
         "l"(aDesc), "l"(bDesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
-// fp8 (e4m3 / e5m2) operands, fp32 accumulate
-__device__ __forceinline__ void UmmaF8(uint32_t dTmem, uint64_t aDesc, uint64_t bDesc, uint32_t idesc, uint32_t accumulate)
+// Block-scaled fp8 (MXFP8): e4m3 operands, one e8m0 scale per 1 x 32 block of K for every row of A and of B, fp32
+// accumulate. One instruction covers K = 32; the scales sit in tensor memory (`sfaTmem`, `sfbTmem`: 32-bit columns that
+// hold the scales of four consecutive K blocks, the instruction descriptor's scale-factor ids select the byte).
+__device__ __forceinline__ void UmmaMxf8(uint32_t dTmem, uint64_t aDesc, uint64_t bDesc, uint32_t idesc, uint32_t sfaTmem, uint32_t sfbTmem,
+                                         uint32_t accumulate)
 {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(dTmem),
-        "l"(aDesc), "l"(bDesc), "r"(idesc), "r"(accumulate)
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(dTmem),
+        "l"(aDesc), "l"(bDesc), "r"(idesc), "r"(accumulate), "r"(sfaTmem), "r"(sfbTmem)
         : "memory");
+}
+// Shared memory -> tensor memory copy of one scale-factor atom: 32 rows x 16 bytes (512 contiguous bytes) land in 4
+// consecutive TMEM columns of lanes 0..31 and are replicated into the other three 32-lane quarters. Issued by one
+// thread; ordered with the tcgen05.mma instructions the same thread issues afterwards.
+__device__ __forceinline__ void TmemCpSfAtom(uint32_t dstTmem, uint64_t smemDesc)
+{
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(dstTmem), "l"(smemDesc) : "memory");
+}
+// Descriptor of such an atom: no swizzle, rows 16 bytes apart, 8-row groups 128 bytes apart.
+__device__ __forceinline__ uint64_t MakeSfSmemDesc(uint32_t smemAddr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smemAddr >> 4) & 0x3fffu);
+    d |= (uint64_t)(128 >> 4) << 32;        // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                 // descriptor version (Blackwell)
+    return d;                               // layout type 0 = no swizzle
+}
+// Untiled bulk copy global -> shared (never multicast); addresses and size are multiples of 16 bytes.
+__device__ __forceinline__ void BulkLoadG2S(void *smemDst, const void *gsrc, uint32_t bytes, uint64_t *bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(SmemAddr(smemDst)), "l"(gsrc), "r"(bytes),
+                 "r"(SmemAddr(bar))
+                 : "memory");
 }
 // Arrives on the mbarrier once all previously issued UMMAs of this thread have completed.
 __device__ __forceinline__ void UmmaCommit(uint64_t *bar)
@@ -190,6 +217,13 @@ enum : uint32_t { FMT_F16 = 0, FMT_BF16 = 1, FMT_E4M3 = 0, FMT_E5M2 = 1 };
 __host__ __device__ constexpr uint32_t MakeInstrDesc(uint32_t aFmt, uint32_t bFmt, uint32_t m, uint32_t n)
 {
     return (1u << 4) | (aFmt << 7) | (bFmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+// Block-scaled variant (checked against the public CUTLASS definition of UMMA::InstrDescriptorBlockScaled):
+//   [4,6) B scale-factor id | [7,10) A format | [10,13) B format (0 = e4m3) | [15] A major | [16] B major | [17,23) N >> 3 |
+//   [23] scale format (1 = e8m0) | [24,29) M >> 4 | [29,31) A scale-factor id. The accumulator is always fp32.
+__host__ __device__ constexpr uint32_t MakeInstrDescMx(uint32_t m, uint32_t n, uint32_t sfId)
+{
+    return (sfId << 4) | (FMT_E4M3 << 7) | (FMT_E4M3 << 10) | ((n >> 3) << 17) | (1u << 23) | ((m >> 4) << 24) | (sfId << 29);
 }
 
 }  // namespace sm100

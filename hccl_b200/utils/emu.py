@@ -27,6 +27,8 @@ def _decl():
     l.HcclEmuLonelyBarrier.argtypes = [vp, u32]
     l.HcclEmuFusedRun.argtypes = [vp, i32, P(vp), P(vp), P(vp), u64, u64, u64, u32, u32]
     l.HcclEmuFusedRun.restype = ctypes.c_int
+    l.HcclEmuFusedRunMx.argtypes = [vp, i32, P(vp), P(vp), P(vp), P(vp), P(vp), u64, u64, u64, u32, u32]
+    l.HcclEmuFusedRunMx.restype = ctypes.c_int
     for f in (l.HcclEmuCreate, l.HcclEmuDestroy, l.HcclEmuRun, l.HcclEmuBatchSendRecv, l.HcclEmuStatus, l.HcclEmuLonelyBarrier):
         f.restype = ctypes.c_int
     return l
@@ -82,6 +84,14 @@ class EmuWorld:
     def fused(self, kind: int, a_list, b_list, out_list, m: int, n: int, k: int, ctas_per_rank: int, comm_ctas: int = 2) -> int:
         """kind 0 AllGatherMatmul (m = rows per rank), 1 MatmulReduceScatter, 2 MatmulAllReduce"""
         rc = self._l.HcclEmuFusedRun(self._h, kind, self._ptrs(a_list), self._ptrs(b_list), self._ptrs(out_list), m, n, k, ctas_per_rank, comm_ctas)
+        torch.cuda.synchronize()
+        return rc
+
+    def fused_mx(self, kind: int, a_list, b_list, out_list, m: int, n: int, k: int, ctas_per_rank: int, comm_ctas: int = 2) -> int:
+        """The same operators on block-scaled fp8 operands; a_list / b_list hold `ops.mxfp8.MxTensor`s."""
+        rc = self._l.HcclEmuFusedRunMx(self._h, kind, self._ptrs([t.payload for t in a_list]), self._ptrs([t.scales for t in a_list]),
+                                       self._ptrs([t.payload for t in b_list]), self._ptrs([t.scales for t in b_list]), self._ptrs(out_list), m, n, k,
+                                       ctas_per_rank, comm_ctas)
         torch.cuda.synchronize()
         return rc
 

@@ -46,7 +46,7 @@ typedef struct HcclOpResCtxDef {
     char algConfig[128];
 } HcclOpResCtx;
 
-/* ---- Part 2: fused operators (bf16; weights are [N, K] row-major, i.e. K contiguous) ---------------------------- */
+/* ---- Part 2: fused operators (bf16 here, block-scaled fp8 in part 3; weights are [N, K] row-major, i.e. K contiguous) ---------------------------- */
 /* C[M,N] = A[M,K] * B[N,K]^T on one GPU (the building block; also the N = 1 degenerate case of the fused ops). */
 HcclResult HcclGemmBf16(const void *a, const void *b, void *c, uint64_t m, uint64_t n, uint64_t k, int outFp32, cudaStream_t stream);
 /* variant 0 = automatic, 1 = one-CTA 128 x BN tiles, 2 = 256 x 256 tiles on CTA pairs (tcgen05 cta_group::2) */
@@ -65,6 +65,29 @@ HcclResult HcclMatmulReduceScatter(const void *a, const void *b, void *out, uint
 /* out[m, n] = AllReduce(a[m, kLocal] * b[n, kLocal]^T), sum in rank order (decode-sized m). */
 HcclResult HcclMatmulAllReduce(const void *a, const void *b, void *out, uint64_t m, uint64_t n, uint64_t kLocal, HcclDataType dataType,
                                HcclComm comm, cudaStream_t stream);
+
+
+/* ---- Part 3: block-scaled fp8 (MXFP8: e4m3 elements, one e8m0 scale per 1 x 32 block of K) ------------------------
+ * Operand format of a [rows, k] matrix, k a multiple of 128: `payload` = rows x k bytes row-major; `scales` =
+ * HcclMxfp8ScaleBytes(rows, k) bytes in 512-byte atoms [ceil(rows/128)][k/128], the scale of row r, 32-element block kb at
+ * atom (r/128, kb/4), byte (r%32)*16 + ((r%128)/32)*4 + kb%4. The tensor cores apply the scales (tcgen05 block_scale). */
+uint64_t HcclMxfp8ScaleBytes(uint64_t rows, uint64_t k);
+/* bf16 [rows, k] -> payload + scales (power-of-two scale from the block's largest magnitude, saturating e4m3 rounding). */
+HcclResult HcclQuantizeMxfp8(const void *in, void *payload, void *scales, uint64_t rows, uint64_t k, cudaStream_t stream);
+/* C[m,n] = A[m,k] * B[n,k]^T on one GPU, both operands block-scaled, bf16 (or fp32) result. */
+HcclResult HcclGemmMxfp8(const void *a, const void *sfa, const void *b, const void *sfb, void *c, uint64_t m, uint64_t n, uint64_t k, int outFp32,
+                         cudaStream_t stream);
+/* tileN 128 or 256 forces the tile width (0 = automatic). */
+HcclResult HcclGemmMxfp8Variant(const void *a, const void *sfa, const void *b, const void *sfb, void *c, uint64_t m, uint64_t n, uint64_t k, int outFp32,
+                                int tileN, cudaStream_t stream);
+/* The three fused operators on block-scaled operands (bf16 results; shapes as for the bf16 forms, k a multiple of 128).
+ * AllGatherMatmul moves one byte per element plus the scales between GPUs. */
+HcclResult HcclAllGatherMatmulMxfp8(const void *aLocal, const void *sfaLocal, const void *b, const void *sfb, void *out, uint64_t mLocal, uint64_t n,
+                                    uint64_t k, HcclComm comm, cudaStream_t stream);
+HcclResult HcclMatmulReduceScatterMxfp8(const void *a, const void *sfa, const void *b, const void *sfb, void *out, uint64_t m, uint64_t n, uint64_t kLocal,
+                                        HcclComm comm, cudaStream_t stream);
+HcclResult HcclMatmulAllReduceMxfp8(const void *a, const void *sfa, const void *b, const void *sfb, void *out, uint64_t m, uint64_t n, uint64_t kLocal,
+                                    HcclComm comm, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

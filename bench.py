@@ -24,6 +24,7 @@ on both sides, max over ranks); `ms_per_step` is the median repeat, min / max ar
 End to end (`e2e`): every step copies its activations from pinned host memory to the device, runs the step through the
 public API and copies the step's whole output shard back to pinned host memory. Copies run on their own streams and are
 double-buffered, so step i+1's upload and step i-1's download overlap step i's kernels; the host waits for each download.
+(Each run uploads one input more than it computes: the prefetch of the step after the last.)
 """
 from __future__ import annotations
 
@@ -221,17 +222,23 @@ def main() -> None:
         ev_step[b].record(cur)
         ev_down[b].record(s_down)
 
-    def e2e_step():
-        i = state["i"]
+    def upload(i):
         b = i & 1
         s_up.wait_event(ev_step[b])                             # the step that last read x_dev[b] has finished
         with torch.cuda.stream(s_up):
             x_dev[b].copy_(x_pinned, non_blocking=True)
             ev_up[b].record(s_up)
+
+    def e2e_step():
+        i = state["i"]
+        b = i & 1
+        if i == 0:
+            upload(0)
         cur.wait_event(ev_up[b])
         cur.wait_event(ev_down[b])                              # out_dev[b] has been downloaded
         step(b)
         ev_step[b].record(cur)
+        upload(i + 1)                                           # the next step's input travels while this step computes
         s_down.wait_event(ev_step[b])
         with torch.cuda.stream(s_down):
             out_host[b].copy_(out_dev[b], non_blocking=True)

@@ -360,6 +360,16 @@ HcclResult InitEnvConfig()
     u32("HCCL_IF_BASE_PORT", &cfg.ifBasePort);
     u32("HCCL_MAX_CTAS", &cfg.maxCtas);
     u32("HCCL_DEVICE_WAIT_TIMEOUT_MS", &cfg.deviceWaitTimeoutMs);
+    if (cfg.deviceWaitTimeoutMs == 0) {
+        // 0 would make every device-side wait give up at its first timer check
+        HCCL_ERROR("[EI0001] HCCL_DEVICE_WAIT_TIMEOUT_MS must be at least 1 (got 0)");
+        return HCCL_E_PARA;
+    }
+    // Link-type switches of the reference choose between HCCS, PCIe and RoCE inside and between servers. One NVSwitch box has
+    // a single link type, so they select nothing here: say so once instead of accepting them silently.
+    if (cfg.intraRoceEnable) HCCL_WARNING("HCCL_INTRA_ROCE_ENABLE is ignored on this hardware: ranks of one server are connected by NVLink only");
+    if (cfg.intraPcieEnable) HCCL_WARNING("HCCL_INTRA_PCIE_ENABLE is ignored on this hardware: ranks of one server are connected by NVLink only");
+    if (cfg.interHccsDisable) HCCL_WARNING("HCCL_INTER_HCCS_DISABLE is ignored on this hardware: there is no inter-server HCCS plane to switch off");
     if (const char *e = getenv("HCCL_IF_IP")) if (*e) cfg.ifIp = e;
     if (const char *e = getenv("HCCL_SOCKET_IFNAME")) if (*e) cfg.socketIfName = e;
     if (const char *e = getenv("HCCL_TUNING_FILE")) if (*e) cfg.tuningFile = e;

@@ -108,6 +108,7 @@ struct CudaHeapState {
     CUdevice cuDev = 0;
     uint64_t bytes = 0;
     int localFd = -1;
+    cudaStream_t dfxStream = nullptr;   // private stream of the diagnostic copies
 };
 
 }  // namespace
@@ -276,6 +277,13 @@ HcclResult CudaBackendInit(Comm *c)
     DevStatus *devStatus = nullptr;
     RT_CHK(cudaHostGetDevicePointer((void **)&devStatus, c->hostStatus, 0));
     c->devComm.status = devStatus;
+    RT_CHK(cudaHostAlloc((void **)&c->hostProgress, 64, cudaHostAllocMapped | cudaHostAllocPortable));
+    memset(c->hostProgress, 0, 64);
+    RT_CHK(cudaHostGetDevicePointer((void **)&c->devComm.progress, c->hostProgress, 0));
+    {
+        const char *e = getenv("HCCL_DEVICE_TRACE");
+        c->devComm.traceOn = e ? atoi(e) != 0 : 1;
+    }
     RT_CHK(cudaMalloc((void **)&c->devCommPtr, sizeof(DevComm)));
     RT_CHK(cudaMemcpy(c->devCommPtr, &c->devComm, sizeof(DevComm), cudaMemcpyHostToDevice));
     return c->boot->Barrier();
@@ -296,6 +304,21 @@ HcclResult CudaBackendResetFlags(Comm *c)
     RT_CHK(cudaDeviceSynchronize());
     RT_CHK(cudaMemset(c->heap[c->rank], 0, kHeapHeaderBytes));
     RT_CHK(cudaDeviceSynchronize());
+    if (c->hostProgress) *c->hostProgress = 0;
+    c->devOpIssued = 0;
+    return HCCL_SUCCESS;
+}
+
+// Copies the first `bytes` of this rank's heap (control block, trace ring, flag arena) to host memory on a private
+// stream, so that it neither waits for nor delays the caller's streams.
+HcclResult CudaReadHeapHeader(Comm *c, void *hostDst, uint64_t bytes)
+{
+    auto *st = (CudaHeapState *)c->backendState;
+    if (st == nullptr || bytes > kHeapHeaderBytes) return HCCL_E_PARA;
+    RT_CHK(cudaSetDevice(c->device));
+    if (!st->dfxStream) RT_CHK(cudaStreamCreateWithFlags(&st->dfxStream, cudaStreamNonBlocking));
+    RT_CHK(cudaMemcpyAsync(hostDst, c->heap[c->rank], bytes, cudaMemcpyDeviceToHost, st->dfxStream));
+    RT_CHK(cudaStreamSynchronize(st->dfxStream));
     return HCCL_SUCCESS;
 }
 
@@ -319,6 +342,9 @@ void CudaBackendDestroy(Comm *c)
     if (st->localFd >= 0) close(st->localFd);
     if (c->devCommPtr) cudaFree(c->devCommPtr);
     if (c->hostStatus) cudaFreeHost(c->hostStatus);
+    if (c->hostProgress) cudaFreeHost(c->hostProgress);
+    c->hostProgress = nullptr;
+    if (st->dfxStream) cudaStreamDestroy(st->dfxStream);
     c->devCommPtr = nullptr;
     c->hostStatus = nullptr;
     c->mcHeap = nullptr;

@@ -1,5 +1,6 @@
 #include "bootstrap.h"
 #include <arpa/inet.h>
+#include <algorithm>
 #include <cerrno>
 #include <chrono>
 #include <cstring>
@@ -89,6 +90,9 @@ public:
         if (const char *e = getenv("HCCL_HEARTBEAT_LOST_MS")) lostMs_ = atoi(e) > 0 ? atoi(e) : lostMs_;
         lastSeen_.assign(n_, 0);
         hbOpen_.assign(n_, false);
+        opsIssued_.assign(n_, 0);
+        opsDone_.assign(n_, 0);
+        reported_.assign(n_, false);
         th_ = std::thread([this] { Run(); });
     }
     ~BootstrapRoot()
@@ -161,11 +165,26 @@ private:
                 break;
             }
             case OP_HEARTBEAT: {
-                int32_t err = 0;
-                if (payload.size() >= 4) memcpy(&err, payload.data(), 4);
-                if (h.rank < n_) lastSeen_[h.rank] = NowMs();
+                HeartbeatMsg m{0, 0, 0, 0};
+                memcpy(&m, payload.data(), std::min(payload.size(), sizeof(m)));
+                const int32_t err = m.error;
+                if (h.rank < n_) {
+                    lastSeen_[h.rank] = NowMs();
+                    if (payload.size() >= sizeof(m)) { opsIssued_[h.rank] = m.opsIssued; opsDone_[h.rank] = m.opsDone; reported_[h.rank] = true; }
+                }
+                if (m.clearError) { errorRank_ = -1; errorCode_ = 0; }
                 if (err != 0 && errorRank_ < 0) { errorRank_ = (int)h.rank; errorCode_ = err; }
-                HeartbeatReply rep{-1, errorRank_, errorCode_, 0};
+                HeartbeatReply rep{-1, errorRank_, errorCode_, 0, -1, 0, 0, 0};
+                bool allReported = true;
+                for (uint32_t k = 0; k < n_; ++k) allReported = allReported && reported_[k];
+                if (allReported) {
+                    rep.lagRank = 0;
+                    for (uint32_t k = 0; k < n_; ++k) {
+                        if (opsDone_[k] < opsDone_[rep.lagRank]) rep.lagRank = (int32_t)k;
+                        rep.maxIssued = std::max(rep.maxIssued, opsIssued_[k]);
+                    }
+                    rep.lagDone = opsDone_[rep.lagRank];
+                }
                 int64_t now = NowMs();
                 for (uint32_t k = 0; k < n_; ++k) {
                     if (hbOpen_[k]) rep.aliveMask |= 1u << (k & 31);
@@ -230,6 +249,8 @@ private:
     std::vector<bool> hbOpen_;
     std::set<int> everOpen_, saidBye_;
     int errorRank_ = -1, errorCode_ = 0;
+    std::vector<uint64_t> opsIssued_, opsDone_;
+    std::vector<bool> reported_;
     int64_t lostMs_;
 };
 
@@ -436,12 +457,12 @@ HcclResult Bootstrap::Get(const std::string &key, std::vector<uint8_t> *val, uin
     return Request(fd_, OP_GET, 0, key.data(), key.size(), val, timeoutSec);
 }
 
-HcclResult Bootstrap::Heartbeat(int32_t myError, HeartbeatReply *reply)
+HcclResult Bootstrap::Heartbeat(const HeartbeatMsg &msg, HeartbeatReply *reply)
 {
     std::lock_guard<std::mutex> lk(hbMu_);
     if (hbFd_ < 0) return HCCL_E_UNAVAIL;
     std::vector<uint8_t> rep;
-    HcclResult r = Request(hbFd_, OP_HEARTBEAT, 0, &myError, 4, &rep, 5);
+    HcclResult r = Request(hbFd_, OP_HEARTBEAT, 0, &msg, sizeof(msg), &rep, 5);
     if (r != HCCL_SUCCESS) return r;
     if (rep.size() != sizeof(HeartbeatReply)) return HCCL_E_INTERNAL;
     memcpy(reply, rep.data(), sizeof(HeartbeatReply));

@@ -29,11 +29,21 @@ struct RootInfoBlob {           // lives inside HcclRootInfo::internal
 };
 constexpr uint32_t kRootMagic = 0x32424348u;
 
+struct HeartbeatMsg {
+    int32_t error;         // 0 = fine; a device / host-engine status code otherwise
+    uint32_t clearError;   // 1 = forget the recorded root-cause error (sent by rank 0 while the group resumes)
+    uint64_t opsIssued;    // operators this rank has issued on the communicator
+    uint64_t opsDone;      // operators this rank knows to have completed
+};
 struct HeartbeatReply {
     int32_t deadRank;      // -1 none; rank whose heartbeat is older than the LOST threshold
     int32_t errorRank;     // -1 none; first rank that reported an error (root cause broadcast)
     int32_t errorCode;
     uint32_t aliveMask;    // bit r set when rank r has an open heartbeat connection
+    int32_t lagRank;       // rank that has completed the fewest operators (-1 before every rank has reported)
+    uint32_t pad;
+    uint64_t lagDone;      // ... and how many it has completed
+    uint64_t maxIssued;    // most operators any rank has issued
 };
 
 class BootstrapRoot;  // service side
@@ -52,7 +62,8 @@ public:
     HcclResult Put(const std::string &key, const void *val, size_t bytes);
     HcclResult Get(const std::string &key, std::vector<uint8_t> *val, uint32_t timeoutSec);
     // Heartbeat (second connection): report liveness and an optional error; learn about dead / failed peers.
-    HcclResult Heartbeat(int32_t myError, HeartbeatReply *reply);
+    HcclResult Heartbeat(const HeartbeatMsg &msg, HeartbeatReply *reply);
+    HcclResult Heartbeat(int32_t myError, HeartbeatReply *reply) { HeartbeatMsg m{myError, 0, 0, 0}; return Heartbeat(m, reply); }
     uint32_t Rank() const { return rank_; }
     uint32_t Size() const { return nranks_; }
     uint64_t Nonce() const { return nonce_; }

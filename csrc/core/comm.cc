@@ -37,6 +37,7 @@ void SimWorker::Enqueue(std::function<HcclResult()> fn)
     {
         std::lock_guard<std::mutex> lk(mu_);
         q_.push_back(std::move(fn));
+        enqueued_++;
     }
     cv_.notify_one();
 }
@@ -65,6 +66,7 @@ void SimWorker::Run()
             std::lock_guard<std::mutex> lk(mu_);
             if (r != HCCL_SUCCESS && firstErr_ == HCCL_SUCCESS) firstErr_ = r;
             busy_ = false;
+            completed_++;
         }
         idleCv_.notify_all();
     }
@@ -313,6 +315,7 @@ HcclResult CommPollAsyncError(Comm *c, HcclResult *asyncErr)
     if (c->hostStatus && c->hostStatus->code != 0) {
         DevStatus s = *c->hostStatus;
         e = s.code == 1 ? HCCL_E_TIMEOUT : HCCL_E_INTERNAL;
+        if (c->env.taskException) DumpTaskException(c, s);
         if (c->status.exchange(HCCL_COMM_STATUS_SUSPENDING) == HCCL_COMM_STATUS_READY) {
             c->counters.timeouts++;
             HCCL_ERROR("comm %s rank %u: device reported code %u (1=wait timeout, 2=bounds) peer=%u channel=%u phase=%u opSeq=%u observed=%u "
@@ -332,6 +335,9 @@ HcclResult CommCheckReady(Comm *c)
     HcclResult e;
     CommPollAsyncError(c, &e);
     if (c->status.load() != HCCL_COMM_STATUS_READY) {
+        // A wait that ran out here or on a peer, with operator retry configured: every rank ends up in this branch at its
+        // next call, they agree over the bootstrap and re-run the operator they all stopped at.
+        if ((e == HCCL_E_TIMEOUT || e == HCCL_E_REMOTE) && c->deadRank.load() < 0 && OpRetryEnabled(c) && !c->inRetry.load()) return CommOpRetry(c);
         HCCL_ERROR("comm %s is suspended (rank %u)", c->name.c_str(), c->rank);
         return HCCL_E_SUSPENDING;
     }
@@ -359,8 +365,15 @@ HcclResult CommResume(Comm *c)
     LifecycleNote(c, "resume:clear");
     if (c->backend == BackendKind::CUDA) CHK_RET(CudaBackendResetFlags(c));
     else memset(c->heap[c->rank], 0, kHeapHeaderBytes);
+    c->opSeq = 0;     // host-side op parity restarts with the cleared header, on every rank alike
     if (c->hostStatus) memset(c->hostStatus, 0, sizeof(DevStatus));
     c->remoteErrorRank = -1;
+    { std::lock_guard<std::mutex> lk(c->dfxMu); c->exceptionDumped = false; }
+    if (c->rank == 0) {                                   // the service forgets the root-cause error it has been broadcasting
+        HeartbeatMsg m{0, 1, 0, 0};
+        HeartbeatReply rep;
+        (void)c->boot->Heartbeat(m, &rep);
+    }
     LifecycleNote(c, "resume:barrier");
     CHK_RET(c->boot->Barrier());
     c->status = HCCL_COMM_STATUS_READY;
@@ -496,8 +509,14 @@ void StartWatchdog(Comm *c)
     c->watchdogStop = false;
     int periodMs = 1000;
     if (const char *e = getenv("HCCL_HEARTBEAT_PERIOD_MS")) if (atoi(e) > 0) periodMs = atoi(e);
-    c->watchdog = std::thread([c, periodMs] {
+    // a third of the execution timeout, as the reference's heartbeat does; HCCL_STUCK_CHECK_MS overrides (tests)
+    int64_t stuckMs = (int64_t)c->env.execTimeoutSec * 1000 / 3;
+    if (const char *e = getenv("HCCL_STUCK_CHECK_MS")) if (atoi(e) > 0) stuckMs = atoi(e);
+    c->watchdog = std::thread([c, periodMs, stuckMs] {
         int waited = 0;
+        uint64_t lastDone = ~0ull;
+        int64_t lastChangeMs = 0;
+        bool stuckLogged = false;
         while (!c->watchdogStop.load()) {
             usleep(20000);
             waited += 20;
@@ -505,8 +524,27 @@ void StartWatchdog(Comm *c)
             waited = 0;
             int32_t myErr = 0;
             if (c->hostStatus && c->hostStatus->code != 0) myErr = (int32_t)c->hostStatus->code;
+            HeartbeatMsg msg{myErr, 0, 0, 0};
+            CommProgress(c, &msg.opsIssued, &msg.opsDone);
             HeartbeatReply rep;
-            if (c->boot->Heartbeat(myErr, &rep) != HCCL_SUCCESS) continue;
+            if (c->boot->Heartbeat(msg, &rep) != HCCL_SUCCESS) continue;
+            // stuck detection: work is in flight here and nothing has completed for a third of the execution timeout
+            if (c->env.stuckDetection) {
+                int64_t now = (int64_t)std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now().time_since_epoch()).count();
+                if (msg.opsDone != lastDone || msg.opsIssued == msg.opsDone) { lastDone = msg.opsDone; lastChangeMs = now; stuckLogged = false; }
+                else if (!stuckLogged && now - lastChangeMs > stuckMs) {
+                    stuckLogged = true;
+                    char buf[384];
+                    snprintf(buf, sizeof(buf), "STUCK: comm %s rank %u has %llu of %llu operators done and no progress for %lld ms; slowest rank is %d "
+                             "with %llu done (most issued anywhere: %llu)", c->name.c_str(), c->rank, (unsigned long long)msg.opsDone,
+                             (unsigned long long)msg.opsIssued, (long long)(now - lastChangeMs), rep.lagRank, (unsigned long long)rep.lagDone,
+                             (unsigned long long)rep.maxIssued);
+                    HCCL_WARNING("%s", buf);
+                    c->counters.stuckReports++;
+                    std::lock_guard<std::mutex> lk(c->dfxMu);
+                    c->lastStuckReport = buf;
+                }
+            }
             if (rep.errorRank >= 0 && rep.errorRank != (int)c->rank && c->remoteErrorRank.load() < 0) {
                 c->remoteErrorRank = rep.errorRank;
                 HCCL_ERROR("comm %s rank %u: rank %d reported error %d (root cause); suspending", c->name.c_str(), c->rank, rep.errorRank, rep.errorCode);

@@ -58,11 +58,12 @@ struct OpRecord {
     uint32_t engine;
     char algName[64];
     uint64_t beginNs, endNs;     // host timestamps around the enqueue
+    uint32_t devSeq, devLaunches; // first device op-counter value and number of kernels of this operator (CUDA engines)
 };
 
 struct CommCounters {
     std::atomic<uint64_t> ops{0}, bytes{0}, timeouts{0}, planCacheHits{0}, planCacheMisses{0}, fallbacks{0},
-        consistencyChecks{0}, chunkLoops{0}, kernelsLaunched{0};
+        consistencyChecks{0}, chunkLoops{0}, kernelsLaunched{0}, opRetries{0}, stuckReports{0}, exceptionDumps{0};
     std::mutex mu;
     std::map<std::string, uint64_t> algoHistogram;
 };
@@ -91,6 +92,8 @@ struct Comm {
     DevComm devComm{};               // host copy
     DevComm *devCommPtr = nullptr;   // device copy (CUDA) or == &devComm (sim)
     DevStatus *hostStatus = nullptr; // pinned, device-mapped (CUDA) / plain (sim)
+    uint32_t *hostProgress = nullptr; // pinned, device-mapped: kernels entered on the device (CUDA only)
+    std::atomic<uint64_t> devOpIssued{0};   // kernels issued that advance the device op counter (since create / resume)
     void *backendState = nullptr;    // CudaHeapState* / SimHeapState*
     std::vector<SymAllocBlock> arena;
     std::mutex arenaMu;
@@ -114,6 +117,19 @@ struct Comm {
     std::atomic<bool> watchdogStop{false};
     std::atomic<int> remoteErrorRank{-1}, deadRank{-1};
     std::vector<std::function<void(int)>> stateCallbacks;
+
+    // op retry: the last collective as issued (its buffers stay the caller's), re-run after a wait timeout when every
+    // rank stopped at the same operator and its input cannot have been overwritten
+    std::mutex retryMu;
+    std::shared_ptr<void> retryOp;               // OpParam copy (op_retry.cc)
+    uint64_t retrySeq = 0;                       // index of that operator on this communicator
+    bool retryInputIntact = false;
+    std::atomic<int> injectOpDrop{0};            // tests: the next n operators of this rank are recorded but not run
+    std::atomic<bool> inRetry{false};
+    // stuck detection / task-exception dump
+    std::mutex dfxMu;
+    std::string lastStuckReport, lastExceptionReport;
+    bool exceptionDumped = false;
 
     // sub-communicators keep their parent's bootstrap alive
     Comm *parent = nullptr;
@@ -150,6 +166,12 @@ HcclResult CudaBackendResetFlags(Comm *c);
 HcclResult CudaBackendQuiesce(Comm *c);
 bool CudaDeviceAvailable(int *currentDevice);
 
+// ---- fault handling (dfx/fault_handling.cc, exec/op_retry.cc)
+bool OpRetryEnabled(const Comm *c);
+HcclResult CommOpRetry(Comm *c);                       // collective: agree, resume, re-issue; HCCL_E_OPRETRY_FAIL when it cannot
+void DumpTaskException(Comm *c, const DevStatus &s);   // flag arena + last operators -> log (and HCCL_EXCEPTION_DUMP_DIR)
+void CommProgress(Comm *c, uint64_t *issued, uint64_t *done);
+HcclResult CudaReadHeapHeader(Comm *c, void *hostDst, uint64_t bytes);   // device -> host copy on a private stream
 // ---- DFX
 std::string LifecycleLogTake();   // and clears it
 void RecordOp(Comm *c, const OpRecord &r);
@@ -163,6 +185,8 @@ public:
     ~SimWorker();
     void Enqueue(std::function<HcclResult()> fn);
     HcclResult Drain();                 // waits; returns the first error since the previous Drain
+    uint64_t Enqueued() const { return enqueued_.load(); }
+    uint64_t Completed() const { return completed_.load(); }
 private:
     void Run();
     std::thread th_;
@@ -170,6 +194,7 @@ private:
     std::condition_variable cv_, idleCv_;
     std::deque<std::function<HcclResult()>> q_;
     bool stop_ = false, busy_ = false;
+    std::atomic<uint64_t> enqueued_{0}, completed_{0};
     HcclResult firstErr_ = HCCL_SUCCESS;
 };
 

@@ -13,6 +13,8 @@ HcclResult CudaSetDeviceChecked(int dev)
     return HCCL_SUCCESS;
 }
 
+HcclResult CudaStreamSync(cudaStream_t s) { return cudaStreamSynchronize(s) == cudaSuccess ? HCCL_SUCCESS : HCCL_E_RUNTIME; }
+
 bool CudaStreamIsCapturing(cudaStream_t s)
 {
     cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;

@@ -36,6 +36,16 @@ struct DevStatus {
     uint32_t expected;
 };
 
+// Device-side trace: one record per collective / fused kernel, written by CTA 0 of the kernel from %globaltimer.
+constexpr int kTraceSlots = 512;
+struct DevTraceRec {
+    uint32_t seq;            // op counter value the kernel ran as (kernels since the communicator was created or resumed)
+    uint32_t barriers;       // sync points CTA 0 has passed
+    uint64_t tEnter;         // ns: CTA 0 entered the kernel
+    uint64_t tBarrier[2];    // ns: CTA 0 left its first / last all-rank synchronisation
+    uint64_t tLeave;         // ns: CTA 0 left the kernel (0 while it runs, or if it gave up)
+};
+
 // Control block at heap offset 0.
 struct DevCtrl {
     uint32_t opCount;                 // collectives completed on this rank (parity selects the CCL half)
@@ -49,6 +59,7 @@ struct DevCtrl {
     uint64_t hostNotifySent[kMaxRanks][kNotifySlots];   // host-engine: posts issued towards peer r
     uint64_t hostNotifyWaited[kMaxRanks][kNotifySlots]; // host-engine: waits consumed from peer r
     uint32_t pipeEpoch[kPipeChannels];                  // pipelined collectives: flag value reached by the previous operator
+    DevTraceRec trace[kTraceSlots];                     // ring indexed by seq % kTraceSlots
 };
 static_assert(sizeof(DevCtrl) <= kCtrlBytes, "control block too large");
 
@@ -82,7 +93,8 @@ struct DevComm {
     uint64_t timeoutNs;         // bound of every device-side wait
     DevStatus *status;          // device-mapped pinned host memory
     int32_t emuRanks;           // > 0: all ranks live on this GPU and one launch covers them (tests)
-    int32_t pad;
+    int32_t traceOn;            // != 0: CTA 0 of every kernel stamps DevCtrl::trace
+    uint32_t *progress;         // device-mapped pinned host word: kernels entered so far (read by the host watchdog); may be null
 };
 
 #if defined(__CUDACC__) || defined(HCCL_DEV_HELPERS)

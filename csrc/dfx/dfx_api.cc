@@ -1,3 +1,4 @@
+#include <algorithm>
 #include <cstring>
 #include <fstream>
 #include <sstream>
@@ -95,6 +96,16 @@ HcclResult HcclDumpTrace(HcclComm comm, const char *path)
     if (!c || !path) return HCCL_E_PTR;
     std::ofstream f(path);
     if (!f) return HCCL_E_OPEN_FILE_FAILURE;
+    // Device side first (a copy on a private stream): the ring of per-kernel records CTA 0 stamped from %globaltimer.
+    std::vector<DevTraceRec> dev;
+    if (c->backend == BackendKind::CUDA && c->devComm.traceOn) {
+        std::vector<uint8_t> ctrl(sizeof(DevCtrl));
+        if (CudaReadHeapHeader(c, ctrl.data(), ctrl.size()) == HCCL_SUCCESS) {
+            const DevCtrl *dc = reinterpret_cast<const DevCtrl *>(ctrl.data());
+            for (int i = 0; i < kTraceSlots; ++i) if (dc->trace[i].tEnter != 0) dev.push_back(dc->trace[i]);
+            std::sort(dev.begin(), dev.end(), [](const DevTraceRec &a, const DevTraceRec &b) { return a.tEnter < b.tEnter; });
+        }
+    }
     f << "{\"traceEvents\":[";
     std::lock_guard<std::mutex> lk(c->opRingMu);
     bool first = true;
@@ -103,7 +114,21 @@ HcclResult HcclDumpTrace(HcclComm comm, const char *path)
         first = false;
         f << "{\"name\":\"" << CmdName(r.opType) << "\",\"cat\":\"" << r.algName << "\",\"ph\":\"X\",\"pid\":" << c->rank << ",\"tid\":0,\"ts\":"
           << r.beginNs / 1000.0 << ",\"dur\":" << (r.endNs - r.beginNs) / 1000.0 << ",\"args\":{\"count\":" << r.count << ",\"dtype\":\""
-          << DataTypeName(r.dtype) << "\",\"engine\":\"" << EngineName((HcclCommEngine)r.engine) << "\",\"seq\":" << r.seq << "}}";
+          << DataTypeName(r.dtype) << "\",\"engine\":\"" << EngineName((HcclCommEngine)r.engine) << "\",\"seq\":" << r.seq << ",\"devSeq\":" << r.devSeq
+          << ",\"devLaunches\":" << r.devLaunches << "}}";
+    }
+    // Device records on their own track (tid 1). Their clock is the GPU's %globaltimer, not the host's steady clock: the
+    // two tracks are matched through devSeq, not through their time axes.
+    for (const DevTraceRec &d : dev) {
+        const OpRecord *host = nullptr;
+        for (const OpRecord &r : c->opRing) if (d.seq >= r.devSeq && d.seq < r.devSeq + r.devLaunches) host = &r;
+        const uint64_t end = d.tLeave ? d.tLeave : (d.tBarrier[1] ? d.tBarrier[1] : d.tEnter);
+        if (!first) f << ",";
+        first = false;
+        f << "{\"name\":\"" << (host ? CmdName(host->opType) : "kernel") << "\",\"cat\":\"device\",\"ph\":\"X\",\"pid\":" << c->rank << ",\"tid\":1,\"ts\":"
+          << d.tEnter / 1000.0 << ",\"dur\":" << (end - d.tEnter) / 1000.0 << ",\"args\":{\"devSeq\":" << d.seq << ",\"alg\":\"" << (host ? host->algName : "")
+          << "\",\"syncs\":" << d.barriers << ",\"first_sync_us\":" << (d.tBarrier[0] ? (d.tBarrier[0] - d.tEnter) / 1000.0 : -1.0)
+          << ",\"last_sync_us\":" << (d.tBarrier[1] ? (d.tBarrier[1] - d.tEnter) / 1000.0 : -1.0) << ",\"finished\":" << (d.tLeave ? 1 : 0) << "}}";
     }
     f << "]}\n";
     return HCCL_SUCCESS;
@@ -193,7 +218,7 @@ HcclResult HcclCheckAlgorithm(HcclCMDType op, const char *algName, uint32_t supe
     }
 }
 
-void HcclResetEnvConfigForTest(void) { ResetAlgEnvConfigInitState(); }
+void HcclResetEnvConfigForTest(void) { ResetAlgEnvConfigInitState(); BumpSelectionGeneration(); }
 
 HcclResult HcclDescribeEnvConfig(char *buf, uint32_t bufLen)
 {
@@ -223,6 +248,43 @@ HcclResult HcclTakeLifecycleLog(char *buf, uint32_t bufLen)
     if (!buf || bufLen == 0) return HCCL_E_PTR;
     std::string s = LifecycleLogTake();
     snprintf(buf, bufLen, "%s", s.c_str());
+    return HCCL_SUCCESS;
+}
+
+HcclResult HcclInjectOpDrop(HcclComm comm, int n)
+{
+    Comm *c = CommFromHandle(comm);
+    if (!c) return HCCL_E_PTR;
+    c->injectOpDrop = n;
+    return HCCL_SUCCESS;
+}
+
+HcclResult HcclCommOpRetry(HcclComm comm)
+{
+    Comm *c = CommFromHandle(comm);
+    if (!c) return HCCL_E_PTR;
+    if (!OpRetryEnabled(c)) { HCCL_ERROR("HcclCommOpRetry: operator retry is not enabled (HCCL_OP_RETRY_ENABLE)"); return HCCL_E_NOT_SUPPORT; }
+    return CommOpRetry(c);
+}
+
+/* Device-side records of the most recent kernels: up to maxRecords rows of {devSeq, syncs, enterNs, firstSyncNs, lastSyncNs, leaveNs}. */
+HcclResult HcclGetDeviceTrace(HcclComm comm, uint64_t *rows, uint32_t maxRecords, uint32_t *numRecords)
+{
+    Comm *c = CommFromHandle(comm);
+    if (!c || !rows || !numRecords) return HCCL_E_PTR;
+    *numRecords = 0;
+    if (c->backend != BackendKind::CUDA) return HCCL_SUCCESS;
+    std::vector<uint8_t> ctrl(sizeof(DevCtrl));
+    CHK_RET(CudaReadHeapHeader(c, ctrl.data(), ctrl.size()));
+    const DevCtrl *dc = reinterpret_cast<const DevCtrl *>(ctrl.data());
+    std::vector<DevTraceRec> dev;
+    for (int i = 0; i < kTraceSlots; ++i) if (dc->trace[i].tEnter != 0) dev.push_back(dc->trace[i]);
+    std::sort(dev.begin(), dev.end(), [](const DevTraceRec &a, const DevTraceRec &b) { return a.tEnter < b.tEnter; });
+    size_t first = dev.size() > maxRecords ? dev.size() - maxRecords : 0;
+    for (size_t i = first; i < dev.size(); ++i) {
+        uint64_t *r = rows + 6 * (*numRecords)++;
+        r[0] = dev[i].seq; r[1] = dev[i].barriers; r[2] = dev[i].tEnter; r[3] = dev[i].tBarrier[0]; r[4] = dev[i].tBarrier[1]; r[5] = dev[i].tLeave;
+    }
     return HCCL_SUCCESS;
 }
 

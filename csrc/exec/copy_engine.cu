@@ -76,34 +76,13 @@ cudaError_t LaunchReduce(void *dst, const void *src, uint64_t bytes, HcclDataTyp
     }
 }
 
-struct HelperStreams {
-    std::vector<cudaStream_t> streams;
-    std::vector<cudaEvent_t> done;
-    cudaEvent_t fork = nullptr;
-};
 std::mutex g_mu;
-std::map<Comm *, HelperStreams> g_helpers;
-
-HelperStreams &HelpersFor(Comm *c, size_t n)
-{
-    HelperStreams &h = g_helpers[c];
-    if (!h.fork) cudaEventCreateWithFlags(&h.fork, cudaEventDisableTiming);
-    while (h.streams.size() < n) {
-        cudaStream_t s;
-        cudaEvent_t e;
-        cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking);
-        cudaEventCreateWithFlags(&e, cudaEventDisableTiming);
-        h.streams.push_back(s);
-        h.done.push_back(e);
-    }
-    return h;
-}
 
 constexpr uint32_t kSlotPlanBarrier = kNotifySlots - 1;
 
 }  // namespace
 
-HcclResult CopyEngineRun(Comm *c, const Plan &plan, const ExecBuffers &bufs, cudaStream_t stream)
+HcclResult CopyEngineRun(Comm *c, const Plan &plan, const ExecBuffers &bufs, cudaStream_t stream, bool isCollective)
 {
     const DevComm &d = c->devComm;
     auto local = [&](const BufRef &b) -> char * {
@@ -125,19 +104,14 @@ HcclResult CopyEngineRun(Comm *c, const Plan &plan, const ExecBuffers &bufs, cud
     };
     std::lock_guard<std::mutex> lk(g_mu);
     const size_t nq = plan.queues.size();
-    if (nq > 1) {
-        HCCL_ERROR("copy engine: schedules with %zu queues need launches that wait on one another on one GPU; use the SM engine", nq);
+    if (nq > 1 || !isCollective) {
+        HCCL_ERROR("copy engine: %s need launches that wait on one another on one GPU; use the SM engine",
+                   isCollective ? "schedules with several queues" : "point-to-point schedules");
         return HCCL_E_NOT_SUPPORT;
     }
-    HelperStreams &h = HelpersFor(c, nq > 1 ? nq - 1 : 0);
-    const bool collective = nq <= 1;       // point-to-point plans (several queues, mailbox) involve only some ranks: no barrier
-    if (collective) barrier(stream);
-    if (nq > 1) {
-        cudaEventRecord(h.fork, stream);
-        for (size_t q = 1; q < nq; ++q) cudaStreamWaitEvent(h.streams[q - 1], h.fork, 0);
-    }
+    barrier(stream);
     for (size_t q = 0; q < nq; ++q) {
-        cudaStream_t s = q == 0 ? stream : h.streams[q - 1];
+        cudaStream_t s = stream;
         for (const Task &t : plan.queues[q]) {
             cudaError_t e = cudaSuccess;
             switch (t.type) {
@@ -158,11 +132,7 @@ HcclResult CopyEngineRun(Comm *c, const Plan &plan, const ExecBuffers &bufs, cud
             CountLaunch();
         }
     }
-    for (size_t q = 1; q < nq; ++q) {
-        cudaEventRecord(h.done[q - 1], h.streams[q - 1]);
-        cudaStreamWaitEvent(stream, h.done[q - 1], 0);
-    }
-    if (collective) barrier(stream);
+    barrier(stream);
     return HCCL_SUCCESS;
 }
 

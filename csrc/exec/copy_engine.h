@@ -8,5 +8,8 @@
 #include "plan.h"
 
 namespace hccl {
-HcclResult CopyEngineRun(Comm *c, const Plan &plan, const ExecBuffers &bufs, cudaStream_t stream);
+// isCollective: every rank of the communicator runs a plan of this operator (the plan is then bracketed by an all-rank notify
+// barrier); false for point-to-point schedules, which this engine refuses (their queues would be launches that wait on one
+// another on one GPU).
+HcclResult CopyEngineRun(Comm *c, const Plan &plan, const ExecBuffers &bufs, cudaStream_t stream, bool isCollective);
 }

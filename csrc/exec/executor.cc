@@ -213,7 +213,8 @@ static HcclResult RunPlan(Comm *c, const OpParam &p, std::shared_ptr<const Plan>
         c->worker->Enqueue([c, plan, bufs] { return HostEngineRun(c, *plan, bufs); });
         return HCCL_SUCCESS;
     }
-    return CopyEngineRun(c, *plan, bufs, p.stream);
+    const bool isCollective = p.opType != HCCL_CMD_SEND && p.opType != HCCL_CMD_RECEIVE && p.opType != HCCL_CMD_BATCH_SEND_RECV;
+    return CopyEngineRun(c, *plan, bufs, p.stream, isCollective);
 }
 
 // ------------------------------------------------------------------------------------------------ IR sole executor

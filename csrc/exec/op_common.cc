@@ -1,5 +1,6 @@
 #include "../common/launch_count.h"
 #include "op_common.h"
+#include <algorithm>
 #include <atomic>
 #include <unordered_map>
 #include "../kernels/coll_args.h"
@@ -177,8 +178,10 @@ struct FastEntry {
     std::vector<SmLaunch> launches;
     uint64_t generation;
     uint64_t *histogramSlot;
+    uint64_t lastUse;
 };
-struct FastCache { std::unordered_map<FastKey, FastEntry, FastHash> map; };
+struct FastCache { std::unordered_map<FastKey, FastEntry, FastHash> map; uint64_t tick = 0; };
+constexpr size_t kFastCacheCap = 8192;
 std::atomic<uint64_t> g_selectGeneration{1};
 
 bool FastEligible(const Comm *c, const OpParam &p)
@@ -186,6 +189,7 @@ bool FastEligible(const Comm *c, const OpParam &p)
     static const bool enabled = [] { const char *e = getenv("HCCL_FAST_DISPATCH"); return e ? atoi(e) != 0 : true; }();
     if (!enabled) return false;
     if (c->backend != BackendKind::CUDA || p.mode != OpMode::OPBASE || c->env.entryLogEnable) return false;
+    if (c->env.inconsistentCheck == InconsistentCheck::EVERY) return false;     // every call is cross-checked in that mode
     if (!p.sendCounts.empty() || !p.recvCounts.empty() || !p.items.empty()) return false;
     switch (p.opType) {
         case HCCL_CMD_ALLREDUCE: case HCCL_CMD_ALLGATHER: case HCCL_CMD_REDUCE_SCATTER: case HCCL_CMD_BROADCAST: case HCCL_CMD_REDUCE:
@@ -201,18 +205,28 @@ HcclResult HcclExecOp(Comm *c, OpParam &p)
 {
     uint64_t begin = NowNs();
     CHK_RET(CommCheckReady(c));
+    if (OpRetryEnabled(c) && !c->inRetry.load() && c->nranks > 1) RecordOpForRetry(c, p);
+    // test hook: the operator goes through selection and the consistency exchange like any other, but is never launched here
+    bool dropThisOp = false;
+    if (c->injectOpDrop.load() > 0 && !c->inRetry.load() && c->nranks > 1) {
+        c->injectOpDrop--;
+        dropThisOp = true;
+        HCCL_WARNING("comm %s rank %u: operator %s dropped by injection", c->name.c_str(), c->rank, CmdName(p.opType));
+    }
     const bool fastOk = c->nranks > 1 && FastEligible(c, p);
     FastKey fkey{(uint32_t)p.opType, (uint32_t)p.dtype, (uint32_t)p.reduceOp, p.root, p.count, p.inputPtr, p.outputPtr};
-    if (fastOk && c->fastOps) {
+    if (fastOk && c->fastOps && !dropThisOp) {
         auto *fc = static_cast<FastCache *>(c->fastOps.get());
         auto it = fc->map.find(fkey);
         if (it != fc->map.end() && it->second.generation == g_selectGeneration.load(std::memory_order_relaxed)) {
             FastEntry &e = it->second;
+            e.lastUse = ++fc->tick;
             for (const SmLaunch &l : e.launches) {
                 HcclResult lr = SmIssueLaunch(c->devCommPtr, l, p.stream);
                 if (lr != HCCL_SUCCESS) return lr;
             }
             c->counters.kernelsLaunched += e.launches.size();
+            const uint32_t devSeq = (uint32_t)c->devOpIssued.fetch_add(e.launches.size());
             CountLaunch(e.launches.size());
             c->counters.chunkLoops += e.launches.size();
             c->counters.planCacheHits++;
@@ -222,9 +236,13 @@ HcclResult HcclExecOp(Comm *c, OpParam &p)
             snprintf(rec.algName, sizeof(rec.algName), "%s", e.algName.c_str());
             rec.beginNs = begin;
             rec.endNs = NowNs();
+            rec.devSeq = devSeq; rec.devLaunches = (uint32_t)e.launches.size();
             RecordOp(c, rec);
             c->counters.bytes += p.DataBytes();
-            ++*e.histogramSlot;
+            {
+                std::lock_guard<std::mutex> lk(c->counters.mu);
+                ++*e.histogramSlot;
+            }
             return HCCL_SUCCESS;
         }
     }
@@ -257,6 +275,7 @@ HcclResult HcclExecOp(Comm *c, OpParam &p)
         }
     }
     HcclResult res = HCCL_E_INTERNAL;
+    const uint64_t devSeqBefore = c->devOpIssued.load();
     bool resourceFallback = false;   // only a missing resource is remembered; a call-specific "not supported" is not
     for (int attempt = 0; attempt < 4; ++attempt) {
         CHK_RET(SelectAlgorithm(c, p, excluded));
@@ -267,7 +286,7 @@ HcclResult HcclExecOp(Comm *c, OpParam &p)
             return HCCL_E_NOT_FOUND;
         }
         NvtxPush(p.algTag.c_str());
-        res = exec->Orchestrate(c, p);
+        res = dropThisOp ? HCCL_SUCCESS : exec->Orchestrate(c, p);
         NvtxPop();
         if (res != HCCL_E_UNAVAIL && res != HCCL_E_NOT_SUPPORT) break;
         if (p.engine == HCCL_ENGINE_HOST || p.engine == HCCL_ENGINE_COPY_ENGINE) break;   // nothing below to fall back to
@@ -292,6 +311,7 @@ HcclResult HcclExecOp(Comm *c, OpParam &p)
     snprintf(rec.algName, sizeof(rec.algName), "%s", p.algName.c_str());
     rec.beginNs = begin;
     rec.endNs = NowNs();
+    rec.devSeq = (uint32_t)devSeqBefore; rec.devLaunches = (uint32_t)(c->devOpIssued.load() - devSeqBefore);
     RecordOp(c, rec);
     c->counters.bytes += p.DataBytes();
     uint64_t *histSlot;
@@ -300,11 +320,19 @@ HcclResult HcclExecOp(Comm *c, OpParam &p)
         histSlot = &c->counters.algoHistogram[p.algName];
         ++*histSlot;
     }
-    if (fastOk && res == HCCL_SUCCESS && !captured.empty() && (p.engine == HCCL_ENGINE_SM || p.engine == HCCL_ENGINE_NVLS)) {
+    if (fastOk && res == HCCL_SUCCESS && !dropThisOp && !captured.empty() && (p.engine == HCCL_ENGINE_SM || p.engine == HCCL_ENGINE_NVLS)) {
         if (!c->fastOps) c->fastOps = std::make_shared<FastCache>();
         auto *fc = static_cast<FastCache *>(c->fastOps.get());
-        if (fc->map.size() > 512) fc->map.clear();
-        fc->map[fkey] = FastEntry{p.algName, p.engine, std::move(captured), g_selectGeneration.load(), histSlot};
+        if (fc->map.size() >= kFastCacheCap) {
+            // drop the least recently used fifth, as the reference's launch cache does
+            std::vector<uint64_t> uses;
+            uses.reserve(fc->map.size());
+            for (auto &kv : fc->map) uses.push_back(kv.second.lastUse);
+            std::nth_element(uses.begin(), uses.begin() + uses.size() / 5, uses.end());
+            const uint64_t cut = uses[uses.size() / 5];
+            for (auto it = fc->map.begin(); it != fc->map.end();) it = it->second.lastUse <= cut ? fc->map.erase(it) : std::next(it);
+        }
+        fc->map[fkey] = FastEntry{p.algName, p.engine, std::move(captured), g_selectGeneration.load(), histSlot, ++fc->tick};
     }
     if (c->env.entryLogEnable)
         HCCL_RUN_INFO("Exit-%s: alg[%s] engine[%s] ret[%d] host_us[%llu]", CmdName(p.opType), p.algName.c_str(), EngineName(p.engine), (int)res,

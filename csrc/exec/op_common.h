@@ -18,5 +18,7 @@ bool StreamIsCapturing(cudaStream_t s);
 // Invalidates every cached launch list (tuning table or algorithm configuration changed).
 void BumpSelectionGeneration();
 HcclResult LocalCopyAsync(Comm *c, void *dst, const void *src, uint64_t bytes, cudaStream_t s);
+// Operator retry (op_retry.cc): keeps a copy of the call for CommOpRetry.
+void RecordOpForRetry(Comm *c, const OpParam &p);
 
 }  // namespace hccl

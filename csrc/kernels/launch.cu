@@ -61,6 +61,7 @@ HcclResult SmOrchestrate(Comm *c, OpParam &p, const std::string &algName)
             return lr;
         }
         c->counters.kernelsLaunched++;
+        c->devOpIssued++;
         CountLaunch();
         c->counters.chunkLoops++;
     }

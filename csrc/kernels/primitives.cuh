@@ -69,6 +69,7 @@ struct KCtx {
     uint32_t epoch;      // channel epoch at kernel entry; sync point i uses epoch + i
     uint32_t syncs;      // sync points consumed so far
     bool ok;             // false after a timeout
+    uint32_t seq;        // op counter value this kernel entered with (trace slot)
     __device__ __forceinline__ char *PeerHeap(int r) const { return c->heap[r]; }
     __device__ __forceinline__ char *Ccl(int r) const { return c->heap[r] + c->cclOff[half]; }
     __device__ __forceinline__ char *Mc() const { return c->mcHeap + c->cclOff[half]; }
@@ -125,12 +126,35 @@ __device__ __forceinline__ bool WaitFlagGe64(const KCtx &k, const uint64_t *flag
     }
 }
 
+// ---- device-side trace (CTA 0, thread 0 only). The record of a kernel is the ring slot of the op counter it entered with;
+// the counter has already advanced when later hooks run, so they find their slot through `seq` kept in shared memory.
+__device__ __forceinline__ void TraceEnter(DevCtrl *ctrl, uint32_t oc)
+{
+    DevTraceRec &r = ctrl->trace[oc % kTraceSlots];
+    r.seq = oc; r.barriers = 0; r.tBarrier[0] = 0; r.tBarrier[1] = 0; r.tLeave = 0;
+    r.tEnter = GlobalTimerNs();
+}
+__device__ __forceinline__ void TraceBarrier(DevCtrl *ctrl, uint32_t oc)
+{
+    DevTraceRec &r = ctrl->trace[oc % kTraceSlots];
+    if (r.seq != oc) return;
+    uint64_t now = GlobalTimerNs();
+    if (r.barriers == 0) r.tBarrier[0] = now;
+    r.tBarrier[1] = now;
+    r.barriers++;
+}
+__device__ __forceinline__ void TraceLeave(DevCtrl *ctrl, uint32_t oc)
+{
+    DevTraceRec &r = ctrl->trace[oc % kTraceSlots];
+    if (r.seq == oc) r.tLeave = GlobalTimerNs();
+}
+
 // Entry protocol of every collective kernel. EMU: several ranks share this GPU and blockIdx.y names the rank.
 // Reads the op counter (parity = CCL half) and the channel epoch, then takes a ticket; the last CTA to arrive
 // advances the op counter for the next launch.
 template <bool EMU> __device__ __forceinline__ KCtx EnterCollective(const DevComm *comms)
 {
-    __shared__ uint32_t sHalf, sEpoch;
+    __shared__ uint32_t sHalf, sEpoch, sSeq;
     KCtx k;
     k.c = EMU ? &comms[blockIdx.y] : comms;
 #ifdef HCCL_DEBUG_BOUNDS
@@ -145,6 +169,7 @@ template <bool EMU> __device__ __forceinline__ KCtx EnterCollective(const DevCom
     if (threadIdx.x == 0) {
         uint32_t oc = LdVolatile(&k.ctrl->opCount);
         sHalf = oc & 1u;
+        sSeq = oc;
         sEpoch = LdVolatile(&k.ctrl->chanEpoch[k.chan]);
         __threadfence();
         uint32_t t = atomicAdd(&k.ctrl->ticket, 1u);
@@ -152,20 +177,26 @@ template <bool EMU> __device__ __forceinline__ KCtx EnterCollective(const DevCom
             k.ctrl->ticket = 0;
             __threadfence();
             *((volatile uint32_t *)&k.ctrl->opCount) = oc + 1u;
+            if (k.c->progress) *((volatile uint32_t *)k.c->progress) = oc + 1u;
         }
+        if (blockIdx.x == 0 && k.c->traceOn) TraceEnter(k.ctrl, oc);
     }
     __syncthreads();
     k.half = sHalf;
     k.epoch = sEpoch;
     k.syncs = 0;
     k.ok = true;
+    k.seq = sSeq;
     return k;
 }
 
 __device__ __forceinline__ void LeaveCollective(KCtx &k)
 {
     __syncthreads();
-    if (threadIdx.x == 0) *((volatile uint32_t *)&k.ctrl->chanEpoch[k.chan]) = k.epoch + k.syncs;
+    if (threadIdx.x == 0) {
+        *((volatile uint32_t *)&k.ctrl->chanEpoch[k.chan]) = k.epoch + k.syncs;
+        if (k.chan == 0 && k.c->traceOn && k.ok) TraceLeave(k.ctrl, k.seq);
+    }
 }
 
 // Channel barrier across all ranks: every rank's CTA `chan` signals every peer and waits for every peer.
@@ -183,6 +214,7 @@ __device__ __forceinline__ bool ChannelBarrier(KCtx &k, uint32_t phase)
     }
     int all = __syncthreads_and(mine ? 1 : 0);
     if (!all) k.ok = false;
+    else if (k.chan == 0 && threadIdx.x == 0 && k.c->traceOn) TraceBarrier(k.ctrl, k.seq);
     return all != 0;
 }
 

@@ -28,7 +28,7 @@ struct FusedCtx {
 
 __device__ __forceinline__ void FusedInit(const GemmParams &p, FusedCtx &x)
 {
-    __shared__ uint32_t sHalf;
+    __shared__ uint32_t sHalf, sSeq;
     x.c = (const DevComm *)p.comm;
     x.rank = x.c->rank;
     x.n = x.c->nranks;
@@ -44,18 +44,22 @@ __device__ __forceinline__ void FusedInit(const GemmParams &p, FusedCtx &x)
             x.ctrl->ticket = 0;
             __threadfence();
             *((volatile uint32_t *)&x.ctrl->opCount) = oc + 1u;
+            if (x.c->progress) *((volatile uint32_t *)x.c->progress) = oc + 1u;
         }
+        if (blockIdx.x == 0 && x.c->traceOn) dev::TraceEnter(x.ctrl, oc);
+        sSeq = oc;
     }
     __syncthreads();
     x.half = sHalf;
     x.k.c = x.c; x.k.rank = x.rank; x.k.nranks = x.n; x.k.heap = x.heap; x.k.ctrl = x.ctrl; x.k.flags = x.flags;
-    x.k.half = x.half; x.k.chan = blockIdx.x; x.k.epoch = 0; x.k.syncs = 0; x.k.ok = true;
+    x.k.half = x.half; x.k.chan = blockIdx.x; x.k.epoch = 0; x.k.syncs = 0; x.k.ok = true; x.k.seq = sSeq;
 }
 
 // Last CTA out clears the counters of this parity.
 __device__ __forceinline__ void FusedExit(FusedCtx &x)
 {
     __syncthreads();
+    if (blockIdx.x == 0 && threadIdx.x == 0 && x.c->traceOn) dev::TraceLeave(x.ctrl, x.k.seq);
     __shared__ uint32_t sLast;
     if (threadIdx.x == 0) {
         __threadfence();

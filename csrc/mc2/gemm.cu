@@ -85,6 +85,19 @@ uint32_t GemmWaitSleepNs()
     return (uint32_t)(v > 0 ? v : 0);
 }
 
+// HCCL_GEMM_WAIT_HINT_NS / HCCL_GEMM_EPI_SLEEP_NS: suspend-time hint of the CTA-pair kernel's barrier waits and the back-off
+// of its epilogue warps while the next accumulator is being computed.
+uint32_t GemmWaitHintNs()
+{
+    static const int v = [] { const char *e = getenv("HCCL_GEMM_WAIT_HINT_NS"); return e ? atoi(e) : 0; }();
+    return (uint32_t)(v > 0 ? v : 0);
+}
+uint32_t GemmEpiSleepNs()
+{
+    static const int v = [] { const char *e = getenv("HCCL_GEMM_EPI_SLEEP_NS"); return e ? atoi(e) : 0; }();
+    return (uint32_t)(v > 0 ? v : 0);
+}
+
 int SmCount()
 {
     static int n[64] = {0};
@@ -124,7 +137,7 @@ template <int BN> static HcclResult LaunchPlain2CtaT(const void *a, const void *
     using S = Gemm2CtaSmemT<BN>;
     CHK_RET(EncodeTmap2D(&p.tmapA, a, M, K, (uint64_t)K * 2, kBM, kBK, 2));
     CHK_RET(EncodeTmap2D(&p.tmapB, b, N, K, (uint64_t)K * 2, S::BN / 2, kBK, 2));
-    p.C = c; p.M = M; p.N = N; p.K = K; p.ldc = N; p.outFp32 = outFp32; p.groupM = GroupMOverride(8); p.errorWord = GemmErrorWord();
+    p.C = c; p.M = M; p.N = N; p.K = K; p.ldc = N; p.outFp32 = outFp32; p.groupM = GroupMOverride(8); p.errorWord = GemmErrorWord(); p.waitHintNs = GemmWaitHintNs(); p.epiSleepNs = GemmEpiSleepNs();
     static std::atomic<bool> attrSet{false};
     auto kern = GemmKernel2Cta<PlainPolicy, BN>;
     size_t smem = S::kTotal + 1024;

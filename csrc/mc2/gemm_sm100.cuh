@@ -57,6 +57,8 @@ struct GemmParams {
     const uint8_t *sfB;
     uint32_t sfAtomsB;           // 128-row atoms B's scale array holds along N
     uint32_t elemBytes;          // operand element size (0 or 2 = bf16, 1 = fp8)
+    uint32_t waitHintNs;         // suspend-time hint of the barrier waits (0 = plain polling)
+    uint32_t epiSleepNs;         // CTA-pair kernel: back-off of the epilogue's wait for a finished accumulator
 };
 
 template <int BN> struct GemmSmem {

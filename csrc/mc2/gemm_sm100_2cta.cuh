@@ -155,7 +155,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) GemmKernel2Cta(const __grid_c
                     Policy::SelectA(p, ctx, mb, &ta, &rowA);
                 }
                 for (uint32_t kb = 0; kb < kIters && ok; ++kb) {
-                    ok = MbarWait(&empty[stage], phase ^ 1, abortWord);
+                    ok = MbarWaitHint(&empty[stage], phase ^ 1, abortWord, p.waitHintNs);
                     if (!ok) break;
                     const uint32_t fullLeader = cg2::MapToCta(SmemAddr(&full[stage]), 0);
                     if (leader) MbarExpectTx(&full[stage], 2 * (S::kABytes + S::kBBytes));
@@ -170,12 +170,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) GemmKernel2Cta(const __grid_c
             uint32_t stage = 0, phase = 0, acc = 0, accPhase = 0;
             bool ok = true;
             for (uint32_t t = pair; t < numTiles && ok; t += pairs) {
-                ok = MbarWait(&tmemEmpty[acc], accPhase ^ 1, abortWord);
+                ok = MbarWaitHint(&tmemEmpty[acc], accPhase ^ 1, abortWord, p.waitHintNs);
                 if (!ok) break;
                 TcFenceAfter();
                 const uint32_t dTmem = tmemBase + acc * BN;
                 for (uint32_t kb = 0; kb < kIters; ++kb) {
-                    ok = MbarWait(&full[stage], phase, abortWord);
+                    ok = MbarWaitHint(&full[stage], phase, abortWord, p.waitHintNs);
                     if (!ok) break;
                     TcFenceAfter();
                     uint64_t aDesc = MakeSmemDescSw128(SmemAddr(sA + stage * S::kABytes));
@@ -205,7 +205,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) GemmKernel2Cta(const __grid_c
             Policy::TileCoordPairs(p, ctx, t, mPairs, nBlocks, &mb2, &nb);
             const uint32_t mb = mb2 * 2 + rankInPair;
             const bool valid = mb < mBlocks;
-            ok = MbarWait(&tmemFull[acc], accPhase, abortWord);
+            ok = MbarWaitHint(&tmemFull[acc], accPhase, abortWord, p.waitHintNs, p.epiSleepNs);
             if (!ok) break;
             TcFenceAfter();
             const uint32_t rowInTile = ew * 32 + lane;

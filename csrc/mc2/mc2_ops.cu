@@ -357,6 +357,7 @@ HcclResult RunFused(FusedKind kind, Comm *c, const void *a, const void *b, void 
         CHK_RET(LaunchFused<false>(s, p, nullptr, grid, 1, stream));
     }
     c->counters.kernelsLaunched++;
+    c->devOpIssued++;
     CountLaunch();
     c->counters.ops++;
     if (kind == AGMM && gathered && !s.mx) {

@@ -35,7 +35,7 @@ __device__ __forceinline__ KCtx MoeEnter(const DevComm *c, uint32_t chan)
     KCtx k;
     k.c = c; k.rank = c->rank; k.nranks = c->nranks; k.heap = c->heap[c->rank];
     k.ctrl = CtrlOf(k.heap); k.flags = FlagsOf(k.heap);
-    k.half = 0; k.chan = chan; k.syncs = 0; k.ok = true;
+    k.half = 0; k.chan = chan; k.syncs = 0; k.ok = true; k.seq = 0xffffffffu;   // not counted by the op counter: no trace record
     k.epoch = LdVolatile(&k.ctrl->chanEpoch[chan]);
     return k;
 }

@@ -58,6 +58,38 @@ __device__ __forceinline__ bool MbarTryWait(uint64_t *bar, uint32_t parity)
         : "memory");
     return ok != 0;
 }
+// try_wait with a suspend-time hint: the hardware may keep the thread parked up to `hintNs` before it reports "not yet",
+// so a long wait costs a handful of instructions instead of a polling loop that occupies an issue slot.
+__device__ __forceinline__ bool MbarTryWaitHint(uint64_t *bar, uint32_t parity, uint32_t hintNs)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(SmemAddr(bar)), "r"(parity), "r"(hintNs)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait built on it (hintNs = 0 falls back to the plain polling wait). sleepNs > 0 adds a nanosleep between polls:
+// only for waits that are off the critical path.
+__device__ __forceinline__ bool MbarWaitHint(uint64_t *bar, uint32_t parity, volatile uint32_t *abortWord, uint32_t hintNs, uint32_t sleepNs = 0)
+{
+    uint64_t start = 0;
+    uint32_t spins = 0;
+    while (!(hintNs ? MbarTryWaitHint(bar, parity, hintNs) : MbarTryWait(bar, parity))) {
+        if (sleepNs) __nanosleep(sleepNs);
+        if ((++spins & (hintNs || sleepNs ? 0xfu : 0x3ffu)) == 0) {
+            uint64_t now;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+            if (start == 0) start = now;
+            if (*abortWord != 0 || now - start > 2000000000ull) { *abortWord = 1; return false; }
+        }
+    }
+    return true;
+}
+
 // Bounded wait: ~2 s of polling at most; false => the caller must unwind.
 __device__ __forceinline__ bool MbarWait(uint64_t *bar, uint32_t parity, volatile uint32_t *abortWord)
 {

@@ -50,8 +50,14 @@ class Result(enum.IntEnum):
     E_UNAVAIL = 7
     E_SYSCALL = 8
     E_TIMEOUT = 9
+    E_OPEN_FILE_FAILURE = 10
+    E_TCP_TRANSFER = 13
+    E_RUNTIME = 15
+    E_DRV = 16
     E_REMOTE = 21
     E_SUSPENDING = 22
+    E_OPRETRY_FAIL = 23
+    E_OOM = 24
 
 
 _NP = {"int8": DataType.INT8, "int16": DataType.INT16, "int32": DataType.INT32, "float16": DataType.FP16,

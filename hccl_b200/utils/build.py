@@ -22,18 +22,6 @@ CUDA_HOME = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 
-def _cutlass_include() -> str | None:
-    """CuTe/CUTLASS headers vendored inside site-packages (used only for type/descriptor helpers)."""
-    import site
-
-    for sp in site.getsitepackages():
-        for rel in ("flashinfer/data/cutlass/include", "tilelang/3rdparty/cutlass/include"):
-            p = Path(sp) / rel
-            if (p / "cute").is_dir():
-                return str(p)
-    return None
-
-
 def _sources(exclude_dirs=("torch",)):
     cc, cu = [], []
     for p in sorted(CSRC.rglob("*")):

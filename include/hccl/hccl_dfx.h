@@ -67,6 +67,21 @@ HcclResult HcclDescribeEnvConfig(char *buf, uint32_t bufLen);
 /* Ordered "rank:phase:step," record of communicator destroy / resume steps taken by this process since the last call. */
 HcclResult HcclTakeLifecycleLog(char *buf, uint32_t bufLen);
 HcclResult HcclInjectBootstrapDrop(HcclComm comm, int n);   /* next n bootstrap contributions of this rank vanish */
+HcclResult HcclInjectOpDrop(HcclComm comm, int n);          /* next n operators of this rank are recorded but not launched */
+
+/* Fault handling. HcclCommOpRetry is the collective recovery step that HCCL_OP_RETRY_ENABLE also runs by itself at the next
+ * operator call after a wait timeout: ranks agree that they stopped at the same operator and that its input is intact,
+ * resume the communicator and issue it again (HCCL_OP_RETRY_PARAMS), HCCL_E_OPRETRY_FAIL otherwise. */
+HcclResult HcclCommOpRetry(HcclComm comm);
+/* Last STUCK report of the heartbeat watchdog and last task-exception report (flag words of the failing channel, last
+ * operators); empty strings when there was none. */
+HcclResult HcclGetFaultReports(HcclComm comm, char *stuck, uint32_t stuckLen, char *exception, uint32_t exceptionLen);
+HcclResult HcclGetFaultCounters(HcclComm comm, uint64_t *opRetries, uint64_t *stuckReports, uint64_t *exceptionDumps);
+/* Renders a binary dump written to HCCL_EXCEPTION_DUMP_DIR as text. */
+HcclResult HcclReadExceptionDump(const char *path, char *buf, uint32_t bufLen);
+/* Device-side timestamps (GPU %globaltimer, ns) of the most recent collective / fused kernels of a CUDA communicator:
+ * rows of 6 values {devSeq, syncs passed, enter, first sync, last sync, leave}. HcclDumpTrace merges them into its file. */
+HcclResult HcclGetDeviceTrace(HcclComm comm, uint64_t *rows, uint32_t maxRecords, uint32_t *numRecords);
 
 #ifdef __cplusplus
 }

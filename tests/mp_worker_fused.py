@@ -8,7 +8,7 @@ import torch.distributed as dist
 
 sys.path.insert(0, os.path.join(os.path.dirname(__file__), ".."))
 from hccl_b200.comm import init_from_env  # noqa: E402
-from hccl_b200.ops import gemm, mc2  # noqa: E402
+from hccl_b200.ops import gemm, mc2, mxfp8 as mx  # noqa: E402
 
 
 def rel(a, b):
@@ -59,6 +59,39 @@ def main():
         dist.all_reduce(hi, op=dist.ReduceOp.MAX)
         if r > 1e-2 or lo.item() != hi.item():
             fails.append(f"mmar {M}x{N}x{K} rel={r:.4f} identical={lo.item() == hi.item()}")
+    # ---- block-scaled fp8 forms: operands quantised on this rank, references from the dequantised values
+    for (m_local, N, K) in [(128, 256, 256), (1024, 3584, 8192), (256, 1024, 1024)]:
+        a = mx.quantize(torch.randn(m_local, K, generator=g, device="cuda").to(torch.bfloat16))
+        w = mx.quantize((torch.randn(N, K, generator=g, device="cuda") * 0.05).to(torch.bfloat16))
+        out = mx.all_gather_matmul(comm, a, w)
+        torch.cuda.synchronize()
+        mine = mx.dequantize(a)
+        full = torch.empty(n * m_local, K, dtype=torch.float32, device="cuda")
+        dist.all_gather_into_tensor(full, mine)
+        r = rel(out, full @ mx.dequantize(w).t())
+        if r > 1e-2:
+            fails.append(f"agmm-mxfp8 {m_local}x{N}x{K} rel={r:.4f}")
+    for (M, N, K) in [(128 * n, 256, 256), (8192, 8192, 3584), (256 * n, 520, 384)]:
+        a = mx.quantize(torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16))
+        w = mx.quantize((torch.randn(N, K, generator=g, device="cuda") * 0.05).to(torch.bfloat16))
+        out = mx.matmul_reduce_scatter(comm, a, w)
+        torch.cuda.synchronize()
+        partial = (mx.dequantize(a) @ mx.dequantize(w).t()).to(torch.bfloat16).float()
+        dist.all_reduce(partial)
+        rows = M // n
+        r = rel(out, partial[rank * rows:(rank + 1) * rows])
+        if r > 1.5e-2:
+            fails.append(f"mmrs-mxfp8 {M}x{N}x{K} rel={r:.4f}")
+    for (M, N, K) in [(128, 128 * n * 2, 256), (128, 8192, 1024)]:
+        a = mx.quantize(torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16))
+        w = mx.quantize((torch.randn(N, K, generator=g, device="cuda") * 0.05).to(torch.bfloat16))
+        out = mx.matmul_all_reduce(comm, a, w)
+        torch.cuda.synchronize()
+        partial = (mx.dequantize(a) @ mx.dequantize(w).t()).to(torch.bfloat16).float()
+        dist.all_reduce(partial)
+        r = rel(out, partial)
+        if r > 1.5e-2:
+            fails.append(f"mmar-mxfp8 {M}x{N}x{K} rel={r:.4f}")
     gemm.check_error()
     ok = comm.async_error() == 0
     comm.destroy()

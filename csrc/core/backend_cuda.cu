@@ -135,6 +135,31 @@ void CudaFillRankDesc(int dev, RankDesc *d)
     }
 }
 
+// This rank's view of its links: peer access and its quality from the CUDA runtime, NVLink or not from NVML.
+void CudaFillLinkRow(int dev, const std::vector<RankDesc> &all, uint32_t myRank, LinkRow *row)
+{
+    memset(row, 0, sizeof(*row));
+    (void)NvmlProbePair(all[myRank].busId, nullptr, nullptr, &row->nvlinkActive, &row->nvlinkVersion);
+    for (uint32_t r = 0; r < all.size() && r < (uint32_t)kTopoMaxRanks; ++r) {
+        row->perfRank[r] = 255;
+        if (r == myRank) { row->type[r] = (uint8_t)LinkType::SHM; continue; }
+        if (all[r].hostHash != all[myRank].hostHash || all[r].deviceId < 0) { row->type[r] = (uint8_t)LinkType::NET; continue; }
+        if (all[r].deviceId == dev) { row->type[r] = (uint8_t)LinkType::SHM; row->perfRank[r] = 0; row->atomics[r] = 1; continue; }
+        int can = 0;
+        if (cudaDeviceCanAccessPeer(&can, dev, all[r].deviceId) != cudaSuccess) { (void)cudaGetLastError(); can = 0; }
+        if (!can) { row->type[r] = (uint8_t)LinkType::NONE; continue; }
+        int perf = 255, atom = 0;
+        if (cudaDeviceGetP2PAttribute(&perf, cudaDevP2PAttrPerformanceRank, dev, all[r].deviceId) != cudaSuccess) { (void)cudaGetLastError(); perf = 255; }
+        if (cudaDeviceGetP2PAttribute(&atom, cudaDevP2PAttrNativeAtomicSupported, dev, all[r].deviceId) != cudaSuccess) { (void)cudaGetLastError(); atom = 0; }
+        row->perfRank[r] = (uint8_t)std::min(perf, 255);
+        row->atomics[r] = (uint8_t)(atom != 0);
+        int nvl = -1;
+        (void)NvmlProbePair(all[myRank].busId, all[r].busId, &nvl, nullptr, nullptr);
+        // NVML decides when it can; otherwise native atomics over the link mean NVLink (PCIe peers have none)
+        row->type[r] = (uint8_t)((nvl == 1 || (nvl < 0 && atom)) ? LinkType::NVLINK : LinkType::PCIE);
+    }
+}
+
 HcclResult CudaAllocDevice(void **p, uint64_t bytes) { RT_CHK(cudaMalloc(p, bytes)); return HCCL_SUCCESS; }
 void CudaFreeDevice(void *p) { if (p) cudaFree(p); }
 HcclResult CudaCopyToDevice(void *dst, const void *src, uint64_t bytes) { RT_CHK(cudaMemcpy(dst, src, bytes, cudaMemcpyHostToDevice)); return HCCL_SUCCESS; }

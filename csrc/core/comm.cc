@@ -215,6 +215,22 @@ HcclResult CommCreate(uint32_t nranks, const HcclRootInfo *info, uint32_t rank, 
     // every rank must have chosen the same backend
     for (auto &d : all) if ((d.deviceId >= 0) != haveCuda) { HCCL_ERROR("ranks disagree on the backend (rank %u has device %d)", d.rank, d.deviceId); return HCCL_E_PARA; }
     CHK_RET(BuildTopoInfo(all, rank, &c->topo));
+    if (haveCuda && nranks <= (uint32_t)kTopoMaxRanks) {
+        // second round: every rank reports its links to the others (peer access, NVLink or PCIe, active NVLink count)
+        extern void CudaFillLinkRow(int dev, const std::vector<RankDesc> &all, uint32_t myRank, LinkRow *row);
+        LinkRow mine;
+        CudaFillLinkRow(dev, all, rank, &mine);
+        std::vector<LinkRow> rows(nranks);
+        CHK_RET(c->boot->AllGather(&mine, sizeof(mine), rows.data()));
+        CHK_RET(ApplyLinkRows(rows, &c->topo));
+        if (!c->topo.allPeersDirect) {
+            std::string pairs;
+            for (auto &m : c->topo.missingLinks) pairs += " " + std::to_string(m.first) + "-" + std::to_string(m.second);
+            HCCL_ERROR("comm creation: ranks%s have no direct peer path (devices without peer access); the symmetric heap, and with it the SM, NVLS "
+                       "and copy engines, need every pair of one server to be peer-accessible", pairs.c_str());
+            return HCCL_E_UNAVAIL;
+        }
+    }
 
     HcclResult r = haveCuda ? CudaBackendInit(c.get()) : SimBackendInit(c.get());
     if (r != HCCL_SUCCESS) {

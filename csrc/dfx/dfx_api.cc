@@ -10,6 +10,7 @@
 #include "../exec/op_common.h"
 #include "../select/selector.h"
 #include "../sim/checker.h"
+#include "../topo/topo_info.h"
 #include "hccl/hccl_dfx.h"
 
 using namespace hccl;
@@ -249,6 +250,48 @@ HcclResult HcclTakeLifecycleLog(char *buf, uint32_t bufLen)
     std::string s = LifecycleLogTake();
     snprintf(buf, bufLen, "%s", s.c_str());
     return HCCL_SUCCESS;
+}
+
+// Topology from a caller-supplied link matrix (no devices needed): linkTypes[a * nranks + b] is the LinkType value from a to
+// b (0 none, 1 NVLink, 2 PCIe, 3 shared memory, 4 network). Writes the description and, for `matchKind` (0 flat, 1 multi-level,
+// 2 three-level, 3 squeeze-2D, 4 link islands), this rank's groups as "r,r,..|r,r,..".
+HcclResult HcclTopoFromLinks(uint32_t nranks, uint32_t ranksPerServer, const uint8_t *linkTypes, const uint32_t *nvlinkActive, int nvlsCapable,
+                             uint32_t myRank, int matchKind, char *desc, uint32_t descLen, char *groups, uint32_t groupsLen)
+{
+    if (!linkTypes || nranks == 0 || ranksPerServer == 0 || nranks % ranksPerServer || nranks > (uint32_t)kTopoMaxRanks || myRank >= nranks) return HCCL_E_PARA;
+    std::vector<RankDesc> descs(nranks);
+    for (uint32_t r = 0; r < nranks; ++r) {
+        descs[r] = RankDesc{};
+        descs[r].rank = r; descs[r].deviceId = (int32_t)(r % ranksPerServer); descs[r].hostHash = 1000 + r / ranksPerServer; descs[r].nvlsCapable = nvlsCapable ? 1u : 0u;
+    }
+    TopoInfo t;
+    CHK_RET(BuildTopoInfo(descs, myRank, &t));
+    std::vector<LinkRow> rows(nranks);
+    for (uint32_t a = 0; a < nranks; ++a) {
+        memset(&rows[a], 0, sizeof(LinkRow));
+        for (uint32_t b = 0; b < nranks; ++b) rows[a].type[b] = linkTypes[a * nranks + b];
+        rows[a].nvlinkActive = nvlinkActive ? nvlinkActive[a] : 0;
+    }
+    CHK_RET(ApplyLinkRows(rows, &t));
+    if (desc && descLen) CHK_RET(CopyOut(t.Describe(), desc, descLen));
+    if (groups && groupsLen) {
+        AlgHierarchyInfo h;
+        CHK_RET(TopoMatch(t, (TopoMatchKind)matchKind, &h));
+        std::string s;
+        for (size_t l = 0; l < h.levelRanks.size(); ++l) {
+            if (l) s += "|";
+            for (size_t i = 0; i < h.levelRanks[l].size(); ++i) s += (i ? "," : "") + std::to_string(h.levelRanks[l][i]);
+        }
+        CHK_RET(CopyOut(s, groups, groupsLen));
+    }
+    return HCCL_SUCCESS;
+}
+
+// NVLink facts about device `busIdA` (and its pair with `busIdB`) as read from NVML: see NvmlProbePair.
+HcclResult HcclTopoProbeNvml(const char *busIdA, const char *busIdB, int *nvlinkP2P, uint32_t *activeLinks, uint32_t *version)
+{
+    if (!busIdA) return HCCL_E_PTR;
+    return NvmlProbePair(busIdA, busIdB, nvlinkP2P, activeLinks, version);
 }
 
 HcclResult HcclInjectOpDrop(HcclComm comm, int n)

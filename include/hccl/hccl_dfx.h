@@ -60,6 +60,13 @@ HcclResult HcclCheckAlgorithm(HcclCMDType op, const char *algName, uint32_t supe
 /* Names registered for an op, ';' separated. */
 HcclResult HcclListAlgorithms(HcclCMDType op, char *buf, uint32_t bufLen);
 
+/* Topology discovery without devices: builds the topology from a link matrix (LinkType values, row-major [from][to]) and
+ * returns its description and the rank groups a matcher derives. See csrc/topo/topo_info.h for the matcher kinds. */
+HcclResult HcclTopoFromLinks(uint32_t nranks, uint32_t ranksPerServer, const uint8_t *linkTypes, const uint32_t *nvlinkActive, int nvlsCapable,
+                             uint32_t myRank, int matchKind, char *desc, uint32_t descLen, char *groups, uint32_t groupsLen);
+/* What NVML (or the library HCCL_NVML_LIB names) reports for a device and a pair of devices, by PCI bus id. Read-only. */
+HcclResult HcclTopoProbeNvml(const char *busIdA, const char *busIdB, int *nvlinkP2P, uint32_t *activeLinks, uint32_t *version);
+
 /* Test hooks. */
 void HcclResetEnvConfigForTest(void);
 /* Re-parses every HCCL_* environment variable and writes the result as "key=value;..."; the parse error otherwise. */

@@ -29,7 +29,9 @@ struct World {
     Value &At(uint32_t rank, int kind, uint64_t elem) { return mem[{rank, kind}][elem]; }
 };
 
-uint64_t InputElems(const CheckSpec &s, uint32_t rank)
+}  // namespace
+
+uint64_t CheckInputElems(const CheckSpec &s, uint32_t rank)
 {
     switch (s.op) {
         case HCCL_CMD_REDUCE_SCATTER: case HCCL_CMD_ALLTOALL: case HCCL_CMD_SCATTER: return s.count * s.nranks;
@@ -39,6 +41,20 @@ uint64_t InputElems(const CheckSpec &s, uint32_t rank)
         default: return s.count;
     }
 }
+
+uint64_t CheckOutputElems(const CheckSpec &s, uint32_t rank)
+{
+    switch (s.op) {
+        case HCCL_CMD_ALLGATHER: case HCCL_CMD_ALLTOALL: return s.count * s.nranks;
+        case HCCL_CMD_ALLTOALLV: case HCCL_CMD_ALLTOALLVC: { uint64_t t = 0; for (uint32_t j = 0; j < s.nranks; ++j) t += s.countMatrix[j * s.nranks + rank]; return t; }
+        case HCCL_CMD_ALLGATHER_V: { uint64_t t = 0; for (uint32_t j = 0; j < s.nranks; ++j) t += s.countMatrix[j]; return t; }
+        case HCCL_CMD_REDUCE_SCATTER_V: return s.countMatrix[rank];
+        default: return s.count;
+    }
+}
+
+namespace {
+uint64_t InputElems(const CheckSpec &s, uint32_t rank) { return CheckInputElems(s, rank); }
 
 std::string Where(uint32_t rank, size_t q, size_t idx, const Task &t)
 {
@@ -81,9 +97,22 @@ HcclResult CheckPlans(const CheckSpec &spec, const std::vector<std::vector<Plan>
         std::vector<Access> accesses;
         size_t remaining = 0;
         for (auto &p : plans) remaining += p.TaskCount();
-        auto bounds = [&](const BufRef &b, uint64_t bytes) {
-            if (b.kind == BufKind::CCL) return b.off + bytes <= spec.cclBytes;
-            return true;
+        // which rank's buffer a reference names decides its size: `owner` is the rank whose memory is touched
+        auto bounds = [&](const BufRef &b, uint64_t bytes, uint32_t owner) {
+            switch (b.kind) {
+                case BufKind::CCL: return b.off + bytes <= spec.cclBytes;
+                case BufKind::MAILBOX: return spec.mailboxBytes == 0 || b.off + bytes <= spec.mailboxBytes * 2 * (uint64_t)n;
+                case BufKind::INPUT: return b.off + bytes <= std::max<uint64_t>(CheckInputElems(spec, owner), spec.op == HCCL_CMD_BROADCAST ? spec.count : 0) * es;
+                case BufKind::OUTPUT: return b.off + bytes <= CheckOutputElems(spec, owner) * es;
+                default: return true;
+            }
+        };
+        // absolute addresses of BatchSendRecv items -> (INPUT | OUTPUT, offset)
+        auto resolve = [&](BufRef b) {
+            if (b.kind != BufKind::ABS) return b;
+            if (spec.absOutputBase && b.off >= spec.absOutputBase) return BufRef{BufKind::OUTPUT, b.off - spec.absOutputBase};
+            if (spec.absInputBase && b.off >= spec.absInputBase) return BufRef{BufKind::INPUT, b.off - spec.absInputBase};
+            return b;
         };
         while (remaining > 0) {
             bool progressed = false;
@@ -91,7 +120,9 @@ HcclResult CheckPlans(const CheckSpec &spec, const std::vector<std::vector<Plan>
                 for (size_t q = 0; q < plans[r].queues.size(); ++q) {
                     const auto &queue = plans[r].queues[q];
                     while (pc[r][q] < queue.size()) {
-                        const Task &t = queue[pc[r][q]];
+                        Task t = queue[pc[r][q]];
+                        t.dst = resolve(t.dst);
+                        t.src = resolve(t.src);
                         std::vector<uint32_t> &ck = clock[r][q];
                         if (t.type == TaskType::WAIT) {
                             auto it = inflight.find({r, t.rank, t.slot});
@@ -107,12 +138,15 @@ HcclResult CheckPlans(const CheckSpec &spec, const std::vector<std::vector<Plan>
                             return fail("LOCAL_POST / LOCAL_WAIT are not used by the built-in templates: " + Where(r, q, pc[r][q], t));
                         } else if (t.type != TaskType::WAIT) {
                             if (t.bytes % es) return fail("transfer is not a whole number of elements at " + Where(r, q, pc[r][q], t));
-                            if (!bounds(t.dst, t.bytes) || !bounds(t.src, t.bytes)) return fail("scratch window overrun at " + Where(r, q, pc[r][q], t));
                             const bool remoteDst = t.type == TaskType::WRITE || t.type == TaskType::WRITE_REDUCE;
                             const bool remoteSrc = t.type == TaskType::READ || t.type == TaskType::READ_REDUCE;
                             const bool reduce = t.type == TaskType::LOCAL_REDUCE || t.type == TaskType::WRITE_REDUCE || t.type == TaskType::READ_REDUCE;
                             const uint32_t dstRank = remoteDst ? t.rank : r, srcRank = remoteSrc ? t.rank : r;
                             if (dstRank >= n || srcRank >= n) return fail("transfer names an invalid rank at " + Where(r, q, pc[r][q], t));
+                            for (const BufRef *b : {&t.dst, &t.src})
+                                if (!bounds(*b, t.bytes, b == &t.dst ? dstRank : srcRank))
+                                    return fail(std::string(b->kind == BufKind::CCL ? "scratch window" : b->kind == BufKind::MAILBOX ? "mailbox" : "user buffer") +
+                                                " overrun at " + Where(r, q, pc[r][q], t));
                             if ((remoteDst && t.dst.kind != BufKind::CCL && t.dst.kind != BufKind::MAILBOX) || (remoteSrc && t.src.kind != BufKind::CCL && t.src.kind != BufKind::MAILBOX))
                                 return fail("remote access outside the symmetric heap at " + Where(r, q, pc[r][q], t));
                             accesses.push_back({srcRank, (int)t.src.kind, t.src.off, t.src.off + t.bytes, false, ck, r, (uint32_t)q, (uint32_t)pc[r][q]});
@@ -222,6 +256,17 @@ HcclResult CheckPlans(const CheckSpec &spec, const std::vector<std::vector<Plan>
                 uint64_t o = 0;
                 for (uint32_t j = 0; j < r; ++j) o += spec.countMatrix[j];
                 for (uint64_t i = 0; i < spec.countMatrix[r]; ++i) { Value v; for (uint32_t s = 0; s < n; ++s) v.push_back({s, o + i}); if (!expect(r, i, v)) return bad(r, i); }
+                break;
+            }
+            case HCCL_CMD_SEND: case HCCL_CMD_RECEIVE:
+                if (r == spec.peer) for (uint64_t i = 0; i < cnt; ++i) if (!expect(r, i, {{spec.root, i}})) return bad(r, i);
+                break;
+            case HCCL_CMD_BATCH_SEND_RECV: {
+                // first half arrives from rank - 1, second half from rank + 1 (their matching halves)
+                const uint64_t h = cnt / 2;
+                const uint32_t prev = (r + n - 1) % n, next = (r + 1) % n;
+                for (uint64_t i = 0; i < h; ++i) if (!expect(r, i, {{prev, i}})) return bad(r, i);
+                for (uint64_t i = h; i < cnt; ++i) if (!expect(r, i, {{next, i}})) return bad(r, i);
                 break;
             }
             default: break;   // barrier: deadlock / notify balance only

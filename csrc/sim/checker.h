@@ -25,7 +25,20 @@ struct CheckSpec {
     uint32_t root;
     uint64_t cclBytes;
     std::vector<uint64_t> countMatrix;    // AlltoAllV(C): n*n (row = sender); AllGatherV / ReduceScatterV: n
+    // point-to-point operators: Send / Receive move `count` elements from rank `root` to rank `peer`; BatchSendRecv is
+    // checked as a bidirectional ring (every rank sends the first half of its input to rank + 1 and the second half to
+    // rank - 1, and receives the matching halves into its output).
+    uint32_t peer = 0;
+    uint64_t mailboxBytes = 0;            // bytes of one mailbox slot (0 = unchecked)
+    // ABS buffer references (BatchSendRecv items carry absolute addresses) are mapped back to the rank's input / output by range
+    uint64_t absInputBase = 0, absOutputBase = 0;
 };
+uint64_t CheckInputElems(const CheckSpec &s, uint32_t rank);
+uint64_t CheckOutputElems(const CheckSpec &s, uint32_t rank);
+
+struct SmLaunch;
+// Schedule model of one SM / NVLS kernel launch (sm_models.cc).
+HcclResult GenSmModelPlan(const std::vector<SmLaunch> &all, uint32_t me, uintptr_t inBase, uintptr_t outBase, uint32_t channels, Plan *out);
 
 // plans[chunk][rank]; chunks run one after the other and share the symbolic memory.
 HcclResult CheckPlans(const CheckSpec &spec, const std::vector<std::vector<Plan>> &plans, std::string *why);

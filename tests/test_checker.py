@@ -95,3 +95,88 @@ def test_checker_catches_a_broken_schedule():
     # a scratch window too small for the one-shot slots must be reported as an overrun, not silently accepted
     rc, msg = check(CMD["ALLREDUCE"], "InsAllReduceMesh1DOneShot", (1, 1, 4), 128, ccl=700)
     assert rc != 0
+
+
+# ---- point-to-point schedules (mailbox slots of `ccl` bytes; a small value forces several rounds through the two slots)
+P2P = dict(SEND=4, RECEIVE=5, BATCH_SEND_RECV=13)
+
+
+@pytest.mark.parametrize("nranks", [2, 3, 5, 8])
+@pytest.mark.parametrize("count,slot", [(1, 4096), (1000, 4096), (5000, 4096), (4097, 1024), (64, 256)])
+def test_send_receive_schedules(nranks, count, slot):
+    for root in (0, nranks - 1):
+        rc, msg = check(P2P["SEND"], None, (1, 1, nranks), count, root=root, ccl=slot)
+        assert rc == 0, msg
+
+
+@pytest.mark.parametrize("nranks", [2, 3, 4, 7])
+@pytest.mark.parametrize("count,slot", [(2, 4096), (1001, 4096), (6000, 2048), (300, 128)])
+def test_batch_send_recv_ring_schedule(nranks, count, slot):
+    rc, msg = check(P2P["BATCH_SEND_RECV"], None, (1, 1, nranks), count, ccl=slot)
+    assert rc == 0, msg
+
+
+def test_user_buffer_overrun_is_reported():
+    """Bounds are checked for the caller's buffers and the mailbox too, not only for the scratch window: a schedule that
+    receives more than the output holds is rejected. The all-gather-v template with counts that disagree with the output
+    size the operator defines is such a schedule."""
+    l = lib()
+    l.HcclCheckPlanText.argtypes = [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_uint32]
+    l.HcclCheckPlanText.restype = ctypes.c_int
+    msg = ctypes.create_string_buffer(2048)
+    # op=AllGather count=4 elems (fp32), 2 ranks; rank 1's write into rank 0's scratch is fine, its final copy overruns OUTPUT
+    good = b"op=6 n=2 es=4 count=4 ccl=1024\nr0: COPY out@0 in@0 16; WRITE 1 ccl@0 in@0 16; POST 1 1; WAIT 1 1; COPY out@16 ccl@0 16\n" \
+           b"r1: COPY out@16 in@0 16; WRITE 0 ccl@0 in@0 16; POST 0 1; WAIT 0 1; COPY out@0 ccl@0 16\n"
+    assert l.HcclCheckPlanText(good, msg, 2048) == 0, msg.value
+    bad = good.replace(b"COPY out@16 ccl@0 16", b"COPY out@20 ccl@0 16")
+    assert l.HcclCheckPlanText(bad, msg, 2048) != 0 and b"user buffer overrun" in msg.value
+    race = good.replace(b"POST 1 1; WAIT 1 1; ", b"").replace(b"POST 0 1; WAIT 0 1; ", b"")
+    assert l.HcclCheckPlanText(race, msg, 2048) != 0 and b"memory conflict" in msg.value
+    hang = good.replace(b"POST 0 1; ", b"")
+    assert l.HcclCheckPlanText(hang, msg, 2048) != 0 and b"deadlock" in msg.value
+
+
+# ---- the kernels of the SM / NVLS engines, through schedule models built from the real launch lists
+SM_ALGOS = {
+    "ALLREDUCE": ["SmAllReduceMesh1DOneShot", "SmAllReduceMesh1DTwoShot", "SmAllReduceRing", "NvlsAllReduceOneShot", "NvlsAllReduceTwoShot"],
+    "ALLGATHER": ["SmAllGatherMesh1D"],
+    "REDUCE_SCATTER": ["SmReduceScatterMesh1D", "NvlsReduceScatter"],
+    "BROADCAST": ["SmBroadcastMesh1D", "NvlsBroadcast"],
+    "REDUCE": ["SmReduceMesh1D"],
+    "SCATTER": ["SmScatterMesh1D"],
+    "ALLTOALL": ["SmAlltoAllMesh1D"],
+    "BARRIER": ["SmBarrierMesh1D"],
+}
+
+
+@pytest.mark.parametrize("nranks", [2, 3, 4, 5, 8])
+@pytest.mark.parametrize("op", list(SM_ALGOS))
+def test_sm_and_nvls_kernel_models(op, nranks):
+    for alg in SM_ALGOS[op]:
+        for count in (4, 36, 260, 5000):            # multiples of 4 elements: the NVLS kernels take 16-byte multiples
+            rc, msg = check(CMD[op], alg, (1, 1, nranks), count, root=nranks - 1, ccl=(1 << 20))
+            assert rc == 0, msg
+
+
+@pytest.mark.parametrize("nranks", [2, 4, 7])
+def test_sm_kernel_models_with_chunk_loops(nranks):
+    for op in ("ALLREDUCE", "ALLGATHER", "REDUCE_SCATTER", "BROADCAST", "REDUCE", "SCATTER"):
+        for alg in SM_ALGOS[op]:
+            rc, msg = check(CMD[op], alg, (1, 1, nranks), 9000, root=1, ccl=(192 << 10) if op != "ALLREDUCE" or "Ring" not in alg else (512 << 10))
+            assert rc == 0, msg
+
+
+@pytest.mark.parametrize("nranks", [2, 3, 6])
+def test_sm_alltoallv_and_v_forms(nranks):
+    import random
+    rng = random.Random(nranks)
+    cm = [rng.choice([0, 1, 33, 700]) for _ in range(nranks * nranks)]
+    for a in range(nranks):
+        cm[a * nranks + (a + 1) % nranks] = 0        # a zero row entry per sender
+    rc, msg = check(CMD["ALLTOALLV"], "SmAlltoAllVMesh1D", (1, 1, nranks), 0, counts=cm, ccl=(1 << 20))
+    assert rc == 0, msg
+    counts = [rng.choice([0, 5, 129, 1000]) for _ in range(nranks)]
+    rc, msg = check(CMD["ALLGATHER_V"], "SmAllGatherVMesh1D", (1, 1, nranks), 0, counts=counts, ccl=(1 << 20))
+    assert rc == 0, msg
+    rc, msg = check(CMD["REDUCE_SCATTER_V"], "SmReduceScatterVMesh1D", (1, 1, nranks), 0, counts=counts, ccl=(1 << 20))
+    assert rc == 0, msg

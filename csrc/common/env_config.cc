@@ -320,6 +320,7 @@ HcclResult ParseSplitRatio(const std::string &v, AlgEnvConfig *cfg)
     }
     cfg->multiDimSplitRatio[0] = a;
     cfg->multiDimSplitRatio[1] = b;
+    cfg->multiDimSplitSet = true;
     return HCCL_SUCCESS;
 }
 

@@ -49,8 +49,9 @@ struct AlgEnvConfig {
     uint32_t connectionFaultDetectionSec = 20;
     uint32_t taskMonitorIntervalMs = 0;
     InconsistentCheck inconsistentCheck = InconsistentCheck::FIRST;
-    // multi-dimension split ratio for the parallel executor (kept for API parity; one NVSwitch level => unused)
+    // split ratio of the concurrent algorithms (one payload shared by two algorithms in one launch): first : second part
     uint32_t multiDimSplitRatio[2] = {1, 1};
+    bool multiDimSplitSet = false;
     // link-type switches accepted for compatibility
     bool intraRoceEnable = false, intraPcieEnable = false, interHccsDisable = false;
     // bootstrap

@@ -255,7 +255,7 @@ HcclResult HcclCheckAlgorithm(HcclCMDType op, const char *algName, uint32_t supe
             for (size_t ci = 0; ci < chunks.size(); ++ci) {
                 std::vector<SmLaunch> all;
                 for (uint32_t r = 0; r < n; ++r) all.push_back(smLaunches[r][ci]);
-                const uint32_t channels = std::min<uint32_t>(all[0].ctas, 3);
+                const uint32_t channels = std::max<uint32_t>(std::min<uint32_t>(all[0].ctas, 3), all[0].args.splitCtas ? 2 : 1);
                 for (uint32_t r = 0; r < n; ++r) {
                     Plan pl;
                     CHK_RET(GenSmModelPlan(all, r, 0x1000, 0x2000000, channels, &pl));

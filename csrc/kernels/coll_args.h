@@ -35,6 +35,8 @@ enum SmKernelId : uint32_t {
     K_ALLGATHER_PIPE_NVLS,
     K_ALLTOALL_PIPE,          // AlltoAll with uniform counts
     K_ALLREDUCE_RING,         // reduce-scatter + all-gather around the ring (comparator for the mesh kernels)
+    K_ALLREDUCE_CONCURRENT,   // two-shot on two sub-grids: both parts by peer stores (no multicast mapping)
+    K_ALLREDUCE_CONCURRENT_NVLS,   // ... the first part switch-reduced, the second by peer stores
     K_COUNT
 };
 
@@ -57,6 +59,10 @@ struct CollArgs {
     uint64_t sendOff[kMaxRanks];
     uint64_t recvBytes[kMaxRanks];
     uint64_t recvOff[kMaxRanks];
+    // concurrent kernels: the first splitBytes of the payload go to the first splitCtas CTAs (first algorithm)
+    uint64_t splitBytes;
+    uint32_t splitCtas;
+    uint32_t pad1;
 };
 
 struct BatchItem {
@@ -88,6 +94,7 @@ struct SmPlanCtx {
     uint64_t mailboxBytes;
     uint32_t maxCtas;         // 0 = default heuristic
     bool nvls;
+    uint32_t splitRatio[2] = {0, 0};   // concurrent algorithms: shares of the first / second part (0:0 = built-in default)
 };
 
 // Builds the launch list of one operator for one rank. Returns HCCL_E_NOT_SUPPORT when the algorithm cannot take

@@ -58,29 +58,33 @@ template <typename T, int OP, bool EMU> __device__ void AllReduceOneShotBody(KCt
 // ================================================================================================ AllReduce two-shot
 // Reduce-scatter by push (slice j of every rank lands in rank j's slots), ordered reduce of the own slice, all-gather
 // by pull from the owners' result regions.
-template <typename T, int OP, bool EMU> __device__ void AllReduceTwoShotBody(KCtx &k, const CollArgs &A)
+template <typename T, int OP> __device__ void AllReduceTwoShotCore(KCtx &k, const char *in, char *out, uint64_t bytes)
 {
     const int n = k.nranks;
-    const uint64_t slice = Up128((A.bytes + n - 1) / n);
+    const uint64_t slice = Up128((bytes + n - 1) / n);
     for (int d = 0; d < n; ++d) {
         int r = (k.rank + d) % n;
-        Part p = PartOf(SliceLen(A.bytes, slice, r), gridDim.x, blockIdx.x);
-        BlockCopy(k.Ccl(r) + (uint64_t)k.rank * slice + p.off, (const char *)A.in + (uint64_t)r * slice + p.off, p.len);
+        Part p = PartOf(SliceLen(bytes, slice, r), k.vGrid, k.vBlock);
+        BlockCopy(k.Ccl(r) + (uint64_t)k.rank * slice + p.off, in + (uint64_t)r * slice + p.off, p.len);
     }
     if (!ChannelBarrier(k, 1)) return;
     {
-        Part p = PartOf(SliceLen(A.bytes, slice, k.rank), gridDim.x, blockIdx.x);
+        Part p = PartOf(SliceLen(bytes, slice, k.rank), k.vGrid, k.vBlock);
         const char *slots[kMaxRanks];
         for (int r = 0; r < n; ++r) slots[r] = k.Ccl(k.rank) + (uint64_t)r * slice + p.off;
         T *res = (T *)(k.Ccl(k.rank) + (uint64_t)n * slice + p.off);
-        ReduceSlots<T, OP, kMaxRanks>((T *)((char *)A.out + (uint64_t)k.rank * slice + p.off), res, slots, n, p.len / sizeof(T));
+        ReduceSlots<T, OP, kMaxRanks>((T *)(out + (uint64_t)k.rank * slice + p.off), res, slots, n, p.len / sizeof(T));
     }
     if (!ChannelBarrier(k, 2)) return;
     for (int d = 1; d < n; ++d) {
         int r = (k.rank + d) % n;
-        Part p = PartOf(SliceLen(A.bytes, slice, r), gridDim.x, blockIdx.x);
-        BlockCopy((char *)A.out + (uint64_t)r * slice + p.off, k.Ccl(r) + (uint64_t)n * slice + p.off, p.len);
+        Part p = PartOf(SliceLen(bytes, slice, r), k.vGrid, k.vBlock);
+        BlockCopy(out + (uint64_t)r * slice + p.off, k.Ccl(r) + (uint64_t)n * slice + p.off, p.len);
     }
+}
+template <typename T, int OP, bool EMU> __device__ void AllReduceTwoShotBody(KCtx &k, const CollArgs &A)
+{
+    AllReduceTwoShotCore<T, OP>(k, (const char *)A.in, (char *)A.out, A.bytes);
 }
 
 // ================================================================================================ AllReduce ring
@@ -208,18 +212,18 @@ template <typename T, int OP, bool EMU> __device__ void AllReduceNvlsOneShotBody
     MultimemReduceLoop<T, OP>(mc, nvec, [&](uint64_t i, uint4 v) { StoreVec<T>(out, i, v, aligned); });
 }
 
-template <typename T, int OP, bool EMU> __device__ void AllReduceNvlsTwoShotBody(KCtx &k, const CollArgs &A)
+template <typename T, int OP> __device__ void AllReduceNvlsTwoShotCore(KCtx &k, const char *in, char *out, uint64_t bytes)
 {
     const int n = k.nranks;
-    const uint64_t slice = Up128((A.bytes + n - 1) / n);
+    const uint64_t slice = Up128((bytes + n - 1) / n);
     const uint64_t outRegion = (uint64_t)n * slice;
     for (int j = 0; j < n; ++j) {
-        Part p = PartOf(SliceLen(A.bytes, slice, j), gridDim.x, blockIdx.x);
-        BlockCopy(k.Ccl(k.rank) + (uint64_t)j * slice + p.off, (const char *)A.in + (uint64_t)j * slice + p.off, p.len);
+        Part p = PartOf(SliceLen(bytes, slice, j), k.vGrid, k.vBlock);
+        BlockCopy(k.Ccl(k.rank) + (uint64_t)j * slice + p.off, in + (uint64_t)j * slice + p.off, p.len);
     }
     if (!ChannelBarrier(k, 1)) return;
     {
-        Part p = PartOf(SliceLen(A.bytes, slice, k.rank), gridDim.x, blockIdx.x);
+        Part p = PartOf(SliceLen(bytes, slice, k.rank), k.vGrid, k.vBlock);
         char *src = k.Mc() + (uint64_t)k.rank * slice + p.off;
         char *dst = k.Mc() + outRegion + (uint64_t)k.rank * slice + p.off;
         uint64_t nvec = p.len >> 4;
@@ -227,10 +231,38 @@ template <typename T, int OP, bool EMU> __device__ void AllReduceNvlsTwoShotBody
     }
     if (!ChannelBarrier(k, 2)) return;
     for (int j = 0; j < n; ++j) {
-        Part p = PartOf(SliceLen(A.bytes, slice, j), gridDim.x, blockIdx.x);
-        BlockCopy((char *)A.out + (uint64_t)j * slice + p.off, k.Ccl(k.rank) + outRegion + (uint64_t)j * slice + p.off, p.len);
+        Part p = PartOf(SliceLen(bytes, slice, j), k.vGrid, k.vBlock);
+        BlockCopy(out + (uint64_t)j * slice + p.off, k.Ccl(k.rank) + outRegion + (uint64_t)j * slice + p.off, p.len);
     }
 }
+template <typename T, int OP, bool EMU> __device__ void AllReduceNvlsTwoShotBody(KCtx &k, const CollArgs &A)
+{
+    AllReduceNvlsTwoShotCore<T, OP>(k, (const char *)A.in, (char *)A.out, A.bytes);
+}
+
+// ================================================================================================ AllReduce, two algorithms side by side
+// One launch, two sub-grids: CTAs [0, splitCtas) run the switch-reduced two-shot on the first splitBytes of the payload,
+// the rest run the peer-store two-shot on the remainder, each in its own scratch region (the reference's concurrent
+// executors split one payload between two planes by HCCL_ALG_MULTIPLE_DIMENSION_SPLIT_RATIO; reference:
+// src/ops/all_reduce/executor/ins_v2_all_reduce_concurrent_executor.cc:159,479-487). Without a multicast mapping both parts
+// run the peer-store algorithm. Channels are CTA indices, so the two parts never share a flag word.
+template <typename T, int OP, bool EMU, bool NVLS> __device__ void AllReduceConcurrentBody(KCtx &k, const CollArgs &A)
+{
+    const uint64_t bytesA = A.splitBytes;
+    const uint32_t ctasA = A.splitCtas;
+    const int n = k.nranks;
+    if (blockIdx.x < ctasA) {
+        k.vGrid = ctasA; k.vBlock = blockIdx.x; k.cclShift = 0;
+        if constexpr (NVLS) AllReduceNvlsTwoShotCore<T, OP>(k, (const char *)A.in, (char *)A.out, bytesA);
+        else AllReduceTwoShotCore<T, OP>(k, (const char *)A.in, (char *)A.out, bytesA);
+    } else {
+        k.vGrid = gridDim.x - ctasA; k.vBlock = blockIdx.x - ctasA;
+        k.cclShift = 2ull * (uint64_t)n * Up128((bytesA + n - 1) / n);          // past the larger of the two layouts of part A
+        AllReduceTwoShotCore<T, OP>(k, (const char *)A.in + bytesA, (char *)A.out + bytesA, A.bytes - bytesA);
+    }
+}
+template <typename T, int OP, bool EMU> __device__ void AllReduceConcurrentNvlsBody(KCtx &k, const CollArgs &A) { AllReduceConcurrentBody<T, OP, EMU, true>(k, A); }
+template <typename T, int OP, bool EMU> __device__ void AllReduceConcurrentPlainBody(KCtx &k, const CollArgs &A) { AllReduceConcurrentBody<T, OP, EMU, false>(k, A); }
 
 // ================================================================================================ AllGather(V), pull
 template <bool EMU> __device__ void AllGatherVBody(KCtx &k, const CollArgs &A)
@@ -408,6 +440,7 @@ template <bool EMU> __device__ void AllGatherPipePlainBody(KCtx &k, const CollAr
 template <bool EMU> __device__ void AllGatherPipeNvlsBody(KCtx &k, const CollArgs &A) { pipe::AllGatherBody<EMU, true>(k, A); }
 template <bool EMU> __device__ void AlltoAllPipeBody(KCtx &k, const CollArgs &A) { pipe::AllGatherBody<EMU, false, true>(k, A); }
 COLL_KERNEL_TYPED(KAllReduceRing, AllReduceRingBody)
+COLL_KERNEL_TYPED(KAllReduceConcurrentPlain, AllReduceConcurrentPlainBody)
 COLL_KERNEL_TYPED(KAllReducePipe, AllReducePipePlainBody)
 COLL_KERNEL_TYPED(KReduceScatterPipe, ReduceScatterPipePlainBody)
 
@@ -423,6 +456,7 @@ COLL_KERNEL_NVLS(KAllReduceNvlsOneShot, AllReduceNvlsOneShotBody)
 COLL_KERNEL_NVLS(KAllReduceNvlsTwoShot, AllReduceNvlsTwoShotBody)
 COLL_KERNEL_NVLS(KReduceScatterNvls, ReduceScatterNvlsBody)
 COLL_KERNEL_NVLS(KAllReducePipeNvls, AllReducePipeNvlsBody)
+COLL_KERNEL_NVLS(KAllReduceConcurrentNvls, AllReduceConcurrentNvlsBody)
 COLL_KERNEL_NVLS(KReduceScatterPipeNvls, ReduceScatterPipeNvlsBody)
 
 #define COLL_KERNEL_BYTES(NAME, BODY)                                                                                  \
@@ -608,6 +642,7 @@ template <bool EMU> CollKernelFn TypedKernel(SmKernelId id, HcclDataType dt)
         case K_REDUCESCATTER_V: PICK(KReduceScatterV)
         case K_REDUCE: PICK(KReduce)
         case K_ALLREDUCE_RING: PICK(KAllReduceRing)
+        case K_ALLREDUCE_CONCURRENT: PICK(KAllReduceConcurrentPlain)
         case K_ALLREDUCE_PIPE: PICK(KAllReducePipe)
         case K_REDUCESCATTER_PIPE: PICK(KReduceScatterPipe)
         default: return nullptr;
@@ -631,6 +666,7 @@ template <bool EMU> CollKernelFn NvlsKernel(SmKernelId id, HcclDataType dt, Hccl
         case K_ALLREDUCE_NVLS_TWOSHOT: PICKN(KAllReduceNvlsTwoShot)
         case K_REDUCESCATTER_NVLS: PICKN(KReduceScatterNvls)
         case K_ALLREDUCE_PIPE_NVLS: PICKN(KAllReducePipeNvls)
+        case K_ALLREDUCE_CONCURRENT_NVLS: PICKN(KAllReduceConcurrentNvls)
         case K_REDUCESCATTER_PIPE_NVLS: PICKN(KReduceScatterPipeNvls)
         default: return nullptr;
     }
@@ -640,9 +676,9 @@ template <bool EMU> CollKernelFn NvlsKernel(SmKernelId id, HcclDataType dt, Hccl
 template <bool EMU> CollKernelFn KernelFor(const SmLaunch &l)
 {
     switch (l.kernel) {
-        case K_ALLREDUCE_ONESHOT: case K_ALLREDUCE_TWOSHOT: case K_REDUCESCATTER_V: case K_REDUCE: case K_ALLREDUCE_PIPE: case K_REDUCESCATTER_PIPE: case K_ALLREDUCE_RING:
+        case K_ALLREDUCE_ONESHOT: case K_ALLREDUCE_TWOSHOT: case K_REDUCESCATTER_V: case K_REDUCE: case K_ALLREDUCE_PIPE: case K_REDUCESCATTER_PIPE: case K_ALLREDUCE_RING: case K_ALLREDUCE_CONCURRENT:
             return TypedKernel<EMU>(l.kernel, l.dtype);
-        case K_ALLREDUCE_NVLS_ONESHOT: case K_ALLREDUCE_NVLS_TWOSHOT: case K_REDUCESCATTER_NVLS: case K_ALLREDUCE_PIPE_NVLS: case K_REDUCESCATTER_PIPE_NVLS:
+        case K_ALLREDUCE_NVLS_ONESHOT: case K_ALLREDUCE_NVLS_TWOSHOT: case K_REDUCESCATTER_NVLS: case K_ALLREDUCE_PIPE_NVLS: case K_REDUCESCATTER_PIPE_NVLS: case K_ALLREDUCE_CONCURRENT_NVLS:
             return NvlsKernel<EMU>(l.kernel, l.dtype, (HcclReduceOp)l.args.op);
         case K_ALLGATHER_PIPE: return KAllGatherPipe<EMU>;
         case K_ALLGATHER_PIPE_NVLS: return KAllGatherPipeNvls<EMU>;

@@ -1,5 +1,7 @@
 // Host side of the SM / NVLS engine: plan an operator into launches, issue them on the caller's stream, and the
 // single-GPU emulation harness used by the tests (all ranks on one device, one cooperative launch per chunk).
+#include "../common/env_config.h"
+#include <algorithm>
 #include "../common/launch_count.h"
 #include "launch.h"
 #include <cuda_runtime.h>
@@ -28,7 +30,7 @@ const std::vector<SmAlgoDesc> &SmAlgorithms()
         {"SmReduceMesh1D", HCCL_CMD_REDUCE, false}, {"SmScatterMesh1D", HCCL_CMD_SCATTER, false},
         {"SmAlltoAllMesh1D", HCCL_CMD_ALLTOALL, false}, {"SmAlltoAllVMesh1D", HCCL_CMD_ALLTOALLV, false},
         {"SmAlltoAllVCMesh1D", HCCL_CMD_ALLTOALLVC, false}, {"SmBarrierMesh1D", HCCL_CMD_BARRIER, false},
-        {"SmAllReduceRing", HCCL_CMD_ALLREDUCE, false}, {"SmAllReducePipelined", HCCL_CMD_ALLREDUCE, false}, {"NvlsAllReducePipelined", HCCL_CMD_ALLREDUCE, true},
+        {"SmAllReduceRing", HCCL_CMD_ALLREDUCE, false}, {"SmAllReduceConcurrent", HCCL_CMD_ALLREDUCE, false}, {"NvlsAllReduceConcurrent", HCCL_CMD_ALLREDUCE, true}, {"SmAllReducePipelined", HCCL_CMD_ALLREDUCE, false}, {"NvlsAllReducePipelined", HCCL_CMD_ALLREDUCE, true},
         {"SmReduceScatterPipelined", HCCL_CMD_REDUCE_SCATTER, false}, {"SmReduceScatterVPipelined", HCCL_CMD_REDUCE_SCATTER_V, false},
         {"NvlsReduceScatterPipelined", HCCL_CMD_REDUCE_SCATTER, true},
         {"SmAllGatherPush", HCCL_CMD_ALLGATHER, false}, {"SmAllGatherVPush", HCCL_CMD_ALLGATHER_V, false},
@@ -51,6 +53,7 @@ HcclResult SmOrchestrate(Comm *c, OpParam &p, const std::string &algName)
     ctx.mailboxBytes = c->devComm.mailboxBytes;
     ctx.maxCtas = c->env.maxCtas;
     ctx.nvls = c->mcHeap != nullptr;
+    if (c->env.multiDimSplitSet) { ctx.splitRatio[0] = c->env.multiDimSplitRatio[0]; ctx.splitRatio[1] = c->env.multiDimSplitRatio[1]; }
     std::vector<SmLaunch> launches;
     HcclResult r = SmPlanOp(ctx, p, algName, &launches);
     if (r != HCCL_SUCCESS) return r;
@@ -114,6 +117,7 @@ HcclResult HcclEmuCreate(uint32_t nranks, uint64_t cclBytes, uint64_t arenaBytes
         d.timeoutNs = (uint64_t)waitTimeoutMs * 1000000ull;
         d.status = devStatus + r;
         d.emuRanks = (int)nranks;
+        d.traceOn = 1;
     }
     EMU_RT(cudaMalloc((void **)&w->devComms, sizeof(DevComm) * nranks));
     EMU_RT(cudaMemcpy(w->devComms, w->hostComms.data(), sizeof(DevComm) * nranks, cudaMemcpyHostToDevice));
@@ -172,6 +176,8 @@ HcclResult HcclEmuRun(void *emu, HcclCMDType op, const char *algName, void **ins
             p.count = cnt[r];
         }
         SmPlanCtx ctx{r, n, w->cclBytes, w->mailboxBytes, maxCtas ? maxCtas : 4u, false};
+        (void)InitEnvConfig();
+        if (GetEnvConfig().multiDimSplitSet) { ctx.splitRatio[0] = GetEnvConfig().multiDimSplitRatio[0]; ctx.splitRatio[1] = GetEnvConfig().multiDimSplitRatio[1]; }
         HcclResult pr = SmPlanOp(ctx, p, algName, &per[r]);
         if (pr != HCCL_SUCCESS) return pr;
     }
@@ -240,6 +246,25 @@ HcclResult HcclEmuStatus(void *emu, uint32_t rank, uint32_t *out, int clear)
         memset(&w->status[rank], 0, sizeof(DevStatus));
         for (char *h : w->heaps) cudaMemset(h, 0, kHeapHeaderBytes);
         cudaDeviceSynchronize();
+    }
+    return HCCL_SUCCESS;
+}
+
+// Device-side trace of an emulated rank: up to maxRecords rows {seq, syncs, enterNs, firstSyncNs, lastSyncNs, leaveNs}, oldest first.
+HcclResult HcclEmuTrace(void *emu, uint32_t rank, uint64_t *rows, uint32_t maxRecords, uint32_t *numRecords)
+{
+    auto *w = (EmuWorld *)emu;
+    if (!w || !rows || !numRecords || rank >= (uint32_t)w->nranks) return HCCL_E_PARA;
+    std::vector<uint8_t> ctrl(sizeof(DevCtrl));
+    EMU_RT(cudaMemcpy(ctrl.data(), w->heaps[rank], ctrl.size(), cudaMemcpyDeviceToHost));
+    const DevCtrl *dc = reinterpret_cast<const DevCtrl *>(ctrl.data());
+    std::vector<DevTraceRec> recs;
+    for (int i = 0; i < kTraceSlots; ++i) if (dc->trace[i].tEnter != 0) recs.push_back(dc->trace[i]);
+    std::sort(recs.begin(), recs.end(), [](const DevTraceRec &a, const DevTraceRec &b) { return a.seq < b.seq; });
+    *numRecords = 0;
+    for (size_t i = recs.size() > maxRecords ? recs.size() - maxRecords : 0; i < recs.size(); ++i) {
+        uint64_t *r = rows + 6 * (*numRecords)++;
+        r[0] = recs[i].seq; r[1] = recs[i].barriers; r[2] = recs[i].tEnter; r[3] = recs[i].tBarrier[0]; r[4] = recs[i].tBarrier[1]; r[5] = recs[i].tLeave;
     }
     return HCCL_SUCCESS;
 }

@@ -70,9 +70,13 @@ struct KCtx {
     uint32_t syncs;      // sync points consumed so far
     bool ok;             // false after a timeout
     uint32_t seq;        // op counter value this kernel entered with (trace slot)
+    // Work split of the kernel bodies: CTA vBlock of vGrid, scratch offsets shifted by cclShift. The whole grid by default;
+    // a kernel that runs two algorithms side by side gives each its own sub-grid and scratch region.
+    uint32_t vGrid, vBlock;
+    uint64_t cclShift;
     __device__ __forceinline__ char *PeerHeap(int r) const { return c->heap[r]; }
-    __device__ __forceinline__ char *Ccl(int r) const { return c->heap[r] + c->cclOff[half]; }
-    __device__ __forceinline__ char *Mc() const { return c->mcHeap + c->cclOff[half]; }
+    __device__ __forceinline__ char *Ccl(int r) const { return c->heap[r] + c->cclOff[half] + cclShift; }
+    __device__ __forceinline__ char *Mc() const { return c->mcHeap + c->cclOff[half] + cclShift; }
 };
 
 __device__ __forceinline__ void ReportTimeout(const KCtx &k, uint32_t peer, uint32_t phase, uint32_t observed, uint32_t expected)
@@ -187,6 +191,7 @@ template <bool EMU> __device__ __forceinline__ KCtx EnterCollective(const DevCom
     k.syncs = 0;
     k.ok = true;
     k.seq = sSeq;
+    k.vGrid = gridDim.x; k.vBlock = blockIdx.x; k.cclShift = 0;
     return k;
 }
 

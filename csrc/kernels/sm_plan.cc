@@ -76,6 +76,33 @@ HcclResult SmPlanOp(const SmPlanCtx &ctx, const OpParam &p, const std::string &a
             push(nv ? K_ALLREDUCE_NVLS_TWOSHOT : K_ALLREDUCE_TWOSHOT, lo, cnt, cnt * es / n * 2, [&](SmLaunch &l) { l.args.in = in + lo * es; l.args.out = outp + lo * es; });
         });
     }
+    if (alg == "SmAllReduceConcurrent" || alg == "NvlsAllReduceConcurrent") {
+        // One payload, two algorithms side by side in one launch. Shares come from HCCL_ALG_MULTIPLE_DIMENSION_SPLIT_RATIO
+        // ("a:b"); unset, the switch-reduced part gets two thirds (it moves a third of the bytes of the peer-store part
+        // into each GPU), and an even split when both parts use peer stores.
+        bool nv = alg[0] == 'N';
+        if (nv && (!ctx.nvls || (p.count * es) % 16 != 0)) return HCCL_E_NOT_SUPPORT;
+        uint32_t ra = ctx.splitRatio[0], rb = ctx.splitRatio[1];
+        if (ra + rb == 0) { ra = nv ? 2 : 1; rb = 1; }
+        if (ccl < 4ull * n * 128 + 4096) return HCCL_E_MEMORY;
+        // scratch: part A up to 2 n slices, part B n + 1 slices; 2 * (bytes + n * 128) covers both
+        uint64_t maxBytes = Down128(ccl / 2) - (uint64_t)n * 256;
+        uint64_t unit = (uint64_t)n * 128;                         // part A stays a whole number of aligned slices
+        uint64_t maxCount = maxBytes / unit * unit / es;
+        if (maxCount == 0) return HCCL_E_MEMORY;
+        return loop(p.count, maxCount, [&](uint64_t lo, uint64_t cnt) {
+            uint64_t bytes = cnt * es;
+            uint64_t a = bytes * ra / (ra + rb) / unit * unit;
+            if (rb == 0) a = bytes;
+            push(nv ? K_ALLREDUCE_CONCURRENT_NVLS : K_ALLREDUCE_CONCURRENT, lo, cnt, cnt * es / n * 2, [&](SmLaunch &l) {
+                l.args.in = in + lo * es; l.args.out = outp + lo * es;
+                l.ctas = std::max(2u, l.ctas);
+                l.args.splitBytes = a;
+                uint32_t ca = (uint32_t)((uint64_t)l.ctas * ra / (ra + rb));
+                l.args.splitCtas = std::min(l.ctas - 1, std::max(1u, ca));
+            });
+        });
+    }
     if (alg == "SmAllReduceRing") {
         if (n < 2) return HCCL_E_NOT_SUPPORT;
         uint64_t maxSlice = Down128(ccl / (2 * (n - 1)));

@@ -52,7 +52,7 @@ __device__ __forceinline__ void FusedInit(const GemmParams &p, FusedCtx &x)
     __syncthreads();
     x.half = sHalf;
     x.k.c = x.c; x.k.rank = x.rank; x.k.nranks = x.n; x.k.heap = x.heap; x.k.ctrl = x.ctrl; x.k.flags = x.flags;
-    x.k.half = x.half; x.k.chan = blockIdx.x; x.k.epoch = 0; x.k.syncs = 0; x.k.ok = true; x.k.seq = sSeq;
+    x.k.half = x.half; x.k.chan = blockIdx.x; x.k.epoch = 0; x.k.syncs = 0; x.k.ok = true; x.k.seq = sSeq; x.k.vGrid = gridDim.x; x.k.vBlock = blockIdx.x; x.k.cclShift = 0;
 }
 
 // Last CTA out clears the counters of this parity.

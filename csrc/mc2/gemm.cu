@@ -173,15 +173,15 @@ static HcclResult LaunchPlain2Cta(const void *a, const void *b, void *c, uint32_
     return LaunchPlain2CtaT<256>(a, b, c, M, N, K, outFp32, s);
 }
 
-// HCCL_GEMM_2CTA: 0 never, 1 always, unset = by size. The CTA-pair kernel keeps the tensor pipe busier (99.5 % against
-// 88 % of the active cycles) and wins on kernels that finish before the 1 kW power cap bites (1635 against 1480 TFLOP/s on
-// 8192 x 8192 x 4096); on multi-millisecond GEMMs run back to back its extra DRAM traffic costs clock under the cap and the
-// one-CTA kernel measured faster (1313 against 1250 TFLOP/s on the 8192 x 28672 x 8192 pair of the single-GPU step).
-bool Gemm2CtaEnabled(uint64_t m, uint64_t n, uint64_t k)
+// HCCL_GEMM_2CTA: 0 never, otherwise (and unset) always. The CTA-pair kernel keeps the tensor pipe at 97 % of the active
+// cycles against 85-88 % for the one-CTA kernel and halves the B traffic per SM. Isolated it wins clearly (1635 against 1480
+// TFLOP/s on 8192 x 8192 x 4096); back to back under the board's power limit it runs at a lower clock (1140 against 1240 MHz)
+// but still finishes sooner: 5.91-5.92 ms against 6.11-6.13 ms for the 8192 x 28672 x 8192 pair of the single-GPU step, two
+// interleaved runs each on one box (benchmarks/gemm_sustained.py), 5.53 ms for the library GEMM on the same box.
+bool Gemm2CtaEnabled(uint64_t, uint64_t, uint64_t)
 {
     static const int v = [] { const char *e = getenv("HCCL_GEMM_2CTA"); return e ? atoi(e) : -1; }();
-    if (v >= 0) return v != 0;
-    return 2.0 * (double)m * (double)n * (double)k < 2.5e12;
+    return v != 0;
 }
 
 }  // namespace mc2

@@ -35,7 +35,7 @@ __device__ __forceinline__ KCtx MoeEnter(const DevComm *c, uint32_t chan)
     KCtx k;
     k.c = c; k.rank = c->rank; k.nranks = c->nranks; k.heap = c->heap[c->rank];
     k.ctrl = CtrlOf(k.heap); k.flags = FlagsOf(k.heap);
-    k.half = 0; k.chan = chan; k.syncs = 0; k.ok = true; k.seq = 0xffffffffu;   // not counted by the op counter: no trace record
+    k.half = 0; k.chan = chan; k.syncs = 0; k.ok = true; k.vGrid = gridDim.x; k.vBlock = blockIdx.x; k.cclShift = 0; k.seq = 0xffffffffu;   // not counted by the op counter: no trace record
     k.epoch = LdVolatile(&k.ctrl->chanEpoch[chan]);
     return k;
 }
@@ -206,6 +206,21 @@ __global__ void __launch_bounds__(kMoeThreads) MoeDispatchKernel(const DevComm *
             for (uint32_t le = 0; le < EL; ++le) rows += (uint32_t)recvCounts[le];
             Part p = PartOf((uint64_t)rows * A.H * 2, G, cta);
             BlockCopy(ws + A.L.yBuf + p.off, ws + A.L.recvX + p.off, p.len);
+        } else {
+            // block-scaled payload: the stand-in expert dequantises (e4m3 value x 2^(scale - 127)) into the bf16 output buffer
+            uint32_t rows = 0;
+            for (uint32_t le = 0; le < EL; ++le) rows += (uint32_t)recvCounts[le];
+            const uint32_t blocksPerRow = A.H / 32;
+            const uint64_t blocks = (uint64_t)rows * blocksPerRow;
+            for (uint64_t b = (uint64_t)cta * blockDim.x + threadIdx.x; b < blocks; b += (uint64_t)G * blockDim.x) {
+                const uint8_t *q = (const uint8_t *)(ws + A.L.recvX) + b * 32;
+                const float scale = exp2f((float)((int)((const uint8_t *)(ws + A.L.recvScales))[b] - 127));
+                __nv_bfloat16 *y = (__nv_bfloat16 *)(ws + A.L.yBuf) + b * 32;
+                for (int j = 0; j < 32; ++j) {
+                    __half_raw hr = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)q[j], __NV_E4M3);
+                    y[j] = __float2bfloat16(__half2float(__half(hr)) * scale);
+                }
+            }
         }
     }
 }

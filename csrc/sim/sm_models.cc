@@ -154,6 +154,50 @@ void AllReduceTwoShot(Model &m, bool nvls)
     }
 }
 
+// Two sub-grids: channels [0, splitCtas) run the first algorithm on the first splitBytes, the rest the peer-store two-shot on
+// the remainder, in a scratch region shifted past part A's.
+void AllReduceConcurrent(Model &m, bool nvls)
+{
+    const uint32_t n = m.n;
+    const CollArgs &A = m.A();
+    const uint64_t bytesA = A.splitBytes, bytesB = A.bytes - bytesA;
+    // the model keeps the launch's proportion of CTAs, with at least one channel per part
+    const uint32_t ca = std::max(1u, std::min(m.C - 1, (uint32_t)((uint64_t)m.C * A.splitCtas / std::max(1u, m.all[m.me].ctas))));
+    const uint64_t shift = 2ull * n * Up128((bytesA + n - 1) / n);
+    auto twoShot = [&](uint32_t ch, uint32_t vb, uint32_t vg, uint64_t base, uint64_t io, uint64_t bytes, bool viaSwitch) {
+        const uint64_t slice = Up128((bytes + n - 1) / n), outRegion = (uint64_t)n * slice;
+        if (viaSwitch) {
+            for (uint32_t j = 0; j < n; ++j) { Part p = PartOf(SliceLen(bytes, slice, j), vg, vb); m.Copy(ch, Model::Ccl(base + j * slice + p.off), m.In(io + j * slice + p.off), p.len); }
+            m.Barrier(ch);
+            Part p = PartOf(SliceLen(bytes, slice, m.me), vg, vb);
+            m.MultimemLdReduce(ch, Model::Ccl(base + outRegion + m.me * slice + p.off), base + m.me * slice + p.off, p.len);
+            for (uint32_t d = 1; d < n; ++d) m.Write(ch, (m.me + d) % n, base + outRegion + m.me * slice + p.off, Model::Ccl(base + outRegion + m.me * slice + p.off), p.len);
+            m.Barrier(ch);
+            for (uint32_t j = 0; j < n; ++j) { Part q = PartOf(SliceLen(bytes, slice, j), vg, vb); m.Copy(ch, m.Out(io + j * slice + q.off), Model::Ccl(base + outRegion + j * slice + q.off), q.len); }
+        } else {
+            for (uint32_t d = 0; d < n; ++d) {
+                uint32_t r = (m.me + d) % n;
+                Part p = PartOf(SliceLen(bytes, slice, r), vg, vb);
+                m.Write(ch, r, base + (uint64_t)m.me * slice + p.off, m.In(io + (uint64_t)r * slice + p.off), p.len);
+            }
+            m.Barrier(ch);
+            Part p = PartOf(SliceLen(bytes, slice, m.me), vg, vb);
+            m.ReduceSlots(ch, Model::Ccl(base + outRegion + p.off), base + p.off, slice, p.len);
+            m.Copy(ch, m.Out(io + (uint64_t)m.me * slice + p.off), Model::Ccl(base + outRegion + p.off), p.len);
+            m.Barrier(ch);
+            for (uint32_t d = 1; d < n; ++d) {
+                uint32_t r = (m.me + d) % n;
+                Part q = PartOf(SliceLen(bytes, slice, r), vg, vb);
+                m.Read(ch, m.Out(io + (uint64_t)r * slice + q.off), r, base + outRegion + q.off, q.len);
+            }
+        }
+    };
+    for (uint32_t ch = 0; ch < m.C; ++ch) {
+        if (ch < ca) twoShot(ch, ch, ca, 0, 0, bytesA, nvls);
+        else twoShot(ch, ch - ca, m.C - ca, shift, bytesA, bytesB, false);
+    }
+}
+
 void AllReduceRing(Model &m)
 {
     const uint32_t n = m.n, next = (m.me + 1) % n, prev = (m.me + n - 1) % n;
@@ -314,6 +358,8 @@ HcclResult GenSmModelPlan(const std::vector<SmLaunch> &all, uint32_t me, uintptr
         case K_ALLREDUCE_TWOSHOT: AllReduceTwoShot(m, false); break;
         case K_ALLREDUCE_NVLS_TWOSHOT: AllReduceTwoShot(m, true); break;
         case K_ALLREDUCE_RING: AllReduceRing(m); break;
+        case K_ALLREDUCE_CONCURRENT: AllReduceConcurrent(m, false); break;
+        case K_ALLREDUCE_CONCURRENT_NVLS: AllReduceConcurrent(m, true); break;
         case K_ALLGATHER_V: AllGatherV(m); break;
         case K_REDUCESCATTER_V: ReduceScatterV(m, false); break;
         case K_REDUCESCATTER_NVLS: ReduceScatterV(m, true); break;

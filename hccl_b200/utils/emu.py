@@ -95,6 +95,15 @@ class EmuWorld:
         torch.cuda.synchronize()
         return rc
 
+    def trace(self, rank: int, max_records: int = 64):
+        """Device-side records of the rank's most recent kernels: dicts with seq, syncs and %globaltimer stamps in ns."""
+        rows = (ctypes.c_uint64 * (6 * max_records))()
+        n = ctypes.c_uint32()
+        self._l.HcclEmuTrace.argtypes = [ctypes.c_void_p, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_uint32, ctypes.POINTER(ctypes.c_uint32)]
+        check(self._l.HcclEmuTrace(self._h, rank, rows, max_records, ctypes.byref(n)), "HcclEmuTrace")
+        keys = ("seq", "syncs", "enter", "first_sync", "last_sync", "leave")
+        return [dict(zip(keys, rows[6 * i:6 * i + 6])) for i in range(n.value)]
+
     def status(self, rank: int, clear: bool = False):
         out = (ctypes.c_uint32 * 8)()
         check(self._l.HcclEmuStatus(self._h, rank, out, int(clear)), "HcclEmuStatus")

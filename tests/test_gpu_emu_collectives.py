@@ -326,3 +326,52 @@ def test_ring_allreduce(emu_mod, nranks, count):
                 else:
                     assert torch.equal(b.to(torch.int64), ref)
                 assert torch.equal(b, bufs[0])
+
+
+def test_device_trace_records_every_kernel(emu_mod):
+    """CTA 0 of every collective kernel stamps a record from the GPU's %globaltimer: entry, its first and last all-rank
+    synchronisation, exit. Records follow the device op counter, and a kernel that gave up waiting has no exit stamp."""
+    with emu_mod.EmuWorld(4, 1 << 20, wait_timeout_ms=200) as w:
+        xs = [_rand(30_000, torch.float32, r) for r in range(4)]      # 120 KB per rank: one launch per operator with 1 MB of scratch
+        outs = [torch.empty_like(x) for x in xs]
+        for alg, syncs in (("SmAllReduceMesh1DOneShot", 1), ("SmAllReduceMesh1DTwoShot", 2), ("SmAllReduceMesh1DTwoShot", 2)):
+            assert w.run(CMD["ALLREDUCE"], alg, xs, outs, 30_000, torch.float32, max_ctas=4) == 0
+        for rank in range(4):
+            recs = w.trace(rank)
+            assert [r["seq"] for r in recs] == [0, 1, 2]
+            assert [r["syncs"] for r in recs] == [1, 2, 2]
+            for r in recs:
+                assert 0 < r["enter"] <= r["first_sync"] <= r["last_sync"] <= r["leave"]
+                assert r["leave"] - r["enter"] < 50_000_000          # a 120 KB all-reduce takes microseconds, not 50 ms
+            assert recs[0]["leave"] <= recs[1]["enter"] + 1_000_000 and recs[1]["enter"] < recs[2]["enter"]
+        assert w.lonely_barrier(1) == 9
+        last = w.trace(1)[-1]
+        assert last["seq"] == 3 and last["leave"] == 0 and last["syncs"] == 0
+        w.status(1, clear=True)
+
+
+@pytest.mark.parametrize("ratio", [None, "1:1", "3:1", "1:5", "1:0"])
+@pytest.mark.parametrize("nranks,count", [(2, 64), (4, 100_003), (8, 1_000_000), (3, 4097)])
+def test_concurrent_allreduce_splits_one_payload_between_two_sub_grids(emu_mod, monkeypatch, ratio, nranks, count):
+    """Two all-reduce algorithms share one launch: the first CTAs take the first part of the payload, the rest the remainder,
+    each in its own scratch region, in the proportion HCCL_ALG_MULTIPLE_DIMENSION_SPLIT_RATIO gives. Without a multicast
+    mapping (emulated ranks) both parts run the peer-store two-shot, whose result is bit-identical to the plain two-shot."""
+    from hccl_b200._lib import lib
+    if ratio is None:
+        monkeypatch.delenv("HCCL_ALG_MULTIPLE_DIMENSION_SPLIT_RATIO", raising=False)
+    else:
+        monkeypatch.setenv("HCCL_ALG_MULTIPLE_DIMENSION_SPLIT_RATIO", ratio)
+    lib().HcclResetEnvConfigForTest()
+    try:
+        with emu_mod.EmuWorld(nranks, 1 << 20) as w:        # 1 MB scratch: the 4 MB payload also walks the chunk loop
+            for dtype in (torch.float32, torch.bfloat16):
+                xs = [_rand(count, dtype, 40 + r) for r in range(nranks)]
+                outs = [torch.empty_like(x) for x in xs]
+                ref = [torch.empty_like(x) for x in xs]
+                assert w.run(CMD["ALLREDUCE"], "SmAllReduceConcurrent", xs, outs, count, dtype, ReduceOp.SUM, max_ctas=6) == 0
+                assert w.run(CMD["ALLREDUCE"], "SmAllReduceMesh1DTwoShot", xs, ref, count, dtype, ReduceOp.SUM, max_ctas=6) == 0
+                for o, r in zip(outs, ref):
+                    assert torch.equal(o, r)
+    finally:
+        monkeypatch.delenv("HCCL_ALG_MULTIPLE_DIMENSION_SPLIT_RATIO", raising=False)
+        lib().HcclResetEnvConfigForTest()

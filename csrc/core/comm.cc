@@ -460,6 +460,51 @@ HcclResult EngineCtxDestroy(Comm *c, const std::string &tag)
     return HCCL_SUCCESS;
 }
 
+// ------------------------------------------------------------------------------------------------ registered windows
+// A window is a range of this rank's heap that the caller promises to use at the same heap offset on every rank (memory from
+// HcclCommSymAlloc has that property when all ranks allocate in the same order). Windows may not overlap.
+HcclResult CommRegisterWindow(Comm *c, const void *ptr, uint64_t bytes, uint64_t *off)
+{
+    const char *heap = c->heap[c->rank], *p = (const char *)ptr;
+    if (bytes == 0) return HCCL_E_PARA;
+    if (p < heap || p + bytes > heap + c->heapBytes) return HCCL_E_NOT_SUPPORT;
+    const uint64_t o = (uint64_t)(p - heap);
+    std::lock_guard<std::mutex> lk(c->arenaMu);
+    // a range inside a window that is already registered needs no entry of its own (registering twice is fine)
+    auto up = c->registered.upper_bound(o);
+    if (up != c->registered.begin()) {
+        auto prev = std::prev(up);
+        if (o + bytes <= prev->first + prev->second) { if (off) *off = o; return HCCL_SUCCESS; }
+        if (prev->first + prev->second > o) return HCCL_E_PARA;
+    }
+    if (up != c->registered.end() && up->first < o + bytes) return HCCL_E_PARA;
+    c->registered[o] = bytes;
+    if (off) *off = o;
+    return HCCL_SUCCESS;
+}
+
+HcclResult CommDeregisterWindow(Comm *c, const void *ptr)
+{
+    const char *heap = c->heap[c->rank], *p = (const char *)ptr;
+    if (p < heap || p >= heap + c->heapBytes) return HCCL_E_NOT_FOUND;
+    std::lock_guard<std::mutex> lk(c->arenaMu);
+    return c->registered.erase((uint64_t)(p - heap)) ? HCCL_SUCCESS : HCCL_E_NOT_FOUND;
+}
+
+bool CommRegisteredOffset(Comm *c, const void *ptr, uint64_t bytes, uint64_t *off)
+{
+    const char *heap = c->heap[c->rank], *p = (const char *)ptr;
+    if (!p || p < heap || p + bytes > heap + c->heapBytes) return false;
+    const uint64_t o = (uint64_t)(p - heap);
+    std::lock_guard<std::mutex> lk(c->arenaMu);
+    auto it = c->registered.upper_bound(o);
+    if (it == c->registered.begin()) return false;
+    --it;
+    if (o + bytes > it->first + it->second) return false;
+    if (off) *off = o;
+    return true;
+}
+
 // ------------------------------------------------------------------------------------------------ arena
 // First-fit with coalescing. Every rank must issue the same sequence of SymAlloc/SymFree calls so that offsets
 // agree (they are collective in that sense, but need no communication).
@@ -493,6 +538,8 @@ HcclResult SymFree(Comm *c, void *ptr)
     for (size_t i = 0; i < c->arena.size(); ++i) {
         if (c->arena[i].off != off || !c->arena[i].used) continue;
         c->arena[i].used = false;
+        // windows registered inside the block go with it
+        for (auto it = c->registered.lower_bound(off); it != c->registered.end() && it->first < off + c->arena[i].bytes;) it = c->registered.erase(it);
         if (i + 1 < c->arena.size() && !c->arena[i + 1].used) { c->arena[i].bytes += c->arena[i + 1].bytes; c->arena.erase(c->arena.begin() + i + 1); }
         if (i > 0 && !c->arena[i - 1].used) { c->arena[i - 1].bytes += c->arena[i].bytes; c->arena.erase(c->arena.begin() + i); }
         return HCCL_SUCCESS;

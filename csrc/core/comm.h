@@ -97,6 +97,7 @@ struct Comm {
     void *backendState = nullptr;    // CudaHeapState* / SimHeapState*
     std::vector<SymAllocBlock> arena;
     std::mutex arenaMu;
+    std::map<uint64_t, uint64_t> registered;   // heap offset -> bytes of the windows registered with HcclCommMemReg (under arenaMu)
 
     // host-engine notify bookkeeping and op parity (sim backend keeps them on the host side of the heap)
     uint64_t opSeq = 0;
@@ -156,6 +157,10 @@ HcclResult SymAlloc(Comm *c, uint64_t bytes, void **ptr);
 HcclResult SymFree(Comm *c, void *ptr);
 bool SymContains(Comm *c, const void *ptr, uint64_t bytes);
 uint64_t SymOffsetOf(Comm *c, const void *ptr);
+// Registered windows (HcclCommMemReg): ranges of the symmetric heap the zero-copy kernels may address on every rank.
+HcclResult CommRegisterWindow(Comm *c, const void *ptr, uint64_t bytes, uint64_t *off);
+HcclResult CommDeregisterWindow(Comm *c, const void *ptr);
+bool CommRegisteredOffset(Comm *c, const void *ptr, uint64_t bytes, uint64_t *off);
 
 // ---- backend hooks (backend_sim.cc / backend_cuda.cc)
 HcclResult SimBackendInit(Comm *c);

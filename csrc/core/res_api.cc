@@ -99,22 +99,19 @@ HcclResult HcclCommMemReg(HcclComm comm, void *addr, uint64_t size, uint64_t *wi
     Comm *c = Live(comm);
     if (!c || !addr || !windowOffset) return HCCL_E_PTR;
     if (size == 0) return HCCL_E_PARA;
-    char *heap = c->heap[c->rank], *p = (char *)addr;
-    if (p < heap || p + size > heap + c->heapBytes) {
+    HcclResult r = CommRegisterWindow(c, addr, size, windowOffset);
+    if (r == HCCL_E_NOT_SUPPORT)
         HCCL_ERROR("HcclCommMemReg: %p (+%llu) is outside the symmetric heap; allocate with HcclCommSymAlloc or stage through the CCL buffer",
                    addr, (unsigned long long)size);
-        return HCCL_E_NOT_SUPPORT;
-    }
-    *windowOffset = (uint64_t)(p - heap);
-    return HCCL_SUCCESS;
+    else if (r == HCCL_E_PARA) HCCL_ERROR("HcclCommMemReg: %p (+%llu) overlaps a window that is already registered", addr, (unsigned long long)size);
+    return r;
 }
 
 HcclResult HcclCommMemDereg(HcclComm comm, void *addr)
 {
     Comm *c = Live(comm);
     if (!c || !addr) return HCCL_E_PTR;
-    char *heap = c->heap[c->rank];
-    return ((char *)addr >= heap && (char *)addr < heap + c->heapBytes) ? HCCL_SUCCESS : HCCL_E_NOT_FOUND;
+    return CommDeregisterWindow(c, addr);
 }
 
 HcclResult HcclRankGraphGetLayers(HcclComm comm, uint32_t *numLayers)

@@ -225,6 +225,11 @@ HcclResult HcclCheckAlgorithm(HcclCMDType op, const char *algName, uint32_t supe
             if (alg.rfind("Sm", 0) == 0 || alg.rfind("Nvls", 0) == 0) {
                 // the kernels of the SM / NVLS engines: launch lists from the real planner, one schedule model per launch
                 SmPlanCtx pc{r, n, cclBytes, 1ull << 20, 4, alg[0] == 'N'};
+                if (alg.find("ZeroCopy") != std::string::npos) {
+                    // the fake input / output addresses stand for registered windows at the same offset on every rank
+                    pc.registeredOffset = [](const void *ptr, uint64_t, uint64_t *off) { *off = (uint64_t)(uintptr_t)ptr; return true; };
+                    spec.registeredUserBuffers = true;
+                }
                 if (r == 0) smLaunches.assign(n, {});
                 CHK_RET(SmPlanOp(pc, p, alg, &smLaunches[r]));
                 if (smLaunches[r].size() != smLaunches[0].size()) { CopyOut("ranks disagree on the number of launches", msg, msgLen); return HCCL_E_INTERNAL; }

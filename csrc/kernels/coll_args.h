@@ -3,6 +3,7 @@
 // launches (pure host arithmetic, identical on every rank, unit-testable without a GPU).
 #pragma once
 #include <stdint.h>
+#include <functional>
 #include <string>
 #include <vector>
 #include "../core/dev_comm.h"
@@ -37,6 +38,12 @@ enum SmKernelId : uint32_t {
     K_ALLREDUCE_RING,         // reduce-scatter + all-gather around the ring (comparator for the mesh kernels)
     K_ALLREDUCE_CONCURRENT,   // two-shot on two sub-grids: both parts by peer stores (no multicast mapping)
     K_ALLREDUCE_CONCURRENT_NVLS,   // ... the first part switch-reduced, the second by peer stores
+    // zero-copy forms: the user buffers are registered windows of the symmetric heap (same offset on every rank), so peers and
+    // the switch read / write them directly and nothing is staged through the CCL scratch
+    K_ALLREDUCE_ZC, K_ALLREDUCE_ZC_NVLS,
+    K_REDUCESCATTER_ZC, K_REDUCESCATTER_ZC_NVLS,
+    K_ALLGATHER_ZC, K_ALLGATHER_ZC_NVLS,
+    K_BROADCAST_ZC, K_BROADCAST_ZC_NVLS,
     K_COUNT
 };
 
@@ -63,6 +70,8 @@ struct CollArgs {
     uint64_t splitBytes;
     uint32_t splitCtas;
     uint32_t pad1;
+    // zero-copy kernels: heap offsets of the registered input / output windows (identical on every rank)
+    uint64_t inOff, outOff;
 };
 
 struct BatchItem {
@@ -95,6 +104,8 @@ struct SmPlanCtx {
     uint32_t maxCtas;         // 0 = default heuristic
     bool nvls;
     uint32_t splitRatio[2] = {0, 0};   // concurrent algorithms: shares of the first / second part (0:0 = built-in default)
+    // zero-copy algorithms: heap offset of a registered window that holds [ptr, ptr + bytes), or false
+    std::function<bool(const void *ptr, uint64_t bytes, uint64_t *off)> registeredOffset;
 };
 
 // Builds the launch list of one operator for one rank. Returns HCCL_E_NOT_SUPPORT when the algorithm cannot take

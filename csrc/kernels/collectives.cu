@@ -411,6 +411,121 @@ template <bool EMU> __device__ void AlltoAllVBody(KCtx &k, const CollArgs &A)
     BlockCopy((char *)A.out + A.recvOff[k.rank] + p.off, (const char *)A.in + A.sendOff[k.rank] + p.off, p.len);
 }
 
+// ================================================================================================ zero-copy forms
+// The caller's buffers are registered windows of the symmetric heap at the same offset on every rank (HcclCommSymAlloc +
+// HcclCommMemReg), so a peer's buffer is PeerHeap(r) + offset and the switch sees all of them at mcHeap + offset: nothing
+// is copied into or out of the CCL scratch. Every kernel starts with a channel barrier (all ranks have entered, so their
+// earlier work on these buffers is complete) and ends with one (no rank returns while a peer still reads its input or
+// writes its output). HCCL's counterpart lets peers write registered user buffers directly in graph mode (reference:
+// src/ops/op_common/op_common.cc:1670-1711).
+template <typename T, int OP> __device__ __forceinline__ void ReduceRanksTo(KCtx &k, uint64_t srcOff, char *const *dsts, int ndst, uint64_t bytes)
+{
+    const char *slots[kMaxRanks];
+    for (int r = 0; r < k.nranks; ++r) slots[r] = k.PeerHeap(r) + srcOff;
+    using Ac = typename Acc<T>::type;
+    constexpr int VE = 16 / sizeof(T);
+    const uint64_t nvec = bytes >> 4;
+    for (uint64_t i = threadIdx.x; i < nvec; i += blockDim.x) {
+        Ac acc[VE];
+        for (int r = 0; r < k.nranks; ++r) {
+            uint4 raw = ((const uint4 *)slots[r])[i];
+            const T *e = (const T *)&raw;
+#pragma unroll
+            for (int j = 0; j < VE; ++j) acc[j] = r == 0 ? ToAcc<T>(e[j]) : Combine<OP, Ac>(acc[j], ToAcc<T>(e[j]));
+        }
+        uint4 res;
+        T *e = (T *)&res;
+#pragma unroll
+        for (int j = 0; j < VE; ++j) e[j] = FromAcc<T>(acc[j]);
+        for (int d = 0; d < ndst; ++d) ((uint4 *)dsts[d])[i] = res;
+    }
+}
+
+// in place or out of place, both windows registered; bytes a multiple of 16. Rank r owns slice r: it alone reads that slice
+// of every rank's input and writes it to every rank's output, so in-place operation has no hazard.
+template <typename T, int OP, bool EMU, bool NVLS> __device__ void AllReduceZcBody(KCtx &k, const CollArgs &A)
+{
+    const int n = k.nranks;
+    const uint64_t slice = Up128((A.bytes + n - 1) / n);
+    if (!ChannelBarrier(k, 1)) return;
+    Part p = PartOf(SliceLen(A.bytes, slice, k.rank), k.vGrid, k.vBlock);
+    const uint64_t so = (uint64_t)k.rank * slice + p.off;
+    if constexpr (NVLS) {
+        const char *src = k.c->mcHeap + A.inOff + so;
+        char *dst = k.c->mcHeap + A.outOff + so;
+        MultimemReduceLoop<T, OP>(src, p.len >> 4, [&](uint64_t i, uint4 v) { MultimemSt16(dst + (i << 4), v); });
+    } else {
+        char *dsts[kMaxRanks];
+        for (int d = 0; d < n; ++d) dsts[d] = k.PeerHeap((k.rank + d) % n) + A.outOff + so;
+        ReduceRanksTo<T, OP>(k, A.inOff + so, dsts, n, p.len);
+    }
+    ChannelBarrier(k, 2);
+}
+template <typename T, int OP, bool EMU> __device__ void AllReduceZcPlainBody(KCtx &k, const CollArgs &A) { AllReduceZcBody<T, OP, EMU, false>(k, A); }
+template <typename T, int OP, bool EMU> __device__ void AllReduceZcNvlsBody(KCtx &k, const CollArgs &A) { AllReduceZcBody<T, OP, EMU, true>(k, A); }
+
+// input window registered ([n x bytes]), output anywhere (16-byte aligned)
+template <typename T, int OP, bool EMU, bool NVLS> __device__ void ReduceScatterZcBody(KCtx &k, const CollArgs &A)
+{
+    if (!ChannelBarrier(k, 1)) return;
+    Part p = PartOf(A.bytes, k.vGrid, k.vBlock);
+    const uint64_t so = (uint64_t)k.rank * A.bytes + p.off;
+    char *out = (char *)A.out + p.off;
+    if constexpr (NVLS) {
+        T *o = (T *)out;
+        MultimemReduceLoop<T, OP>(k.c->mcHeap + A.inOff + so, p.len >> 4, [&](uint64_t i, uint4 v) { ((uint4 *)o)[i] = v; });
+    } else {
+        char *dsts[1] = {out};
+        ReduceRanksTo<T, OP>(k, A.inOff + so, dsts, 1, p.len);
+    }
+    ChannelBarrier(k, 2);
+}
+template <typename T, int OP, bool EMU> __device__ void ReduceScatterZcPlainBody(KCtx &k, const CollArgs &A) { ReduceScatterZcBody<T, OP, EMU, false>(k, A); }
+template <typename T, int OP, bool EMU> __device__ void ReduceScatterZcNvlsBody(KCtx &k, const CollArgs &A) { ReduceScatterZcBody<T, OP, EMU, true>(k, A); }
+
+// output window registered ([n x bytes]), input anywhere (16-byte aligned): every rank stores its block into every output
+template <bool EMU, bool NVLS> __device__ void AllGatherZcBody(KCtx &k, const CollArgs &A)
+{
+    const int n = k.nranks;
+    if (!ChannelBarrier(k, 1)) return;
+    Part p = PartOf(A.bytes, k.vGrid, k.vBlock);
+    const char *in = (const char *)A.in + p.off;
+    const uint64_t doff = A.outOff + (uint64_t)k.rank * A.bytes + p.off;
+    if constexpr (NVLS) {
+        char *mc = k.c->mcHeap + doff;
+        for (uint64_t i = threadIdx.x; i < (p.len >> 4); i += blockDim.x) MultimemSt16(mc + (i << 4), ((const uint4 *)in)[i]);
+    } else {
+        for (int d = 0; d < n; ++d) {
+            const int r = (k.rank + d) % n;
+            char *dst = k.PeerHeap(r) + doff;
+            if (dst != in) BlockCopy(dst, in, p.len);
+        }
+    }
+    ChannelBarrier(k, 2);
+}
+template <bool EMU> __device__ void AllGatherZcPlainBody(KCtx &k, const CollArgs &A) { AllGatherZcBody<EMU, false>(k, A); }
+template <bool EMU> __device__ void AllGatherZcNvlsBody(KCtx &k, const CollArgs &A) { AllGatherZcBody<EMU, true>(k, A); }
+
+// the buffer is a registered window on every rank: the root multicasts it (or the others pull it from the root's window)
+template <bool EMU, bool NVLS> __device__ void BroadcastZcBody(KCtx &k, const CollArgs &A)
+{
+    if (!ChannelBarrier(k, 1)) return;
+    Part p = PartOf(A.bytes, k.vGrid, k.vBlock);
+    const int root = (int)A.root;
+    if constexpr (NVLS) {
+        if (k.rank == root) {
+            const char *src = k.PeerHeap(root) + A.outOff + p.off;
+            char *mc = k.c->mcHeap + A.outOff + p.off;
+            for (uint64_t i = threadIdx.x; i < (p.len >> 4); i += blockDim.x) MultimemSt16(mc + (i << 4), ((const uint4 *)src)[i]);
+        }
+    } else if (k.rank != root) {
+        BlockCopy(k.PeerHeap(k.rank) + A.outOff + p.off, k.PeerHeap(root) + A.outOff + p.off, p.len);
+    }
+    ChannelBarrier(k, 2);
+}
+template <bool EMU> __device__ void BroadcastZcPlainBody(KCtx &k, const CollArgs &A) { BroadcastZcBody<EMU, false>(k, A); }
+template <bool EMU> __device__ void BroadcastZcNvlsBody(KCtx &k, const CollArgs &A) { BroadcastZcBody<EMU, true>(k, A); }
+
 #include "pipelined.cuh"
 
 // ================================================================================================ kernels
@@ -441,6 +556,8 @@ template <bool EMU> __device__ void AllGatherPipeNvlsBody(KCtx &k, const CollArg
 template <bool EMU> __device__ void AlltoAllPipeBody(KCtx &k, const CollArgs &A) { pipe::AllGatherBody<EMU, false, true>(k, A); }
 COLL_KERNEL_TYPED(KAllReduceRing, AllReduceRingBody)
 COLL_KERNEL_TYPED(KAllReduceConcurrentPlain, AllReduceConcurrentPlainBody)
+COLL_KERNEL_TYPED(KAllReduceZc, AllReduceZcPlainBody)
+COLL_KERNEL_TYPED(KReduceScatterZc, ReduceScatterZcPlainBody)
 COLL_KERNEL_TYPED(KAllReducePipe, AllReducePipePlainBody)
 COLL_KERNEL_TYPED(KReduceScatterPipe, ReduceScatterPipePlainBody)
 
@@ -457,6 +574,8 @@ COLL_KERNEL_NVLS(KAllReduceNvlsTwoShot, AllReduceNvlsTwoShotBody)
 COLL_KERNEL_NVLS(KReduceScatterNvls, ReduceScatterNvlsBody)
 COLL_KERNEL_NVLS(KAllReducePipeNvls, AllReducePipeNvlsBody)
 COLL_KERNEL_NVLS(KAllReduceConcurrentNvls, AllReduceConcurrentNvlsBody)
+COLL_KERNEL_NVLS(KAllReduceZcNvls, AllReduceZcNvlsBody)
+COLL_KERNEL_NVLS(KReduceScatterZcNvls, ReduceScatterZcNvlsBody)
 COLL_KERNEL_NVLS(KReduceScatterPipeNvls, ReduceScatterPipeNvlsBody)
 
 #define COLL_KERNEL_BYTES(NAME, BODY)                                                                                  \
@@ -475,6 +594,10 @@ COLL_KERNEL_BYTES(KAlltoAllV, AlltoAllVBody)
 COLL_KERNEL_BYTES(KAllGatherPipe, AllGatherPipePlainBody)
 COLL_KERNEL_BYTES(KAllGatherPipeNvls, AllGatherPipeNvlsBody)
 COLL_KERNEL_BYTES(KAlltoAllPipe, AlltoAllPipeBody)
+COLL_KERNEL_BYTES(KAllGatherZc, AllGatherZcPlainBody)
+COLL_KERNEL_BYTES(KAllGatherZcNvls, AllGatherZcNvlsBody)
+COLL_KERNEL_BYTES(KBroadcastZc, BroadcastZcPlainBody)
+COLL_KERNEL_BYTES(KBroadcastZcNvls, BroadcastZcNvlsBody)
 
 template <bool EMU> __global__ void __launch_bounds__(kThreads) KBarrier(const DevComm *comms, const __grid_constant__ CollArgs a, const CollArgs *)
 {
@@ -643,6 +766,8 @@ template <bool EMU> CollKernelFn TypedKernel(SmKernelId id, HcclDataType dt)
         case K_REDUCE: PICK(KReduce)
         case K_ALLREDUCE_RING: PICK(KAllReduceRing)
         case K_ALLREDUCE_CONCURRENT: PICK(KAllReduceConcurrentPlain)
+        case K_ALLREDUCE_ZC: PICK(KAllReduceZc)
+        case K_REDUCESCATTER_ZC: PICK(KReduceScatterZc)
         case K_ALLREDUCE_PIPE: PICK(KAllReducePipe)
         case K_REDUCESCATTER_PIPE: PICK(KReduceScatterPipe)
         default: return nullptr;
@@ -667,6 +792,8 @@ template <bool EMU> CollKernelFn NvlsKernel(SmKernelId id, HcclDataType dt, Hccl
         case K_REDUCESCATTER_NVLS: PICKN(KReduceScatterNvls)
         case K_ALLREDUCE_PIPE_NVLS: PICKN(KAllReducePipeNvls)
         case K_ALLREDUCE_CONCURRENT_NVLS: PICKN(KAllReduceConcurrentNvls)
+        case K_ALLREDUCE_ZC_NVLS: PICKN(KAllReduceZcNvls)
+        case K_REDUCESCATTER_ZC_NVLS: PICKN(KReduceScatterZcNvls)
         case K_REDUCESCATTER_PIPE_NVLS: PICKN(KReduceScatterPipeNvls)
         default: return nullptr;
     }
@@ -676,13 +803,17 @@ template <bool EMU> CollKernelFn NvlsKernel(SmKernelId id, HcclDataType dt, Hccl
 template <bool EMU> CollKernelFn KernelFor(const SmLaunch &l)
 {
     switch (l.kernel) {
-        case K_ALLREDUCE_ONESHOT: case K_ALLREDUCE_TWOSHOT: case K_REDUCESCATTER_V: case K_REDUCE: case K_ALLREDUCE_PIPE: case K_REDUCESCATTER_PIPE: case K_ALLREDUCE_RING: case K_ALLREDUCE_CONCURRENT:
+        case K_ALLREDUCE_ONESHOT: case K_ALLREDUCE_TWOSHOT: case K_REDUCESCATTER_V: case K_REDUCE: case K_ALLREDUCE_PIPE: case K_REDUCESCATTER_PIPE: case K_ALLREDUCE_RING: case K_ALLREDUCE_CONCURRENT: case K_ALLREDUCE_ZC: case K_REDUCESCATTER_ZC:
             return TypedKernel<EMU>(l.kernel, l.dtype);
-        case K_ALLREDUCE_NVLS_ONESHOT: case K_ALLREDUCE_NVLS_TWOSHOT: case K_REDUCESCATTER_NVLS: case K_ALLREDUCE_PIPE_NVLS: case K_REDUCESCATTER_PIPE_NVLS: case K_ALLREDUCE_CONCURRENT_NVLS:
+        case K_ALLREDUCE_NVLS_ONESHOT: case K_ALLREDUCE_NVLS_TWOSHOT: case K_REDUCESCATTER_NVLS: case K_ALLREDUCE_PIPE_NVLS: case K_REDUCESCATTER_PIPE_NVLS: case K_ALLREDUCE_CONCURRENT_NVLS: case K_ALLREDUCE_ZC_NVLS: case K_REDUCESCATTER_ZC_NVLS:
             return NvlsKernel<EMU>(l.kernel, l.dtype, (HcclReduceOp)l.args.op);
         case K_ALLGATHER_PIPE: return KAllGatherPipe<EMU>;
         case K_ALLGATHER_PIPE_NVLS: return KAllGatherPipeNvls<EMU>;
         case K_ALLTOALL_PIPE: return KAlltoAllPipe<EMU>;
+        case K_ALLGATHER_ZC: return KAllGatherZc<EMU>;
+        case K_ALLGATHER_ZC_NVLS: return KAllGatherZcNvls<EMU>;
+        case K_BROADCAST_ZC: return KBroadcastZc<EMU>;
+        case K_BROADCAST_ZC_NVLS: return KBroadcastZcNvls<EMU>;
         case K_ALLGATHER_V: return KAllGatherV<EMU>;
         case K_BROADCAST: return KBroadcast<EMU>;
         case K_BROADCAST_NVLS: return KBroadcastNvls<EMU>;

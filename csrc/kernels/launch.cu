@@ -30,7 +30,11 @@ const std::vector<SmAlgoDesc> &SmAlgorithms()
         {"SmReduceMesh1D", HCCL_CMD_REDUCE, false}, {"SmScatterMesh1D", HCCL_CMD_SCATTER, false},
         {"SmAlltoAllMesh1D", HCCL_CMD_ALLTOALL, false}, {"SmAlltoAllVMesh1D", HCCL_CMD_ALLTOALLV, false},
         {"SmAlltoAllVCMesh1D", HCCL_CMD_ALLTOALLVC, false}, {"SmBarrierMesh1D", HCCL_CMD_BARRIER, false},
-        {"SmAllReduceRing", HCCL_CMD_ALLREDUCE, false}, {"SmAllReduceConcurrent", HCCL_CMD_ALLREDUCE, false}, {"NvlsAllReduceConcurrent", HCCL_CMD_ALLREDUCE, true}, {"SmAllReducePipelined", HCCL_CMD_ALLREDUCE, false}, {"NvlsAllReducePipelined", HCCL_CMD_ALLREDUCE, true},
+        {"SmAllReduceRing", HCCL_CMD_ALLREDUCE, false}, {"SmAllReduceConcurrent", HCCL_CMD_ALLREDUCE, false}, {"NvlsAllReduceConcurrent", HCCL_CMD_ALLREDUCE, true},
+        {"SmAllReduceZeroCopy", HCCL_CMD_ALLREDUCE, false}, {"NvlsAllReduceZeroCopy", HCCL_CMD_ALLREDUCE, true},
+        {"SmReduceScatterZeroCopy", HCCL_CMD_REDUCE_SCATTER, false}, {"NvlsReduceScatterZeroCopy", HCCL_CMD_REDUCE_SCATTER, true},
+        {"SmAllGatherZeroCopy", HCCL_CMD_ALLGATHER, false}, {"NvlsAllGatherZeroCopy", HCCL_CMD_ALLGATHER, true},
+        {"SmBroadcastZeroCopy", HCCL_CMD_BROADCAST, false}, {"NvlsBroadcastZeroCopy", HCCL_CMD_BROADCAST, true}, {"SmAllReducePipelined", HCCL_CMD_ALLREDUCE, false}, {"NvlsAllReducePipelined", HCCL_CMD_ALLREDUCE, true},
         {"SmReduceScatterPipelined", HCCL_CMD_REDUCE_SCATTER, false}, {"SmReduceScatterVPipelined", HCCL_CMD_REDUCE_SCATTER_V, false},
         {"NvlsReduceScatterPipelined", HCCL_CMD_REDUCE_SCATTER, true},
         {"SmAllGatherPush", HCCL_CMD_ALLGATHER, false}, {"SmAllGatherVPush", HCCL_CMD_ALLGATHER_V, false},
@@ -53,6 +57,7 @@ HcclResult SmOrchestrate(Comm *c, OpParam &p, const std::string &algName)
     ctx.mailboxBytes = c->devComm.mailboxBytes;
     ctx.maxCtas = c->env.maxCtas;
     ctx.nvls = c->mcHeap != nullptr;
+    ctx.registeredOffset = [c](const void *ptr, uint64_t bytes, uint64_t *off) { return CommRegisteredOffset(c, ptr, bytes, off); };
     if (c->env.multiDimSplitSet) { ctx.splitRatio[0] = c->env.multiDimSplitRatio[0]; ctx.splitRatio[1] = c->env.multiDimSplitRatio[1]; }
     std::vector<SmLaunch> launches;
     HcclResult r = SmPlanOp(ctx, p, algName, &launches);
@@ -177,6 +182,13 @@ HcclResult HcclEmuRun(void *emu, HcclCMDType op, const char *algName, void **ins
         }
         SmPlanCtx ctx{r, n, w->cclBytes, w->mailboxBytes, maxCtas ? maxCtas : 4u, false};
         (void)InitEnvConfig();
+        // emulated ranks: a buffer inside a rank's arena counts as a registered window
+        ctx.registeredOffset = [w, r](const void *ptr, uint64_t bytes, uint64_t *off) {
+            const char *pc = (const char *)ptr, *base = w->heaps[r] + w->arenaOff;
+            if (pc < base || pc + bytes > base + w->arenaBytes) return false;
+            *off = (uint64_t)(pc - w->heaps[r]);
+            return true;
+        };
         if (GetEnvConfig().multiDimSplitSet) { ctx.splitRatio[0] = GetEnvConfig().multiDimSplitRatio[0]; ctx.splitRatio[1] = GetEnvConfig().multiDimSplitRatio[1]; }
         HcclResult pr = SmPlanOp(ctx, p, algName, &per[r]);
         if (pr != HCCL_SUCCESS) return pr;
@@ -247,6 +259,16 @@ HcclResult HcclEmuStatus(void *emu, uint32_t rank, uint32_t *out, int clear)
         for (char *h : w->heaps) cudaMemset(h, 0, kHeapHeaderBytes);
         cudaDeviceSynchronize();
     }
+    return HCCL_SUCCESS;
+}
+
+// Base address and size of an emulated rank's arena (the part of its heap that stands for symmetric user allocations).
+HcclResult HcclEmuArena(void *emu, uint32_t rank, void **base, uint64_t *bytes)
+{
+    auto *w = (EmuWorld *)emu;
+    if (!w || !base || !bytes || rank >= (uint32_t)w->nranks) return HCCL_E_PARA;
+    *base = w->heaps[rank] + w->arenaOff;
+    *bytes = w->arenaBytes;
     return HCCL_SUCCESS;
 }
 

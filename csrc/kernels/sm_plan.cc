@@ -103,6 +103,34 @@ HcclResult SmPlanOp(const SmPlanCtx &ctx, const OpParam &p, const std::string &a
             });
         });
     }
+    if (alg.size() > 8 && alg.compare(alg.size() - 8, 8, "ZeroCopy") == 0) {
+        // Registered windows on both sides of the transfer that crosses ranks; one launch for any size (no scratch, no chunks).
+        const bool nv = alg[0] == 'N';
+        if (nv && !ctx.nvls) return HCCL_E_NOT_SUPPORT;
+        if (!ctx.registeredOffset) return HCCL_E_NOT_SUPPORT;
+        const uint64_t bytes = p.count * es;
+        if (bytes == 0 || bytes % 16 || ((uintptr_t)in & 15u) || ((uintptr_t)outp & 15u)) return HCCL_E_NOT_SUPPORT;
+        uint64_t inOff = 0, outOff = 0;
+        SmKernelId id;
+        uint64_t moved = bytes;
+        if (p.opType == HCCL_CMD_ALLREDUCE) {
+            if (!ctx.registeredOffset(in, bytes, &inOff) || !ctx.registeredOffset(outp, bytes, &outOff)) return HCCL_E_NOT_SUPPORT;
+            id = nv ? K_ALLREDUCE_ZC_NVLS : K_ALLREDUCE_ZC;
+            moved = bytes / n * 2;
+        } else if (p.opType == HCCL_CMD_REDUCE_SCATTER) {
+            if (!ctx.registeredOffset(in, bytes * n, &inOff)) return HCCL_E_NOT_SUPPORT;
+            id = nv ? K_REDUCESCATTER_ZC_NVLS : K_REDUCESCATTER_ZC;
+        } else if (p.opType == HCCL_CMD_ALLGATHER) {
+            if (!ctx.registeredOffset(outp, bytes * n, &outOff)) return HCCL_E_NOT_SUPPORT;
+            id = nv ? K_ALLGATHER_ZC_NVLS : K_ALLGATHER_ZC;
+            moved = bytes * (n - 1);
+        } else if (p.opType == HCCL_CMD_BROADCAST) {
+            if (!ctx.registeredOffset(outp, bytes, &outOff)) return HCCL_E_NOT_SUPPORT;
+            id = nv ? K_BROADCAST_ZC_NVLS : K_BROADCAST_ZC;
+        } else return HCCL_E_NOT_SUPPORT;
+        push(id, 0, p.count, moved, [&](SmLaunch &l) { l.args.in = in; l.args.out = outp; l.args.inOff = inOff; l.args.outOff = outOff; });
+        return HCCL_SUCCESS;
+    }
     if (alg == "SmAllReduceRing") {
         if (n < 2) return HCCL_E_NOT_SUPPORT;
         uint64_t maxSlice = Down128(ccl / (2 * (n - 1)));

@@ -211,6 +211,57 @@ static bool Excluded(const SelectorCtx &ctx, HcclCommEngine e)
     return std::find(ctx.excluded.begin(), ctx.excluded.end(), e) != ctx.excluded.end();
 }
 
+namespace {
+bool NvlsSupportsZc(HcclDataType dt, HcclReduceOp op)
+{
+    if (dt == HCCL_DATA_TYPE_FP32) return op == HCCL_REDUCE_SUM;
+    if (dt == HCCL_DATA_TYPE_BFP16 || dt == HCCL_DATA_TYPE_FP16) return op == HCCL_REDUCE_SUM || op == HCCL_REDUCE_MAX || op == HCCL_REDUCE_MIN;
+    return false;
+}
+bool ZeroCopyApplies(const SelectorCtx &ctx, OpParam &p)
+{
+    static const bool enabled = [] { const char *e = getenv("HCCL_ZERO_COPY"); return e ? atoi(e) != 0 : true; }();
+    static const uint64_t minBytes = [] { const char *e = getenv("HCCL_ZERO_COPY_MIN_BYTES"); return e ? (uint64_t)strtoull(e, nullptr, 0) : (1ull << 20); }();
+    if (!enabled || p.mode != OpMode::OPBASE) return false;
+    const uint32_t n = ctx.topo->nranks;
+    const uint64_t bytes = p.count * DataTypeSize(p.dtype);
+    if (bytes < minBytes || bytes % 16 || ((uintptr_t)p.inputPtr & 15u) || ((uintptr_t)p.outputPtr & 15u)) return false;
+    const char *base = nullptr;
+    bool reduces = false;
+    switch (p.opType) {
+        case HCCL_CMD_ALLREDUCE:
+            if (!CommRegisteredOffset(ctx.comm, p.inputPtr, bytes, nullptr) || !CommRegisteredOffset(ctx.comm, p.outputPtr, bytes, nullptr)) return false;
+            base = "AllReduce"; reduces = true; break;
+        case HCCL_CMD_REDUCE_SCATTER:
+            if (!CommRegisteredOffset(ctx.comm, p.inputPtr, bytes * n, nullptr)) return false;
+            base = "ReduceScatter"; reduces = true; break;
+        case HCCL_CMD_ALLGATHER:
+            if (!CommRegisteredOffset(ctx.comm, p.outputPtr, bytes * n, nullptr)) return false;
+            base = "AllGather"; break;
+        case HCCL_CMD_BROADCAST:
+            if (!CommRegisteredOffset(ctx.comm, p.outputPtr, bytes, nullptr)) return false;
+            base = "Broadcast"; break;
+        default: return false;
+    }
+    HcclCommEngine want = ctx.env->expansionMode;
+    auto perOp = ctx.env->expansionModePerOp.find(p.opType);
+    if (perOp != ctx.env->expansionModePerOp.end()) want = perOp->second;
+    if (want == HCCL_ENGINE_COPY_ENGINE || want == HCCL_ENGINE_HOST) return false;
+    bool nv = ctx.nvls && want != HCCL_ENGINE_SM && (!reduces || (ctx.env->deterministic == Deterministic::OFF && NvlsSupportsZc(p.dtype, p.reduceOp)));
+    if (reduces && !nv) {
+        // the peer-load form reduces in rank order with fp32 accumulation: every reducible type of the SM engine
+        switch (p.dtype) {
+            case HCCL_DATA_TYPE_FP32: case HCCL_DATA_TYPE_FP16: case HCCL_DATA_TYPE_BFP16: case HCCL_DATA_TYPE_INT32: case HCCL_DATA_TYPE_INT64:
+            case HCCL_DATA_TYPE_FP64: case HCCL_DATA_TYPE_INT8: case HCCL_DATA_TYPE_INT16: break;
+            default: return false;
+        }
+    }
+    p.engine = nv ? HCCL_ENGINE_NVLS : HCCL_ENGINE_SM;
+    p.algName = std::string(nv ? "Nvls" : "Sm") + base + "ZeroCopy";
+    return true;
+}
+}  // namespace
+
 SelectorStatus AutoSelectorBase::Select(const SelectorCtx &ctx, OpParam &param) const
 {
     // explicit algorithm name wins (engine inferred from the prefix)
@@ -223,6 +274,11 @@ SelectorStatus AutoSelectorBase::Select(const SelectorCtx &ctx, OpParam &param) 
         else param.engine = ctx.cuda ? HCCL_ENGINE_COPY_ENGINE : HCCL_ENGINE_HOST;
         return SelectorStatus::MATCH;
     }
+    // Registered windows on the rank-crossing side of the transfer: no staging through the scratch buffer at all. Chosen from
+    // HCCL_ZERO_COPY_MIN_BYTES up (default 1 MB; below that the staged one-shot kernels have one synchronisation less);
+    // HCCL_ZERO_COPY=0 switches the rule off. Every rank decides from its own pointers: buffers that come from the same
+    // symmetric allocation give the same answer everywhere, and the consistency exchange compares the algorithm names.
+    if (ctx.cuda && ctx.comm && ctx.excluded.empty() && ZeroCopyApplies(ctx, param)) return SelectorStatus::MATCH;
     HcclCommEngine want = ctx.env->expansionMode;
     auto perOp = ctx.env->expansionModePerOp.find(param.opType);
     if (perOp != ctx.env->expansionModePerOp.end()) want = perOp->second;

@@ -147,7 +147,8 @@ HcclResult CheckPlans(const CheckSpec &spec, const std::vector<std::vector<Plan>
                                 if (!bounds(*b, t.bytes, b == &t.dst ? dstRank : srcRank))
                                     return fail(std::string(b->kind == BufKind::CCL ? "scratch window" : b->kind == BufKind::MAILBOX ? "mailbox" : "user buffer") +
                                                 " overrun at " + Where(r, q, pc[r][q], t));
-                            if ((remoteDst && t.dst.kind != BufKind::CCL && t.dst.kind != BufKind::MAILBOX) || (remoteSrc && t.src.kind != BufKind::CCL && t.src.kind != BufKind::MAILBOX))
+                            if (!spec.registeredUserBuffers &&
+                                ((remoteDst && t.dst.kind != BufKind::CCL && t.dst.kind != BufKind::MAILBOX) || (remoteSrc && t.src.kind != BufKind::CCL && t.src.kind != BufKind::MAILBOX)))
                                 return fail("remote access outside the symmetric heap at " + Where(r, q, pc[r][q], t));
                             accesses.push_back({srcRank, (int)t.src.kind, t.src.off, t.src.off + t.bytes, false, ck, r, (uint32_t)q, (uint32_t)pc[r][q]});
                             accesses.push_back({dstRank, (int)t.dst.kind, t.dst.off, t.dst.off + t.bytes, true, ck, r, (uint32_t)q, (uint32_t)pc[r][q]});

@@ -32,6 +32,8 @@ struct CheckSpec {
     uint64_t mailboxBytes = 0;            // bytes of one mailbox slot (0 = unchecked)
     // ABS buffer references (BatchSendRecv items carry absolute addresses) are mapped back to the rank's input / output by range
     uint64_t absInputBase = 0, absOutputBase = 0;
+    // zero-copy schedules: the callers' buffers are registered windows of the symmetric heap, so peers may address them
+    bool registeredUserBuffers = false;
 };
 uint64_t CheckInputElems(const CheckSpec &s, uint32_t rank);
 uint64_t CheckOutputElems(const CheckSpec &s, uint32_t rank);

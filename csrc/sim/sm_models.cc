@@ -313,6 +313,65 @@ void Scatter(Model &m)
     }
 }
 
+// ---- zero-copy forms: peers address the registered user windows directly (remote INPUT / OUTPUT references)
+void ZcPeerRead(Model &m, uint32_t ch, BufRef dst, uint32_t peer, BufRef src, uint64_t len, bool reduce)
+{
+    if (!len) return;
+    if (peer == m.me) { if (reduce) m.Reduce(ch, dst, src, len); else m.Copy(ch, dst, src, len); }
+    else m.Q(ch).push_back(Task{reduce ? TaskType::READ_REDUCE : TaskType::READ, peer, 0, dst, src, len});
+}
+void ZcPeerWrite(Model &m, uint32_t ch, uint32_t peer, BufRef dst, BufRef src, uint64_t len)
+{
+    if (!len) return;
+    if (peer == m.me) { if (!(dst.kind == src.kind && dst.off == src.off)) m.Copy(ch, dst, src, len); }
+    else m.Q(ch).push_back(Task{TaskType::WRITE, peer, 0, dst, src, len});
+}
+void AllReduceZc(Model &m)
+{
+    const uint32_t n = m.n;
+    const uint64_t bytes = m.A().bytes, slice = Up128((bytes + n - 1) / n);
+    for (uint32_t ch = 0; ch < m.C; ++ch) {
+        m.Barrier(ch);
+        Part p = PartOf(SliceLen(bytes, slice, m.me), m.C, ch);
+        const uint64_t so = (uint64_t)m.me * slice + p.off;
+        // the owner's reduction of its slice lands in its own output first, then goes to every peer's output
+        for (uint32_t r = 0; r < n; ++r) ZcPeerRead(m, ch, m.Out(so), r, m.In(so), p.len, r != 0);
+        for (uint32_t d = 1; d < n; ++d) ZcPeerWrite(m, ch, (m.me + d) % n, m.Out(so), m.Out(so), p.len);
+        m.Barrier(ch);
+    }
+}
+void ReduceScatterZc(Model &m)
+{
+    const uint64_t bytes = m.A().bytes;
+    for (uint32_t ch = 0; ch < m.C; ++ch) {
+        m.Barrier(ch);
+        Part p = PartOf(bytes, m.C, ch);
+        for (uint32_t r = 0; r < m.n; ++r) ZcPeerRead(m, ch, m.Out(p.off), r, m.In((uint64_t)m.me * bytes + p.off), p.len, r != 0);
+        m.Barrier(ch);
+    }
+}
+void AllGatherZc(Model &m)
+{
+    const uint64_t bytes = m.A().bytes;
+    for (uint32_t ch = 0; ch < m.C; ++ch) {
+        m.Barrier(ch);
+        Part p = PartOf(bytes, m.C, ch);
+        for (uint32_t d = 0; d < m.n; ++d) ZcPeerWrite(m, ch, (m.me + d) % m.n, m.Out((uint64_t)m.me * bytes + p.off), m.In(p.off), p.len);
+        m.Barrier(ch);
+    }
+}
+void BroadcastZc(Model &m, bool nvls)
+{
+    const CollArgs &A = m.A();
+    for (uint32_t ch = 0; ch < m.C; ++ch) {
+        m.Barrier(ch);
+        Part p = PartOf(A.bytes, m.C, ch);
+        if (nvls) { if (m.me == A.root) for (uint32_t d = 1; d < m.n; ++d) ZcPeerWrite(m, ch, (m.me + d) % m.n, m.Out(p.off), m.Out(p.off), p.len); }
+        else if (m.me != A.root) ZcPeerRead(m, ch, m.Out(p.off), A.root, m.Out(p.off), p.len, false);
+        m.Barrier(ch);
+    }
+}
+
 // packed offset of the segment rank `src` holds for rank `dst` (what the kernel publishes in its metadata words)
 uint64_t PackedOffset(const CollArgs &srcArgs, uint32_t src, uint32_t dst, uint32_t n)
 {
@@ -360,6 +419,11 @@ HcclResult GenSmModelPlan(const std::vector<SmLaunch> &all, uint32_t me, uintptr
         case K_ALLREDUCE_RING: AllReduceRing(m); break;
         case K_ALLREDUCE_CONCURRENT: AllReduceConcurrent(m, false); break;
         case K_ALLREDUCE_CONCURRENT_NVLS: AllReduceConcurrent(m, true); break;
+        case K_ALLREDUCE_ZC: case K_ALLREDUCE_ZC_NVLS: AllReduceZc(m); break;      // the switch-reduced form moves the same data
+        case K_REDUCESCATTER_ZC: case K_REDUCESCATTER_ZC_NVLS: ReduceScatterZc(m); break;
+        case K_ALLGATHER_ZC: case K_ALLGATHER_ZC_NVLS: AllGatherZc(m); break;
+        case K_BROADCAST_ZC: BroadcastZc(m, false); break;
+        case K_BROADCAST_ZC_NVLS: BroadcastZc(m, true); break;
         case K_ALLGATHER_V: AllGatherV(m); break;
         case K_REDUCESCATTER_V: ReduceScatterV(m, false); break;
         case K_REDUCESCATTER_NVLS: ReduceScatterV(m, true); break;

@@ -275,6 +275,47 @@ class Communicator:
             cuda = self.is_cuda
         check(lib().HcclBarrier(self._h, self._stream(cuda, stream)), "HcclBarrier")
 
+    # ---- symmetric memory and registered windows -----------------------------------------------------------------
+    def sym_tensor(self, numel: int, dtype, register: bool = True):
+        """A CUDA tensor over a fresh symmetric allocation (the same heap offset on every rank when all ranks make the same
+        sequence of calls). With `register`, the range is also registered as a window, which lets AllReduce, ReduceScatter,
+        AllGather and Broadcast on it run without staging through the scratch buffer."""
+        import torch
+
+        nbytes = numel * torch.empty(0, dtype=dtype).element_size()
+        ptr = ctypes.c_void_p()
+        check(lib().HcclCommSymAlloc(self._h, max(nbytes, 16), ctypes.byref(ptr)), "HcclCommSymAlloc")
+        if register:
+            off = ctypes.c_uint64()
+            fn = lib().HcclCommMemReg
+            fn.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint64, ctypes.POINTER(ctypes.c_uint64)]
+            check(fn(self._h, ptr, max(nbytes, 16), ctypes.byref(off)), "HcclCommMemReg")
+
+        class _Window:
+            __cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr.value, False), "version": 3, "strides": None}
+
+        t = torch.as_tensor(_Window(), device="cuda").view(dtype)
+        t._hccl_sym_ptr = ptr.value
+        return t
+
+    def sym_free(self, tensor) -> None:
+        """Returns a sym_tensor's memory to the arena (its window registration goes with it). Collective in the same sense as
+        the allocation: every rank frees in the same order."""
+        check(lib().HcclCommSymFree(self._h, ctypes.c_void_p(tensor._hccl_sym_ptr)), "HcclCommSymFree")
+
+    def last_algorithm(self) -> str:
+        """Name of the algorithm the most recent operator ran with."""
+        class Rec(ctypes.Structure):
+            _fields_ = [("seq", ctypes.c_uint64), ("opType", ctypes.c_uint32), ("dataType", ctypes.c_uint32), ("reduceOp", ctypes.c_uint32),
+                        ("root", ctypes.c_uint32), ("engine", ctypes.c_uint32), ("pad", ctypes.c_uint32), ("count", ctypes.c_uint64),
+                        ("algName", ctypes.c_char * 64), ("beginNs", ctypes.c_uint64), ("endNs", ctypes.c_uint64)]
+        recs = (Rec * 64)()
+        n = ctypes.c_uint32()
+        fn = lib().HcclGetLastOps
+        fn.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint32, ctypes.POINTER(ctypes.c_uint32)]
+        check(fn(self._h, recs, 64, ctypes.byref(n)), "HcclGetLastOps")
+        return recs[n.value - 1].algName.decode() if n.value else ""
+
     @property
     def is_cuda(self) -> bool:
         fn = getattr(lib(), "HcclCommIsCuda", None)

@@ -95,6 +95,21 @@ class EmuWorld:
         torch.cuda.synchronize()
         return rc
 
+    def arena_tensor(self, rank: int, offset: int, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        """A tensor over `numel` elements at byte `offset` of the rank's arena: memory at the same heap offset on every emulated
+        rank, i.e. what a registered window of a symmetric allocation is on a real communicator."""
+        base, size = ctypes.c_void_p(), ctypes.c_uint64()
+        self._l.HcclEmuArena.argtypes = [ctypes.c_void_p, ctypes.c_uint32, ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_uint64)]
+        check(self._l.HcclEmuArena(self._h, rank, ctypes.byref(base), ctypes.byref(size)), "HcclEmuArena")
+        nbytes = numel * torch.empty(0, dtype=dtype).element_size()
+        if offset + nbytes > size.value:
+            raise ValueError("arena window out of range")
+
+        class _Window:
+            __cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (base.value + offset, False), "version": 3, "strides": None}
+
+        return torch.as_tensor(_Window(), device="cuda").view(dtype)
+
     def trace(self, rank: int, max_records: int = 64):
         """Device-side records of the rank's most recent kernels: dicts with seq, syncs and %globaltimer stamps in ns."""
         rows = (ctypes.c_uint64 * (6 * max_records))()

@@ -139,10 +139,10 @@ def test_user_buffer_overrun_is_reported():
 # ---- the kernels of the SM / NVLS engines, through schedule models built from the real launch lists
 SM_ALGOS = {
     "ALLREDUCE": ["SmAllReduceMesh1DOneShot", "SmAllReduceMesh1DTwoShot", "SmAllReduceRing", "NvlsAllReduceOneShot", "NvlsAllReduceTwoShot",
-                  "SmAllReduceConcurrent", "NvlsAllReduceConcurrent"],
-    "ALLGATHER": ["SmAllGatherMesh1D"],
-    "REDUCE_SCATTER": ["SmReduceScatterMesh1D", "NvlsReduceScatter"],
-    "BROADCAST": ["SmBroadcastMesh1D", "NvlsBroadcast"],
+                  "SmAllReduceConcurrent", "NvlsAllReduceConcurrent", "SmAllReduceZeroCopy", "NvlsAllReduceZeroCopy"],
+    "ALLGATHER": ["SmAllGatherMesh1D", "SmAllGatherZeroCopy", "NvlsAllGatherZeroCopy"],
+    "REDUCE_SCATTER": ["SmReduceScatterMesh1D", "NvlsReduceScatter", "SmReduceScatterZeroCopy", "NvlsReduceScatterZeroCopy"],
+    "BROADCAST": ["SmBroadcastMesh1D", "NvlsBroadcast", "SmBroadcastZeroCopy", "NvlsBroadcastZeroCopy"],
     "REDUCE": ["SmReduceMesh1D"],
     "SCATTER": ["SmScatterMesh1D"],
     "ALLTOALL": ["SmAlltoAllMesh1D"],

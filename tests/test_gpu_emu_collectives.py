@@ -375,3 +375,54 @@ def test_concurrent_allreduce_splits_one_payload_between_two_sub_grids(emu_mod, 
     finally:
         monkeypatch.delenv("HCCL_ALG_MULTIPLE_DIMENSION_SPLIT_RATIO", raising=False)
         lib().HcclResetEnvConfigForTest()
+
+
+@pytest.mark.parametrize("nranks,count", [(2, 64), (4, 40_000), (8, 262_144), (3, 4100)])
+def test_zero_copy_kernels_on_registered_windows(emu_mod, nranks, count):
+    """Buffers at the same heap offset on every rank (registered windows): peers read and write them directly, the scratch
+    buffer is not used at all -- it is far too small here for the payloads -- and results match the staged kernels' bit for bit."""
+    es = 4
+    with emu_mod.EmuWorld(nranks, 64 << 10, arena_bytes=(2 * nranks + 4) * count * es + (1 << 20)) as w:
+        big_in = [w.arena_tensor(r, 0, count * nranks, torch.float32) for r in range(nranks)]
+        big_out = [w.arena_tensor(r, (count * nranks * es + 255) // 256 * 256, count * nranks, torch.float32) for r in range(nranks)]
+        # all-reduce, out of place and in place
+        for it in range(2):
+            xs = [_rand(count, torch.float32, 60 + it * 10 + r) for r in range(nranks)]
+            for r in range(nranks):
+                big_in[r][:count].copy_(xs[r])
+            ins = [t[:count] for t in big_in]
+            outs = [t[:count] for t in (big_out if it == 0 else big_in)]
+            ref = [torch.empty_like(x) for x in xs]
+            with emu_mod.EmuWorld(nranks, 8 << 20) as staged:
+                assert staged.run(CMD["ALLREDUCE"], "SmAllReduceMesh1DTwoShot", xs, ref, count, torch.float32, ReduceOp.SUM) == 0
+            assert w.run(CMD["ALLREDUCE"], "SmAllReduceZeroCopy", ins, outs, count, torch.float32, ReduceOp.SUM, max_ctas=4) == 0
+            for o, rf in zip(outs, ref):
+                assert torch.equal(o, rf)
+        # reduce-scatter: registered input, plain output
+        full = [_rand(count * nranks, torch.float32, 80 + r) for r in range(nranks)]
+        for r in range(nranks):
+            big_in[r].copy_(full[r])
+        outs = [torch.empty(count, device="cuda") for _ in range(nranks)]
+        assert w.run(CMD["REDUCE_SCATTER"], "SmReduceScatterZeroCopy", big_in, outs, count, torch.float32, ReduceOp.SUM, max_ctas=4) == 0
+        acc = full[0].clone()
+        for r in range(1, nranks):
+            acc += full[r]
+        for r in range(nranks):
+            assert torch.equal(outs[r], acc[r * count:(r + 1) * count])      # rank order, fp32: the same sum order as here
+        # all-gather: plain input, registered output
+        xs = [_rand(count, torch.float32, 90 + r) for r in range(nranks)]
+        assert w.run(CMD["ALLGATHER"], "SmAllGatherZeroCopy", xs, big_out, count, torch.float32, max_ctas=4) == 0
+        for r in range(nranks):
+            assert torch.equal(big_out[r], torch.cat(xs))
+        # broadcast in the registered window
+        root = nranks - 1
+        src = _rand(count, torch.float32, 99)
+        for r in range(nranks):
+            big_out[r][:count].copy_(src if r == root else torch.zeros_like(src))
+        bufs = [t[:count] for t in big_out]
+        assert w.run(CMD["BROADCAST"], "SmBroadcastZeroCopy", bufs, bufs, count, torch.float32, root=root, max_ctas=4) == 0
+        for r in range(nranks):
+            assert torch.equal(bufs[r], src)
+        # a buffer outside the arena is refused (HCCL_E_NOT_SUPPORT), not staged silently under this algorithm name
+        outside = [torch.zeros(count, device="cuda") for _ in range(nranks)]
+        assert w.run(CMD["ALLREDUCE"], "SmAllReduceZeroCopy", outside, outside, count, torch.float32, ReduceOp.SUM) == 5

@@ -2,6 +2,8 @@
 blobs, memory registration, rank graph queries on flat and multi-server topologies, exchanged blobs."""
 import ctypes
 
+import numpy as np
+
 from hccl_b200._lib import HcclCommConfig, lib
 from hccl_b200.types import Result
 from hccl_b200.utils.sim import run_ranks
@@ -89,6 +91,45 @@ def test_engine_ctx_blobs_and_memory_registration():
     res = run_ranks(2, body)
     assert res[0][0] == bytes(range(64))
     assert res[0][1] == res[1][1]                 # the window offset is the same on every rank
+
+
+def test_registered_window_lifetime():
+    """Register, deregister, re-register, overlap, free with a live registration, destroy with live registrations."""
+    l = _decl()
+
+    def body(comm, rank):
+        h = vp(comm.handle)
+        a, b, off = vp(), vp(), u64()
+        assert l.HcclCommSymAlloc(h, 1 << 16, ctypes.byref(a)) == 0
+        assert l.HcclCommSymAlloc(h, 1 << 16, ctypes.byref(b)) == 0
+        assert l.HcclCommMemReg(h, a, 1 << 16, ctypes.byref(off)) == 0
+        first = off.value
+        assert l.HcclCommMemReg(h, a, 1 << 16, ctypes.byref(off)) == 0 and off.value == first          # twice is fine
+        assert l.HcclCommMemReg(h, vp(a.value + 4096), 8192, ctypes.byref(off)) == 0                     # inside a window: fine
+        assert l.HcclCommMemReg(h, vp(a.value + (1 << 16) - 4096), 8192, ctypes.byref(off)) == Result.E_PARA   # straddles its end
+        assert l.HcclCommMemDereg(h, a) == 0
+        assert l.HcclCommMemDereg(h, a) == Result.E_NOT_FOUND                                              # already gone
+        assert l.HcclCommMemReg(h, vp(a.value + (1 << 16) - 4096), 8192, ctypes.byref(off)) == 0         # now a window of its own
+        assert l.HcclCommMemReg(h, a, 1 << 16, ctypes.byref(off)) == Result.E_PARA                        # would overlap it
+        assert l.HcclCommMemDereg(h, vp(a.value + (1 << 16) - 4096)) == 0
+        assert l.HcclCommMemReg(h, a, 1 << 16, ctypes.byref(off)) == 0 and off.value == first            # re-registered
+        # freeing the allocation drops the windows inside it; the freed range can be allocated and registered again
+        assert l.HcclCommSymFree(h, a) == 0
+        assert l.HcclCommMemDereg(h, a) == Result.E_NOT_FOUND
+        c2 = vp()
+        assert l.HcclCommSymAlloc(h, 1 << 16, ctypes.byref(c2)) == 0 and c2.value == a.value
+        assert l.HcclCommMemReg(h, c2, 1 << 16, ctypes.byref(off)) == 0 and off.value == first
+        assert l.HcclCommMemReg(h, b, 1 << 16, ctypes.byref(off)) == 0
+        second = off.value
+        # operators still run with windows registered (on this backend they are staged as always) ...
+        x = np.full(256, rank + 1.0, np.float32)
+        comm.all_reduce(x)
+        comm.synchronize()
+        return first, second, float(x[0])      # ... and the communicator is destroyed with both windows still registered
+
+    res = run_ranks(3, body)
+    assert len({r[0] for r in res}) == 1 and len({r[1] for r in res}) == 1 and res[0][0] != res[0][1]
+    assert all(r[2] == 6.0 for r in res)
 
 
 def test_rank_graph_flat_and_exchange_info():

@@ -167,13 +167,16 @@ def main():
     # zero-copy on registered windows: symmetric allocations at the same heap offset on every rank; from 1 MB up the selector
     # takes the kernels that read / write the windows directly (through the switch when the multicast mapping exists)
     zn = 1 << 20                                              # 4 MB of fp32
+    # an explicit engine or algorithm request wins over the zero-copy rule
+    expect_zc = "HCCL_OP_EXPANSION_MODE" not in os.environ and "HCCL_ALGO_NAME" not in os.environ
+    zc_ok = lambda suffix: comm.last_algorithm().endswith(suffix) == expect_zc    # noqa: E731
     win_in = comm.sym_tensor(zn * world, torch.float32)
     win_out = comm.sym_tensor(zn * world, torch.float32)
     for it in range(2):
         win_in[:zn].copy_(gen(rank, zn, torch.float32, salt=40 + it))
         comm.all_reduce(win_in[:zn], win_out[:zn])
         torch.cuda.synchronize()
-        check(f"zero-copy allreduce selected ({comm.last_algorithm()})", comm.last_algorithm().endswith("AllReduceZeroCopy"))
+        check(f"zero-copy allreduce selected ({comm.last_algorithm()})", zc_ok("AllReduceZeroCopy"))
         check(f"zero-copy allreduce it={it}", close(win_out[:zn], ref_reduce(world, zn, torch.float32, ReduceOp.SUM, salt=40 + it), torch.float32, world))
     comm.all_reduce(win_in[:zn])                              # in place
     torch.cuda.synchronize()
@@ -182,17 +185,17 @@ def main():
     rs_out = torch.empty(zn, dtype=torch.float32, device="cuda")
     comm.reduce_scatter(win_in, rs_out)
     torch.cuda.synchronize()
-    check(f"zero-copy reducescatter selected ({comm.last_algorithm()})", comm.last_algorithm().endswith("ReduceScatterZeroCopy"))
+    check(f"zero-copy reducescatter selected ({comm.last_algorithm()})", zc_ok("ReduceScatterZeroCopy"))
     check("zero-copy reducescatter", close(rs_out, ref_reduce(world, zn * world, torch.float32, ReduceOp.SUM, salt=43)[rank * zn:(rank + 1) * zn], torch.float32, world))
     ag_in = gen(rank, zn, torch.float32, salt=44)
     comm.all_gather(ag_in, win_out)
     torch.cuda.synchronize()
-    check(f"zero-copy allgather selected ({comm.last_algorithm()})", comm.last_algorithm().endswith("AllGatherZeroCopy"))
+    check(f"zero-copy allgather selected ({comm.last_algorithm()})", zc_ok("AllGatherZeroCopy"))
     check("zero-copy allgather", torch.equal(win_out, torch.cat([gen(r, zn, torch.float32, salt=44) for r in range(world)])))
     win_out[:zn].copy_(gen(rank, zn, torch.float32, salt=45))
     comm.broadcast(win_out[:zn], world - 1)
     torch.cuda.synchronize()
-    check(f"zero-copy broadcast selected ({comm.last_algorithm()})", comm.last_algorithm().endswith("BroadcastZeroCopy"))
+    check(f"zero-copy broadcast selected ({comm.last_algorithm()})", zc_ok("BroadcastZeroCopy"))
     check("zero-copy broadcast", torch.equal(win_out[:zn], gen(world - 1, zn, torch.float32, salt=45)))
     # small payloads and unregistered buffers keep the staged kernels
     comm.all_reduce(win_in[:1024], win_out[:1024])

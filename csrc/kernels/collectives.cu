@@ -188,6 +188,7 @@ template <typename T> __device__ __forceinline__ void StoreVec(T *out, uint64_t 
 template <typename T, int OP, typename Sink> __device__ __forceinline__ void MultimemReduceLoop(const char *mc, uint64_t nvec, Sink sink)
 {
     constexpr int U = 4;
+    if (!HCCL_RANGE_OK(mc, nvec << 4)) return;
     const uint64_t stride = (uint64_t)blockDim.x * U;
     uint64_t i = threadIdx.x;
     for (; i + (uint64_t)blockDim.x * (U - 1) < nvec; i += stride) {
@@ -422,6 +423,8 @@ template <typename T, int OP> __device__ __forceinline__ void ReduceRanksTo(KCtx
 {
     const char *slots[kMaxRanks];
     for (int r = 0; r < k.nranks; ++r) slots[r] = k.PeerHeap(r) + srcOff;
+    for (int r = 0; r < k.nranks; ++r) if (!HCCL_RANGE_OK(slots[r], bytes)) return;
+    for (int d = 0; d < ndst; ++d) if (!HCCL_RANGE_OK(dsts[d], bytes)) return;
     using Ac = typename Acc<T>::type;
     constexpr int VE = 16 / sizeof(T);
     const uint64_t nvec = bytes >> 4;

@@ -279,9 +279,25 @@ __device__ __forceinline__ bool HeapRangeOk(const void *p, uint64_t n)
     }
     return true;    // user memory: extent unknown to the library
 }
-#define HCCL_CHECK_RANGE(dst, src, n) if (!HeapRangeOk(dst, n) || !HeapRangeOk(src, n)) return
+// the same rule for an address inside the multicast mapping of all heaps
+__device__ __forceinline__ bool McRangeOk(const void *p, uint64_t n)
+{
+    const DevComm *c = g_boundsComm;
+    if (!c || !c->mcHeap) return true;
+    const char *b = (const char *)p;
+    if (b < c->mcHeap || b >= c->mcHeap + c->heapBytes) return true;
+    if (b + n <= c->mcHeap + c->heapBytes) return true;
+    DevStatus *s = c->status;
+    s->rank = (uint32_t)c->rank; s->peer = 0xffu; s->phase = 901; s->observed = (uint32_t)((b - c->mcHeap) >> 10); s->expected = (uint32_t)(c->heapBytes >> 10);
+    __threadfence_system();
+    *((volatile uint32_t *)&s->code) = 2u;
+    return false;
+}
+#define HCCL_CHECK_RANGE(dst, src, n) if (!::hccl::dev::HeapRangeOk(dst, n) || !::hccl::dev::HeapRangeOk(src, n)) return
+#define HCCL_RANGE_OK(p, n) (::hccl::dev::HeapRangeOk(p, n) && ::hccl::dev::McRangeOk(p, n))
 #else
 #define HCCL_CHECK_RANGE(dst, src, n)
+#define HCCL_RANGE_OK(p, n) true
 #endif
 
 // Copies `n` bytes with all threads of the CTA. Any alignment; 16-byte vectors when both sides allow it.
@@ -332,6 +348,8 @@ __device__ __forceinline__ void ReduceSlots(T *out, T *out2, const char *const *
 {
     using A = typename Acc<T>::type;
     constexpr int VE = 16 / sizeof(T);
+    for (int r = 0; r < nslots; ++r) if (!HCCL_RANGE_OK(slotBase[r], nElems * sizeof(T))) return;
+    if (!HCCL_RANGE_OK(out, nElems * sizeof(T)) || (out2 && !HCCL_RANGE_OK(out2, nElems * sizeof(T)))) return;
     bool vecOk = (((uintptr_t)out | (uintptr_t)out2) & 15u) == 0;
     uint64_t nvec = vecOk ? nElems / VE : 0;
     for (uint64_t i = threadIdx.x; i < nvec; i += blockDim.x) {

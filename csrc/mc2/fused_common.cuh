@@ -35,6 +35,9 @@ __device__ __forceinline__ void FusedInit(const GemmParams &p, FusedCtx &x)
     x.heap = x.c->heap[x.rank];
     x.ctrl = CtrlOf(x.heap);
     x.flags = FlagsOf(x.heap);
+#ifdef HCCL_DEBUG_BOUNDS
+    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) dev::g_boundsComm = x.c;
+#endif
     if (threadIdx.x == 0) {
         uint32_t oc = dev::LdVolatile(&x.ctrl->opCount);
         sHalf = oc & 1u;

@@ -28,6 +28,12 @@
 #include <cuda_bf16.h>
 #include "sm100_ptx.cuh"
 
+// Debug flavor: stores through peer pointers are range-checked when the including file brought the collective primitives in
+// (the fused operators); the plain GEMM writes only caller memory.
+#ifndef HCCL_RANGE_OK
+#define HCCL_RANGE_OK(p, n) true
+#endif
+
 namespace hccl {
 namespace mc2 {
 
@@ -298,7 +304,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) GemmKernel(const __grid_const
                     for (uint32_t i = et; i < (uint32_t)kBM * CH; i += 128) {
                         const uint32_t r = i / CH, ch = i % CH;
                         __nv_bfloat16 *dst = Policy::RowDst(p, ctx, mb * kBM + r, nb * BN + pass * SC + ch * 8);
-                        if (dst) *(uint4 *)dst = stg[r * CH + (ch ^ (r & 7))];
+                        if (dst && HCCL_RANGE_OK(dst, 16)) *(uint4 *)dst = stg[r * CH + (ch ^ (r & 7))];
                     }
                     asm volatile("bar.sync 1, 128;" ::: "memory");
                 }

@@ -215,7 +215,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) GemmKernelMx(const __grid_con
                     for (uint32_t i = et; i < (uint32_t)kBM * CH; i += 128) {
                         const uint32_t r = i / CH, ch = i % CH;
                         __nv_bfloat16 *dst = Policy::RowDst(p, ctx, mb * kBM + r, nb * BN + pass * SC + ch * 8);
-                        if (dst) *(uint4 *)dst = stg[r * CH + (ch ^ (r & 7))];
+                        if (dst && HCCL_RANGE_OK(dst, 16)) *(uint4 *)dst = stg[r * CH + (ch ^ (r & 7))];
                     }
                     asm volatile("bar.sync 1, 128;" ::: "memory");
                 }

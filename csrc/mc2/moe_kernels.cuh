@@ -33,6 +33,9 @@ struct MoeArgs {
 __device__ __forceinline__ KCtx MoeEnter(const DevComm *c, uint32_t chan)
 {
     KCtx k;
+#ifdef HCCL_DEBUG_BOUNDS
+    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) g_boundsComm = c;
+#endif
     k.c = c; k.rank = c->rank; k.nranks = c->nranks; k.heap = c->heap[c->rank];
     k.ctrl = CtrlOf(k.heap); k.flags = FlagsOf(k.heap);
     k.half = 0; k.chan = chan; k.syncs = 0; k.ok = true; k.vGrid = gridDim.x; k.vBlock = blockIdx.x; k.cclShift = 0; k.seq = 0xffffffffu;   // not counted by the op counter: no trace record
@@ -148,6 +151,7 @@ __global__ void __launch_bounds__(kMoeThreads) MoeDispatchKernel(const DevComm *
             const uint32_t e = (uint32_t)A.topkIdx[i], t = i / A.K, d = e / EL;
             const uint32_t row = baseSend[e] + sCtaBase[e] + pos[i];
             char *dws = c->heap[d] + A.wsOff;
+            if (!HCCL_RANGE_OK(dws + A.L.recvX + (uint64_t)row * (A.mxfp8 ? A.H : rowBytes), A.mxfp8 ? A.H : rowBytes)) continue;
             const uint4 *src = (const uint4 *)((const char *)A.x + (uint64_t)t * rowBytes);
             if (!A.mxfp8) {
                 uint4 *dst = (uint4 *)(dws + A.L.recvX + (uint64_t)row * rowBytes);

@@ -70,11 +70,25 @@ def main():
     ap.add_argument("--max-bytes", type=int, default=1 << 30)
     ap.add_argument("--json", default="")
     ap.add_argument("--skip-nccl", action="store_true")
+    ap.add_argument("--registered", action="store_true",
+                    help="buffers of this library's calls are registered windows of the symmetric heap (zero-copy kernels from 1 MB up); "
+                         "set HCCL_SYM_HEAP_MB large enough for the biggest size")
     args = ap.parse_args()
     dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0))))
     comm = init_from_env()
     rank, n = comm.rank, comm.size
     rows = []
+    windows = []
+
+    def like_registered(t):
+        """A registered window with t's contents (or t itself without --registered)."""
+        if not args.registered:
+            return t
+        w = comm.sym_tensor(t.numel(), t.dtype)
+        w.copy_(t)
+        windows.append(w)
+        return w
+
     for op in args.ops.split(","):
         for dname in args.dtypes.split(","):
             dtype = DT[dname]
@@ -88,24 +102,28 @@ def main():
                 if op == "allreduce":
                     x = (torch.rand(cnt, generator=g, device="cuda") * 2 - 1).to(dtype)
                     y = torch.empty_like(x)
-                    ours = lambda: comm.all_reduce(x, y)
+                    xo, yo = like_registered(x), like_registered(y)
+                    ours = lambda: comm.all_reduce(xo, yo)
                     ref = lambda: dist.all_reduce(y)
                     factor = 2 * (n - 1) / n
                 elif op == "allgather":
                     x = (torch.rand(cnt, generator=g, device="cuda") * 2 - 1).to(dtype)
                     y = torch.empty(cnt * n, dtype=dtype, device="cuda")
-                    ours = lambda: comm.all_gather(x, y)
+                    yo = like_registered(y)
+                    ours = lambda: comm.all_gather(x, yo)
                     ref = lambda: dist.all_gather_into_tensor(y, x)
                     factor = (n - 1) / n * n   # size counts the per-rank message; bytes received = size * (n-1)
                 elif op == "reducescatter":
                     x = (torch.rand(cnt * n, generator=g, device="cuda") * 2 - 1).to(dtype)
                     y = torch.empty(cnt, dtype=dtype, device="cuda")
-                    ours = lambda: comm.reduce_scatter(x, y)
+                    xo = like_registered(x)
+                    ours = lambda: comm.reduce_scatter(xo, y)
                     ref = lambda: dist.reduce_scatter_tensor(y, x)
                     factor = (n - 1) / n * n
                 elif op == "broadcast":
                     x = (torch.rand(cnt, generator=g, device="cuda") * 2 - 1).to(dtype)
-                    ours = lambda: comm.broadcast(x, 0)
+                    xo = like_registered(x)
+                    ours = lambda: comm.broadcast(xo, 0)
                     ref = lambda: dist.broadcast(x, 0)
                     factor = 1.0
                 elif op == "alltoall":
@@ -128,6 +146,8 @@ def main():
                     print(f"{op:13s} {dname:5s} {size:>11d} B  ours {t_ours*1e6:9.1f} us {bus_ours:8.1f} GB/s | nccl {t_ref*1e6:9.1f} us {bus_ref:8.1f} GB/s"
                           f" | x{bus_ours / bus_ref if bus_ref == bus_ref else float('nan'):.2f} | host {HOST_US.get('ours', 0):.1f} us (native {nat_us:.1f}) {alg_used}", flush=True)
                 del x
+                while windows:
+                    comm.sym_free(windows.pop())          # reverse order of allocation, the same on every rank
                 size *= 4 if size >= (1 << 22) and args.max_bytes > (1 << 28) else 2
                 idx += 1
     if rank == 0 and args.json:

@@ -80,6 +80,29 @@ def main():
         contrib[order] = back
         return (contrib.view(T, K, H).float() * weights.unsqueeze(-1)).sum(1).to(torch.bfloat16)
 
+    # MXFP8 dispatch baseline: a separate quantisation pass (1 x 32 blocks, e8m0 scales, OCP rule) written with torch ops, payload and
+    # scales in two all-to-alls, bf16 on the way back (the experts' output stands in as a persistent bf16 buffer, as on the fused side)
+    HB = H // 32
+    back_src = torch.zeros(sum(out_sp), H, dtype=torch.bfloat16, device="cuda")
+
+    def baseline_mx():
+        send = x[tok_of[order]]
+        v = send.float().view(-1, HB, 32)
+        e = (v.abs().amax(dim=2).view(torch.int32) >> 23) & 0xFF
+        se = (e - 8).clamp(0, 254)
+        inv = ((254 - se) << 23).to(torch.int32).view(torch.float32)
+        q = (v * inv.unsqueeze(2)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(torch.uint8).view(-1, H)
+        sc = se.to(torch.uint8)
+        recv_q = torch.empty(sum(out_sp), H, dtype=torch.uint8, device="cuda")
+        recv_s = torch.empty(sum(out_sp), HB, dtype=torch.uint8, device="cuda")
+        dist.all_to_all_single(recv_q, q, out_sp, in_sp)
+        dist.all_to_all_single(recv_s, sc, out_sp, in_sp)
+        back = torch.empty_like(send)
+        dist.all_to_all_single(back, back_src, in_sp, out_sp)
+        contrib = torch.empty(T * K, H, dtype=torch.bfloat16, device="cuda")
+        contrib[order] = back
+        return (contrib.view(T, K, H).float() * weights.unsqueeze(-1)).sum(1).to(torch.bfloat16)
+
     def timed(f, it):
         for _ in range(3):
             f()
@@ -102,11 +125,15 @@ def main():
         if not ok:
             print(f"[rank {rank}] MISMATCH fused vs baseline: rel err {err}", flush=True)
     t_f = timed(fused_comm_only, args.iters)
-    t_b = timed(baseline, args.iters)
-    moved = T * K * H * 2 * (n - 1) / n * 2     # bytes leaving + returning per rank (bf16)
+    t_b = timed(baseline_mx if args.mxfp8 else baseline, args.iters)
+    out_bytes = (1 + 1 / 32) if args.mxfp8 else 2                       # dispatch: e4m3 + one scale byte per 32, or bf16
+    moved = T * K * H * (out_bytes + 2) * (n - 1) / n                   # bytes leaving + returning per rank (uniform-routing estimate)
+    load = torch.tensor([float(sum(out_sp))], device="cuda")
+    dist.all_reduce(load, op=dist.ReduceOp.MAX)
     if rank == 0:
         res = dict(ranks=n, tokens=T, hidden=H, experts=E, topk=K, mxfp8=args.mxfp8, fused_ms=round(t_f, 4), nccl_torch_ms=round(t_b, 4),
-                   speedup=round(t_b / t_f, 3), fused_GBs_per_rank=round(moved / (t_f * 1e-3) / 1e9, 1), results_match=ok)
+                   speedup=round(t_b / t_f, 3), fused_GBs_per_rank=round(moved / (t_f * 1e-3) / 1e9, 1), results_match=ok,
+                   routing="N(0,1) logits + Zipf(1.1)-shaped expert bias", busiest_rank_rows_over_mean=round(load.item() / (T * K), 3))
         print(json.dumps(res), flush=True)
         if args.json:
             with open(args.json, "w") as f:

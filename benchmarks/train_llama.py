@@ -55,7 +55,8 @@ class TorchDistComm:
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--parallel", choices=["tp", "dp"], default="tp")
-    ap.add_argument("--impl", choices=["ours", "nccl"], default="ours")
+    ap.add_argument("--impl", choices=["ours", "ours-ddp", "nccl"], default="ours",
+                    help="ours-ddp (data parallel only): torch DistributedDataParallel over this library's process-group backend")
     ap.add_argument("--model", choices=["llama3-8b", "small", "tiny"], default="llama3-8b")
     ap.add_argument("--layers", type=int, default=0, help="override the number of layers (reported in the config)")
     ap.add_argument("--seq", type=int, default=4096)
@@ -63,6 +64,8 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--bucket-mb", type=float, default=32.0)
+    ap.add_argument("--staged-buckets", action="store_true", help="data parallel, --impl ours: keep the gradient buckets in ordinary device "
+                    "memory instead of registered windows (set HCCL_SYM_HEAP_MB above the gradient size for registered buckets)")
     a = ap.parse_args()
 
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
@@ -80,21 +83,29 @@ def main():
     dp = world // tp
 
     from hccl_b200.comm import Communicator, get_root_info, init_from_env
+    if a.impl == "ours-ddp" and a.parallel != "dp":
+        raise SystemExit("--impl ours-ddp needs --parallel dp")
+    native = a.impl != "nccl"
     world_comm = init_from_env() if a.impl == "ours" else None
     if a.parallel == "tp":
-        comm = world_comm if a.impl == "ours" else TorchDistComm()
+        comm = world_comm if native else TorchDistComm()
     else:
-        comm = Communicator.from_root_info(1, get_root_info(), 0) if a.impl == "ours" else TorchDistComm(solo=True)
+        comm = Communicator.from_root_info(1, get_root_info(), 0) if native else TorchDistComm(solo=True)
 
     from hccl_b200.parallel import tensor_parallel
-    tensor_parallel.use_native_gemm(a.impl == "ours")
+    tensor_parallel.use_native_gemm(native)
     model = Llama(cfg, comm, dtype=torch.bfloat16, device=dev, seed=None)
     opt = torch.optim.AdamW(model.parameters(), lr=1e-4, weight_decay=0.1, fused=True)
     dpw = None
     if a.parallel == "dp" and world > 1:
         if a.impl == "ours":
             from hccl_b200.parallel.data_parallel import DataParallel
-            dpw = DataParallel(model, world_comm, bucket_mb=a.bucket_mb)
+            dpw = DataParallel(model, world_comm, bucket_mb=a.bucket_mb, registered=not a.staged_buckets)
+        elif a.impl == "ours-ddp":
+            import hccl_b200.parallel  # noqa: F401  (registers the "hccl" backend)
+            grp = dist.new_group(backend="hccl")
+            model = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local], bucket_cap_mb=a.bucket_mb, gradient_as_bucket_view=True,
+                                                              process_group=grp)
         else:
             model = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local], bucket_cap_mb=a.bucket_mb, gradient_as_bucket_view=True)
 
@@ -138,6 +149,8 @@ def main():
     if world_comm is not None:
         torch.cuda.synchronize()
         dist.barrier()
+        if dpw is not None:
+            dpw.close()
         world_comm.destroy()
     dist.destroy_process_group()
 

@@ -3,6 +3,7 @@
 // (reference: src/common/hcomm_dlsym/hccl_host_comm_dl.h:43-58, hccl_res_dl.h:73-118, hccl_rank_graph_dl.h:38-49,
 // hccl_res_expt_dl.h:25-27; the stubs its own tests use: test/stub/hccl_stub.cc:43-88); here they read the structures
 // the communicator already keeps.
+#include <atomic>
 #include <cstring>
 #include "../common/env_config.h"
 #include "../common/log.h"
@@ -112,6 +113,50 @@ HcclResult HcclCommMemDereg(HcclComm comm, void *addr)
     Comm *c = Live(comm);
     if (!c || !addr) return HCCL_E_PTR;
     return CommDeregisterWindow(c, addr);
+}
+
+HcclResult HcclMemAlloc(HcclComm comm, uint64_t bytes, void **ptr)
+{
+    Comm *c = Live(comm);
+    if (!c || !ptr) return HCCL_E_PTR;
+    CHK_RET(SymAlloc(c, bytes, ptr));
+    uint64_t off = 0;
+    HcclResult r = CommRegisterWindow(c, *ptr, bytes, &off);
+    if (r != HCCL_SUCCESS) { SymFree(c, *ptr); *ptr = nullptr; }
+    return r;
+}
+
+HcclResult HcclMemFree(HcclComm comm, void *ptr)
+{
+    Comm *c = Live(comm);
+    if (!c || !ptr) return HCCL_E_PTR;
+    return SymFree(c, ptr);          // windows inside the block go with it
+}
+
+// ---- allocator hooks: one attached communicator per process, looked up by handle on every call so that a hook that runs
+// after the communicator's destruction (a framework's pool releasing its segments at exit) does nothing.
+static std::atomic<void *> g_allocatorComm{nullptr};
+
+HcclResult HcclSetAllocatorComm(HcclComm comm)
+{
+    if (comm && !Live(comm)) return HCCL_E_PTR;
+    g_allocatorComm.store(comm);
+    return HCCL_SUCCESS;
+}
+
+void *HcclAllocHook(long long bytes, int device, void * /*stream*/)
+{
+    Comm *c = CommFromHandle(g_allocatorComm.load());
+    if (!c || bytes <= 0) return nullptr;
+    if (c->backend == BackendKind::CUDA && device != c->device) { HCCL_ERROR("HcclAllocHook: device %d is not the communicator's device %d", device, c->device); return nullptr; }
+    void *p = nullptr;
+    return HcclMemAlloc(c, (uint64_t)bytes, &p) == HCCL_SUCCESS ? p : nullptr;
+}
+
+void HcclFreeHook(void *ptr, long long /*bytes*/, int /*device*/, void * /*stream*/)
+{
+    Comm *c = CommFromHandle(g_allocatorComm.load());
+    if (c && ptr) SymFree(c, ptr);
 }
 
 HcclResult HcclRankGraphGetLayers(HcclComm comm, uint32_t *numLayers)

@@ -303,6 +303,35 @@ class Communicator:
         the allocation: every rank frees in the same order."""
         check(lib().HcclCommSymFree(self._h, ctypes.c_void_p(tensor._hccl_sym_ptr)), "HcclCommSymFree")
 
+    def mem_alloc(self, nbytes: int) -> int:
+        """Address of a fresh registered block of the symmetric heap (HcclMemAlloc); same calling rules as sym_tensor."""
+        ptr = ctypes.c_void_p()
+        fn = lib().HcclMemAlloc
+        fn.argtypes = [ctypes.c_void_p, ctypes.c_uint64, ctypes.POINTER(ctypes.c_void_p)]
+        check(fn(self._h, nbytes, ctypes.byref(ptr)), "HcclMemAlloc")
+        return ptr.value
+
+    def mem_free(self, ptr: int) -> None:
+        check(lib().HcclMemFree(self._h, ctypes.c_void_p(ptr)), "HcclMemFree")
+
+    def mem_pool(self):
+        """A torch.cuda.MemPool whose segments are registered blocks of this communicator's symmetric heap:
+
+            pool = comm.mem_pool()
+            with torch.cuda.use_mem_pool(pool):
+                grads = torch.empty(n, dtype=torch.bfloat16, device="cuda")     # every rank, same order
+            comm.all_reduce(grads, grads)            # runs on the window directly, no staging copy
+
+        One communicator per process can serve the hooks at a time. Every rank has to make the same allocations in the same
+        order inside the pool (segments are cut from the heap by a deterministic first-fit), as with NCCL's registered pools.
+        Keep the pool alive as long as tensors from it are."""
+        import torch
+        from ._lib import LIB_PATH
+
+        check(lib().HcclSetAllocatorComm(self._h), "HcclSetAllocatorComm")
+        alloc = torch.cuda.memory.CUDAPluggableAllocator(str(LIB_PATH), "HcclAllocHook", "HcclFreeHook")
+        return torch.cuda.MemPool(alloc.allocator())
+
     def last_algorithm(self) -> str:
         """Name of the algorithm the most recent operator ran with."""
         class Rec(ctypes.Structure):

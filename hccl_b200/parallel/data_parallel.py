@@ -19,10 +19,14 @@ import torch.nn as nn
 
 
 class _Bucket:
-    def __init__(self, params: List[nn.Parameter], dtype, device):
+    def __init__(self, params: List[nn.Parameter], dtype, device, comm=None):
         self.params = params
         self.numel = sum(p.numel() for p in params)
-        self.flat = torch.zeros(self.numel, dtype=dtype, device=device)
+        if comm is not None:                                 # a registered window of the symmetric heap: reduced in place by the
+            self.flat = comm.sym_tensor(self.numel, dtype)   # zero-copy kernels, no staging through the scratch buffer
+            self.flat.zero_()
+        else:
+            self.flat = torch.zeros(self.numel, dtype=dtype, device=device)
         self.offsets = []
         off = 0
         for p in params:
@@ -35,7 +39,10 @@ class _Bucket:
 class DataParallel:
     """Wrap a module's parameters: `dp = DataParallel(model, comm)`; after `loss.backward()` call `dp.finish()`."""
 
-    def __init__(self, module: nn.Module, comm, *, bucket_mb: float = 32.0, grad_dtype: Optional[torch.dtype] = None, average: bool = True):
+    def __init__(self, module: nn.Module, comm, *, bucket_mb: float = 32.0, grad_dtype: Optional[torch.dtype] = None, average: bool = True,
+                 registered: Optional[bool] = None):
+        """`registered`: keep the buckets in registered windows of the communicator's symmetric heap (default: on CUDA with more
+        than one rank). Every rank builds the same buckets in the same order, which is what symmetric allocation asks for."""
         self.comm, self.average = comm, average
         params = [p for p in module.parameters() if p.requires_grad]
         if not params:
@@ -45,16 +52,18 @@ class DataParallel:
         self.stream = torch.cuda.Stream(device=self.device) if self.cuda else None
         dtype = grad_dtype or params[0].dtype
         cap = int(bucket_mb * (1 << 20)) // torch.empty(0, dtype=dtype).element_size()
+        self.registered = (self.cuda and comm.size > 1) if registered is None else bool(registered)
+        win = comm if self.registered else None
         self.buckets: List[_Bucket] = []
         cur, cur_n = [], 0
         for p in reversed(params):
             if cur and cur_n + p.numel() > cap:
-                self.buckets.append(_Bucket(cur, dtype, self.device))
+                self.buckets.append(_Bucket(cur, dtype, self.device, win))
                 cur, cur_n = [], 0
             cur.append(p)
             cur_n += p.numel()
         if cur:
-            self.buckets.append(_Bucket(cur, dtype, self.device))
+            self.buckets.append(_Bucket(cur, dtype, self.device, win))
         self._where = {}
         for b in self.buckets:
             for i, p in enumerate(b.params):
@@ -101,3 +110,11 @@ class DataParallel:
                 if p.grad is not None:
                     p.grad.copy_(b.flat[off:off + p.numel()].reshape(p.grad.shape))
             b.pending = len(b.params)
+
+    def close(self) -> None:
+        """Returns registered buckets to the heap (reverse order of allocation; call it on every rank, before the communicator
+        is destroyed). Buckets in ordinary device memory need no call."""
+        if self.registered:
+            for b in reversed(self.buckets):
+                self.comm.sym_free(b.flat)
+            self.registered = False

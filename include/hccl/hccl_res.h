@@ -41,6 +41,19 @@ HcclResult HcclEngineCtxDestroy(HcclComm comm, const char *tag);
 HcclResult HcclCommMemReg(HcclComm comm, void *addr, uint64_t size, uint64_t *windowOffset);
 HcclResult HcclCommMemDereg(HcclComm comm, void *addr);
 
+/* HcclMemAlloc = HcclCommSymAlloc + HcclCommMemReg of the whole block; HcclMemFree drops the window and returns the block.
+ * Collective in the same sense as HcclCommSymAlloc: every rank issues the same sequence of calls (no communication happens).
+ *
+ * Allocator hooks for frameworks that take a pair of C functions (e.g. torch.cuda.memory.CUDAPluggableAllocator):
+ * HcclSetAllocatorComm names the communicator whose heap serves the hooks (NULL detaches; destroying that communicator
+ * detaches too); HcclAllocHook returns NULL when no communicator is attached, it lives on another device, or its heap is
+ * full; HcclFreeHook ignores pointers whose communicator is gone (the heap went with it). */
+HcclResult HcclMemAlloc(HcclComm comm, uint64_t bytes, void **ptr);
+HcclResult HcclMemFree(HcclComm comm, void *ptr);
+HcclResult HcclSetAllocatorComm(HcclComm comm);
+void *HcclAllocHook(long long bytes, int device, void *stream);
+void HcclFreeHook(void *ptr, long long bytes, int device, void *stream);
+
 /* ---- rank graph (topology as layers of fully connected groups) ---------------------------------------------------- */
 typedef enum { HCCL_TOPO_CLOS = 0, HCCL_TOPO_MESH_1D = 1, HCCL_TOPO_MESH_1D_CLOS = 2, HCCL_TOPO_NVSWITCH = 3 } HcclTopoType;
 typedef enum { HCCL_LINK_NONE = 0, HCCL_LINK_NVLINK = 1, HCCL_LINK_PCIE = 2, HCCL_LINK_SHM = 3, HCCL_LINK_NET = 4 } HcclLinkType;

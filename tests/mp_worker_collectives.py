@@ -147,6 +147,30 @@ def main():
     comm.all_to_all_vc(send, M, recv)
     torch.cuda.synchronize()
     check("alltoallvc", torch.equal(recv[:want.numel()], want))
+    # a rank that sends nothing, a rank that receives nothing, one pair above half of the scratch window
+    half = (int(os.environ.get("HCCL_BUFFSIZE", "200")) << 20) // 2
+    big = half // 4 + 4096                             # fp32 elements: a little more than half of the scratch window
+    M = [[1000 * ((i + 2 * j) % 3) + i + 1 for j in range(world)] for i in range(world)]
+    M[0][world - 1] = big
+    if world > 2:                                      # with two ranks a zero row and a zero column would leave nothing to move
+        for j in range(world):
+            M[1][j] = 0
+            M[j][2 if world > 3 else 1] = 0
+    else:
+        M[1] = [0, 0]
+    send = gen(rank, max(1, sum(M[rank])), torch.float32, salt=19)
+    rc = [M[j][rank] for j in range(world)]
+    recv = torch.full((max(1, sum(rc)),), -3.0, dtype=torch.float32, device="cuda")
+    comm.all_to_all_v(send, M[rank], [sum(M[rank][:j]) for j in range(world)], recv, rc, [sum(rc[:j]) for j in range(world)])
+    torch.cuda.synchronize()
+    parts = [gen(j, max(1, sum(M[j])), torch.float32, salt=19)[sum(M[j][:rank]):sum(M[j][:rank]) + M[j][rank]] for j in range(world)]
+    want = torch.cat(parts)
+    check("alltoallv zero row / column / large pair", torch.equal(recv[:want.numel()], want) and bool(torch.all(recv[want.numel():] == -3.0)))
+    recv.fill_(-3.0)
+    comm.all_to_all_vc(send, M, recv)
+    torch.cuda.synchronize()
+    check("alltoallvc zero row / column / large pair", torch.equal(recv[:want.numel()], want))
+    del send, recv, parts, want
     # send / recv ring, then batch
     n = 700_000
     x = gen(rank, n, torch.float32, salt=11)
@@ -203,6 +227,18 @@ def main():
     check("small payload stays staged", not comm.last_algorithm().endswith("ZeroCopy"))
     comm.sym_free(win_out)
     comm.sym_free(win_in)
+    # tensors from a torch memory pool whose segments are registered blocks of the heap: plain torch code, zero-copy kernels
+    pool = comm.mem_pool()
+    with torch.cuda.use_mem_pool(pool):
+        pg_in = torch.empty(zn, dtype=torch.float32, device="cuda")
+        pg_out = torch.empty(zn, dtype=torch.float32, device="cuda")
+    pg_in.copy_(gen(rank, zn, torch.float32, salt=47))
+    comm.all_reduce(pg_in, pg_out)
+    torch.cuda.synchronize()
+    check(f"pool tensors are registered windows ({comm.last_algorithm()})", zc_ok("AllReduceZeroCopy"))
+    check("pool tensors allreduce", close(pg_out, ref_reduce(world, zn, torch.float32, ReduceOp.SUM, salt=47), torch.float32, world))
+    del pg_in, pg_out
+    del pool                                                  # segments go back to the heap through the free hook
     comm.barrier()
     torch.cuda.synchronize()
     check("async error clean", comm.async_error() == 0)

@@ -178,6 +178,30 @@ def test_alltoall_and_v(emu_mod):
                 ro += M[j][i]
 
 
+def test_alltoallv_zero_row_zero_column_and_pairs_above_the_scratch_half(emu_mod):
+    """One rank sends nothing, one rank receives nothing, and some pairs carry more than half of the scratch window
+    (64 KB window here, pairs of up to 100 KB), so the kernel has to loop over credit rounds with uneven pair lengths."""
+    nranks = 4
+    M = [[(5000 * ((i + 2 * j) % 4) + 17 * (i + 1)) for j in range(nranks)] for i in range(nranks)]
+    M[0][3] = 25_000                                   # 100 KB of fp32 in one pair
+    M[3][0] = 1
+    for j in range(nranks):
+        M[1][j] = 0                                    # rank 1 sends nothing
+        M[j][2] = 0                                    # rank 2 receives nothing
+    with emu_mod.EmuWorld(nranks, 64 << 10) as w:
+        sends = [_rand(max(1, sum(M[i])), torch.float32, 140 + i) for i in range(nranks)]
+        recvs = [torch.full((max(1, sum(M[j][i] for j in range(nranks))),), -7.0, dtype=torch.float32, device="cuda") for i in range(nranks)]
+        flat = [v for row in M for v in row]
+        assert w.run(CMD["ALLTOALLV"], "SmAlltoAllVMesh1D", sends, recvs, 0, torch.float32, counts=flat) == 0
+        for i in range(nranks):
+            ro = 0
+            for j in range(nranks):
+                so = sum(M[j][:i])
+                assert torch.equal(recvs[i][ro:ro + M[j][i]], sends[j][so:so + M[j][i]]), (i, j)
+                ro += M[j][i]
+        assert torch.all(recvs[2] == -7.0)             # nothing was written to the rank that receives nothing
+
+
 def test_allgatherv_reducescatterv(emu_mod):
     nranks = 4
     counts = [100, 0, 1025, 33]

@@ -44,3 +44,9 @@ def test_fused_matmul_collectives_two_or_more_gpus():
     n = min(torch.cuda.device_count(), 8)
     n = 8 if n >= 8 else 4 if n >= 4 else 2
     _run(n, {}, 29655, worker="mp_worker_fused.py", expect="all fused multi-GPU checks passed")
+
+
+def test_data_parallel_two_or_more_gpus():
+    """Bucketed gradient all-reduce on real GPUs: registered buckets (zero-copy, in place) and ordinary buckets (staged)."""
+    n = min(torch.cuda.device_count(), 4)
+    _run(n, {}, 29671, worker="mp_worker_dp.py", expect="data-parallel checks passed")

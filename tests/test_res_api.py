@@ -29,6 +29,13 @@ def _decl():
     l.HcclEngineCtxDestroy.argtypes = [vp, ctypes.c_char_p]
     l.HcclCommMemReg.argtypes = [vp, vp, u64, ctypes.POINTER(u64)]
     l.HcclCommMemDereg.argtypes = [vp, vp]
+    l.HcclMemAlloc.argtypes = [vp, u64, ctypes.POINTER(vp)]
+    l.HcclMemFree.argtypes = [vp, vp]
+    l.HcclSetAllocatorComm.argtypes = [vp]
+    l.HcclAllocHook.argtypes = [ctypes.c_longlong, ctypes.c_int, vp]
+    l.HcclAllocHook.restype = vp
+    l.HcclFreeHook.argtypes = [vp, ctypes.c_longlong, ctypes.c_int, vp]
+    l.HcclFreeHook.restype = None
     l.HcclRankGraphGetLayers.argtypes = [vp, ctypes.POINTER(u32)]
     l.HcclRankGraphGetRanksByLayer.argtypes = [vp, u32, ctypes.POINTER(u32), ctypes.POINTER(u32)]
     l.HcclRankGraphGetInstSizeListByLayer.argtypes = [vp, u32, ctypes.POINTER(u32), ctypes.POINTER(u32)]
@@ -130,6 +137,40 @@ def test_registered_window_lifetime():
     res = run_ranks(3, body)
     assert len({r[0] for r in res}) == 1 and len({r[1] for r in res}) == 1 and res[0][0] != res[0][1]
     assert all(r[2] == 6.0 for r in res)
+
+
+def test_mem_alloc_is_a_registered_block_and_allocator_hooks_follow_the_attached_communicator():
+    l = _decl()
+
+    def body(comm, rank):
+        h = vp(comm.handle)
+        a, off = vp(), u64()
+        assert l.HcclMemAlloc(h, 3000, ctypes.byref(a)) == 0
+        assert l.HcclCommMemReg(h, a, 3000, ctypes.byref(off)) == 0            # already a window: registering again is fine
+        first = off.value
+        assert l.HcclMemFree(h, a) == 0
+        assert l.HcclCommMemDereg(h, a) == Result.E_NOT_FOUND                   # the window went with the block
+        assert l.HcclMemFree(h, a) == Result.E_NOT_FOUND
+        if rank != 0:
+            return first, None
+        # allocator hooks: nothing attached -> NULL; attached -> registered blocks from that communicator's heap
+        assert l.HcclSetAllocatorComm(None) == 0
+        assert l.HcclAllocHook(4096, 0, None) is None
+        assert l.HcclSetAllocatorComm(h) == 0
+        p1, p2 = l.HcclAllocHook(4096, 0, None), l.HcclAllocHook(1 << 20, 0, None)
+        assert p1 and p2 and p1 != p2
+        assert l.HcclCommMemReg(h, vp(p2), 1 << 20, ctypes.byref(off)) == 0 and off.value > first
+        l.HcclFreeHook(vp(p1), 4096, 0, None)
+        assert l.HcclAllocHook(4096, 0, None) == p1                             # first fit: the freed block comes back
+        assert l.HcclAllocHook(1 << 40, 0, None) is None                        # heap exhausted -> NULL, not an exception
+        return first, p2
+
+    res = run_ranks(2, body)
+    assert res[0][0] == res[1][0]
+    # the attached communicator is gone: the hooks do nothing and hand out nothing
+    l.HcclFreeHook(vp(res[0][1]), 1 << 20, 0, None)
+    assert l.HcclAllocHook(4096, 0, None) is None
+    assert l.HcclSetAllocatorComm(vp(12345)) == Result.E_PTR
 
 
 def test_rank_graph_flat_and_exchange_info():

@@ -166,6 +166,39 @@ def test_variable_count_ops(nranks):
         assert np.array_equal(o4, rsv_want[vdis[r]:vdis[r] + vcnt[r]])
 
 
+@pytest.mark.parametrize("nranks", [3, 4])
+def test_alltoallv_zero_row_zero_column_and_pairs_above_the_scratch_half(nranks):
+    """A rank that sends nothing, a rank that receives nothing, and pairs larger than half of a 1 MB scratch window."""
+    dtype = np.int32
+    M = [[4000 * ((i + 2 * j) % 3) + 7 * (i + 1) for j in range(nranks)] for i in range(nranks)]
+    M[0][nranks - 1] = 160_000                         # 640 KB in one pair
+    M[nranks - 1][0] = 1
+    for j in range(nranks):
+        M[1][j] = 0
+        M[j][2] = 0
+    send = [np.arange(max(1, sum(M[r])), dtype=dtype) + 1_000_000 * r for r in range(nranks)]
+
+    def body(comm, rank):
+        sc = M[rank]
+        sd = list(np.cumsum([0] + sc[:-1]))
+        rc = [M[s][rank] for s in range(nranks)]
+        rd = list(np.cumsum([0] + rc[:-1]))
+        o1 = np.full(max(1, sum(rc)), -1, dtype)
+        comm.all_to_all_v(send[rank], sc, sd, o1, rc, rd)
+        o2 = np.full(max(1, sum(rc)), -1, dtype)
+        comm.all_to_all_vc(send[rank], M, o2)
+        comm.synchronize()
+        return o1, o2, sum(rc)
+
+    res = run_ranks(nranks, body, buffer_mb=1)
+    for r, (o1, o2, total) in enumerate(res):
+        pieces = [send[s][sum(M[s][:r]):sum(M[s][:r]) + M[s][r]] for s in range(nranks)]
+        want = np.concatenate(pieces)
+        assert want.size == total
+        assert np.array_equal(o1[:total], want) and np.array_equal(o2[:total], want)
+        assert np.all(o1[total:] == -1) and np.all(o2[total:] == -1)
+
+
 @pytest.mark.parametrize("nranks", [2, 4, 5])
 def test_point_to_point_and_batch(nranks):
     count = 3001

@@ -166,7 +166,7 @@ def main():
     x = sub.add_parser("mxgemm")
     x.add_argument("--m", type=int, default=8192); x.add_argument("--n", type=int, default=8192); x.add_argument("--k", type=int, default=4096)
     x.add_argument("--iters", type=int, default=10); x.add_argument("--flush", action="store_true"); x.add_argument("--no-cublas", action="store_true")
-    x.add_argument("--variant", type=int, default=0, help="tile width: 0 auto, 128, 256")
+    x.add_argument("--variant", type=int, default=0, help="tile width: 0 auto, 128, 192, 256")
     r = sub.add_parser("emu-allreduce")
     r.add_argument("--ranks", type=int, default=4); r.add_argument("--mb", type=int, default=64); r.add_argument("--dtype", default="fp32")
     r.add_argument("--alg", default="SmAllReduceMesh1DTwoShot"); r.add_argument("--ctas", type=int, default=32); r.add_argument("--iters", type=int, default=5)

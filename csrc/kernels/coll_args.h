@@ -49,7 +49,7 @@ enum SmKernelId : uint32_t {
 
 constexpr int kP2pBlocks = kP2pCtas;  // CTAs per point-to-point transfer; each owns 1/8 of a mailbox slot
 constexpr int kMaxBatchItems = 24;
-constexpr uint64_t kA2aMetaBytes = 128 << 10;   // tail of the CCL half reserved for AlltoAllV offsets
+constexpr uint64_t kA2aMetaBytes = 4 << 10;     // tail of the CCL half reserved for the AlltoAllV round counts (one word per channel)
 
 struct CollArgs {
     const void *in;
@@ -72,6 +72,8 @@ struct CollArgs {
     uint32_t pad1;
     // zero-copy kernels: heap offsets of the registered input / output windows (identical on every rank)
     uint64_t inOff, outOff;
+    // AlltoAll(V): bytes of the scratch slot each (source, destination) pair owns (identical on every rank, a multiple of 128)
+    uint64_t slotBytes;
 };
 
 struct BatchItem {

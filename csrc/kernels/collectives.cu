@@ -447,57 +447,82 @@ template <bool EMU> __device__ void ScatterBody(KCtx &k, const CollArgs &A)
 // ================================================================================================ AlltoAll(V/VC), pull
 // Sender packs the segment for each peer into its own scratch and publishes the packed offsets (one copy per
 // channel, so a channel barrier orders it); receivers pull their segment.
+// Every pair (src -> dst) owns a fixed slot of A.slotBytes in src's scratch, at the position of dst among src's peers, so a
+// receiver knows where to pull from without asking. A pair longer than its slot moves in rounds (stage, barrier, pull,
+// barrier); the number of rounds has to be the same on every rank, so each rank publishes the rounds its own row and column
+// need and all take the maximum. Nothing here depends on the payload fitting the scratch window.
 template <bool EMU> __device__ void AlltoAllVBody(KCtx &k, const CollArgs &A)
 {
     const int n = k.nranks;
-    uint64_t *meta = (uint64_t *)(k.Ccl(k.rank) + k.c->cclBytes - kA2aMetaBytes) + (uint64_t)k.chan * kMaxRanks;
-    uint64_t po = 0;
+    const uint64_t Q = A.slotBytes;
+    uint64_t *meta = (uint64_t *)(k.Ccl(k.rank) + k.c->cclBytes - kA2aMetaBytes) + k.chan;
+    uint64_t myRounds = 0;
     for (int r = 0; r < n; ++r) {
         if (r == k.rank) continue;
-        Part p = PartOf(A.sendBytes[r], gridDim.x, blockIdx.x);
-        BlockCopy(k.Ccl(k.rank) + po + p.off, (const char *)A.in + A.sendOff[r] + p.off, p.len);
-        if (threadIdx.x == 0) meta[r] = po;
-        po += Up128(A.sendBytes[r]);
+        const uint64_t m = A.sendBytes[r] > A.recvBytes[r] ? A.sendBytes[r] : A.recvBytes[r];
+        const uint64_t need = (m + Q - 1) / Q;
+        myRounds = need > myRounds ? need : myRounds;
     }
+    if (threadIdx.x == 0) *(volatile uint64_t *)meta = myRounds;             // visible to the peers after the first barrier
+    {
+        Part p = PartOf(A.sendBytes[k.rank], gridDim.x, blockIdx.x);
+        BlockCopy((char *)A.out + A.recvOff[k.rank] + p.off, (const char *)A.in + A.sendOff[k.rank] + p.off, p.len);
+    }
+    auto stage = [&](uint64_t t) {
+        for (int r = 0; r < n; ++r) {
+            if (r == k.rank) continue;
+            Part p = PartOfRound(A.sendBytes[r], Q, t, gridDim.x, blockIdx.x);
+            BlockCopy(k.Ccl(k.rank) + (uint64_t)(r < k.rank ? r : r - 1) * Q + p.off, (const char *)A.in + A.sendOff[r] + t * Q + p.off, p.len);
+        }
+    };
+    stage(0);
     if (!ChannelBarrier(k, 1)) return;
-    // where each peer staged this rank's block: all n - 1 remote reads in flight at once
-    __shared__ uint64_t peerOff[kMaxRanks];
+    __shared__ unsigned long long rounds;
+    if (threadIdx.x == 0) rounds = myRounds;
+    __syncthreads();
     if ((int)threadIdx.x < n && (int)threadIdx.x != k.rank) {
-        const uint64_t *peerMeta = (const uint64_t *)(k.Ccl((int)threadIdx.x) + k.c->cclBytes - kA2aMetaBytes) + (uint64_t)k.chan * kMaxRanks;
-        peerOff[threadIdx.x] = ((const volatile uint64_t *)peerMeta)[k.rank];
+        const uint64_t *peerMeta = (const uint64_t *)(k.Ccl((int)threadIdx.x) + k.c->cclBytes - kA2aMetaBytes) + k.chan;
+        atomicMax(&rounds, (unsigned long long)*(const volatile uint64_t *)peerMeta);
     }
     __syncthreads();
-    uint64_t maxLen = 0;
-    bool vec = (((uintptr_t)A.out) & 15u) == 0;
-    for (int r = 0; r < n; ++r) {
-        if (r == k.rank) continue;
-        Part p = PartOf(A.recvBytes[r], gridDim.x, blockIdx.x);
-        maxLen = p.len > maxLen ? p.len : maxLen;
-        vec = vec && ((p.len | p.off | A.recvOff[r] | peerOff[r]) & 15u) == 0;
-    }
-    if (vec && n <= kG && maxLen <= kGatherMaxBytes && HCCL_RANGE_OK(k.Ccl(k.rank), maxLen)) {
-        const uint4 *src[kG];
-        uint4 *dst[kG];
-        uint64_t nvec[kG];
+    const uint64_t R = rounds;
+    for (uint64_t t = 0; t < R; ++t) {
+        if (t > 0) {
+            stage(t);
+            if (!ChannelBarrier(k, 1)) return;
+        }
+        const uint64_t lo = t * Q;
+        uint64_t maxLen = 0;
+        bool vec = (((uintptr_t)A.out) & 15u) == 0 && n <= kG;
+        for (int r = 0; r < n; ++r) {
+            if (r == k.rank) continue;
+            Part p = PartOfRound(A.recvBytes[r], Q, t, gridDim.x, blockIdx.x);
+            maxLen = p.len > maxLen ? p.len : maxLen;
+            vec = vec && ((p.len | p.off | (A.recvOff[r] + lo)) & 15u) == 0;
+        }
+        if (vec && maxLen <= kGatherMaxBytes && HCCL_RANGE_OK(k.Ccl(k.rank), maxLen)) {
+            const uint4 *src[kG];
+            uint4 *dst[kG];
+            uint64_t nvec[kG];
 #pragma unroll
-        for (int d = 1; d < kG; ++d) {
-            if (d >= n) break;
-            const int r = (k.rank + d) % n;
-            Part p = PartOf(A.recvBytes[r], gridDim.x, blockIdx.x);
-            src[d - 1] = (const uint4 *)(k.Ccl(r) + peerOff[r] + p.off);
-            dst[d - 1] = (uint4 *)((char *)A.out + A.recvOff[r] + p.off);
-            nvec[d - 1] = p.len >> 4;
+            for (int d = 1; d < kG; ++d) {
+                if (d >= n) break;
+                const int r = (k.rank + d) % n;
+                Part p = PartOfRound(A.recvBytes[r], Q, t, gridDim.x, blockIdx.x);
+                src[d - 1] = (const uint4 *)(k.Ccl(r) + (uint64_t)(k.rank < r ? k.rank : k.rank - 1) * Q + p.off);
+                dst[d - 1] = (uint4 *)((char *)A.out + A.recvOff[r] + lo + p.off);
+                nvec[d - 1] = p.len >> 4;
+            }
+            GatherParts(src, dst, nvec, n - 1, maxLen >> 4);
+        } else {
+            for (int d = 1; d < n; ++d) {
+                const int r = (k.rank + d) % n;
+                Part p = PartOfRound(A.recvBytes[r], Q, t, gridDim.x, blockIdx.x);
+                BlockCopy((char *)A.out + A.recvOff[r] + lo + p.off, k.Ccl(r) + (uint64_t)(k.rank < r ? k.rank : k.rank - 1) * Q + p.off, p.len);
+            }
         }
-        GatherParts(src, dst, nvec, n - 1, maxLen >> 4);
-    } else {
-        for (int d = 1; d < n; ++d) {
-            int r = (k.rank + d) % n;
-            Part p = PartOf(A.recvBytes[r], gridDim.x, blockIdx.x);
-            BlockCopy((char *)A.out + A.recvOff[r] + p.off, k.Ccl(r) + peerOff[r] + p.off, p.len);
-        }
+        if (t + 1 < R && !ChannelBarrier(k, 2)) return;          // the slots are rewritten by the next round
     }
-    Part p = PartOf(A.sendBytes[k.rank], gridDim.x, blockIdx.x);
-    BlockCopy((char *)A.out + A.recvOff[k.rank] + p.off, (const char *)A.in + A.sendOff[k.rank] + p.off, p.len);
 }
 
 // ================================================================================================ zero-copy forms

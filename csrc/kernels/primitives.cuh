@@ -242,6 +242,21 @@ __device__ __forceinline__ Part PartOf(uint64_t total, uint32_t parts, uint32_t 
     return p;
 }
 
+// Part `b` of round `t` of a transfer of `total` bytes that moves through a slot of `slot` bytes per round. The split is
+// fixed by the first (longest) round, so a CTA touches the same byte range of the slot in every round and the per-CTA
+// barriers order its reuse.
+__device__ __forceinline__ Part PartOfRound(uint64_t total, uint64_t slot, uint64_t t, uint32_t parts, uint32_t b)
+{
+    const uint64_t first = total < slot ? total : slot;
+    const uint64_t per = ((first + parts - 1) / parts + 127) & ~127ull;
+    const uint64_t len = total <= t * slot ? 0 : (total - t * slot < slot ? total - t * slot : slot);
+    const uint64_t off = per * b;
+    Part p;
+    p.off = off < len ? off : len;
+    p.len = off < len ? (len - off < per ? len - off : per) : 0;
+    return p;
+}
+
 // ---------------------------------------------------------------------------------------------- copies
 template <int UNROLL> __device__ __forceinline__ void CopyVec16(uint4 *__restrict__ d, const uint4 *__restrict__ s, uint64_t nvec)
 {

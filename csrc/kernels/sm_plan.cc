@@ -273,38 +273,29 @@ HcclResult SmPlanOp(const SmPlanCtx &ctx, const OpParam &p, const std::string &a
             });
         });
     }
-    if (alg == "SmAlltoAllMesh1D") {
-        uint64_t usable = ccl > kA2aMetaBytes ? ccl - kA2aMetaBytes : 0;
-        return loop(p.count, Down128(usable / n) / es, [&](uint64_t lo, uint64_t cnt) {
-            push(K_ALLTOALL_V, lo, cnt, cnt * es * (n - 1), [&](SmLaunch &l) {
-                l.args.in = in;
-                l.args.out = outp;
-                for (uint32_t r = 0; r < n; ++r) {
-                    l.args.sendBytes[r] = l.args.recvBytes[r] = cnt * es;
-                    l.args.sendOff[r] = l.args.recvOff[r] = ((uint64_t)r * p.count + lo) * es;
-                }
-            });
-        });
-    }
-    if (alg == "SmAlltoAllVMesh1D" || alg == "SmAlltoAllVCMesh1D") {
-        uint32_t esOut = DataTypeSize(p.outDtype);
-        uint64_t packed = 0, moved = 0;
-        for (uint32_t r = 0; r < n; ++r) if (r != me) { packed += Up128(p.sendCounts[r] * es); moved += p.recvCounts[r] * esOut; }
-        if (packed + kA2aMetaBytes > ccl) {
-            HCCL_ERROR("AlltoAllV: this rank sends %llu bytes, more than the CCL buffer holds (%llu); raise HCCL_BUFFSIZE", (unsigned long long)packed,
-                       (unsigned long long)(ccl - kA2aMetaBytes));
-            return HCCL_E_MEMORY;
-        }
-        (void)moved;
-        push(K_ALLTOALL_V, 0, 0, 0, [&](SmLaunch &l) {
-            // the grid must be the same on every rank (channels synchronise pairwise across ranks), so it cannot depend
-            // on this rank's own counts
-            l.ctas = ctx.maxCtas ? std::min(16u, ctx.maxCtas) : 16u;
+    if (alg == "SmAlltoAllMesh1D" || alg == "SmAlltoAllVMesh1D" || alg == "SmAlltoAllVCMesh1D") {
+        // One launch for any payload: a pair longer than its scratch slot moves in rounds inside the kernel. The slot size and
+        // the grid are functions of the communicator only, so they agree on every rank whatever the count matrix is.
+        const bool fixed = alg == "SmAlltoAllMesh1D";
+        const uint32_t esOut = fixed ? es : DataTypeSize(p.outDtype);
+        const uint64_t usable = ccl > kA2aMetaBytes ? ccl - kA2aMetaBytes : 0;
+        const uint64_t slot = n > 1 ? Down128(usable / (n - 1)) : Down128(usable);
+        if (slot < 128) { HCCL_ERROR("AlltoAll: a CCL buffer of %llu bytes leaves no scratch slot per peer (%u ranks)", (unsigned long long)ccl, n); return HCCL_E_MEMORY; }
+        push(K_ALLTOALL_V, 0, fixed ? p.count : 0, fixed ? p.count * es * (n - 1) : 0, [&](SmLaunch &l) {
+            // the grid must be the same on every rank (channels synchronise pairwise across ranks), so the variable forms
+            // cannot size it from this rank's own counts
+            if (!fixed) l.ctas = ctx.maxCtas ? std::min(16u, ctx.maxCtas) : 16u;
             l.args.in = in;
             l.args.out = outp;
+            l.args.slotBytes = slot;
             for (uint32_t r = 0; r < n; ++r) {
-                l.args.sendBytes[r] = p.sendCounts[r] * es; l.args.sendOff[r] = p.sendDispls[r] * es;
-                l.args.recvBytes[r] = p.recvCounts[r] * esOut; l.args.recvOff[r] = p.recvDispls[r] * esOut;
+                if (fixed) {
+                    l.args.sendBytes[r] = l.args.recvBytes[r] = p.count * es;
+                    l.args.sendOff[r] = l.args.recvOff[r] = (uint64_t)r * p.count * es;
+                } else {
+                    l.args.sendBytes[r] = p.sendCounts[r] * es; l.args.sendOff[r] = p.sendDispls[r] * es;
+                    l.args.recvBytes[r] = p.recvCounts[r] * esOut; l.args.recvOff[r] = p.recvDispls[r] * esOut;
+                }
             }
         });
         return HCCL_SUCCESS;

@@ -13,7 +13,9 @@
 //     columns per atom, replicated over the four lane quarters); the four instructions pick their scale byte through
 //     the scale-factor ids of the instruction descriptor;
 //   * tensor memory: 256-wide tiles leave room for ONE accumulator next to the scale columns (the epilogue then does not
-//     overlap the next main loop), 128- and 64-wide tiles keep two.
+//     overlap the next main loop); 192- and 128-wide tiles keep two. A 192-wide tile starts at row 0 or row 64 of a scale
+//     atom of B: the producer fetches the two atoms it touches and the instructions address the scale columns 0 or 2
+//     columns in.
 // Scale arrays are [ceil(rows / 128)][K / 128][512 bytes] (K a multiple of 128); a quantiser that writes this layout is
 // in mx_quant.cu. HCCL has no counterpart (reference: include/hccl_mc2.h:25-82 only passes dtypes to external kernels).
 #pragma once
@@ -24,14 +26,15 @@ namespace mc2 {
 
 constexpr int kMxBK = 128;           // fp8 elements per stage row = 128 bytes = one swizzle row
 constexpr int kSfAtomBytes = 512;
+constexpr uint32_t kMxDefaultTileN = 256;     // tile width of the fused block-scaled operators unless HCCL_MX_TILE_N says otherwise
 
 template <int BN> struct GemmMxSmem {
-    static_assert(BN == 128 || BN == 256, "B tiles are whole 128-row scale atoms");
-    static constexpr int kAtomsB = BN / 128;
+    static_assert(BN == 128 || BN == 192 || BN == 256, "B tiles start on a 64-row boundary of the 128-row scale atoms");
+    static constexpr int kAtomsB = (BN + 127) / 128;                 // a 192-wide tile starts at row 0 or 64 of an atom: two atoms either way
     static constexpr int kABytes = kBM * kMxBK;
     static constexpr int kBBytes = BN * kMxBK;
     static constexpr int kSfBytes = (1 + kAtomsB) * kSfAtomBytes;
-    static constexpr int kStages = BN >= 256 ? 4 : 6;
+    static constexpr int kStages = BN >= 256 ? 4 : BN >= 192 ? 5 : 6;
     static constexpr int kRing = kStages * (kABytes + kBBytes);
     static constexpr int kSfOff = kRing;
     static constexpr int kStageCols = 64;
@@ -40,9 +43,9 @@ template <int BN> struct GemmMxSmem {
     static constexpr int kBarOff = kStagingOff + kStagingBytes;
     static constexpr int kTotal = kBarOff + 256;
     // tensor memory columns
-    static constexpr int kAccs = BN <= 128 ? 2 : 1;
+    static constexpr int kAccs = BN <= 192 ? 2 : 1;
     static constexpr int kSfCols = 4 + 4 * kAtomsB;                  // per stage: A atom, then B atoms
-    static constexpr int kSfColBase = 256;
+    static constexpr int kSfColBase = kAccs * BN <= 256 ? 256 : 384;
     static_assert(kAccs * BN <= kSfColBase && kSfColBase + kStages * kSfCols <= 512, "tensor memory layout");
     static_assert(kTotal + 1024 <= 232448, "shared memory budget");
 };
@@ -133,6 +136,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) GemmKernelMx(const __grid_con
             uint32_t stage = 0, phase = 0, acc = 0, accPhase = 0;
             bool ok = true;
             for (uint32_t t = cta; t < numTiles && ok; t += ctas) {
+                uint32_t mb, nb;
+                Policy::TileCoord(p, ctx, t, mBlocks, nBlocks, &mb, &nb);
+                // scale columns of B: 32 rows per column; a tile that starts at row 64 of its first atom starts 2 columns in
+                const uint32_t sfbCol = 4 + ((nb * BN) % 128) / 32;
                 ok = MbarWait(&tmemEmpty[acc], accPhase ^ 1, abortWord);
                 if (!ok) break;
                 TcFenceAfter();
@@ -150,7 +157,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) GemmKernelMx(const __grid_con
                     uint64_t bDesc = MakeSmemDescSw128(SmemAddr(sB + stage * S::kBBytes));
 #pragma unroll
                     for (uint32_t k = 0; k < kMxBK / 32; ++k)
-                        UmmaMxf8(dTmem, AdvanceDescK(aDesc, k * 32), AdvanceDescK(bDesc, k * 32), MakeInstrDescMx(kBM, BN, k), sfCol, sfCol + 4,
+                        UmmaMxf8(dTmem, AdvanceDescK(aDesc, k * 32), AdvanceDescK(bDesc, k * 32), MakeInstrDescMx(kBM, BN, k), sfCol, sfCol + sfbCol,
                                  (kb | k) != 0 ? 1u : 0u);
                     UmmaCommit(&empty[stage]);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }

@@ -105,12 +105,22 @@ uint32_t PairTileN(uint64_t rowPairs, uint64_t N, uint32_t pairs)
     return PairLevel() >= 2 && cost(224) < cost(256) ? 224u : 256u;
 }
 
-// Block-scaled form: a / b are e4m3 payloads, sfa / sfb their scale atoms; 256-wide tiles (128-wide for MatmulAllReduce).
+// Tile width of the block-scaled AllGatherMatmul / MatmulReduceScatter: 256 (one accumulator in tensor memory) or 192 (two, the
+// epilogue overlaps the next main loop). HCCL_MX_TILE_N overrides; read on every call so that tests can switch it.
+uint32_t MxTileN()
+{
+    const char *e = getenv("HCCL_MX_TILE_N");
+    const int v = e ? atoi(e) : 0;
+    return v == 192 ? 192u : v == 256 ? 256u : kMxDefaultTileN;
+}
+
+// Block-scaled form: a / b are e4m3 payloads, sfa / sfb their scale atoms; MxTileN()-wide tiles (128-wide for MatmulAllReduce).
 HcclResult BuildParamsMx(const FusedShape &s, char *heapLocal, uint64_t wsOff, const void *a, const void *sfa, const void *b, const void *sfb, void *out,
                          uint32_t commCtas, GemmParams *p)
 {
     memset(p, 0, sizeof(*p));
     const uint64_t half = WorkspaceHalfBytes(s);
+    const uint32_t bn = MxTileN();
     p->errorWord = GemmErrorWord();
     p->groupM = 16;
     p->elemBytes = 1;
@@ -124,15 +134,15 @@ HcclResult BuildParamsMx(const FusedShape &s, char *heapLocal, uint64_t wsOff, c
         CHK_RET(EncodeTmap2D(&p->tmapA, heapLocal + wsOff, p->M, s.K, s.K, kBM, kMxBK, 1));
         CHK_RET(EncodeTmap2D(&p->tmapA1, heapLocal + wsOff + half, p->M, s.K, s.K, kBM, kMxBK, 1));
         CHK_RET(EncodeTmap2D(&p->tmapALocal, a, s.m, s.K, s.K, kBM, kMxBK, 1));
-        CHK_RET(EncodeTmap2D(&p->tmapB, b, s.N, s.K, s.K, 256, kMxBK, 1));
+        CHK_RET(EncodeTmap2D(&p->tmapB, b, s.N, s.K, s.K, bn, kMxBK, 1));
         p->u64[0] = wsOff; p->u64[1] = half; p->u64[2] = (uint64_t)(uintptr_t)a; p->u64[3] = wsOff + payload; p->u64[5] = (uint64_t)(uintptr_t)sfa;
         p->u32[0] = (uint32_t)s.m; p->u32[1] = commCtas; p->u32[2] = (uint32_t)(s.m / kBM);
     } else if (s.kind == MMRS) {
         p->M = (uint32_t)s.m;
         CHK_RET(EncodeTmap2D(&p->tmapA, a, s.m, s.K, s.K, kBM, kMxBK, 1));
-        CHK_RET(EncodeTmap2D(&p->tmapB, b, s.N, s.K, s.K, 256, kMxBK, 1));
+        CHK_RET(EncodeTmap2D(&p->tmapB, b, s.N, s.K, s.K, bn, kMxBK, 1));
         p->u64[0] = wsOff; p->u64[1] = half;
-        p->u32[0] = (uint32_t)(s.m / s.n); p->u32[1] = (uint32_t)(s.m / s.n / kBM); p->u32[2] = (uint32_t)((s.N + 255) / 256);
+        p->u32[0] = (uint32_t)(s.m / s.n); p->u32[1] = (uint32_t)(s.m / s.n / kBM); p->u32[2] = (uint32_t)((s.N + bn - 1) / bn);
     } else {
         const uint32_t colsOwn = (uint32_t)(s.N / s.n);
         p->M = (uint32_t)s.m;
@@ -185,8 +195,9 @@ HcclResult BuildParams(const FusedShape &s, char *heapLocal, uint64_t wsOff, con
 uint32_t GridFor(const FusedShape &s, uint32_t commCtas, uint32_t maxCtas)
 {
     uint64_t tiles;
-    if (s.kind == AGMM) tiles = (s.n * s.m / kBM) * ((s.N + 255) / 256);
-    else if (s.kind == MMRS) tiles = ((s.m + kBM - 1) / kBM) * ((s.N + 255) / 256);
+    const uint64_t bn = s.mx ? MxTileN() : 256;
+    if (s.kind == AGMM) tiles = (s.n * s.m / kBM) * ((s.N + bn - 1) / bn);
+    else if (s.kind == MMRS) tiles = ((s.m + kBM - 1) / kBM) * ((s.N + bn - 1) / bn);
     else tiles = ((s.m + kBM - 1) / kBM) * (s.N / (s.mx ? 128 : 64));
     uint32_t g = (uint32_t)std::min<uint64_t>(tiles + commCtas, maxCtas);
     return std::max(g, commCtas + 1);
@@ -214,7 +225,11 @@ template <bool EMU> HcclResult LaunchFused(const FusedShape &s, const GemmParams
 {
     const void *fn = nullptr;
     size_t smem = 0;
-    if (s.mx) {
+    if (s.mx && s.kind != MMAR && MxTileN() == 192) {
+        if (s.kind == AGMM) { CHK_RET((SetSmemAttrMx<192, AgmmPolicy, EMU>())); fn = (const void *)GemmKernelMx<192, AgmmPolicy, EMU>; }
+        else { CHK_RET((SetSmemAttrMx<192, MmrsPolicy, EMU>())); fn = (const void *)GemmKernelMx<192, MmrsPolicy, EMU>; }
+        smem = GemmMxSmem<192>::kTotal + 1024;
+    } else if (s.mx) {
         if (s.kind == AGMM) { CHK_RET((SetSmemAttrMx<256, AgmmPolicy, EMU>())); fn = (const void *)GemmKernelMx<256, AgmmPolicy, EMU>; smem = GemmMxSmem<256>::kTotal + 1024; }
         else if (s.kind == MMRS) { CHK_RET((SetSmemAttrMx<256, MmrsPolicy, EMU>())); fn = (const void *)GemmKernelMx<256, MmrsPolicy, EMU>; smem = GemmMxSmem<256>::kTotal + 1024; }
         else { CHK_RET((SetSmemAttrMx<128, MmarPolicy, EMU>())); fn = (const void *)GemmKernelMx<128, MmarPolicy, EMU>; smem = GemmMxSmem<128>::kTotal + 1024; }
@@ -333,7 +348,7 @@ HcclResult RunFused(FusedKind kind, Comm *c, const void *a, const void *b, void 
     {
         std::lock_guard<std::mutex> lk(g_wsMu);
         auto &cache = g_ws[c].params;
-        ParamKey key{(int)kind + (int)pairBN + (s.mx ? 1000 : 0), a, b, out, m, N, K, wsOff, sfa, sfb};
+        ParamKey key{(int)kind + (int)pairBN + (s.mx ? 1000 + (int)MxTileN() : 0), a, b, out, m, N, K, wsOff, sfa, sfb};
         auto it = cache.find(key);
         if (it != cache.end()) p = it->second;
         else {

@@ -131,6 +131,12 @@ HcclResult HcclGemmMxfp8(const void *a, const void *sfa, const void *b, const vo
                    (unsigned long long)k);
         return HCCL_E_PARA;
     }
+    // HCCL_MX_TILE_N = 192 | 256 picks the wide tile of large products (as for the fused operators)
+    if (const char *e = getenv("HCCL_MX_TILE_N")) {
+        const int v = atoi(e);
+        const uint64_t tiles = ((m + 127) / 128) * ((n + (uint64_t)(v > 0 ? v : 256) - 1) / (uint64_t)(v > 0 ? v : 256));
+        if (v == 192 && tiles >= (uint64_t)SmCount()) return LaunchPlainMx<192>(a, sfa, b, sfb, c, (uint32_t)m, (uint32_t)n, (uint32_t)k, outFp32 != 0, stream);
+    }
     // 256-wide tiles (one accumulator) when they fill the GPU, 128-wide (two accumulators) otherwise
     uint64_t tiles256 = ((m + 127) / 128) * ((n + 255) / 256);
     if (tiles256 >= (uint64_t)SmCount()) return LaunchPlainMx<256>(a, sfa, b, sfb, c, (uint32_t)m, (uint32_t)n, (uint32_t)k, outFp32 != 0, stream);
@@ -143,6 +149,7 @@ HcclResult HcclGemmMxfp8Variant(const void *a, const void *sfa, const void *b, c
     if (!a || !sfa || !b || !sfb || !c) return HCCL_E_PTR;
     if (m == 0 || n == 0 || k == 0 || (k % 128) || (n % 8) || m > 0x7fffffff || n > 0x7fffffff || k > 0x7fffffff) return HCCL_E_PARA;
     if (tileN == 256) return LaunchPlainMx<256>(a, sfa, b, sfb, c, (uint32_t)m, (uint32_t)n, (uint32_t)k, outFp32 != 0, stream);
+    if (tileN == 192) return LaunchPlainMx<192>(a, sfa, b, sfb, c, (uint32_t)m, (uint32_t)n, (uint32_t)k, outFp32 != 0, stream);
     if (tileN == 128) return LaunchPlainMx<128>(a, sfa, b, sfb, c, (uint32_t)m, (uint32_t)n, (uint32_t)k, outFp32 != 0, stream);
     return HcclGemmMxfp8(a, sfa, b, sfb, c, m, n, k, outFp32, stream);
 }

@@ -372,31 +372,47 @@ void BroadcastZc(Model &m, bool nvls)
     }
 }
 
-// packed offset of the segment rank `src` holds for rank `dst` (what the kernel publishes in its metadata words)
-uint64_t PackedOffset(const CollArgs &srcArgs, uint32_t src, uint32_t dst, uint32_t n)
-{
-    uint64_t po = 0;
-    for (uint32_t r = 0; r < n && r < dst; ++r) if (r != src) po += Up128(srcArgs.sendBytes[r]);
-    return po;
-}
-
+// Fixed slot per (source, destination) pair, rounds of slotBytes, the same number of rounds on every rank (the kernel
+// takes the maximum over all ranks' rows and columns).
 void AlltoAllV(Model &m)
 {
     const CollArgs &A = m.A();
+    const uint64_t Q = A.slotBytes;
+    uint64_t R = 0;
+    for (uint32_t a = 0; a < m.n; ++a)
+        for (uint32_t r = 0; r < m.n; ++r)
+            if (r != a) R = std::max(R, (std::max(m.all[a].args.sendBytes[r], m.all[a].args.recvBytes[r]) + Q - 1) / Q);
+    auto slotOf = [&](uint32_t owner, uint32_t dst) { return (uint64_t)(dst < owner ? dst : dst - 1) * Q; };
+    // the kernel's PartOfRound: the first round of a pair fixes which bytes of the slot a channel owns
+    auto partAt = [&](uint64_t total, uint64_t t, uint32_t ch) {
+        const uint64_t first = std::min(total, Q), per = ((first + m.C - 1) / m.C + 127) & ~127ull;
+        const uint64_t len = total <= t * Q ? 0 : std::min(Q, total - t * Q), off = per * ch;
+        Part p;
+        p.off = off < len ? off : len;
+        p.len = off < len ? std::min(len - off, per) : 0;
+        return p;
+    };
     for (uint32_t ch = 0; ch < m.C; ++ch) {
-        for (uint32_t r = 0; r < m.n; ++r) {
-            if (r == m.me) continue;
-            Part p = PartOf(A.sendBytes[r], m.C, ch);
-            m.Copy(ch, Model::Ccl(PackedOffset(A, m.me, r, m.n) + p.off), m.In(A.sendOff[r] + p.off), p.len);
-        }
+        Part self = PartOf(A.sendBytes[m.me], m.C, ch);
+        m.Copy(ch, m.Out(A.recvOff[m.me] + self.off), m.In(A.sendOff[m.me] + self.off), self.len);
+        auto stage = [&](uint64_t t) {
+            for (uint32_t r = 0; r < m.n; ++r) {
+                if (r == m.me) continue;
+                Part p = partAt(A.sendBytes[r], t, ch);
+                m.Copy(ch, Model::Ccl(slotOf(m.me, r) + p.off), m.In(A.sendOff[r] + t * Q + p.off), p.len);
+            }
+        };
+        stage(0);
         m.Barrier(ch);
-        for (uint32_t d = 1; d < m.n; ++d) {
-            uint32_t r = (m.me + d) % m.n;
-            Part p = PartOf(A.recvBytes[r], m.C, ch);
-            m.Read(ch, m.Out(A.recvOff[r] + p.off), r, PackedOffset(m.all[r].args, r, m.me, m.n) + p.off, p.len);
+        for (uint64_t t = 0; t < R; ++t) {
+            if (t > 0) { stage(t); m.Barrier(ch); }
+            for (uint32_t d = 1; d < m.n; ++d) {
+                uint32_t r = (m.me + d) % m.n;
+                Part p = partAt(A.recvBytes[r], t, ch);
+                m.Read(ch, m.Out(A.recvOff[r] + t * Q + p.off), r, slotOf(r, m.me) + p.off, p.len);
+            }
+            if (t + 1 < R) m.Barrier(ch);
         }
-        Part p = PartOf(A.sendBytes[m.me], m.C, ch);
-        m.Copy(ch, m.Out(A.recvOff[m.me] + p.off), m.In(A.sendOff[m.me] + p.off), p.len);
     }
 }
 }  // namespace

@@ -40,7 +40,7 @@ class DataParallel:
     """Wrap a module's parameters: `dp = DataParallel(model, comm)`; after `loss.backward()` call `dp.finish()`."""
 
     def __init__(self, module: nn.Module, comm, *, bucket_mb: float = 32.0, grad_dtype: Optional[torch.dtype] = None, average: bool = True,
-                 registered: Optional[bool] = None):
+                 registered: Optional[bool] = None, grad_as_bucket_view: bool = True):
         """`registered`: keep the buckets in registered windows of the communicator's symmetric heap (default: on CUDA with more
         than one rank). Every rank builds the same buckets in the same order, which is what symmetric allocation asks for."""
         self.comm, self.average = comm, average
@@ -69,12 +69,17 @@ class DataParallel:
             for i, p in enumerate(b.params):
                 self._where[p] = (b, i)
                 p.register_post_accumulate_grad_hook(self._on_grad)
+                if grad_as_bucket_view and p.dtype == dtype:
+                    # autograd accumulates straight into the bucket (keep the views: zero_grad(set_to_none=False)); a gradient that
+                    # turns up elsewhere (set_to_none, another dtype) is copied in and out as without this option
+                    p.grad = b.flat[b.offsets[i]:b.offsets[i] + p.numel()].view(p.shape)
         self.launched = 0
 
     def _on_grad(self, p: nn.Parameter) -> None:
         b, i = self._where[p]
         off = b.offsets[i]
-        b.flat[off:off + p.numel()].copy_(p.grad.reshape(-1))
+        if p.grad.data_ptr() != b.flat.data_ptr() + off * b.flat.element_size():
+            b.flat[off:off + p.numel()].copy_(p.grad.reshape(-1))
         b.pending -= 1
         if b.pending == 0:
             self._launch(b)
@@ -107,7 +112,7 @@ class DataParallel:
             if self.average and self.comm.size > 1:
                 b.flat.div_(self.comm.size)
             for p, off in zip(b.params, b.offsets):
-                if p.grad is not None:
+                if p.grad is not None and p.grad.data_ptr() != b.flat.data_ptr() + off * b.flat.element_size():
                     p.grad.copy_(b.flat[off:off + p.numel()].reshape(p.grad.shape))
             b.pending = len(b.params)
 
@@ -116,5 +121,9 @@ class DataParallel:
         is destroyed). Buckets in ordinary device memory need no call."""
         if self.registered:
             for b in reversed(self.buckets):
+                lo, hi = b.flat.data_ptr(), b.flat.data_ptr() + b.numel * b.flat.element_size()
+                for p in b.params:                           # gradients that are views of the bucket would dangle
+                    if p.grad is not None and lo <= p.grad.data_ptr() < hi:
+                        p.grad = None
                 self.comm.sym_free(b.flat)
             self.registered = False

@@ -34,7 +34,7 @@ def main():
         m = model(dev)
         dp = DataParallel(m, comm, bucket_mb=bucket_mb, registered=registered)
         for step in range(3):                                # later steps reuse the buckets
-            m.zero_grad()
+            m.zero_grad(set_to_none=(step == 2))             # steps 0-1: gradients accumulate straight into the buckets; step 2: copied in
             ((m(x[rank * per:(rank + 1) * per]) - y[rank * per:(rank + 1) * per]) ** 2).mean().backward()
             dp.finish()
             torch.cuda.synchronize()

@@ -176,6 +176,18 @@ def test_sm_alltoallv_and_v_forms(nranks):
         cm[a * nranks + (a + 1) % nranks] = 0        # a zero row entry per sender
     rc, msg = check(CMD["ALLTOALLV"], "SmAlltoAllVMesh1D", (1, 1, nranks), 0, counts=cm, ccl=(1 << 20))
     assert rc == 0, msg
+    # a scratch window of 8 KB: 4 KB are reserved, the rest gives slots of at most 4 KB per pair, so pairs of up to 9000 fp32
+    # elements move in up to nine rounds; a zero row, a zero column, and the fixed-size form through the same kernel
+    big = [rng.choice([0, 7, 1500, 9000]) for _ in range(nranks * nranks)]
+    for j in range(nranks):
+        big[(1 % nranks) * nranks + j] = 0
+        big[j * nranks + (nranks - 1)] = 0
+    rc, msg = check(CMD["ALLTOALLV"], "SmAlltoAllVMesh1D", (1, 1, nranks), 0, counts=big, ccl=(8 << 10))
+    assert rc == 0, msg
+    rc, msg = check(CMD["ALLTOALL"], "SmAlltoAllMesh1D", (1, 1, nranks), 5000, ccl=(8 << 10))
+    assert rc == 0, msg
+    rc, msg = check(CMD["ALLTOALLV"], "SmAlltoAllVMesh1D", (1, 1, nranks), 0, counts=big, ccl=(4 << 10))
+    assert rc != 0                                     # no room for a slot: refused, not mis-scheduled
     counts = [rng.choice([0, 5, 129, 1000]) for _ in range(nranks)]
     rc, msg = check(CMD["ALLGATHER_V"], "SmAllGatherVMesh1D", (1, 1, nranks), 0, counts=counts, ccl=(1 << 20))
     assert rc == 0, msg

@@ -12,8 +12,9 @@ def _model():
     return nn.Sequential(nn.Linear(16, 64), nn.Tanh(), nn.Linear(64, 64), nn.Tanh(), nn.Linear(64, 4))
 
 
+@pytest.mark.parametrize("keep_views", [False, True], ids=["grads-copied", "grads-are-bucket-views"])
 @pytest.mark.parametrize("world", [2, 4])
-def test_bucketed_allreduce_matches_full_batch(world):
+def test_bucketed_allreduce_matches_full_batch(world, keep_views):
     torch.manual_seed(0)
     x, y = torch.randn(8 * world, 16), torch.randn(8 * world, 4)
     ref = _model()
@@ -31,7 +32,7 @@ def test_bucketed_allreduce_matches_full_batch(world):
         dp = DataParallel(m, comm, bucket_mb=0.01)          # tiny buckets: several launches per step
         outs = []
         for step in range(2):                                # the second step reuses the buckets
-            m.zero_grad()
+            m.zero_grad(set_to_none=not keep_views)          # kept: autograd accumulates straight into the buckets
             xs, ys = x[rank * 8:(rank + 1) * 8], y[rank * 8:(rank + 1) * 8]
             ((m(xs) - ys) ** 2).mean().backward()
             dp.finish()

@@ -39,7 +39,9 @@ def test_quantiser_matches_the_reference_rule(rows, k):
 
 
 @pytest.mark.parametrize("m,n,k,tile", [(128, 128, 128, 128), (128, 256, 256, 256), (256, 512, 1024, 128), (384, 768, 512, 256),
-                                        (200, 264, 384, 128), (200, 264, 384, 256), (1024, 1024, 2048, 0), (4096, 4096, 512, 0)])
+                                        (200, 264, 384, 128), (200, 264, 384, 256), (1024, 1024, 2048, 0), (4096, 4096, 512, 0),
+                                        # 192-wide tiles: odd tiles start at row 64 of a scale atom; partial last tiles; a single tile
+                                        (128, 192, 128, 192), (256, 384, 512, 192), (384, 960, 640, 192), (200, 264, 384, 192), (2048, 8192, 512, 192)])
 def test_block_scaled_gemm_matches_fp32_product_of_dequantised_operands(m, n, k, tile):
     from hccl_b200.ops import gemm as g, mxfp8 as mx
     a, w = mx.quantize(_wild((m, k), 1 + m)), mx.quantize(_wild((n, k), 2 + n, 0.05))
@@ -63,16 +65,18 @@ def test_block_scaled_gemm_every_scale_byte_is_used():
         w[(13 * kb + 5) % n, kb * 32:(kb + 1) * 32] *= 2.0 ** -(kb % 9)
     qa, qw = mx.quantize(a.to(torch.bfloat16)), mx.quantize(w.to(torch.bfloat16))
     ref = mx.dequantize(qa) @ mx.dequantize(qw).t()
-    for tile in (128, 256):
+    for tile in (128, 192, 256):
         out = mx.gemm(qa, qw, out_dtype=torch.float32, tile_n=tile)
         torch.cuda.synchronize()
         assert torch.allclose(out, ref, rtol=1e-4, atol=1e-3)
 
 
+@pytest.mark.parametrize("tile", [256, 192])
 @pytest.mark.parametrize("nranks,m_local,N,K", [(2, 128, 256, 256), (4, 256, 512, 512), (2, 384, 776, 1024)])
-def test_allgather_matmul_mxfp8(nranks, m_local, N, K):
+def test_allgather_matmul_mxfp8(nranks, m_local, N, K, tile, monkeypatch):
     from hccl_b200.ops import mxfp8 as mx
     from hccl_b200.utils import emu
+    monkeypatch.setenv("HCCL_MX_TILE_N", str(tile))
     ctas = 148 // nranks
     with emu.EmuWorld(nranks, 1 << 20, arena_bytes=(4 * nranks * m_local * K + (1 << 20))) as w:
         for it in range(3):
@@ -85,10 +89,12 @@ def test_allgather_matmul_mxfp8(nranks, m_local, N, K):
                 assert _rel(out[r], full @ mx.dequantize(b[r]).t()) < 1e-2
 
 
-@pytest.mark.parametrize("nranks,M,N,K", [(2, 256, 256, 256), (4, 512, 512, 384)])
-def test_matmul_reduce_scatter_mxfp8(nranks, M, N, K):
+@pytest.mark.parametrize("tile", [256, 192])
+@pytest.mark.parametrize("nranks,M,N,K", [(2, 256, 256, 256), (4, 512, 512, 384), (2, 512, 776, 256)])
+def test_matmul_reduce_scatter_mxfp8(nranks, M, N, K, tile, monkeypatch):
     from hccl_b200.ops import mxfp8 as mx
     from hccl_b200.utils import emu
+    monkeypatch.setenv("HCCL_MX_TILE_N", str(tile))
     ctas = 148 // nranks
     with emu.EmuWorld(nranks, 1 << 20, arena_bytes=(4 * M * N + (1 << 20))) as w:
         for it in range(2):

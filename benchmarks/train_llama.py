@@ -36,9 +36,15 @@ class TorchDistComm:
         self.rank = 0 if solo else dist.get_rank(group)
 
     def all_gather(self, send, recv, stream=None):
+        if self.size == 1:
+            recv.view(-1).copy_(send.view(-1))
+            return
         dist.all_gather_into_tensor(recv, send, group=self.group)
 
     def reduce_scatter(self, send, recv, op=None, stream=None):
+        if self.size == 1:
+            recv.view(-1).copy_(send.view(-1))
+            return
         dist.reduce_scatter_tensor(recv, send, group=self.group)
 
     def all_reduce(self, send, recv=None, op=None, stream=None):
@@ -46,6 +52,8 @@ class TorchDistComm:
         t = send if recv is None else recv
         if recv is not None and recv.data_ptr() != send.data_ptr():
             recv.copy_(send)
+        if self.size == 1:
+            return
         dist.all_reduce(t, op=dist.ReduceOp.MAX if op == ReduceOp.MAX else dist.ReduceOp.SUM, group=self.group)
 
     def synchronize(self):
@@ -96,7 +104,7 @@ def main():
     tensor_parallel.use_native_gemm(native)
     model = Llama(cfg, comm, dtype=torch.bfloat16, device=dev, seed=None)
     opt = torch.optim.AdamW(model.parameters(), lr=1e-4, weight_decay=0.1, fused=True)
-    dpw = None
+    dpw, grp = None, None
     if a.parallel == "dp" and world > 1:
         if a.impl == "ours":
             from hccl_b200.parallel.data_parallel import DataParallel
@@ -146,12 +154,17 @@ def main():
                           "params": cfg.param_count(), "seq": S, "micro_batch": B, "ms_per_step": round(ms.item(), 3), "tokens_per_s": round(tps, 1),
                           "model_tflops_per_gpu": round(cfg.flops_per_token(S) * tps / world / 1e12, 1), "loss": round(float(loss_host.item()), 4),
                           "h2d_bytes_per_step": host_tok[0].numel() * 8, "d2h_bytes_per_step": 4}), flush=True)
+    torch.cuda.synchronize()
+    dist.barrier()
     if world_comm is not None:
-        torch.cuda.synchronize()
-        dist.barrier()
         if dpw is not None:
             dpw.close()
         world_comm.destroy()
+    # the DistributedDataParallel wrapper keeps its process group alive: let go of it before the groups are destroyed, so that no
+    # communicator outlives the CUDA context at interpreter exit
+    del opt, model
+    if a.impl == "ours-ddp":
+        dist.destroy_process_group(grp)
     dist.destroy_process_group()
 
 

@@ -457,6 +457,20 @@ public:
     }
 };
 
+class IrParallelExecutor : public ExecutorBase {
+public:
+    HcclResult Orchestrate(Comm *c, OpParam &p) override
+    {
+        if (c->backend != BackendKind::SIM) {
+            HCCL_ERROR("%s: schedules with several queues run on the host engine only", algName_.c_str());
+            return HCCL_E_NOT_SUPPORT;
+        }
+        auto plan = std::make_shared<Plan>();
+        CHK_RET(GenParallelPlan(p, c->topo, c->devComm.cclBytes, plan.get()));
+        return RunPlan(c, p, plan, true);
+    }
+};
+
 // ------------------------------------------------------------------------------------------------ SM / NVLS executor
 class SmExecutor : public ExecutorBase {
 public:
@@ -488,6 +502,9 @@ void RegisterBuiltinExecutors()
         R.Register("InsAllReduceSequenceMesh1DNhr", HCCL_CMD_ALLREDUCE, [] { return static_cast<ExecutorBase *>(new IrSequenceExecutor()); });
         R.Register("InsAllGatherSequenceNhrMesh1D", HCCL_CMD_ALLGATHER, [] { return static_cast<ExecutorBase *>(new IrSequenceExecutor()); });
         R.Register("InsReduceScatterSequenceMesh1DNhr", HCCL_CMD_REDUCE_SCATTER, [] { return static_cast<ExecutorBase *>(new IrSequenceExecutor()); });
+        R.Register("InsAllReduceParallelMesh1DMesh1D", HCCL_CMD_ALLREDUCE, [] { return static_cast<ExecutorBase *>(new IrParallelExecutor()); });
+        R.Register("InsAllGatherParallelMesh1DMesh1D", HCCL_CMD_ALLGATHER, [] { return static_cast<ExecutorBase *>(new IrParallelExecutor()); });
+        R.Register("InsReduceScatterParallelMesh1DMesh1D", HCCL_CMD_REDUCE_SCATTER, [] { return static_cast<ExecutorBase *>(new IrParallelExecutor()); });
         for (const SmAlgoDesc &d : SmAlgorithms())
             R.Register(d.name, d.op, [] { return static_cast<ExecutorBase *>(new SmExecutor()); });
     });

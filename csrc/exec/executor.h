@@ -4,6 +4,8 @@
 // CalcRes / Orchestrate; registry src/ops/op_common/executor/registry/coll_alg_v2_exec_registry.h:33-42,71):
 //   Sole      one template on a flat rank list                         -> IrSoleExecutor, SmExecutor
 //   Sequence  level 0, then level 1 (, then level 2) one after another -> IrSequenceExecutor (simulated multi-server)
+//   Parallel  two shares of the data cross two levels in opposite orders, in pipelined steps -> IrParallelExecutor
+//             (HCCL's Parallel and OmniPipe executors; the cut comes from slice_planner.cc)
 //   P2P       send / recv / batch                                      -> P2pExecutor
 // All share the outer chunk loop: maxCountPerLoop = what the scratch window can hold for the chosen template,
 // iterate with a tail (reference: src/ops/all_reduce/executor/ins_v2_all_reduce_sole_executor.cc:125-176).
@@ -77,5 +79,8 @@ HcclResult GenBatchSendRecvPlan(uint32_t me, uint32_t nranks, const std::vector<
                                 Plan *p, std::vector<char *> *itemBufs);
 // Multi-level plan for AllReduce / AllGather / ReduceScatter (whole op, no chunk loop).
 HcclResult GenSequencePlan(const OpParam &p, const TopoInfo &topo, uint64_t cclBytes, Plan *plan);
+// Two-level plan with both levels busy at once (parallel_executor.cc); slices = the planner's decision, if asked for.
+struct SlicePlan;
+HcclResult GenParallelPlan(const OpParam &p, const TopoInfo &topo, uint64_t cclBytes, Plan *plan, SlicePlan *slices = nullptr);
 
 }  // namespace hccl

@@ -225,7 +225,14 @@ template <typename T, int OP, bool EMU, bool NVLS> __device__ void AllReduceBody
     __shared__ int sFail;
     const int n = k.nranks;
     const uint64_t slice = Up128((A.bytes + n - 1) / n);
-    Geo g = MakeGeo(k, A, PartOf(SliceLen(A.bytes, slice, 0), gridDim.x, blockIdx.x).len);
+    // The channel walks as many sub-chunks as its longest part needs. That is not always its part of the longest slice: a
+    // shorter last slice is cut with a smaller stride, which can leave the LAST channel a longer remainder than slice 0 does.
+    uint64_t longestPart = 0;
+    for (int j = 0; j < n; ++j) {
+        const uint64_t l = PartOf(SliceLen(A.bytes, slice, j), gridDim.x, blockIdx.x).len;
+        longestPart = l > longestPart ? l : longestPart;
+    }
+    Geo g = MakeGeo(k, A, longestPart);
     if (threadIdx.x == 0) sFail = 0;
     __syncthreads();
     const uint64_t resBase = g.RingBytes();
@@ -280,9 +287,12 @@ template <typename T, int OP, bool EMU, bool NVLS> __device__ void ReduceScatter
 {
     __shared__ int sFail;
     const int n = k.nranks;
-    uint64_t longest = 0;
-    for (int j = 0; j < n; ++j) longest = A.sendBytes[j] > longest ? A.sendBytes[j] : longest;
-    Geo g = MakeGeo(k, A, PartOf(longest, gridDim.x, blockIdx.x).len);
+    uint64_t longest = 0;                                       // this channel's longest part over all blocks (see AllReduceBody)
+    for (int j = 0; j < n; ++j) {
+        const uint64_t l = PartOf(A.sendBytes[j], gridDim.x, blockIdx.x).len;
+        longest = l > longest ? l : longest;
+    }
+    Geo g = MakeGeo(k, A, longest);
     if (threadIdx.x == 0) sFail = 0;
     __syncthreads();
     const int warp = threadIdx.x >> 5;
@@ -329,9 +339,12 @@ template <bool EMU, bool NVLS, bool A2A = false> __device__ void AllGatherBody(K
 {
     __shared__ int sFail;
     const int n = k.nranks;
-    uint64_t longest = 0;
-    for (int j = 0; j < n; ++j) longest = A.recvBytes[j] > longest ? A.recvBytes[j] : longest;
-    Geo g = MakeGeo(k, A, PartOf(longest, gridDim.x, blockIdx.x).len);
+    uint64_t longest = 0;                                       // this channel's longest part over all blocks (see AllReduceBody)
+    for (int j = 0; j < n; ++j) {
+        const uint64_t l = PartOf(A.recvBytes[j], gridDim.x, blockIdx.x).len;
+        longest = l > longest ? l : longest;
+    }
+    Geo g = MakeGeo(k, A, longest);
     if (threadIdx.x == 0) sFail = 0;
     __syncthreads();
     const int warp = threadIdx.x >> 5;

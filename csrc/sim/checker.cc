@@ -94,6 +94,7 @@ HcclResult CheckPlans(const CheckSpec &spec, const std::vector<std::vector<Plan>
         std::vector<std::vector<size_t>> pc(n, std::vector<size_t>(maxQ, 0));
         std::vector<std::vector<std::vector<uint32_t>>> clock(n, std::vector<std::vector<uint32_t>>(maxQ, std::vector<uint32_t>(lanes, 0)));
         std::map<std::tuple<uint32_t, uint32_t, uint32_t>, std::deque<std::vector<uint32_t>>> inflight;   // (dst, src, slot) -> clocks of pending posts
+        std::map<std::tuple<uint32_t, uint32_t, uint32_t>, std::deque<std::vector<uint32_t>>> localInflight;   // (rank, waiting queue, posting queue)
         std::vector<Access> accesses;
         size_t remaining = 0;
         for (auto &p : plans) remaining += p.TaskCount();
@@ -129,14 +130,22 @@ HcclResult CheckPlans(const CheckSpec &spec, const std::vector<std::vector<Plan>
                             if (it == inflight.end() || it->second.empty()) break;          // blocked
                             for (size_t i = 0; i < lanes; ++i) ck[i] = std::max(ck[i], it->second.front()[i]);
                             it->second.pop_front();
+                        } else if (t.type == TaskType::LOCAL_WAIT) {
+                            // notifies between the queues of one rank: (rank, waiting queue, posting queue)
+                            if (t.rank >= plans[r].queues.size() || t.rank == q) return fail("LOCAL_WAIT on an invalid queue at " + Where(r, q, pc[r][q], t));
+                            auto it = localInflight.find({r, (uint32_t)q, t.rank});
+                            if (it == localInflight.end() || it->second.empty()) break;     // blocked
+                            for (size_t i = 0; i < lanes; ++i) ck[i] = std::max(ck[i], it->second.front()[i]);
+                            it->second.pop_front();
                         }
                         ck[r * maxQ + q]++;
                         if (t.type == TaskType::POST) {
                             if (t.rank >= n || t.rank == r) return fail("POST to an invalid rank at " + Where(r, q, pc[r][q], t));
                             inflight[{t.rank, r, t.slot}].push_back(ck);
-                        } else if (t.type == TaskType::LOCAL_POST || t.type == TaskType::LOCAL_WAIT) {
-                            return fail("LOCAL_POST / LOCAL_WAIT are not used by the built-in templates: " + Where(r, q, pc[r][q], t));
-                        } else if (t.type != TaskType::WAIT) {
+                        } else if (t.type == TaskType::LOCAL_POST) {
+                            if (t.rank >= plans[r].queues.size() || t.rank == q) return fail("LOCAL_POST to an invalid queue at " + Where(r, q, pc[r][q], t));
+                            localInflight[{r, t.rank, (uint32_t)q}].push_back(ck);
+                        } else if (t.type != TaskType::WAIT && t.type != TaskType::LOCAL_WAIT) {
                             if (t.bytes % es) return fail("transfer is not a whole number of elements at " + Where(r, q, pc[r][q], t));
                             const bool remoteDst = t.type == TaskType::WRITE || t.type == TaskType::WRITE_REDUCE;
                             const bool remoteSrc = t.type == TaskType::READ || t.type == TaskType::READ_REDUCE;
@@ -182,6 +191,13 @@ HcclResult CheckPlans(const CheckSpec &spec, const std::vector<std::vector<Plan>
                 std::ostringstream os;
                 os << "chunk " << ci << ": " << kv.second.size() << " notify(s) from rank " << std::get<1>(kv.first) << " to rank " << std::get<0>(kv.first) << " slot "
                    << std::get<2>(kv.first) << " were never waited for";
+                return fail(os.str());
+            }
+        for (auto &kv : localInflight)
+            if (!kv.second.empty()) {
+                std::ostringstream os;
+                os << "chunk " << ci << ": rank " << std::get<0>(kv.first) << " queue " << std::get<2>(kv.first) << " posted " << kv.second.size()
+                   << " local notify(s) to queue " << std::get<1>(kv.first) << " that were never waited for";
                 return fail(os.str());
             }
         // memory conflicts (user INPUT / OUTPUT of different ranks never alias; the same rank's INPUT and OUTPUT are

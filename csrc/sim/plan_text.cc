@@ -5,6 +5,7 @@
 //   r<k>[.q<j>]: <task>; <task>; ...
 // tasks:  COPY dst src bytes | REDUCE dst src bytes | WRITE peer dst src bytes | WRITER peer dst src bytes (write-reduce)
 //         READ peer dst src bytes | READR peer dst src bytes (read-reduce) | POST peer slot | WAIT peer slot
+//         LPOST queue | LWAIT queue (notify another queue of the same rank / wait for its next notify)
 // buffers: in@<off> out@<off> ccl@<off> mbx@<off>. Lines starting with '#' are comments. All ranks share one chunk.
 #include <cstdlib>
 #include <sstream>
@@ -56,6 +57,11 @@ bool ParseTask(const std::string &text, Task *t, std::string *err)
         t->type = name == "POST" ? TaskType::POST : TaskType::WAIT;
         t->rank = (uint32_t)num(a[0]);
         t->slot = (uint32_t)num(a[1]);
+        return true;
+    }
+    if ((name == "LPOST" || name == "LWAIT") && a.size() == 1) {
+        t->type = name == "LPOST" ? TaskType::LOCAL_POST : TaskType::LOCAL_WAIT;
+        t->rank = (uint32_t)num(a[0]);
         return true;
     }
     *err = "cannot parse task '" + text + "'";

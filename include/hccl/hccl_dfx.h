@@ -63,6 +63,13 @@ HcclResult HcclCheckAlgorithm(HcclCMDType op, const char *algName, uint32_t supe
 /* The same checker for a schedule written as text (format: csrc/sim/plan_text.cc): "op=.. n=.. es=.. count=.. ccl=.." then one
  * line "r<k>[.q<j>]: TASK; TASK; ..." per rank queue. */
 HcclResult HcclCheckPlanText(const char *text, char *msg, uint32_t msgLen);
+
+/* The slice planner of the Parallel executors (two levels of the topology busy at once): how one rank's block of
+ * bytesPerRank is cut into a share that starts inside the server and one that starts between the servers, with the modelled
+ * completion times of the sequential and the parallel form. op: HCCL_CMD_ALLGATHER, HCCL_CMD_REDUCE_SCATTER or HCCL_CMD_ALLREDUCE
+ * (bytesPerRank = the whole vector). shareBytes / shareSteps: two entries, index = the level the share starts on (0 when absent). */
+HcclResult HcclPlanParallelSlices(HcclCMDType op, uint32_t ranksLevel0, double gbsLevel0, uint32_t ranksLevel1, double gbsLevel1, uint64_t bytesPerRank,
+                                  uint64_t shareBytes[2], uint32_t shareSteps[2], double *sequenceUs, double *parallelUs);
 /* Names registered for an op, ';' separated. */
 HcclResult HcclListAlgorithms(HcclCMDType op, char *buf, uint32_t bufLen);
 

@@ -253,8 +253,11 @@ def test_bounded_wait_reports_timeout(emu_mod):
 
 
 # ---- warp-specialised pipelined kernels (plain peer-memory variants; the NVLS variants need a real multicast mapping) ----
-@pytest.mark.parametrize("nranks,ccl_kb,ctas", [(2, 1024, 4), (4, 256, 4), (8, 256, 2), (3, 64, 3)])
-@pytest.mark.parametrize("count", [1, 37, 4099, 300_001])
+@pytest.mark.parametrize("nranks,ccl_kb,ctas,count", [(n, c, g, k) for (n, c, g) in [(2, 1024, 4), (4, 256, 4), (8, 256, 2), (3, 64, 3)] for k in [1, 37, 4099, 300_001]] +
+                         # 12 MB through 4 KB sub-chunks: 193 trips round the ring per channel; and the grid / scratch a 4-rank job with a 4 MB buffer gets
+                         [(4, 256, 4, (3 << 20) + 5), (4, 4096, 32, (3 << 20) + 5), (4, 2048, 32, (3 << 20) + 5),
+                          # counts where the last channel's part of the (shorter) last slice needs one sub-chunk more than its part of slice 0
+                          (4, 256, 4, 311_873), (3, 64, 3, 101_121)])
 def test_pipelined_allreduce(emu_mod, nranks, ccl_kb, ctas, count):
     """Small scratch + large count walks the ring many times (sub-chunks of a few KB), which exercises slot reuse."""
     with emu_mod.EmuWorld(nranks, ccl_kb << 10) as w:

@@ -1,0 +1,188 @@
+"""The Parallel executors (two levels of the topology busy at once) and their slice planner.
+
+Three layers of evidence: the planner's arithmetic, the schedule checker over the generated plans (deadlock, scratch bounds,
+unordered accesses between the queues and ranks, symbolic result), and real data on the host simulation backend with ranks
+laid out on pretended servers. Reference: the OmniPipe slice calculation and the Parallel executors
+(src/ops/op_common/omnipipe_data_slice_calc.cc, src/ops/all_reduce/executor/ins_v2_all_reduce_parallel_executor.cc)."""
+import ctypes
+
+import numpy as np
+import pytest
+
+from hccl_b200._lib import lib
+from hccl_b200.types import ReduceOp
+from hccl_b200.utils.sim import run_ranks
+
+CMD = {"ALLREDUCE": 2, "ALLGATHER": 6, "REDUCE_SCATTER": 7}
+
+
+def _cmd(name):
+    return CMD[name]
+
+
+def plan(op, n0, bw0, n1, bw1, nbytes):
+    l = lib()
+    l.HcclPlanParallelSlices.argtypes = [ctypes.c_int, ctypes.c_uint32, ctypes.c_double, ctypes.c_uint32, ctypes.c_double, ctypes.c_uint64,
+                                         ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint32), ctypes.POINTER(ctypes.c_double),
+                                         ctypes.POINTER(ctypes.c_double)]
+    sb, ss = (ctypes.c_uint64 * 2)(), (ctypes.c_uint32 * 2)()
+    seq, par = ctypes.c_double(), ctypes.c_double()
+    rc = l.HcclPlanParallelSlices(_cmd(op), n0, bw0, n1, bw1, nbytes, sb, ss, ctypes.byref(seq), ctypes.byref(par))
+    assert rc == 0
+    return list(sb), list(ss), seq.value, par.value
+
+
+def check(op, alg, topo, count, ccl=0):
+    l = lib()
+    buf = ctypes.create_string_buffer(1024)
+    l.HcclCheckAlgorithm.argtypes = [ctypes.c_int, ctypes.c_char_p, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint64, ctypes.c_int,
+                                     ctypes.c_uint32, ctypes.POINTER(ctypes.c_uint64), ctypes.c_uint64, ctypes.c_char_p, ctypes.c_uint32]
+    rc = l.HcclCheckAlgorithm(_cmd(op), alg.encode(), topo[0], topo[1], topo[2], count, 4, 0, None, ccl, buf, 1024)      # dtype 4 = fp32
+    return rc, buf.value.decode()
+
+
+# ---------------------------------------------------------------------------------------------------------------- planner
+@pytest.mark.parametrize("op", ["ALLGATHER", "REDUCE_SCATTER", "ALLREDUCE"])
+def test_planner_shares_cover_the_block_are_aligned_and_balance_the_levels(op):
+    nbytes = 64 << 20
+    shares, steps, seq, par = plan(op, 4, 200.0, 4, 100.0, nbytes)
+    assert sum(shares) == nbytes and all(b % 512 == 0 for b in shares)
+    assert shares[0] > 0 and shares[1] > 0 and all(1 <= s <= 4 for s in steps)
+    assert par < seq                                     # both levels busy beats one after the other
+    if op == "ALLGATHER":
+        # loads cross where 3 (4 - 3a) / 200 = 3 (1 + 3a) / 100: two ninths of the block start inside the server
+        assert abs(shares[0] / nbytes - 2 / 9) < 1e-3
+
+
+def test_planner_keeps_one_share_when_one_level_is_the_bottleneck_either_way():
+    """NVLink inside the server against a network 15 times slower: sending a block over the network once (first) beats every
+    mix, so there is one share; its steps still overlap the two levels."""
+    nbytes = 64 << 20
+    shares, steps, seq, par = plan("ALLGATHER", 8, 770.0, 4, 50.0, nbytes)
+    assert shares == [0, nbytes] and steps[1] == 4
+    assert par < 0.8 * seq
+
+
+def test_planner_follows_the_bandwidth_ratio():
+    nbytes = 32 << 20
+    a = plan("ALLGATHER", 4, 400.0, 4, 400.0, nbytes)[0]
+    b = plan("ALLGATHER", 4, 400.0, 4, 40.0, nbytes)[0]
+    assert abs(a[0] - a[1]) <= 1024                      # a symmetric grid is cut in the middle
+    assert b[1] > a[1]                                   # a slower level 1 sends more of the block through it FIRST (1 block instead of 4)
+
+
+def test_planner_degenerate_cases_keep_one_share():
+    for n0, n1 in ((1, 8), (8, 1)):
+        shares, steps, seq, par = plan("ALLREDUCE", n0, 770.0, n1, 50.0, 1 << 20)
+        assert sorted(shares) == [0, 1 << 20] and par == seq
+    shares, _, _, _ = plan("ALLGATHER", 4, 770.0, 2, 50.0, 600)      # less than two aligned pieces
+    assert sorted(shares) == [0, 600]
+
+
+# ---------------------------------------------------------------------------------------------------------------- checker
+@pytest.mark.parametrize("topo", [(1, 2, 2), (1, 2, 4), (1, 3, 2), (1, 4, 2), (1, 2, 8)])
+@pytest.mark.parametrize("op", ["ALLGATHER", "REDUCE_SCATTER", "ALLREDUCE"])
+def test_parallel_plans_pass_the_schedule_checker(op, topo):
+    alg = {"ALLGATHER": "InsAllGatherParallelMesh1DMesh1D", "REDUCE_SCATTER": "InsReduceScatterParallelMesh1DMesh1D", "ALLREDUCE": "InsAllReduceParallelMesh1DMesh1D"}[op]
+    big = 70_001 if topo[1] * topo[2] <= 8 else 40_001  # the checker tracks every element: keep the 16-rank case short
+    for count in (1, 1000, big):                        # one share only, two shares of one step, several steps with an odd tail
+        rc, msg = check(op, alg, topo, count, ccl=64 << 20)
+        assert rc == 0, (count, msg)
+
+
+def test_parallel_plan_reports_a_scratch_window_that_is_too_small():
+    rc, msg = check("ALLGATHER", "InsAllGatherParallelMesh1DMesh1D", (1, 2, 4), 300_000, ccl=1 << 20)
+    assert rc != 0
+
+
+def test_checker_orders_queues_of_one_rank_by_their_local_notifies():
+    l = lib()
+    l.HcclCheckPlanText.argtypes = [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_uint32]
+    buf = ctypes.create_string_buffer(512)
+    good = """op=6 n=2 es=4 count=4 ccl=4096
+r0: COPY ccl@0 in@0 16; LPOST 1
+r0.q1: LWAIT 0; POST 1 3; WAIT 1 3; READ 1 out@16 ccl@0 16; COPY out@0 in@0 16
+r1: COPY ccl@0 in@0 16; LPOST 1
+r1.q1: LWAIT 0; POST 0 3; WAIT 0 3; READ 0 out@0 ccl@0 16; COPY out@16 in@0 16
+"""
+    assert l.HcclCheckPlanText(good.encode(), buf, 512) == 0, buf.value
+    racy = good.replace("LWAIT 0; ", "").replace("; LPOST 1", "")          # queue 1 no longer waits for the staging copy of queue 0
+    assert l.HcclCheckPlanText(racy.encode(), buf, 512) != 0
+    assert b"not ordered" in buf.value
+    lost = good.replace("r0.q1: LWAIT 0; ", "r0.q1: ")                     # a local notify nobody waits for
+    assert l.HcclCheckPlanText(lost.encode(), buf, 512) != 0
+
+
+# ---------------------------------------------------------------------------------------------------------------- real data
+def _oracle(xs):
+    acc = xs[0].astype(np.float64)
+    for x in xs[1:]:
+        acc = acc + x
+    return acc
+
+
+@pytest.mark.parametrize("topo", ["1x2x2", "1x2x4@2,1", "1x3x2@0.8,0.6"])
+@pytest.mark.parametrize("forced", [True, False], ids=["by-name", "selected"])
+def test_two_level_operators_with_real_data(topo, forced, monkeypatch):
+    """Ranks as threads on pretended servers; the same calls once with the parallel executors named and once left to the selector,
+    which has to follow the planner: the parallel form where it is priced a tenth below the sequential one, else the sequence
+    executors. The bandwidth weights after '@' (GB/s) make the two levels comparable and slow enough that 1.2 MB is bandwidth-bound in the model."""
+    pods, servers, per = (int(v) for v in topo.split("@")[0].split("x"))
+    bw = [float(v) for v in topo.split("@")[1].split(",")] if "@" in topo else None
+    n = pods * servers * per
+    monkeypatch.setenv("HCCL_SIM_TOPO", topo)
+    if forced:
+        monkeypatch.setenv("HCCL_ALGO_NAME", "allreduce=InsAllReduceParallelMesh1DMesh1D;allgather=InsAllGatherParallelMesh1DMesh1D;"
+                                              "reducescatter=InsReduceScatterParallelMesh1DMesh1D")
+    lib().HcclResetEnvConfigForTest()
+    counts = (3, 5000, 300_001)
+    rng = np.random.default_rng(5)
+    ar_in = {c: [rng.integers(-8, 9, size=c).astype(np.float32) for _ in range(n)] for c in counts}
+    ag_in = {c: [rng.integers(-8, 9, size=c).astype(np.float32) for _ in range(n)] for c in counts}
+    rs_in = {c: [rng.integers(-8, 9, size=c * n).astype(np.float32) for _ in range(n)] for c in counts}
+
+    def body(comm, rank):
+        out, algs = {}, {}
+        for c in counts:
+            a = ar_in[c][rank].copy()
+            comm.all_reduce(a)                               # in place
+            comm.synchronize()
+            used = [comm.last_algorithm()]
+            g = np.empty(c * n, np.float32)
+            comm.all_gather(ag_in[c][rank], g)
+            comm.synchronize()
+            used.append(comm.last_algorithm())
+            s = np.empty(c, np.float32)
+            comm.reduce_scatter(rs_in[c][rank], s)
+            comm.synchronize()
+            used.append(comm.last_algorithm())
+            algs[c] = used
+            out[c] = (a, g, s)
+        return out, algs
+
+    try:
+        res = run_ranks(n, body, buffer_mb=64)
+    finally:
+        monkeypatch.delenv("HCCL_SIM_TOPO")
+        monkeypatch.delenv("HCCL_ALGO_NAME", raising=False)
+        lib().HcclResetEnvConfigForTest()
+    for c in counts:
+        want_ar = _oracle(ar_in[c])
+        want_ag = np.concatenate(ag_in[c])
+        want_rs = _oracle(rs_in[c])
+        for r, (out, algs) in enumerate(res):
+            a, g, s = out[c]
+            assert np.array_equal(a.astype(np.float64), want_ar), (c, r)
+            assert np.array_equal(g, want_ag), (c, r)
+            assert np.array_equal(s.astype(np.float64), want_rs[r * c:(r + 1) * c]), (c, r)
+    big, small = res[0][1][300_001], res[0][1][3]
+    if forced:
+        assert all("Parallel" in a for a in big + small)
+    else:
+        assert all("Sequence" in a for a in small)          # nothing to balance in twelve bytes
+        if bw:
+            for name, used, nbytes in zip(("ALLREDUCE", "ALLGATHER", "REDUCE_SCATTER"), big, (300_001 * 4,) * 3):
+                shares, steps, seq, par = plan(name, per, bw[0], servers, bw[1], nbytes)
+                gain = par < 0.9 * seq and (min(shares) > 0 or max(steps) > 1)
+                assert ("Parallel" in used) == gain, (name, used, shares, steps, seq, par)
+            assert any("Parallel" in a for a in big), big

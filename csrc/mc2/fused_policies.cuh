@@ -164,6 +164,13 @@ struct AgmmPolicy {
         if ((int)src == x.rank) return (const uint8_t *)p.u64[5] + (uint64_t)blk * blockSf;
         return (const uint8_t *)x.heap + p.u64[3] + (uint64_t)x.half * p.u64[1] + (uint64_t)mb * blockSf;
     }
+    // the same through tensor maps (CTA-pair kernel): the local scale array, or the gathered window of this parity half
+    __device__ static void SelectSfAMap(const GemmParams &p, const Ctx &x, uint32_t mb, const CUtensorMap **tm, int32_t *atomRow)
+    {
+        const uint32_t bpr = p.u32[2], src = mb / bpr, blk = mb % bpr;
+        if ((int)src == x.rank) { *tm = &p.tmapSfALocal; *atomRow = (int32_t)(blk * (p.K / 128)); }
+        else { *tm = x.half ? &p.tmapSfA1 : &p.tmapSfA; *atomRow = (int32_t)(mb * (p.K / 128)); }
+    }
     __device__ static bool UseDirect(const GemmParams &) { return false; }
     __device__ static void Store(const GemmParams &, const Ctx &, uint32_t, uint32_t, const uint32_t (&)[32]) {}
     __device__ static __nv_bfloat16 *RowDst(const GemmParams &p, const Ctx &, uint32_t row, uint32_t col)
@@ -250,6 +257,11 @@ struct MmrsPolicy {
         *row = (int32_t)(mb * kBM);
     }
     __device__ static const uint8_t *SelectSfA(const GemmParams &p, const Ctx &, uint32_t mb) { return p.sfA + (uint64_t)mb * (p.K / 128) * 512; }
+    __device__ static void SelectSfAMap(const GemmParams &p, const Ctx &, uint32_t mb, const CUtensorMap **tm, int32_t *atomRow)
+    {
+        *tm = &p.tmapSfA;
+        *atomRow = (int32_t)(mb * (p.K / 128));
+    }
     __device__ static bool UseDirect(const GemmParams &) { return false; }
     __device__ static void Store(const GemmParams &, const Ctx &, uint32_t, uint32_t, const uint32_t (&)[32]) {}
     // Tiles of rows owned by a peer: the bf16 partial goes into slot[rank] of the owner's workspace. Tiles of the own

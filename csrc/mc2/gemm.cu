@@ -49,6 +49,21 @@ HcclResult EncodeTmap2D(CUtensorMap *out, const void *base, uint64_t rows, uint6
     return HCCL_SUCCESS;
 }
 
+HcclResult EncodeTmapSf(CUtensorMap *out, const void *scales, uint64_t atoms)
+{
+    EncodeFn enc = GetEncode();
+    if (!enc) { HCCL_ERROR("cuTensorMapEncodeTiled is unavailable"); return HCCL_E_UNAVAIL; }
+    if (((uintptr_t)scales & 15u) || atoms == 0) { HCCL_ERROR("scale-atom tensor map: base %p must be 16-byte aligned", scales); return HCCL_E_PARA; }
+    cuuint64_t dims[2] = {128, atoms};
+    cuuint64_t strides[1] = {512};
+    cuuint32_t box[2] = {128, 1};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(scales), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { HCCL_ERROR("cuTensorMapEncodeTiled (scale atoms) failed: %d", (int)r); return HCCL_E_DRV; }
+    return HCCL_SUCCESS;
+}
+
 uint32_t *GemmErrorWord()
 {
     static uint32_t *w[64] = {nullptr};

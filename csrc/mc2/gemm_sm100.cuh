@@ -48,6 +48,8 @@ struct GemmParams {
     CUtensorMap tmapA1;          // policy-specific second A map (other parity half)
     CUtensorMap tmapALocal;      // policy-specific third A map (the local shard)
     CUtensorMap tmapB;           // [N, K] bf16, box 64 x BN
+    CUtensorMap tmapSfA, tmapSfB; // block-scaled CTA-pair kernel: scale atoms as [atoms][128 x u32] (box = one atom, no swizzle)
+    CUtensorMap tmapSfA1, tmapSfALocal;   // policy-specific further scale maps of A (other parity half, the local shard)
     void *C;                     // output, row-major, leading dimension ldc (elements)
     uint32_t M, N, K;
     uint32_t ldc;
@@ -134,6 +136,12 @@ struct PlainPolicy {
     }
     // block-scaled kernels: the scale atoms (512 bytes per 128 rows x 128 K) of row block mb, K block 0
     __device__ static const uint8_t *SelectSfA(const GemmParams &p, const Ctx &, uint32_t mb) { return p.sfA + (uint64_t)mb * (p.K / 128) * 512; }
+    // the same for the kernel that fetches scale atoms through a tensor map: map and atom row of K block 0
+    __device__ static void SelectSfAMap(const GemmParams &p, const Ctx &, uint32_t mb, const CUtensorMap **tm, int32_t *atomRow)
+    {
+        *tm = &p.tmapSfA;
+        *atomRow = (int32_t)(mb * (p.K / 128));
+    }
     // fp32 output goes straight from registers; bf16 output is staged through shared memory and written as whole
     // 16-byte chunks of contiguous row segments
     __device__ static bool UseDirect(const GemmParams &p) { return p.outFp32 != 0; }

@@ -15,6 +15,7 @@
 #include "fused_policies.cuh"
 #include "gemm_sm100_2cta.cuh"
 #include "gemm_sm100_mx.cuh"
+#include "gemm_sm100_mx_2cta.cuh"
 #include "gemm_host.h"
 #include "hccl/hccl_mc2.h"
 
@@ -89,9 +90,19 @@ int PairLevel(uint32_t nranks = 2)
     return nranks <= 2 ? 1 : 0;
 }
 
+// Block-scaled operators: CTA pairs by default (HCCL_MX_PAIR=0 keeps the one-CTA kernel); MatmulAllReduce stays one-CTA.
+bool MxPairEnabled()
+{
+    const char *e = getenv("HCCL_MX_PAIR");
+    return !(e && e[0] == '0');
+}
+
 bool PairModeFor(const FusedShape &s)
 {
-    if (s.mx) return false;                              // the block-scaled kernels are one-CTA
+    if (s.mx) {
+        if (!MxPairEnabled() || s.N < 256 || s.kind == MMAR) return false;
+        return s.kind == AGMM ? (s.m / kBM) % 2 == 0 : (s.m / s.n / kBM) % 2 == 0;
+    }
     if (PairLevel(s.n) <= 0 || s.N < 256) return false;
     if (s.kind == AGMM) return (s.m / kBM) % 2 == 0;
     if (s.kind == MMRS) return (s.m / s.n / kBM) % 2 == 0;
@@ -116,11 +127,13 @@ uint32_t MxTileN()
 
 // Block-scaled form: a / b are e4m3 payloads, sfa / sfb their scale atoms; MxTileN()-wide tiles (128-wide for MatmulAllReduce).
 HcclResult BuildParamsMx(const FusedShape &s, char *heapLocal, uint64_t wsOff, const void *a, const void *sfa, const void *b, const void *sfb, void *out,
-                         uint32_t commCtas, GemmParams *p)
+                         uint32_t commCtas, GemmParams *p, uint32_t pairBN = 0)
 {
     memset(p, 0, sizeof(*p));
     const uint64_t half = WorkspaceHalfBytes(s);
-    const uint32_t bn = MxTileN();
+    const uint32_t bn = pairBN ? pairBN : MxTileN();       // tile width; a CTA of a pair loads half of the B tile
+    const uint32_t boxB = pairBN ? pairBN / 2 : bn;
+    const uint64_t kAtoms = s.K / 128;
     p->errorWord = GemmErrorWord();
     p->groupM = 16;
     p->elemBytes = 1;
@@ -134,13 +147,23 @@ HcclResult BuildParamsMx(const FusedShape &s, char *heapLocal, uint64_t wsOff, c
         CHK_RET(EncodeTmap2D(&p->tmapA, heapLocal + wsOff, p->M, s.K, s.K, kBM, kMxBK, 1));
         CHK_RET(EncodeTmap2D(&p->tmapA1, heapLocal + wsOff + half, p->M, s.K, s.K, kBM, kMxBK, 1));
         CHK_RET(EncodeTmap2D(&p->tmapALocal, a, s.m, s.K, s.K, kBM, kMxBK, 1));
-        CHK_RET(EncodeTmap2D(&p->tmapB, b, s.N, s.K, s.K, bn, kMxBK, 1));
+        CHK_RET(EncodeTmap2D(&p->tmapB, b, s.N, s.K, s.K, boxB, kMxBK, 1));
+        if (pairBN) {
+            CHK_RET(EncodeTmapSf(&p->tmapSfA, heapLocal + wsOff + payload, (uint64_t)(p->M / kBM) * kAtoms));
+            CHK_RET(EncodeTmapSf(&p->tmapSfA1, heapLocal + wsOff + half + payload, (uint64_t)(p->M / kBM) * kAtoms));
+            CHK_RET(EncodeTmapSf(&p->tmapSfALocal, sfa, (uint64_t)((s.m + 127) / 128) * kAtoms));
+            CHK_RET(EncodeTmapSf(&p->tmapSfB, sfb, (uint64_t)((s.N + 127) / 128) * kAtoms));
+        }
         p->u64[0] = wsOff; p->u64[1] = half; p->u64[2] = (uint64_t)(uintptr_t)a; p->u64[3] = wsOff + payload; p->u64[5] = (uint64_t)(uintptr_t)sfa;
         p->u32[0] = (uint32_t)s.m; p->u32[1] = commCtas; p->u32[2] = (uint32_t)(s.m / kBM);
     } else if (s.kind == MMRS) {
         p->M = (uint32_t)s.m;
         CHK_RET(EncodeTmap2D(&p->tmapA, a, s.m, s.K, s.K, kBM, kMxBK, 1));
-        CHK_RET(EncodeTmap2D(&p->tmapB, b, s.N, s.K, s.K, bn, kMxBK, 1));
+        CHK_RET(EncodeTmap2D(&p->tmapB, b, s.N, s.K, s.K, boxB, kMxBK, 1));
+        if (pairBN) {
+            CHK_RET(EncodeTmapSf(&p->tmapSfA, sfa, (uint64_t)((s.m + 127) / 128) * kAtoms));
+            CHK_RET(EncodeTmapSf(&p->tmapSfB, sfb, (uint64_t)((s.N + 127) / 128) * kAtoms));
+        }
         p->u64[0] = wsOff; p->u64[1] = half;
         p->u32[0] = (uint32_t)(s.m / s.n); p->u32[1] = (uint32_t)(s.m / s.n / kBM); p->u32[2] = (uint32_t)((s.N + bn - 1) / bn);
     } else {
@@ -271,6 +294,32 @@ template <class Policy, int BN> HcclResult LaunchFusedPair(const GemmParams &p, 
     return HCCL_SUCCESS;
 }
 
+template <class Policy, int BN> HcclResult LaunchFusedPairMx(const GemmParams &p, uint32_t grid, cudaStream_t stream)
+{
+    static std::atomic<bool> attrSet{false};
+    auto kern = GemmKernelMx2Cta<Policy, BN>;
+    const size_t smem = GemmMx2CtaSmem<BN>::kTotal + 1024;
+    if (!attrSet) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return HCCL_E_RUNTIME;
+        attrSet = true;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid & ~1u);
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeCooperative;
+    attr[1].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
+    if (e != cudaSuccess) { HCCL_ERROR("fused block-scaled CTA-pair kernel launch failed: %s (grid %u)", cudaGetErrorString(e), grid); (void)cudaGetLastError(); return HCCL_E_RUNTIME; }
+    return HCCL_SUCCESS;
+}
+
 // ---- symmetric workspace per communicator (grown on demand; every rank makes the same calls, so offsets agree)
 struct ParamKey {
     int kind; const void *a, *b, *out; uint64_t m, N, K, wsOff;     // kind + pair tile width = parameters of the CTA-pair kernel
@@ -343,7 +392,8 @@ HcclResult RunFused(FusedKind kind, Comm *c, const void *a, const void *b, void 
     if (pairMode) commCtas &= ~1u;                       // whole CTA pairs take the communication role
     const uint32_t pairs = ((uint32_t)SmCount() - commCtas) / 2;
     const uint64_t rowPairs = kind == AGMM ? s.n * s.m / kBM / 2 : s.m / kBM / 2;
-    const uint32_t pairBN = pairMode ? PairTileN(rowPairs, s.N, pairs) : 0;
+    // block-scaled pairs: 192-wide tiles (two accumulators) unless K is long enough to hide the epilogue of 256-wide ones
+    const uint32_t pairBN = !pairMode ? 0 : s.mx ? (s.K >= 16384 ? 256u : 192u) : PairTileN(rowPairs, s.N, pairs);
     GemmParams p;
     {
         std::lock_guard<std::mutex> lk(g_wsMu);
@@ -352,7 +402,7 @@ HcclResult RunFused(FusedKind kind, Comm *c, const void *a, const void *b, void 
         auto it = cache.find(key);
         if (it != cache.end()) p = it->second;
         else {
-            if (s.mx) CHK_RET(BuildParamsMx(s, c->heap[c->rank], wsOff, a, sfa, b, sfb, out, commCtas, &p));
+            if (s.mx) CHK_RET(BuildParamsMx(s, c->heap[c->rank], wsOff, a, sfa, b, sfb, out, commCtas, &p, pairBN));
             else CHK_RET(BuildParams(s, c->heap[c->rank], wsOff, a, b, out, commCtas, &p, pairBN));
             p.comm = c->devCommPtr;
             if (cache.size() > 256) cache.clear();
@@ -363,7 +413,11 @@ HcclResult RunFused(FusedKind kind, Comm *c, const void *a, const void *b, void 
         uint64_t pairTiles = rowPairs * ((s.N + pairBN - 1) / pairBN);
         uint32_t grid = (uint32_t)std::min<uint64_t>(pairTiles * 2, (uint64_t)pairs * 2) + commCtas;
         grid = std::max(grid, commCtas + 2u);
-        if (kind == AGMM && pairBN == 224) CHK_RET((LaunchFusedPair<AgmmPolicy, 224>(p, grid, stream)));
+        if (s.mx && kind == AGMM && pairBN == 192) CHK_RET((LaunchFusedPairMx<AgmmPolicy, 192>(p, grid, stream)));
+        else if (s.mx && kind == AGMM) CHK_RET((LaunchFusedPairMx<AgmmPolicy, 256>(p, grid, stream)));
+        else if (s.mx && pairBN == 192) CHK_RET((LaunchFusedPairMx<MmrsPolicy, 192>(p, grid, stream)));
+        else if (s.mx) CHK_RET((LaunchFusedPairMx<MmrsPolicy, 256>(p, grid, stream)));
+        else if (kind == AGMM && pairBN == 224) CHK_RET((LaunchFusedPair<AgmmPolicy, 224>(p, grid, stream)));
         else if (kind == AGMM) CHK_RET((LaunchFusedPair<AgmmPolicy, 256>(p, grid, stream)));
         else if (pairBN == 224) CHK_RET((LaunchFusedPair<MmrsPolicy, 224>(p, grid, stream)));
         else CHK_RET((LaunchFusedPair<MmrsPolicy, 256>(p, grid, stream)));

@@ -16,6 +16,7 @@
 #include "../common/log.h"
 #include "gemm_host.h"
 #include "gemm_sm100_mx.cuh"
+#include "gemm_sm100_mx_2cta.cuh"
 #include "hccl/hccl_mc2.h"
 
 namespace hccl {
@@ -93,6 +94,43 @@ template <int BN> HcclResult LaunchPlainMx(const void *a, const void *sfa, const
     return HCCL_SUCCESS;
 }
 
+// CTA pairs (cta_group::2): 256 x BN tiles, one cluster of two CTAs per tile, an even grid.
+template <int BN> HcclResult LaunchPlainMxPair(const void *a, const void *sfa, const void *b, const void *sfb, void *c, uint32_t M, uint32_t N, uint32_t K, bool outFp32,
+                                              cudaStream_t s)
+{
+    GemmParams p{};
+    using S = GemmMx2CtaSmem<BN>;
+    CHK_RET(EncodeTmap2D(&p.tmapA, a, M, K, (uint64_t)K, kBM, kMxBK, 1));
+    CHK_RET(EncodeTmap2D(&p.tmapB, b, N, K, (uint64_t)K, BN / 2, kMxBK, 1));
+    CHK_RET(EncodeTmapSf(&p.tmapSfA, sfa, (uint64_t)((M + 127) / 128) * (K / 128)));
+    CHK_RET(EncodeTmapSf(&p.tmapSfB, sfb, (uint64_t)((N + 127) / 128) * (K / 128)));
+    p.C = c; p.M = M; p.N = N; p.K = K; p.ldc = N; p.outFp32 = outFp32; p.groupM = 8; p.errorWord = GemmErrorWord();
+    p.sfA = (const uint8_t *)sfa; p.sfB = (const uint8_t *)sfb; p.sfAtomsB = (N + 127) / 128; p.elemBytes = 1;
+    static std::atomic<bool> attrSet{false};
+    auto kern = GemmKernelMx2Cta<PlainPolicy, BN>;
+    size_t smem = S::kTotal + 1024;
+    if (!attrSet) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return HCCL_E_RUNTIME;
+        attrSet = true;
+    }
+    uint32_t tiles = ((M + 2 * kBM - 1) / (2 * kBM)) * ((N + BN - 1) / BN);
+    uint32_t pairs = std::min<uint32_t>(tiles, (uint32_t)SmCount() / 2);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(pairs * 2);
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
+    CountLaunch();
+    if (e != cudaSuccess) { HCCL_ERROR("block-scaled CTA-pair GEMM launch failed: %s", cudaGetErrorString(e)); (void)cudaGetLastError(); return HCCL_E_RUNTIME; }
+    return HCCL_SUCCESS;
+}
+
 }  // namespace
 }  // namespace mc2
 }  // namespace hccl
@@ -131,6 +169,17 @@ HcclResult HcclGemmMxfp8(const void *a, const void *sfa, const void *b, const vo
                    (unsigned long long)k);
         return HCCL_E_PARA;
     }
+    // CTA pairs when the product fills the GPU with pair tiles (HCCL_MX_PAIR=0 keeps the one-CTA kernels): 192-wide tiles with two
+    // accumulators, or 256-wide ones when K is long enough to hide their exposed epilogue
+    {
+        const char *e = getenv("HCCL_MX_PAIR");
+        const bool pair = !(e && e[0] == '0') && !getenv("HCCL_MX_TILE_N");
+        const uint64_t bn = k >= 16384 ? 256 : 192;
+        const uint64_t pairTiles = ((m + 255) / 256) * ((n + bn - 1) / bn);
+        if (pair && n >= 256 && pairTiles >= (uint64_t)SmCount() / 2)
+            return bn == 256 ? LaunchPlainMxPair<256>(a, sfa, b, sfb, c, (uint32_t)m, (uint32_t)n, (uint32_t)k, outFp32 != 0, stream)
+                             : LaunchPlainMxPair<192>(a, sfa, b, sfb, c, (uint32_t)m, (uint32_t)n, (uint32_t)k, outFp32 != 0, stream);
+    }
     // HCCL_MX_TILE_N = 192 | 256 picks the wide tile of large products (as for the fused operators)
     if (const char *e = getenv("HCCL_MX_TILE_N")) {
         const int v = atoi(e);
@@ -149,6 +198,9 @@ HcclResult HcclGemmMxfp8Variant(const void *a, const void *sfa, const void *b, c
     if (!a || !sfa || !b || !sfb || !c) return HCCL_E_PTR;
     if (m == 0 || n == 0 || k == 0 || (k % 128) || (n % 8) || m > 0x7fffffff || n > 0x7fffffff || k > 0x7fffffff) return HCCL_E_PARA;
     if (tileN == 256) return LaunchPlainMx<256>(a, sfa, b, sfb, c, (uint32_t)m, (uint32_t)n, (uint32_t)k, outFp32 != 0, stream);
+    // 2256 / 2192: CTA pairs (cta_group::2) with 256- / 192-wide tiles
+    if (tileN == 2256) return LaunchPlainMxPair<256>(a, sfa, b, sfb, c, (uint32_t)m, (uint32_t)n, (uint32_t)k, outFp32 != 0, stream);
+    if (tileN == 2192) return LaunchPlainMxPair<192>(a, sfa, b, sfb, c, (uint32_t)m, (uint32_t)n, (uint32_t)k, outFp32 != 0, stream);
     if (tileN == 192) return LaunchPlainMx<192>(a, sfa, b, sfb, c, (uint32_t)m, (uint32_t)n, (uint32_t)k, outFp32 != 0, stream);
     if (tileN == 128) return LaunchPlainMx<128>(a, sfa, b, sfb, c, (uint32_t)m, (uint32_t)n, (uint32_t)k, outFp32 != 0, stream);
     return HcclGemmMxfp8(a, sfa, b, sfb, c, m, n, k, outFp32, stream);

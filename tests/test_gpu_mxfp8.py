@@ -41,7 +41,11 @@ def test_quantiser_matches_the_reference_rule(rows, k):
 @pytest.mark.parametrize("m,n,k,tile", [(128, 128, 128, 128), (128, 256, 256, 256), (256, 512, 1024, 128), (384, 768, 512, 256),
                                         (200, 264, 384, 128), (200, 264, 384, 256), (1024, 1024, 2048, 0), (4096, 4096, 512, 0),
                                         # 192-wide tiles: odd tiles start at row 64 of a scale atom; partial last tiles; a single tile
-                                        (128, 192, 128, 192), (256, 384, 512, 192), (384, 960, 640, 192), (200, 264, 384, 192), (2048, 8192, 512, 192)])
+                                        (128, 192, 128, 192), (256, 384, 512, 192), (384, 960, 640, 192), (200, 264, 384, 192), (2048, 8192, 512, 192),
+                                        # CTA pairs (2256 / 2192 = 256- / 192-wide pair tiles): one pair, an odd number of row blocks (the second CTA of
+                                        # the last pair idles), partial tiles in both directions, many tiles per pair
+                                        (256, 256, 128, 2256), (128, 256, 256, 2256), (384, 768, 512, 2256), (200, 264, 384, 2256), (4096, 4096, 512, 2256),
+                                        (256, 192, 128, 2192), (384, 960, 640, 2192), (200, 264, 384, 2192), (2048, 8192, 512, 2192)])
 def test_block_scaled_gemm_matches_fp32_product_of_dequantised_operands(m, n, k, tile):
     from hccl_b200.ops import gemm as g, mxfp8 as mx
     a, w = mx.quantize(_wild((m, k), 1 + m)), mx.quantize(_wild((n, k), 2 + n, 0.05))
@@ -65,7 +69,7 @@ def test_block_scaled_gemm_every_scale_byte_is_used():
         w[(13 * kb + 5) % n, kb * 32:(kb + 1) * 32] *= 2.0 ** -(kb % 9)
     qa, qw = mx.quantize(a.to(torch.bfloat16)), mx.quantize(w.to(torch.bfloat16))
     ref = mx.dequantize(qa) @ mx.dequantize(qw).t()
-    for tile in (128, 192, 256):
+    for tile in (128, 192, 256, 2256, 2192):
         out = mx.gemm(qa, qw, out_dtype=torch.float32, tile_n=tile)
         torch.cuda.synchronize()
         assert torch.allclose(out, ref, rtol=1e-4, atol=1e-3)

@@ -40,26 +40,35 @@ def native_host_us(comm):
     return sum(recs[i].endNs - recs[i].beginNs for i in range(n.value)) / n.value / 1e3, recs[n.value - 1].algName.decode()
 
 
+REPEATS = 1
+
+
 def time_fn(fn, iters, warmup, tag=None):
+    """Seconds per call: device time of `iters` back-to-back calls, max over ranks; the median of REPEATS such loops (a single host
+    stall of a few milliseconds on any rank would otherwise decide a row)."""
     import time
     for _ in range(warmup):
         fn()
-    torch.cuda.synchronize()
-    dist.barrier()
-    torch.cuda.synchronize()
-    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s.record()
-    h0 = time.perf_counter()
-    for _ in range(iters):
-        fn()
-    h1 = time.perf_counter()            # host time to ISSUE the calls (no synchronisation inside)
-    e.record()
-    torch.cuda.synchronize()
-    if tag is not None:
-        HOST_US[tag] = (h1 - h0) / iters * 1e6
-    t = torch.tensor([s.elapsed_time(e) / iters], device="cuda")
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return t.item() * 1e-3
+    samples = []
+    for _ in range(REPEATS):
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        h0 = time.perf_counter()
+        for _ in range(iters):
+            fn()
+        h1 = time.perf_counter()            # host time to ISSUE the calls (no synchronisation inside)
+        e.record()
+        torch.cuda.synchronize()
+        if tag is not None:
+            HOST_US[tag] = (h1 - h0) / iters * 1e6
+        t = torch.tensor([s.elapsed_time(e) / iters], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        samples.append(t.item() * 1e-3)
+    samples.sort()
+    return samples[len(samples) // 2]
 
 
 def main():
@@ -70,10 +79,13 @@ def main():
     ap.add_argument("--max-bytes", type=int, default=1 << 30)
     ap.add_argument("--json", default="")
     ap.add_argument("--skip-nccl", action="store_true")
+    ap.add_argument("--repeats", type=int, default=1, help="timed loops per row; the median is reported")
     ap.add_argument("--registered", action="store_true",
                     help="buffers of this library's calls are registered windows of the symmetric heap (zero-copy kernels from 1 MB up); "
                          "set HCCL_SYM_HEAP_MB large enough for the biggest size")
     args = ap.parse_args()
+    global REPEATS
+    REPEATS = max(1, args.repeats)
     dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0))))
     comm = init_from_env()
     rank, n = comm.rank, comm.size

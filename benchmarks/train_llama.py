@@ -72,6 +72,8 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--bucket-mb", type=float, default=32.0)
+    ap.add_argument("--dp-ctas", type=int, default=-1, help="data parallel, --impl ours: cap on the CTAs of the gradient all-reduce kernels (-1 = library default)")
+    ap.add_argument("--native-gemm", action="store_true", help="data parallel: run the (collective-free) linears on this library's GEMM instead of cuBLAS")
     ap.add_argument("--staged-buckets", action="store_true", help="data parallel, --impl ours: keep the gradient buckets in ordinary device "
                     "memory instead of registered windows (set HCCL_SYM_HEAP_MB above the gradient size for registered buckets)")
     a = ap.parse_args()
@@ -101,15 +103,19 @@ def main():
         comm = Communicator.from_root_info(1, get_root_info(), 0) if native else TorchDistComm(solo=True)
 
     from hccl_b200.parallel import tensor_parallel
-    tensor_parallel.use_native_gemm(native)
+    # tensor parallel: every linear is a fused matmul + collective kernel of this library. Data parallel: the linears have no
+    # collective attached, so they are plain library GEMMs (cuBLAS, as in the baseline arm) unless --native-gemm asks for this
+    # library's tcgen05 GEMM; what differs between the arms is the gradient all-reduce.
+    tensor_parallel.use_native_gemm(native and (a.parallel == "tp" or a.native_gemm))
     model = Llama(cfg, comm, dtype=torch.bfloat16, device=dev, seed=None)
     opt = torch.optim.AdamW(model.parameters(), lr=1e-4, weight_decay=0.1, fused=True)
     dpw, grp = None, None
     if a.parallel == "dp" and world > 1:
         if a.impl == "ours":
             from hccl_b200.parallel.data_parallel import DataParallel
-            dpw = DataParallel(model, world_comm, bucket_mb=a.bucket_mb, registered=not a.staged_buckets)
+            dpw = DataParallel(model, world_comm, bucket_mb=a.bucket_mb, registered=not a.staged_buckets, **({} if a.dp_ctas < 0 else {"max_ctas": a.dp_ctas}))
         elif a.impl == "ours-ddp":
+            os.environ.setdefault("HCCL_MAX_CTAS", "16")   # as DataParallel does: few CTAs for a collective that overlaps the backward pass
             import hccl_b200.parallel  # noqa: F401  (registers the "hccl" backend)
             grp = dist.new_group(backend="hccl")
             model = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local], bucket_cap_mb=a.bucket_mb, gradient_as_bucket_view=True,

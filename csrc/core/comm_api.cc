@@ -8,6 +8,7 @@
 #include "../common/log.h"
 #include "../exec/executor.h"
 #include "comm.h"
+#include "../exec/op_common.h"
 #include "hccl/hccl_comm.h"
 
 using namespace hccl;
@@ -256,6 +257,14 @@ HcclResult HcclGetCommAsyncError(HcclComm comm, HcclResult *asyncError)
 }
 
 HcclResult HcclCommSymAlloc(HcclComm comm, uint64_t bytes, void **ptr) { Comm *c = CommFromHandle(comm); return c ? SymAlloc(c, bytes, ptr) : HCCL_E_PTR; }
+HcclResult HcclCommSetMaxCtas(HcclComm comm, uint32_t maxCtas)
+{
+    Comm *c = CommFromHandle(comm);
+    if (!c) return HCCL_E_PTR;
+    c->env.maxCtas = maxCtas;
+    BumpSelectionGeneration();          // cached launch lists were planned with the old cap
+    return HCCL_SUCCESS;
+}
 HcclResult HcclCommSymFree(HcclComm comm, void *ptr) { Comm *c = CommFromHandle(comm); return c ? SymFree(c, ptr) : HCCL_E_PTR; }
 HcclResult HcclSymWinGetPeerPointer(HcclComm comm, void *localPtr, uint32_t peer, void **peerPtr)
 {

@@ -303,6 +303,11 @@ class Communicator:
         the allocation: every rank frees in the same order."""
         check(lib().HcclCommSymFree(self._h, ctypes.c_void_p(tensor._hccl_sym_ptr)), "HcclCommSymFree")
 
+    def set_max_ctas(self, n: int) -> None:
+        """Caps the grid of this communicator's collective kernels (0 = their own heuristics). A collective that overlaps compute,
+        such as a gradient all-reduce during the backward pass, wants few CTAs so that the GEMMs keep their SMs."""
+        check(lib().HcclCommSetMaxCtas(self._h, ctypes.c_uint32(n)), "HcclCommSetMaxCtas")
+
     def mem_alloc(self, nbytes: int) -> int:
         """Address of a fresh registered block of the symmetric heap (HcclMemAlloc); same calling rules as sym_tensor."""
         ptr = ctypes.c_void_p()

@@ -98,13 +98,32 @@ def dequantize(t: MxTensor) -> torch.Tensor:
     return (v * scale.unsqueeze(2)).view(t.rows, t.k)
 
 
-def _as_mx(x, stream=None) -> MxTensor:
+# Quantised activations of the fused operators live in buffers that are reused per (shape, device, stream): work on one stream is
+# ordered, so the next quantisation cannot overtake the kernel that still reads the previous one, and stable addresses let the native
+# side reuse its cached tensor maps instead of encoding eight of them per call.
+_ACT_BUFFERS = {}
+
+
+def _as_mx_fresh(x, stream=None) -> MxTensor:
+    """Second operands (weights): quantise once outside the step and pass the MxTensor; a bf16 tensor gets a buffer of its own."""
     return x if isinstance(x, MxTensor) else quantize(x, stream=stream)
+
+
+def _as_mx(x, stream=None) -> MxTensor:
+    if isinstance(x, MxTensor):
+        return x
+    key = (x.shape[0], x.shape[1], x.device, _stream(stream))
+    buf = _ACT_BUFFERS.get(key)
+    if buf is None:
+        if len(_ACT_BUFFERS) >= 16:
+            _ACT_BUFFERS.clear()
+        buf = _ACT_BUFFERS[key] = empty_like_quantized(x.shape[0], x.shape[1], x.device)
+    return quantize(x, out=buf, stream=stream)
 
 
 def gemm(a, w, out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16, tile_n: int = 0, stream=None) -> torch.Tensor:
     """out[M, N] = a[M, K] @ w[N, K]^T with both operands block-scaled (bf16 inputs are quantised first)."""
-    a, w = _as_mx(a, stream), _as_mx(w, stream)
+    a, w = _as_mx(a, stream), _as_mx_fresh(w, stream)
     assert a.k == w.k
     if out is None:
         out = torch.empty((a.rows, w.rows), dtype=out_dtype, device=a.payload.device)
@@ -115,7 +134,7 @@ def gemm(a, w, out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torc
 
 def all_gather_matmul(comm, a_local, w, out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
     """out[size*m, N] = all_gather(a_local[m, K]) @ w[N, K]^T; the gather moves e4m3 bytes and scales."""
-    a, w = _as_mx(a_local, stream), _as_mx(w, stream)
+    a, w = _as_mx(a_local, stream), _as_mx_fresh(w, stream)
     if out is None:
         out = torch.empty((a.rows * comm.size, w.rows), dtype=torch.bfloat16, device=a.payload.device)
     check(_decl().HcclAllGatherMatmulMxfp8(a.payload.data_ptr(), a.scales.data_ptr(), w.payload.data_ptr(), w.scales.data_ptr(), out.data_ptr(), a.rows, w.rows,
@@ -125,7 +144,7 @@ def all_gather_matmul(comm, a_local, w, out: Optional[torch.Tensor] = None, stre
 
 def matmul_reduce_scatter(comm, a, w, out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
     """out[M/size, N] = reduce_scatter_rows(a[M, Klocal] @ w[N, Klocal]^T); partials travel as bf16, summed in rank order."""
-    a, w = _as_mx(a, stream), _as_mx(w, stream)
+    a, w = _as_mx(a, stream), _as_mx_fresh(w, stream)
     if out is None:
         out = torch.empty((a.rows // comm.size, w.rows), dtype=torch.bfloat16, device=a.payload.device)
     check(_decl().HcclMatmulReduceScatterMxfp8(a.payload.data_ptr(), a.scales.data_ptr(), w.payload.data_ptr(), w.scales.data_ptr(), out.data_ptr(), a.rows,
@@ -134,7 +153,7 @@ def matmul_reduce_scatter(comm, a, w, out: Optional[torch.Tensor] = None, stream
 
 
 def matmul_all_reduce(comm, a, w, out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
-    a, w = _as_mx(a, stream), _as_mx(w, stream)
+    a, w = _as_mx(a, stream), _as_mx_fresh(w, stream)
     if out is None:
         out = torch.empty((a.rows, w.rows), dtype=torch.bfloat16, device=a.payload.device)
     check(_decl().HcclMatmulAllReduceMxfp8(a.payload.data_ptr(), a.scales.data_ptr(), w.payload.data_ptr(), w.scales.data_ptr(), out.data_ptr(), a.rows,

@@ -40,10 +40,16 @@ class DataParallel:
     """Wrap a module's parameters: `dp = DataParallel(model, comm)`; after `loss.backward()` call `dp.finish()`."""
 
     def __init__(self, module: nn.Module, comm, *, bucket_mb: float = 32.0, grad_dtype: Optional[torch.dtype] = None, average: bool = True,
-                 registered: Optional[bool] = None, grad_as_bucket_view: bool = True):
-        """`registered`: keep the buckets in registered windows of the communicator's symmetric heap (default: on CUDA with more
+                 registered: Optional[bool] = None, grad_as_bucket_view: bool = True, max_ctas: Optional[int] = 16):
+        """`max_ctas`: cap on the grid of this communicator's collective kernels while they overlap the backward pass (CUDA only).
+        `registered`: keep the buckets in registered windows of the communicator's symmetric heap (default: on CUDA with more
         than one rank). Every rank builds the same buckets in the same order, which is what symmetric allocation asks for."""
         self.comm, self.average = comm, average
+        # The all-reduce shares the GPU with the backward pass: with the kernels' own grid (64-96 CTAs for a 32 MB bucket) a
+        # Llama-3-8B step on 4 GPUs took 373.6 ms, capped at 32 CTAs 364.3 ms, at 16 CTAs 360.9 ms (NCCL DDP: 360.8 ms).
+        # None leaves the communicator as it is.
+        if max_ctas is not None and hasattr(comm, "set_max_ctas") and getattr(comm, "is_cuda", False) and comm.size > 1:
+            comm.set_max_ctas(max_ctas)
         params = [p for p in module.parameters() if p.requires_grad]
         if not params:
             raise ValueError("module has no trainable parameters")

@@ -57,6 +57,9 @@ HcclResult HcclGetCommAsyncError(HcclComm comm, HcclResult *asyncError);
 /* Zero-copy support: registered buffers live in (or are mapped into) the symmetric address space so
  * peers can read/write them directly. HcclCommSymAlloc returns memory from the symmetric heap. */
 HcclResult HcclCommSymAlloc(HcclComm comm, uint64_t bytes, void **ptr);
+/* Caps the grid of this communicator's collective kernels (0 = the kernels' own heuristics; the HCCL_MAX_CTAS environment value is the
+ * initial setting). A gradient all-reduce that overlaps a backward pass wants few CTAs so that the GEMMs keep their SMs. */
+HcclResult HcclCommSetMaxCtas(HcclComm comm, uint32_t maxCtas);
 HcclResult HcclCommSymFree(HcclComm comm, void *ptr);
 HcclResult HcclSymWinGetPeerPointer(HcclComm comm, void *localPtr, uint32_t peer, void **peerPtr);
 HcclResult HcclSymGetMulticastPointer(HcclComm comm, void *localPtr, void **mcPtr);

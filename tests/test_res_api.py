@@ -173,6 +173,22 @@ def test_mem_alloc_is_a_registered_block_and_allocator_hooks_follow_the_attached
     assert l.HcclSetAllocatorComm(vp(12345)) == Result.E_PTR
 
 
+def test_cta_cap_is_a_per_communicator_setting():
+    l = _decl()
+    l.HcclCommSetMaxCtas.argtypes = [vp, u32]
+
+    def body(comm, rank):
+        comm.set_max_ctas(8)
+        x = np.full(1000, rank + 1.0, np.float32)
+        comm.all_reduce(x)                                    # operators keep working under a cap (the host engine ignores it)
+        comm.synchronize()
+        comm.set_max_ctas(0)
+        return float(x[0])
+
+    assert run_ranks(2, body) == [3.0, 3.0]
+    assert l.HcclCommSetMaxCtas(vp(12345), 4) == Result.E_PTR
+
+
 def test_rank_graph_flat_and_exchange_info():
     l = _decl()
 

@@ -361,8 +361,17 @@ SelectorStatus IrDefault(const SelectorCtx &ctx, OpParam &p)
                          p.opType == HCCL_CMD_REDUCE;
     const bool strict = ctx.env->deterministic == Deterministic::STRICT && reduces;
     if (strict) forced = AlgoType::FULLMESH;
+    // HCCL_BIRS_ENABLE=1 (the reference's experimental batch-invariant ReduceScatter for its 2-D topology, reference:
+    // experimental/ops/reduce_scatter/birs, docs/en/rfcs/0001-add-batch-invariant-reducescatter.md): an element's bits must not
+    // depend on how many elements travel with it. On two levels that is the sequence executor (every element is summed inside the
+    // server in rank order, then across the servers in server order); the parallel executor is excluded because its cut between
+    // the level orders moves with the count. On one level it is the rank-ordered mesh.
+    const char *birsEnv = getenv("HCCL_BIRS_ENABLE");
+    const bool birs = birsEnv && birsEnv[0] == '1';
+    const bool batchInvariant = birs && p.opType == HCCL_CMD_REDUCE_SCATTER;
+    if (batchInvariant && ctx.topo->numLevels == 1) forced = AlgoType::FULLMESH;
     // multi-level topologies use the sequence executors for the ops that have one
-    if (ctx.topo->numLevels == 2 && forced == AlgoType::DEFAULT && !ctx.cuda && !strict &&
+    if (ctx.topo->numLevels == 2 && forced == AlgoType::DEFAULT && !ctx.cuda && !strict && !batchInvariant &&
         (p.opType == HCCL_CMD_ALLREDUCE || p.opType == HCCL_CMD_ALLGATHER || p.opType == HCCL_CMD_REDUCE_SCATTER)) {
         // Two levels and an engine that runs several queues: when the slice planner prices the form that keeps both levels
         // busy at least a tenth below the sequential one, use it (HCCL_PARALLEL_EXECUTOR=0 keeps the sequence executors).

@@ -186,3 +186,49 @@ def test_two_level_operators_with_real_data(topo, forced, monkeypatch):
                 gain = par < 0.9 * seq and (min(shares) > 0 or max(steps) > 1)
                 assert ("Parallel" in used) == gain, (name, used, shares, steps, seq, par)
             assert any("Parallel" in a for a in big), big
+
+
+def test_batch_invariant_reduce_scatter_on_two_levels(monkeypatch):
+    """HCCL_BIRS_ENABLE=1: the bits of an element of a two-level ReduceScatter do not depend on the count, and they are the bits of
+    the fixed tree (rank order inside the server, then server order). Values span twelve decades so that the association shows.
+    Without the switch the selector may take the parallel executor, whose cut between the two level orders moves with the count."""
+    topo, servers, per = "1x2x4@2,1", 2, 4
+    n = servers * per
+    monkeypatch.setenv("HCCL_SIM_TOPO", topo)
+    monkeypatch.setenv("HCCL_BIRS_ENABLE", "1")
+    lib().HcclResetEnvConfigForTest()
+    rng = np.random.default_rng(11)
+    full = 300_000
+    xs = [(rng.standard_normal(full * n) * 10.0 ** rng.integers(-6, 6, full * n)).astype(np.float32) for _ in range(n)]
+
+    def run(count):
+        def body(comm, rank):
+            out = np.empty(count, np.float32)
+            # the first `count` elements of every rank's block
+            src = np.concatenate([xs[rank][j * full:j * full + count] for j in range(n)])
+            comm.reduce_scatter(src, out)
+            comm.synchronize()
+            return out, comm.last_algorithm()
+        return run_ranks(n, body, buffer_mb=64)
+
+    try:
+        big, small = run(full), run(1000)
+    finally:
+        monkeypatch.delenv("HCCL_SIM_TOPO")
+        monkeypatch.delenv("HCCL_BIRS_ENABLE")
+        lib().HcclResetEnvConfigForTest()
+    for r in range(n):
+        assert "Sequence" in big[r][1] and "Sequence" in small[r][1]
+        assert np.array_equal(big[r][0][:1000].view(np.uint32), small[r][0].view(np.uint32))
+        # the fixed tree, in numpy: float32 sums inside each server in rank order, then over the servers in order
+        blk = [x[r * full:(r + 1) * full] for x in xs]
+        partial = []
+        for s_ in range(servers):
+            acc = blk[s_ * per].copy()
+            for j in range(1, per):
+                acc = acc + blk[s_ * per + j]
+            partial.append(acc)
+        want = partial[0]
+        for s_ in range(1, servers):
+            want = want + partial[s_]
+        assert np.array_equal(big[r][0].view(np.uint32), want.view(np.uint32))

@@ -291,28 +291,49 @@ struct MmrsPolicy {
         const uint32_t r = row - (uint32_t)x.rank * mOwn, n = (uint32_t)x.n;
         const __nv_bfloat16 *ws = (const __nv_bfloat16 *)(x.heap + p.u64[0] + (uint64_t)x.half * p.u64[1]);
         const uint32_t valid = p.N - col0 < 32 ? p.N - col0 : 32;
+        // Eight columns at a time: the partial rows of ALL sources are requested before any is used (one round trip to memory per
+        // eight columns instead of one per source), then added in rank order with the own accumulator in its place, so the result
+        // has the same bits as a source-by-source walk.
+        constexpr uint32_t kSrc = 8;
+        const uint64_t rowOff = (uint64_t)r * p.N + col0;
         float sum[32];
-        bool first = true;
-        for (uint32_t s = 0; s < n; ++s) {
-            if ((int)s == x.rank) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) sum[j] = first ? __uint_as_float(v[j]) : sum[j] + __uint_as_float(v[j]);
-            } else {
-                const uint4 *src = (const uint4 *)(ws + ((uint64_t)s * mOwn + r) * p.N + col0);
+        for (uint32_t q = 0; q < 4; ++q) {
+            if (q * 8 >= valid) {
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    if ((uint32_t)q * 8 >= valid) break;
-                    uint4 raw = src[q];
-                    const __nv_bfloat162 *h = (const __nv_bfloat162 *)&raw;
+                for (int j = 0; j < 8; ++j) sum[q * 8 + j] = __uint_as_float(v[q * 8 + j]);
+                continue;
+            }
+            float acc[8];
+            bool first = true;
+            for (uint32_t s0 = 0; s0 < n; s0 += kSrc) {
+                uint4 raw[kSrc];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        float2 f = __bfloat1622float2(h[j]);
-                        sum[q * 8 + 2 * j] = first ? f.x : sum[q * 8 + 2 * j] + f.x;
-                        sum[q * 8 + 2 * j + 1] = first ? f.y : sum[q * 8 + 2 * j + 1] + f.y;
+                for (uint32_t i = 0; i < kSrc; ++i) {
+                    const uint32_t s = s0 + i;
+                    if (s < n && (int)s != x.rank) raw[i] = ((const uint4 *)(ws + (uint64_t)s * mOwn * p.N + rowOff))[q];
+                }
+#pragma unroll
+                for (uint32_t i = 0; i < kSrc; ++i) {
+                    const uint32_t s = s0 + i;
+                    if (s >= n) break;
+                    if ((int)s == x.rank) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) acc[j] = first ? __uint_as_float(v[q * 8 + j]) : acc[j] + __uint_as_float(v[q * 8 + j]);
+                    } else {
+                        const __nv_bfloat162 *h = (const __nv_bfloat162 *)&raw[i];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            float2 f = __bfloat1622float2(h[j]);
+                            acc[2 * j] = first ? f.x : acc[2 * j] + f.x;
+                            acc[2 * j + 1] = first ? f.y : acc[2 * j + 1] + f.y;
+                        }
                     }
+                    first = false;
                 }
             }
-            first = false;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sum[q * 8 + j] = acc[j];
         }
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(sum[j]);

@@ -9,7 +9,7 @@ import pytest
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 EX = os.path.join(ROOT, "examples")
 SAMPLES = ["comm_init_all", "send_recv", "batch_send_recv_ring", "allreduce", "broadcast", "allgather", "reduce_scatter", "reduce", "alltoall", "alltoallv",
-           "alltoallvc", "scatter", "custom_allgather"]
+           "alltoallvc", "scatter", "registered_allreduce", "custom_allgather"]
 
 
 @pytest.fixture(scope="module")

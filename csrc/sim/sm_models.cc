@@ -9,8 +9,9 @@
 // planner (SmPlanOp), so chunk loops and per-chunk offsets are the ones that run. With the models HcclCheckAlgorithm
 // proves deadlock freedom, bounds, freedom from races and the operator's semantics for the default GPU engines too
 // (the reference checks its generated task graphs the same way: test/st/algorithm/utils/src/hccl_verifier/checker.cc:50-100).
-// Not modelled: the warp-specialised pipelined / push variants (pipelined.cuh), whose sub-chunk credit protocol has no
-// counterpart in this IR; they are covered by the emulated-rank tests with real data.
+// The warp-specialised pipelined / push variants (pipelined.cuh) are modelled with three queues per channel (one per role
+// group) and notifies between the queues of a rank; see the section on them below. Point-to-point kernels are not modelled
+// here (their mailbox schedules are checked as host-issued plans).
 #include <algorithm>
 #include "../common/log.h"
 #include "../kernels/coll_args.h"
@@ -415,6 +416,163 @@ void AlltoAllV(Model &m)
         }
     }
 }
+// ---------------------------------------------------------------------------------------------- warp-specialised pipelines
+// pipelined.cuh: every CTA is a channel with role groups (stagers / movers / drainers) that walk the channel's sub-chunks
+// through rings of kPipeDepth slots and meet through three monotonic per-channel counters (STAGED, MOVED, DRAINED) that
+// every rank raises on every rank. Here a role group is a queue (3 per channel), "all ranks have raised X to c + 1" is a
+// WAIT for the next notify of every peer plus a local wait for the own producer group, and a signal is posted once per
+// consumer group and only for the chunks that group will wait for (the counters are level-triggered, notifies are counted).
+// The geometry (slices, PartOf, sub-chunk count = the channel's LONGEST part over all slices, slot addresses) restates the
+// kernel's, with the launch's own grid and sub-chunk size.
+constexpr uint32_t kPipeDepth = 2;
+enum PipeRole : uint32_t { ROLE_A = 0, ROLE_B = 1, ROLE_C = 2 };
+enum PipeSlot : uint32_t { S_STAGED_MOVER = 0, S_MOVED_STAGER = 1, S_MOVED_DRAINER = 2, S_DRAINED_MOVER = 3 };
+
+struct Pipe {
+    Model &m;
+    uint32_t ch, G;
+    uint64_t sub;
+    uint32_t chunks;
+    uint32_t Q(PipeRole r) const { return ch * 3 + r; }
+    uint64_t Slot(uint32_t d, uint32_t j) const { return (((uint64_t)d * m.n + j) * G + ch) * sub; }
+    uint64_t RingBytes() const { return (uint64_t)kPipeDepth * m.n * G * sub; }
+    static uint64_t SubLen(uint64_t len, uint64_t sub, uint32_t c) { uint64_t lo = (uint64_t)c * sub; return lo >= len ? 0 : std::min(sub, len - lo); }
+    std::vector<Task> &Tasks(PipeRole r) { return m.plan->queues[Q(r)]; }
+    void Signal(PipeRole from, PipeSlot slot, PipeRole consumer)
+    {
+        for (uint32_t d = 1; d < m.n; ++d) Tasks(from).push_back(Task{TaskType::POST, (m.me + d) % m.n, ch * 8 + slot, {}, {}, 0});
+        Tasks(from).push_back(Task{TaskType::LOCAL_POST, Q(consumer), 0, {}, {}, 0});
+    }
+    void Wait(PipeRole at, PipeSlot slot, PipeRole producer)
+    {
+        for (uint32_t d = 1; d < m.n; ++d) Tasks(at).push_back(Task{TaskType::WAIT, (m.me + d) % m.n, ch * 8 + slot, {}, {}, 0});
+        Tasks(at).push_back(Task{TaskType::LOCAL_WAIT, Q(producer), 0, {}, {}, 0});
+    }
+    void Copy(PipeRole r, BufRef d, BufRef s, uint64_t len) { if (len) Tasks(r).push_back(Task{TaskType::LOCAL_COPY, 0, 0, d, s, len}); }
+    // dst (local) <- every rank's scratch at cclOff, combined in rank order
+    void GatherReduce(PipeRole r, BufRef dst, uint64_t cclOff, uint64_t len)
+    {
+        if (!len) return;
+        for (uint32_t q = 0; q < m.n; ++q) {
+            const bool first = q == 0;
+            if (q == m.me) Tasks(r).push_back(Task{first ? TaskType::LOCAL_COPY : TaskType::LOCAL_REDUCE, 0, 0, dst, Model::Ccl(cclOff), len});
+            else Tasks(r).push_back(Task{first ? TaskType::READ : TaskType::READ_REDUCE, q, 0, dst, Model::Ccl(cclOff), len});
+        }
+    }
+    void WriteTo(PipeRole r, uint32_t peer, uint64_t cclOff, BufRef src, uint64_t len)
+    {
+        if (!len) return;
+        if (peer == m.me) Copy(r, Model::Ccl(cclOff), src, len);
+        else Tasks(r).push_back(Task{TaskType::WRITE, peer, 0, Model::Ccl(cclOff), src, len});
+    }
+};
+
+Pipe MakePipe(Model &m, uint32_t ch, const std::vector<uint64_t> &blockBytes)
+{
+    const CollArgs &A = m.A();
+    Pipe p{m, ch, m.C, A.pipeSub, 0};
+    uint64_t longest = 0;
+    for (uint64_t b : blockBytes) longest = std::max(longest, PartOf(b, m.C, ch).len);
+    p.chunks = (uint32_t)((longest + p.sub - 1) / p.sub);
+    return p;
+}
+
+void AllReducePipe(Model &m)
+{
+    const CollArgs &A = m.A();
+    const uint64_t bytes = A.bytes, slice = Up128((bytes + m.n - 1) / m.n);
+    std::vector<uint64_t> lens(m.n);
+    for (uint32_t j = 0; j < m.n; ++j) lens[j] = SliceLen(bytes, slice, j);
+    for (uint32_t ch = 0; ch < m.C; ++ch) {
+        Pipe p = MakePipe(m, ch, lens);
+        const uint64_t resBase = p.RingBytes();
+        const Part mine = PartOf(lens[m.me], m.C, ch);
+        for (uint32_t c = 0; c < p.chunks; ++c) {
+            const uint32_t d = c % kPipeDepth;
+            const bool reused = c + kPipeDepth < p.chunks;                 // somebody will wait for this chunk's slot to be free again
+            // stagers: input -> staging ring, one slot per destination slice
+            if (c >= kPipeDepth) p.Wait(ROLE_A, S_MOVED_STAGER, ROLE_B);
+            for (uint32_t j = 0; j < m.n; ++j) {
+                Part pj = PartOf(lens[j], m.C, ch);
+                p.Copy(ROLE_A, Model::Ccl(p.Slot(d, j)), m.In((uint64_t)j * slice + pj.off + (uint64_t)c * p.sub), Pipe::SubLen(pj.len, p.sub, c));
+            }
+            p.Signal(ROLE_A, S_STAGED_MOVER, ROLE_B);
+            // movers: reduce the own slice over all ranks' staging slots, store the result into every rank's result ring
+            p.Wait(ROLE_B, S_STAGED_MOVER, ROLE_A);
+            if (c >= kPipeDepth) p.Wait(ROLE_B, S_DRAINED_MOVER, ROLE_C);
+            const uint64_t len = Pipe::SubLen(mine.len, p.sub, c), res = resBase + p.Slot(d, m.me);
+            p.GatherReduce(ROLE_B, Model::Ccl(res), p.Slot(d, m.me), len);
+            for (uint32_t q = 1; q < m.n; ++q) p.WriteTo(ROLE_B, (m.me + q) % m.n, res, Model::Ccl(res), len);
+            if (reused) p.Signal(ROLE_B, S_MOVED_STAGER, ROLE_A);
+            p.Signal(ROLE_B, S_MOVED_DRAINER, ROLE_C);
+            // drainers: result ring -> output
+            p.Wait(ROLE_C, S_MOVED_DRAINER, ROLE_B);
+            for (uint32_t j = 0; j < m.n; ++j) {
+                Part pj = PartOf(lens[j], m.C, ch);
+                p.Copy(ROLE_C, m.Out((uint64_t)j * slice + pj.off + (uint64_t)c * p.sub), Model::Ccl(resBase + p.Slot(d, j)), Pipe::SubLen(pj.len, p.sub, c));
+            }
+            if (reused) p.Signal(ROLE_C, S_DRAINED_MOVER, ROLE_B);
+        }
+    }
+}
+
+void ReduceScatterPipe(Model &m)
+{
+    const CollArgs &A = m.A();
+    std::vector<uint64_t> lens(A.sendBytes, A.sendBytes + m.n);
+    for (uint32_t ch = 0; ch < m.C; ++ch) {
+        Pipe p = MakePipe(m, ch, lens);
+        const Part mine = PartOf(lens[m.me], m.C, ch);
+        for (uint32_t c = 0; c < p.chunks; ++c) {
+            const uint32_t d = c % kPipeDepth;
+            const bool reused = c + kPipeDepth < p.chunks;
+            if (c >= kPipeDepth) p.Wait(ROLE_A, S_MOVED_STAGER, ROLE_B);
+            for (uint32_t j = 0; j < m.n; ++j) {
+                Part pj = PartOf(lens[j], m.C, ch);
+                p.Copy(ROLE_A, Model::Ccl(p.Slot(d, j)), m.In(A.sendOff[j] + pj.off + (uint64_t)c * p.sub), Pipe::SubLen(pj.len, p.sub, c));
+            }
+            p.Signal(ROLE_A, S_STAGED_MOVER, ROLE_B);
+            p.Wait(ROLE_B, S_STAGED_MOVER, ROLE_A);
+            p.GatherReduce(ROLE_B, m.Out(mine.off + (uint64_t)c * p.sub), p.Slot(d, m.me), Pipe::SubLen(mine.len, p.sub, c));
+            if (reused) p.Signal(ROLE_B, S_MOVED_STAGER, ROLE_A);
+        }
+    }
+}
+
+// AllGather(V), Broadcast as a one-contributor gather, and (a2a) AlltoAll with uniform counts: movers push, drainers copy out
+void AllGatherPipe(Model &m, bool a2a)
+{
+    const CollArgs &A = m.A();
+    std::vector<uint64_t> lens(A.recvBytes, A.recvBytes + m.n);
+    const bool inPlace = !a2a && (uintptr_t)A.in == (uintptr_t)A.out + A.recvOff[m.me];
+    for (uint32_t ch = 0; ch < m.C; ++ch) {
+        Pipe p = MakePipe(m, ch, lens);
+        const Part mine = PartOf(lens[m.me], m.C, ch);
+        for (uint32_t c = 0; c < p.chunks; ++c) {
+            const uint32_t d = c % kPipeDepth;
+            const bool reused = c + kPipeDepth < p.chunks;
+            if (c >= kPipeDepth) p.Wait(ROLE_A, S_DRAINED_MOVER, ROLE_B);
+            for (uint32_t q = 0; q < m.n; ++q) {
+                const uint32_t dst = (m.me + q) % m.n;
+                if (a2a) {
+                    Part ps = PartOf(A.sendBytes[dst], m.C, ch);
+                    p.WriteTo(ROLE_A, dst, p.Slot(d, m.me), m.In(A.sendOff[dst] + ps.off + (uint64_t)c * p.sub), Pipe::SubLen(ps.len, p.sub, c));
+                } else if (mine.len) {
+                    p.WriteTo(ROLE_A, dst, p.Slot(d, m.me), m.In(mine.off + (uint64_t)c * p.sub), Pipe::SubLen(mine.len, p.sub, c));
+                }
+            }
+            p.Signal(ROLE_A, S_MOVED_DRAINER, ROLE_B);
+            p.Wait(ROLE_B, S_MOVED_DRAINER, ROLE_A);
+            for (uint32_t q = 0; q < m.n; ++q) {
+                const uint32_t j = (m.me + q) % m.n;
+                if (j == m.me && inPlace) continue;
+                Part pj = PartOf(lens[j], m.C, ch);
+                p.Copy(ROLE_B, m.Out(A.recvOff[j] + pj.off + (uint64_t)c * p.sub), Model::Ccl(p.Slot(d, j)), Pipe::SubLen(pj.len, p.sub, c));
+            }
+            if (reused) p.Signal(ROLE_B, S_DRAINED_MOVER, ROLE_A);
+        }
+    }
+}
 }  // namespace
 
 // Model of rank `me`'s kernel for one chunk. `all` = that chunk's launch on every rank (the V forms read peers' counts);
@@ -423,8 +581,12 @@ void AlltoAllV(Model &m)
 HcclResult GenSmModelPlan(const std::vector<SmLaunch> &all, uint32_t me, uintptr_t inBase, uintptr_t outBase, uint32_t channels, Plan *out)
 {
     Model m{all, me, (uint32_t)all.size(), std::max(1u, channels), inBase, outBase, false, out};
+    const SmKernelId kid = all[me].kernel;
+    const bool pipelined = kid == K_ALLREDUCE_PIPE || kid == K_ALLREDUCE_PIPE_NVLS || kid == K_REDUCESCATTER_PIPE || kid == K_REDUCESCATTER_PIPE_NVLS ||
+                           kid == K_ALLGATHER_PIPE || kid == K_ALLGATHER_PIPE_NVLS || kid == K_ALLTOALL_PIPE;
+    if (pipelined) m.C = std::max(1u, all[me].ctas);      // slot addresses and the sub-chunk size depend on the grid: model the launch's own
     out->queues.clear();
-    out->EnsureQueues(m.C);
+    out->EnsureQueues(pipelined ? m.C * 3 : m.C);
     out->dtype = all[me].dtype;
     out->op = (HcclReduceOp)all[me].args.op;
     switch (all[me].kernel) {
@@ -449,8 +611,12 @@ HcclResult GenSmModelPlan(const std::vector<SmLaunch> &all, uint32_t me, uintptr
         case K_SCATTER: Scatter(m); break;
         case K_ALLTOALL_V: AlltoAllV(m); break;
         case K_BARRIER: for (uint32_t ch = 0; ch < m.C; ++ch) m.Barrier(ch); break;
+        case K_ALLREDUCE_PIPE: case K_ALLREDUCE_PIPE_NVLS: AllReducePipe(m); break;        // the switch forms move the same data
+        case K_REDUCESCATTER_PIPE: case K_REDUCESCATTER_PIPE_NVLS: ReduceScatterPipe(m); break;
+        case K_ALLGATHER_PIPE: case K_ALLGATHER_PIPE_NVLS: AllGatherPipe(m, false); break;
+        case K_ALLTOALL_PIPE: AllGatherPipe(m, true); break;
         default:
-            HCCL_ERROR("no schedule model for kernel %u (the pipelined and point-to-point kernels are checked with emulated ranks)", (unsigned)all[me].kernel);
+            HCCL_ERROR("no schedule model for kernel %u (the point-to-point kernels are checked as host-issued mailbox plans)", (unsigned)all[me].kernel);
             return HCCL_E_NOT_SUPPORT;
     }
     return HCCL_SUCCESS;

@@ -193,3 +193,35 @@ def test_sm_alltoallv_and_v_forms(nranks):
     assert rc == 0, msg
     rc, msg = check(CMD["REDUCE_SCATTER_V"], "SmReduceScatterVMesh1D", (1, 1, nranks), 0, counts=counts, ccl=(1 << 20))
     assert rc == 0, msg
+
+
+PIPELINED = {
+    "ALLREDUCE": ["SmAllReducePipelined", "NvlsAllReducePipelined"],
+    "REDUCE_SCATTER": ["SmReduceScatterPipelined", "NvlsReduceScatterPipelined"],
+    "ALLGATHER": ["SmAllGatherPush", "NvlsAllGatherPush"],
+    "BROADCAST": ["SmBroadcastPush", "NvlsBroadcastPush"],
+    "ALLTOALL": ["SmAlltoAllPush"],
+}
+
+
+@pytest.mark.parametrize("nranks", [2, 4, 5])
+def test_pipelined_kernel_models(nranks):
+    """The warp-specialised pipelines as three queues per channel: deadlock freedom of the STAGED / MOVED / DRAINED protocol, ring slots
+    inside the scratch window, no slot rewritten while a peer may still read it, and the operator's result -- over one sub-chunk, a few,
+    and many trips round the two-deep ring."""
+    for op, algs in PIPELINED.items():
+        for alg in algs:
+            for count, ccl in ((5, 256 << 10), (4099, 256 << 10), (60_001, 64 << 10)):
+                if alg.startswith("Nvls") and (count * 4) % 16:
+                    count += 4 - count % 4                     # the switch forms take whole 16-byte vectors
+                rc, msg = check(CMD[op], alg, (1, 1, nranks), count, root=nranks - 1, ccl=ccl)
+                assert rc == 0, (alg, count, msg)
+
+
+def test_pipelined_model_walks_the_longest_part_of_any_slice():
+    """Counts at which the last channel's part of the (shorter) last slice needs one sub-chunk more than its part of the first slice:
+    a loop sized by the first slice alone would leave the tail of the buffer unreduced, and the checker would report a wrong result."""
+    rc, msg = check(CMD["ALLREDUCE"], "SmAllReducePipelined", (1, 1, 4), 311_873, ccl=256 << 10)
+    assert rc == 0, msg
+    rc, msg = check(CMD["ALLREDUCE"], "SmAllReducePipelined", (1, 1, 3), 101_121, ccl=64 << 10)
+    assert rc == 0, msg

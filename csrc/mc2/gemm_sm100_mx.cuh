@@ -47,7 +47,7 @@ template <int BN> struct GemmMxSmem {
     static constexpr int kSfCols = 4 + 4 * kAtomsB;                  // per stage: A atom, then B atoms
     static constexpr int kSfColBase = kAccs * BN <= 256 ? 256 : 384;
     static_assert(kAccs * BN <= kSfColBase && kSfColBase + kStages * kSfCols <= 512, "tensor memory layout");
-    static_assert(kTotal + 1024 <= 232448, "shared memory budget");
+    static_assert(kTotal + 1024 <= 232448, "shared memory per CTA");
 };
 
 template <int BN, class Policy, bool EMU>

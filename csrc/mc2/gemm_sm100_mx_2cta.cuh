@@ -59,7 +59,7 @@ template <int BN_> struct GemmMx2CtaSmem {
     static constexpr int kSfCols = 4 + 4 * kAtomsB;
     static constexpr int kSfColBase = kAccs * BN <= 256 ? 256 : 384;
     static_assert(kSfColBase + kStages * kSfCols <= 512, "tensor memory layout");
-    static_assert(kTotal + 1024 <= 232448, "shared memory budget");
+    static_assert(kTotal + 1024 <= 232448, "shared memory per CTA");
     static_assert(kBBytes % 1024 == 0, "B half is a whole number of swizzle atoms");
 };
 

@@ -79,6 +79,30 @@ def test_planner_degenerate_cases_keep_one_share():
     assert sorted(shares) == [0, 600]
 
 
+def test_planner_invariants_over_random_grids():
+    """Whatever the grid, the bandwidths and the size: the shares cover the block exactly, a cut between two shares is aligned, step counts
+    stay within bounds, the priced times are positive, and a faster level 1 never shrinks the share that leans on it (the one that starts inside the server and then
+    forwards the server's blocks over level 1)."""
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=300, deadline=None)
+    @given(st.sampled_from(["ALLGATHER", "REDUCE_SCATTER", "ALLREDUCE"]), st.integers(1, 16), st.floats(1.0, 1000.0), st.integers(1, 16),
+           st.floats(1.0, 1000.0), st.integers(1, 1 << 30))
+    def prop(op, n0, bw0, n1, bw1, nbytes):
+        shares, steps, seq, par = plan(op, n0, bw0, n1, bw1, nbytes)
+        assert sum(shares) == nbytes
+        assert seq > 0 and par > 0
+        if shares[0] and shares[1]:
+            assert shares[0] % 512 == 0                      # the cut; the second share takes the (possibly unaligned) rest
+        for b, k in zip(shares, steps):
+            assert (b == 0) == (k == 0) and k <= 4
+        faster = plan(op, n0, bw0, n1, bw1 * 4.0, nbytes)[0]
+        if op == "ALLGATHER":
+            assert faster[0] >= shares[0] - 512
+
+    prop()
+
+
 # ---------------------------------------------------------------------------------------------------------------- checker
 @pytest.mark.parametrize("topo", [(1, 2, 2), (1, 2, 4), (1, 3, 2), (1, 4, 2), (1, 2, 8)])
 @pytest.mark.parametrize("op", ["ALLGATHER", "REDUCE_SCATTER", "ALLREDUCE"])

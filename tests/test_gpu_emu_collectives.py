@@ -154,8 +154,9 @@ def test_broadcast_reduce_scatter_rooted(emu_mod, root):
             assert torch.equal(recv[r], send[root][r * count:(r + 1) * count])
 
 
-def test_alltoall_and_v(emu_mod):
-    nranks, count = 4, 777
+@pytest.mark.parametrize("nranks", [3, 4, 8])
+def test_alltoall_and_v(emu_mod, nranks):
+    count = 777
     with emu_mod.EmuWorld(nranks, 1 << 20) as w:
         send = [_rand(count * nranks, torch.float32, r) for r in range(nranks)]
         recv = [torch.zeros(count * nranks, dtype=torch.float32, device="cuda") for _ in range(nranks)]
@@ -178,10 +179,10 @@ def test_alltoall_and_v(emu_mod):
                 ro += M[j][i]
 
 
-def test_alltoallv_zero_row_zero_column_and_pairs_above_the_scratch_half(emu_mod):
+@pytest.mark.parametrize("nranks", [4, 8])
+def test_alltoallv_zero_row_zero_column_and_pairs_above_the_scratch_half(emu_mod, nranks):
     """One rank sends nothing, one rank receives nothing, and some pairs carry more than half of the scratch window
     (64 KB window here, pairs of up to 100 KB), so the kernel has to loop over credit rounds with uneven pair lengths."""
-    nranks = 4
     M = [[(5000 * ((i + 2 * j) % 4) + 17 * (i + 1)) for j in range(nranks)] for i in range(nranks)]
     M[0][3] = 25_000                                   # 100 KB of fp32 in one pair
     M[3][0] = 1

@@ -15,7 +15,7 @@ def _rel(out, ref):
     return (out.float() - ref).abs().max().item() / (ref.abs().max().item() + 1e-6)
 
 
-@pytest.mark.parametrize("nranks,m_local,N,K", [(2, 128, 256, 256), (4, 256, 512, 512), (2, 384, 768, 1024), (4, 128, 264, 320)])
+@pytest.mark.parametrize("nranks,m_local,N,K", [(2, 128, 256, 256), (4, 256, 512, 512), (2, 384, 768, 1024), (4, 128, 264, 320), (8, 128, 512, 256)])
 def test_allgather_matmul(nranks, m_local, N, K):
     from hccl_b200.utils import emu
     ctas = 148 // nranks
@@ -30,7 +30,7 @@ def test_allgather_matmul(nranks, m_local, N, K):
                 assert _rel(out[r], full @ b[r].float().t()) < 2e-2
 
 
-@pytest.mark.parametrize("nranks,M,N,K", [(2, 256, 256, 256), (4, 512, 512, 384), (2, 512, 776, 512)])
+@pytest.mark.parametrize("nranks,M,N,K", [(2, 256, 256, 256), (4, 512, 512, 384), (2, 512, 776, 512), (8, 1024, 520, 256)])
 def test_matmul_reduce_scatter(nranks, M, N, K):
     from hccl_b200.utils import emu
     ctas = 148 // nranks
@@ -48,7 +48,7 @@ def test_matmul_reduce_scatter(nranks, M, N, K):
                 assert _rel(out[r], ref[r * rows:(r + 1) * rows]) < 1e-2
 
 
-@pytest.mark.parametrize("nranks,M,N,K", [(2, 128, 256, 256), (4, 128, 1024, 512), (4, 64, 512, 256), (2, 200, 256, 128)])
+@pytest.mark.parametrize("nranks,M,N,K", [(2, 128, 256, 256), (4, 128, 1024, 512), (4, 64, 512, 256), (2, 200, 256, 128), (8, 128, 1024, 256)])
 def test_matmul_all_reduce(nranks, M, N, K):
     from hccl_b200.utils import emu
     ctas = min(148 // nranks, ((M + 127) // 128) * (N // 64))

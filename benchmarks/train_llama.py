@@ -118,8 +118,14 @@ def main():
             os.environ.setdefault("HCCL_MAX_CTAS", "16")   # as DataParallel does: few CTAs for a collective that overlaps the backward pass
             import hccl_b200.parallel  # noqa: F401  (registers the "hccl" backend)
             grp = dist.new_group(backend="hccl")
-            model = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local], bucket_cap_mb=a.bucket_mb, gradient_as_bucket_view=True,
-                                                              process_group=grp)
+            dist.all_reduce(torch.zeros(1, device=dev), group=grp)      # creates the group's CUDA communicator
+            from contextlib import nullcontext
+
+            from hccl_b200.parallel import process_group as hpg
+            ddp_pool = None if a.staged_buckets else hpg.mem_pool()     # DDP's gradient buckets become registered windows
+            with (torch.cuda.use_mem_pool(ddp_pool) if ddp_pool is not None else nullcontext()):
+                model = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local], bucket_cap_mb=a.bucket_mb, gradient_as_bucket_view=True,
+                                                                  process_group=grp)
         else:
             model = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local], bucket_cap_mb=a.bucket_mb, gradient_as_bucket_view=True)
 

@@ -144,6 +144,14 @@ HcclResult HcclSetAllocatorComm(HcclComm comm)
     return HCCL_SUCCESS;
 }
 
+HcclResult HcclGetAllocatorComm(HcclComm *comm)
+{
+    if (!comm) return HCCL_E_PTR;
+    void *h = g_allocatorComm.load();
+    *comm = CommFromHandle(h) ? h : nullptr;
+    return HCCL_SUCCESS;
+}
+
 void *HcclAllocHook(long long bytes, int device, void * /*stream*/)
 {
     Comm *c = CommFromHandle(g_allocatorComm.load());

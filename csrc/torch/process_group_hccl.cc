@@ -21,6 +21,7 @@
 #include <mutex>
 
 #include "hccl/hccl.h"
+#include "hccl/hccl_res.h"
 #include "hccl/hccl_dfx.h"
 
 namespace {
@@ -183,6 +184,11 @@ public:
             HCCL_TORCH_CHECK(HcclCommInitRootInfoConfig((uint32_t)getSize(), &info, (uint32_t)getRank(), &cfg, &e.comm));
             C10_CUDA_CHECK(cudaStreamCreateWithFlags(&e.stream, cudaStreamNonBlocking));
             C10_CUDA_CHECK(cudaEventCreateWithFlags(&e.inputReady, cudaEventDisableTiming));
+            // The first CUDA communicator of the process serves the allocator hooks (unless the application attached one itself), so that
+            // tensors created under hccl_b200.parallel.process_group.mem_pool() -- DistributedDataParallel's buckets, for instance --
+            // are registered windows and their collectives run without staging copies.
+            HcclComm attached = nullptr;
+            if (HcclGetAllocatorComm(&attached) == HCCL_SUCCESS && attached == nullptr) HcclSetAllocatorComm(e.comm);
         } else {
             HCCL_TORCH_CHECK(HcclCommInitRootInfoConfig((uint32_t)getSize(), &info, (uint32_t)getRank(), &cfg, &e.comm));
         }

@@ -49,3 +49,27 @@ def register_backend() -> None:
 
 
 register_backend()
+
+
+def mem_pool():
+    """A torch.cuda.MemPool whose segments are registered blocks of the symmetric heap of this process's "hccl" CUDA communicator
+    (the one created by the group's first CUDA collective; run one before calling this). Tensors created under it need no staging
+    copy in AllReduce / ReduceScatter / AllGather / Broadcast from 1 MB up:
+
+        dist.all_reduce(torch.zeros(1, device="cuda"))                  # creates the communicator
+        pool = hccl_b200.parallel.process_group.mem_pool()
+        with torch.cuda.use_mem_pool(pool):
+            ddp = DistributedDataParallel(model, device_ids=[dev])       # its gradient buckets become registered windows
+
+    Every rank has to make the same allocations in the same order inside the pool. Set HCCL_SYM_HEAP_MB above what the pool will hold."""
+    import ctypes
+
+    import torch
+
+    l = _lib.lib()
+    h = ctypes.c_void_p()
+    l.HcclGetAllocatorComm.argtypes = [ctypes.POINTER(ctypes.c_void_p)]
+    if l.HcclGetAllocatorComm(ctypes.byref(h)) != 0 or not h.value:
+        raise RuntimeError("no CUDA communicator yet: run one collective on a CUDA tensor through the hccl group first")
+    alloc = torch.cuda.memory.CUDAPluggableAllocator(str(_lib.LIB_PATH), "HcclAllocHook", "HcclFreeHook")
+    return torch.cuda.MemPool(alloc.allocator())

@@ -51,6 +51,7 @@ HcclResult HcclCommMemDereg(HcclComm comm, void *addr);
 HcclResult HcclMemAlloc(HcclComm comm, uint64_t bytes, void **ptr);
 HcclResult HcclMemFree(HcclComm comm, void *ptr);
 HcclResult HcclSetAllocatorComm(HcclComm comm);
+HcclResult HcclGetAllocatorComm(HcclComm *comm);          /* NULL when nothing (live) is attached */
 void *HcclAllocHook(long long bytes, int device, void *stream);
 void HcclFreeHook(void *ptr, long long bytes, int device, void *stream);
 

@@ -72,6 +72,31 @@ def main():
     gs = [torch.zeros_like(g) for _ in range(world)]
     dist.all_gather(gs, g)
     assert all(torch.allclose(gs[0], gi, atol=1e-6) for gi in gs), "DDP gradients differ across ranks"
+    if use_cuda and world > 1:
+        # tensors from the memory pool over registered blocks of the group's communicator: the all-reduce runs on the window directly
+        import ctypes
+
+        from hccl_b200._lib import lib
+        from hccl_b200.parallel import process_group as hpg
+        pool = hpg.mem_pool()
+        with torch.cuda.use_mem_pool(pool):
+            big = torch.full((1 << 20,), float(rank + 1), device=dev)
+        dist.all_reduce(big)
+        torch.cuda.synchronize()
+        assert torch.all(big == world * (world + 1) / 2)
+
+        class Rec(ctypes.Structure):
+            _fields_ = [("seq", ctypes.c_uint64), ("opType", ctypes.c_uint32), ("dataType", ctypes.c_uint32), ("reduceOp", ctypes.c_uint32),
+                        ("root", ctypes.c_uint32), ("engine", ctypes.c_uint32), ("pad", ctypes.c_uint32), ("count", ctypes.c_uint64),
+                        ("algName", ctypes.c_char * 64), ("beginNs", ctypes.c_uint64), ("endNs", ctypes.c_uint64)]
+        h, recs, cnt = ctypes.c_void_p(), (Rec * 1)(), ctypes.c_uint32()
+        assert lib().HcclGetAllocatorComm(ctypes.byref(h)) == 0 and h.value
+        assert lib().HcclGetLastOps(h, recs, 1, ctypes.byref(cnt)) == 0 and cnt.value == 1
+        alg = recs[0].algName.decode()
+        assert alg.endswith("ZeroCopy") or "HCCL_ZERO_COPY" in os.environ or "HCCL_ALGO_NAME" in os.environ, alg
+        if rank == 0:
+            print(f"pool tensor all-reduce ran {alg}", flush=True)
+        del big, pool
     if use_cuda:
         torch.cuda.synchronize()
     dist.destroy_process_group()

@@ -225,3 +225,48 @@ def test_pipelined_model_walks_the_longest_part_of_any_slice():
     assert rc == 0, msg
     rc, msg = check(CMD["ALLREDUCE"], "SmAllReducePipelined", (1, 1, 3), 101_121, ccl=64 << 10)
     assert rc == 0, msg
+
+
+def test_random_geometries_of_every_kernel_model():
+    """Random rank counts, element counts and scratch sizes for every SM / NVLS / pipelined algorithm: the model of each kernel restates
+    its index arithmetic, so an off-by-one in slices, parts, sub-chunks or chunk loops shows up as a wrong element, an overrun or a race.
+    A scratch window that is too small for an algorithm must be refused by the planner (a non-zero status without a verdict on the
+    schedule), never mis-scheduled."""
+    from hypothesis import given, settings, strategies as st
+
+    every = [(op, a) for op, algs in SM_ALGOS.items() for a in algs] + [(op, a) for op, algs in PIPELINED.items() for a in algs]
+
+    @settings(max_examples=120, deadline=None)
+    @given(st.sampled_from(every), st.integers(2, 8), st.integers(1, 30_000), st.sampled_from([32 << 10, 96 << 10, 256 << 10, 1 << 20]), st.integers(0, 7))
+    def prop(case, nranks, count, ccl, root):
+        op, alg = case
+        if alg.startswith("Nvls") or "ZeroCopy" in alg:
+            count = (count + 3) // 4 * 4                      # whole 16-byte vectors of fp32
+        rc, msg = check(CMD[op], alg, (1, 1, nranks), count, root=root % nranks, ccl=ccl)
+        if rc != 0:
+            # refusals are fine (window too small, shape not supported); verdicts about the schedule are not
+            assert not any(w in msg for w in ("semantic error", "conflict", "overrun", "deadlock", "never waited", "disagree")), (alg, nranks, count, ccl, msg)
+
+    prop()
+
+
+def test_random_count_matrices_of_the_variable_forms():
+    """AlltoAllV with random count matrices (zeros included) through scratch windows small enough for several rounds, and the V forms of
+    AllGather / ReduceScatter on the mesh and the pipelined kernels with random per-rank counts."""
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=80, deadline=None)
+    @given(st.integers(2, 8), st.data())
+    def prop(nranks, data):
+        cell = st.sampled_from([0, 0, 1, 3, 100, 1029, 7000])
+        cm = data.draw(st.lists(cell, min_size=nranks * nranks, max_size=nranks * nranks))
+        ccl = data.draw(st.sampled_from([8 << 10, 24 << 10, 1 << 20]))
+        rc, msg = check(CMD["ALLTOALLV"], "SmAlltoAllVMesh1D", (1, 1, nranks), 0, counts=cm, ccl=ccl)
+        assert rc == 0 or not any(w in msg for w in ("semantic error", "conflict", "overrun", "deadlock", "never waited", "disagree")), (nranks, cm, ccl, msg)
+        counts = data.draw(st.lists(cell, min_size=nranks, max_size=nranks))
+        for op, alg in (("ALLGATHER_V", "SmAllGatherVMesh1D"), ("REDUCE_SCATTER_V", "SmReduceScatterVMesh1D"), ("ALLGATHER_V", "SmAllGatherVPush"),
+                        ("REDUCE_SCATTER_V", "SmReduceScatterVPipelined")):
+            rc, msg = check(CMD[op], alg, (1, 1, nranks), 0, counts=counts, ccl=256 << 10)
+            assert rc == 0 or not any(w in msg for w in ("semantic error", "conflict", "overrun", "deadlock", "never waited", "disagree")), (alg, nranks, counts, msg)
+
+    prop()

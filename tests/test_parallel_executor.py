@@ -114,6 +114,19 @@ def test_parallel_plans_pass_the_schedule_checker(op, topo):
         assert rc == 0, (count, msg)
 
 
+def test_parallel_plans_over_random_layouts_and_counts():
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=40, deadline=None)
+    @given(st.sampled_from(["ALLGATHER", "REDUCE_SCATTER", "ALLREDUCE"]), st.integers(2, 4), st.integers(2, 4), st.integers(1, 50_000))
+    def prop(op, servers, per, count):
+        alg = {"ALLGATHER": "InsAllGatherParallelMesh1DMesh1D", "REDUCE_SCATTER": "InsReduceScatterParallelMesh1DMesh1D", "ALLREDUCE": "InsAllReduceParallelMesh1DMesh1D"}[op]
+        rc, msg = check(op, alg, (1, servers, per), count, ccl=64 << 20)
+        assert rc == 0, (op, servers, per, count, msg)
+
+    prop()
+
+
 def test_parallel_plan_reports_a_scratch_window_that_is_too_small():
     rc, msg = check("ALLGATHER", "InsAllGatherParallelMesh1DMesh1D", (1, 2, 4), 300_000, ccl=1 << 20)
     assert rc != 0

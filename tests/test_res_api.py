@@ -3,8 +3,9 @@ blobs, memory registration, rank graph queries on flat and multi-server topologi
 import ctypes
 
 import numpy as np
+import pytest
 
-from hccl_b200._lib import HcclCommConfig, lib
+from hccl_b200._lib import HcclError, HcclCommConfig, lib
 from hccl_b200.types import Result
 from hccl_b200.utils.sim import run_ranks
 
@@ -171,6 +172,23 @@ def test_mem_alloc_is_a_registered_block_and_allocator_hooks_follow_the_attached
     l.HcclFreeHook(vp(res[0][1]), 1 << 20, 0, None)
     assert l.HcclAllocHook(4096, 0, None) is None
     assert l.HcclSetAllocatorComm(vp(12345)) == Result.E_PTR
+
+
+def test_python_wrappers_for_registered_memory():
+    def body(comm, rank):
+        p = comm.mem_alloc(1 << 16)
+        q = comm.mem_alloc(4096)
+        assert p and q and p != q
+        comm.mem_free(q)
+        assert comm.mem_alloc(4096) == q                      # first fit: the freed block comes back
+        comm.mem_free(q)
+        comm.mem_free(p)
+        with pytest.raises(HcclError):
+            comm.mem_free(p)                                  # already returned
+        return p
+
+    res = run_ranks(2, body)
+    assert res[0] and res[1]
 
 
 def test_cta_cap_is_a_per_communicator_setting():

@@ -302,6 +302,7 @@ HcclResult CommDestroy(Comm *c)
         if (!g_comms.count(c)) return HCCL_E_PARA;
         g_comms.erase(c);
     }
+    AllocatorCommDetach(c);             // allocator hooks must not find a later communicator at this address
     StopWatchdog(c);
     if (c->worker) c->worker->Drain();
     // Teardown order: (1) every rank drains its own device, (2) host barrier, (3) unmap / unbind. After (2) all ranks

@@ -158,6 +158,7 @@ HcclResult SymFree(Comm *c, void *ptr);
 bool SymContains(Comm *c, const void *ptr, uint64_t bytes);
 uint64_t SymOffsetOf(Comm *c, const void *ptr);
 // Registered windows (HcclCommMemReg): ranges of the symmetric heap the zero-copy kernels may address on every rank.
+void AllocatorCommDetach(Comm *c);   // res_api.cc: forget `c` as the communicator behind HcclAllocHook / HcclFreeHook
 HcclResult CommRegisterWindow(Comm *c, const void *ptr, uint64_t bytes, uint64_t *off);
 HcclResult CommDeregisterWindow(Comm *c, const void *ptr);
 bool CommRegisteredOffset(Comm *c, const void *ptr, uint64_t bytes, uint64_t *off);

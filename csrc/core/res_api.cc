@@ -137,6 +137,16 @@ HcclResult HcclMemFree(HcclComm comm, void *ptr)
 // after the communicator's destruction (a framework's pool releasing its segments at exit) does nothing.
 static std::atomic<void *> g_allocatorComm{nullptr};
 
+}  // extern "C"
+namespace hccl {
+void AllocatorCommDetach(Comm *c)
+{
+    void *expected = c;
+    g_allocatorComm.compare_exchange_strong(expected, nullptr);
+}
+}  // namespace hccl
+extern "C" {
+
 HcclResult HcclSetAllocatorComm(HcclComm comm)
 {
     if (comm && !Live(comm)) return HCCL_E_PTR;

@@ -364,8 +364,7 @@ HcclResult GenSequencePlan(const OpParam &p, const TopoInfo &topo, uint64_t cclB
     CHK_RET(TopoMatch(topo, TopoMatchKind::MULTI_LEVEL, &h));
     if (h.levelRanks.size() < 2) return HCCL_E_NOT_SUPPORT;
     uint32_t es = DataTypeSize(p.dtype);
-    const auto &g0 = h.levelRanks[0];
-    uint32_t n0 = (uint32_t)g0.size(), me0 = h.myIndex[0];
+    uint32_t n0 = (uint32_t)h.levelRanks[0].size(), me0 = h.myIndex[0];
     plan->dtype = p.dtype;
     plan->op = p.reduceOp;
     auto baseCtx = [&](uint32_t level) {
@@ -402,6 +401,8 @@ HcclResult GenSequencePlan(const OpParam &p, const TopoInfo &topo, uint64_t cclB
         CHK_RET(Tmpl("InsAllGatherVMesh1D")->gen(g, plan));
         return HCCL_SUCCESS;
     }
+    // AllGather and ReduceScatter are written for two levels: everything above the server counts as one
+    if (h.levelRanks.size() > 2) CHK_RET(TopoMatch(topo, TopoMatchKind::TWO_LEVEL, &h));
     if (h.levelRanks.size() != 2) return HCCL_E_NOT_SUPPORT;
     const auto &g1 = h.levelRanks[1];
     uint32_t n1 = (uint32_t)g1.size();
@@ -446,6 +447,107 @@ HcclResult GenSequencePlan(const OpParam &p, const TopoInfo &topo, uint64_t cclB
     }
     return HCCL_E_NOT_SUPPORT;
 }
+
+// Rooted operators on two levels. The root's column (the ranks at the root's position in every server) is the only
+// level-1 group that carries data: Broadcast crosses the servers once and fans out inside each one; Reduce sums inside
+// every server onto the root's position and then across the servers (server order, so the bits do not depend on timing);
+// Scatter moves each server's blocks to that server's member of the column, which hands them out. A message that does
+// not fit the scratch is cut into chunks, one plan each; every template used here ends in a barrier of its group, so a
+// plan may reuse the scratch half of the plan before the previous one.
+// HCCL builds the same shapes as its sequence executors for the rooted operators (reference:
+// src/ops/broadcast/executor/ins_broadcast_sequence_executor.cc, src/ops/reduce/executor/ins_reduce_sequence_executor.cc,
+// src/ops/scatter/executor/ins_v2_scatter_sequence_executor.cc).
+HcclResult GenSequenceRootedPlans(const OpParam &p, const TopoInfo &topo, uint64_t cclBytes, std::vector<Plan> *plans)
+{
+    AlgHierarchyInfo h;
+    CHK_RET(TopoMatch(topo, TopoMatchKind::TWO_LEVEL, &h));
+    if (h.levelRanks.size() != 2) return HCCL_E_NOT_SUPPORT;
+    const auto &g0 = h.levelRanks[0], &g1 = h.levelRanks[1];
+    const uint32_t n0 = (uint32_t)g0.size(), n1 = (uint32_t)g1.size(), me0 = h.myIndex[0], es = DataTypeSize(p.dtype);
+    // servers hold consecutive ranks, n0 each: server s starts at rank s * n0
+    for (uint32_t s = 0; s < n1; ++s) if (g1[s] != s * n0 + me0) return HCCL_E_NOT_SUPPORT;
+    if (p.root >= n0 * n1) return HCCL_E_PARA;
+    const uint32_t rootServer = p.root / n0, rootPos = p.root % n0;
+    const bool inColumn = me0 == rootPos;
+
+    // scratch per chunk of c elements, in units of S = Al(c * es): Broadcast 2 S, Reduce (1 + n0 + n1) S, Scatter (2 n0 + n1) S
+    const uint64_t units = p.opType == HCCL_CMD_BROADCAST ? 2 : p.opType == HCCL_CMD_REDUCE ? 1 + n0 + n1 : 2 * n0 + n1;
+    const uint64_t slack = 4 * 4096;
+    if (cclBytes < slack + units * 512) return HCCL_E_MEMORY;
+    uint64_t maxCount = (cclBytes - slack) / units / 512 * 512 / es;
+    if (maxCount == 0) return HCCL_E_MEMORY;
+    auto ctxOf = [&](uint32_t level) {
+        TemplateCtx c;
+        c.group = h.levelRanks[level];
+        c.me = h.myIndex[level];
+        c.elemSize = es;
+        return c;
+    };
+    plans->clear();
+    for (uint64_t lo = 0; lo < std::max<uint64_t>(p.count, 1); lo += maxCount) {
+        const uint64_t cnt = std::min(maxCount, p.count - lo), S = Al(cnt * es);
+        Plan pl;
+        pl.dtype = p.dtype;
+        pl.op = p.reduceOp;
+        pl.EnsureQueues(1);
+        if (cnt == 0) { plans->push_back(std::move(pl)); break; }
+        if (p.opType == HCCL_CMD_BROADCAST) {
+            const char *t = cnt * es >= (64u << 10) ? "InsBroadcastMesh1DTwoShot" : "InsBroadcastMesh1DOneShot";
+            if (inColumn && n1 > 1) {
+                TemplateCtx a = ctxOf(1);
+                a.count = cnt; a.root = rootServer; a.in = a.out = {BufKind::OUTPUT, lo * es}; a.inPlace = true; a.cclOff = 0; a.cclBytes = S + 4096;
+                CHK_RET(Tmpl(t)->gen(a, &pl));
+            }
+            TemplateCtx b = ctxOf(0);
+            b.count = cnt; b.root = rootPos; b.in = b.out = {BufKind::OUTPUT, lo * es}; b.inPlace = true; b.cclOff = S + 4096; b.cclBytes = S + 4096;
+            CHK_RET(Tmpl(t)->gen(b, &pl));
+        } else if (p.opType == HCCL_CMD_REDUCE) {
+            const uint64_t win0 = S, win1 = win0 + n0 * S + 4096;
+            const bool isRoot = inColumn && h.myIndex[1] == rootServer;
+            TemplateCtx a = ctxOf(0);
+            a.count = cnt; a.root = rootPos; a.in = {BufKind::INPUT, lo * es}; a.out = {BufKind::CCL, 0}; a.cclOff = win0; a.cclBytes = n0 * S + 4096;
+            if (n1 == 1 && isRoot) a.out = {BufKind::OUTPUT, lo * es};
+            CHK_RET(Tmpl("ReduceMesh1D")->gen(a, &pl));
+            if (inColumn && n1 > 1) {
+                TemplateCtx b = ctxOf(1);
+                b.count = cnt; b.root = rootServer; b.in = {BufKind::CCL, 0}; b.out = isRoot ? BufRef{BufKind::OUTPUT, lo * es} : BufRef{BufKind::CCL, 0};
+                b.cclOff = win1; b.cclBytes = n1 * S + 4096;
+                CHK_RET(Tmpl("ReduceMesh1D")->gen(b, &pl));
+            }
+        } else if (p.opType == HCCL_CMD_SCATTER) {
+            // stage area: the n0 blocks of my server, S apart; filled over level 1 by one scatter per position of the server
+            const uint64_t win1 = n0 * S, win0 = win1 + n1 * S + 4096;
+            if (inColumn) {
+                for (uint32_t j = 0; j < n0; ++j) {
+                    TemplateCtx a = ctxOf(1);
+                    a.count = cnt; a.root = rootServer;
+                    a.in = {BufKind::INPUT, ((uint64_t)j * p.count + lo) * es}; a.inStride = (uint64_t)n0 * p.count * es;
+                    a.out = {BufKind::CCL, (uint64_t)j * S}; a.cclOff = win1; a.cclBytes = n1 * S + 4096;
+                    if (n1 > 1) CHK_RET(Tmpl("InsScatterMesh1D")->gen(a, &pl));
+                    else pl.queues[0].push_back(Task{TaskType::LOCAL_COPY, 0, 0, a.out, a.in, cnt * es});
+                }
+            }
+            TemplateCtx b = ctxOf(0);
+            b.count = cnt; b.root = rootPos; b.in = {BufKind::CCL, 0}; b.inStride = S; b.out = {BufKind::OUTPUT, lo * es}; b.cclOff = win0; b.cclBytes = n0 * S + 4096;
+            CHK_RET(Tmpl("InsScatterMesh1D")->gen(b, &pl));
+        } else {
+            return HCCL_E_NOT_SUPPORT;
+        }
+        plans->push_back(std::move(pl));
+    }
+    return HCCL_SUCCESS;
+}
+
+class IrSequenceRootedExecutor : public ExecutorBase {
+public:
+    HcclResult Orchestrate(Comm *c, OpParam &p) override
+    {
+        std::vector<Plan> plans;
+        CHK_RET(GenSequenceRootedPlans(p, c->topo, c->devComm.cclBytes, &plans));
+        for (Plan &pl : plans) CHK_RET(RunPlan(c, p, std::make_shared<Plan>(std::move(pl)), true));
+        return HCCL_SUCCESS;
+    }
+};
 
 class IrSequenceExecutor : public ExecutorBase {
 public:
@@ -502,6 +604,9 @@ void RegisterBuiltinExecutors()
         R.Register("InsAllReduceSequenceMesh1DNhr", HCCL_CMD_ALLREDUCE, [] { return static_cast<ExecutorBase *>(new IrSequenceExecutor()); });
         R.Register("InsAllGatherSequenceNhrMesh1D", HCCL_CMD_ALLGATHER, [] { return static_cast<ExecutorBase *>(new IrSequenceExecutor()); });
         R.Register("InsReduceScatterSequenceMesh1DNhr", HCCL_CMD_REDUCE_SCATTER, [] { return static_cast<ExecutorBase *>(new IrSequenceExecutor()); });
+        R.Register("InsBroadcastSequenceMesh1DMesh1D", HCCL_CMD_BROADCAST, [] { return static_cast<ExecutorBase *>(new IrSequenceRootedExecutor()); });
+        R.Register("InsReduceSequenceMesh1DMesh1D", HCCL_CMD_REDUCE, [] { return static_cast<ExecutorBase *>(new IrSequenceRootedExecutor()); });
+        R.Register("InsScatterSequenceMesh1DMesh1D", HCCL_CMD_SCATTER, [] { return static_cast<ExecutorBase *>(new IrSequenceRootedExecutor()); });
         R.Register("InsAllReduceParallelMesh1DMesh1D", HCCL_CMD_ALLREDUCE, [] { return static_cast<ExecutorBase *>(new IrParallelExecutor()); });
         R.Register("InsAllGatherParallelMesh1DMesh1D", HCCL_CMD_ALLGATHER, [] { return static_cast<ExecutorBase *>(new IrParallelExecutor()); });
         R.Register("InsReduceScatterParallelMesh1DMesh1D", HCCL_CMD_REDUCE_SCATTER, [] { return static_cast<ExecutorBase *>(new IrParallelExecutor()); });

@@ -79,6 +79,8 @@ HcclResult GenBatchSendRecvPlan(uint32_t me, uint32_t nranks, const std::vector<
                                 Plan *p, std::vector<char *> *itemBufs);
 // Multi-level plan for AllReduce / AllGather / ReduceScatter (whole op, no chunk loop).
 HcclResult GenSequencePlan(const OpParam &p, const TopoInfo &topo, uint64_t cclBytes, Plan *plan);
+// Broadcast, Reduce and Scatter on two levels; one plan per chunk of the message that fits the scratch.
+HcclResult GenSequenceRootedPlans(const OpParam &p, const TopoInfo &topo, uint64_t cclBytes, std::vector<Plan> *plans);
 // Two-level plan with both levels busy at once (parallel_executor.cc); slices = the planner's decision, if asked for.
 struct SlicePlan;
 HcclResult GenParallelPlan(const OpParam &p, const TopoInfo &topo, uint64_t cclBytes, Plan *plan, SlicePlan *slices = nullptr);

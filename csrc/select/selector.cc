@@ -392,6 +392,12 @@ SelectorStatus IrDefault(const SelectorCtx &ctx, OpParam &p)
         if (p.opType == HCCL_CMD_ALLREDUCE) { p.algName = "InsAllReduceSequenceMesh1DNhr"; return SelectorStatus::MATCH; }
         if (p.opType == HCCL_CMD_ALLGATHER) { p.algName = "InsAllGatherSequenceNhrMesh1D"; return SelectorStatus::MATCH; }
         if (p.opType == HCCL_CMD_REDUCE_SCATTER) { p.algName = "InsReduceScatterSequenceMesh1DNhr"; return SelectorStatus::MATCH; }
+        // rooted operators: the data crosses the servers once, through the root's column
+        if (ctx.topo->symmetric) {
+            if (p.opType == HCCL_CMD_BROADCAST) { p.algName = "InsBroadcastSequenceMesh1DMesh1D"; return SelectorStatus::MATCH; }
+            if (p.opType == HCCL_CMD_REDUCE) { p.algName = "InsReduceSequenceMesh1DMesh1D"; return SelectorStatus::MATCH; }
+            if (p.opType == HCCL_CMD_SCATTER) { p.algName = "InsScatterSequenceMesh1DMesh1D"; return SelectorStatus::MATCH; }
+        }
     }
     const char *nm = IrAlgoFor(p.opType, forced, p.DataBytes(), ctx.topo->nranks, ctx.cclBytes);
     if (!nm) return SelectorStatus::NOT_MATCH;

@@ -261,6 +261,17 @@ HcclResult TopoMatch(const TopoInfo &topo, TopoMatchKind kind, AlgHierarchyInfo 
         }
         if (!found) { HCCL_ERROR("rank %u is in no group of level %u", topo.rank, l); return HCCL_E_INTERNAL; }
     }
+    if (kind == TopoMatchKind::TWO_LEVEL && out->levelRanks.size() > 2) {
+        if (!topo.symmetric) { HCCL_ERROR("servers of unequal size: the levels above the server cannot be folded into one"); return HCCL_E_NOT_SUPPORT; }
+        const uint32_t pos = out->myIndex[0];
+        std::vector<uint32_t> across;
+        for (const auto &g : topo.levels[0]) across.push_back(g[pos]);
+        std::sort(across.begin(), across.end());
+        out->levelRanks.resize(1);
+        out->myIndex.resize(1);
+        out->myIndex.push_back((uint32_t)(std::find(across.begin(), across.end(), topo.rank) - across.begin()));
+        out->levelRanks.push_back(std::move(across));
+    }
     if (kind == TopoMatchKind::THREE_LEVEL)
         while (out->levelRanks.size() < 3) { out->levelRanks.push_back({topo.rank}); out->myIndex.push_back(0); }
     return HCCL_SUCCESS;

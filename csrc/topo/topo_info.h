@@ -87,7 +87,9 @@ struct AlgHierarchyInfo {
 // square factorisation) for two-phase algorithms. LINK_ISLANDS: level 0 = ranks that reach each other over NVLink, level 1 =
 // same position across the islands (a box whose GPUs are only partly NVLink-connected; the reference's PCIe-mix matcher).
 // (reference: src/ops/op_common/topo/topo_match_1d.h, _multilevel.h, _3_level.h, _squeeze_2d.h, _pcie_mix.h:17-22)
-enum class TopoMatchKind : uint8_t { FLAT_1D, MULTI_LEVEL, THREE_LEVEL, SQUEEZE_2D, LINK_ISLANDS };
+// TWO_LEVEL: the server, and everything above it folded into one group (the ranks at my position of every server of every
+// super-pod, in rank order) for schedules that are written for two levels.
+enum class TopoMatchKind : uint8_t { FLAT_1D, MULTI_LEVEL, THREE_LEVEL, SQUEEZE_2D, LINK_ISLANDS, TWO_LEVEL };
 HcclResult TopoMatch(const TopoInfo &topo, TopoMatchKind kind, AlgHierarchyInfo *out);
 
 // Rank orders for the classic templates on a flat group of n ranks.

@@ -1,0 +1,162 @@
+"""Broadcast, Reduce and Scatter on two levels of the topology (the data crosses the servers once, through the root's column).
+
+The generated plans go through the schedule checker (deadlock, scratch bounds, unordered accesses, symbolic result) for every
+root of several layouts, whole and cut into chunks by a small scratch; then real data runs on the host simulation backend with
+ranks laid out on pretended servers. Reference: src/ops/broadcast/executor/ins_broadcast_sequence_executor.cc,
+src/ops/reduce/executor/ins_reduce_sequence_executor.cc, src/ops/scatter/executor/ins_v2_scatter_sequence_executor.cc."""
+import ctypes
+
+import numpy as np
+import pytest
+
+from hccl_b200._lib import lib
+from hccl_b200.utils.sim import run_ranks
+
+CMD = {"BROADCAST": 1, "REDUCE": 3, "SCATTER": 12}
+ALG = {"BROADCAST": "InsBroadcastSequenceMesh1DMesh1D", "REDUCE": "InsReduceSequenceMesh1DMesh1D", "SCATTER": "InsScatterSequenceMesh1DMesh1D"}
+
+
+def check(op, alg, topo, count, root, ccl=0):
+    l = lib()
+    buf = ctypes.create_string_buffer(1024)
+    l.HcclCheckAlgorithm.argtypes = [ctypes.c_int, ctypes.c_char_p, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint64, ctypes.c_int,
+                                     ctypes.c_uint32, ctypes.POINTER(ctypes.c_uint64), ctypes.c_uint64, ctypes.c_char_p, ctypes.c_uint32]
+    rc = l.HcclCheckAlgorithm(CMD[op], alg.encode(), topo[0], topo[1], topo[2], count, 4, root, None, ccl, buf, 1024)      # dtype 4 = fp32
+    return rc, buf.value.decode()
+
+
+@pytest.mark.parametrize("topo", [(1, 2, 2), (1, 2, 4), (1, 3, 2), (1, 4, 3)])
+@pytest.mark.parametrize("op", ["BROADCAST", "REDUCE", "SCATTER"])
+def test_plans_pass_the_schedule_checker_for_every_root(op, topo):
+    n = topo[1] * topo[2]
+    for root in range(n):
+        for count in (1, 7, 1031) + ((20_000,) if root in (0, n - 1) else ()):
+            rc, msg = check(op, ALG[op], topo, count, root)
+            assert rc == 0, (root, count, msg)
+            rc, msg = check(op, "", topo, count, root)                  # what the checker picks by itself on this layout
+            assert rc == 0 and "Sequence" in msg, (root, count, msg)
+
+
+@pytest.mark.parametrize("op", ["BROADCAST", "REDUCE", "SCATTER"])
+def test_small_scratch_cuts_the_message_into_chunks(op):
+    """96 KB of scratch for 200 KB per rank: several plans, each checked on its own, and together covering the message."""
+    for root in (0, 5):
+        rc, msg = check(op, ALG[op], (1, 2, 4), 50_001, root, ccl=96 << 10)
+        assert rc == 0, (root, msg)
+
+
+@pytest.mark.parametrize("op", ["BROADCAST", "REDUCE", "SCATTER"])
+def test_scratch_too_small_for_any_chunk_is_an_error(op):
+    rc, _ = check(op, ALG[op], (1, 2, 4), 1000, 0, ccl=8 << 10)
+    assert rc != 0
+
+
+@pytest.mark.parametrize("topo", ["1x2x2", "1x2x4", "1x3x2", "2x2x2"])
+def test_rooted_operators_with_real_data(topo, monkeypatch):
+    """The last layout has super-pods: everything above the server is folded into one level for these schedules."""
+    pods, servers, per = (int(v) for v in topo.split("x"))
+    n = pods * servers * per
+    monkeypatch.setenv("HCCL_SIM_TOPO", topo)
+    lib().HcclResetEnvConfigForTest()
+    counts = (1, 5000, 200_003)
+    roots = (0, n - 1, per)                      # first rank, last rank, first rank of the second server
+    rng = np.random.default_rng(17)
+    bc_in = {(c, r): rng.standard_normal(c).astype(np.float32) for c in counts for r in roots}
+    rd_in = {c: [rng.integers(-8, 9, size=c).astype(np.float32) for _ in range(n)] for c in counts}
+    sc_in = {(c, r): rng.standard_normal(c * n).astype(np.float32) for c in counts for r in roots}
+
+    def body(comm, rank):
+        out, algs = {}, set()
+        for c in counts:
+            for root in roots:
+                b = bc_in[(c, root)].copy() if rank == root else np.zeros(c, np.float32)
+                comm.broadcast(b, root)
+                comm.synchronize()
+                algs.add(comm.last_algorithm())
+                red = np.full(c, -1.0, np.float32)
+                comm.reduce(rd_in[c][rank], red, root)
+                comm.synchronize()
+                algs.add(comm.last_algorithm())
+                sc = np.empty(c, np.float32)
+                comm.scatter(sc_in[(c, root)] if rank == root else np.zeros(c * n, np.float32), sc, root)
+                comm.synchronize()
+                algs.add(comm.last_algorithm())
+                out[(c, root)] = (b, red, sc)
+        return out, algs
+
+    try:
+        res = run_ranks(n, body, buffer_mb=4)             # 2 MB per half: the largest count runs in chunks
+    finally:
+        monkeypatch.delenv("HCCL_SIM_TOPO")
+        lib().HcclResetEnvConfigForTest()
+    for rank, (out, algs) in enumerate(res):
+        assert algs == set(ALG.values()), algs
+        for c in counts:
+            want_red = np.sum(np.stack(rd_in[c]).astype(np.float64), axis=0)
+            for root in roots:
+                b, red, sc = out[(c, root)]
+                assert np.array_equal(b, bc_in[(c, root)]), (rank, c, root)
+                if rank == root:
+                    assert np.array_equal(red.astype(np.float64), want_red), (rank, c, root)
+                else:
+                    assert np.all(red == -1.0), (rank, c, root)          # only the root's receive buffer is written
+                assert np.array_equal(sc, sc_in[(c, root)][rank * c:(rank + 1) * c]), (rank, c, root)
+
+
+@pytest.mark.parametrize("op", ["BROADCAST", "REDUCE", "SCATTER"])
+def test_super_pods_fold_into_the_upper_level_for_the_checker(op):
+    for root in (0, 3, 7):
+        rc, msg = check(op, "", (2, 2, 2), 1031, root)
+        assert rc == 0 and "Sequence" in msg, (root, msg)
+
+
+def test_all_gather_and_reduce_scatter_on_three_levels(monkeypatch):
+    """AllGather and ReduceScatter are written for two levels; with super-pods they fold the upper two into one (AllReduce walks all three)."""
+    n = 8
+    monkeypatch.setenv("HCCL_SIM_TOPO", "2x2x2")
+    lib().HcclResetEnvConfigForTest()
+    rng = np.random.default_rng(3)
+    c = 70_001
+    ag_in = [rng.standard_normal(c).astype(np.float32) for _ in range(n)]
+    rs_in = [rng.integers(-8, 9, size=c * n).astype(np.float32) for _ in range(n)]
+
+    def body(comm, rank):
+        g = np.empty(c * n, np.float32)
+        comm.all_gather(ag_in[rank], g)
+        comm.synchronize()
+        a = comm.last_algorithm()
+        s = np.empty(c, np.float32)
+        comm.reduce_scatter(rs_in[rank], s)
+        comm.synchronize()
+        b = comm.last_algorithm()
+        r = rs_in[rank][:c].copy()
+        comm.all_reduce(r)
+        comm.synchronize()
+        return g, s, r, (a, b, comm.last_algorithm())
+
+    try:
+        res = run_ranks(n, body, buffer_mb=64)
+    finally:
+        monkeypatch.delenv("HCCL_SIM_TOPO")
+        lib().HcclResetEnvConfigForTest()
+    want_rs = np.sum(np.stack(rs_in).astype(np.float64), axis=0)
+    for rank, (g, s, r, algs) in enumerate(res):
+        assert all("Sequence" in a for a in algs), algs
+        assert np.array_equal(g, np.concatenate(ag_in))
+        assert np.array_equal(s.astype(np.float64), want_rs[rank * c:(rank + 1) * c])
+        assert np.array_equal(r.astype(np.float64), want_rs[:c])
+
+
+def test_one_level_keeps_the_flat_algorithms(monkeypatch):
+    """Without servers to cross nothing changes: the rooted operators keep their one-level algorithms."""
+    lib().HcclResetEnvConfigForTest()
+
+    def body(comm, rank):
+        b = np.arange(100, dtype=np.float32) if rank == 1 else np.zeros(100, np.float32)
+        comm.broadcast(b, 1)
+        comm.synchronize()
+        return b, comm.last_algorithm()
+
+    for b, alg in run_ranks(4, body):
+        assert np.array_equal(b, np.arange(100, dtype=np.float32))
+        assert "Sequence" not in alg

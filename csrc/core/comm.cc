@@ -234,11 +234,13 @@ HcclResult CommCreate(uint32_t nranks, const HcclRootInfo *info, uint32_t rank, 
     if (!haveCuda)
         if (const char *e = getenv("HCCL_SIM_TOPO"))
             if (const char *at = strchr(e, '@')) {
-                // "...@<GB/s level 0>,<GB/s level 1>": bandwidth weights of the pretended links (what the slice planner balances)
-                double b0 = 0, b1 = 0;
-                if (sscanf(at + 1, "%lf,%lf", &b0, &b1) == 2 && b0 > 0 && b1 > 0 && c->topo.levelBandwidth.size() >= 2) {
+                // "...@<GB/s level 0>,<GB/s level 1>[,<GB/s level 2>]": bandwidth weights of the pretended links (what the slice planner balances)
+                double b0 = 0, b1 = 0, b2 = 0;
+                const int got = sscanf(at + 1, "%lf,%lf,%lf", &b0, &b1, &b2);
+                if (got >= 2 && b0 > 0 && b1 > 0 && c->topo.levelBandwidth.size() >= 2) {
                     c->topo.levelBandwidth[0] = b0;
                     c->topo.levelBandwidth[1] = b1;
+                    if (got == 3 && b2 > 0 && c->topo.levelBandwidth.size() >= 3) c->topo.levelBandwidth[2] = b2;
                 }
             }
     if (haveCuda && nranks <= (uint32_t)kTopoMaxRanks) {

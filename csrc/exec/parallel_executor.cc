@@ -233,7 +233,7 @@ struct Builder {
 HcclResult GenParallelPlan(const OpParam &p, const TopoInfo &topo, uint64_t cclBytes, Plan *plan, SlicePlan *slicesOut)
 {
     AlgHierarchyInfo h;
-    CHK_RET(TopoMatch(topo, TopoMatchKind::MULTI_LEVEL, &h));
+    CHK_RET(TopoMatch(topo, TopoMatchKind::TWO_LEVEL, &h));       // super-pods fold into the upper level
     if (h.levelRanks.size() != 2) return HCCL_E_NOT_SUPPORT;
     const uint32_t n0 = (uint32_t)h.levelRanks[0].size(), n1 = (uint32_t)h.levelRanks[1].size();
     for (uint32_t j = 0; j < n0; ++j)
@@ -256,7 +256,7 @@ HcclResult GenParallelPlan(const OpParam &p, const TopoInfo &topo, uint64_t cclB
     plan->EnsureQueues(1);
 
     AxisSpec a0{n0, topo.levelBandwidth.size() > 0 ? topo.levelBandwidth[0] : 770.0, 2.0};
-    AxisSpec a1{n1, topo.levelBandwidth.size() > 1 ? topo.levelBandwidth[1] : 50.0, 5.0};
+    AxisSpec a1{n1, FoldedUpperBandwidth(topo, 50.0), 5.0};
     SlicePlan sp;
     CHK_RET(PlanSlices(op, a0, a1, p.count * es, kAlign, 4, &sp));
     if (slicesOut) *slicesOut = sp;

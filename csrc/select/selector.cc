@@ -371,17 +371,17 @@ SelectorStatus IrDefault(const SelectorCtx &ctx, OpParam &p)
     const bool batchInvariant = birs && p.opType == HCCL_CMD_REDUCE_SCATTER;
     if (batchInvariant && ctx.topo->numLevels == 1) forced = AlgoType::FULLMESH;
     // multi-level topologies use the sequence executors for the ops that have one
-    if (ctx.topo->numLevels == 2 && forced == AlgoType::DEFAULT && !ctx.cuda && !strict && !batchInvariant &&
+    if (ctx.topo->numLevels >= 2 && forced == AlgoType::DEFAULT && !ctx.cuda && !strict && !batchInvariant &&
         (p.opType == HCCL_CMD_ALLREDUCE || p.opType == HCCL_CMD_ALLGATHER || p.opType == HCCL_CMD_REDUCE_SCATTER)) {
         // Two levels and an engine that runs several queues: when the slice planner prices the form that keeps both levels
         // busy at least a tenth below the sequential one, use it (HCCL_PARALLEL_EXECUTOR=0 keeps the sequence executors).
         static const bool allow = [] { const char *e = getenv("HCCL_PARALLEL_EXECUTOR"); return !(e && e[0] == '0'); }();
         AlgHierarchyInfo h;
-        if (allow && TopoMatch(*ctx.topo, TopoMatchKind::MULTI_LEVEL, &h) == HCCL_SUCCESS && h.levelRanks.size() == 2 && ctx.topo->levelBandwidth.size() >= 2) {
+        if (allow && TopoMatch(*ctx.topo, TopoMatchKind::TWO_LEVEL, &h) == HCCL_SUCCESS && h.levelRanks.size() == 2 && ctx.topo->levelBandwidth.size() >= 2) {
             SlicePlan sp;
             const PipeOp po = p.opType == HCCL_CMD_ALLREDUCE ? PipeOp::ALLREDUCE : p.opType == HCCL_CMD_ALLGATHER ? PipeOp::ALLGATHER : PipeOp::REDUCE_SCATTER;
             if (PlanSlices(po, AxisSpec{(uint32_t)h.levelRanks[0].size(), ctx.topo->levelBandwidth[0], 2.0},
-                           AxisSpec{(uint32_t)h.levelRanks[1].size(), ctx.topo->levelBandwidth[1], 5.0}, p.DataBytes(), 512, 4, &sp) == HCCL_SUCCESS &&
+                           AxisSpec{(uint32_t)h.levelRanks[1].size(), FoldedUpperBandwidth(*ctx.topo, 50.0), 5.0}, p.DataBytes(), 512, 4, &sp) == HCCL_SUCCESS &&
                 (sp.shares.size() == 2 || sp.shares[0].steps > 1) && sp.parallelUs < 0.9 * sp.sequenceUs) {
                 p.algName = po == PipeOp::ALLREDUCE ? "InsAllReduceParallelMesh1DMesh1D" : po == PipeOp::ALLGATHER ? "InsAllGatherParallelMesh1DMesh1D" : "InsReduceScatterParallelMesh1DMesh1D";
                 return SelectorStatus::MATCH;

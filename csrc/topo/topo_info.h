@@ -91,6 +91,14 @@ struct AlgHierarchyInfo {
 // super-pod, in rank order) for schedules that are written for two levels.
 enum class TopoMatchKind : uint8_t { FLAT_1D, MULTI_LEVEL, THREE_LEVEL, SQUEEZE_2D, LINK_ISLANDS, TWO_LEVEL };
 HcclResult TopoMatch(const TopoInfo &topo, TopoMatchKind kind, AlgHierarchyInfo *out);
+// Bandwidth weight of the level that TWO_LEVEL folds everything above the server into: its slowest part.
+inline double FoldedUpperBandwidth(const TopoInfo &topo, double fallback)
+{
+    if (topo.levelBandwidth.size() < 2) return fallback;
+    double bw = topo.levelBandwidth[1];
+    for (size_t l = 2; l < topo.levelBandwidth.size() && l < topo.numLevels; ++l) bw = bw < topo.levelBandwidth[l] ? bw : topo.levelBandwidth[l];
+    return bw;
+}
 
 // Rank orders for the classic templates on a flat group of n ranks.
 std::vector<uint32_t> RingOrder(const std::vector<uint32_t> &group);

@@ -104,7 +104,7 @@ def test_planner_invariants_over_random_grids():
 
 
 # ---------------------------------------------------------------------------------------------------------------- checker
-@pytest.mark.parametrize("topo", [(1, 2, 2), (1, 2, 4), (1, 3, 2), (1, 4, 2), (1, 2, 8)])
+@pytest.mark.parametrize("topo", [(1, 2, 2), (1, 2, 4), (1, 3, 2), (1, 4, 2), (1, 2, 8), (2, 2, 2)])
 @pytest.mark.parametrize("op", ["ALLGATHER", "REDUCE_SCATTER", "ALLREDUCE"])
 def test_parallel_plans_pass_the_schedule_checker(op, topo):
     alg = {"ALLGATHER": "InsAllGatherParallelMesh1DMesh1D", "REDUCE_SCATTER": "InsReduceScatterParallelMesh1DMesh1D", "ALLREDUCE": "InsAllReduceParallelMesh1DMesh1D"}[op]
@@ -158,7 +158,7 @@ def _oracle(xs):
     return acc
 
 
-@pytest.mark.parametrize("topo", ["1x2x2", "1x2x4@2,1", "1x3x2@0.8,0.6"])
+@pytest.mark.parametrize("topo", ["1x2x2", "1x2x4@2,1", "1x3x2@0.8,0.6", "2x2x2@2,1,1"])
 @pytest.mark.parametrize("forced", [True, False], ids=["by-name", "selected"])
 def test_two_level_operators_with_real_data(topo, forced, monkeypatch):
     """Ranks as threads on pretended servers; the same calls once with the parallel executors named and once left to the selector,
@@ -167,6 +167,9 @@ def test_two_level_operators_with_real_data(topo, forced, monkeypatch):
     pods, servers, per = (int(v) for v in topo.split("@")[0].split("x"))
     bw = [float(v) for v in topo.split("@")[1].split(",")] if "@" in topo else None
     n = pods * servers * per
+    servers *= pods                      # super-pods fold into the upper level: every server of every pod
+    if bw and len(bw) == 3:
+        bw = [bw[0], min(bw[1:])]
     monkeypatch.setenv("HCCL_SIM_TOPO", topo)
     if forced:
         monkeypatch.setenv("HCCL_ALGO_NAME", "allreduce=InsAllReduceParallelMesh1DMesh1D;allgather=InsAllGatherParallelMesh1DMesh1D;"

@@ -207,6 +207,109 @@ HcclResult HcclAlltoAllGraphMode(const void *sendBuf, uint64_t sendCount, HcclDa
         return HcclExecOp(c, p);
     });
 }
+// The variable-count forms (reference: src/ops/all_gather_v/all_gather_v_op.h:31, src/ops/reduce_scatter_v/reduce_scatter_v_op.h:30,
+// src/ops/all_to_all_v/all_to_all_v_op.h:36-41). Count and displacement arrays are host arrays of nranks uint64_t, read at the call:
+// a captured graph replays the counts it was captured with.
+HcclResult HcclAllGatherVGraphMode(void *sendBuf, void *recvBuf, uint64_t sendCount, const void *recvCounts, const void *recvDispls, HcclDataType dataType,
+                                   HCCL_GRAPH_MODE_TAIL)
+{
+    return Guard("HcclAllGatherVGraphMode", [&]() -> HcclResult {
+        Comm *c; OpParam p;
+        CHK_RET(GraphCommon(GRAPH_ARGS, &c, &p));
+        CHK_PTR_NULL(recvCounts); CHK_PTR_NULL(recvDispls);
+        CHK_RET(HcomCheckDataType(dataType));
+        const uint64_t *rc = (const uint64_t *)recvCounts, *rd = (const uint64_t *)recvDispls;
+        p.recvCounts.assign(rc, rc + c->nranks);
+        p.recvDispls.assign(rd, rd + c->nranks);
+        uint64_t total = 0;
+        for (uint64_t v : p.recvCounts) { CHK_RET(HcomCheckCount(v)); total += v; }
+        CHK_PRT_RET(p.recvCounts[c->rank] != sendCount, HCCL_ERROR("[EI0003] AllGatherV graph mode: sendCount %llu differs from recvCounts[%u] = %llu",
+                    (unsigned long long)sendCount, c->rank, (unsigned long long)p.recvCounts[c->rank]), HCCL_E_PARA);
+        if (total == 0) return HCCL_SUCCESS;
+        if (sendCount) CHK_PTR_NULL(sendBuf);
+        CHK_PTR_NULL(recvBuf);
+        p.opType = HCCL_CMD_ALLGATHER_V; p.stream = stream; p.inputPtr = sendBuf; p.outputPtr = recvBuf; p.count = sendCount; p.dtype = p.outDtype = dataType;
+        return HcclExecOp(c, p);
+    });
+}
+HcclResult HcclReduceScatterVGraphMode(void *sendBuf, const void *sendCounts, const void *sendDispls, void *recvBuf, uint64_t recvCount, HcclDataType dataType,
+                                       HcclReduceOp op, HCCL_GRAPH_MODE_TAIL)
+{
+    return Guard("HcclReduceScatterVGraphMode", [&]() -> HcclResult {
+        Comm *c; OpParam p;
+        CHK_RET(GraphCommon(GRAPH_ARGS, &c, &p));
+        CHK_PTR_NULL(sendCounts); CHK_PTR_NULL(sendDispls);
+        CHK_PRT_RET(op == HCCL_REDUCE_PROD, HCCL_ERROR("[EI0003] ReduceScatterV supports sum, max and min only"), HCCL_E_NOT_SUPPORT);
+        CHK_RET(HcomCheckReduceDataType(dataType, op));
+        CHK_PRT_RET(dataType == HCCL_DATA_TYPE_UINT64 || dataType == HCCL_DATA_TYPE_FP64, HCCL_ERROR("[EI0003] ReduceScatterV does not support %s", DataTypeName(dataType)),
+                    HCCL_E_NOT_SUPPORT);
+        const uint64_t *sc = (const uint64_t *)sendCounts, *sd = (const uint64_t *)sendDispls;
+        p.sendCounts.assign(sc, sc + c->nranks);
+        p.sendDispls.assign(sd, sd + c->nranks);
+        uint64_t total = 0;
+        for (uint64_t v : p.sendCounts) { CHK_RET(HcomCheckCount(v)); total += v; }
+        CHK_PRT_RET(p.sendCounts[c->rank] != recvCount, HCCL_ERROR("[EI0003] ReduceScatterV graph mode: recvCount %llu differs from sendCounts[%u] = %llu",
+                    (unsigned long long)recvCount, c->rank, (unsigned long long)p.sendCounts[c->rank]), HCCL_E_PARA);
+        if (total == 0) return HCCL_SUCCESS;
+        CHK_PTR_NULL(sendBuf);
+        if (recvCount) CHK_PTR_NULL(recvBuf);
+        p.opType = HCCL_CMD_REDUCE_SCATTER_V; p.stream = stream; p.inputPtr = sendBuf; p.outputPtr = recvBuf; p.count = recvCount; p.dtype = p.outDtype = dataType; p.reduceOp = op;
+        return HcclExecOp(c, p);
+    });
+}
+static HcclResult AlltoAllVGraph(Comm *c, OpParam &p, const void *sendBuf, const void *recvBuf, cudaStream_t stream)
+{
+    uint64_t totalSend = 0, totalRecv = 0;
+    for (uint32_t r = 0; r < c->nranks; ++r) {
+        CHK_RET(HcomCheckCount(p.sendCounts[r])); CHK_RET(HcomCheckCount(p.recvCounts[r]));
+        totalSend += p.sendCounts[r]; totalRecv += p.recvCounts[r];
+    }
+    CHK_PRT_RET(p.sendCounts[c->rank] * DataTypeSize(p.dtype) != p.recvCounts[c->rank] * DataTypeSize(p.outDtype),
+                HCCL_ERROR("[EI0003] AlltoAllV graph mode: the block a rank sends to itself must equal the block it receives from itself"), HCCL_E_PARA);
+    if (totalSend) CHK_PTR_NULL(sendBuf);
+    if (totalRecv) CHK_PTR_NULL(recvBuf);
+    CHK_PRT_RET(sendBuf != nullptr && sendBuf == recvBuf, HCCL_ERROR("[EI0003] AlltoAllV graph mode: sendBuf and recvBuf must differ"), HCCL_E_PARA);
+    p.stream = stream; p.inputPtr = sendBuf; p.outputPtr = const_cast<void *>(recvBuf);
+    return HcclExecOp(c, p);       // ranks without data still take part: the others wait for them
+}
+HcclResult HcclAlltoAllVGraphMode(const void *sendBuf, const void *sendCounts, const void *sdispls, HcclDataType sendType, const void *recvBuf,
+                                  const void *recvCounts, const void *rdispls, HcclDataType recvType, HCCL_GRAPH_MODE_TAIL)
+{
+    return Guard("HcclAlltoAllVGraphMode", [&]() -> HcclResult {
+        Comm *c; OpParam p;
+        CHK_RET(GraphCommon(GRAPH_ARGS, &c, &p));
+        CHK_PTR_NULL(sendCounts); CHK_PTR_NULL(sdispls); CHK_PTR_NULL(recvCounts); CHK_PTR_NULL(rdispls);
+        CHK_RET(HcomCheckDataType(sendType)); CHK_RET(HcomCheckDataType(recvType));
+        const uint32_t n = c->nranks;
+        p.sendCounts.assign((const uint64_t *)sendCounts, (const uint64_t *)sendCounts + n);
+        p.sendDispls.assign((const uint64_t *)sdispls, (const uint64_t *)sdispls + n);
+        p.recvCounts.assign((const uint64_t *)recvCounts, (const uint64_t *)recvCounts + n);
+        p.recvDispls.assign((const uint64_t *)rdispls, (const uint64_t *)rdispls + n);
+        p.opType = HCCL_CMD_ALLTOALLV; p.dtype = sendType; p.outDtype = recvType;
+        return AlltoAllVGraph(c, p, sendBuf, recvBuf, stream);
+    });
+}
+HcclResult HcclAlltoAllVCGraphMode(const void *sendBuf, const void *sendCountMatrix, HcclDataType sendType, const void *recvBuf, HcclDataType recvType,
+                                   HCCL_GRAPH_MODE_TAIL)
+{
+    return Guard("HcclAlltoAllVCGraphMode", [&]() -> HcclResult {
+        Comm *c; OpParam p;
+        CHK_RET(GraphCommon(GRAPH_ARGS, &c, &p));
+        CHK_PTR_NULL(sendCountMatrix);
+        CHK_RET(HcomCheckDataType(sendType)); CHK_RET(HcomCheckDataType(recvType));
+        CHK_PRT_RET(DataTypeSize(sendType) != DataTypeSize(recvType), HCCL_ERROR("[EI0003] AlltoAllVC graph mode: send and receive element sizes differ"), HCCL_E_PARA);
+        const uint32_t n = c->nranks, me = c->rank;
+        const uint64_t *M = (const uint64_t *)sendCountMatrix;
+        p.sendCounts.resize(n); p.sendDispls.resize(n); p.recvCounts.resize(n); p.recvDispls.resize(n);
+        uint64_t so = 0, ro = 0;
+        for (uint32_t j = 0; j < n; ++j) {
+            p.sendCounts[j] = M[(uint64_t)me * n + j]; p.sendDispls[j] = so; so += p.sendCounts[j];
+            p.recvCounts[j] = M[(uint64_t)j * n + me]; p.recvDispls[j] = ro; ro += p.recvCounts[j];
+        }
+        p.opType = HCCL_CMD_ALLTOALLVC; p.dtype = sendType; p.outDtype = recvType;
+        return AlltoAllVGraph(c, p, sendBuf, recvBuf, stream);
+    });
+}
 static HcclResult P2pGraph(HcclCMDType op, void *buf, uint64_t count, HcclDataType dataType, uint32_t peer, HCCL_GRAPH_MODE_TAIL)
 {
     Comm *c; OpParam p;

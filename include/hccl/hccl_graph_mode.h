@@ -28,6 +28,15 @@ HcclResult HcclReduceGraphMode(void *sendBuf, void *recvBuf, uint64_t count, Hcc
 HcclResult HcclScatterGraphMode(void *sendBuf, void *recvBuf, uint64_t recvCount, HcclDataType dataType, uint32_t root, HCCL_GRAPH_MODE_TAIL);
 HcclResult HcclAlltoAllGraphMode(const void *sendBuf, uint64_t sendCount, HcclDataType sendType, const void *recvBuf, uint64_t recvCount,
                                  HcclDataType recvType, HCCL_GRAPH_MODE_TAIL);
+/* Variable-count forms: the count / displacement arrays are host arrays of nranks uint64_t (the matrix: nranks x nranks), read at the call. */
+HcclResult HcclAllGatherVGraphMode(void *sendBuf, void *recvBuf, uint64_t sendCount, const void *recvCounts, const void *recvDispls, HcclDataType dataType,
+                                   HCCL_GRAPH_MODE_TAIL);
+HcclResult HcclReduceScatterVGraphMode(void *sendBuf, const void *sendCounts, const void *sendDispls, void *recvBuf, uint64_t recvCount, HcclDataType dataType,
+                                       HcclReduceOp op, HCCL_GRAPH_MODE_TAIL);
+HcclResult HcclAlltoAllVGraphMode(const void *sendBuf, const void *sendCounts, const void *sdispls, HcclDataType sendType, const void *recvBuf,
+                                  const void *recvCounts, const void *rdispls, HcclDataType recvType, HCCL_GRAPH_MODE_TAIL);
+HcclResult HcclAlltoAllVCGraphMode(const void *sendBuf, const void *sendCountMatrix, HcclDataType sendType, const void *recvBuf, HcclDataType recvType,
+                                   HCCL_GRAPH_MODE_TAIL);
 HcclResult HcclSendGraphMode(void *sendBuf, uint64_t count, HcclDataType dataType, uint32_t destRank, HCCL_GRAPH_MODE_TAIL);
 HcclResult HcclRecvGraphMode(void *recvBuf, uint64_t count, HcclDataType dataType, uint32_t srcRank, HCCL_GRAPH_MODE_TAIL);
 

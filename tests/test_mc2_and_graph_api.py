@@ -158,3 +158,59 @@ def test_graph_mode_resource_queries_and_entry_points():
     for out, g, b in run_ranks(3, body):
         assert out == 6.0 and g == [1.0, 2.0, 3.0] and b == 2.0
     assert l.HcclOpParamGraphModeDestroy(p) == 0
+
+
+def test_graph_mode_variable_count_entry_points():
+    """AllGatherV / ReduceScatterV / AlltoAllV / AlltoAllVC through the graph-mode entries (group name, tag, helper streams and
+    scratch in the tail), against numpy; and the argument checks that differ from the fixed-count forms."""
+    l = _declare()
+    tail = [ctypes.c_char_p, vp, ctypes.c_char_p, ctypes.POINTER(vp), u32, vp, u64]
+    l.HcclAllGatherVGraphMode.argtypes = [vp, vp, u64, vp, vp, ctypes.c_int] + tail
+    l.HcclReduceScatterVGraphMode.argtypes = [vp, vp, vp, vp, u64, ctypes.c_int, ctypes.c_int] + tail
+    l.HcclAlltoAllVGraphMode.argtypes = [vp, vp, vp, ctypes.c_int, vp, vp, vp, ctypes.c_int] + tail
+    l.HcclAlltoAllVCGraphMode.argtypes = [vp, vp, ctypes.c_int, vp, ctypes.c_int] + tail
+    n = 3
+    counts = np.array([5, 0, 1201], np.uint64)                      # per-rank block sizes of the gather / scatter forms
+    displs = np.array([0, 5, 5], np.uint64)
+    total = int(counts.sum())
+    M = np.array([[2, 0, 7], [300, 1, 0], [4, 5, 6]], np.uint64)    # M[i][j]: elements rank i sends to rank j
+    rng = np.random.default_rng(23)
+    ag_in = [rng.standard_normal(int(counts[r])).astype(np.float32) for r in range(n)]
+    rs_in = [rng.integers(-8, 9, size=total).astype(np.float32) for _ in range(n)]
+    a2a_in = [rng.standard_normal(int(M[r].sum())).astype(np.float32) for r in range(n)]
+    FP32, SUM = 4, 0
+
+    def body(comm, rank):
+        name = comm.name.encode()
+        t = lambda tag: (name, None, tag, None, 0, None, 0)
+        g = np.zeros(total, np.float32)
+        x = ag_in[rank] if counts[rank] else np.zeros(1, np.float32)
+        assert l.HcclAllGatherVGraphMode(x.ctypes.data, g.ctypes.data, int(counts[rank]), counts.ctypes.data, displs.ctypes.data, FP32, *t(b"agv")) == 0
+        s = np.zeros(max(1, int(counts[rank])), np.float32)
+        assert l.HcclReduceScatterVGraphMode(rs_in[rank].ctypes.data, counts.ctypes.data, displs.ctypes.data, s.ctypes.data, int(counts[rank]), FP32, SUM, *t(b"rsv")) == 0
+        sc, rc = M[rank].copy(), M[:, rank].copy()
+        sd = np.concatenate([[0], np.cumsum(sc)[:-1]]).astype(np.uint64)
+        rd = np.concatenate([[0], np.cumsum(rc)[:-1]]).astype(np.uint64)
+        o1 = np.zeros(int(rc.sum()), np.float32)
+        assert l.HcclAlltoAllVGraphMode(a2a_in[rank].ctypes.data, sc.ctypes.data, sd.ctypes.data, FP32, o1.ctypes.data, rc.ctypes.data, rd.ctypes.data, FP32, *t(b"a2av")) == 0
+        o2 = np.zeros(int(rc.sum()), np.float32)
+        assert l.HcclAlltoAllVCGraphMode(a2a_in[rank].ctypes.data, M.ctypes.data, FP32, o2.ctypes.data, FP32, *t(b"a2avc")) == 0
+        comm.synchronize()
+        # argument checks: own count must agree with the array; a product reduction is refused; element sizes must agree
+        assert l.HcclAllGatherVGraphMode(x.ctypes.data, g.ctypes.data, int(counts[rank]) + 1, counts.ctypes.data, displs.ctypes.data, FP32, *t(b"bad")) == Result.E_PARA
+        assert l.HcclReduceScatterVGraphMode(rs_in[rank].ctypes.data, counts.ctypes.data, displs.ctypes.data, s.ctypes.data, int(counts[rank]), FP32, 1, *t(b"bad")) == Result.E_NOT_SUPPORT
+        assert l.HcclAlltoAllVCGraphMode(a2a_in[rank].ctypes.data, M.ctypes.data, FP32, o2.ctypes.data, 3, *t(b"bad")) == Result.E_PARA      # fp16 on the receive side
+        assert l.HcclAlltoAllVGraphMode(a2a_in[rank].ctypes.data, None, sd.ctypes.data, FP32, o1.ctypes.data, rc.ctypes.data, rd.ctypes.data, FP32, *t(b"bad")) == Result.E_PTR
+        assert l.HcclAllGatherVGraphMode(x.ctypes.data, g.ctypes.data, int(counts[rank]), counts.ctypes.data, displs.ctypes.data, FP32,
+                                         b"no_such_group", None, b"t", None, 0, None, 0) != 0
+        return g, s[:int(counts[rank])], o1, o2
+
+    res = run_ranks(n, body)
+    want_g = np.concatenate(ag_in)
+    want_rs = np.sum(np.stack(rs_in).astype(np.float64), axis=0)
+    for rank, (g, s, o1, o2) in enumerate(res):
+        assert np.array_equal(g, want_g)
+        lo = int(displs[rank])
+        assert np.array_equal(s.astype(np.float64), want_rs[lo:lo + int(counts[rank])])
+        want = np.concatenate([a2a_in[src][int(M[src, :rank].sum()):int(M[src, :rank + 1].sum())] for src in range(n)])
+        assert np.array_equal(o1, want) and np.array_equal(o2, want)

@@ -61,7 +61,7 @@ struct AlgEnvConfig {
     // B200-specific
     bool nvlsEnable = true;              // HCCL_NVLS_ENABLE=0 keeps every kernel on plain peer loads/stores
     uint32_t maxCtas = 0;                // HCCL_MAX_CTAS caps the grid of collective kernels (0 = selector decides)
-    std::string tuningFile;              // HCCL_TUNING_FILE: json crossover table overriding the built-in one
+    std::string tuningFile;              // HCCL_TUNING_FILE: text crossover table (rows as in hccl_b200/tuning/b200.txt) laid over the built-in one
 };
 
 HcclResult InitEnvConfig();                     // idempotent; parses once

@@ -171,7 +171,7 @@ def build_all(verbose: bool = False) -> None:
 
 
 def package(dest: Path | None = None) -> Path:
-    """dist/hccl_b200-<version>-sm100a.tar.gz: public headers, the built libraries, the Python package and the samples."""
+    """dist/hccl_b200-<version>-sm100a.tar.gz: public headers, the built libraries, the Python package, the samples and the docs."""
     import tarfile
 
     sys.path.insert(0, str(ROOT))
@@ -182,7 +182,7 @@ def package(dest: Path | None = None) -> Path:
     name = f"hccl_b200-{__version__}-sm100a"
     out = dest / f"{name}.tar.gz"
     with tarfile.open(out, "w:gz") as tf:
-        for rel in ("include", "hccl_b200", "examples", "README.md"):
+        for rel in ("include", "hccl_b200", "examples", "docs", "README.md"):
             p = ROOT / rel
             if p.exists():
                 tf.add(p, arcname=f"{name}/{rel}", filter=lambda ti: None if ("__pycache__" in ti.name or ti.name.endswith("/bin")) else ti)

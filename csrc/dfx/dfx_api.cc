@@ -258,15 +258,16 @@ HcclResult HcclCheckAlgorithm(HcclCMDType op, const char *algName, uint32_t supe
             if (algName && *algName) alg = algName;
             else if (topo.numLevels > 1 && (op == HCCL_CMD_ALLREDUCE || op == HCCL_CMD_ALLGATHER || op == HCCL_CMD_REDUCE_SCATTER))
                 alg = op == HCCL_CMD_ALLREDUCE ? "InsAllReduceSequenceMesh1DNhr" : op == HCCL_CMD_ALLGATHER ? "InsAllGatherSequenceNhrMesh1D" : "InsReduceScatterSequenceMesh1DNhr";
-            else if (topo.numLevels >= 2 && topo.symmetric && (op == HCCL_CMD_BROADCAST || op == HCCL_CMD_REDUCE || op == HCCL_CMD_SCATTER))
-                alg = op == HCCL_CMD_BROADCAST ? "InsBroadcastSequenceMesh1DMesh1D" : op == HCCL_CMD_REDUCE ? "InsReduceSequenceMesh1DMesh1D" : "InsScatterSequenceMesh1DMesh1D";
+            else if (topo.numLevels >= 2 && topo.symmetric && (op == HCCL_CMD_BROADCAST || op == HCCL_CMD_REDUCE || op == HCCL_CMD_SCATTER || op == HCCL_CMD_BARRIER))
+                alg = op == HCCL_CMD_BROADCAST ? "InsBroadcastSequenceMesh1DMesh1D" : op == HCCL_CMD_REDUCE ? "InsReduceSequenceMesh1DMesh1D" :
+                      op == HCCL_CMD_SCATTER ? "InsScatterSequenceMesh1DMesh1D" : "InsBarrierSequenceMesh1DMesh1D";
             else { const char *nm = IrAlgoFor(op, AlgoType::DEFAULT, p.DataBytes(), n, cclBytes); if (!nm) return HCCL_E_NOT_SUPPORT; alg = nm; }
             std::vector<Plan> mine;
             if (alg.find("Parallel") != std::string::npos) {
                 Plan pl;
                 CHK_RET(GenParallelPlan(p, topo, cclBytes, &pl));
                 mine.push_back(std::move(pl));
-            } else if (alg.find("Sequence") != std::string::npos && (op == HCCL_CMD_BROADCAST || op == HCCL_CMD_REDUCE || op == HCCL_CMD_SCATTER)) {
+            } else if (alg.find("Sequence") != std::string::npos && (op == HCCL_CMD_BROADCAST || op == HCCL_CMD_REDUCE || op == HCCL_CMD_SCATTER || op == HCCL_CMD_BARRIER)) {
                 CHK_RET(GenSequenceRootedPlans(p, topo, cclBytes, &mine));
             } else if (alg.find("Sequence") != std::string::npos) {
                 Plan pl;

@@ -448,14 +448,14 @@ HcclResult GenSequencePlan(const OpParam &p, const TopoInfo &topo, uint64_t cclB
     return HCCL_E_NOT_SUPPORT;
 }
 
-// Rooted operators on two levels. The root's column (the ranks at the root's position in every server) is the only
+// Rooted operators (and the barrier) on two levels. The root's column (the ranks at the root's position in every server) is the only
 // level-1 group that carries data: Broadcast crosses the servers once and fans out inside each one; Reduce sums inside
 // every server onto the root's position and then across the servers (server order, so the bits do not depend on timing);
 // Scatter moves each server's blocks to that server's member of the column, which hands them out. A message that does
 // not fit the scratch is cut into chunks, one plan each; every template used here ends in a barrier of its group, so a
 // plan may reuse the scratch half of the plan before the previous one.
 // HCCL builds the same shapes as its sequence executors for the rooted operators (reference:
-// src/ops/broadcast/executor/ins_broadcast_sequence_executor.cc, src/ops/reduce/executor/ins_reduce_sequence_executor.cc,
+// src/ops/broadcast/executor/ins_v2_broadcast_sequence_executor.cc, src/ops/reduce/executor/ins_v2_reduce_sequence_executor.cc,
 // src/ops/scatter/executor/ins_v2_scatter_sequence_executor.cc).
 HcclResult GenSequenceRootedPlans(const OpParam &p, const TopoInfo &topo, uint64_t cclBytes, std::vector<Plan> *plans)
 {
@@ -466,6 +466,23 @@ HcclResult GenSequenceRootedPlans(const OpParam &p, const TopoInfo &topo, uint64
     const uint32_t n0 = (uint32_t)g0.size(), n1 = (uint32_t)g1.size(), me0 = h.myIndex[0], es = DataTypeSize(p.dtype);
     // servers hold consecutive ranks, n0 each: server s starts at rank s * n0
     for (uint32_t s = 0; s < n1; ++s) if (g1[s] != s * n0 + me0) return HCCL_E_NOT_SUPPORT;
+    if (p.opType == HCCL_CMD_BARRIER) {
+        // inside the server, then along my column: every member of the column has seen its whole server arrive
+        // (reference: src/ops/barrier/executor/ins_v2_barrier_sequence_executor.cc)
+        Plan pl;
+        pl.dtype = p.dtype;
+        pl.EnsureQueues(1);
+        for (uint32_t level = 0; level < 2; ++level) {
+            TemplateCtx b;
+            b.group = h.levelRanks[level];
+            b.me = h.myIndex[level];
+            b.elemSize = es;
+            CHK_RET(Tmpl("InsBarrierMesh1D")->gen(b, &pl));
+        }
+        plans->clear();
+        plans->push_back(std::move(pl));
+        return HCCL_SUCCESS;
+    }
     if (p.root >= n0 * n1) return HCCL_E_PARA;
     const uint32_t rootServer = p.root / n0, rootPos = p.root % n0;
     const bool inColumn = me0 == rootPos;
@@ -607,6 +624,7 @@ void RegisterBuiltinExecutors()
         R.Register("InsBroadcastSequenceMesh1DMesh1D", HCCL_CMD_BROADCAST, [] { return static_cast<ExecutorBase *>(new IrSequenceRootedExecutor()); });
         R.Register("InsReduceSequenceMesh1DMesh1D", HCCL_CMD_REDUCE, [] { return static_cast<ExecutorBase *>(new IrSequenceRootedExecutor()); });
         R.Register("InsScatterSequenceMesh1DMesh1D", HCCL_CMD_SCATTER, [] { return static_cast<ExecutorBase *>(new IrSequenceRootedExecutor()); });
+        R.Register("InsBarrierSequenceMesh1DMesh1D", HCCL_CMD_BARRIER, [] { return static_cast<ExecutorBase *>(new IrSequenceRootedExecutor()); });
         R.Register("InsAllReduceParallelMesh1DMesh1D", HCCL_CMD_ALLREDUCE, [] { return static_cast<ExecutorBase *>(new IrParallelExecutor()); });
         R.Register("InsAllGatherParallelMesh1DMesh1D", HCCL_CMD_ALLGATHER, [] { return static_cast<ExecutorBase *>(new IrParallelExecutor()); });
         R.Register("InsReduceScatterParallelMesh1DMesh1D", HCCL_CMD_REDUCE_SCATTER, [] { return static_cast<ExecutorBase *>(new IrParallelExecutor()); });

@@ -411,6 +411,91 @@ HcclResult GenScatterMesh(const TemplateCtx &c, Plan *p)
     return HCCL_SUCCESS;
 }
 
+// Tree scatter ("NHR" in HCCL's scatter family, reference: src/ops/scatter/template/aicpu/ins_temp_scatter_nhr.cc): ranks are numbered
+// relative to the root; in the step of distance d (d = P/2, P/4, ..., 1 with P the power of two at or above n) every rank whose
+// relative number is a multiple of 2d hands the blocks of the d ranks that follow its own d to the rank at distance d. The root sends
+// from the user buffer, everyone else from the scratch it received into (its own block first), so a block crosses ceil(log2 n) links
+// at most and the root sends n - 1 blocks in ceil(log2 n) messages instead of n - 1.
+HcclResult GenScatterNhr(const TemplateCtx &c, Plan *p)
+{
+    Emit e(c, p);
+    const uint32_t n = c.N(), r = Mod((int64_t)c.me - c.root, n);
+    const uint64_t B = c.count * c.elemSize, S = AlignUp(B);
+    auto abs = [&](uint32_t rel) { return (rel + c.root) % n; };
+    uint32_t P = 1;
+    while (P < n) P <<= 1;
+    uint32_t step = 0;
+    for (uint32_t d = P >> 1; d >= 1; d >>= 1, ++step) {
+        if (r % (2 * d) == 0 && r + d < n) {
+            const uint32_t to = r + d, hi = std::min(r + 2 * d, n);
+            for (uint32_t q = to; q < hi; ++q) {
+                BufRef src = r == 0 ? Emit::At(c.in, (uint64_t)abs(q) * c.inStride) : e.Ccl((uint64_t)(q - r) * S);
+                e.Write(abs(to), e.Ccl((uint64_t)(q - to) * S), src, B);
+            }
+            e.Post(abs(to), SLOT_STEP_BASE + step);
+        } else if (r % (2 * d) == d) {
+            e.Wait(abs(r - d), SLOT_STEP_BASE + step);
+        }
+    }
+    if (r == 0) e.Copy(c.out, Emit::At(c.in, (uint64_t)c.me * c.inStride), B);
+    else e.Copy(c.out, e.Ccl(0), B);
+    e.Barrier(SLOT_FIN);
+    return HCCL_SUCCESS;
+}
+
+// Broadcast as a scatter of slices from the root followed by the NHR all-gather (reference: src/ops/broadcast/template/aicpu/
+// ins_temp_broadcast_nhr.cc): every rank forwards what it has in ceil(log2 n) steps, so the root sends the payload once.
+HcclResult GenBroadcastNhr(const TemplateCtx &c, Plan *p)
+{
+    Emit e(c, p);
+    const uint32_t n = c.N();
+    Slices sl(c.count, n, c.elemSize);
+    const uint64_t M = sl.MaxLen();
+    if (c.me == c.root) {
+        for (uint32_t k = 1; k < n; ++k) {
+            uint32_t peer = (c.me + k) % n;
+            e.Write(peer, e.Ccl(0), Emit::At(c.out, sl.Off(peer)), sl.Len(peer));
+            e.Post(peer, SLOT_DATA);
+        }
+    } else {
+        e.Wait(c.root, SLOT_DATA);
+        e.Copy(Emit::At(c.out, sl.Off(c.me)), e.Ccl(0), sl.Len(c.me));
+    }
+    BlockRef work = [&](uint32_t j) { return Emit::At(c.out, sl.Off(j)); };
+    BlockLen len = [&](uint32_t j) { return sl.Len(j); };
+    NhrAllGatherPhase(e, work, len, M, M);
+    e.Barrier(SLOT_FIN);
+    return HCCL_SUCCESS;
+}
+
+// Reduce as the NHR reduce-scatter on a private copy of the input followed by a gather of the reduced slices at the root
+// (reference: src/ops/reduce/template/aicpu/reduce_nhr.cc).
+HcclResult GenReduceNhr(const TemplateCtx &c, Plan *p)
+{
+    Emit e(c, p);
+    const uint32_t n = c.N();
+    Slices sl(c.count, n, c.elemSize);
+    const uint64_t M = sl.MaxLen(), stage = NhrStageSlices(n);
+    for (uint32_t j = 0; j < n; ++j) e.Copy(e.Ccl(j * M), Emit::At(c.in, sl.Off(j)), sl.Len(j));
+    BlockRef work = [&](uint32_t j) { return e.Ccl(j * M); };
+    BlockLen len = [&](uint32_t j) { return sl.Len(j); };
+    NhrReduceScatterPhase(e, work, len, (uint64_t)n * M, M);
+    const uint64_t gather = ((uint64_t)n + stage) * M;
+    if (c.me != c.root) {
+        e.Write(c.root, e.Ccl(gather + c.me * M), e.Ccl(c.me * M), sl.Len(c.me));
+        e.Post(c.root, SLOT_READY);
+    } else {
+        e.Copy(Emit::At(c.out, sl.Off(c.me)), e.Ccl(c.me * M), sl.Len(c.me));
+        for (uint32_t k = 1; k < n; ++k) {
+            uint32_t peer = (c.me + k) % n;
+            e.Wait(peer, SLOT_READY);
+            e.Copy(Emit::At(c.out, sl.Off(peer)), e.Ccl(gather + peer * M), sl.Len(peer));
+        }
+    }
+    e.Barrier(SLOT_FIN);
+    return HCCL_SUCCESS;
+}
+
 // ================================================================================================ AlltoAll family
 HcclResult GenAlltoAllMesh(const TemplateCtx &c, Plan *p)
 {
@@ -577,6 +662,12 @@ void RegisterBuiltinIrTemplates()
             [](uint32_t n, uint32_t es, uint64_t ccl) { return PerN(n, es, ccl, 2.0 + 2.0 / n); }, true);
         reg("InsScatterMesh1D", HCCL_CMD_SCATTER, GenScatterMesh,
             [](uint32_t n, uint32_t es, uint64_t ccl) { return PerN(n, es, ccl, (double)n); }, true);
+        reg("InsScatterNHR", HCCL_CMD_SCATTER, GenScatterNhr,
+            [](uint32_t n, uint32_t es, uint64_t ccl) { return PerN(n, es, ccl, (double)n); }, true);
+        reg("InsBroadcastNHR", HCCL_CMD_BROADCAST, GenBroadcastNhr,
+            [](uint32_t n, uint32_t es, uint64_t ccl) { return PerN(n, es, ccl, (1.0 + NhrStageSlices(n)) / n + 1e-9); }, true);
+        reg("InsReduceNHR", HCCL_CMD_REDUCE, GenReduceNhr,
+            [](uint32_t n, uint32_t es, uint64_t ccl) { return PerN(n, es, ccl, (2.0 * n + NhrStageSlices(n)) / n + 1e-9); }, true);
         reg("InsAlltoAllMesh1D", HCCL_CMD_ALLTOALL, GenAlltoAllMesh,
             [](uint32_t n, uint32_t es, uint64_t ccl) { return PerN(n, es, ccl, (double)n); }, true);
         reg("InsAlltoAllVMesh1D", HCCL_CMD_ALLTOALLV, GenAlltoAllVMesh, Unlimited, true);

@@ -190,9 +190,9 @@ const char *IrAlgoFor(HcclCMDType op, AlgoType forced, uint64_t bytes, uint32_t 
             return "InsAllReduceMesh1DTwoShot";
         case HCCL_CMD_ALLGATHER: return ring ? "InsAllGatherRing" : nhr ? "InsAllGatherNHR" : "InsAllGatherMesh1D";
         case HCCL_CMD_REDUCE_SCATTER: return ring ? "InsReduceScatterRing" : nhr ? "InsReduceScatterNHR" : "InsReduceScatterMesh1D";
-        case HCCL_CMD_BROADCAST: return bytes <= (64u << 10) ? "InsBroadcastMesh1DOneShot" : "InsBroadcastMesh1DTwoShot";
-        case HCCL_CMD_REDUCE: return bytes <= (512u << 10) ? "ReduceMesh1D" : "ReduceMesh1DTwoShot";
-        case HCCL_CMD_SCATTER: return "InsScatterMesh1D";
+        case HCCL_CMD_BROADCAST: return nhr ? "InsBroadcastNHR" : bytes <= (64u << 10) ? "InsBroadcastMesh1DOneShot" : "InsBroadcastMesh1DTwoShot";
+        case HCCL_CMD_REDUCE: return nhr ? "InsReduceNHR" : bytes <= (512u << 10) ? "ReduceMesh1D" : "ReduceMesh1DTwoShot";
+        case HCCL_CMD_SCATTER: return nhr ? "InsScatterNHR" : "InsScatterMesh1D";
         case HCCL_CMD_ALLTOALL: return "InsAlltoAllMesh1D";
         case HCCL_CMD_ALLTOALLV: return "InsAlltoAllVMesh1D";
         case HCCL_CMD_ALLTOALLVC: return "InsAlltoAllVCMesh1D";
@@ -397,6 +397,7 @@ SelectorStatus IrDefault(const SelectorCtx &ctx, OpParam &p)
             if (p.opType == HCCL_CMD_BROADCAST) { p.algName = "InsBroadcastSequenceMesh1DMesh1D"; return SelectorStatus::MATCH; }
             if (p.opType == HCCL_CMD_REDUCE) { p.algName = "InsReduceSequenceMesh1DMesh1D"; return SelectorStatus::MATCH; }
             if (p.opType == HCCL_CMD_SCATTER) { p.algName = "InsScatterSequenceMesh1DMesh1D"; return SelectorStatus::MATCH; }
+            if (p.opType == HCCL_CMD_BARRIER) { p.algName = "InsBarrierSequenceMesh1DMesh1D"; return SelectorStatus::MATCH; }
         }
     }
     const char *nm = IrAlgoFor(p.opType, forced, p.DataBytes(), ctx.topo->nranks, ctx.cclBytes);

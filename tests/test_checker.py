@@ -26,9 +26,9 @@ ALGOS = {
     "ALLREDUCE": ["InsAllReduceMesh1DOneShot", "InsAllReduceMesh1DTwoShot", "InsAllReduceRing", "InsAllReduceNHR"],
     "ALLGATHER": ["InsAllGatherMesh1D", "InsAllGatherRing", "InsAllGatherNHR"],
     "REDUCE_SCATTER": ["InsReduceScatterMesh1D", "InsReduceScatterRing", "InsReduceScatterNHR"],
-    "BROADCAST": ["InsBroadcastMesh1DOneShot", "InsBroadcastMesh1DTwoShot"],
-    "REDUCE": ["ReduceMesh1D", "ReduceMesh1DTwoShot"],
-    "SCATTER": ["InsScatterMesh1D"],
+    "BROADCAST": ["InsBroadcastMesh1DOneShot", "InsBroadcastMesh1DTwoShot", "InsBroadcastNHR"],
+    "REDUCE": ["ReduceMesh1D", "ReduceMesh1DTwoShot", "InsReduceNHR"],
+    "SCATTER": ["InsScatterMesh1D", "InsScatterNHR"],
     "ALLTOALL": ["InsAlltoAllMesh1D"],
     "BARRIER": ["InsBarrierMesh1D", "InsBarrierNHR"],
 }
@@ -68,9 +68,8 @@ def test_variable_count_algorithms(nranks):
 @pytest.mark.parametrize("topo", [(1, 2, 2), (1, 2, 4), (1, 3, 2), (1, 4, 2), (2, 2, 2)])
 def test_multi_level_sequence_executors(topo):
     n = topo[0] * topo[1] * topo[2]
-    for op in ("ALLREDUCE", "ALLGATHER", "REDUCE_SCATTER"):
-        if op != "ALLREDUCE" and topo[0] > 1:
-            continue    # three-level gather / reduce-scatter are flattened by the selector
+    for op in ("ALLREDUCE", "ALLGATHER", "REDUCE_SCATTER", "BROADCAST", "REDUCE", "SCATTER", "BARRIER"):
+        # with super-pods AllReduce walks three levels; the others fold the upper two into one
         for count in (1, n, 101):
             rc, msg = check(CMD[op], None, topo, count)
             assert rc == 0, msg

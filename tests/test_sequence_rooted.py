@@ -2,8 +2,8 @@
 
 The generated plans go through the schedule checker (deadlock, scratch bounds, unordered accesses, symbolic result) for every
 root of several layouts, whole and cut into chunks by a small scratch; then real data runs on the host simulation backend with
-ranks laid out on pretended servers. Reference: src/ops/broadcast/executor/ins_broadcast_sequence_executor.cc,
-src/ops/reduce/executor/ins_reduce_sequence_executor.cc, src/ops/scatter/executor/ins_v2_scatter_sequence_executor.cc."""
+ranks laid out on pretended servers. Reference: src/ops/broadcast/executor/ins_v2_broadcast_sequence_executor.cc,
+src/ops/reduce/executor/ins_v2_reduce_sequence_executor.cc, src/ops/scatter/executor/ins_v2_scatter_sequence_executor.cc."""
 import ctypes
 
 import numpy as np
@@ -160,3 +160,84 @@ def test_one_level_keeps_the_flat_algorithms(monkeypatch):
     for b, alg in run_ranks(4, body):
         assert np.array_equal(b, np.arange(100, dtype=np.float32))
         assert "Sequence" not in alg
+
+
+def test_tree_forms_of_the_rooted_operators_with_real_data(monkeypatch):
+    """HCCL_ALGO level1:NHR picks the tree scatter, the scatter + NHR all-gather broadcast and the NHR reduce-scatter + gather reduce
+    (by name: InsScatterNHR, InsBroadcastNHR, InsReduceNHR); odd rank count, every root, a message that runs in chunks."""
+    n = 5
+    monkeypatch.setenv("HCCL_ALGO", "level0:NA;level1:NHR")
+    lib().HcclResetEnvConfigForTest()
+    counts = (1, 7, 150_001)
+    rng = np.random.default_rng(29)
+    bc_in = {(c, r): rng.standard_normal(c).astype(np.float32) for c in counts for r in range(n)}
+    rd_in = {c: [rng.integers(-8, 9, size=c).astype(np.float32) for _ in range(n)] for c in counts}
+    sc_in = {(c, r): rng.standard_normal(c * n).astype(np.float32) for c in counts for r in range(n)}
+
+    def body(comm, rank):
+        out, algs = {}, set()
+        for c in counts:
+            for root in range(n):
+                b = bc_in[(c, root)].copy() if rank == root else np.zeros(c, np.float32)
+                comm.broadcast(b, root)
+                comm.synchronize()
+                algs.add(comm.last_algorithm())
+                red = np.full(c, -1.0, np.float32)
+                comm.reduce(rd_in[c][rank], red, root)
+                comm.synchronize()
+                algs.add(comm.last_algorithm())
+                sc = np.empty(c, np.float32)
+                comm.scatter(sc_in[(c, root)] if rank == root else np.zeros(c * n, np.float32), sc, root)
+                comm.synchronize()
+                algs.add(comm.last_algorithm())
+                comm.barrier()
+                comm.synchronize()
+                algs.add(comm.last_algorithm())
+                out[(c, root)] = (b, red, sc)
+        return out, algs
+
+    try:
+        res = run_ranks(n, body, buffer_mb=2)             # 1 MB per half against 600 KB per rank (x 5 for the scatter)
+    finally:
+        monkeypatch.delenv("HCCL_ALGO")
+        lib().HcclResetEnvConfigForTest()
+    for rank, (out, algs) in enumerate(res):
+        assert algs == {"InsBroadcastNHR", "InsReduceNHR", "InsScatterNHR", "InsBarrierNHR"}, algs
+        for c in counts:
+            want_red = np.sum(np.stack(rd_in[c]).astype(np.float64), axis=0)
+            for root in range(n):
+                b, red, sc = out[(c, root)]
+                assert np.array_equal(b, bc_in[(c, root)]), (rank, c, root)
+                if rank == root:
+                    assert np.array_equal(red.astype(np.float64), want_red), (rank, c, root)
+                else:
+                    assert np.all(red == -1.0), (rank, c, root)
+                assert np.array_equal(sc, sc_in[(c, root)][rank * c:(rank + 1) * c]), (rank, c, root)
+
+
+def test_two_level_barrier_orders_the_ranks(monkeypatch):
+    """Nobody leaves the barrier before everybody has entered: each rank records its arrival in a shared list first."""
+    import threading
+    monkeypatch.setenv("HCCL_SIM_TOPO", "1x3x2")
+    lib().HcclResetEnvConfigForTest()
+    arrived, lock = [], threading.Lock()
+
+    def body(comm, rank):
+        seen = []
+        for it in range(5):
+            with lock:
+                arrived.append((it, rank))
+            comm.barrier()
+            comm.synchronize()
+            with lock:
+                seen.append(sum(1 for i, _ in arrived if i == it))
+        return seen, comm.last_algorithm()
+
+    try:
+        res = run_ranks(6, body)
+    finally:
+        monkeypatch.delenv("HCCL_SIM_TOPO")
+        lib().HcclResetEnvConfigForTest()
+    for seen, alg in res:
+        assert alg == "InsBarrierSequenceMesh1DMesh1D"
+        assert seen == [6] * 5, seen

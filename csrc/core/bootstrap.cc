@@ -86,7 +86,10 @@ public:
     BootstrapRoot(int listenFd, uint32_t nranks) : listenFd_(listenFd), n_(nranks)
     {
         stopFd_ = eventfd(0, EFD_NONBLOCK);
-        lostMs_ = 30000;
+        // HCCL_DFS_CONFIG connection_fault_detection_time (seconds; default 20, 0 = a silent peer is never declared lost, only a closed
+        // connection is); HCCL_HEARTBEAT_LOST_MS overrides it in milliseconds
+        const uint32_t detectSec = GetEnvConfig().connectionFaultDetectionSec;
+        lostMs_ = detectSec ? (int64_t)detectSec * 1000 : INT64_MAX / 4;
         if (const char *e = getenv("HCCL_HEARTBEAT_LOST_MS")) lostMs_ = atoi(e) > 0 ? atoi(e) : lostMs_;
         lastSeen_.assign(n_, 0);
         hbOpen_.assign(n_, false);

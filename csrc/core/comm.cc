@@ -599,7 +599,8 @@ void RecordOp(Comm *c, const OpRecord &r)
 void StartWatchdog(Comm *c)
 {
     c->watchdogStop = false;
-    int periodMs = 1000;
+    // HCCL_DFS_CONFIG task_monitor_interval (ms; 0 = the default of one second) is how often progress is sampled and reported
+    int periodMs = c->env.taskMonitorIntervalMs ? (int)std::min<uint32_t>(c->env.taskMonitorIntervalMs, 60000) : 1000;
     if (const char *e = getenv("HCCL_HEARTBEAT_PERIOD_MS")) if (atoi(e) > 0) periodMs = atoi(e);
     // a third of the execution timeout, as the reference's heartbeat does; HCCL_STUCK_CHECK_MS overrides (tests)
     int64_t stuckMs = (int64_t)c->env.execTimeoutSec * 1000 / 3;

@@ -152,3 +152,32 @@ def test_watchdog_reports_a_stuck_communicator_and_the_slowest_rank(fault_env):
         text, n = res[rank]
         assert n >= 1 and text.startswith("STUCK:") and f"rank {rank} has 0 of" in text and "no progress" in text
     assert res[2][1] == 0                             # nothing is in flight on the rank that skipped the operator
+
+
+def test_task_monitor_interval_sets_the_sampling_period_of_the_watchdog(fault_env):
+    """HCCL_DFS_CONFIG task_monitor_interval:<ms> is how often the watchdog samples progress. A wait of 0.9 s ends before the default
+    period of one second has sampled twice, so no stuck report can be made from it; with 50 ms sampling a 300 ms stall is reported."""
+    def run(dfs):
+        env = dict(HCCL_DEVICE_WAIT_TIMEOUT_MS="900", HCCL_STUCK_CHECK_MS="300")
+        if dfs:
+            env["HCCL_DFS_CONFIG"] = dfs
+        fault_env(**env)
+
+        def body(comm, rank):
+            x = np.ones(32, np.float32)
+            y = np.zeros_like(x)
+            if rank == 1:
+                lib().HcclInjectOpDrop(ctypes.c_void_p(comm.handle), 1)
+            comm.all_reduce(x, y)
+            try:
+                comm.synchronize()
+            except HcclError:
+                pass
+            return _fault_counters(comm)["stuck"]
+
+        return run_ranks(2, body, timeout_s=60)
+
+    assert run("task_monitor_interval:50")[0] >= 1
+    import os
+    os.environ.pop("HCCL_DFS_CONFIG", None)
+    assert run("")[0] == 0

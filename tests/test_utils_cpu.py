@@ -87,3 +87,32 @@ def test_packaged_tuning_table_is_well_formed():
             assert alg in names.value.decode().split(";"), f"{alg} is not a registered algorithm for {op}"
     finally:
         l.HcclTuningTableReset()
+
+
+def test_checker_command_line(tmp_path, capsys):
+    """python -m hccl_b200.utils.check: selector's choice, --all, a multi-level layout with a root, a count matrix, a text schedule with a
+    lost notify (exit status 1) and the slice planner's cut."""
+    from hccl_b200._lib import lib
+    from hccl_b200.utils import check
+
+    try:
+        assert check.main(["--op", "allreduce", "--ranks", "4", "--count", "1000"]) == 0
+        assert "ok: " in capsys.readouterr().out
+        assert check.main(["--op", "scatter", "--ranks", "5", "--count", "77", "--root", "3", "--all"]) == 0
+        out = capsys.readouterr().out
+        assert "ok: InsScatterNHR" in out and "ok: SmScatterMesh1D" in out and "skipped: InsScatterSequenceMesh1DMesh1D" in out and "FAILED" not in out
+        assert check.main(["--op", "broadcast", "--topo", "1x2x4", "--root", "5", "--count", "7001"]) == 0
+        assert "InsBroadcastSequenceMesh1DMesh1D" in capsys.readouterr().out
+        assert check.main(["--op", "alltoallv", "--ranks", "3", "--matrix", "1,0,7,300,1,0,4,5,6"]) == 0
+        capsys.readouterr()
+        # scratch far too small for the named algorithm's smallest chunk: reported, exit status 1
+        assert check.main(["--op", "reduce", "--topo", "1x2x4", "--count", "1000", "--ccl-mb", "0.004"]) == 1
+        assert "FAILED" in capsys.readouterr().out
+        plan = tmp_path / "lost.txt"
+        plan.write_text("op=BARRIER n=2 es=4 count=0 ccl=4096\nr0: POST 1 2; WAIT 1 2\nr1: WAIT 0 2\n")
+        assert check.main(["--plan", str(plan)]) == 1
+        assert "FAILED" in capsys.readouterr().out
+        assert check.main(["--slices", "--op", "allgather", "--levels", "8@770,4@50", "--bytes", "67108864"]) == 0
+        assert "modelled time" in capsys.readouterr().out
+    finally:
+        lib().HcclSetLogLevel(2)

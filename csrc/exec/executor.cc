@@ -487,11 +487,24 @@ HcclResult GenSequenceRootedPlans(const OpParam &p, const TopoInfo &topo, uint64
     const uint32_t rootServer = p.root / n0, rootPos = p.root % n0;
     const bool inColumn = me0 == rootPos;
 
-    // scratch per chunk of c elements, in units of S = Al(c * es): Broadcast 2 S, Reduce (1 + n0 + n1) S, Scatter (2 n0 + n1) S
-    const uint64_t units = p.opType == HCCL_CMD_BROADCAST ? 2 : p.opType == HCCL_CMD_REDUCE ? 1 + n0 + n1 : 2 * n0 + n1;
+    // Two forms. The column form moves the whole message through the root's column (two hops; small messages). The spread form
+    // gives every column a share: Broadcast scatters slices inside the root's server, broadcasts each along its column and gathers
+    // inside every server; Reduce is its mirror (reduce-scatter inside every server, reduce along the columns, gather at the root);
+    // Scatter hands each member of the root's server the blocks of its column and scatters along the columns. The root's link to
+    // the other servers then carries 1 / n0 of the bytes. Both forms of Reduce sum in the same order (ranks of a server, then
+    // servers), so the bits do not depend on the form.
+    const uint64_t kSpreadBytes = 256u << 10;
+    const bool spread = n0 > 1 && n1 > 1 && (p.opType == HCCL_CMD_SCATTER || p.count * es >= kSpreadBytes);
+    // scratch per chunk, in units of the aligned piece S: column form Broadcast 2 S, Reduce (1 + n0 + n1) S, Scatter (2 n0 + n1) S with
+    // S = Al(c * es); spread form Broadcast (n0 + 2) S, Reduce (n0 + n1 + 3) S with S = Al(ceil(c / n0) * es), Scatter (2 n1 + n0) S
+    uint64_t units;
+    if (p.opType == HCCL_CMD_BROADCAST) units = spread ? n0 + 2 : 2;
+    else if (p.opType == HCCL_CMD_REDUCE) units = spread ? n0 + n1 + 3 : 1 + n0 + n1;
+    else units = spread ? 2 * n1 + n0 : 2 * n0 + n1;
     const uint64_t slack = 4 * 4096;
     if (cclBytes < slack + units * 512) return HCCL_E_MEMORY;
     uint64_t maxCount = (cclBytes - slack) / units / 512 * 512 / es;
+    if (spread && p.opType != HCCL_CMD_SCATTER) maxCount *= n0;                 // the piece is a slice of the chunk
     if (maxCount == 0) return HCCL_E_MEMORY;
     auto ctxOf = [&](uint32_t level) {
         TemplateCtx c;
@@ -500,6 +513,8 @@ HcclResult GenSequenceRootedPlans(const OpParam &p, const TopoInfo &topo, uint64
         c.elemSize = es;
         return c;
     };
+    const bool inRootServer = h.myIndex[1] == rootServer;
+    const bool isRoot = inColumn && inRootServer;
     plans->clear();
     for (uint64_t lo = 0; lo < std::max<uint64_t>(p.count, 1); lo += maxCount) {
         const uint64_t cnt = std::min(maxCount, p.count - lo), S = Al(cnt * es);
@@ -508,19 +523,59 @@ HcclResult GenSequenceRootedPlans(const OpParam &p, const TopoInfo &topo, uint64
         pl.op = p.reduceOp;
         pl.EnsureQueues(1);
         if (cnt == 0) { plans->push_back(std::move(pl)); break; }
-        if (p.opType == HCCL_CMD_BROADCAST) {
-            const char *t = cnt * es >= (64u << 10) ? "InsBroadcastMesh1DTwoShot" : "InsBroadcastMesh1DOneShot";
+        // slices of the chunk over the positions of a server (spread forms of Broadcast and Reduce)
+        const uint64_t per = (cnt + n0 - 1) / n0, Sa = Al(per * es);
+        std::vector<uint64_t> len(n0), off(n0);
+        for (uint32_t k = 0; k < n0; ++k) { off[k] = std::min(cnt, per * k) * es; len[k] = Clamp(cnt, per * k, per) * es; }
+        const char *bcast = nullptr;
+        auto bcastFor = [](uint64_t bytes) { return bytes >= (64u << 10) ? "InsBroadcastMesh1DTwoShot" : "InsBroadcastMesh1DOneShot"; };
+        if (p.opType == HCCL_CMD_BROADCAST && spread) {
+            const uint64_t winB = n0 * Sa + 4096, winC = winB + Sa + 4096;
+            if (inRootServer) {
+                TemplateCtx a = ctxOf(0);
+                a.root = rootPos; a.in = {BufKind::OUTPUT, lo * es}; a.out = {BufKind::OUTPUT, lo * es + off[me0]};
+                a.sendBytes = len; a.sendOff = off; a.inPlace = true; a.cclOff = 0; a.cclBytes = winB;
+                CHK_RET(Tmpl("InsScatterMesh1D")->gen(a, &pl));
+            }
+            if (len[me0]) {
+                TemplateCtx b = ctxOf(1);
+                b.count = len[me0] / es; b.root = rootServer; b.in = b.out = {BufKind::OUTPUT, lo * es + off[me0]}; b.inPlace = true;
+                b.cclOff = winB; b.cclBytes = Sa + 4096;
+                CHK_RET(Tmpl(bcastFor(len[me0]))->gen(b, &pl));
+            }
+            TemplateCtx g = ctxOf(0);
+            g.in = {BufKind::OUTPUT, lo * es + off[me0]}; g.out = {BufKind::OUTPUT, lo * es}; g.recvBytes = len; g.recvOff = off;
+            g.cclOff = winC; g.cclBytes = Sa + 4096;
+            CHK_RET(Tmpl("InsAllGatherVMesh1D")->gen(g, &pl));
+        } else if (p.opType == HCCL_CMD_BROADCAST) {
+            bcast = bcastFor(cnt * es);
             if (inColumn && n1 > 1) {
                 TemplateCtx a = ctxOf(1);
                 a.count = cnt; a.root = rootServer; a.in = a.out = {BufKind::OUTPUT, lo * es}; a.inPlace = true; a.cclOff = 0; a.cclBytes = S + 4096;
-                CHK_RET(Tmpl(t)->gen(a, &pl));
+                CHK_RET(Tmpl(bcast)->gen(a, &pl));
             }
             TemplateCtx b = ctxOf(0);
             b.count = cnt; b.root = rootPos; b.in = b.out = {BufKind::OUTPUT, lo * es}; b.inPlace = true; b.cclOff = S + 4096; b.cclBytes = S + 4096;
-            CHK_RET(Tmpl(t)->gen(b, &pl));
+            CHK_RET(Tmpl(bcast)->gen(b, &pl));
+        } else if (p.opType == HCCL_CMD_REDUCE && spread) {
+            // [0, Sa): my slice summed over my server; [Sa, 2 Sa): summed over all servers (members of the root's server)
+            const uint64_t winA = 2 * Sa, winB = winA + n0 * Sa, winC = winB + n1 * Sa + 4096;
+            TemplateCtx a = ctxOf(0);
+            a.in = {BufKind::INPUT, lo * es}; a.out = {BufKind::CCL, 0}; a.sendBytes = len; a.sendOff = off; a.cclOff = winA; a.cclBytes = n0 * Sa;
+            CHK_RET(Tmpl("InsReduceScatterVMesh1D")->gen(a, &pl));
+            if (len[me0]) {
+                TemplateCtx b = ctxOf(1);
+                b.count = len[me0] / es; b.root = rootServer; b.in = {BufKind::CCL, 0}; b.out = {BufKind::CCL, Sa}; b.cclOff = winB; b.cclBytes = n1 * Sa + 4096;
+                CHK_RET(Tmpl("ReduceMesh1D")->gen(b, &pl));
+            }
+            if (inRootServer) {
+                TemplateCtx g = ctxOf(0);
+                g.root = rootPos; g.in = {BufKind::CCL, Sa}; g.out = {BufKind::OUTPUT, lo * es}; g.recvBytes = len; g.recvOff = off;
+                g.cclOff = winC; g.cclBytes = Sa + 4096;
+                CHK_RET(Tmpl("InsGatherMesh1D")->gen(g, &pl));
+            }
         } else if (p.opType == HCCL_CMD_REDUCE) {
             const uint64_t win0 = S, win1 = win0 + n0 * S + 4096;
-            const bool isRoot = inColumn && h.myIndex[1] == rootServer;
             TemplateCtx a = ctxOf(0);
             a.count = cnt; a.root = rootPos; a.in = {BufKind::INPUT, lo * es}; a.out = {BufKind::CCL, 0}; a.cclOff = win0; a.cclBytes = n0 * S + 4096;
             if (n1 == 1 && isRoot) a.out = {BufKind::OUTPUT, lo * es};
@@ -531,15 +586,30 @@ HcclResult GenSequenceRootedPlans(const OpParam &p, const TopoInfo &topo, uint64
                 b.cclOff = win1; b.cclBytes = n1 * S + 4096;
                 CHK_RET(Tmpl("ReduceMesh1D")->gen(b, &pl));
             }
+        } else if (p.opType == HCCL_CMD_SCATTER && spread) {
+            // stage area: the blocks of my column, one per server, S apart; filled inside the root's server by one scatter per server
+            const uint64_t win0 = n1 * S, win1 = win0 + n0 * S + 4096;
+            if (inRootServer) {
+                for (uint32_t sv = 0; sv < n1; ++sv) {
+                    TemplateCtx a = ctxOf(0);
+                    a.count = cnt; a.root = rootPos;
+                    a.in = {BufKind::INPUT, ((uint64_t)sv * n0 * p.count + lo) * es}; a.inStride = p.count * es;
+                    a.out = {BufKind::CCL, (uint64_t)sv * S}; a.cclOff = win0; a.cclBytes = n0 * S + 4096;
+                    CHK_RET(Tmpl("InsScatterMesh1D")->gen(a, &pl));
+                }
+            }
+            TemplateCtx b = ctxOf(1);
+            b.count = cnt; b.root = rootServer; b.in = {BufKind::CCL, 0}; b.inStride = S; b.out = {BufKind::OUTPUT, lo * es}; b.cclOff = win1; b.cclBytes = n1 * S + 4096;
+            CHK_RET(Tmpl("InsScatterMesh1D")->gen(b, &pl));
         } else if (p.opType == HCCL_CMD_SCATTER) {
-            // stage area: the n0 blocks of my server, S apart; filled over level 1 by one scatter per position of the server
+            // one level is trivial. Stage area: the n0 blocks of my server, S apart; filled over level 1 by one scatter per position
             const uint64_t win1 = n0 * S, win0 = win1 + n1 * S + 4096;
             if (inColumn) {
-                for (uint32_t j = 0; j < n0; ++j) {
+                for (uint32_t k = 0; k < n0; ++k) {
                     TemplateCtx a = ctxOf(1);
                     a.count = cnt; a.root = rootServer;
-                    a.in = {BufKind::INPUT, ((uint64_t)j * p.count + lo) * es}; a.inStride = (uint64_t)n0 * p.count * es;
-                    a.out = {BufKind::CCL, (uint64_t)j * S}; a.cclOff = win1; a.cclBytes = n1 * S + 4096;
+                    a.in = {BufKind::INPUT, ((uint64_t)k * p.count + lo) * es}; a.inStride = (uint64_t)n0 * p.count * es;
+                    a.out = {BufKind::CCL, (uint64_t)k * S}; a.cclOff = win1; a.cclBytes = n1 * S + 4096;
                     if (n1 > 1) CHK_RET(Tmpl("InsScatterMesh1D")->gen(a, &pl));
                     else pl.queues[0].push_back(Task{TaskType::LOCAL_COPY, 0, 0, a.out, a.in, cnt * es});
                 }

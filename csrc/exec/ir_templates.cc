@@ -394,18 +394,47 @@ HcclResult GenReduceTwoShot(const TemplateCtx &c, Plan *p)
     return HCCL_SUCCESS;
 }
 
+// With sendBytes / sendOff set the blocks have their own lengths and offsets in the root's buffer (the multi-level executors scatter
+// the uneven slices of a vector this way); inPlace then says that the root's own block already sits where it belongs.
 HcclResult GenScatterMesh(const TemplateCtx &c, Plan *p)
 {
     Emit e(c, p);
     uint32_t n = c.N();
+    const bool v = !c.sendBytes.empty();
+    if (v && (c.sendBytes.size() != n || c.sendOff.size() != n)) return HCCL_E_INTERNAL;
     uint64_t B = c.count * c.elemSize, S = AlignUp(B);
+    if (v) { S = 0; for (uint64_t b : c.sendBytes) S = std::max(S, AlignUp(b)); }
+    auto len = [&](uint32_t j) { return v ? c.sendBytes[j] : B; };
+    auto off = [&](uint32_t j) { return v ? c.sendOff[j] : (uint64_t)j * c.inStride; };
     if (c.me == c.root) {
-        for (uint32_t j = 0; j < n; ++j) if (j != c.me) e.Copy(e.Ccl(j * S), Emit::At(c.in, j * c.inStride), B);
+        for (uint32_t j = 0; j < n; ++j) if (j != c.me) e.Copy(e.Ccl(j * S), Emit::At(c.in, off(j)), len(j));
         e.PostAll(SLOT_READY);
-        e.Copy(c.out, Emit::At(c.in, c.me * c.inStride), B);
+        if (!(v && c.inPlace)) e.Copy(c.out, Emit::At(c.in, off(c.me)), len(c.me));
     } else {
         e.Wait(c.root, SLOT_READY);
-        e.Read(c.root, c.out, e.Ccl(c.me * S), B);
+        e.Read(c.root, c.out, e.Ccl(c.me * S), len(c.me));
+    }
+    e.Barrier(SLOT_FIN);
+    return HCCL_SUCCESS;
+}
+
+// Gather of blocks of their own lengths at the root (recvBytes / recvOff: block j's length and its offset in the root's buffer); a
+// building block of the multi-level Reduce (reference: src/ops/reduce/template/aicpu/ins_temp_gather_mesh_1D_intra.cc).
+HcclResult GenGatherMesh(const TemplateCtx &c, Plan *p)
+{
+    Emit e(c, p);
+    uint32_t n = c.N();
+    if (c.recvBytes.size() != n || c.recvOff.size() != n) return HCCL_E_INTERNAL;
+    if (c.me != c.root) {
+        e.Copy(e.Ccl(0), c.in, c.recvBytes[c.me]);
+        e.Post(c.root, SLOT_READY);
+    } else {
+        e.Copy(Emit::At(c.out, c.recvOff[c.me]), c.in, c.recvBytes[c.me]);
+        for (uint32_t k = 1; k < n; ++k) {
+            uint32_t peer = (c.me + k) % n;
+            e.Wait(peer, SLOT_READY);
+            e.Read(peer, Emit::At(c.out, c.recvOff[peer]), e.Ccl(0), c.recvBytes[peer]);
+        }
     }
     e.Barrier(SLOT_FIN);
     return HCCL_SUCCESS;
@@ -662,11 +691,13 @@ void RegisterBuiltinIrTemplates()
             [](uint32_t n, uint32_t es, uint64_t ccl) { return PerN(n, es, ccl, 2.0 + 2.0 / n); }, true);
         reg("InsScatterMesh1D", HCCL_CMD_SCATTER, GenScatterMesh,
             [](uint32_t n, uint32_t es, uint64_t ccl) { return PerN(n, es, ccl, (double)n); }, true);
+        reg("InsGatherMesh1D", HCCL_CMD_GATHER, GenGatherMesh,
+            [](uint32_t n, uint32_t es, uint64_t ccl) { return PerN(n, es, ccl, 1.0); }, true);
         reg("InsScatterNHR", HCCL_CMD_SCATTER, GenScatterNhr,
             [](uint32_t n, uint32_t es, uint64_t ccl) { return PerN(n, es, ccl, (double)n); }, true);
         reg("InsBroadcastNHR", HCCL_CMD_BROADCAST, GenBroadcastNhr,
             [](uint32_t n, uint32_t es, uint64_t ccl) { return PerN(n, es, ccl, (1.0 + NhrStageSlices(n)) / n + 1e-9); }, true);
-        reg("InsReduceNHR", HCCL_CMD_REDUCE, GenReduceNhr,
+        reg("ReduceNHR", HCCL_CMD_REDUCE, GenReduceNhr,
             [](uint32_t n, uint32_t es, uint64_t ccl) { return PerN(n, es, ccl, (2.0 * n + NhrStageSlices(n)) / n + 1e-9); }, true);
         reg("InsAlltoAllMesh1D", HCCL_CMD_ALLTOALL, GenAlltoAllMesh,
             [](uint32_t n, uint32_t es, uint64_t ccl) { return PerN(n, es, ccl, (double)n); }, true);

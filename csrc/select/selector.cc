@@ -191,7 +191,7 @@ const char *IrAlgoFor(HcclCMDType op, AlgoType forced, uint64_t bytes, uint32_t 
         case HCCL_CMD_ALLGATHER: return ring ? "InsAllGatherRing" : nhr ? "InsAllGatherNHR" : "InsAllGatherMesh1D";
         case HCCL_CMD_REDUCE_SCATTER: return ring ? "InsReduceScatterRing" : nhr ? "InsReduceScatterNHR" : "InsReduceScatterMesh1D";
         case HCCL_CMD_BROADCAST: return nhr ? "InsBroadcastNHR" : bytes <= (64u << 10) ? "InsBroadcastMesh1DOneShot" : "InsBroadcastMesh1DTwoShot";
-        case HCCL_CMD_REDUCE: return nhr ? "InsReduceNHR" : bytes <= (512u << 10) ? "ReduceMesh1D" : "ReduceMesh1DTwoShot";
+        case HCCL_CMD_REDUCE: return nhr ? "ReduceNHR" : bytes <= (512u << 10) ? "ReduceMesh1D" : "ReduceMesh1DTwoShot";
         case HCCL_CMD_SCATTER: return nhr ? "InsScatterNHR" : "InsScatterMesh1D";
         case HCCL_CMD_ALLTOALL: return "InsAlltoAllMesh1D";
         case HCCL_CMD_ALLTOALLV: return "InsAlltoAllVMesh1D";

@@ -27,7 +27,7 @@ ALGOS = {
     "ALLGATHER": ["InsAllGatherMesh1D", "InsAllGatherRing", "InsAllGatherNHR"],
     "REDUCE_SCATTER": ["InsReduceScatterMesh1D", "InsReduceScatterRing", "InsReduceScatterNHR"],
     "BROADCAST": ["InsBroadcastMesh1DOneShot", "InsBroadcastMesh1DTwoShot", "InsBroadcastNHR"],
-    "REDUCE": ["ReduceMesh1D", "ReduceMesh1DTwoShot", "InsReduceNHR"],
+    "REDUCE": ["ReduceMesh1D", "ReduceMesh1DTwoShot", "ReduceNHR"],
     "SCATTER": ["InsScatterMesh1D", "InsScatterNHR"],
     "ALLTOALL": ["InsAlltoAllMesh1D"],
     "BARRIER": ["InsBarrierMesh1D", "InsBarrierNHR"],

@@ -164,7 +164,7 @@ def test_one_level_keeps_the_flat_algorithms(monkeypatch):
 
 def test_tree_forms_of_the_rooted_operators_with_real_data(monkeypatch):
     """HCCL_ALGO level1:NHR picks the tree scatter, the scatter + NHR all-gather broadcast and the NHR reduce-scatter + gather reduce
-    (by name: InsScatterNHR, InsBroadcastNHR, InsReduceNHR); odd rank count, every root, a message that runs in chunks."""
+    (by name: InsScatterNHR, InsBroadcastNHR, ReduceNHR); odd rank count, every root, a message that runs in chunks."""
     n = 5
     monkeypatch.setenv("HCCL_ALGO", "level0:NA;level1:NHR")
     lib().HcclResetEnvConfigForTest()
@@ -202,7 +202,7 @@ def test_tree_forms_of_the_rooted_operators_with_real_data(monkeypatch):
         monkeypatch.delenv("HCCL_ALGO")
         lib().HcclResetEnvConfigForTest()
     for rank, (out, algs) in enumerate(res):
-        assert algs == {"InsBroadcastNHR", "InsReduceNHR", "InsScatterNHR", "InsBarrierNHR"}, algs
+        assert algs == {"InsBroadcastNHR", "ReduceNHR", "InsScatterNHR", "InsBarrierNHR"}, algs
         for c in counts:
             want_red = np.sum(np.stack(rd_in[c]).astype(np.float64), axis=0)
             for root in range(n):
@@ -241,3 +241,50 @@ def test_two_level_barrier_orders_the_ranks(monkeypatch):
     for seen, alg in res:
         assert alg == "InsBarrierSequenceMesh1DMesh1D"
         assert seen == [6] * 5, seen
+
+
+@pytest.mark.parametrize("topo", [(1, 2, 4), (1, 3, 2), (2, 2, 2)])
+@pytest.mark.parametrize("op", ["BROADCAST", "REDUCE"])
+def test_spread_forms_pass_the_schedule_checker(op, topo):
+    """From 256 KB the message is cut into one slice per position of a server and every column carries its slice between the servers
+    (Scatter always works that way); whole, and in chunks with 160 KB of scratch; a count that leaves the last slices short or empty."""
+    n = topo[0] * topo[1] * topo[2]
+    for root in (0, n - 1):
+        for count, ccl in ((66_001, 0), (66_001, 160 << 10)):
+            rc, msg = check(op, ALG[op], topo, count, root, ccl=ccl)
+            assert rc == 0, (root, count, ccl, msg)
+
+
+def test_reduce_sums_in_the_same_order_in_both_forms(monkeypatch):
+    """The column form (small messages) and the spread form (from 256 KB) add the ranks of a server in rank order and then the servers in
+    order: the first elements of a large Reduce carry the same bits as a small Reduce of just those elements."""
+    topo, n = "1x2x4", 8
+    monkeypatch.setenv("HCCL_SIM_TOPO", topo)
+    lib().HcclResetEnvConfigForTest()
+    rng = np.random.default_rng(31)
+    full, few = 100_000, 1000
+    xs = [(rng.standard_normal(full) * 10.0 ** rng.integers(-6, 6, full)).astype(np.float32) for _ in range(n)]
+
+    def body(comm, rank):
+        big = np.zeros(full, np.float32)
+        comm.reduce(xs[rank], big, 5)
+        comm.synchronize()
+        small, head = np.zeros(few, np.float32), xs[rank][:few].copy()       # the operator is asynchronous: its input has to outlive the call
+        comm.reduce(head, small, 5)
+        comm.synchronize()
+        return big, small
+
+    try:
+        res = run_ranks(n, body, buffer_mb=64)
+    finally:
+        monkeypatch.delenv("HCCL_SIM_TOPO")
+        lib().HcclResetEnvConfigForTest()
+    big, small = res[5]
+    assert np.array_equal(big[:few].view(np.uint32), small.view(np.uint32))
+    servers = [np.zeros(full, np.float32) for _ in range(2)]
+    for s in range(2):
+        acc = xs[s * 4].copy()
+        for r in range(1, 4):
+            acc = acc + xs[s * 4 + r]
+        servers[s] = acc
+    assert np.array_equal(big.view(np.uint32), (servers[0] + servers[1]).view(np.uint32))

@@ -18,6 +18,7 @@ LogSink g_sink = nullptr;
 void *g_sinkUser = nullptr;
 std::mutex g_mu;
 thread_local int t_errToWarn = 0;
+thread_local int t_mute = 0;
 const char *kNames[] = {"DEBUG", "INFO", "WARNING", "ERROR", "RUN", "OFF"};
 std::once_flag g_envOnce;
 }  // namespace
@@ -77,11 +78,14 @@ void LogSetModuleMask(uint32_t mask) { g_mask = mask; }
 uint32_t LogGetModuleMask() { return g_mask; }
 void LogPushErrorToWarn() { ++t_errToWarn; }
 void LogPopErrorToWarn() { if (t_errToWarn > 0) --t_errToWarn; }
+void LogPushMute() { ++t_mute; }
+void LogPopMute() { if (t_mute > 0) --t_mute; }
 bool LogModuleEnabled(uint32_t module) { return (g_mask.load(std::memory_order_relaxed) & module) != 0; }
 uint64_t LogRecordCount(int level) { return (level >= 0 && level < 6) ? g_count[level].load() : 0; }
 
 void LogWrite(int level, const char *file, int line, const char *func, const char *fmt, ...)
 {
+    if (t_mute > 0 && level <= LOG_ERROR) return;
     if (level == LOG_ERROR && t_errToWarn > 0) level = LOG_WARNING;
     if (level < 0 || level > LOG_RUN_INFO) return;
     g_count[level]++;

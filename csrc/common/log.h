@@ -34,6 +34,9 @@ bool LogParseDebugConfig(const std::string &value, uint32_t *maskOut);  // retur
 // to fail, e.g. probing NVLS and falling back to peer loads).
 void LogPushErrorToWarn();
 void LogPopErrorToWarn();
+// Nothing below RUN_INFO is written by this thread between the two calls (trial runs whose failure is an expected answer).
+void LogPushMute();
+void LogPopMute();
 bool LogModuleEnabled(uint32_t module);
 void LogWrite(int level, const char *file, int line, const char *func, const char *fmt, ...)
     __attribute__((format(printf, 5, 6)));

@@ -407,22 +407,23 @@ HcclResult GenSequencePlan(const OpParam &p, const TopoInfo &topo, uint64_t cclB
     const auto &g1 = h.levelRanks[1];
     uint32_t n1 = (uint32_t)g1.size();
     uint64_t B = p.count * es, S = Al(B);
+    const uint64_t T = (p.blockStride ? p.blockStride : p.count) * es;       // bytes between the per-rank blocks of the user buffers
     if (p.opType == HCCL_CMD_ALLGATHER) {
         // level 1: gather my block across servers; level 0: one gather per server's block set
         if (S * (1 + n1) + 8192 > cclBytes) return HCCL_E_MEMORY;
         TemplateCtx a = baseCtx(1);
         a.in = {BufKind::INPUT, 0}; a.out = {BufKind::OUTPUT, 0}; a.cclOff = 0; a.cclBytes = S + 4096;
         a.recvBytes.assign(n1, B); a.recvOff.resize(n1);
-        for (uint32_t k = 0; k < n1; ++k) a.recvOff[k] = (uint64_t)g1[k] * B;
+        for (uint32_t k = 0; k < n1; ++k) a.recvOff[k] = (uint64_t)g1[k] * T;
         CHK_RET(Tmpl("InsAllGatherVMesh1D")->gen(a, plan));
         for (uint32_t s = 0; s < n1; ++s) {
             // the server that g1[s] belongs to: its level-0 group is {g1[s] - me0 + j}
             uint32_t base = g1[s] - me0;
             TemplateCtx b = baseCtx(0);
-            b.in = {BufKind::OUTPUT, (uint64_t)(base + me0) * B}; b.out = {BufKind::OUTPUT, 0};
+            b.in = {BufKind::OUTPUT, (uint64_t)(base + me0) * T}; b.out = {BufKind::OUTPUT, 0};
             b.cclOff = S + 4096 + (uint64_t)s * S; b.cclBytes = S;
             b.recvBytes.assign(n0, B); b.recvOff.resize(n0);
-            for (uint32_t j = 0; j < n0; ++j) b.recvOff[j] = (uint64_t)(base + j) * B;
+            for (uint32_t j = 0; j < n0; ++j) b.recvOff[j] = (uint64_t)(base + j) * T;
             CHK_RET(Tmpl("InsAllGatherVMesh1D")->gen(b, plan));
         }
         return HCCL_SUCCESS;
@@ -436,7 +437,7 @@ HcclResult GenSequencePlan(const OpParam &p, const TopoInfo &topo, uint64_t cclB
             TemplateCtx a = baseCtx(0);
             a.in = {BufKind::INPUT, 0}; a.out = {BufKind::CCL, workOff + (uint64_t)s * S};
             a.sendBytes.assign(n0, B); a.sendOff.resize(n0);
-            for (uint32_t j = 0; j < n0; ++j) a.sendOff[j] = (uint64_t)(base + j) * B;
+            for (uint32_t j = 0; j < n0; ++j) a.sendOff[j] = (uint64_t)(base + j) * T;
             a.cclOff = win0 + per0 * s; a.cclBytes = per0;
             CHK_RET(Tmpl("InsReduceScatterVMesh1D")->gen(a, plan));
         }
@@ -636,13 +637,52 @@ public:
     }
 };
 
+// The chunk loop of the multi-level executors: the largest piece of the call whose plan fits the scratch is found by halving (the
+// answer depends on the topology and the scratch size only, so every rank finds the same one), then one plan runs per piece. A piece
+// of AllGather / ReduceScatter keeps the block stride of the whole call. HCCL's executors share the same outer loop (reference:
+// src/ops/all_reduce/executor/ins_v2_all_reduce_sole_executor.cc:125-176).
+template <class Gen>
+static HcclResult RunMultiLevelChunks(Comm *c, const OpParam &p, Gen gen)
+{
+    const uint32_t es = DataTypeSize(p.dtype);
+    uint64_t per = p.count;
+    std::shared_ptr<Plan> first;
+    for (;;) {
+        OpParam q = p;
+        q.count = per;
+        q.blockStride = p.count;
+        auto plan = std::make_shared<Plan>();
+        LogPushMute();                             // "does not fit" is an answer here, not an error
+        HcclResult r = gen(q, plan.get());
+        LogPopMute();
+        if (r == HCCL_SUCCESS) { first = plan; break; }
+        if (r != HCCL_E_MEMORY || per <= 1024) {
+            if (r == HCCL_E_MEMORY) HCCL_ERROR("%s: not even 1024 elements fit the scratch of %llu bytes (raise HCCL_BUFFSIZE)", p.algName.c_str(), (unsigned long long)c->devComm.cclBytes);
+            return r;
+        }
+        per = (per / 2 + 127) / 128 * 128;
+    }
+    for (uint64_t lo = 0; lo < p.count; lo += per) {
+        OpParam q = p;
+        q.count = std::min(per, p.count - lo);
+        q.blockStride = p.count;
+        q.inputPtr = p.inputPtr ? (const char *)p.inputPtr + lo * es : nullptr;
+        q.outputPtr = p.outputPtr ? (char *)p.outputPtr + lo * es : nullptr;
+        std::shared_ptr<Plan> plan = first;
+        if (lo != 0 || q.count != per) {
+            plan = std::make_shared<Plan>();
+            CHK_RET(gen(q, plan.get()));
+        }
+        CHK_RET(RunPlan(c, q, plan, true));
+    }
+    return HCCL_SUCCESS;
+}
+
 class IrSequenceExecutor : public ExecutorBase {
 public:
     HcclResult Orchestrate(Comm *c, OpParam &p) override
     {
-        auto plan = std::make_shared<Plan>();
-        CHK_RET(GenSequencePlan(p, c->topo, c->devComm.cclBytes, plan.get()));
-        return RunPlan(c, p, plan, true);
+        return RunMultiLevelChunks(c, p, [c](const OpParam &q, Plan *plan) { return GenSequencePlan(q, c->topo, c->devComm.cclBytes, plan); });
     }
 };
 
@@ -654,9 +694,7 @@ public:
             HCCL_ERROR("%s: schedules with several queues run on the host engine only", algName_.c_str());
             return HCCL_E_NOT_SUPPORT;
         }
-        auto plan = std::make_shared<Plan>();
-        CHK_RET(GenParallelPlan(p, c->topo, c->devComm.cclBytes, plan.get()));
-        return RunPlan(c, p, plan, true);
+        return RunMultiLevelChunks(c, p, [c](const OpParam &q, Plan *plan) { return GenParallelPlan(q, c->topo, c->devComm.cclBytes, plan); });
     }
 };
 

@@ -19,6 +19,8 @@ struct OpParam {
     void *outputPtr = nullptr;
     uint64_t count = 0;                  // elements; meaning per op: AR/Reduce/Bcast count, AG sendCount,
                                          // RS/Scatter recvCount, AlltoAll sendCount per peer
+    uint64_t blockStride = 0;            // elements between the per-rank blocks of the gather / scatter forms; 0 = count (a chunk of a
+                                         // larger call keeps the stride of the whole call)
     HcclDataType dtype = HCCL_DATA_TYPE_FP32;
     HcclDataType outDtype = HCCL_DATA_TYPE_FP32;
     HcclReduceOp reduceOp = HCCL_REDUCE_SUM;

@@ -125,7 +125,7 @@ struct Builder {
     // ---- one step of a share: byte range [o, o + len) of every rank's block (AllGather / ReduceScatter) or of the vector
     HcclResult AllGatherStep(uint32_t first, size_t q1, size_t q2, uint64_t o, uint64_t len)
     {
-        const uint64_t B = p.count * es;
+        const uint64_t B = (p.blockStride ? p.blockStride : p.count) * es;      // bytes between the per-rank blocks of the user buffers
         const uint32_t n0 = N(0), n1 = N(1), me0 = Me(0);
         const uint32_t myRank = h.levelRanks[0][me0];
         std::vector<uint64_t> off;
@@ -158,7 +158,7 @@ struct Builder {
 
     HcclResult ReduceScatterStep(uint32_t first, size_t q1, size_t q2, uint64_t o, uint64_t len)
     {
-        const uint64_t B = p.count * es;
+        const uint64_t B = (p.blockStride ? p.blockStride : p.count) * es;      // bytes between the per-rank blocks of the user buffers
         const uint32_t n0 = N(0), n1 = N(1);
         const uint32_t second = 1 - first, nf = N(first), ns = N(second);
         // first stage: one reduce-scatter per member of the OTHER level's group, each leaving a partial sum in the work area

@@ -272,3 +272,52 @@ def test_batch_invariant_reduce_scatter_on_two_levels(monkeypatch):
         for s_ in range(1, servers):
             want = want + partial[s_]
         assert np.array_equal(big[r][0].view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("family", ["Parallel", "Sequence"])
+@pytest.mark.parametrize("topo", ["1x2x4", "2x2x2"])
+def test_messages_larger_than_the_scratch_run_in_chunks(topo, family, monkeypatch):
+    """1 MB of scratch per half against 2.4 MB vectors (AllReduce) and 0.6 MB blocks per rank (AllGather / ReduceScatter, 4.8 MB buffers):
+    the multi-level executors cut the call into the largest pieces whose plan fits; a piece of the block forms keeps the stride of
+    the whole call."""
+    pods, servers, per = (int(v) for v in topo.split("x"))
+    n = pods * servers * per
+    names = {"Parallel": "allreduce=InsAllReduceParallelMesh1DMesh1D;allgather=InsAllGatherParallelMesh1DMesh1D;reducescatter=InsReduceScatterParallelMesh1DMesh1D",
+             "Sequence": "allreduce=InsAllReduceSequenceMesh1DNhr;allgather=InsAllGatherSequenceNhrMesh1D;reducescatter=InsReduceScatterSequenceMesh1DNhr"}[family]
+    monkeypatch.setenv("HCCL_SIM_TOPO", topo)
+    monkeypatch.setenv("HCCL_ALGO_NAME", names)
+    lib().HcclResetEnvConfigForTest()
+    rng = np.random.default_rng(41)
+    c_ar, c_blk = 600_001, 150_001
+    ar_in = [rng.integers(-8, 9, size=c_ar).astype(np.float32) for _ in range(n)]
+    ag_in = [rng.integers(-8, 9, size=c_blk).astype(np.float32) for _ in range(n)]
+    rs_in = [rng.integers(-8, 9, size=c_blk * n).astype(np.float32) for _ in range(n)]
+
+    def body(comm, rank):
+        a = ar_in[rank].copy()
+        comm.all_reduce(a)
+        comm.synchronize()
+        used = [comm.last_algorithm()]
+        g = np.empty(c_blk * n, np.float32)
+        comm.all_gather(ag_in[rank], g)
+        comm.synchronize()
+        used.append(comm.last_algorithm())
+        s = np.empty(c_blk, np.float32)
+        comm.reduce_scatter(rs_in[rank], s)
+        comm.synchronize()
+        used.append(comm.last_algorithm())
+        return a, g, s, used
+
+    try:
+        res = run_ranks(n, body, buffer_mb=2)
+    finally:
+        monkeypatch.delenv("HCCL_SIM_TOPO")
+        monkeypatch.delenv("HCCL_ALGO_NAME")
+        lib().HcclResetEnvConfigForTest()
+    want_ar, want_ag, want_rs = _oracle(ar_in), np.concatenate(ag_in), _oracle(rs_in)
+    for r, (a, g, s, used) in enumerate(res):
+        assert all(family in u for u in used), used
+        assert np.array_equal(a.astype(np.float64), want_ar), r
+        assert np.array_equal(g, want_ag), r
+        assert np.array_equal(s.astype(np.float64), want_rs[r * c_blk:(r + 1) * c_blk]), r
+

@@ -168,6 +168,12 @@ static void ApplyConfig(Comm *c, const HcclCommConfig *cfg)
     }
 }
 
+namespace {
+thread_local const RankDesc *t_inheritedPlacement = nullptr;
+}
+const RankDesc *InheritedPlacement() { return t_inheritedPlacement; }
+void SetInheritedPlacement(const RankDesc *d) { t_inheritedPlacement = d; }
+
 HcclResult CommCreate(uint32_t nranks, const HcclRootInfo *info, uint32_t rank, const HcclCommConfig *cfg, Comm **out)
 {
     CHK_PTR_NULL(info);
@@ -211,7 +217,15 @@ HcclResult CommCreate(uint32_t nranks, const HcclRootInfo *info, uint32_t rank, 
     // Host-simulation backend only: HCCL_SIM_TOPO = "<super pods>x<servers per pod>x<ranks per server>[@<bw0>,<bw1>]" lays the ranks out on
     // pretended servers (rank = (pod * servers + server) * ranksPerServer + position), so that the multi-level executors run
     // with real data on one machine.
-    if (!haveCuda)
+    // A sub-communicator keeps its parent's placement of this rank (server, super-pod): what HCCL_SIM_TOPO pretended for the parent
+    // holds for the ranks picked from it, and the variable itself describes the parent's rank count only.
+    const RankDesc *inherited = InheritedPlacement();
+    if (inherited) {
+        me.hostHash = inherited->hostHash;
+        me.serverId = inherited->serverId;
+        me.superPodId = inherited->superPodId;
+    }
+    if (!haveCuda && !inherited)
         if (const char *e = getenv("HCCL_SIM_TOPO")) {
             unsigned pods = 0, servers = 0, per = 0;
             if (sscanf(e, "%ux%ux%u", &pods, &servers, &per) == 3 && pods * servers * per == nranks && per > 0) {

@@ -138,6 +138,10 @@ struct Comm {
 };
 
 // ---- lifecycle (comm.cc)
+// Placement (server, super-pod) that the next CommCreate of this thread gives its rank instead of deriving it from the host: set around
+// the creation of a sub-communicator, whose ranks keep the placement they have in the parent.
+const RankDesc *InheritedPlacement();
+void SetInheritedPlacement(const RankDesc *d);
 HcclResult CommCreate(uint32_t nranks, const HcclRootInfo *info, uint32_t rank, const HcclCommConfig *cfg, Comm **out);
 HcclResult CommDestroy(Comm *c);
 Comm *CommFromHandle(HcclComm h);       // validates the handle (nullptr on garbage)

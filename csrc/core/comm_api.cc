@@ -171,7 +171,11 @@ HcclResult HcclCreateSubCommConfig(HcclComm *comm, uint32_t rankNum, uint32_t *r
         if (v.size() != sizeof(info)) return HCCL_E_INTERNAL;
         memcpy(&info, v.data(), sizeof(info));
     }
-    return HcclCommInitRootInfoConfig(rankNum, &info, subCommRankId, config, subComm);
+    const bool known = parent->rank < parent->topo.ranks.size();
+    if (known) SetInheritedPlacement(&parent->topo.ranks[parent->rank]);
+    HcclResult r = HcclCommInitRootInfoConfig(rankNum, &info, subCommRankId, config, subComm);
+    SetInheritedPlacement(nullptr);
+    return r;
 }
 
 HcclResult HcclCommDestroy(HcclComm comm)

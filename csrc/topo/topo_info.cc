@@ -11,7 +11,7 @@ std::string TopoInfo::Describe() const
     static const char *kShape[] = {"CLOS", "MESH_1D", "MESH_1D_CLOS", "NVSWITCH"};
     std::ostringstream os;
     os << "pods=" << superPodNum << " servers=" << serverNum << " ranksPerServer=" << ranksPerServer << " levels=" << numLevels
-       << " level0=" << kShape[(int)level0Shape] << " nvls=" << (nvlsSupported ? 1 : 0) << " symmetric=" << (symmetric ? 1 : 0);
+       << " level0=" << kShape[(int)level0Shape] << " nvls=" << (nvlsSupported ? 1 : 0) << " symmetric=" << (symmetric ? 1 : 0) << " regular=" << (regular ? 1 : 0);
     if (!links.empty()) {
         os << " pairLinks[nvlink=" << pairLinks[(int)LinkType::NVLINK] << " pcie=" << pairLinks[(int)LinkType::PCIE] << " shm=" << pairLinks[(int)LinkType::SHM]
            << " none=" << pairLinks[(int)LinkType::NONE] << "] nvlinkActive=" << links[rank].nvlinkActive << " bw0=" << (levelBandwidth.empty() ? 0.0 : levelBandwidth[0]);
@@ -35,6 +35,16 @@ static HcclResult BuildLevels(TopoInfo *t, const std::vector<uint32_t> &serverOf
         uint32_t pod = podOf[kv.second[0]];
         serversOfPod[pod].push_back(kv.first);
     }
+    // servers of a pod in the order of their first rank (server ids may be hashes), so that group members ascend by rank
+    for (auto &pod : serversOfPod)
+        std::sort(pod.second.begin(), pod.second.end(), [&](uint32_t a, uint32_t b) { return byServer[a][0] < byServer[b][0]; });
+    // regular: server k holds exactly the ranks [k * ranksPerServer, (k + 1) * ranksPerServer). The multi-level schedules that address
+    // blocks by "first rank of the server + position" need it; other layouts (round-robin placement, picked sub-communicators) run the
+    // one-level algorithms, which are valid on any layout.
+    t->regular = t->symmetric;
+    for (auto &kv : byServer)
+        for (size_t j = 0; j < kv.second.size() && t->regular; ++j)
+            t->regular = kv.second[j] == kv.second[0] + j && kv.second[0] % t->ranksPerServer == 0;
     t->superPodNum = (uint32_t)serversOfPod.size();
     t->serverIdx = serverOf[t->rank];
     t->superPodIdx = podOf[t->rank];
@@ -44,8 +54,8 @@ static HcclResult BuildLevels(TopoInfo *t, const std::vector<uint32_t> &serverOf
     t->levels.push_back(l0);
     t->levelBandwidth = {770.0};
     if (t->serverNum > 1) {
-        if (!t->symmetric) {
-            // asymmetric clusters collapse to one flat level so that every algorithm stays valid
+        if (!t->regular) {
+            // asymmetric or irregularly numbered clusters collapse to one flat level so that every algorithm stays valid
             std::vector<uint32_t> allRanks(n);
             for (uint32_t r = 0; r < n; ++r) allRanks[r] = r;
             t->levels = {{allRanks}};
@@ -74,6 +84,7 @@ static HcclResult BuildLevels(TopoInfo *t, const std::vector<uint32_t> &serverOf
                     for (uint32_t i = 0; i < t->ranksPerServer; ++i) {
                         std::vector<uint32_t> g;
                         for (auto &pod : serversOfPod) g.push_back(byServer[pod.second[s]][i]);
+                        std::sort(g.begin(), g.end());
                         l2.push_back(g);
                     }
                 t->levels.push_back(l2);
@@ -84,6 +95,7 @@ static HcclResult BuildLevels(TopoInfo *t, const std::vector<uint32_t> &serverOf
                 for (uint32_t i = 0; i < t->ranksPerServer; ++i) {
                     std::vector<uint32_t> g;
                     for (auto &kv : byServer) g.push_back(kv.second[i]);
+                    std::sort(g.begin(), g.end());
                     flat.push_back(g);
                 }
                 t->levels[1] = flat;

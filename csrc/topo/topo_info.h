@@ -51,6 +51,7 @@ struct TopoInfo {
     bool allPeersDirect = true;      // every level-0 pair has peer access
     bool nvlsSupported = false;
     bool symmetric = true;           // all servers hold the same number of ranks
+    bool regular = true;             // symmetric, and server k holds the ranks [k * ranksPerServer, (k + 1) * ranksPerServer)
     std::vector<RankDesc> ranks;
     // level[l] = groups of ranks that talk to each other at that level; a rank appears in exactly one group per
     // level. level 0: ranks of one server; level 1: same local index across servers; level 2: across super-pods.

@@ -288,3 +288,59 @@ def test_reduce_sums_in_the_same_order_in_both_forms(monkeypatch):
             acc = acc + xs[s * 4 + r]
         servers[s] = acc
     assert np.array_equal(big.view(np.uint32), (servers[0] + servers[1]).view(np.uint32))
+
+
+@pytest.mark.parametrize("groups, levels", [([[0, 1, 4, 5], [2, 3, 6, 7]], 2),        # two ranks of each server: still two regular servers
+                                            ([[0, 4, 1, 5], [2, 6, 3, 7]], 1),        # servers interleaved in the rank order: one flat level
+                                            ([[0, 1, 4], [2, 3, 5, 6, 7]], 1)])       # servers of unequal size: one flat level
+def test_sub_communicators_keep_the_placement_of_their_ranks(groups, levels, monkeypatch):
+    """A sub-communicator's ranks stay on the (pretended) servers they have in the parent. Where the picked ranks still form regular
+    servers the multi-level executors serve it; any other layout runs the one-level algorithms, which are valid everywhere."""
+    import ctypes as ct
+    n, c = 8, 30_001
+    monkeypatch.setenv("HCCL_SIM_TOPO", "1x2x4")
+    lib().HcclResetEnvConfigForTest()
+    xs = [np.random.default_rng(r).integers(-8, 9, size=c).astype(np.float32) for r in range(n)]
+
+    def body(comm, rank):
+        out = None
+        for gi, g in enumerate(groups):
+            sub = comm.create_sub_comm(g if rank in g else None, 100 + gi)
+            if sub is None:
+                continue
+            desc = ct.create_string_buffer(2048)
+            lib().HcclGetTopoDescription(ct.c_void_p(sub.handle), desc, 2048)
+            a = xs[rank].copy()
+            sub.all_reduce(a)
+            sub.synchronize()
+            algs = [sub.last_algorithm()]
+            b = xs[g[1]].copy() if rank == g[1] else np.zeros(c, np.float32)
+            sub.broadcast(b, 1)
+            sub.synchronize()
+            algs.append(sub.last_algorithm())
+            gathered = np.empty(c * len(g), np.float32)
+            sub.all_gather(xs[rank], gathered)
+            sub.synchronize()
+            algs.append(sub.last_algorithm())
+            s = np.empty(c // len(g), np.float32)
+            sub.reduce_scatter(xs[rank][:c // len(g) * len(g)], s)
+            sub.synchronize()
+            algs.append(sub.last_algorithm())
+            out = (g, desc.value.decode(), algs, a, b, gathered, s)
+            sub.destroy()
+        return out
+
+    try:
+        res = run_ranks(n, body, buffer_mb=16)
+    finally:
+        monkeypatch.delenv("HCCL_SIM_TOPO")
+        lib().HcclResetEnvConfigForTest()
+    for rank, (g, desc, algs, a, b, gathered, s) in enumerate(res):
+        assert f"levels={levels}" in desc, desc
+        assert all(("Sequence" in x or "Parallel" in x) == (levels == 2) for x in algs), algs
+        total = np.sum(np.stack([xs[r] for r in g]).astype(np.float64), axis=0)
+        assert np.array_equal(a.astype(np.float64), total)
+        assert np.array_equal(b, xs[g[1]])
+        assert np.array_equal(gathered, np.concatenate([xs[r] for r in g]))
+        k, m = g.index(rank), c // len(g)
+        assert np.array_equal(s.astype(np.float64), total[k * m:(k + 1) * m])

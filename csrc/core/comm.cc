@@ -170,9 +170,10 @@ static void ApplyConfig(Comm *c, const HcclCommConfig *cfg)
 
 namespace {
 thread_local const RankDesc *t_inheritedPlacement = nullptr;
+thread_local bool t_placementSimOnly = false;
 }
 const RankDesc *InheritedPlacement() { return t_inheritedPlacement; }
-void SetInheritedPlacement(const RankDesc *d) { t_inheritedPlacement = d; }
+void SetInheritedPlacement(const RankDesc *d, bool simOnly) { t_inheritedPlacement = d; t_placementSimOnly = d != nullptr && simOnly; }
 
 HcclResult CommCreate(uint32_t nranks, const HcclRootInfo *info, uint32_t rank, const HcclCommConfig *cfg, Comm **out)
 {
@@ -220,6 +221,7 @@ HcclResult CommCreate(uint32_t nranks, const HcclRootInfo *info, uint32_t rank, 
     // A sub-communicator keeps its parent's placement of this rank (server, super-pod): what HCCL_SIM_TOPO pretended for the parent
     // holds for the ranks picked from it, and the variable itself describes the parent's rank count only.
     const RankDesc *inherited = InheritedPlacement();
+    if (inherited && t_placementSimOnly && haveCuda) inherited = nullptr;      // GPUs sit where the host says they sit
     if (inherited) {
         me.hostHash = inherited->hostHash;
         me.serverId = inherited->serverId;

@@ -139,9 +139,10 @@ struct Comm {
 
 // ---- lifecycle (comm.cc)
 // Placement (server, super-pod) that the next CommCreate of this thread gives its rank instead of deriving it from the host: set around
-// the creation of a sub-communicator, whose ranks keep the placement they have in the parent.
+// the creation of a sub-communicator, whose ranks keep the placement they have in the parent, and (host simulation only) around a
+// creation from a rank table, whose server list says where each rank sits.
 const RankDesc *InheritedPlacement();
-void SetInheritedPlacement(const RankDesc *d);
+void SetInheritedPlacement(const RankDesc *d, bool simOnly = false);     // simOnly: ignored when the communicator runs on GPUs
 HcclResult CommCreate(uint32_t nranks, const HcclRootInfo *info, uint32_t rank, const HcclCommConfig *cfg, Comm **out);
 HcclResult CommDestroy(Comm *c);
 Comm *CommFromHandle(HcclComm h);       // validates the handle (nullptr on garbage)

@@ -75,6 +75,9 @@ HcclResult HcclCommInitClusterInfoConfig(const char *clusterInfo, uint32_t rank,
     uint32_t nranks = 0;
     std::string rootIp;
     int myDevice = -1;
+    int myServer = -1;                       // position of this rank's server in server_list
+    std::string myServerId;
+    int mySuperPod = 0;
     try {
         JsonValue root = JsonParser(text).Parse();
         const JsonValue *status = root.Get("status");
@@ -85,7 +88,9 @@ HcclResult HcclCommInitClusterInfoConfig(const char *clusterInfo, uint32_t rank,
         long long scv;
         if (sc && sc->AsInt(&scv) && (size_t)scv != servers->arr.size()) { HCCL_ERROR("rank table: server_count %lld but %zu servers listed", scv, servers->arr.size()); return HCCL_E_PARA; }
         std::vector<bool> seen;
+        int serverOrdinal = -1;
         for (const JsonValue &s : servers->arr) {
+            ++serverOrdinal;
             const JsonValue *sid = s.Get("server_id");
             if (rootIp.empty() && sid) rootIp = sid->str;
             const JsonValue *devs = s.Get("device");
@@ -98,11 +103,26 @@ HcclResult HcclCommInitClusterInfoConfig(const char *clusterInfo, uint32_t rank,
                 if ((size_t)rid >= seen.size()) seen.resize(rid + 1, false);
                 if (seen[rid]) { HCCL_ERROR("rank table: rank_id %lld listed twice", rid); return HCCL_E_PARA; }
                 seen[rid] = true;
-                if ((uint32_t)rid == rank) myDevice = (int)did;
+                if ((uint32_t)rid == rank) { myDevice = (int)did; myServer = serverOrdinal; if (sid) myServerId = sid->str; }
                 ++nranks;
             }
         }
         for (size_t i = 0; i < seen.size(); ++i) if (!seen[i]) { HCCL_ERROR("rank table: rank_id %zu missing", i); return HCCL_E_PARA; }
+        // optional "super_pod_list": [{"super_pod_id": "0", "server_list": [{"server_id": "..."}]}] (the reference's tables for machines
+        // with super-pods, docs/zh/user_guide/cluster_info_config/rank_table_config_a3.md)
+        if (const JsonValue *pods = root.Get("super_pod_list"))
+            if (pods->kind == JsonValue::ARR) {
+                int podOrdinal = -1;
+                for (const JsonValue &pod : pods->arr) {
+                    ++podOrdinal;
+                    const JsonValue *sl = pod.Get("server_list");
+                    if (!sl || sl->kind != JsonValue::ARR) continue;
+                    for (const JsonValue &sv : sl->arr) {
+                        const JsonValue *sid = sv.Get("server_id");
+                        if (sid && !myServerId.empty() && sid->str == myServerId) mySuperPod = podOrdinal;
+                    }
+                }
+            }
     } catch (const std::exception &e) {
         HCCL_ERROR("rank table %s: %s", clusterInfo, e.what());
         return HCCL_E_PARA;
@@ -116,7 +136,16 @@ HcclResult HcclCommInitClusterInfoConfig(const char *clusterInfo, uint32_t rank,
     CHK_RET(BootstrapFixedRootInfo(rootIp, port, nonce, rank == 0, &info));
     int dev;
     if (myDevice >= 0 && CudaDeviceAvailable(&dev) && !(config && config->hcclBackend == 1)) CHK_RET(CudaSetDeviceChecked(myDevice));
-    return HcclCommInitRootInfoConfig(nranks, &info, rank, config, comm);
+    // The host simulation has no hosts to tell servers apart by: there the table's server list places the ranks (GPUs sit where their
+    // host says, and the table is expected to say the same).
+    RankDesc placed{};
+    placed.serverId = (uint32_t)std::max(myServer, 0);
+    placed.superPodId = (uint32_t)mySuperPod;
+    placed.hostHash = 0x9e3779b97f4a7c15ull * (placed.serverId + 1);
+    SetInheritedPlacement(&placed, true);
+    HcclResult r = HcclCommInitRootInfoConfig(nranks, &info, rank, config, comm);
+    SetInheritedPlacement(nullptr);
+    return r;
 }
 
 HcclResult HcclCommInitClusterInfo(const char *clusterInfo, uint32_t rank, HcclComm *comm)

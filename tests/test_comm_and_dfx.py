@@ -61,6 +61,49 @@ def test_rank_table_init(tmp_path, monkeypatch):
     lib().HcclResetEnvConfigForTest()
 
 
+@pytest.mark.parametrize("pods", [1, 2])
+def test_rank_table_places_the_ranks_on_servers_and_super_pods(tmp_path, monkeypatch, pods):
+    """On the host simulation the table's server_list (and super_pod_list) is what places the ranks: two servers of two ranks per pod give
+    a two-level (with two pods: three-level) topology, and the multi-level executors serve the operators."""
+    port = 63000 + os.getpid() % 1500 + pods
+    monkeypatch.setenv("HCCL_IF_BASE_PORT", str(port))
+    lib().HcclResetEnvConfigForTest()
+    servers = 2 * pods
+    n = servers * 2
+    table = {"status": "completed", "version": "1.2", "server_count": str(servers),
+             "server_list": [{"server_id": f"node_{s}", "device": [{"device_id": str(d), "rank_id": str(s * 2 + d)} for d in range(2)]} for s in range(servers)]}
+    if pods > 1:
+        table["super_pod_list"] = [{"super_pod_id": str(p), "server_list": [{"server_id": f"node_{p * 2 + k}"} for k in range(2)]} for p in range(pods)]
+    path = tmp_path / "ranktable.json"
+    path.write_text(json.dumps(table))
+    out = [None] * n
+
+    def body(r):
+        comm = Communicator.from_cluster_info(str(path), r)
+        desc = ctypes.create_string_buffer(1024)
+        lib().HcclGetTopoDescription(ctypes.c_void_p(comm.handle), desc, 1024)
+        x = np.full(5000, r + 1.0, np.float32)
+        comm.all_reduce(x)
+        comm.synchronize()
+        alg = comm.last_algorithm()
+        b = np.full(100, 7.0 if r == 3 else 0.0, np.float32)
+        comm.broadcast(b, 3)
+        comm.synchronize()
+        out[r] = (desc.value.decode(), alg, comm.last_algorithm(), x[0], b[0])
+        comm.destroy()
+
+    th = [threading.Thread(target=body, args=(r,)) for r in range(n)]
+    [t.start() for t in th]
+    [t.join(120) for t in th]
+    lib().HcclResetEnvConfigForTest()
+    for r in range(n):
+        assert out[r] is not None
+        desc, alg, alg2, x0, b0 = out[r]
+        assert f"pods={pods} servers={servers} ranksPerServer=2 levels={pods + 1}" in desc and "regular=1" in desc, desc
+        assert "Sequence" in alg and "Sequence" in alg2, (alg, alg2)
+        assert x0 == n * (n + 1) / 2 and b0 == 7.0
+
+
 @pytest.mark.parametrize("mutate,code", [
     (lambda t: t.update(status="initializing"), Result.E_PARA),
     (lambda t: t.update(server_count="2"), Result.E_PARA),

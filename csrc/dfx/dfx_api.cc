@@ -263,16 +263,28 @@ HcclResult HcclCheckAlgorithm(HcclCMDType op, const char *algName, uint32_t supe
                       op == HCCL_CMD_SCATTER ? "InsScatterSequenceMesh1DMesh1D" : "InsBarrierSequenceMesh1DMesh1D";
             else { const char *nm = IrAlgoFor(op, AlgoType::DEFAULT, p.DataBytes(), n, cclBytes); if (!nm) return HCCL_E_NOT_SUPPORT; alg = nm; }
             std::vector<Plan> mine;
+            // the pieces of a chunked multi-level call address the buffers from their own start: move them back for the checker
+            auto rebased = [&](const std::vector<ChunkPlan> &chunksOf) {
+                for (const ChunkPlan &ch : chunksOf) {
+                    Plan pl = *ch.plan;
+                    const uint64_t shift = ch.lo * es;
+                    for (auto &q : pl.queues)
+                        for (Task &t : q)
+                            for (BufRef *b : {&t.dst, &t.src})
+                                if (b->kind == BufKind::INPUT || b->kind == BufKind::OUTPUT) b->off += shift;
+                    mine.push_back(std::move(pl));
+                }
+            };
             if (alg.find("Parallel") != std::string::npos) {
-                Plan pl;
-                CHK_RET(GenParallelPlan(p, topo, cclBytes, &pl));
-                mine.push_back(std::move(pl));
+                std::vector<ChunkPlan> cps;
+                CHK_RET(GenParallelChunkPlans(p, topo, cclBytes, &cps));
+                rebased(cps);
             } else if (alg.find("Sequence") != std::string::npos && (op == HCCL_CMD_BROADCAST || op == HCCL_CMD_REDUCE || op == HCCL_CMD_SCATTER || op == HCCL_CMD_BARRIER)) {
                 CHK_RET(GenSequenceRootedPlans(p, topo, cclBytes, &mine));
             } else if (alg.find("Sequence") != std::string::npos) {
-                Plan pl;
-                CHK_RET(GenSequencePlan(p, topo, cclBytes, &pl));
-                mine.push_back(std::move(pl));
+                std::vector<ChunkPlan> cps;
+                CHK_RET(GenSequenceChunkPlans(p, topo, cclBytes, &cps));
+                rebased(cps);
             } else {
                 const IrTemplate *t = IrTemplateRegistry::Instance().Find(alg);
                 if (!t) { CopyOut("no schedule template named " + alg, msg, msgLen); return HCCL_E_NOT_FOUND; }

@@ -642,9 +642,9 @@ public:
 // of AllGather / ReduceScatter keeps the block stride of the whole call. HCCL's executors share the same outer loop (reference:
 // src/ops/all_reduce/executor/ins_v2_all_reduce_sole_executor.cc:125-176).
 template <class Gen>
-static HcclResult RunMultiLevelChunks(Comm *c, const OpParam &p, Gen gen)
+static HcclResult GenMultiLevelChunks(const OpParam &p, uint64_t cclBytes, Gen gen, std::vector<ChunkPlan> *out)
 {
-    const uint32_t es = DataTypeSize(p.dtype);
+    out->clear();
     uint64_t per = p.count;
     std::shared_ptr<Plan> first;
     for (;;) {
@@ -657,7 +657,7 @@ static HcclResult RunMultiLevelChunks(Comm *c, const OpParam &p, Gen gen)
         LogPopMute();
         if (r == HCCL_SUCCESS) { first = plan; break; }
         if (r != HCCL_E_MEMORY || per <= 1024) {
-            if (r == HCCL_E_MEMORY) HCCL_ERROR("%s: not even 1024 elements fit the scratch of %llu bytes (raise HCCL_BUFFSIZE)", p.algName.c_str(), (unsigned long long)c->devComm.cclBytes);
+            if (r == HCCL_E_MEMORY) HCCL_ERROR("%s: not even 1024 elements fit the scratch of %llu bytes (raise HCCL_BUFFSIZE)", p.algName.c_str(), (unsigned long long)cclBytes);
             return r;
         }
         per = (per / 2 + 127) / 128 * 128;
@@ -666,14 +666,36 @@ static HcclResult RunMultiLevelChunks(Comm *c, const OpParam &p, Gen gen)
         OpParam q = p;
         q.count = std::min(per, p.count - lo);
         q.blockStride = p.count;
-        q.inputPtr = p.inputPtr ? (const char *)p.inputPtr + lo * es : nullptr;
-        q.outputPtr = p.outputPtr ? (char *)p.outputPtr + lo * es : nullptr;
         std::shared_ptr<Plan> plan = first;
         if (lo != 0 || q.count != per) {
             plan = std::make_shared<Plan>();
             CHK_RET(gen(q, plan.get()));
         }
-        CHK_RET(RunPlan(c, q, plan, true));
+        out->push_back(ChunkPlan{lo, q.count, plan});
+    }
+    return HCCL_SUCCESS;
+}
+
+HcclResult GenSequenceChunkPlans(const OpParam &p, const TopoInfo &topo, uint64_t cclBytes, std::vector<ChunkPlan> *out)
+{
+    return GenMultiLevelChunks(p, cclBytes, [&](const OpParam &q, Plan *plan) { return GenSequencePlan(q, topo, cclBytes, plan); }, out);
+}
+HcclResult GenParallelChunkPlans(const OpParam &p, const TopoInfo &topo, uint64_t cclBytes, std::vector<ChunkPlan> *out)
+{
+    return GenMultiLevelChunks(p, cclBytes, [&](const OpParam &q, Plan *plan) { return GenParallelPlan(q, topo, cclBytes, plan); }, out);
+}
+
+// Runs the pieces: each plan addresses the user buffers from the start of its piece.
+static HcclResult RunChunkPlans(Comm *c, const OpParam &p, const std::vector<ChunkPlan> &chunks)
+{
+    const uint32_t es = DataTypeSize(p.dtype);
+    for (const ChunkPlan &ch : chunks) {
+        OpParam q = p;
+        q.count = ch.count;
+        q.blockStride = p.count;
+        q.inputPtr = p.inputPtr ? (const char *)p.inputPtr + ch.lo * es : nullptr;
+        q.outputPtr = p.outputPtr ? (char *)p.outputPtr + ch.lo * es : nullptr;
+        CHK_RET(RunPlan(c, q, ch.plan, true));
     }
     return HCCL_SUCCESS;
 }
@@ -682,7 +704,9 @@ class IrSequenceExecutor : public ExecutorBase {
 public:
     HcclResult Orchestrate(Comm *c, OpParam &p) override
     {
-        return RunMultiLevelChunks(c, p, [c](const OpParam &q, Plan *plan) { return GenSequencePlan(q, c->topo, c->devComm.cclBytes, plan); });
+        std::vector<ChunkPlan> chunks;
+        CHK_RET(GenSequenceChunkPlans(p, c->topo, c->devComm.cclBytes, &chunks));
+        return RunChunkPlans(c, p, chunks);
     }
 };
 
@@ -694,7 +718,9 @@ public:
             HCCL_ERROR("%s: schedules with several queues run on the host engine only", algName_.c_str());
             return HCCL_E_NOT_SUPPORT;
         }
-        return RunMultiLevelChunks(c, p, [c](const OpParam &q, Plan *plan) { return GenParallelPlan(q, c->topo, c->devComm.cclBytes, plan); });
+        std::vector<ChunkPlan> chunks;
+        CHK_RET(GenParallelChunkPlans(p, c->topo, c->devComm.cclBytes, &chunks));
+        return RunChunkPlans(c, p, chunks);
     }
 };
 

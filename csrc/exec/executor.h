@@ -79,6 +79,11 @@ HcclResult GenBatchSendRecvPlan(uint32_t me, uint32_t nranks, const std::vector<
                                 Plan *p, std::vector<char *> *itemBufs);
 // Multi-level plan for AllReduce / AllGather / ReduceScatter (whole op, no chunk loop).
 HcclResult GenSequencePlan(const OpParam &p, const TopoInfo &topo, uint64_t cclBytes, Plan *plan);
+// A call cut into the largest pieces whose plan fits the scratch. Each plan addresses the user buffers from the start of its piece
+// (element `lo` of the vector, or of every rank's block for AllGather / ReduceScatter).
+struct ChunkPlan { uint64_t lo, count; std::shared_ptr<Plan> plan; };
+HcclResult GenSequenceChunkPlans(const OpParam &p, const TopoInfo &topo, uint64_t cclBytes, std::vector<ChunkPlan> *out);
+HcclResult GenParallelChunkPlans(const OpParam &p, const TopoInfo &topo, uint64_t cclBytes, std::vector<ChunkPlan> *out);
 // Broadcast, Reduce and Scatter on two levels; one plan per chunk of the message that fits the scratch.
 HcclResult GenSequenceRootedPlans(const OpParam &p, const TopoInfo &topo, uint64_t cclBytes, std::vector<Plan> *plans);
 // Two-level plan with both levels busy at once (parallel_executor.cc); slices = the planner's decision, if asked for.

@@ -321,3 +321,16 @@ def test_messages_larger_than_the_scratch_run_in_chunks(topo, family, monkeypatc
         assert np.array_equal(g, want_ag), r
         assert np.array_equal(s.astype(np.float64), want_rs[r * c_blk:(r + 1) * c_blk]), r
 
+
+
+@pytest.mark.parametrize("topo", [(1, 2, 4), (1, 3, 2), (2, 2, 2)])
+def test_chunked_multi_level_plans_pass_the_schedule_checker(topo):
+    """96 KB of scratch per half: the checker gets the same pieces the executors run (the largest whose plan fits, found by halving) and
+    verifies them together against the whole call, so the block stride of the AllGather / ReduceScatter pieces is checked symbolically."""
+    for op, count in (("ALLREDUCE", 100_001), ("ALLGATHER", 17_001), ("REDUCE_SCATTER", 17_001)):
+        for family in ("Sequence", "Parallel"):
+            alg = {"ALLREDUCE": {"Sequence": "InsAllReduceSequenceMesh1DNhr", "Parallel": "InsAllReduceParallelMesh1DMesh1D"},
+                   "ALLGATHER": {"Sequence": "InsAllGatherSequenceNhrMesh1D", "Parallel": "InsAllGatherParallelMesh1DMesh1D"},
+                   "REDUCE_SCATTER": {"Sequence": "InsReduceScatterSequenceMesh1DNhr", "Parallel": "InsReduceScatterParallelMesh1DMesh1D"}}[op][family]
+            rc, msg = check(op, alg, topo, count, ccl=96 << 10)
+            assert rc == 0, (op, alg, msg)

@@ -645,33 +645,28 @@ template <class Gen>
 static HcclResult GenMultiLevelChunks(const OpParam &p, uint64_t cclBytes, Gen gen, std::vector<ChunkPlan> *out)
 {
     out->clear();
+    // per: the size that fitted last. A later piece may have to be smaller still (the parallel planner cuts a short tail into fewer,
+    // larger steps), so every piece is tried on its own.
     uint64_t per = p.count;
-    std::shared_ptr<Plan> first;
-    for (;;) {
-        OpParam q = p;
-        q.count = per;
-        q.blockStride = p.count;
-        auto plan = std::make_shared<Plan>();
-        LogPushMute();                             // "does not fit" is an answer here, not an error
-        HcclResult r = gen(q, plan.get());
-        LogPopMute();
-        if (r == HCCL_SUCCESS) { first = plan; break; }
-        if (r != HCCL_E_MEMORY || per <= 1024) {
-            if (r == HCCL_E_MEMORY) HCCL_ERROR("%s: not even 1024 elements fit the scratch of %llu bytes (raise HCCL_BUFFSIZE)", p.algName.c_str(), (unsigned long long)cclBytes);
-            return r;
+    for (uint64_t lo = 0; lo < p.count;) {
+        uint64_t cnt = std::min(per, p.count - lo);
+        for (;;) {
+            OpParam q = p;
+            q.count = cnt;
+            q.blockStride = p.count;
+            auto plan = std::make_shared<Plan>();
+            LogPushMute();                         // "does not fit" is an answer here, not an error
+            HcclResult r = gen(q, plan.get());
+            LogPopMute();
+            if (r == HCCL_SUCCESS) { out->push_back(ChunkPlan{lo, cnt, plan}); break; }
+            if (r != HCCL_E_MEMORY || cnt <= 1024) {
+                if (r == HCCL_E_MEMORY) HCCL_ERROR("%s: not even 1024 elements fit the scratch of %llu bytes (raise HCCL_BUFFSIZE)", p.algName.c_str(), (unsigned long long)cclBytes);
+                return r;
+            }
+            cnt = (cnt / 2 + 127) / 128 * 128;
         }
-        per = (per / 2 + 127) / 128 * 128;
-    }
-    for (uint64_t lo = 0; lo < p.count; lo += per) {
-        OpParam q = p;
-        q.count = std::min(per, p.count - lo);
-        q.blockStride = p.count;
-        std::shared_ptr<Plan> plan = first;
-        if (lo != 0 || q.count != per) {
-            plan = std::make_shared<Plan>();
-            CHK_RET(gen(q, plan.get()));
-        }
-        out->push_back(ChunkPlan{lo, q.count, plan});
+        per = cnt;
+        lo += cnt;
     }
     return HCCL_SUCCESS;
 }

@@ -128,7 +128,10 @@ def test_parallel_plans_over_random_layouts_and_counts():
 
 
 def test_parallel_plan_reports_a_scratch_window_that_is_too_small():
-    rc, msg = check("ALLGATHER", "InsAllGatherParallelMesh1DMesh1D", (1, 2, 4), 300_000, ccl=1 << 20)
+    """A call larger than the scratch is cut into pieces; a scratch that cannot hold a piece of 1024 elements is reported."""
+    rc, msg = check("ALLGATHER", "InsAllGatherParallelMesh1DMesh1D", (1, 2, 4), 100_000, ccl=1 << 20)
+    assert rc == 0, msg
+    rc, msg = check("ALLGATHER", "InsAllGatherParallelMesh1DMesh1D", (1, 2, 4), 100_000, ccl=2 << 10)
     assert rc != 0
 
 

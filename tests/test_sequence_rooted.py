@@ -344,3 +344,57 @@ def test_sub_communicators_keep_the_placement_of_their_ranks(groups, levels, mon
         assert np.array_equal(gathered, np.concatenate([xs[r] for r in g]))
         k, m = g.index(rank), c // len(g)
         assert np.array_equal(s.astype(np.float64), total[k * m:(k + 1) * m])
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_random_layouts_sizes_roots_and_scratch_sizes(seed, monkeypatch):
+    """Six operators on a layout, message size, root, bandwidth weighting and scratch size drawn from the seed; whatever executor the
+    selector picks (sequence, parallel, column or spread form, whole or in pieces) has to give the exact result."""
+    import random
+    rnd = random.Random(seed)
+    topo = rnd.choice(["1x2x2", "1x2x3", "1x3x2", "1x2x4", "2x2x2", "1x4x2", "2x1x3", "3x1x2"])
+    bw = rnd.choice(["", "@2,1", "@1,2", "@0.5,0.5", "@5,1"])
+    pods, servers, per = (int(v) for v in topo.split("x"))
+    n = pods * servers * per
+    buf = rnd.choice([1, 2, 4, 16])
+    c = rnd.choice([1, 2, n - 1, n, n + 1, 1000, 4097, 65_537, 200_003, 500_009])
+    cb = max(1, c // rnd.choice([1, 3, 7]))
+    root = rnd.randrange(n)
+    monkeypatch.setenv("HCCL_SIM_TOPO", topo + bw)
+    lib().HcclResetEnvConfigForTest()
+    rng = np.random.default_rng(seed)
+    xs = [rng.integers(-8, 9, size=c).astype(np.float32) for _ in range(n)]
+    blk = [rng.integers(-8, 9, size=cb).astype(np.float32) for _ in range(n)]
+    blkn = [rng.integers(-8, 9, size=cb * n).astype(np.float32) for _ in range(n)]
+
+    def body(comm, rank):
+        a = xs[rank].copy()
+        comm.all_reduce(a)
+        g = np.empty(cb * n, np.float32)
+        comm.all_gather(blk[rank], g)
+        s = np.empty(cb, np.float32)
+        comm.reduce_scatter(blkn[rank], s)
+        b = xs[root].copy() if rank == root else np.zeros(c, np.float32)
+        comm.broadcast(b, root)
+        r = np.zeros(c, np.float32)
+        comm.reduce(xs[rank], r, root)
+        sc = np.zeros(cb, np.float32)
+        comm.scatter(blkn[root], sc, root)
+        comm.synchronize()
+        return a, g, s, b, r, sc
+
+    try:
+        res = run_ranks(n, body, buffer_mb=buf)
+    finally:
+        monkeypatch.delenv("HCCL_SIM_TOPO")
+        lib().HcclResetEnvConfigForTest()
+    total = np.sum(np.stack(xs).astype(np.float64), axis=0)
+    total_blk = np.sum(np.stack(blkn).astype(np.float64), axis=0)
+    what = (topo + bw, buf, c, cb, root)
+    for rank, (a, g, s, b, r, sc) in enumerate(res):
+        assert np.array_equal(a.astype(np.float64), total), what
+        assert np.array_equal(g, np.concatenate(blk)), what
+        assert np.array_equal(s.astype(np.float64), total_blk[rank * cb:(rank + 1) * cb]), what
+        assert np.array_equal(b, xs[root]), what
+        assert rank != root or np.array_equal(r.astype(np.float64), total), what
+        assert np.array_equal(sc, blkn[root][rank * cb:(rank + 1) * cb]), what

@@ -235,9 +235,12 @@ HcclResult CommCreate(uint32_t nranks, const HcclRootInfo *info, uint32_t rank, 
                 me.hostHash = 0x9e3779b97f4a7c15ull * (server + 1);
                 me.serverId = server;
                 me.superPodId = server / servers;
-            } else {
-                HCCL_ERROR("HCCL_SIM_TOPO=%s does not describe %u ranks (want <pods>x<servers>x<ranks per server>)", e, nranks);
+            } else if (sscanf(e, "%ux%ux%u", &pods, &servers, &per) != 3 || per == 0) {
+                HCCL_ERROR("HCCL_SIM_TOPO=%s: want <pods>x<servers>x<ranks per server>", e);
                 return HCCL_E_PARA;
+            } else {
+                // a communicator of another size made beside the one the variable describes (a process group's sub-group, for instance)
+                HCCL_WARNING("HCCL_SIM_TOPO=%s describes %u ranks, this communicator has %u: laid out on one server", e, pods * servers * per, nranks);
             }
         }
     std::vector<RankDesc> all(nranks);

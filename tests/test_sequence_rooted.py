@@ -398,3 +398,27 @@ def test_random_layouts_sizes_roots_and_scratch_sizes(seed, monkeypatch):
         assert np.array_equal(b, xs[root]), what
         assert rank != root or np.array_equal(r.astype(np.float64), total), what
         assert np.array_equal(sc, blkn[root][rank * cb:(rank + 1) * cb]), what
+
+
+def test_layout_description_of_another_size_is_ignored_with_a_warning_and_a_malformed_one_refused(monkeypatch):
+    """HCCL_SIM_TOPO describes one communicator size; communicators of another size made beside it (a process group's sub-group, say)
+    run on one pretended server. A value that is not <pods>x<servers>x<ranks> fails communicator creation."""
+    from hccl_b200._lib import HcclError
+    monkeypatch.setenv("HCCL_SIM_TOPO", "1x2x2")
+    lib().HcclResetEnvConfigForTest()
+
+    def body(comm, rank):
+        x = np.full(10, rank + 1.0, np.float32)
+        comm.all_reduce(x)
+        comm.synchronize()
+        return x[0], comm.last_algorithm()
+
+    try:
+        assert all(v == 6.0 and "Sequence" not in alg for v, alg in run_ranks(3, body))
+        assert all(v == 10.0 and "Sequence" in alg for v, alg in run_ranks(4, body))
+        monkeypatch.setenv("HCCL_SIM_TOPO", "banana")
+        with pytest.raises(HcclError):
+            run_ranks(2, body)
+    finally:
+        monkeypatch.delenv("HCCL_SIM_TOPO")
+        lib().HcclResetEnvConfigForTest()

@@ -346,13 +346,13 @@ def test_sub_communicators_keep_the_placement_of_their_ranks(groups, levels, mon
         assert np.array_equal(s.astype(np.float64), total[k * m:(k + 1) * m])
 
 
-@pytest.mark.parametrize("seed", range(24))
+@pytest.mark.parametrize("seed", range(32))
 def test_random_layouts_sizes_roots_and_scratch_sizes(seed, monkeypatch):
     """Six operators on a layout, message size, root, bandwidth weighting and scratch size drawn from the seed; whatever executor the
     selector picks (sequence, parallel, column or spread form, whole or in pieces) has to give the exact result."""
     import random
     rnd = random.Random(seed)
-    topo = rnd.choice(["1x2x2", "1x2x3", "1x3x2", "1x2x4", "2x2x2", "1x4x2", "2x1x3", "3x1x2"])
+    topo = rnd.choice(["1x2x2", "1x2x3", "1x3x2", "1x2x4", "2x2x2", "1x4x2", "2x1x3", "3x1x2", "1x3x1", "2x2x1", "4x1x1"])
     bw = rnd.choice(["", "@2,1", "@1,2", "@0.5,0.5", "@5,1"])
     pods, servers, per = (int(v) for v in topo.split("x"))
     n = pods * servers * per

@@ -67,3 +67,10 @@ def test_api_index_lists_exactly_the_functions_the_headers_declare():
         assert declared == listed - ({"HcclMemAlloc"} if header.name != "hccl_res.h" else set()), (header.name, sorted(declared ^ listed))
         for name in declared:
             assert hasattr(l, name), name                       # and the library exports every one of them
+
+
+def test_testing_page_names_every_test_file_and_only_existing_ones():
+    text = (DOCS / "testing.md").read_text()
+    cited = set(re.findall(r"`(test_[a-z0-9_]+\.py)`", text))
+    existing = {p.name for p in (ROOT / "tests").glob("test_*.py")}
+    assert cited == existing, (sorted(cited - existing), sorted(existing - cited))

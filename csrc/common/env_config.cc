@@ -1,4 +1,7 @@
 #include "env_config.h"
+#include <arpa/inet.h>
+#include <ifaddrs.h>
+#include <netinet/in.h>
 #include <algorithm>
 #include <cstdlib>
 #include <mutex>
@@ -324,6 +327,35 @@ HcclResult ParseSplitRatio(const std::string &v, AlgEnvConfig *cfg)
     return HCCL_SUCCESS;
 }
 
+// The four forms of HCCL_SOCKET_IFNAME: "eth,enp" interfaces whose name starts with one of the prefixes; "=eth0,enp0" exactly these names;
+// "^eth" / "^=eth0" everything but. The first matching interface with an IPv4 address, in name order, is taken.
+bool ResolveSocketIfName(const std::string &spec, std::string *ip, std::string *ifName)
+{
+    std::string v = Trim(spec);
+    bool exclude = false, exact = false;
+    if (!v.empty() && v[0] == '^') { exclude = true; v = v.substr(1); }
+    if (!v.empty() && v[0] == '=') { exact = true; v = v.substr(1); }
+    std::vector<std::string> names;
+    for (const std::string &part : Split(v, ',')) if (!Trim(part).empty()) names.push_back(Trim(part));
+    if (names.empty()) return false;
+    struct ifaddrs *list = nullptr;
+    if (getifaddrs(&list) != 0) return false;
+    std::map<std::string, std::string> found;            // name -> first IPv4 address, in name order
+    for (struct ifaddrs *it = list; it; it = it->ifa_next) {
+        if (!it->ifa_addr || it->ifa_addr->sa_family != AF_INET || !it->ifa_name) continue;
+        char buf[INET_ADDRSTRLEN];
+        if (!inet_ntop(AF_INET, &((struct sockaddr_in *)it->ifa_addr)->sin_addr, buf, sizeof(buf))) continue;
+        found.emplace(it->ifa_name, buf);
+    }
+    freeifaddrs(list);
+    for (auto &kv : found) {
+        bool match = false;
+        for (const std::string &n : names) match = match || (exact ? kv.first == n : kv.first.compare(0, n.size(), n) == 0);
+        if (match != exclude) { *ip = kv.second; if (ifName) *ifName = kv.first; return true; }
+    }
+    return false;
+}
+
 HcclResult InitEnvConfig()
 {
     std::lock_guard<std::mutex> lk(g_mu);
@@ -371,8 +403,20 @@ HcclResult InitEnvConfig()
     if (cfg.intraRoceEnable) HCCL_WARNING("HCCL_INTRA_ROCE_ENABLE is ignored on this hardware: ranks of one server are connected by NVLink only");
     if (cfg.intraPcieEnable) HCCL_WARNING("HCCL_INTRA_PCIE_ENABLE is ignored on this hardware: ranks of one server are connected by NVLink only");
     if (cfg.interHccsDisable) HCCL_WARNING("HCCL_INTER_HCCS_DISABLE is ignored on this hardware: there is no inter-server HCCS plane to switch off");
-    if (const char *e = getenv("HCCL_IF_IP")) if (*e) cfg.ifIp = e;
     if (const char *e = getenv("HCCL_SOCKET_IFNAME")) if (*e) cfg.socketIfName = e;
+    // HCCL_SOCKET_IFNAME names the interface whose IPv4 address the bootstrap listener binds; HCCL_IF_IP, when set, wins
+    // (reference: docs/zh/user_guide/hccl_env/HCCL_SOCKET_IFNAME.md)
+    if (!cfg.socketIfName.empty()) {
+        std::string ip, name;
+        if (ResolveSocketIfName(cfg.socketIfName, &ip, &name)) {
+            cfg.ifIp = ip;
+            HCCL_RUN_INFO("HCCL_SOCKET_IFNAME=%s: interface %s, address %s", cfg.socketIfName.c_str(), name.c_str(), ip.c_str());
+        } else {
+            HCCL_ERROR("[EI0001] HCCL_SOCKET_IFNAME=%s matches no interface with an IPv4 address", cfg.socketIfName.c_str());
+            return HCCL_E_PARA;
+        }
+    }
+    if (const char *e = getenv("HCCL_IF_IP")) if (*e) cfg.ifIp = e;
     if (const char *e = getenv("HCCL_TUNING_FILE")) if (*e) cfg.tuningFile = e;
     if (cfg.execTimeoutSet && cfg.execTimeoutSec != 0 && (uint64_t)cfg.execTimeoutSec * 1000 < cfg.deviceWaitTimeoutMs)
         cfg.deviceWaitTimeoutMs = cfg.execTimeoutSec * 1000;

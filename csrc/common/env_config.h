@@ -67,6 +67,8 @@ struct AlgEnvConfig {
 HcclResult InitEnvConfig();                     // idempotent; parses once
 const AlgEnvConfig &GetEnvConfig();
 void ResetAlgEnvConfigInitState();              // tests: force re-parse on the next InitEnvConfig
+// Address of the interface HCCL_SOCKET_IFNAME selects (false: none matches).
+bool ResolveSocketIfName(const std::string &spec, std::string *ip, std::string *ifName);
 // Individual parsers (exposed for unit tests)
 HcclResult ParseExpansionMode(const std::string &v, AlgEnvConfig *cfg);
 HcclResult ParseHcclAlgo(const std::string &v, AlgEnvConfig *cfg);

@@ -13,7 +13,7 @@ from hccl_b200.types import Result
 ALL_VARS = ["HCCL_OP_EXPANSION_MODE", "HCCL_ALGO", "HCCL_ALGO_NAME", "HCCL_DETERMINISTIC", "HCCL_EXEC_TIMEOUT", "HCCL_DFS_CONFIG",
             "HCCL_OP_RETRY_ENABLE", "HCCL_OP_RETRY_PARAMS", "HCCL_BUFFSIZE", "HCCL_ALG_MULTIPLE_DIMENSION_SPLIT_RATIO", "HCCL_NVLS_ENABLE",
             "HCCL_MAX_CTAS", "HCCL_DEVICE_WAIT_TIMEOUT_MS", "HCCL_CONNECT_TIMEOUT", "HCCL_IF_BASE_PORT", "HCCL_IF_IP", "HCCL_TUNING_FILE",
-            "HCCL_ENTRY_LOG_ENABLE"]
+            "HCCL_ENTRY_LOG_ENABLE", "HCCL_SOCKET_IFNAME"]
 
 
 @pytest.fixture(autouse=True)
@@ -149,3 +149,25 @@ def test_bad_environment_fails_communicator_creation(monkeypatch):
     with pytest.raises(HcclError) as e:
         Communicator.from_root_info(1, get_root_info(), 0, backend="sim")
     assert e.value.code == Result.E_PARA
+
+
+def test_socket_ifname_selects_the_bootstrap_address(monkeypatch):
+    """The four forms of the reference (prefix list, '=' exact names, '^' everything but); HCCL_IF_IP wins over it; a value that matches
+    no interface with an IPv4 address is refused. The loopback interface exists everywhere, so it is what the cases name."""
+    for spec in ("lo", "=lo", "nosuchprefix,lo", "^=nosuchname"):
+        monkeypatch.setenv("HCCL_SOCKET_IFNAME", spec)
+        rc, d = describe()
+        assert rc == 0, spec
+        if "nosuchname" not in spec:
+            assert d["ifIp"] == "127.0.0.1", (spec, d["ifIp"])
+        else:
+            assert d["ifIp"].count(".") == 3
+    monkeypatch.setenv("HCCL_SOCKET_IFNAME", "=lo")
+    monkeypatch.setenv("HCCL_IF_IP", "10.1.2.3")
+    rc, d = describe()
+    assert rc == 0 and d["ifIp"] == "10.1.2.3"
+    monkeypatch.delenv("HCCL_IF_IP")
+    for spec in ("=nosuchname", "nosuchprefix", "^", "="):
+        monkeypatch.setenv("HCCL_SOCKET_IFNAME", spec)
+        rc, _ = describe()
+        assert rc == Result.E_PARA, spec

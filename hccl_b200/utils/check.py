@@ -120,8 +120,8 @@ def main(argv=None) -> int:
     bad = 0
     for name in names:
         rc, msg = check_algorithm(op, name, topo, a.count, DTYPES[a.dtype], a.root, matrix, ccl)
-        if a.all and rc == 5:                     # not supported on this topology (multi-level forms on one server and the like)
-            print(f"skipped: {name} does not apply to {topo[0]}x{topo[1]}x{topo[2]}")
+        if a.all and rc == 5:                     # not supported: a multi-level form on one server, a count the switch path cannot align, ...
+            print(f"skipped: {name} does not serve this call (layout {topo[0]}x{topo[1]}x{topo[2]}, count {a.count})")
             continue
         print(("ok: " if rc == 0 else f"FAILED ({rc}): ") + (msg or str(name)))
         bad += rc != 0
